@@ -1,0 +1,386 @@
+// CPU oracle for the CP-HNSW hot path.  TEST INFRASTRUCTURE ONLY.
+//
+// This file restates, on the CPU and in the plainest possible form, the arithmetic
+// of the reference project's encode -> code distance -> kNN graph -> select_neighbors
+// -> beam search -> rerank path.  It exists so that the CUDA library can be checked
+// against it; nothing in the product links, loads or calls it.  Only the test-suite,
+// the smoke check and the CPU-baseline leg of the benchmark may load this library.
+//
+// Parity status: the FHT, the sign tables, the rotation and the K-byte code are pinned
+// against the reference's own headers compiled in place (see ref_shim.cpp and the golden
+// fixtures).  Code distance, kNN lists, select_neighbors, beam search, rerank and
+// multiprobe follow call sites and papers only, because the reference's legacy sources
+// for them are absent from its tree: for those functions parity is UNPINNED by any
+// reference-side golden vector.
+//
+// Every function cites the reference file:line it follows (paths relative to the
+// reference project root).
+//
+// Build: g++ -O2 -fopenmp -ffp-contract=off -shared -fPIC (see Makefile).  Contraction is
+// off so that every float add below is a single IEEE operation in program order.
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <queue>
+#include <random>
+#include <set>
+#include <utility>
+#include <vector>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+constexpr uint32_t kInvalid = 0xFFFFFFFFu;  // include/cphnsw/core/types.hpp:28-30 (INVALID_NODE)
+
+size_t next_pow2(size_t n) {  // include/cphnsw/encoder/rotation.hpp:128-132
+    size_t p = 1;
+    while (p < n) p *= 2;
+    return p;
+}
+
+// include/cphnsw/encoder/transform/fht.hpp:56-69 (fht_scalar): stages h = 1, 2, 4, ...;
+// each butterfly writes lo = x + y, hi = x - y.
+void fht_scalar(float* v, size_t n) {
+    for (size_t h = 1; h < n; h *= 2)
+        for (size_t i = 0; i < n; i += 2 * h)
+            for (size_t j = i; j < i + h; ++j) {
+                float x = v[j], y = v[j + h];
+                v[j] = x + y;
+                v[j + h] = x - y;
+            }
+}
+
+// Width of the in-register phase the reference's SIMD FHT runs for a given build and length.
+// fht.hpp:141-147: the AVX-512 routine defers to AVX2 below 16; fht.hpp:81-87: AVX2 defers
+// to scalar below 8.  convention: 0 scalar build, 1 AVX2 build, 2 AVX-512 build.
+size_t simd_width(int convention, size_t n) {
+    if (convention == 2 && n >= 16) return 16;
+    if (convention >= 1 && n >= 8) return 8;
+    return 1;
+}
+
+// The reference's SIMD FHT.  Its in-register stages (fht.hpp:96-111 for AVX2, :155-180 for
+// AVX-512) blend `v - v_swap` into the upper lane of each pair, i.e. hi = y - x, where the
+// scalar butterfly writes x - y.  Every later stage only adds or subtracts whole values, so
+// the result equals the scalar transform with element i negated when popcount(i & (W-1))
+// is odd; magnitudes are bit-equal.
+void fht_convention(float* v, size_t n, int convention) {
+    fht_scalar(v, n);
+    size_t w = simd_width(convention, n);
+    if (w > 1)
+        for (size_t i = 0; i < n; ++i)
+            if (__builtin_popcountll(i & (w - 1)) & 1) v[i] = -v[i];
+}
+
+// include/cphnsw/encoder/rotation.hpp:90-111 (apply_copy + apply): zero-pad, then three times
+// (multiply by the +-1 diagonal, FHT).
+void rotate(const float* x, size_t dim, size_t P, const int8_t* signs /*[3][P]*/, int convention,
+            float* buf) {
+    std::memcpy(buf, x, dim * sizeof(float));
+    std::memset(buf + dim, 0, (P - dim) * sizeof(float));
+    for (int layer = 0; layer < 3; ++layer) {
+        const int8_t* s = signs + (size_t)layer * P;
+        for (size_t i = 0; i < P; ++i) buf[i] *= static_cast<float>(s[i]);  // rotation.hpp:146-150
+        fht_convention(buf, P, convention);
+    }
+}
+
+// include/cphnsw/encoder/cp_encoder.hpp:78-91 (scalar form; the AVX-512 form at :27-76 returns
+// the same index: first position whose magnitude equals the maximum).
+void argmax_abs(const float* b, size_t n, size_t& idx, float& mag) {
+    idx = 0;
+    mag = 0.0f;
+    for (size_t i = 0; i < n; ++i) {
+        float a = std::fabs(b[i]);
+        if (a > mag) {
+            mag = a;
+            idx = i;
+        }
+    }
+}
+
+// include/cphnsw/core/types.hpp:88-90 (CPCode::encode): component = (index << 1) | negative.
+inline uint32_t component(size_t idx, bool neg) { return (uint32_t)((idx << 1) | (neg ? 1 : 0)); }
+
+inline uint32_t load_comp(const void* codes, size_t comp_bytes, size_t i) {
+    return comp_bytes == 1 ? ((const uint8_t*)codes)[i] : ((const uint16_t*)codes)[i];
+}
+inline void store_comp(void* codes, size_t comp_bytes, size_t i, uint32_t c) {
+    if (comp_bytes == 1)
+        ((uint8_t*)codes)[i] = (uint8_t)c;
+    else
+        ((uint16_t*)codes)[i] = (uint16_t)c;
+}
+
+// Legacy hamming_distance(CPCode, CPCode): number of the K components that differ
+// (use sites: evaluation/debug_estimator.cpp:149,172; evaluation/debug_code_storage.cpp:81).
+inline uint32_t code_dist(const void* a, size_t ia, const void* b, size_t ib, size_t K,
+                          size_t comp_bytes) {
+    uint32_t d = 0;
+    for (size_t r = 0; r < K; ++r)
+        d += load_comp(a, comp_bytes, ia * K + r) != load_comp(b, comp_bytes, ib * K + r);
+    return d;
+}
+
+// Legacy asymmetric_search_distance(CPQuery, CPCode), restated by hand in the reference at
+// evaluation/debug_estimator.cpp:47-55: score += neg ? -val : val over r = 0..K-1, distance = -score.
+inline float asym_dist(const float* table /*[K][P]*/, size_t K, size_t P, const void* codes,
+                       size_t comp_bytes, size_t id) {
+    float score = 0.0f;
+    for (size_t r = 0; r < K; ++r) {
+        uint32_t c = load_comp(codes, comp_bytes, id * K + r);
+        float val = table[r * P + (c >> 1)];
+        score += (c & 1) ? -val : val;
+    }
+    return -score;
+}
+
+using Cand = std::pair<float, uint32_t>;  // total order (distance, id)
+
+}  // namespace
+
+extern "C" {
+
+// include/cphnsw/encoder/rotation.hpp:134-144 (generate_signs) and :173-178 (rotation r is
+// seeded base_seed + r): mt19937_64(seed), uniform_int_distribution<int>(0,1), layer-major draws.
+// Output int8 [K][3][P].
+int orc_sign_tables(uint64_t dim, uint64_t K, uint64_t seed, int8_t* out) {
+    size_t P = next_pow2(dim);
+    for (size_t r = 0; r < K; ++r) {
+        std::mt19937_64 rng(seed + r);
+        std::uniform_int_distribution<int> coin(0, 1);
+        for (int layer = 0; layer < 3; ++layer)
+            for (size_t i = 0; i < P; ++i) out[(r * 3 + layer) * P + i] = coin(rng) ? 1 : -1;
+    }
+    return 0;
+}
+
+int orc_fht(float* v, uint64_t n, int convention) {
+    fht_convention(v, n, convention);
+    return 0;
+}
+
+// Legacy CPEncoder<ComponentT,K>::encode (absent); loop structure from
+// include/cphnsw/encoder/cp_encoder.hpp:161-184, byte format from types.hpp:88-90 and
+// src/cuda/gpu_encoder.cu:214-218.  Sign test `buffer[idx] < 0` (cp_encoder.hpp:174).
+// Optional outputs: rotated [n][K][P], magnitudes [n][K] (CPQuery, types.hpp:324-337).
+int orc_encode(const float* x, uint64_t n, uint64_t dim, uint64_t K, uint64_t comp_bytes,
+               const int8_t* signs, int convention, void* codes, float* rotated, float* magnitudes) {
+    size_t P = next_pow2(dim);
+#pragma omp parallel
+    {
+        std::vector<float> buf(P);
+#pragma omp for schedule(static)
+        for (int64_t i = 0; i < (int64_t)n; ++i)
+            for (size_t r = 0; r < K; ++r) {
+                rotate(x + (size_t)i * dim, dim, P, signs + r * 3 * P, convention, buf.data());
+                size_t idx;
+                float mag;
+                argmax_abs(buf.data(), P, idx, mag);
+                store_comp(codes, comp_bytes, (size_t)i * K + r, component(idx, buf[idx] < 0));
+                if (rotated) std::memcpy(rotated + ((size_t)i * K + r) * P, buf.data(), P * sizeof(float));
+                if (magnitudes) magnitudes[(size_t)i * K + r] = mag;
+            }
+    }
+    return 0;
+}
+
+// All-pairs code distance, out[na][nb] uint16 (HammingDist, types.hpp:35).
+int orc_code_distance(const void* a, uint64_t na, const void* b, uint64_t nb, uint64_t K,
+                      uint64_t comp_bytes, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)na; ++i)
+        for (size_t j = 0; j < nb; ++j)
+            out[(size_t)i * nb + j] = (uint16_t)code_dist(a, i, b, j, K, comp_bytes);
+    return 0;
+}
+
+// Brute-force code-distance kNN rows [row_begin,row_end) against all n codes: self excluded,
+// k smallest under (distance, id); rows with fewer than k candidates are padded with
+// 0xFFFFFFFF / 0xFFFF (padding convention of src/cuda/gpu_knn_graph.cu:154-181).
+int orc_knn_graph(const void* codes, uint64_t n, uint64_t K, uint64_t comp_bytes, uint64_t k,
+                  uint64_t row_begin, uint64_t row_end, uint32_t* nbrs, uint16_t* dists) {
+#pragma omp parallel
+    {
+        std::vector<std::pair<uint32_t, uint32_t>> best;  // (dist, id) ascending, size <= k
+#pragma omp for schedule(dynamic, 16)
+        for (int64_t i = (int64_t)row_begin; i < (int64_t)row_end; ++i) {
+            best.clear();
+            for (size_t j = 0; j < n; ++j) {
+                if ((size_t)i == j) continue;
+                uint32_t d = code_dist(codes, i, codes, j, K, comp_bytes);
+                // j ascends, so a later id never displaces an equal distance
+                if (best.size() == k && d >= best.back().first) continue;
+                auto it = std::upper_bound(best.begin(), best.end(), std::make_pair(d, (uint32_t)j));
+                best.insert(it, {d, (uint32_t)j});
+                if (best.size() > k) best.pop_back();
+            }
+            size_t o = ((size_t)i - row_begin) * k;
+            for (size_t t = 0; t < k; ++t) {
+                nbrs[o + t] = t < best.size() ? best[t].second : kInvalid;
+                if (dists) dists[o + t] = t < best.size() ? (uint16_t)best[t].first : (uint16_t)0xFFFF;
+            }
+        }
+    }
+    return 0;
+}
+
+// SELECT-NEIGHBORS-HEURISTIC with keepPrunedConnections
+// (resources/hnsw-paper/consolidated.tex:93-115; flag default types.hpp:390-391).
+// Candidates of row i are cand[i][0..k) in the order given (ascending (distance,id) from the
+// kNN build); "closer" is strict < on the integer code distance.  Output adj[rows][M].
+int orc_select_neighbors(const void* codes, uint64_t n, uint64_t K, uint64_t comp_bytes,
+                         const uint32_t* cand, uint64_t k, uint64_t M, int keep_pruned,
+                         uint64_t row_begin, uint64_t row_end, uint32_t* adj) {
+    (void)n;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = (int64_t)row_begin; i < (int64_t)row_end; ++i) {
+        const uint32_t* c = cand + ((size_t)i - row_begin) * k;
+        uint32_t* out = adj + ((size_t)i - row_begin) * M;
+        std::vector<uint32_t> R, Wd;
+        for (size_t t = 0; t < k && R.size() < M; ++t) {
+            uint32_t e = c[t];
+            if (e == kInvalid) continue;
+            uint32_t d_eq = code_dist(codes, e, codes, i, K, comp_bytes);
+            bool keep = true;
+            for (uint32_t r : R)
+                if (!(d_eq < code_dist(codes, e, codes, r, K, comp_bytes))) {
+                    keep = false;
+                    break;
+                }
+            (keep ? R : Wd).push_back(e);
+        }
+        if (keep_pruned)
+            for (size_t t = 0; t < Wd.size() && R.size() < M; ++t) R.push_back(Wd[t]);
+        for (size_t t = 0; t < M; ++t) out[t] = t < R.size() ? R[t] : kInvalid;
+    }
+    return 0;
+}
+
+// Beam search over a flat adjacency; control flow of
+// include/cphnsw/search/search_engine.hpp:86-193 with two declared differences:
+//  * candidates are compared under the total order (distance, id), so the result does not depend
+//    on heap insertion order (the reference compares `distance` only, types.hpp:351-357);
+//  * the best k of W are returned ascending (the reference pops the k worst, :184-190; the
+//    legacy behaviour asserted by evaluation/qa_protocol.cpp:137-165 is ascending best-k).
+// Metric: legacy asymmetric distance against the query's K rotated vectors (table).
+// All entry ids are scored and offered to W first.  W capacity is ef.
+// out_ids/out_dist are [nq][k] padded with 0xFFFFFFFF / +inf; stats[nq][2] = expansions,
+// distance evaluations (optional).
+int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint64_t P,
+               const void* codes, uint64_t comp_bytes, uint64_t n, const uint32_t* adj, uint64_t M,
+               const uint32_t* entry_ids, uint64_t n_entry, uint64_t ef, uint64_t k,
+               uint32_t* out_ids, float* out_dist, uint32_t* stats) {
+#pragma omp parallel
+    {
+        std::vector<uint8_t> visited(n);
+        std::vector<uint32_t> touched;
+#pragma omp for schedule(dynamic, 4)
+        for (int64_t q = 0; q < (int64_t)nq; ++q) {
+            const float* table = tables + (size_t)q * K * P;
+            std::set<Cand> W;  // at most ef best seen so far
+            std::set<Cand> C;  // members of W not yet expanded
+            uint32_t expansions = 0, evals = 0;
+            auto offer = [&](uint32_t id) {
+                if (id == kInvalid || id >= n || visited[id]) return;  // search_engine.hpp:154-160
+                visited[id] = 1;
+                touched.push_back(id);
+                Cand c{asym_dist(table, K, P, codes, comp_bytes, id), id};
+                ++evals;
+                if (W.size() < ef) {  // search_engine.hpp:166-176
+                    W.insert(c);
+                    C.insert(c);
+                } else if (c < *W.rbegin()) {
+                    Cand worst = *W.rbegin();
+                    W.erase(worst);
+                    C.erase(worst);
+                    W.insert(c);
+                    C.insert(c);
+                }
+            };
+            for (size_t e = 0; e < n_entry; ++e) offer(entry_ids[e]);  // :105-115
+            while (!C.empty()) {  // :118-178; C only holds members of W, so the `c > worst` break
+                Cand c = *C.begin();  // of :130-132 is the emptiness of C
+                C.erase(C.begin());
+                ++expansions;
+                const uint32_t* row = adj + (size_t)c.second * M;
+                for (size_t t = 0; t < M; ++t) offer(row[t]);
+            }
+            size_t o = (size_t)q * k, t = 0;
+            for (auto it = W.begin(); it != W.end() && t < k; ++it, ++t) {
+                out_ids[o + t] = it->second;
+                out_dist[o + t] = it->first;
+            }
+            for (; t < k; ++t) {
+                out_ids[o + t] = kInvalid;
+                out_dist[o + t] = INFINITY;
+            }
+            if (stats) {
+                stats[2 * q] = expansions;
+                stats[2 * q + 1] = evals;
+            }
+            for (uint32_t id : touched) visited[id] = 0;
+            touched.clear();
+        }
+    }
+    return 0;
+}
+
+// Exact rerank of candidate ids: distance = -<q, x_id> accumulated in d order in fp32
+// (evaluation/eval_sift.cpp:539-563), sort ascending by (distance, id), keep k.
+// cand is [nq][n_cand] (0xFFFFFFFF entries skipped).
+int orc_rerank(const float* queries, uint64_t nq, uint64_t dim, const float* base,
+               const uint32_t* cand, uint64_t n_cand, uint64_t k, uint32_t* out_ids, float* out_dist) {
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int64_t q = 0; q < (int64_t)nq; ++q) {
+        std::vector<Cand> r;
+        for (size_t t = 0; t < n_cand; ++t) {
+            uint32_t id = cand[(size_t)q * n_cand + t];
+            if (id == kInvalid) continue;
+            float dot = 0.0f;
+            for (size_t d = 0; d < dim; ++d) dot += queries[(size_t)q * dim + d] * base[(size_t)id * dim + d];
+            r.push_back({-dot, id});
+        }
+        std::sort(r.begin(), r.end());
+        for (size_t t = 0; t < k; ++t) {
+            out_ids[(size_t)q * k + t] = t < r.size() ? r[t].second : kInvalid;
+            out_dist[(size_t)q * k + t] = t < r.size() ? r[t].first : INFINITY;
+        }
+    }
+    return 0;
+}
+
+// Exact cosine ground truth for unit vectors (evaluation/datasets/dataset_loader.hpp:187-212):
+// top-k by (-dot, id).
+int orc_ground_truth(const float* queries, uint64_t nq, const float* base, uint64_t n, uint64_t dim,
+                     uint64_t k, uint32_t* out_ids) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t q = 0; q < (int64_t)nq; ++q) {
+        std::vector<Cand> best;
+        for (size_t i = 0; i < n; ++i) {
+            float dot = 0.0f;
+            for (size_t d = 0; d < dim; ++d) dot += queries[(size_t)q * dim + d] * base[i * dim + d];
+            Cand c{-dot, (uint32_t)i};
+            if (best.size() == k && !(c < best.back())) continue;
+            best.insert(std::upper_bound(best.begin(), best.end(), c), c);
+            if (best.size() > k) best.pop_back();
+        }
+        for (size_t t = 0; t < k; ++t) out_ids[(size_t)q * k + t] = t < best.size() ? best[t].second : kInvalid;
+    }
+    return 0;
+}
+
+int orc_num_threads() {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+}  // extern "C"

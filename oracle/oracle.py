@@ -1,0 +1,225 @@
+"""ctypes front-end of the CPU oracle (``liboracle.so``) and of the reference shims (``_ref/``).
+
+TEST INFRASTRUCTURE ONLY: imported by the test-suite, the smoke check and the CPU-baseline leg of
+the benchmark, never by the product package.  Each wrapper is a one-to-one call of the C function
+of the same name in ``cphnsw_oracle.cpp`` / ``ref_shim.cpp``; see those files for the reference
+file:line every function follows.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+INVALID = 0xFFFFFFFF
+FHT_SCALAR, FHT_AVX2, FHT_AVX512 = 0, 1, 2
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def next_pow2(n):
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+def _comp_dtype(comp_bytes):
+    return np.uint8 if comp_bytes == 1 else np.uint16
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            raise RuntimeError("oracle/liboracle.so missing: run `make -C oracle`")
+        _lib = C.CDLL(path)
+    return _lib
+
+
+def num_threads():
+    return lib().orc_num_threads()
+
+
+def sign_tables(dim, K, seed=42):
+    P = next_pow2(dim)
+    out = np.empty((K, 3, P), np.int8)
+    lib().orc_sign_tables(C.c_uint64(dim), C.c_uint64(K), C.c_uint64(seed), _ptr(out))
+    return out
+
+
+def fht(v, convention=FHT_SCALAR):
+    v = np.ascontiguousarray(v, np.float32).copy()
+    lib().orc_fht(_ptr(v), C.c_uint64(v.size), C.c_int(convention))
+    return v
+
+
+def encode(x, K, comp_bytes, signs, convention=FHT_AVX512, want_rotated=False):
+    x = np.ascontiguousarray(x, np.float32)
+    n, dim = x.shape
+    P = next_pow2(dim)
+    signs = np.ascontiguousarray(signs, np.int8)
+    assert signs.shape == (K, 3, P)
+    codes = np.empty((n, K), _comp_dtype(comp_bytes))
+    rot = np.empty((n, K, P), np.float32) if want_rotated else None
+    mag = np.empty((n, K), np.float32) if want_rotated else None
+    lib().orc_encode(_ptr(x), C.c_uint64(n), C.c_uint64(dim), C.c_uint64(K), C.c_uint64(comp_bytes),
+                     _ptr(signs), C.c_int(convention), _ptr(codes), _ptr(rot), _ptr(mag))
+    return (codes, rot, mag) if want_rotated else codes
+
+
+def code_distance(a, b):
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    assert a.dtype == b.dtype and a.shape[1] == b.shape[1]
+    out = np.empty((a.shape[0], b.shape[0]), np.uint16)
+    lib().orc_code_distance(_ptr(a), C.c_uint64(a.shape[0]), _ptr(b), C.c_uint64(b.shape[0]),
+                            C.c_uint64(a.shape[1]), C.c_uint64(a.dtype.itemsize), _ptr(out))
+    return out
+
+
+def knn_graph(codes, k, row_begin=0, row_end=None):
+    codes = np.ascontiguousarray(codes)
+    n, K = codes.shape
+    row_end = n if row_end is None else row_end
+    nb = np.empty((row_end - row_begin, k), np.uint32)
+    ds = np.empty((row_end - row_begin, k), np.uint16)
+    lib().orc_knn_graph(_ptr(codes), C.c_uint64(n), C.c_uint64(K), C.c_uint64(codes.dtype.itemsize),
+                        C.c_uint64(k), C.c_uint64(row_begin), C.c_uint64(row_end), _ptr(nb), _ptr(ds))
+    return nb, ds
+
+
+def select_neighbors(codes, cand, M, keep_pruned=True, row_begin=0):
+    codes = np.ascontiguousarray(codes)
+    cand = np.ascontiguousarray(cand, np.uint32)
+    n, K = codes.shape
+    rows, k = cand.shape
+    adj = np.empty((rows, M), np.uint32)
+    lib().orc_select_neighbors(_ptr(codes), C.c_uint64(n), C.c_uint64(K), C.c_uint64(codes.dtype.itemsize),
+                               _ptr(cand), C.c_uint64(k), C.c_uint64(M), C.c_int(int(keep_pruned)),
+                               C.c_uint64(row_begin), C.c_uint64(row_begin + rows), _ptr(adj))
+    return adj
+
+
+def search(tables, codes, adj, entry_ids, ef, k, want_stats=False):
+    tables = np.ascontiguousarray(tables, np.float32)
+    codes = np.ascontiguousarray(codes)
+    adj = np.ascontiguousarray(adj, np.uint32)
+    entry_ids = np.ascontiguousarray(entry_ids, np.uint32)
+    nq, K, P = tables.shape
+    n, M = adj.shape
+    ids = np.empty((nq, k), np.uint32)
+    dist = np.empty((nq, k), np.float32)
+    stats = np.zeros((nq, 2), np.uint32)
+    lib().orc_search(_ptr(tables), C.c_uint64(nq), C.c_uint64(K), C.c_uint64(P), _ptr(codes),
+                     C.c_uint64(codes.dtype.itemsize), C.c_uint64(n), _ptr(adj), C.c_uint64(M),
+                     _ptr(entry_ids), C.c_uint64(entry_ids.size), C.c_uint64(ef), C.c_uint64(k),
+                     _ptr(ids), _ptr(dist), _ptr(stats))
+    return (ids, dist, stats) if want_stats else (ids, dist)
+
+
+def rerank(queries, base, cand, k):
+    queries = np.ascontiguousarray(queries, np.float32)
+    base = np.ascontiguousarray(base, np.float32)
+    cand = np.ascontiguousarray(cand, np.uint32)
+    nq, dim = queries.shape
+    ids = np.empty((nq, k), np.uint32)
+    dist = np.empty((nq, k), np.float32)
+    lib().orc_rerank(_ptr(queries), C.c_uint64(nq), C.c_uint64(dim), _ptr(base), _ptr(cand),
+                     C.c_uint64(cand.shape[1]), C.c_uint64(k), _ptr(ids), _ptr(dist))
+    return ids, dist
+
+
+def ground_truth(queries, base, k):
+    queries = np.ascontiguousarray(queries, np.float32)
+    base = np.ascontiguousarray(base, np.float32)
+    ids = np.empty((queries.shape[0], k), np.uint32)
+    lib().orc_ground_truth(_ptr(queries), C.c_uint64(queries.shape[0]), _ptr(base),
+                           C.c_uint64(base.shape[0]), C.c_uint64(base.shape[1]), C.c_uint64(k), _ptr(ids))
+    return ids
+
+
+def recall_at_k(found, truth, k):
+    """|retrieved ∩ truth| / k averaged over queries (evaluation/metrics/recall.hpp:22-39)."""
+    hits = 0
+    for f, t in zip(found[:, :k], truth[:, :k]):
+        hits += len(set(f.tolist()) & set(t.tolist()))
+    return hits / (truth.shape[0] * k)
+
+
+# ---------------------------------------------------------------------------------------------
+# reference shims (present only where the reference checkout was available at build time)
+
+_CONV_NAME = {FHT_SCALAR: "scalar", FHT_AVX2: "avx2", FHT_AVX512: "avx512"}
+
+
+def _cpu_has(flag):
+    try:
+        with open("/proc/cpuinfo") as f:
+            return flag in f.read().split("flags", 1)[1].split("\n", 1)[0].split()
+    except Exception:
+        return False
+
+
+def ref_available(convention):
+    path = os.path.join(_HERE, "_ref", "libcphnsw_ref_%s.so" % _CONV_NAME[convention])
+    if not os.path.exists(path):
+        return False
+    need = {FHT_SCALAR: None, FHT_AVX2: "avx2", FHT_AVX512: "avx512f"}[convention]
+    return need is None or _cpu_has(need)
+
+
+class Ref:
+    """The reference's own headers compiled with the ISA flags of one convention."""
+
+    def __init__(self, convention):
+        if not ref_available(convention):
+            raise RuntimeError("reference shim for convention %d not available" % convention)
+        self.l = C.CDLL(os.path.join(_HERE, "_ref", "libcphnsw_ref_%s.so" % _CONV_NAME[convention]))
+        assert self.l.ref_convention() == convention
+
+    def fht(self, v):
+        v = np.ascontiguousarray(v, np.float32).copy()
+        self.l.ref_fht(_ptr(v), C.c_uint64(v.size))
+        return v
+
+    def fht_scalar(self, v):
+        v = np.ascontiguousarray(v, np.float32).copy()
+        self.l.ref_fht_scalar(_ptr(v), C.c_uint64(v.size))
+        return v
+
+    def sign_tables(self, dim, K, seed=42):
+        out = np.empty((K, 3, next_pow2(dim)), np.int8)
+        self.l.ref_sign_tables(C.c_uint64(dim), C.c_uint64(K), C.c_uint64(seed), _ptr(out))
+        return out
+
+    def argmax_abs(self, v):
+        v = np.ascontiguousarray(v, np.float32)
+        idx = C.c_uint64()
+        mag = C.c_float()
+        self.l.ref_argmax_abs(_ptr(v), C.c_uint64(v.size), C.byref(idx), C.byref(mag))
+        return idx.value, mag.value
+
+    def encode(self, x, K, comp_bytes, seed=42, want_rotated=False):
+        x = np.ascontiguousarray(x, np.float32)
+        n, dim = x.shape
+        P = next_pow2(dim)
+        codes = np.empty((n, K), _comp_dtype(comp_bytes))
+        rot = np.empty((n, K, P), np.float32) if want_rotated else None
+        mag = np.empty((n, K), np.float32) if want_rotated else None
+        self.l.ref_encode(_ptr(x), C.c_uint64(n), C.c_uint64(dim), C.c_uint64(K), C.c_uint64(comp_bytes),
+                          C.c_uint64(seed), _ptr(codes), _ptr(rot), _ptr(mag))
+        return (codes, rot, mag) if want_rotated else codes
+
+    def encode_batch_signbits32(self, x, seed=42):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[0], np.uint32)
+        self.l.ref_encode_batch_signbits32(_ptr(x), C.c_uint64(x.shape[0]), C.c_uint64(x.shape[1]),
+                                           C.c_uint64(seed), _ptr(out))
+        return out

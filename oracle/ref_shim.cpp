@@ -1,0 +1,104 @@
+// Thin extern "C" wrapper around the REFERENCE project's own hot-path headers, compiled in
+// place from the reference checkout (-I <reference>/include).  TEST INFRASTRUCTURE ONLY.
+//
+// Nothing from the reference is copied here: this file only instantiates and calls the
+// reference's classes so that the oracle restatement (cphnsw_oracle.cpp) and the golden
+// fixtures can be validated against the real thing.  The Makefile builds it three times
+// (no -m flags, -mavx2, -mavx512f), because the reference's FHT picks its code path from the
+// compiler's ISA macros (include/cphnsw/encoder/transform/fht.hpp:7-17) and the three builds
+// produce three different sign conventions.
+//
+// The resulting libraries live in oracle/_ref/ and exist only where the reference checkout
+// is available at build time.
+
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "cphnsw/core/types.hpp"
+#include "cphnsw/encoder/cp_encoder.hpp"
+#include "cphnsw/encoder/rotation.hpp"
+#include "cphnsw/encoder/transform/fht.hpp"
+
+extern "C" {
+
+// 0 = scalar build, 1 = AVX2 build, 2 = AVX-512 build (fht.hpp:207-215 dispatch).
+int ref_convention() {
+#if CPHNSW_FHT_AVX512
+    return 2;
+#elif CPHNSW_FHT_AVX2
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+int ref_fht(float* v, uint64_t n) {
+    cphnsw::fht(v, n);
+    return 0;
+}
+
+int ref_fht_scalar(float* v, uint64_t n) {
+    cphnsw::fht_scalar(v, n);
+    return 0;
+}
+
+// int8 [K][3][P], rotation r seeded seed + r as RotationChain does (rotation.hpp:173-178).
+int ref_sign_tables(uint64_t dim, uint64_t K, uint64_t seed, int8_t* out) {
+    for (uint64_t r = 0; r < K; ++r) {
+        cphnsw::RandomHadamardRotation rot(dim, seed + r);
+        size_t P = rot.padded_dim();
+        const auto& s = rot.get_signs();
+        for (int l = 0; l < 3; ++l) std::memcpy(out + (r * 3 + l) * P, s[l].data(), P);
+    }
+    return 0;
+}
+
+int ref_argmax_abs(const float* v, uint64_t n, uint64_t* idx, float* mag) {
+    size_t i;
+    float m;
+    cphnsw::detail::find_argmax_abs(v, n, i, m);
+    *idx = i;
+    *mag = m;
+    return 0;
+}
+
+// K-component code from reference parts: RandomHadamardRotation::apply_copy (rotation.hpp:104-111),
+// detail::find_argmax_abs (cp_encoder.hpp:25-92), sign test of cp_encoder.hpp:174,
+// CPCode::encode (types.hpp:88-90).  Optional rotated [n][K][P] and magnitudes [n][K].
+int ref_encode(const float* x, uint64_t n, uint64_t dim, uint64_t K, uint64_t comp_bytes,
+               uint64_t seed, void* codes, float* rotated, float* magnitudes) {
+    std::vector<cphnsw::RandomHadamardRotation> rots;
+    for (uint64_t r = 0; r < K; ++r) rots.emplace_back(dim, seed + r);
+    size_t P = rots[0].padded_dim();
+    std::vector<float> buf(P);
+    for (uint64_t i = 0; i < n; ++i)
+        for (uint64_t r = 0; r < K; ++r) {
+            rots[r].apply_copy(x + i * dim, buf.data());
+            size_t idx;
+            float mag;
+            cphnsw::detail::find_argmax_abs(buf.data(), P, idx, mag);
+            bool neg = buf[idx] < 0;
+            if (comp_bytes == 1)
+                ((uint8_t*)codes)[i * K + r] = cphnsw::CPCode<uint8_t, 1>::encode(idx, neg);
+            else
+                ((uint16_t*)codes)[i * K + r] = cphnsw::CPCode<uint16_t, 1>::encode(idx, neg);
+            if (rotated) std::memcpy(rotated + (i * K + r) * P, buf.data(), P * sizeof(float));
+            if (magnitudes) magnitudes[i * K + r] = mag;
+        }
+    return 0;
+}
+
+// The reference's shipped encoder, unmodified: CPEncoder<32,0>::encode_batch
+// (cp_encoder.hpp:244-260).  Emits the 32 primary sign bits of each vector; it does the same
+// K x 3 FHTs + argmax per vector as the K-byte encode, so it is the timed CPU reference for
+// the encode stage and a cross-check of the sign bit of every component.
+int ref_encode_batch_signbits32(const float* x, uint64_t n, uint64_t dim, uint64_t seed, uint32_t* out) {
+    cphnsw::CPEncoder<32, 0> enc(dim, seed);
+    std::vector<cphnsw::ResidualCode<32, 0>> codes(n);
+    enc.encode_batch(x, n, codes.data());
+    for (uint64_t i = 0; i < n; ++i) out[i] = (uint32_t)codes[i].primary.signs[0];
+    return 0;
+}
+
+}  // extern "C"
