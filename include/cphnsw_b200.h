@@ -1,0 +1,173 @@
+/*
+ * cphnsw_b200 — C ABI of the B200 (sm_100a) implementation of the CP-HNSW data-parallel hot path:
+ * cross-polytope encode, CP-code distance, brute-force code-distance kNN graph, select_neighbors
+ * pruning, batched beam search and exact rerank.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative CPHNSW_B200_E_* code; nothing exits,
+ *     aborts or throws.  cphnsw_b200_last_error() gives the message of the last failure on
+ *     the calling thread.
+ *   - plain entry points take caller-owned HOST pointers (row-major, not retained) and do their
+ *     own host<->device copies, like the reference's GPU classes do
+ *     (include/cphnsw/cuda/gpu_encoder.cuh:24-93, include/cphnsw/cuda/gpu_knn_graph.cuh:28-101).
+ *   - "_dev" entry points take DEVICE pointers on the index's device and a cudaStream_t passed
+ *     as void*; they are asynchronous on that stream and allocate no output.
+ *   - a handle is bound to one CUDA device and is thread-compatible (one thread at a time).
+ *   - code layout is row-major ComponentT[n][K], component = (argmax_index << 1) | negative
+ *     (include/cphnsw/core/types.hpp:68-106).  Node ids are uint32, 0xFFFFFFFF is "no node"
+ *     (types.hpp:28-30).
+ *
+ * The library has no CPU fallback: every entry point fails with CPHNSW_B200_E_CUDA when no
+ * sm_100 device is usable.
+ */
+#ifndef CPHNSW_B200_H
+#define CPHNSW_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CPHNSW_B200_OK 0
+#define CPHNSW_B200_E_INVALID (-1)   /* bad argument (maps to std::invalid_argument, types.hpp:409-457) */
+#define CPHNSW_B200_E_CUDA (-2)      /* CUDA runtime error or no usable device */
+#define CPHNSW_B200_E_STATE (-3)     /* call not valid in the index's current state (e.g. search before build) */
+#define CPHNSW_B200_E_UNSUPPORTED (-4)
+#define CPHNSW_B200_E_DEVICE_WAIT (-5) /* a bounded device-side wait ran out; the context stays usable */
+
+/* FHT sign convention of the reference build being matched
+ * (include/cphnsw/encoder/transform/fht.hpp:56-69 scalar, :81-127 AVX2, :141-196 AVX-512). */
+#define CPHNSW_B200_FHT_SCALAR 0
+#define CPHNSW_B200_FHT_AVX2 1
+#define CPHNSW_B200_FHT_AVX512 2
+
+#define CPHNSW_B200_INVALID_NODE 0xFFFFFFFFu
+
+typedef struct cphnsw_b200_index cphnsw_b200_index;
+
+const char* cphnsw_b200_last_error(void);
+
+/* Number of usable sm_100 devices (0 when none / no driver).  Never fails. */
+int cphnsw_b200_device_count(void);
+
+/* ---- lifetime -------------------------------------------------------------------------------
+ * Replaces the constructors CPHNSWIndex(dim, M, ef_construction) / CPHNSWIndex(const CPHNSWParams&)
+ * (use sites evaluation/eval_sift.cpp:228, evaluation/test_gpu_build.cpp:155-162) and
+ * GPUEncoder(dim, seed) (include/cphnsw/cuda/gpu_encoder.cuh:34).  Parameter bounds are those of
+ * CPHNSWParams::finalize() (include/cphnsw/core/types.hpp:403-469).  Sign tables are generated
+ * like RotationChain does (include/cphnsw/encoder/rotation.hpp:134-144,173-178). */
+int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M,
+                       uint32_t ef_construction, uint64_t seed, int fht_convention, int device,
+                       cphnsw_b200_index** out);
+int cphnsw_b200_destroy(cphnsw_b200_index* h);
+
+/* Named tunables (CPHNSWParams fields, types.hpp:374-400, plus build/search knobs):
+ *   "keep_pruned" (0/1, default 1), "k_entry" (1..100, default 4),
+ *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
+ *   "entry_scan" (nodes scored per query to seed the beam; default = k_entry). */
+int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double value);
+int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* value);
+
+uint64_t cphnsw_b200_dim(const cphnsw_b200_index* h);
+uint64_t cphnsw_b200_padded_dim(const cphnsw_b200_index* h);
+uint64_t cphnsw_b200_size(const cphnsw_b200_index* h); /* CPHNSWIndex::size(), README.md:88 */
+
+/* int8 [K][3][padded_dim] of +1/-1, the tables RandomHadamardRotation::get_signs() exposes
+ * (include/cphnsw/encoder/rotation.hpp:116-121). set_ replaces them (e.g. tables drawn by
+ * another standard library). */
+int cphnsw_b200_get_sign_tables(const cphnsw_b200_index* h, int8_t* out);
+int cphnsw_b200_set_sign_tables(cphnsw_b200_index* h, const int8_t* signs);
+
+/* ---- stage entry points, host pointers ------------------------------------------------------ */
+
+/* Replaces legacy CPEncoder<ComponentT,K>::encode / encode_batch
+ * (include/cphnsw/encoder/cp_encoder.hpp:161-184,244-260) and GPUEncoder::encode_batch
+ * (src/cuda/gpu_encoder.cu:430-471).  x float[n][dim] -> codes ComponentT[n][K]. */
+int cphnsw_b200_encode(cphnsw_b200_index* h, const float* x, uint64_t n, void* codes_out);
+
+/* Replaces legacy encode_query / GPUEncoder::encode_queries_batch (src/cuda/gpu_encoder.cu:473-513):
+ * codes [nq][K]; rotated float[nq][K][padded_dim] (CPQuery::rotated_vecs, types.hpp:324-337) and
+ * magnitudes float[nq][K] are optional (NULL to skip). */
+int cphnsw_b200_encode_queries(cphnsw_b200_index* h, const float* q, uint64_t nq, void* codes_out,
+                               float* rotated_out, float* magnitudes_out);
+
+/* Replaces legacy hamming_distance(CPCode,CPCode) (use sites evaluation/debug_estimator.cpp:149,172):
+ * out[na][nb] = number of differing components. */
+int cphnsw_b200_code_distance(cphnsw_b200_index* h, const void* codes_a, uint64_t na,
+                              const void* codes_b, uint64_t nb, uint16_t* out);
+
+/* Replaces GPUKNNGraphBuilder::build (src/cuda/gpu_knn_graph.cu:330-415) with the CP-code metric:
+ * rows [row_begin,row_end) against all n codes, self excluded, k smallest by (distance, id),
+ * padded with 0xFFFFFFFF / 0xFFFF.  nbrs_out uint32[rows][k]; dist_out uint16[rows][k] or NULL. */
+int cphnsw_b200_knn_graph(cphnsw_b200_index* h, const void* codes, uint64_t n, uint32_t k,
+                          uint64_t row_begin, uint64_t row_end, uint32_t* nbrs_out, uint16_t* dist_out);
+
+/* Replaces legacy select_neighbors (HNSW heuristic with keepPrunedConnections,
+ * resources/hnsw-paper/consolidated.tex:93-115; flag types.hpp:390-391).
+ * cand uint32[rows][k] in ascending (distance,id) order -> adj_out uint32[rows][M]. */
+int cphnsw_b200_select_neighbors(cphnsw_b200_index* h, const void* codes, uint64_t n,
+                                 const uint32_t* cand, uint32_t k, uint64_t row_begin, uint64_t row_end,
+                                 uint32_t M, int keep_pruned, uint32_t* adj_out);
+
+/* ---- index build and search, host pointers -------------------------------------------------- */
+
+/* Replaces CPHNSWIndex::add_batch_parallel / add_batch (use sites evaluation/eval_master.cpp:89,
+ * evaluation/eval_main.cpp:43): appends n vectors (ids continue from size()) and rebuilds the
+ * graph over everything added so far: encode -> code-distance kNN graph (knn_k) -> select_neighbors. */
+int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_t n);
+
+/* CPHNSWIndex::get_code (evaluation/debug_code_storage.cpp:75) for all nodes, and the adjacency
+ * uint32[size][M] (FlatGraph neighbour ids, include/cphnsw/graph/flat_graph.hpp:179-181). */
+int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out);
+int cphnsw_b200_get_adjacency(const cphnsw_b200_index* h, uint32_t* adj_out);
+/* ids scored for every query before the graph walk (entry_scan evenly spaced node ids). */
+int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uint64_t* count);
+
+/* Batched CPHNSWIndex::search(q,k,ef) (evaluation/eval_sift.cpp:387; engine
+ * include/cphnsw/search/search_engine.hpp:86-193): graph walk under the asymmetric CP score,
+ * ids uint32[nq][k], dists float[nq][k] ascending (negative scores), padded 0xFFFFFFFF / +inf.
+ * Beam width is max(ef, k).  stats (optional) uint32[nq][2] = expansions, distance evaluations. */
+int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
+                             uint32_t ef, uint32_t* ids_out, float* dists_out, uint32_t* stats_out);
+
+/* Batched CPHNSWIndex::search_and_rerank(q,k,ef,rerank_k) (evaluation/eval_master.cpp:145;
+ * steps shown by hand at evaluation/eval_sift.cpp:539-563; replaces GPUBruteForce::rerank,
+ * src/cuda/gpu_encoder.cu:605-664): beam max(ef, rerank_k), best rerank_k re-scored with
+ * -<q,x> in fp32, sorted by (distance,id), best k returned. */
+int cphnsw_b200_search_and_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
+                                        uint32_t ef, uint32_t rerank_k, uint32_t* ids_out,
+                                        float* dists_out, uint32_t* stats_out);
+
+/* ---- device-pointer variants (inputs already resident in HBM; used for sharded builds) ------- */
+
+int cphnsw_b200_encode_dev(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_codes,
+                           float* d_rotated, float* d_magnitudes, void* stream);
+int cphnsw_b200_code_distance_dev(cphnsw_b200_index* h, const void* d_a, uint64_t na, const void* d_b,
+                                  uint64_t nb, uint16_t* d_out, void* stream);
+int cphnsw_b200_knn_graph_dev(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k,
+                              uint64_t row_begin, uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist,
+                              void* stream);
+int cphnsw_b200_select_neighbors_dev(cphnsw_b200_index* h, const void* d_codes, uint64_t n,
+                                     const uint32_t* d_cand, uint32_t k, uint64_t row_begin,
+                                     uint64_t row_end, uint32_t M, int keep_pruned, uint32_t* d_adj,
+                                     void* stream);
+/* Install a complete index from device buffers (copied, not retained): vectors float[n][dim],
+ * codes [n][K], adjacency uint32[n][M].  Used after a sharded build has all-gathered its rows. */
+int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const void* d_codes,
+                            const uint32_t* d_adj, uint64_t n, void* stream);
+/* d_q float[nq][dim]; outputs device uint32[nq][k] / float[nq][k]; rerank_k = 0 means plain search. */
+int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, uint32_t k, uint32_t ef,
+                           uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
+                           void* stream);
+/* Reads and clears the device-side status word the kernels raise when a bounded wait runs out. */
+int cphnsw_b200_check_device_status(cphnsw_b200_index* h);
+
+/* Number of kernel launches issued through this handle so far (for benchmark accounting). */
+uint64_t cphnsw_b200_launch_count(const cphnsw_b200_index* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CPHNSW_B200_H */

@@ -1,0 +1,290 @@
+"""ctypes binding of ``libcphnsw_b200.so`` (C ABI in ``include/cphnsw_b200.h``).
+
+``CPHNSWIndex`` mirrors the legacy ``CPHNSWIndex<ComponentT,K>`` surface of the reference (use sites:
+evaluation/eval_sift.cpp:228-266,387, evaluation/eval_master.cpp:89,145, evaluation/eval_main.cpp:43):
+``add_batch`` / ``add_batch_parallel`` / ``search`` / ``search_and_rerank`` with host (numpy) arrays in
+and out, plus batched forms and the individual stages (``encode``, ``code_distance``, ``knn_graph``,
+``select_neighbors``).  Errors that the reference raises as ``std::invalid_argument`` surface as
+``ValueError``; everything else as ``CPHNSWError``.
+
+There is no CPU implementation behind this module: importing it without the built library, or
+constructing an index without a B200, raises.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "libcphnsw_b200.so")
+
+INVALID_NODE = 0xFFFFFFFF
+FHT_SCALAR, FHT_AVX2, FHT_AVX512 = 0, 1, 2
+E_INVALID, E_CUDA, E_STATE, E_UNSUPPORTED, E_DEVICE_WAIT = -1, -2, -3, -4, -5
+
+# every symbol include/cphnsw_b200.h declares
+EXPORTS = [
+    "cphnsw_b200_last_error", "cphnsw_b200_device_count", "cphnsw_b200_create", "cphnsw_b200_destroy",
+    "cphnsw_b200_set_param", "cphnsw_b200_get_param", "cphnsw_b200_dim", "cphnsw_b200_padded_dim",
+    "cphnsw_b200_size", "cphnsw_b200_get_sign_tables", "cphnsw_b200_set_sign_tables", "cphnsw_b200_encode",
+    "cphnsw_b200_encode_queries", "cphnsw_b200_code_distance", "cphnsw_b200_knn_graph",
+    "cphnsw_b200_select_neighbors", "cphnsw_b200_add_batch_parallel", "cphnsw_b200_get_codes",
+    "cphnsw_b200_get_adjacency", "cphnsw_b200_get_entry_ids", "cphnsw_b200_search_batch",
+    "cphnsw_b200_search_and_rerank_batch", "cphnsw_b200_encode_dev", "cphnsw_b200_code_distance_dev",
+    "cphnsw_b200_knn_graph_dev", "cphnsw_b200_select_neighbors_dev", "cphnsw_b200_install_dev",
+    "cphnsw_b200_search_dev", "cphnsw_b200_check_device_status", "cphnsw_b200_launch_count",
+]
+
+
+class CPHNSWError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load_library():
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise CPHNSWError("%s not found: run `python sparse-text-kmeans_b200/build.py`" % LIB_PATH)
+        lib = C.CDLL(LIB_PATH)
+        lib.cphnsw_b200_last_error.restype = C.c_char_p
+        for name in ("cphnsw_b200_dim", "cphnsw_b200_padded_dim", "cphnsw_b200_size", "cphnsw_b200_launch_count"):
+            getattr(lib, name).restype = C.c_uint64
+            getattr(lib, name).argtypes = [C.c_void_p]
+        _lib = lib
+    return _lib
+
+
+def device_count():
+    return load_library().cphnsw_b200_device_count()
+
+
+def _check(rc):
+    if rc == 0:
+        return
+    msg = load_library().cphnsw_b200_last_error().decode()
+    if rc == E_INVALID:
+        raise ValueError(msg)
+    raise CPHNSWError("[%d] %s" % (rc, msg))
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _u64(v):
+    return C.c_uint64(int(v))
+
+
+def _u32(v):
+    return C.c_uint32(int(v))
+
+
+class CPHNSWIndex:
+    """Drop-in mirror of ``CPHNSWIndex<ComponentT,K>``; ``component_bytes`` selects ComponentT."""
+
+    def __init__(self, dim, M=32, ef_construction=200, K=32, component_bytes=1, seed=42,
+                 fht_convention=FHT_AVX512, device=0):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        _check(self._lib.cphnsw_b200_create(_u64(dim), _u32(K), _u32(component_bytes), _u32(M), _u32(ef_construction),
+                                            _u64(seed), C.c_int(fht_convention), C.c_int(device), C.byref(self._h)))
+        self.dim, self.K, self.M, self.component_bytes = dim, K, M, component_bytes
+        self.padded_dim = int(self._lib.cphnsw_b200_padded_dim(self._h))
+        self.code_dtype = np.uint8 if component_bytes == 1 else np.uint16
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            self._lib.cphnsw_b200_destroy(self._h)
+            self._h = C.c_void_p()
+
+    __del__ = close
+
+    @property
+    def handle(self):
+        return self._h
+
+    # ---- parameters -------------------------------------------------------------------------
+    def set_param(self, name, value):
+        _check(self._lib.cphnsw_b200_set_param(self._h, name.encode(), C.c_double(value)))
+
+    def get_param(self, name):
+        v = C.c_double()
+        _check(self._lib.cphnsw_b200_get_param(self._h, name.encode(), C.byref(v)))
+        return v.value
+
+    def size(self):
+        return int(self._lib.cphnsw_b200_size(self._h))
+
+    def launch_count(self):
+        return int(self._lib.cphnsw_b200_launch_count(self._h))
+
+    def sign_tables(self):
+        out = np.empty((self.K, 3, self.padded_dim), np.int8)
+        _check(self._lib.cphnsw_b200_get_sign_tables(self._h, _p(out)))
+        return out
+
+    def set_sign_tables(self, signs):
+        signs = np.ascontiguousarray(signs, np.int8)
+        if signs.shape != (self.K, 3, self.padded_dim):
+            raise ValueError("sign tables must be int8[K][3][padded_dim]")
+        _check(self._lib.cphnsw_b200_set_sign_tables(self._h, _p(signs)))
+
+    # ---- stages --------------------------------------------------------------------------------
+    def _vecs(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        if x.ndim == 1:
+            x = x[None, :]
+        if x.ndim != 2 or x.shape[1] != self.dim:
+            raise ValueError("expected float32[n][%d]" % self.dim)
+        return x
+
+    def _codes(self, c):
+        c = np.ascontiguousarray(c, self.code_dtype)
+        if c.ndim != 2 or c.shape[1] != self.K:
+            raise ValueError("expected codes[n][%d]" % self.K)
+        return c
+
+    def encode(self, x):
+        x = self._vecs(x)
+        codes = np.empty((x.shape[0], self.K), self.code_dtype)
+        _check(self._lib.cphnsw_b200_encode(self._h, _p(x), _u64(x.shape[0]), _p(codes)))
+        return codes
+
+    def encode_queries(self, q):
+        """-> (codes [nq][K], rotated float32[nq][K][padded_dim], magnitudes float32[nq][K])."""
+        q = self._vecs(q)
+        nq = q.shape[0]
+        codes = np.empty((nq, self.K), self.code_dtype)
+        rot = np.empty((nq, self.K, self.padded_dim), np.float32)
+        mag = np.empty((nq, self.K), np.float32)
+        _check(self._lib.cphnsw_b200_encode_queries(self._h, _p(q), _u64(nq), _p(codes), _p(rot), _p(mag)))
+        return codes, rot, mag
+
+    def code_distance(self, a, b):
+        a, b = self._codes(a), self._codes(b)
+        out = np.empty((a.shape[0], b.shape[0]), np.uint16)
+        _check(self._lib.cphnsw_b200_code_distance(self._h, _p(a), _u64(a.shape[0]), _p(b), _u64(b.shape[0]), _p(out)))
+        return out
+
+    def knn_graph(self, codes, k, row_begin=0, row_end=None):
+        codes = self._codes(codes)
+        n = codes.shape[0]
+        row_end = n if row_end is None else row_end
+        rows = max(0, row_end - row_begin)
+        nbrs = np.empty((rows, k), np.uint32)
+        dist = np.empty((rows, k), np.uint16)
+        _check(self._lib.cphnsw_b200_knn_graph(self._h, _p(codes), _u64(n), _u32(k), _u64(row_begin), _u64(row_end),
+                                               _p(nbrs), _p(dist)))
+        return nbrs, dist
+
+    def select_neighbors(self, codes, cand, M=None, keep_pruned=True, row_begin=0):
+        codes = self._codes(codes)
+        cand = np.ascontiguousarray(cand, np.uint32)
+        M = self.M if M is None else M
+        rows, k = cand.shape
+        adj = np.empty((rows, M), np.uint32)
+        _check(self._lib.cphnsw_b200_select_neighbors(self._h, _p(codes), _u64(codes.shape[0]), _p(cand), _u32(k),
+                                                      _u64(row_begin), _u64(row_begin + rows), _u32(M),
+                                                      C.c_int(int(keep_pruned)), _p(adj)))
+        return adj
+
+    # ---- index ---------------------------------------------------------------------------------
+    def add_batch_parallel(self, x):
+        x = self._vecs(x)
+        _check(self._lib.cphnsw_b200_add_batch_parallel(self._h, _p(x), _u64(x.shape[0])))
+
+    add_batch = add_batch_parallel
+
+    def add(self, vec):
+        """Appends one vector and returns its id (CPHNSWIndex::add, evaluation/eval_sift.cpp:239)."""
+        nid = self.size()
+        self.add_batch_parallel(self._vecs(vec))
+        return nid
+
+    def codes(self):
+        out = np.empty((self.size(), self.K), self.code_dtype)
+        _check(self._lib.cphnsw_b200_get_codes(self._h, _p(out)))
+        return out
+
+    def get_code(self, node_id):
+        return self.codes()[node_id]
+
+    def adjacency(self):
+        out = np.empty((self.size(), self.M), np.uint32)
+        _check(self._lib.cphnsw_b200_get_adjacency(self._h, _p(out)))
+        return out
+
+    def entry_ids(self):
+        cnt = C.c_uint64()
+        _check(self._lib.cphnsw_b200_get_entry_ids(self._h, None, C.byref(cnt)))
+        out = np.empty(cnt.value, np.uint32)
+        _check(self._lib.cphnsw_b200_get_entry_ids(self._h, _p(out), C.byref(cnt)))
+        return out
+
+    def search_batch(self, q, k, ef, want_stats=False):
+        q = self._vecs(q)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        stats = np.zeros((nq, 2), np.uint32) if want_stats else None
+        _check(self._lib.cphnsw_b200_search_batch(self._h, _p(q), _u64(nq), _u32(k), _u32(ef), _p(ids), _p(dist), _p(stats)))
+        return (ids, dist, stats) if want_stats else (ids, dist)
+
+    def search_and_rerank_batch(self, q, k, ef, rerank_k, want_stats=False):
+        q = self._vecs(q)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        stats = np.zeros((nq, 2), np.uint32) if want_stats else None
+        _check(self._lib.cphnsw_b200_search_and_rerank_batch(self._h, _p(q), _u64(nq), _u32(k), _u32(ef), _u32(rerank_k),
+                                                             _p(ids), _p(dist), _p(stats)))
+        return (ids, dist, stats) if want_stats else (ids, dist)
+
+    @staticmethod
+    def _results(ids, dist):
+        return [(int(i), float(d)) for i, d in zip(ids, dist) if i != INVALID_NODE]
+
+    def search(self, q, k, ef):
+        """One query -> list of (id, distance) ascending (std::vector<SearchResult>)."""
+        ids, dist = self.search_batch(q, k, ef)
+        return self._results(ids[0], dist[0])
+
+    def search_and_rerank(self, q, k, ef, rerank_k):
+        ids, dist = self.search_and_rerank_batch(q, k, ef, rerank_k)
+        return self._results(ids[0], dist[0])
+
+    # ---- device-pointer forms (integers are raw device addresses, e.g. torch.Tensor.data_ptr()) ----
+    def encode_dev(self, d_x, n, d_codes, d_rotated=0, d_magnitudes=0, stream=0):
+        _check(self._lib.cphnsw_b200_encode_dev(self._h, C.c_void_p(d_x), _u64(n), C.c_void_p(d_codes),
+                                                C.c_void_p(d_rotated), C.c_void_p(d_magnitudes), C.c_void_p(stream)))
+
+    def code_distance_dev(self, d_a, na, d_b, nb, d_out, stream=0):
+        _check(self._lib.cphnsw_b200_code_distance_dev(self._h, C.c_void_p(d_a), _u64(na), C.c_void_p(d_b), _u64(nb),
+                                                       C.c_void_p(d_out), C.c_void_p(stream)))
+
+    def knn_graph_dev(self, d_codes, n, k, row_begin, row_end, d_nbrs, d_dist=0, stream=0):
+        _check(self._lib.cphnsw_b200_knn_graph_dev(self._h, C.c_void_p(d_codes), _u64(n), _u32(k), _u64(row_begin),
+                                                   _u64(row_end), C.c_void_p(d_nbrs), C.c_void_p(d_dist),
+                                                   C.c_void_p(stream)))
+
+    def select_neighbors_dev(self, d_codes, n, d_cand, k, row_begin, row_end, M, keep_pruned, d_adj, stream=0):
+        _check(self._lib.cphnsw_b200_select_neighbors_dev(self._h, C.c_void_p(d_codes), _u64(n), C.c_void_p(d_cand),
+                                                          _u32(k), _u64(row_begin), _u64(row_end), _u32(M),
+                                                          C.c_int(int(keep_pruned)), C.c_void_p(d_adj),
+                                                          C.c_void_p(stream)))
+
+    def install_dev(self, d_vectors, d_codes, d_adj, n, stream=0):
+        _check(self._lib.cphnsw_b200_install_dev(self._h, C.c_void_p(d_vectors), C.c_void_p(d_codes),
+                                                 C.c_void_p(d_adj), _u64(n), C.c_void_p(stream)))
+
+    def search_dev(self, d_q, nq, k, ef, rerank_k, d_ids, d_dists, d_stats=0, stream=0):
+        _check(self._lib.cphnsw_b200_search_dev(self._h, C.c_void_p(d_q), _u64(nq), _u32(k), _u32(ef), _u32(rerank_k),
+                                                C.c_void_p(d_ids), C.c_void_p(d_dists), C.c_void_p(d_stats),
+                                                C.c_void_p(stream)))
+
+    def check_device_status(self):
+        _check(self._lib.cphnsw_b200_check_device_status(self._h))

@@ -1,0 +1,84 @@
+"""Seeded synthetic stand-ins for the datasets the reference measures on (SIFT-1M: 1M x 128 with
+10k queries; GIST-1M: 1M x 960 non-negative).  Shapes and value ranges follow those datasets;
+no item of them is reproduced.  All vectors are float32 and L2-normalised with the
+``norm > 1e-10`` guard of evaluation/datasets/dataset_loader.hpp:225-240.
+"""
+import numpy as np
+
+
+def normalize(x):
+    x = np.ascontiguousarray(x, np.float32)
+    norm = np.sqrt((x.astype(np.float32) ** 2).sum(axis=1, dtype=np.float32))
+    scale = np.where(norm > 1e-10, 1.0 / np.maximum(norm, 1e-30), 1.0).astype(np.float32)
+    return (x * scale[:, None]).astype(np.float32)
+
+
+def gaussian_sphere(n, nq, dim, seed):
+    """i.i.d. N(0,1) per coordinate, then normalised (the random-sphere generator of
+    dataset_loader.hpp:145-185 with a numpy stream)."""
+    rng = np.random.default_rng(seed)
+    base = normalize(rng.standard_normal((n, dim), dtype=np.float32))
+    queries = normalize(rng.standard_normal((nq, dim), dtype=np.float32))
+    return base, queries
+
+
+def gaussian_mixture(n, nq, dim, n_clusters, sigma, seed, chunk=1 << 18):
+    """Uniform-weight mixture: centres ~ N(0,1) per coordinate, points = centre + sigma*N(0,1),
+    normalised; queries from the same mixture with an independent stream."""
+    rng = np.random.default_rng(seed)
+    centres = rng.standard_normal((n_clusters, dim), dtype=np.float32)
+
+    def draw(m, stream):
+        out = np.empty((m, dim), np.float32)
+        for i0 in range(0, m, chunk):
+            i1 = min(m, i0 + chunk)
+            a = stream.integers(0, n_clusters, i1 - i0)
+            out[i0:i1] = normalize(centres[a] + np.float32(sigma) * stream.standard_normal((i1 - i0, dim), dtype=np.float32))
+        return out
+
+    base = draw(n, np.random.default_rng([seed, 1]))
+    queries = draw(nq, np.random.default_rng([seed, 2]))
+    return base, queries
+
+
+def abs_gaussian(n, nq, dim, seed, chunk=1 << 16):
+    """Non-negative |N(0,1)| coordinates, normalised (GIST-like value range)."""
+    def draw(m, stream):
+        out = np.empty((m, dim), np.float32)
+        for i0 in range(0, m, chunk):
+            i1 = min(m, i0 + chunk)
+            out[i0:i1] = normalize(np.abs(stream.standard_normal((i1 - i0, dim), dtype=np.float32)))
+        return out
+
+    return draw(n, np.random.default_rng([seed, 1])), draw(nq, np.random.default_rng([seed, 2]))
+
+
+# The five benchmark workloads (full sizes); ``scale`` shrinks base, queries and clusters together
+# so that cluster populations stay the same.
+def workload(name, scale=1.0):
+    s = float(scale)
+
+    def sz(v, lo=1):
+        return max(lo, int(round(v * s)))
+
+    if name == "C1":
+        base, q = gaussian_sphere(sz(100_000), sz(1_000, 10), 128, 0)
+        return dict(name="C1", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
+                    k=10, ef=100, rerank_k=500, entry_scan=4)
+    if name == "C2":
+        base, q = gaussian_mixture(sz(1_000_000), sz(10_000, 10), 128, sz(1_000), 0.3, 1)
+        return dict(name="C2", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
+                    k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4))
+    if name == "C3":
+        base, q = abs_gaussian(sz(1_000_000), sz(10_000, 10), 960, 2)
+        return dict(name="C3", base=base, queries=q, K=32, component_bytes=2, M=32, ef_construction=200,
+                    k=10, ef=200, rerank_k=1000, entry_scan=4)
+    if name == "C4":
+        base, q = gaussian_mixture(sz(10_000_000), sz(1_000, 10), 96, sz(10_000), 0.25, 3)
+        return dict(name="C4", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
+                    k=10, ef=100, rerank_k=500, knn_k=32, entry_scan=sz(65_536, 4))
+    if name == "C5":
+        base, q = gaussian_mixture(sz(10_000_000), sz(100_000, 10), 128, sz(1_000), 0.3, 4)
+        return dict(name="C5", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
+                    k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4))
+    raise ValueError("unknown workload %r" % name)

@@ -1,0 +1,537 @@
+// C ABI of cphnsw_b200: handle lifetime, parameter validation, host<->device staging and the
+// build / search orchestration on top of the kernel launchers.  No CPU implementation of any
+// stage lives here: without a usable sm_100 device every call fails.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <random>
+
+#include "common.cuh"
+
+namespace cpb {
+
+static thread_local std::string g_error;
+
+void set_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) in %s", int(e), cudaGetErrorString(e), what);
+    return CPHNSW_B200_E_CUDA;
+}
+
+namespace {
+
+uint64_t next_pow2(uint64_t n) {
+    uint64_t p = 1;
+    while (p < n) p *= 2;
+    return p;
+}
+
+// +-1 float tables for the device: layer 0 as drawn; layers 1 and 2 multiplied by the diagonal
+// the reference's SIMD FHT leaves on its output (element i negated when popcount(i & (W-1)) is
+// odd; W = 16 for an AVX-512 build at P >= 16, 8 for AVX2 at P >= 8, none for scalar —
+// include/cphnsw/encoder/transform/fht.hpp:81-87,141-147).
+int upload_signs(cphnsw_b200_index* h) {
+    const size_t P = h->P, K = h->K;
+    size_t w = 1;
+    if (h->convention == CPHNSW_B200_FHT_AVX512 && P >= 16) w = 16;
+    else if (h->convention >= CPHNSW_B200_FHT_AVX2 && P >= 8) w = 8;
+    std::vector<float> f(K * 3 * P);
+    for (size_t r = 0; r < K; ++r)
+        for (size_t l = 0; l < 3; ++l)
+            for (size_t i = 0; i < P; ++i) {
+                float s = float(h->signs[(r * 3 + l) * P + i]);
+                if (l > 0 && (__builtin_popcountll(i & (w - 1)) & 1)) s = -s;
+                f[(r * 3 + l) * P + i] = s;
+            }
+    CPB_TRY(h->d_signs.reserve(f.size() * sizeof(float)));
+    CPB_CUDA(cudaMemcpy(h->d_signs.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+int bind(const cphnsw_b200_index* h) {
+    if (!h) {
+        set_error("null index handle");
+        return CPHNSW_B200_E_INVALID;
+    }
+    CPB_CUDA(cudaSetDevice(h->device));
+    return 0;
+}
+
+int check_status(cphnsw_b200_index* h) {
+    uint32_t s = 0;
+    CPB_CUDA(cudaMemcpy(&s, h->d_status.p, 4, cudaMemcpyDeviceToHost));
+    if (s != kStatusOk) {
+        CPB_CUDA(cudaMemset(h->d_status.p, 0, 4));
+        set_error("a bounded device-side wait ran out (status %u); results of the last call are invalid", s);
+        return CPHNSW_B200_E_DEVICE_WAIT;
+    }
+    return 0;
+}
+
+size_t code_row_bytes(const cphnsw_b200_index* h) { return size_t(h->K) * h->comp_bytes; }
+
+int set_entry_ids(cphnsw_b200_index* h) {
+    uint64_t s = h->entry_scan ? h->entry_scan : h->k_entry;
+    if (s > h->n) s = h->n;
+    std::vector<uint32_t> ids(s);
+    for (uint64_t i = 0; i < s; ++i) ids[i] = uint32_t((unsigned __int128)i * h->n / s);
+    h->n_entry = uint32_t(s);
+    CPB_TRY(h->d_entry.reserve(s * 4 + 16));
+    if (s) CPB_CUDA(cudaMemcpy(h->d_entry.p, ids.data(), s * 4, cudaMemcpyHostToDevice));
+    return 0;
+}
+
+// codes already in d_codes, vectors in d_vectors: build adjacency and entry ids
+int build_graph(cphnsw_b200_index* h, cudaStream_t st) {
+    const uint64_t n = h->n;
+    uint32_t k = h->knn_k ? h->knn_k : (2 * h->M < 64 ? 2 * h->M : 64);
+    if (k < h->M) k = h->M;
+    if (k > 64) k = 64;
+    CPB_TRY(h->s_out.reserve(size_t(n) * k * 4 + 16));
+    CPB_TRY(h->d_adj.reserve(size_t(n) * h->M * 4 + 16));
+    CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, k, 0, n, h->s_out.as<uint32_t>(), nullptr, st));
+    CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n, h->s_out.as<uint32_t>(), k, 0, n, h->M, h->keep_pruned,
+                                    h->d_adj.as<uint32_t>(), st));
+    CPB_CUDA(cudaStreamSynchronize(st));
+    CPB_TRY(check_status(h));
+    return set_entry_ids(h);
+}
+
+int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t nq, uint32_t k, uint32_t ef,
+              uint32_t rerank_k, uint32_t* ids, float* dists, uint32_t* stats, bool out_on_device,
+              cudaStream_t st) {
+    if (h->n == 0) {
+        set_error("search on an empty index");
+        return CPHNSW_B200_E_STATE;
+    }
+    if (k == 0 || (!q && nq) || !ids || !dists) {
+        set_error("search: k must be > 0 and query/output pointers non-null");
+        return CPHNSW_B200_E_INVALID;
+    }
+    uint32_t beam = ef > k ? ef : k;
+    if (rerank_k > beam) beam = rerank_k;
+    if (rerank_k && rerank_k < k) {
+        set_error("search_and_rerank: rerank_k (%u) must be >= k (%u)", rerank_k, k);
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (beam > 1024) {
+        set_error("search: beam width max(ef, k, rerank_k) must be <= 1024 (got %u)", beam);
+        return CPHNSW_B200_E_INVALID;
+    }
+    const uint64_t chunk = 16384;  // queries per launch: bounds the rotated-table scratch
+    const size_t table_floats = size_t(h->K) * h->P;
+    for (uint64_t q0 = 0; q0 < nq; q0 += chunk) {
+        const uint64_t m = nq - q0 < chunk ? nq - q0 : chunk;
+        const float* dq;
+        if (q_on_device) {
+            dq = q + q0 * h->dim;
+        } else {
+            CPB_TRY(h->d_q.reserve(m * h->dim * 4));
+            CPB_CUDA(cudaMemcpyAsync(h->d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
+            dq = h->d_q.as<float>();
+        }
+        CPB_TRY(h->d_qtables.reserve(m * table_floats * 4));
+        CPB_TRY(h->d_qcodes.reserve(m * code_row_bytes(h) + 16));
+        CPB_TRY(launch_encode(h, dq, m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
+        uint32_t *o_ids, *o_stats = nullptr;
+        float* o_d;
+        if (out_on_device) {
+            o_ids = ids + q0 * k;
+            o_d = dists + q0 * k;
+            if (stats) o_stats = stats + q0 * 2;
+        } else {
+            CPB_TRY(h->d_out_ids.reserve(m * k * 4));
+            CPB_TRY(h->d_out_dist.reserve(m * k * 4));
+            o_ids = h->d_out_ids.as<uint32_t>();
+            o_d = h->d_out_dist.as<float>();
+            if (stats) {
+                CPB_TRY(h->d_stats.reserve(m * 8));
+                o_stats = h->d_stats.as<uint32_t>();
+            }
+        }
+        CPB_TRY(launch_search(h, dq, h->d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st));
+        if (!out_on_device) {
+            CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, o_ids, m * k * 4, cudaMemcpyDeviceToHost, st));
+            CPB_CUDA(cudaMemcpyAsync(dists + q0 * k, o_d, m * k * 4, cudaMemcpyDeviceToHost, st));
+            if (stats) CPB_CUDA(cudaMemcpyAsync(stats + q0 * 2, o_stats, m * 8, cudaMemcpyDeviceToHost, st));
+            CPB_CUDA(cudaStreamSynchronize(st));
+        }
+    }
+    return 0;
+}
+
+}  // namespace
+}  // namespace cpb
+
+using namespace cpb;
+
+extern "C" {
+
+const char* cphnsw_b200_last_error(void) { return g_error.c_str(); }
+
+int cphnsw_b200_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int ok = 0;
+    for (int d = 0; d < n; ++d) {
+        cudaDeviceProp p;
+        if (cudaGetDeviceProperties(&p, d) == cudaSuccess && p.major == 10) ++ok;
+    }
+    return ok;
+}
+
+int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M, uint32_t ef_construction,
+                       uint64_t seed, int fht_convention, int device, cphnsw_b200_index** out) {
+    if (!out) {
+        set_error("create: out is null");
+        return CPHNSW_B200_E_INVALID;
+    }
+    *out = nullptr;
+    // bounds of CPHNSWParams::finalize (include/cphnsw/core/types.hpp:403-469)
+    if (dim == 0) { set_error("CPHNSWParams: dim must be > 0"); return CPHNSW_B200_E_INVALID; }
+    if (K == 0) { set_error("CPHNSWParams: k (code width) must be > 0"); return CPHNSW_B200_E_INVALID; }
+    if (K > 256) { set_error("CPHNSWParams: k (code width) must be <= 256"); return CPHNSW_B200_E_INVALID; }
+    if (M == 0) { set_error("CPHNSWParams: M (max connections) must be > 0"); return CPHNSW_B200_E_INVALID; }
+    if (M > 64) { set_error("CPHNSWParams: M must be <= 64 (FLASH_MAX_M limit)"); return CPHNSW_B200_E_INVALID; }
+    if (ef_construction < M) {
+        set_error("CPHNSWParams: ef_construction must be >= M for good graph quality");
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (ef_construction > 10000) { set_error("CPHNSWParams: ef_construction must be <= 10000"); return CPHNSW_B200_E_INVALID; }
+    if (component_bytes != 1 && component_bytes != 2) {
+        set_error("component_bytes must be 1 (uint8_t) or 2 (uint16_t)");
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (fht_convention < 0 || fht_convention > 2) { set_error("unknown fht_convention %d", fht_convention); return CPHNSW_B200_E_INVALID; }
+    const uint64_t P = next_pow2(dim);
+    // a component holds (index << 1) | sign (types.hpp:88-90)
+    if ((component_bytes == 1 && P > 128) || (component_bytes == 2 && P > 32768)) {
+        set_error("padded dim %llu does not fit a %u-byte component (max %d)", (unsigned long long)P,
+                  component_bytes, component_bytes == 1 ? 128 : 32768);
+        return CPHNSW_B200_E_INVALID;
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+        cudaGetLastError();
+        set_error("no CUDA device available: this library has no CPU path");
+        return CPHNSW_B200_E_CUDA;
+    }
+    if (device < 0 || device >= ndev) { set_error("device %d out of range (%d devices)", device, ndev); return CPHNSW_B200_E_INVALID; }
+    cudaDeviceProp prop;
+    CPB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+        return CPHNSW_B200_E_CUDA;
+    }
+    CPB_CUDA(cudaSetDevice(device));
+    auto* h = new cphnsw_b200_index();
+    h->dim = dim;
+    h->P = P;
+    h->K = K;
+    h->comp_bytes = component_bytes;
+    h->M = M;
+    h->ef_construction = ef_construction;
+    h->seed = seed;
+    h->convention = fht_convention;
+    h->device = device;
+    h->sm_count = prop.multiProcessorCount;
+    // RotationChain: rotation r is seeded seed + r (include/cphnsw/encoder/rotation.hpp:173-178);
+    // each table is drawn layer by layer from mt19937_64 through uniform_int_distribution<int>(0,1)
+    // (rotation.hpp:134-144) — the standard library does the draw, as in the reference.
+    h->signs.resize(size_t(K) * 3 * P);
+    for (uint32_t r = 0; r < K; ++r) {
+        std::mt19937_64 rng(seed + r);
+        std::uniform_int_distribution<int> coin(0, 1);
+        for (int l = 0; l < 3; ++l)
+            for (uint64_t i = 0; i < P; ++i) h->signs[(size_t(r) * 3 + l) * P + i] = coin(rng) ? 1 : -1;
+    }
+    int rc = upload_signs(h);
+    if (rc == 0) rc = h->d_status.reserve(16);
+    if (rc == 0 && cudaMemset(h->d_status.p, 0, 16) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "memset status");
+    if (rc != 0) {
+        delete h;
+        return rc;
+    }
+    *out = h;
+    return 0;
+}
+
+int cphnsw_b200_destroy(cphnsw_b200_index* h) {
+    if (!h) return 0;
+    cudaSetDevice(h->device);
+    delete h;
+    return 0;
+}
+
+int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
+    if (!h || !name) { set_error("set_param: null argument"); return CPHNSW_B200_E_INVALID; }
+    std::string s(name);
+    if (s == "keep_pruned") { h->keep_pruned = v != 0.0; return 0; }
+    if (s == "k_entry") {
+        if (v < 1) { set_error("CPHNSWParams: k_entry must be > 0"); return CPHNSW_B200_E_INVALID; }
+        if (v > 100) { set_error("CPHNSWParams: k_entry must be <= 100"); return CPHNSW_B200_E_INVALID; }
+        h->k_entry = uint32_t(v);
+    } else if (s == "knn_k") {
+        if (v < 0 || v > 64) { set_error("knn_k must be in 0..64 (0 = default)"); return CPHNSW_B200_E_INVALID; }
+        h->knn_k = uint32_t(v);
+        return 0;
+    } else if (s == "entry_scan") {
+        if (v < 0 || v > 1048576) { set_error("entry_scan must be in 0..1048576 (0 = k_entry)"); return CPHNSW_B200_E_INVALID; }
+        h->entry_scan = uint32_t(v);
+    } else {
+        set_error("unknown parameter '%s'", name);
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (h->n) {
+        CPB_TRY(bind(h));
+        return set_entry_ids(h);
+    }
+    return 0;
+}
+
+int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* v) {
+    if (!h || !name || !v) { set_error("get_param: null argument"); return CPHNSW_B200_E_INVALID; }
+    std::string s(name);
+    if (s == "keep_pruned") *v = h->keep_pruned;
+    else if (s == "k_entry") *v = h->k_entry;
+    else if (s == "knn_k") *v = h->knn_k;
+    else if (s == "entry_scan") *v = h->entry_scan;
+    else if (s == "M") *v = h->M;
+    else if (s == "K") *v = h->K;
+    else if (s == "ef_construction") *v = h->ef_construction;
+    else if (s == "component_bytes") *v = h->comp_bytes;
+    else { set_error("unknown parameter '%s'", name); return CPHNSW_B200_E_INVALID; }
+    return 0;
+}
+
+uint64_t cphnsw_b200_dim(const cphnsw_b200_index* h) { return h ? h->dim : 0; }
+uint64_t cphnsw_b200_padded_dim(const cphnsw_b200_index* h) { return h ? h->P : 0; }
+uint64_t cphnsw_b200_size(const cphnsw_b200_index* h) { return h ? h->n : 0; }
+uint64_t cphnsw_b200_launch_count(const cphnsw_b200_index* h) { return h ? h->launches : 0; }
+
+int cphnsw_b200_get_sign_tables(const cphnsw_b200_index* h, int8_t* out) {
+    if (!h || !out) { set_error("get_sign_tables: null argument"); return CPHNSW_B200_E_INVALID; }
+    std::memcpy(out, h->signs.data(), h->signs.size());
+    return 0;
+}
+
+int cphnsw_b200_set_sign_tables(cphnsw_b200_index* h, const int8_t* signs) {
+    if (!h || !signs) { set_error("set_sign_tables: null argument"); return CPHNSW_B200_E_INVALID; }
+    for (size_t i = 0; i < h->signs.size(); ++i)
+        if (signs[i] != 1 && signs[i] != -1) { set_error("sign tables must hold +1/-1 only"); return CPHNSW_B200_E_INVALID; }
+    CPB_TRY(bind(h));
+    std::memcpy(h->signs.data(), signs, h->signs.size());
+    return upload_signs(h);
+}
+
+int cphnsw_b200_check_device_status(cphnsw_b200_index* h) {
+    CPB_TRY(bind(h));
+    return check_status(h);
+}
+
+// ---- device-pointer entry points ---------------------------------------------------------------------
+int cphnsw_b200_encode_dev(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_codes, float* d_rotated,
+                           float* d_magnitudes, void* stream) {
+    CPB_TRY(bind(h));
+    if (n && (!d_x || !d_codes)) { set_error("encode: null pointer"); return CPHNSW_B200_E_INVALID; }
+    return launch_encode(h, d_x, n, d_codes, d_rotated, d_magnitudes, (cudaStream_t)stream);
+}
+
+int cphnsw_b200_code_distance_dev(cphnsw_b200_index* h, const void* d_a, uint64_t na, const void* d_b, uint64_t nb,
+                                  uint16_t* d_out, void* stream) {
+    CPB_TRY(bind(h));
+    if (na && nb && (!d_a || !d_b || !d_out)) { set_error("code_distance: null pointer"); return CPHNSW_B200_E_INVALID; }
+    return launch_code_distance(h, d_a, na, d_b, nb, d_out, (cudaStream_t)stream);
+}
+
+int cphnsw_b200_knn_graph_dev(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                              uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, void* stream) {
+    CPB_TRY(bind(h));
+    if (row_end > row_begin && (!d_codes || !d_nbrs)) { set_error("knn_graph: null pointer"); return CPHNSW_B200_E_INVALID; }
+    return launch_knn_graph(h, d_codes, n, k, row_begin, row_end, d_nbrs, d_dist, (cudaStream_t)stream);
+}
+
+int cphnsw_b200_select_neighbors_dev(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
+                                     uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
+                                     uint32_t* d_adj, void* stream) {
+    CPB_TRY(bind(h));
+    if (row_end > row_begin && (!d_codes || !d_cand || !d_adj)) { set_error("select_neighbors: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (row_end > n) { set_error("select_neighbors: row range exceeds n"); return CPHNSW_B200_E_INVALID; }
+    return launch_select_neighbors(h, d_codes, n, d_cand, k, row_begin, row_end, M, keep_pruned, d_adj,
+                                   (cudaStream_t)stream);
+}
+
+int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const void* d_codes, const uint32_t* d_adj,
+                            uint64_t n, void* stream) {
+    CPB_TRY(bind(h));
+    if (n == 0 || !d_vectors || !d_codes || !d_adj) { set_error("install: null pointer or n == 0"); return CPHNSW_B200_E_INVALID; }
+    if (n >= 0xFFFFFFFFull) { set_error("install: n must be < 2^32-1"); return CPHNSW_B200_E_INVALID; }
+    cudaStream_t st = (cudaStream_t)stream;
+    CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
+    CPB_TRY(h->d_codes.reserve(n * code_row_bytes(h) + 16));
+    CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
+    CPB_CUDA(cudaMemcpyAsync(h->d_vectors.p, d_vectors, n * h->dim * 4, cudaMemcpyDeviceToDevice, st));
+    CPB_CUDA(cudaMemcpyAsync(h->d_codes.p, d_codes, n * code_row_bytes(h), cudaMemcpyDeviceToDevice, st));
+    CPB_CUDA(cudaMemcpyAsync(h->d_adj.p, d_adj, n * h->M * 4, cudaMemcpyDeviceToDevice, st));
+    CPB_CUDA(cudaStreamSynchronize(st));
+    h->n = n;
+    h->h_vectors.clear();  // a later add_batch_parallel cannot extend an index installed from device buffers
+    h->d_visited.release();
+    return set_entry_ids(h);
+}
+
+int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, uint32_t k, uint32_t ef,
+                           uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats, void* stream) {
+    CPB_TRY(bind(h));
+    return do_search(h, d_q, true, nq, k, ef, rerank_k, d_ids, d_dists, d_stats, true, (cudaStream_t)stream);
+}
+
+// ---- host-pointer entry points -------------------------------------------------------------------------
+int cphnsw_b200_encode(cphnsw_b200_index* h, const float* x, uint64_t n, void* codes_out) {
+    return cphnsw_b200_encode_queries(h, x, n, codes_out, nullptr, nullptr);
+}
+
+int cphnsw_b200_encode_queries(cphnsw_b200_index* h, const float* q, uint64_t nq, void* codes_out, float* rotated_out,
+                               float* magnitudes_out) {
+    CPB_TRY(bind(h));
+    if (nq == 0) return 0;
+    if (!q || !codes_out) { set_error("encode: null pointer"); return CPHNSW_B200_E_INVALID; }
+    const size_t rb = code_row_bytes(h);
+    const size_t tf = size_t(h->K) * h->P;
+    // bound the staging buffers: rotated output is K*P floats per row
+    const uint64_t chunk = rotated_out ? 8192 : (uint64_t(1) << 22);
+    for (uint64_t i0 = 0; i0 < nq; i0 += chunk) {
+        const uint64_t m = nq - i0 < chunk ? nq - i0 : chunk;
+        CPB_TRY(h->s_in.reserve(m * h->dim * 4));
+        CPB_TRY(h->s_out.reserve(m * rb + 16));
+        float *d_rot = nullptr, *d_mag = nullptr;
+        if (rotated_out) { CPB_TRY(h->d_qtables.reserve(m * tf * 4)); d_rot = h->d_qtables.as<float>(); }
+        if (magnitudes_out) { CPB_TRY(h->s_out2.reserve(m * h->K * 4)); d_mag = h->s_out2.as<float>(); }
+        CPB_CUDA(cudaMemcpy(h->s_in.p, q + i0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice));
+        CPB_TRY(launch_encode(h, h->s_in.as<float>(), m, h->s_out.p, d_rot, d_mag, 0));
+        CPB_CUDA(cudaMemcpy((char*)codes_out + i0 * rb, h->s_out.p, m * rb, cudaMemcpyDeviceToHost));
+        if (rotated_out) CPB_CUDA(cudaMemcpy(rotated_out + i0 * tf, d_rot, m * tf * 4, cudaMemcpyDeviceToHost));
+        if (magnitudes_out) CPB_CUDA(cudaMemcpy(magnitudes_out + i0 * h->K, d_mag, m * h->K * 4, cudaMemcpyDeviceToHost));
+    }
+    return 0;
+}
+
+int cphnsw_b200_code_distance(cphnsw_b200_index* h, const void* a, uint64_t na, const void* b, uint64_t nb,
+                              uint16_t* out) {
+    CPB_TRY(bind(h));
+    if (na == 0 || nb == 0) return 0;
+    if (!a || !b || !out) { set_error("code_distance: null pointer"); return CPHNSW_B200_E_INVALID; }
+    const size_t rb = code_row_bytes(h);
+    CPB_TRY(h->s_in.reserve(na * rb + 16));
+    CPB_TRY(h->s_in2.reserve(nb * rb + 16));
+    CPB_TRY(h->s_out.reserve(na * nb * 2));
+    CPB_CUDA(cudaMemcpy(h->s_in.p, a, na * rb, cudaMemcpyHostToDevice));
+    CPB_CUDA(cudaMemcpy(h->s_in2.p, b, nb * rb, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_code_distance(h, h->s_in.p, na, h->s_in2.p, nb, h->s_out.as<uint16_t>(), 0));
+    CPB_CUDA(cudaMemcpy(out, h->s_out.p, na * nb * 2, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_knn_graph(cphnsw_b200_index* h, const void* codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                          uint64_t row_end, uint32_t* nbrs_out, uint16_t* dist_out) {
+    CPB_TRY(bind(h));
+    if (row_end <= row_begin) return 0;
+    if (!codes || !nbrs_out) { set_error("knn_graph: null pointer"); return CPHNSW_B200_E_INVALID; }
+    const size_t rb = code_row_bytes(h);
+    const uint64_t rows = row_end - row_begin;
+    CPB_TRY(h->s_in.reserve(n * rb + 16));
+    CPB_TRY(h->s_out.reserve(rows * k * 4));
+    if (dist_out) CPB_TRY(h->s_out2.reserve(rows * k * 2));
+    CPB_CUDA(cudaMemcpy(h->s_in.p, codes, n * rb, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_knn_graph(h, h->s_in.p, n, k, row_begin, row_end, h->s_out.as<uint32_t>(),
+                             dist_out ? h->s_out2.as<uint16_t>() : nullptr, 0));
+    CPB_CUDA(cudaMemcpy(nbrs_out, h->s_out.p, rows * k * 4, cudaMemcpyDeviceToHost));
+    if (dist_out) CPB_CUDA(cudaMemcpy(dist_out, h->s_out2.p, rows * k * 2, cudaMemcpyDeviceToHost));
+    return check_status(h);
+}
+
+int cphnsw_b200_select_neighbors(cphnsw_b200_index* h, const void* codes, uint64_t n, const uint32_t* cand, uint32_t k,
+                                 uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned, uint32_t* adj_out) {
+    CPB_TRY(bind(h));
+    if (row_end <= row_begin) return 0;
+    if (!codes || !cand || !adj_out) { set_error("select_neighbors: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (row_end > n) { set_error("select_neighbors: row range exceeds n"); return CPHNSW_B200_E_INVALID; }
+    const size_t rb = code_row_bytes(h);
+    const uint64_t rows = row_end - row_begin;
+    CPB_TRY(h->s_in.reserve(n * rb + 16));
+    CPB_TRY(h->s_in2.reserve(rows * k * 4));
+    CPB_TRY(h->s_out.reserve(rows * M * 4));
+    CPB_CUDA(cudaMemcpy(h->s_in.p, codes, n * rb, cudaMemcpyHostToDevice));
+    CPB_CUDA(cudaMemcpy(h->s_in2.p, cand, rows * k * 4, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_select_neighbors(h, h->s_in.p, n, h->s_in2.as<uint32_t>(), k, row_begin, row_end, M, keep_pruned,
+                                    h->s_out.as<uint32_t>(), 0));
+    CPB_CUDA(cudaMemcpy(adj_out, h->s_out.p, rows * M * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_t n) {
+    CPB_TRY(bind(h));
+    if (n == 0) return 0;
+    if (!x) { set_error("add_batch_parallel: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (h->n && h->h_vectors.size() != h->n * h->dim) {
+        set_error("add_batch_parallel: the index was installed from device buffers and cannot be extended");
+        return CPHNSW_B200_E_STATE;
+    }
+    if (h->n + n >= 0xFFFFFFFFull) { set_error("add_batch_parallel: at most 2^32-2 nodes"); return CPHNSW_B200_E_INVALID; }
+    h->h_vectors.insert(h->h_vectors.end(), x, x + n * h->dim);
+    const uint64_t total = h->n + n;
+    CPB_TRY(h->d_vectors.reserve(total * h->dim * 4));
+    CPB_TRY(h->d_codes.reserve(total * code_row_bytes(h) + 16));
+    CPB_CUDA(cudaMemcpy(h->d_vectors.p, h->h_vectors.data(), total * h->dim * 4, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_encode(h, h->d_vectors.as<float>(), total, h->d_codes.p, nullptr, nullptr, 0));
+    h->n = total;
+    h->d_visited.release();  // sized by n
+    return build_graph(h, 0);
+}
+
+int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out) {
+    CPB_TRY(bind(h));
+    if (!codes_out) { set_error("get_codes: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (h->n) CPB_CUDA(cudaMemcpy(codes_out, h->d_codes.p, h->n * code_row_bytes(h), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_get_adjacency(const cphnsw_b200_index* h, uint32_t* adj_out) {
+    CPB_TRY(bind(h));
+    if (!adj_out) { set_error("get_adjacency: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (h->n) CPB_CUDA(cudaMemcpy(adj_out, h->d_adj.p, h->n * h->M * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uint64_t* count) {
+    CPB_TRY(bind(h));
+    if (count) *count = h->n_entry;
+    if (ids_out && h->n_entry) CPB_CUDA(cudaMemcpy(ids_out, h->d_entry.p, size_t(h->n_entry) * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
+                             uint32_t* ids_out, float* dists_out, uint32_t* stats_out) {
+    CPB_TRY(bind(h));
+    return do_search(h, q, false, nq, k, ef, 0, ids_out, dists_out, stats_out, false, 0);
+}
+
+int cphnsw_b200_search_and_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
+                                        uint32_t rerank_k, uint32_t* ids_out, float* dists_out, uint32_t* stats_out) {
+    CPB_TRY(bind(h));
+    if (rerank_k == 0) { set_error("search_and_rerank: rerank_k must be > 0"); return CPHNSW_B200_E_INVALID; }
+    return do_search(h, q, false, nq, k, ef, rerank_k, ids_out, dists_out, stats_out, false, 0);
+}
+
+}  // extern "C"

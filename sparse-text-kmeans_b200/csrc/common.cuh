@@ -1,0 +1,114 @@
+// Shared declarations of the cphnsw_b200 library: the index handle, error plumbing and the
+// launcher prototypes of each kernel family.  sm_100a only.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/cphnsw_b200.h"
+
+namespace cpb {
+
+constexpr uint32_t kInvalidNode = 0xFFFFFFFFu;
+
+// Device-side status word values raised by kernels (read with cphnsw_b200_check_device_status).
+constexpr uint32_t kStatusOk = 0;
+constexpr uint32_t kStatusWaitTimeout = 1;  // a bounded mbarrier wait ran out
+
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define CPB_CUDA(expr)                                        \
+    do {                                                      \
+        cudaError_t e__ = (expr);                             \
+        if (e__ != cudaSuccess) return cpb::cuda_fail(e__, #expr); \
+    } while (0)
+
+#define CPB_TRY(expr)             \
+    do {                          \
+        int rc__ = (expr);        \
+        if (rc__ != 0) return rc__; \
+    } while (0)
+
+// RAII device buffer (the library owns every scratch / index allocation through this).
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    DevBuf() = default;
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+    ~DevBuf() { release(); }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        bytes = 0;
+    }
+    // grow-only; contents are not preserved
+    int reserve(size_t n) {
+        if (n <= bytes && p) return 0;
+        release();
+        if (n == 0) n = 16;
+        CPB_CUDA(cudaMalloc(&p, n));
+        bytes = n;
+        return 0;
+    }
+    template <class T>
+    T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+}  // namespace cpb
+
+struct cphnsw_b200_index {
+    // parameters (CPHNSWParams, include/cphnsw/core/types.hpp:374-400)
+    uint64_t dim = 0, P = 0;
+    uint32_t K = 0, comp_bytes = 0, M = 0, ef_construction = 0;
+    uint64_t seed = 42;
+    int convention = CPHNSW_B200_FHT_AVX512;
+    int device = 0;
+    int keep_pruned = 1;
+    uint32_t k_entry = 4, knn_k = 0, entry_scan = 0;
+    int sm_count = 0;
+
+    std::vector<int8_t> signs;  // host [K][3][P]
+    cpb::DevBuf d_signs;        // float [K][3][P], +-1 with the FHT convention folded into layers 1,2
+    cpb::DevBuf d_status;       // uint32 status word
+
+    // index contents
+    uint64_t n = 0;
+    std::vector<float> h_vectors;  // host copy of everything added (rebuilds append to it)
+    cpb::DevBuf d_vectors, d_codes, d_adj, d_entry;
+    uint32_t n_entry = 0;
+
+    // search scratch
+    cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
+    // stage scratch for the host-pointer entry points
+    cpb::DevBuf s_in, s_in2, s_out, s_out2, s_pad, s_pad2;
+
+    uint64_t launches = 0;
+};
+
+namespace cpb {
+
+// padded code row width (32-bit words) used by the distance kernels: 4, 8 or 16; 0 = unsupported
+int code_row_words(uint32_t K, uint32_t comp_bytes);
+
+// ---- launchers (each returns 0 or a negative status and counts its launches in h) ----
+int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_codes, float* d_rot,
+                  float* d_mag, cudaStream_t st);
+int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, const void* d_b,
+                         uint64_t nb, uint16_t* d_out, cudaStream_t st);
+int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                     uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st);
+int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
+                            uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
+                            uint32_t* d_adj, cudaStream_t st);
+int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
+                  uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
+                  cudaStream_t st);
+// scratch the search kernel needs for an index of n nodes (visited bitsets, expansion lists)
+int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam);
+
+}  // namespace cpb

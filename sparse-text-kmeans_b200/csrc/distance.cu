@@ -1,0 +1,564 @@
+// CP-code distance, brute-force code-distance kNN graph and select_neighbors pruning.
+//
+// Distance between two codes = number of the K components that differ (the legacy
+// hamming_distance(CPCode,CPCode); use sites evaluation/debug_estimator.cpp:149,172).  All three
+// kernels work on code rows padded to 4, 8 or 16 32-bit words (zero padding on both sides never
+// differs) and count differing bytes / halfwords branch-free in SWAR form: a per-lane "nonzero"
+// flag is raised in the top bit of each byte of (a XOR b), flags of up to 8 (16) words are
+// packed into one register by shifting, and one popcount finishes the row.
+//
+// kNN graph (replaces GPUKNNGraphBuilder::build, src/cuda/gpu_knn_graph.cu:330-415, with the
+// CP-code metric): each warp owns Q query rows and sweeps every candidate; candidate tiles are
+// brought into shared memory by bulk asynchronous copies (cp.async.bulk + mbarrier, two stages)
+// issued by one thread; the running k+1 best of each row live in registers, spread over the
+// warp in sorted order, and are updated by shuffles.  Ties go to the lower id because
+// candidates arrive in ascending id order and only a strictly smaller distance displaces.
+#include "common.cuh"
+
+namespace cpb {
+namespace {
+
+constexpr uint32_t kFull = 0xffffffffu;
+
+// ---- SWAR component-mismatch count -------------------------------------------------------------
+template <int WC, bool U16>
+__device__ __forceinline__ uint32_t mismatch_count(const uint32_t (&a)[WC], const uint32_t (&b)[WC]) {
+    constexpr uint32_t LO = U16 ? 0x7fff7fffu : 0x7f7f7f7fu;
+    constexpr uint32_t HI = ~LO;
+    constexpr int G = U16 ? 16 : 8;  // words whose flags fit one accumulator
+    uint32_t d = 0;
+#pragma unroll
+    for (int g = 0; g < (WC + G - 1) / G; ++g) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int w = g * G; w < WC && w < (g + 1) * G; ++w) {
+            uint32_t x = a[w] ^ b[w];
+            uint32_t t = (x & LO) + LO;  // top bit of each lane set iff its low bits are non-zero
+            uint32_t y = t | x;          // ... or its own top bit is
+            acc |= (y >> (w - g * G)) & (HI >> (w - g * G));
+        }
+        d += __popc(acc);
+    }
+    return d;
+}
+
+// ---- pad [n][K] components to [n][WC] words ---------------------------------------------------------
+__global__ void pad_codes_kernel(const uint8_t* __restrict__ src, uint64_t n, int row_bytes, int WC,
+                                 uint32_t* __restrict__ dst) {
+    uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    uint64_t total = n * uint64_t(WC);
+    if (i >= total) return;
+    uint64_t row = i / WC;
+    int w = int(i % WC);
+    uint32_t v = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        int off = 4 * w + b;
+        if (off < row_bytes) v |= uint32_t(src[row * row_bytes + off]) << (8 * b);
+    }
+    dst[i] = v;
+}
+
+// ---- all-pairs distance matrix ---------------------------------------------------------------------
+constexpr int kCdThreads = 256;
+constexpr int kCdRowsA = 32;
+
+template <int WC, bool U16>
+__global__ void __launch_bounds__(kCdThreads)
+code_distance_kernel(const uint32_t* __restrict__ a, uint64_t na, const uint32_t* __restrict__ b,
+                     uint64_t nb, uint16_t* __restrict__ out) {
+    __shared__ uint32_t atile[kCdRowsA][WC];
+    const uint64_t a0 = uint64_t(blockIdx.y) * kCdRowsA;
+    const uint64_t j = uint64_t(blockIdx.x) * kCdThreads + threadIdx.x;
+    const int rows = int(min(uint64_t(kCdRowsA), na - a0));
+    for (int i = threadIdx.x; i < rows * WC; i += kCdThreads) (&atile[0][0])[i] = a[a0 * WC + i];
+    __syncthreads();
+    if (j >= nb) return;
+    uint32_t mine[WC];
+#pragma unroll
+    for (int w = 0; w < WC; w += 4) {
+        uint4 v = *reinterpret_cast<const uint4*>(b + j * WC + w);
+        mine[w] = v.x;
+        mine[w + 1] = v.y;
+        mine[w + 2] = v.z;
+        mine[w + 3] = v.w;
+    }
+    for (int i = 0; i < rows; ++i) {
+        uint32_t other[WC];
+#pragma unroll
+        for (int w = 0; w < WC; ++w) other[w] = atile[i][w];
+        out[(a0 + i) * nb + j] = uint16_t(mismatch_count<WC, U16>(other, mine));
+    }
+}
+
+// ---- mbarrier / bulk-copy helpers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a short,
+// hardware-bounded time) and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// 1-D bulk asynchronous copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// ---- kNN graph ---------------------------------------------------------------------------------------
+constexpr int kKnnWarps = 4;
+constexpr int kKnnThreads = kKnnWarps * 32;
+constexpr int kKnnTile = 1024;           // candidates per shared-memory stage
+constexpr uint32_t kWaitLimit = 1u << 22;  // polls before a wait is declared lost
+
+template <int WC, bool U16, int SLOTS, int Q>
+__global__ void __launch_bounds__(kKnnThreads)
+knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                 uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
+                 uint32_t* __restrict__ status) {
+    constexpr int CH = WC / 4;  // 16-byte chunks per code row
+    constexpr int CHLOG = CH == 1 ? 0 : (CH == 2 ? 1 : 2);
+    extern __shared__ __align__(128) unsigned char knn_smem[];
+    uint4* stage0 = reinterpret_cast<uint4*>(knn_smem);
+    uint4* stage1 = stage0 + size_t(kKnnTile) * CH;
+    __shared__ uint64_t full_bar[2];
+    __shared__ int abort_flag;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t tiles = (n + kKnnTile - 1) / kKnnTile;
+    auto tile_bytes = [&](uint64_t t) -> uint32_t {
+        uint64_t rows = min(uint64_t(kKnnTile), n - t * kKnnTile);
+        return uint32_t(rows * WC * 4);
+    };
+
+    if (threadIdx.x == 0) {
+        mbar_init(&full_bar[0], 1);
+        mbar_init(&full_bar[1], 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (uint64_t t = 0; t < 2 && t < tiles; ++t) {
+            mbar_expect_tx(&full_bar[t], tile_bytes(t));
+            bulk_g2s(t == 0 ? stage0 : stage1, codes + t * kKnnTile * WC, tile_bytes(t), &full_bar[t]);
+        }
+    }
+
+    // this warp's Q query rows, chunk order rotated per lane so that the shared-memory reads
+    // of a quarter-warp fall into distinct banks
+    const int rot = CH == 1 ? 0 : (lane >> (3 - CHLOG)) & (CH - 1);
+    const uint64_t first_row = row_begin + (uint64_t(blockIdx.x) * kKnnWarps + warp) * Q;
+    uint32_t qw[Q][WC];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        uint64_t row = min(first_row + q, row_end - 1);
+#pragma unroll
+        for (int s = 0; s < CH; ++s) {
+            int c = (s + rot) & (CH - 1);
+            uint4 v = __ldg(reinterpret_cast<const uint4*>(codes + row * WC) + c);
+            qw[q][4 * s] = v.x;
+            qw[q][4 * s + 1] = v.y;
+            qw[q][4 * s + 2] = v.z;
+            qw[q][4 * s + 3] = v.w;
+        }
+    }
+    // sorted running lists: element of rank (s*32 + lane) of row q
+    uint32_t ld[Q][SLOTS], li[Q][SLOTS], tau[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        tau[q] = kFull;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            ld[q][s] = kFull;
+            li[q][s] = kInvalidNode;
+        }
+    }
+
+    bool lost = false;
+    for (uint64_t t = 0; t < tiles; ++t) {
+        const int st = int(t & 1);
+        const uint32_t parity = uint32_t((t >> 1) & 1);
+        if (!mbar_wait_bounded(&full_bar[st], parity, kWaitLimit)) abort_flag = 1;
+        __syncthreads();
+        if (abort_flag) {
+            lost = true;
+            break;
+        }
+        const uint4* tile = st == 0 ? stage0 : stage1;
+        const uint64_t base = t * kKnnTile;
+        const int rows = int(min(uint64_t(kKnnTile), n - base));
+        for (int c0 = 0; c0 < rows; c0 += 32) {
+            const int c = c0 + lane;
+            uint32_t cw[WC];
+#pragma unroll
+            for (int s = 0; s < CH; ++s) {
+                uint4 v = tile[size_t(c) * CH + ((s + rot) & (CH - 1))];
+                cw[4 * s] = v.x;
+                cw[4 * s + 1] = v.y;
+                cw[4 * s + 2] = v.z;
+                cw[4 * s + 3] = v.w;
+            }
+            uint32_t d[Q];
+            bool any = false;
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+                d[q] = c < rows ? mismatch_count<WC, U16>(qw[q], cw) : kFull;
+                any |= d[q] < tau[q];
+            }
+            if (__any_sync(kFull, any)) {
+#pragma unroll
+                for (int q = 0; q < Q; ++q) {
+                    uint32_t m = __ballot_sync(kFull, d[q] < tau[q]);
+                    while (m) {
+                        const int src = __ffs(m) - 1;
+                        m &= m - 1;
+                        const uint32_t dd = __shfl_sync(kFull, d[q], src);
+                        if (dd >= tau[q]) continue;  // tightened by an earlier lane
+                        const uint32_t id = uint32_t(base + c0 + src);
+                        // rank = number of kept elements with distance <= dd (their ids are lower)
+                        int p = 0;
+#pragma unroll
+                        for (int s = 0; s < SLOTS; ++s) p += __popc(__ballot_sync(kFull, ld[q][s] <= dd));
+#pragma unroll
+                        for (int s = SLOTS - 1; s >= 0; --s) {
+                            uint32_t ud = __shfl_up_sync(kFull, ld[q][s], 1);
+                            uint32_t ui = __shfl_up_sync(kFull, li[q][s], 1);
+                            if (s > 0) {
+                                uint32_t cd = __shfl_sync(kFull, ld[q][s - 1], 31);
+                                uint32_t ci = __shfl_sync(kFull, li[q][s - 1], 31);
+                                if (lane == 0) {
+                                    ud = cd;
+                                    ui = ci;
+                                }
+                            }
+                            const int rank = s * 32 + lane;
+                            if (rank > p) {
+                                ld[q][s] = ud;
+                                li[q][s] = ui;
+                            } else if (rank == p) {
+                                ld[q][s] = dd;
+                                li[q][s] = id;
+                            }
+                        }
+                        // threshold = distance of the element of rank k (the (k+1)-th: room for self)
+                        uint32_t tk = kFull;
+#pragma unroll
+                        for (int s = 0; s < SLOTS; ++s) {
+                            const uint32_t v = __shfl_sync(kFull, ld[q][s], int(k & 31));
+                            if (s == int(k >> 5)) tk = v;
+                        }
+                        tau[q] = tk;
+                    }
+                }
+            }
+        }
+        __syncthreads();  // every warp is done with this stage
+        if (threadIdx.x == 0 && t + 2 < tiles) {
+            mbar_expect_tx(&full_bar[st], tile_bytes(t + 2));
+            bulk_g2s(st == 0 ? stage0 : stage1, codes + (t + 2) * kKnnTile * WC, tile_bytes(t + 2),
+                     &full_bar[st]);
+        }
+    }
+    if (lost) {
+        // report, then give copies still in flight a bounded chance to land before the block
+        // (and its shared memory) goes away
+        if (threadIdx.x == 0) {
+            atomicExch(status, kStatusWaitTimeout);
+            mbar_wait_bounded(&full_bar[0], 0, kWaitLimit);
+            mbar_wait_bounded(&full_bar[1], 0, kWaitLimit);
+        }
+        return;
+    }
+
+    // write the rows out, dropping the row's own id
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        const uint64_t row = first_row + q;
+        if (row >= row_end) continue;
+        int selfrank = 0x7fffffff, valid = 0;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            uint32_t ms = __ballot_sync(kFull, li[q][s] == uint32_t(row));
+            if (ms && selfrank == 0x7fffffff) selfrank = s * 32 + __ffs(ms) - 1;
+            valid += __popc(__ballot_sync(kFull, li[q][s] != kInvalidNode));
+        }
+        uint32_t* out_n = nbrs + (row - row_begin) * uint64_t(k);
+        uint16_t* out_d = dists ? dists + (row - row_begin) * uint64_t(k) : nullptr;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int rank = s * 32 + lane;
+            if (li[q][s] == kInvalidNode || rank == selfrank) continue;
+            const int o = rank - (rank > selfrank ? 1 : 0);
+            if (o < int(k)) {
+                out_n[o] = li[q][s];
+                if (out_d) out_d[o] = uint16_t(ld[q][s]);
+            }
+        }
+        int n_out = valid - (selfrank != 0x7fffffff ? 1 : 0);
+        for (int o = n_out + lane; o < int(k); o += 32) {
+            out_n[o] = kInvalidNode;
+            if (out_d) out_d[o] = 0xFFFF;
+        }
+    }
+}
+
+// ---- select_neighbors ----------------------------------------------------------------------------------
+// SELECT-NEIGHBORS-HEURISTIC with keepPrunedConnections (resources/hnsw-paper/consolidated.tex:93-115):
+// one warp per node; the kept set R lives in registers (member m on lane m%32, slot m/32), each
+// candidate is tested against all of R in one step.
+constexpr int kSelWarps = 4;
+constexpr int kSelMaxK = 64;
+
+template <int WC, bool U16>
+__global__ void __launch_bounds__(kSelWarps * 32)
+select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ cand, uint32_t k,
+                        uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
+                        uint32_t* __restrict__ adj) {
+    __shared__ uint32_t csm[kSelWarps][kSelMaxK][WC];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t row = row_begin + uint64_t(blockIdx.x) * kSelWarps + warp;
+    if (row >= row_end) return;
+    const uint32_t* crow = cand + (row - row_begin) * uint64_t(k);
+    uint32_t cid[2];
+    cid[0] = lane < int(k) ? crow[lane] : kInvalidNode;
+    cid[1] = lane + 32 < int(k) ? crow[lane + 32] : kInvalidNode;
+    uint32_t qc[WC];
+#pragma unroll
+    for (int w = 0; w < WC; w += 4) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(codes + row * WC + w));
+        qc[w] = v.x, qc[w + 1] = v.y, qc[w + 2] = v.z, qc[w + 3] = v.w;
+    }
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        const int t = lane + 32 * s;
+        if (cid[s] != kInvalidNode) {
+#pragma unroll
+            for (int w = 0; w < WC; w += 4) {
+                uint4 v = __ldg(reinterpret_cast<const uint4*>(codes + uint64_t(cid[s]) * WC + w));
+                csm[warp][t][w] = v.x, csm[warp][t][w + 1] = v.y, csm[warp][t][w + 2] = v.z,
+                csm[warp][t][w + 3] = v.w;
+            }
+        }
+    }
+    __syncwarp();
+
+    uint32_t rc[2][WC];
+    uint32_t rsize = 0;
+    unsigned long long kept = 0, disc = 0;
+    for (uint32_t t = 0; t < k && rsize < M; ++t) {
+        const uint32_t e = __shfl_sync(kFull, t < 32 ? cid[0] : cid[1], int(t & 31));
+        if (e == kInvalidNode) continue;
+        uint32_t ec[WC];
+#pragma unroll
+        for (int w = 0; w < WC; ++w) ec[w] = csm[warp][t][w];
+        const uint32_t d_eq = mismatch_count<WC, U16>(ec, qc);
+        bool viol = false;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            const uint32_t m = uint32_t(lane + 32 * s);
+            if (m < rsize) viol |= !(d_eq < mismatch_count<WC, U16>(ec, rc[s]));
+        }
+        if (__any_sync(kFull, viol)) {
+            disc |= 1ull << t;
+        } else {
+            kept |= 1ull << t;
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+                if (uint32_t(lane + 32 * s) == rsize) {
+#pragma unroll
+                    for (int w = 0; w < WC; ++w) rc[s][w] = ec[w];
+                }
+            ++rsize;
+        }
+    }
+    uint32_t* out = adj + (row - row_begin) * uint64_t(M);
+    const uint32_t n_disc = keep_pruned ? uint32_t(__popcll(disc)) : 0u;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        const int t = lane + 32 * s;
+        const unsigned long long below = (1ull << t) - 1ull;
+        uint32_t pos = kInvalidNode;
+        if ((kept >> t) & 1ull) pos = uint32_t(__popcll(kept & below));
+        else if (keep_pruned && ((disc >> t) & 1ull)) pos = rsize + uint32_t(__popcll(disc & below));
+        if (pos < M) out[pos] = cid[s];
+    }
+    const uint32_t total = min(M, rsize + n_disc);
+    for (uint32_t o = total + lane; o < M; o += 32) out[o] = kInvalidNode;
+}
+
+// ---- host-side dispatch ----------------------------------------------------------------------------------
+struct PaddedCodes {
+    const uint32_t* p = nullptr;
+};
+
+// Returns a [n][WC]-word view of the codes: the caller's buffer when rows are already WC words,
+// else a zero-padded copy in `scratch`.
+int padded_view(cphnsw_b200_index* h, const void* d_codes, uint64_t n, int WC, DevBuf& scratch,
+                cudaStream_t st, const uint32_t** out) {
+    const int row_bytes = int(h->K * h->comp_bytes);
+    if ((reinterpret_cast<uintptr_t>(d_codes) & 15) != 0 && row_bytes == WC * 4) {
+        set_error("device code buffer must be 16-byte aligned");
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (row_bytes == WC * 4) {
+        *out = static_cast<const uint32_t*>(d_codes);
+        return 0;
+    }
+    CPB_TRY(scratch.reserve(size_t(n) * WC * 4 + 16));
+    uint64_t total = n * uint64_t(WC);
+    if (total) {
+        pad_codes_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(d_codes), n,
+                                                                        row_bytes, WC, scratch.as<uint32_t>());
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+    }
+    *out = scratch.as<uint32_t>();
+    return 0;
+}
+
+}  // namespace
+
+int code_row_words(uint32_t K, uint32_t comp_bytes) {
+    uint32_t bytes = K * comp_bytes;
+    if (bytes <= 16) return 4;
+    if (bytes <= 32) return 8;
+    if (bytes <= 64) return 16;
+    return 0;
+}
+
+#define CPB_DISPATCH_WC(WCV, U16V, CALL)                                   \
+    do {                                                                   \
+        if (WCV == 4 && !(U16V)) { CALL(4, false); }                       \
+        else if (WCV == 4) { CALL(4, true); }                              \
+        else if (WCV == 8 && !(U16V)) { CALL(8, false); }                  \
+        else if (WCV == 8) { CALL(8, true); }                              \
+        else if (!(U16V)) { CALL(16, false); }                             \
+        else { CALL(16, true); }                                           \
+    } while (0)
+
+int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, const void* d_b, uint64_t nb,
+                         uint16_t* d_out, cudaStream_t st) {
+    if (na == 0 || nb == 0) return 0;
+    const int WC = code_row_words(h->K, h->comp_bytes);
+    if (!WC) {
+        set_error("code rows wider than 64 bytes are not supported by the distance kernels (K*component_bytes=%u)",
+                  h->K * h->comp_bytes);
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    const bool u16 = h->comp_bytes == 2;
+    const uint32_t *pa, *pb;
+    CPB_TRY(padded_view(h, d_a, na, WC, h->s_pad, st, &pa));
+    CPB_TRY(padded_view(h, d_b, nb, WC, h->s_pad2, st, &pb));
+    dim3 grid(unsigned((nb + kCdThreads - 1) / kCdThreads), unsigned((na + kCdRowsA - 1) / kCdRowsA));
+#define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out)
+    CPB_DISPATCH_WC(WC, u16, CALL);
+#undef CALL
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <int WC, bool U16, int SLOTS, int Q>
+static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
+                        uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    const size_t smem = size_t(2) * kKnnTile * WC * 4;
+    CPB_CUDA(cudaFuncSetAttribute(knn_graph_kernel<WC, U16, SLOTS, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  int(smem)));
+    const uint64_t rows = re - rb;
+    const uint64_t blocks = (rows + kKnnWarps * Q - 1) / (kKnnWarps * Q);
+    knn_graph_kernel<WC, U16, SLOTS, Q><<<unsigned(blocks), kKnnThreads, smem, st>>>(
+        codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>());
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <int WC, bool U16>
+static int launch_knn_slots(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
+                            uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    constexpr int Q = WC == 16 ? 4 : 8;
+    const uint32_t need = k + 1;  // the row's own id may occupy one place
+    if (need <= 64) return launch_knn_t<WC, U16, 2, Q>(h, codes, n, k, rb, re, nbrs, dist, st);
+    if (need <= 96) return launch_knn_t<WC, U16, 3, Q>(h, codes, n, k, rb, re, nbrs, dist, st);
+    return launch_knn_t<WC, U16, 4, Q>(h, codes, n, k, rb, re, nbrs, dist, st);
+}
+
+int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                     uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st) {
+    if (row_end <= row_begin) return 0;
+    if (k == 0 || k > 127) {
+        set_error("knn_graph: k must be in 1..127 (got %u)", k);
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (row_end > n) {
+        set_error("knn_graph: row range [%llu,%llu) exceeds n=%llu", (unsigned long long)row_begin,
+                  (unsigned long long)row_end, (unsigned long long)n);
+        return CPHNSW_B200_E_INVALID;
+    }
+    const int WC = code_row_words(h->K, h->comp_bytes);
+    if (!WC) {
+        set_error("code rows wider than 64 bytes are not supported by the distance kernels");
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    const bool u16 = h->comp_bytes == 2;
+    const uint32_t* pc;
+    CPB_TRY(padded_view(h, d_codes, n, WC, h->s_pad, st, &pc));
+#define CALL(W, U) return launch_knn_slots<W, U>(h, pc, n, k, row_begin, row_end, d_nbrs, d_dist, st)
+    CPB_DISPATCH_WC(WC, u16, CALL);
+#undef CALL
+    return 0;
+}
+
+int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
+                            uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
+                            uint32_t* d_adj, cudaStream_t st) {
+    if (row_end <= row_begin) return 0;
+    if (k == 0 || k > kSelMaxK || M == 0 || M > 64) {
+        set_error("select_neighbors: need 1 <= k <= 64 and 1 <= M <= 64 (got k=%u M=%u)", k, M);
+        return CPHNSW_B200_E_INVALID;
+    }
+    const int WC = code_row_words(h->K, h->comp_bytes);
+    if (!WC) {
+        set_error("code rows wider than 64 bytes are not supported by the distance kernels");
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    const bool u16 = h->comp_bytes == 2;
+    const uint32_t* pc;
+    CPB_TRY(padded_view(h, d_codes, n, WC, h->s_pad, st, &pc));
+    const uint64_t rows = row_end - row_begin;
+    const unsigned grid = unsigned((rows + kSelWarps - 1) / kSelWarps);
+#define CALL(W, U)                                                                                          \
+    select_neighbors_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_cand, k, row_begin, row_end, M,    \
+                                                                   keep_pruned, d_adj)
+    CPB_DISPATCH_WC(WC, u16, CALL);
+#undef CALL
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace cpb

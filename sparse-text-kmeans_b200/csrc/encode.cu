@@ -1,0 +1,304 @@
+// Cross-polytope encode: Psi(x) = H D3 H D2 H D1 x for K rotations, fused with the signed
+// argmax that produces one code component per rotation.
+//
+// What it computes follows the reference's RandomHadamardRotation::apply_copy
+// (include/cphnsw/encoder/rotation.hpp:90-111), fht (include/cphnsw/encoder/transform/fht.hpp),
+// detail::find_argmax_abs (include/cphnsw/encoder/cp_encoder.hpp:25-92) and CPCode::encode
+// (include/cphnsw/core/types.hpp:88-90).  Bit-exactness rests on three facts:
+//   * every butterfly is one IEEE add or subtract in the stage order h = 1, 2, 4, ... — the
+//     kernels use __fadd_rn/__fsub_rn (never contracted) in that order;
+//   * multiplying by a +-1 diagonal is exact, so folding it into the first butterfly stage as
+//     fma(s1, x1, s0*x0) rounds exactly like (s0*x0) + (s1*x1);
+//   * the reference's SIMD FHT differs from its scalar FHT only by negating element i when
+//     popcount(i & (W-1)) is odd (W = 8 AVX2, 16 AVX-512).  The host folds that diagonal into
+//     the sign tables of layers 1 and 2; the last one only decides the sign bit of the code
+//     (and the sign of the rotated output), applied here through `flip_mask` = W-1.
+//
+// Two kernels:
+//   encode_p128_kernel   padded dim 128 (d in 65..128): one thread owns one vector, the whole
+//                        128-point transform lives in registers (no shuffles, no barriers in the
+//                        inner loop); the bound is the fp32 add pipe.
+//   encode_generic_kernel any power-of-two padded dim: one warp owns one vector in shared memory.
+#include "common.cuh"
+
+namespace cpb {
+namespace {
+
+constexpr int kP128 = 128;
+constexpr int kTileVecs = 128;          // vectors per block = threads per block
+constexpr int kTileStride = kP128 + 1;  // padded row: thread t reads bank (t + i) & 31
+
+template <int H>
+__device__ __forceinline__ void butterfly_stage(float (&v)[kP128]) {
+#pragma unroll
+    for (int i = 0; i < kP128; i += 2 * H) {
+#pragma unroll
+        for (int j = i; j < i + H; ++j) {
+            float x = v[j], y = v[j + H];
+            v[j] = __fadd_rn(x, y);
+            v[j + H] = __fsub_rn(x, y);
+        }
+    }
+}
+
+// D then H on 128 registers.  `sg` points at 128 warp-uniform +-1 floats.
+__device__ __forceinline__ void diag_fht128(float (&v)[kP128], const float* __restrict__ sg) {
+    const float4* s4 = reinterpret_cast<const float4*>(sg);
+#pragma unroll
+    for (int c = 0; c < kP128 / 4; ++c) {
+        float4 s = __ldg(s4 + c);
+        {
+            float t = __fmul_rn(s.x, v[4 * c]);
+            float y = v[4 * c + 1];
+            v[4 * c] = __fmaf_rn(s.y, y, t);
+            v[4 * c + 1] = __fmaf_rn(-s.y, y, t);
+        }
+        {
+            float t = __fmul_rn(s.z, v[4 * c + 2]);
+            float y = v[4 * c + 3];
+            v[4 * c + 2] = __fmaf_rn(s.w, y, t);
+            v[4 * c + 3] = __fmaf_rn(-s.w, y, t);
+        }
+    }
+    butterfly_stage<2>(v);
+    butterfly_stage<4>(v);
+    butterfly_stage<8>(v);
+    butterfly_stage<16>(v);
+    butterfly_stage<32>(v);
+    butterfly_stage<64>(v);
+}
+
+// Lowest-index argmax of |v| by a left-biased tournament: the right operand wins only when it is
+// strictly larger, so among equal magnitudes the lowest index survives every round
+// (same answer as the strict `>` scan of cp_encoder.hpp:82-88).
+__device__ __forceinline__ void argmax128(const float (&v)[kP128], float& win, int& idx) {
+    float w[64];
+    int id[64];
+#pragma unroll
+    for (int j = 0; j < 64; ++j) {
+        bool r = fabsf(v[2 * j + 1]) > fabsf(v[2 * j]);
+        w[j] = r ? v[2 * j + 1] : v[2 * j];
+        id[j] = r ? 2 * j + 1 : 2 * j;
+    }
+#pragma unroll
+    for (int n = 32; n >= 1; n >>= 1) {
+#pragma unroll
+        for (int j = 0; j < n; ++j) {
+            bool r = fabsf(w[2 * j + 1]) > fabsf(w[2 * j]);
+            w[j] = r ? w[2 * j + 1] : w[2 * j];
+            id[j] = r ? id[2 * j + 1] : id[2 * j];
+        }
+    }
+    win = w[0];
+    idx = id[0];
+}
+
+// sign bit of the component: `value < 0` (cp_encoder.hpp:174) after the convention's last
+// diagonal, which negates the value when popcount(idx & flip_mask) is odd.
+__device__ __forceinline__ uint32_t component_of(float win, int idx, int flip_mask) {
+    bool flip = __popc(idx & flip_mask) & 1;
+    bool neg = flip ? (win > 0.0f) : (win < 0.0f);
+    return (uint32_t(idx) << 1) | (neg ? 1u : 0u);
+}
+
+// QUERY = true additionally writes the rotated vectors and winning magnitudes (CPQuery).
+template <typename CompT, bool QUERY>
+__global__ void __launch_bounds__(kTileVecs)
+encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
+                   const float* __restrict__ signs /*[K][3][128]*/, int flip_mask,
+                   CompT* __restrict__ codes, float* __restrict__ rotated, float* __restrict__ mags) {
+    extern __shared__ float smem[];
+    float* tile = smem;                                                 // [kTileVecs][kTileStride]
+    CompT* code_tile = reinterpret_cast<CompT*>(tile + kTileVecs * kTileStride);  // [kTileVecs][K]
+
+    const uint64_t row0 = uint64_t(blockIdx.x) * kTileVecs;
+    const int rows = int(min(uint64_t(kTileVecs), n - row0));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // stage the tile: coalesced 128-bit loads when rows are 16-byte aligned, else 32-bit loads
+    const bool vec4 = (dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    for (int r = warp; r < kTileVecs; r += kTileVecs / 32) {
+        float* dst = tile + r * kTileStride;
+        if (r < rows) {
+            const float* src = x + (row0 + r) * uint64_t(dim);
+            if (vec4) {
+                float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (4 * lane < dim) q = __ldg(reinterpret_cast<const float4*>(src) + lane);
+                dst[4 * lane] = q.x;
+                dst[4 * lane + 1] = q.y;
+                dst[4 * lane + 2] = q.z;
+                dst[4 * lane + 3] = q.w;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    int i = lane + 32 * c;
+                    dst[i] = i < dim ? __ldg(src + i) : 0.0f;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) dst[lane + 32 * c] = 0.0f;
+        }
+    }
+    __syncthreads();
+
+    const int t = threadIdx.x;
+    const float* mine = tile + t * kTileStride;
+    const uint64_t row = row0 + t;
+    for (int r = 0; r < K; ++r) {
+        float v[kP128];
+#pragma unroll
+        for (int i = 0; i < kP128; ++i) v[i] = mine[i];
+        const float* sg = signs + size_t(r) * 3 * kP128;
+        diag_fht128(v, sg);
+        diag_fht128(v, sg + kP128);
+        diag_fht128(v, sg + 2 * kP128);
+        float win;
+        int idx;
+        argmax128(v, win, idx);
+        code_tile[t * K + r] = CompT(component_of(win, idx, flip_mask));
+        if (QUERY && t < rows) {
+            if (mags) mags[row * K + r] = fabsf(win);
+            if (rotated) {
+                float4* out = reinterpret_cast<float4*>(rotated + (row * K + r) * kP128);
+#pragma unroll
+                for (int c = 0; c < kP128 / 4; ++c) {
+                    float4 o;
+                    o.x = (__popc((4 * c) & flip_mask) & 1) ? -v[4 * c] : v[4 * c];
+                    o.y = (__popc((4 * c + 1) & flip_mask) & 1) ? -v[4 * c + 1] : v[4 * c + 1];
+                    o.z = (__popc((4 * c + 2) & flip_mask) & 1) ? -v[4 * c + 2] : v[4 * c + 2];
+                    o.w = (__popc((4 * c + 3) & flip_mask) & 1) ? -v[4 * c + 3] : v[4 * c + 3];
+                    out[c] = o;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // the tile's codes are contiguous in the output: write them back coalesced
+    const int total = rows * K;
+    CompT* dst = codes + row0 * uint64_t(K);
+    for (int i = threadIdx.x; i < total; i += kTileVecs) dst[i] = code_tile[i];
+}
+
+// ---- generic padded dim: one warp per vector, transform in shared memory ----------------------
+template <typename CompT>
+__global__ void encode_generic_kernel(const float* __restrict__ x, uint64_t n, int dim, int P, int K,
+                                      const float* __restrict__ signs /*[K][3][P]*/, int flip_mask,
+                                      CompT* __restrict__ codes, float* __restrict__ rotated,
+                                      float* __restrict__ mags) {
+    extern __shared__ float smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float* buf = smem + size_t(warp) * P;
+    for (uint64_t row = uint64_t(blockIdx.x) * warps + warp; row < n; row += uint64_t(gridDim.x) * warps) {
+        const float* src = x + row * uint64_t(dim);
+        for (int r = 0; r < K; ++r) {
+            const float* sg = signs + size_t(r) * 3 * P;
+            for (int layer = 0; layer < 3; ++layer) {
+                // diagonal (layer 0 also loads and zero-pads)
+                for (int i = lane; i < P; i += 32) {
+                    float a = layer == 0 ? (i < dim ? __ldg(src + i) : 0.0f) : buf[i];
+                    buf[i] = __fmul_rn(a, sg[layer * P + i]);
+                }
+                __syncwarp();
+                for (int h = 1; h < P; h <<= 1) {
+                    for (int b = lane; b < P / 2; b += 32) {
+                        int j = ((b / h) * 2 * h) + (b % h);
+                        float a = buf[j], c = buf[j + h];
+                        buf[j] = __fadd_rn(a, c);
+                        buf[j + h] = __fsub_rn(a, c);
+                    }
+                    __syncwarp();
+                }
+            }
+            // lowest-index argmax: strided scan per lane (ascending index), then a warp
+            // reduction that prefers the lower index on equal magnitude
+            float best = -1.0f, win = 0.0f;  // -1: the first element a lane sees always wins
+            int idx = 0x7fffffff;
+            for (int i = lane; i < P; i += 32) {
+                float a = fabsf(buf[i]);
+                if (a > best) {
+                    best = a;
+                    win = buf[i];
+                    idx = i;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                float ow = __shfl_xor_sync(0xffffffffu, win, o);
+                int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ob > best || (ob == best && oi < idx)) {
+                    best = ob;
+                    win = ow;
+                    idx = oi;
+                }
+            }
+            if (lane == 0) {
+                codes[row * K + r] = CompT(component_of(win, idx, flip_mask));
+                if (mags) mags[row * K + r] = best;
+            }
+            if (rotated) {
+                float* out = rotated + (row * K + r) * uint64_t(P);
+                for (int i = lane; i < P; i += 32)
+                    out[i] = (__popc(i & flip_mask) & 1) ? -buf[i] : buf[i];
+            }
+            __syncwarp();
+        }
+    }
+}
+
+}  // namespace
+
+int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_codes, float* d_rot,
+                  float* d_mag, cudaStream_t st) {
+    if (n == 0) return 0;
+    const int P = int(h->P), K = int(h->K), dim = int(h->dim);
+    // width of the reference's in-register SIMD phase for this build and length
+    // (fht.hpp:141-147: AVX-512 defers to AVX2 below 16; :81-87: AVX2 defers to scalar below 8)
+    int w = 1;
+    if (h->convention == CPHNSW_B200_FHT_AVX512 && P >= 16) w = 16;
+    else if (h->convention >= CPHNSW_B200_FHT_AVX2 && P >= 8) w = 8;
+    const int flip_mask = w - 1;
+    const float* signs = h->d_signs.as<float>();
+
+    if (P == kP128) {
+        size_t smem = size_t(kTileVecs) * kTileStride * sizeof(float) + size_t(kTileVecs) * K * h->comp_bytes;
+        unsigned grid = unsigned((n + kTileVecs - 1) / kTileVecs);
+        const bool query = d_rot || d_mag;
+#define CPB_LAUNCH_P128(T, Q)                                                                              \
+    do {                                                                                                   \
+        CPB_CUDA(cudaFuncSetAttribute(encode_p128_kernel<T, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                      int(smem)));                                                         \
+        encode_p128_kernel<T, Q><<<grid, kTileVecs, smem, st>>>(d_x, n, dim, K, signs, flip_mask,           \
+                                                               (T*)d_codes, d_rot, d_mag);                  \
+    } while (0)
+        if (h->comp_bytes == 1) {
+            if (query) CPB_LAUNCH_P128(uint8_t, true);
+            else CPB_LAUNCH_P128(uint8_t, false);
+        } else {
+            if (query) CPB_LAUNCH_P128(uint16_t, true);
+            else CPB_LAUNCH_P128(uint16_t, false);
+        }
+#undef CPB_LAUNCH_P128
+    } else {
+        int warps = 4;
+        while (warps > 1 && size_t(warps) * P * sizeof(float) > 96 * 1024) warps >>= 1;
+        size_t smem = size_t(warps) * P * sizeof(float);
+        uint64_t blocks = (n + warps - 1) / warps;
+        unsigned grid = unsigned(blocks < uint64_t(h->sm_count) * 16 ? blocks : uint64_t(h->sm_count) * 16);
+        if (h->comp_bytes == 1) {
+            CPB_CUDA(cudaFuncSetAttribute(encode_generic_kernel<uint8_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+            encode_generic_kernel<uint8_t><<<grid, warps * 32, smem, st>>>(d_x, n, dim, P, K, signs, flip_mask,
+                                                                          (uint8_t*)d_codes, d_rot, d_mag);
+        } else {
+            CPB_CUDA(cudaFuncSetAttribute(encode_generic_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+            encode_generic_kernel<uint16_t><<<grid, warps * 32, smem, st>>>(d_x, n, dim, P, K, signs, flip_mask,
+                                                                           (uint16_t*)d_codes, d_rot, d_mag);
+        }
+    }
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace cpb

@@ -1,0 +1,229 @@
+"""GPU parity tests: every stage of the CUDA library, called through the C ABI, against the CPU
+oracle on the same seeded inputs.  Integer results (codes, code distances, neighbour lists, pruned
+lists, graph-walk ids) must be bit-exact; asymmetric distances are bit-exact too (same add order);
+reranked distances agree within 1e-5 relative."""
+import os
+
+import numpy as np
+import pytest
+
+from cphnsw_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+INVALID = 0xFFFFFFFF
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "encode_golden.npz"))
+CASES = [tuple(int(v) for v in row) for row in GOLD["cases"]]
+
+
+def make_index(cp, dim, K=32, cb=1, M=32, conv=2, **kw):
+    return cp.CPHNSWIndex(dim, M=M, ef_construction=max(200, M), K=K, component_bytes=cb, fht_convention=conv, **kw)
+
+
+# ---- encode ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("conv", [0, 1, 2])
+@pytest.mark.parametrize("ci", range(len(CASES)))
+def test_encode_matches_reference_golden(cp, conv, ci):
+    dim, K, cb, n = CASES[ci]
+    idx = make_index(cp, dim, K, cb, conv=conv)
+    P = idx.padded_dim
+    bits = np.unpackbits(GOLD["signs_%d" % ci])[: K * 3 * P].reshape(K, 3, P)
+    assert np.array_equal(idx.sign_tables(), np.where(bits > 0, 1, -1).astype(np.int8))
+    x = GOLD["x_%d" % ci]
+    assert np.array_equal(idx.encode(x), GOLD["codes_%d_c%d" % (ci, conv)])
+    key = "rot_%d_c%d" % (ci, conv)
+    if key in GOLD:
+        codes, rot, mag = idx.encode_queries(x[:4])
+        assert np.array_equal(codes, GOLD["codes_%d_c%d" % (ci, conv)][:4])
+        nz = GOLD[key] != 0
+        assert np.array_equal(rot[nz], GOLD[key][nz]) and (rot[~nz] == 0).all()
+        assert np.array_equal(mag, GOLD["mag_%d_c%d" % (ci, conv)])
+
+
+@pytest.mark.parametrize("dim,K,cb,n", [(128, 32, 1, 1), (128, 32, 1, 31), (128, 32, 1, 129), (128, 32, 1, 1000),
+                                        (96, 32, 1, 777), (100, 16, 1, 300), (65, 1, 1, 50), (128, 32, 2, 200),
+                                        (64, 32, 1, 500), (16, 16, 1, 100), (1, 4, 1, 9), (300, 16, 2, 100),
+                                        (960, 32, 2, 70), (1024, 4, 2, 33)])
+@pytest.mark.parametrize("conv", [0, 2])
+def test_encode_matches_oracle(cp, oracle, dim, K, cb, n, conv):
+    rng = np.random.default_rng(dim * 1000 + n)
+    x = rng.standard_normal((n, dim)).astype(np.float32)
+    if n > 3:
+        x[1] = 0
+        x[2] = np.abs(x[2])
+    idx = make_index(cp, dim, K, cb, conv=conv)
+    signs = oracle.sign_tables(dim, K, 42)
+    assert np.array_equal(idx.sign_tables(), signs)
+    want, wrot, wmag = oracle.encode(x, K, cb, signs, conv, want_rotated=True)
+    assert np.array_equal(idx.encode(x), want)
+    codes, rot, mag = idx.encode_queries(x)
+    assert np.array_equal(codes, want)
+    assert np.array_equal(mag, wmag)
+    nz = wrot != 0
+    assert np.array_equal(rot[nz], wrot[nz]) and (rot[~nz] == 0).all()
+
+
+def test_encode_empty_and_custom_signs(cp, oracle):
+    idx = make_index(cp, 128)
+    assert idx.encode(np.zeros((0, 128), np.float32)).shape == (0, 32)
+    rng = np.random.default_rng(5)
+    signs = np.where(rng.integers(0, 2, (32, 3, 128)) > 0, 1, -1).astype(np.int8)
+    idx.set_sign_tables(signs)
+    x = rng.standard_normal((100, 128)).astype(np.float32)
+    assert np.array_equal(idx.encode(x), oracle.encode(x, 32, 1, signs, 2))
+    with pytest.raises(ValueError):
+        idx.set_sign_tables(np.zeros((32, 3, 128), np.int8))
+
+
+# ---- code distance ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("K,cb", [(32, 1), (16, 1), (64, 1), (32, 2), (16, 2), (5, 1), (7, 2), (1, 1)])
+def test_code_distance_matches_oracle(cp, oracle, K, cb):
+    rng = np.random.default_rng(K * 10 + cb)
+    dt = np.uint8 if cb == 1 else np.uint16
+    hi = 256 if cb == 1 else 2048
+    a = rng.integers(0, hi, (45, K)).astype(dt)
+    b = rng.integers(0, hi, (300, K)).astype(dt)
+    b[:45] = np.where(rng.random((45, K)) < 0.5, a, b[:45])  # plenty of equal components
+    idx = make_index(cp, 128 if cb == 1 else 1024, K, cb)
+    assert np.array_equal(idx.code_distance(a, b), oracle.code_distance(a, b))
+    assert idx.code_distance(a[:0], b).shape == (0, 300)
+
+
+# ---- kNN graph ------------------------------------------------------------------------------------------
+def clustered_codes(oracle, n, dim, K, cb, seed):
+    base, _ = synthetic.gaussian_mixture(n, 1, dim, max(2, n // 200), 0.3, seed)
+    return base, oracle.encode(base, K, cb, oracle.sign_tables(dim, K, 42))
+
+
+@pytest.mark.parametrize("n,k,K,cb,dim", [(1, 4, 32, 1, 128), (2, 4, 32, 1, 128), (33, 40, 32, 1, 128),
+                                          (1000, 32, 32, 1, 128), (2500, 64, 32, 1, 128), (3000, 10, 16, 1, 64),
+                                          (1500, 32, 32, 2, 256), (1200, 100, 32, 1, 128), (900, 16, 12, 1, 32),
+                                          (5000, 32, 32, 1, 96)])
+def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim):
+    _, codes = clustered_codes(oracle, n, dim, K, cb, n + k)
+    idx = make_index(cp, dim, K, cb)
+    nbrs, dist = idx.knn_graph(codes, k)
+    wn, wd = oracle.knn_graph(codes, k)
+    assert np.array_equal(nbrs, wn)
+    assert np.array_equal(dist, wd)
+    if n > 64:  # a row block, as a shard would compute it
+        rb, re = n // 3, n // 3 + 50
+        pn, pd = idx.knn_graph(codes, k, rb, re)
+        assert np.array_equal(pn, wn[rb:re]) and np.array_equal(pd, wd[rb:re])
+
+
+def test_knn_graph_massive_ties_break_by_id(cp, oracle):
+    codes = np.zeros((700, 32), np.uint8)
+    codes[::7, 0] = 3  # two classes; within a class every distance is 0
+    idx = make_index(cp, 128)
+    nbrs, dist = idx.knn_graph(codes, 20)
+    wn, wd = oracle.knn_graph(codes, 20)
+    assert np.array_equal(nbrs, wn) and np.array_equal(dist, wd)
+
+
+# ---- select_neighbors ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n,k,M,K,cb,dim,keep", [(1500, 64, 32, 32, 1, 128, True), (1500, 64, 32, 32, 1, 128, False),
+                                                 (800, 32, 32, 32, 1, 128, True), (800, 40, 16, 16, 1, 64, True),
+                                                 (600, 64, 64, 32, 2, 256, True), (40, 64, 32, 32, 1, 128, True),
+                                                 (500, 20, 8, 12, 1, 32, False)])
+def test_select_neighbors_matches_oracle(cp, oracle, n, k, M, K, cb, dim, keep):
+    _, codes = clustered_codes(oracle, n, dim, K, cb, n + M)
+    cand, _ = oracle.knn_graph(codes, k)
+    idx = make_index(cp, dim, K, cb, M=M)
+    got = idx.select_neighbors(codes, cand, M, keep)
+    assert np.array_equal(got, oracle.select_neighbors(codes, cand, M, keep))
+    rb = n // 4
+    part = idx.select_neighbors(codes, cand[rb:rb + 30], M, keep, row_begin=rb)
+    assert np.array_equal(part, got[rb:rb + 30])
+
+
+# ---- index build + search --------------------------------------------------------------------------------------
+def oracle_index(oracle, base, K, cb, M, knn_k, conv=2):
+    signs = oracle.sign_tables(base.shape[1], K, 42)
+    codes = oracle.encode(base, K, cb, signs, conv)
+    cand, _ = oracle.knn_graph(codes, knn_k)
+    return signs, codes, oracle.select_neighbors(codes, cand, M, True)
+
+
+@pytest.mark.parametrize("n,dim,K,cb,M,scan", [(4000, 128, 32, 1, 32, 64), (3000, 96, 32, 1, 16, 4),
+                                               (1500, 200, 16, 2, 32, 32), (50, 128, 32, 1, 32, 4)])
+def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan):
+    base, q = synthetic.gaussian_mixture(n, 60, dim, max(2, n // 250), 0.3, n)
+    idx = make_index(cp, dim, K, cb, M=M)
+    idx.set_param("entry_scan", scan)
+    idx.add_batch_parallel(base)
+    assert idx.size() == n
+    knn_k = min(64, 2 * M)
+    signs, codes, adj = oracle_index(oracle, base, K, cb, M, knn_k)
+    assert np.array_equal(idx.codes(), codes)                 # stored code == fresh code
+    assert np.array_equal(idx.adjacency(), adj)
+    entry = idx.entry_ids()
+    assert np.array_equal(entry, (np.arange(min(scan, n), dtype=np.uint64) * n // min(scan, n)).astype(np.uint32))
+    _, rot, _ = oracle.encode(q, K, cb, signs, 2, want_rotated=True)
+    for k, ef in ((10, 10), (10, 100), (50, 20), (1, 300)):
+        ids, dist, stats = idx.search_batch(q, k, ef, want_stats=True)
+        wi, wd, ws = oracle.search(rot, codes, adj, entry, max(ef, k), k, want_stats=True)
+        assert np.array_equal(ids, wi), (k, ef)
+        assert np.array_equal(dist, wd)
+        assert np.array_equal(stats, ws)
+    # search_and_rerank: the candidate set is bit-exact, reranked distances agree to 1e-5 relative
+    for k, ef, rr in ((10, 50, 200), (10, 400, 100), (5, 10, 5)):
+        ids, dist = idx.search_and_rerank_batch(q, k, ef, rr)
+        cand, _ = oracle.search(rot, codes, adj, entry, max(ef, rr), rr)
+        wi, wd = oracle.rerank(q, base, cand, k)
+        valid = wi != INVALID
+        assert np.array_equal(ids == INVALID, ~valid)
+        assert np.allclose(dist[valid], wd[valid], rtol=1e-5, atol=1e-6)
+        # ids may swap only where two reranked distances are within the tolerance
+        for qi in range(q.shape[0]):
+            if not np.array_equal(ids[qi], wi[qi]):
+                assert set(ids[qi].tolist()) ^ set(wi[qi].tolist()) == set() or \
+                    np.allclose(np.sort(dist[qi][valid[qi]]), np.sort(wd[qi][valid[qi]]), rtol=1e-5, atol=1e-6)
+    # single-query forms return what the batch forms return
+    one = idx.search_and_rerank(q[0], 10, 50, 200)
+    ids, dist = idx.search_and_rerank_batch(q[:1], 10, 50, 200)
+    assert [i for i, _ in one] == [int(i) for i in ids[0] if i != INVALID]
+
+
+def test_identity_queries_and_ordering(cp):
+    # evaluation/qa_protocol.cpp:65-166: querying a stored vector returns its own id first with a
+    # negative distance; results ascend
+    base, _ = synthetic.gaussian_sphere(3000, 1, 128, 11)
+    idx = make_index(cp, 128)
+    idx.set_param("entry_scan", 3000)
+    idx.add_batch_parallel(base)
+    ids, dist = idx.search_and_rerank_batch(base[:50], 10, 100, 200)
+    assert (ids[:, 0] == np.arange(50)).all()
+    assert np.allclose(dist[:, 0], -1.0, atol=1e-5)
+    assert (np.diff(dist, axis=1) >= 0).all()
+    ids, dist = idx.search_batch(base[:50], 10, 100)
+    assert (ids[:, 0] == np.arange(50)).all() and (dist[:, 0] < 0).all()
+
+
+def test_add_batch_appends_and_rebuilds(cp, oracle):
+    base, _ = synthetic.gaussian_mixture(1200, 1, 128, 5, 0.3, 9)
+    a = make_index(cp, 128)
+    a.add_batch(base[:500])
+    a.add_batch_parallel(base[500:])
+    nid = a.add(base[0])
+    assert nid == 1200 and a.size() == 1201
+    b = make_index(cp, 128)
+    b.add_batch_parallel(np.concatenate([base, base[:1]]))
+    assert np.array_equal(a.codes(), b.codes()) and np.array_equal(a.adjacency(), b.adjacency())
+
+
+def test_errors_do_not_exit(cp):
+    idx = make_index(cp, 128)
+    with pytest.raises(cp.CPHNSWError):
+        idx.search_batch(np.zeros((1, 128), np.float32), 10, 10)  # empty index
+    base, _ = synthetic.gaussian_sphere(100, 1, 128, 1)
+    idx.add_batch_parallel(base)
+    with pytest.raises(ValueError):
+        idx.search_and_rerank_batch(base[:2], 10, 10, 5)  # rerank_k < k
+    with pytest.raises(ValueError):
+        idx.search_batch(base[:2], 10, 5000)  # beam too wide
+    with pytest.raises(ValueError):
+        idx.knn_graph(idx.codes(), 500)
+    with pytest.raises(ValueError):
+        idx.set_param("k_entry", 0)
+    ids, _ = idx.search_batch(base[:2], 10, 10)  # still usable
+    assert ids.shape == (2, 10)

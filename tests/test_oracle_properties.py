@@ -1,0 +1,146 @@
+"""Properties of the oracle's distance / kNN / select_neighbors / search / rerank restatements,
+cross-checked against independent numpy formulations (the reference's legacy sources for these
+are absent, so these pin the oracle's own definitions)."""
+import numpy as np
+import pytest
+
+from cphnsw_b200 import synthetic
+
+INVALID = 0xFFFFFFFF
+
+
+def small_index(oracle, n=600, nq=20, dim=32, K=16, seed=3, cb=1):
+    base, q = synthetic.gaussian_mixture(n, nq, dim, 6, 0.3, seed)
+    signs = oracle.sign_tables(dim, K, 42)
+    codes = oracle.encode(base, K, cb, signs)
+    return base, q, signs, codes
+
+
+def test_code_distance_counts_differing_components(oracle):
+    rng = np.random.default_rng(0)
+    for dt in (np.uint8, np.uint16):
+        a = rng.integers(0, 6, (17, 32)).astype(dt)
+        b = rng.integers(0, 6, (23, 32)).astype(dt)
+        want = (a[:, None, :] != b[None, :, :]).sum(-1).astype(np.uint16)
+        assert np.array_equal(oracle.code_distance(a, b), want)
+    # identical code -> 0 (evaluation/debug_code_storage.cpp:63-105)
+    assert (np.diag(oracle.code_distance(a, a)) == 0).all()
+
+
+def test_knn_graph_against_full_sort(oracle):
+    base, q, signs, codes = small_index(oracle)
+    n = codes.shape[0]
+    k = 10
+    nbrs, dist = oracle.knn_graph(codes, k)
+    D = oracle.code_distance(codes, codes).astype(np.int64)
+    for i in range(n):
+        order = sorted((int(D[i, j]), j) for j in range(n) if j != i)[:k]
+        assert nbrs[i].tolist() == [j for _, j in order]
+        assert dist[i].tolist() == [d for d, _ in order]
+    assert not (nbrs == np.arange(n)[:, None]).any()  # no self loops (evaluation/debug_gpu_knn.cpp:42-68)
+    # row-range form returns the same rows
+    part, _ = oracle.knn_graph(codes, k, 100, 164)
+    assert np.array_equal(part, nbrs[100:164])
+
+
+def test_knn_graph_pads_small_inputs(oracle):
+    codes = np.random.default_rng(1).integers(0, 4, (5, 8)).astype(np.uint8)
+    nbrs, dist = oracle.knn_graph(codes, 8)
+    assert (nbrs[:, 4:] == INVALID).all() and (dist[:, 4:] == 0xFFFF).all()
+    assert (np.sort(nbrs[:, :4], axis=1) == np.array([[j for j in range(5) if j != i] for i in range(5)])).all()
+
+
+def select_py(codes, i, cand, M, keep):
+    def d(a, b):
+        return int((codes[a] != codes[b]).sum())
+    R, Wd = [], []
+    for e in cand:
+        if len(R) >= M:
+            break
+        if e == INVALID:
+            continue
+        (R if all(d(e, i) < d(e, r) for r in R) else Wd).append(int(e))
+    if keep:
+        R += Wd[: max(0, M - len(R))]
+    return R + [INVALID] * (M - len(R))
+
+
+@pytest.mark.parametrize("keep", [True, False])
+def test_select_neighbors_matches_python(oracle, keep):
+    base, q, signs, codes = small_index(oracle, n=300)
+    nbrs, _ = oracle.knn_graph(codes, 24)
+    nbrs[5, 20:] = INVALID
+    adj = oracle.select_neighbors(codes, nbrs, 12, keep)
+    for i in range(codes.shape[0]):
+        assert adj[i].tolist() == select_py(codes, i, nbrs[i], 12, keep), i
+    if keep:  # with k <= M nothing is dropped, only reordered
+        adj2 = oracle.select_neighbors(codes, nbrs, 24, True)
+        assert np.array_equal(np.sort(adj2, axis=1), np.sort(nbrs, axis=1))
+
+
+def test_search_is_exhaustive_when_beam_covers_component(oracle):
+    """With ef >= n and a connected graph the walk visits everything, so it must return the exact
+    top-k under the asymmetric score; results are ascending (evaluation/qa_protocol.cpp:116-166)."""
+    base, q, signs, codes = small_index(oracle, n=400, dim=32, K=16)
+    n = codes.shape[0]
+    _, rot, _ = oracle.encode(q, 16, 1, signs, want_rotated=True)
+    # ring + kNN edges: connected
+    nbrs, _ = oracle.knn_graph(codes, 7)
+    adj = np.concatenate([nbrs, ((np.arange(n) + 1) % n)[:, None].astype(np.uint32)], axis=1)
+    ids, dist = oracle.search(rot, codes, adj, np.array([0], np.uint32), n, 10)
+    P = rot.shape[2]
+    for qi in range(q.shape[0]):
+        score = np.zeros(n, np.float32)
+        for r in range(16):
+            v = rot[qi, r, codes[:, r] >> 1]
+            score = score + np.where(codes[:, r] & 1, -v, v).astype(np.float32)
+        order = sorted((float(-score[j]), j) for j in range(n))[:10]
+        assert ids[qi].tolist() == [j for _, j in order]
+        assert np.array_equal(dist[qi], np.array([d for d, _ in order], np.float32))
+        assert (np.diff(dist[qi]) >= 0).all()
+
+
+def test_identity_query_scores_sum_of_magnitudes(oracle):
+    # Score(X, Code_X) = sum of winning magnitudes (evaluation/debug_estimator.cpp:74-82)
+    base, q, signs, codes = small_index(oracle, n=50)
+    c, rot, mag = oracle.encode(base[:5], 16, 1, signs, want_rotated=True)
+    for i in range(5):
+        s = np.float32(0)
+        for r in range(16):
+            v = rot[i, r, c[i, r] >> 1]
+            s = np.float32(s + (-v if c[i, r] & 1 else v))
+        assert np.isclose(s, mag[i].sum(), rtol=1e-5)
+
+
+def test_recall_non_decreasing_in_beam_and_rerank_orders(oracle):
+    base, q, signs, codes = small_index(oracle, n=2000, nq=40, dim=64, K=16)
+    _, rot, _ = oracle.encode(q, 16, 1, signs, want_rotated=True)
+    nbrs, _ = oracle.knn_graph(codes, 32)
+    adj = oracle.select_neighbors(codes, nbrs, 16)
+    entry = (np.arange(64) * 2000 // 64).astype(np.uint32)
+    gt = oracle.ground_truth(q, base, 10)
+    last = -1.0
+    for ef in (20, 80, 320):  # evaluation/qa_protocol.cpp:559-640
+        ids, _ = oracle.search(rot, codes, adj, entry, ef, ef)
+        rid, rd = oracle.rerank(q, base, ids, 10)
+        r = oracle.recall_at_k(rid, gt, 10)
+        assert r >= last - 1e-9
+        last = r
+        assert (np.diff(rd, axis=1) >= 0).all()
+        # reranked distance is -<q,x>
+        for qi in range(3):
+            assert np.allclose(rd[qi], -(base[rid[qi]] @ q[qi]), rtol=1e-5, atol=1e-6)
+    assert last > 0.5
+
+
+def test_zero_vector_and_duplicates_do_not_break(oracle):
+    # evaluation/qa_protocol.cpp:409-553: N < batch, duplicates, zero vector -> no NaN
+    dim, K = 16, 8
+    x = np.zeros((4, dim), np.float32)
+    x[1, 0] = 1.0
+    x[2] = x[1]
+    signs = oracle.sign_tables(dim, K, 42)
+    codes, rot, mag = oracle.encode(x, K, 1, signs, want_rotated=True)
+    assert (codes[0] == 0).all()  # all-zero rotation: index 0, positive
+    assert np.array_equal(codes[1], codes[2])
+    assert np.isfinite(rot).all()
