@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the CP-HNSW hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload C2] [--scale S]
+
+One "step" is one batched ``search_and_rerank`` pass over this rank's query batch (10,000 queries of
+the clustered 1M x 128 workload by default) against the replicated index.  Before the timed region
+the index is built on the GPUs (encode -> all-gather of codes -> code-distance kNN graph ->
+select_neighbors -> all-gather of adjacency), sharded by row block across the ranks; the build's
+stage throughputs are reported in the same JSON line.
+
+``value`` is queries/s with the queries already resident in HBM (device pointers in, device
+pointers out), timed with CUDA events on the launching stream, max over ranks.  ``e2e`` is the same
+metric through the host-pointer C-ABI call (pinned host buffers, H2D and D2H inside the timed region).
+``--impl reference`` times the CPU oracle (the reference's algorithm restated; its legacy sources
+for this path are absent from its tree) on the box's host cores, on a bounded sample.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "sparse-text-kmeans_b200"))
+
+METRIC = "batch-search QPS @ recall@10>=0.9 (search_and_rerank)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="C2")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink base/queries/clusters together (testing)")
+    ap.add_argument("--ef", type=int, default=None)
+    ap.add_argument("--rerank-k", type=int, default=None)
+    ap.add_argument("--entry-scan", type=int, default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.samples = []
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples for i in range(4) if s[2 + i].lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def overrides(w, args):
+    if args.ef is not None:
+        w["ef"] = args.ef
+    if args.rerank_k is not None:
+        w["rerank_k"] = args.rerank_k
+    if args.entry_scan is not None:
+        w["entry_scan"] = args.entry_scan
+    return w
+
+
+def oracle_index(O, w):
+    """Builds the workload's index with the CPU oracle (setup for the CPU arms; untimed)."""
+    base = w["base"]
+    K, cb, M = w["K"], w["component_bytes"], w["M"]
+    signs = O.sign_tables(base.shape[1], K, 42)
+    codes = O.encode(base, K, cb, signs, O.FHT_AVX512)
+    cand, _ = O.knn_graph(codes, w.get("knn_k", min(64, 2 * M)))
+    adj = O.select_neighbors(codes, cand, M, True)
+    n = base.shape[0]
+    scan = min(w["entry_scan"], n)
+    entry = (np.arange(scan, dtype=np.uint64) * n // scan).astype(np.uint32)
+    return signs, codes, adj, entry
+
+
+def cpu_sample(args, n_queries):
+    """The bounded CPU sample of the workload: the same generator scaled so that the oracle's
+    O(n^2) graph build stays within a minute (cluster population, entry scan and beam unchanged)."""
+    from cphnsw_b200 import synthetic
+    scale = min(args.scale, 50_000.0 / full_base_size(args.workload))
+    w = overrides(synthetic.workload(args.workload, scale), args)
+    w["entry_scan"] = min(full_entry_scan(args), w["base"].shape[0])
+    w["queries"] = w["queries"][:n_queries]
+    return w, scale
+
+
+def cpu_steps(args, n_queries, steps, warmup):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+    w, scale = cpu_sample(args, n_queries)
+    signs, codes, adj, entry = oracle_index(O, w)
+    base, q, K, cb = w["base"], w["queries"], w["K"], w["component_bytes"]
+    beam = max(w["ef"], w["rerank_k"], w["k"])
+
+    def step():
+        _, rot, _ = O.encode(q, K, cb, signs, O.FHT_AVX512, want_rotated=True)
+        cands, _ = O.search(rot, codes, adj, entry, beam, w["rerank_k"])
+        return O.rerank(q, base, cands, w["k"])
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ids, _ = step()
+    dt = (time.perf_counter() - t0) / steps
+    recall = O.recall_at_k(ids, O.ground_truth(q, base, w["k"]), w["k"])
+    sample = ("%d queries per step on an index of %d points (%s at %.3g of its size, same cluster population; "
+              "entry_scan=%d, beam=%d, rerank_k=%d); CPU oracle with OpenMP - the reference's legacy search sources are "
+              "absent from its tree" % (q.shape[0], base.shape[0], w["name"], scale, entry.size, beam, w["rerank_k"]))
+    return w, q.shape[0] / dt, dt, recall, O.num_threads(), sample
+
+
+def run_reference(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    w, qps, dt, recall, cores, sample = cpu_steps(args, 500, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "k": w["k"], "ef": w["ef"], "rerank_k": w["rerank_k"], "K": w["K"], "M": w["M"]},
+        "recall_at_10": recall,
+        "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def full_base_size(name):
+    return {"C1": 100_000, "C2": 1_000_000, "C3": 1_000_000, "C4": 10_000_000, "C5": 10_000_000}[name]
+
+
+def full_entry_scan(args):
+    if args.entry_scan is not None:
+        return args.entry_scan
+    return {"C2": 8192, "C5": 8192, "C4": 65536}.get(args.workload, 4)
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    import cphnsw_b200 as cp
+    from cphnsw_b200 import sharded, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if cp.device_count() < 1:
+        raise SystemExit("bench.py needs a B200: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # weak scaling of the search: every rank answers its own batch of queries (an independent stream
+    # of the same distribution) against the replicated index
+    w = overrides(synthetic.workload(args.workload, args.scale, query_stream=rank), args)
+    base, K, cb, M, dim = w["base"], w["K"], w["component_bytes"], w["M"], w["base"].shape[1]
+    n = base.shape[0]
+    queries = w["queries"]
+    nq = queries.shape[0]
+    k, ef, rerank_k = w["k"], w["ef"], w["rerank_k"]
+    knn_k = w.get("knn_k", min(64, 2 * M))
+
+    idx = cp.CPHNSWIndex(dim, M=M, ef_construction=w["ef_construction"], K=K, component_bytes=cb, device=local_rank)
+    idx.set_param("entry_scan", w["entry_scan"])
+    idx.set_param("profile", 1)
+
+    # ---- build (sharded by row block), each stage timed with CUDA events, max over ranks ----
+    rb, re = sharded.shard_range(n, rank, world)
+    d_base = torch.from_numpy(base).to(dev)
+    stage_ms = {}
+
+    class Timer:
+        def __init__(self, name):
+            self.name = name
+
+        def __enter__(self):
+            barrier()
+            self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+
+        def __exit__(self, *a):
+            self.e1.record()
+            torch.cuda.synchronize()
+            stage_ms[self.name] = max_over_ranks(self.e0.elapsed_time(self.e1))
+
+    stages = sharded.CudaStages(idx)
+    # untimed warm pass of the encode kernel (first-launch overheads), then the timed build
+    stages.encode(d_base[rb:min(re, rb + 4096)])
+    codes_all, adj_all = sharded.build_sharded(stages, d_base[rb:re], n, rank, world, dist if world > 1 else None, knn_k, M,
+                                               True, timers=Timer)
+    idx.check_device_status()
+    idx.install_dev(d_base.data_ptr(), codes_all.data_ptr(), adj_all.data_ptr(), n)
+    for kind in ("encode", "knn_graph", "select_neighbors"):
+        idx.kernel_time(kind)  # reset the per-kernel records
+
+    # ---- ground truth for this rank's queries: exact cosine top-k (fp32 matmul, measurement support) ----
+    d_q = torch.from_numpy(queries).to(dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    gt = torch.empty((nq, k), dtype=torch.int64, device=dev)
+    for q0 in range(0, nq, 1024):
+        sims = d_q[q0:q0 + 1024] @ d_base.T
+        gt[q0:q0 + 1024] = sims.topk(k, dim=1).indices
+    gt = gt.cpu().numpy()
+    del sims
+
+    d_ids = torch.empty((nq, k), dtype=torch.int32, device=dev)
+    d_dist = torch.empty((nq, k), dtype=torch.float32, device=dev)
+    d_stats = torch.zeros((nq, 2), dtype=torch.int32, device=dev)
+
+    def step_resident():
+        idx.search_dev(d_q.data_ptr(), nq, k, ef, rerank_k, d_ids.data_ptr(), d_dist.data_ptr(), d_stats.data_ptr())
+
+    # ---- timed region 1: inputs resident in HBM ----
+    for _ in range(max(3, args.warmup)):
+        step_resident()
+    barrier()
+    idx.kernel_time("search")
+    idx.kernel_time("encode")
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = idx.launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = idx.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    search_ms, search_launches = idx.kernel_time("search")
+    qenc_ms, _ = idx.kernel_time("encode")
+    ms_per_step = ms_total / args.steps
+    value = world * nq / (ms_per_step * 1e-3)
+
+    ids = d_ids.cpu().numpy().astype(np.uint32)
+    stats = d_stats.cpu().numpy()
+    recall = sharded.recall_at_k(ids, gt, k)
+    if world > 1:
+        t = torch.tensor([recall], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        recall = float(t.item()) / world
+
+    # ---- timed region 2: end to end through the host-pointer C ABI (pinned host buffers) ----
+    h_q = torch.from_numpy(queries).pin_memory()
+    h_ids = torch.empty((nq, k), dtype=torch.int32).pin_memory()
+    h_dist = torch.empty((nq, k), dtype=torch.float32).pin_memory()
+    lib = cp.load_library()
+    import ctypes as C
+
+    def step_e2e():
+        rc = lib.cphnsw_b200_search_and_rerank_batch(idx.handle, C.c_void_p(h_q.data_ptr()), C.c_uint64(nq), C.c_uint32(k),
+                                                     C.c_uint32(ef), C.c_uint32(rerank_k), C.c_void_p(h_ids.data_ptr()),
+                                                     C.c_void_p(h_dist.data_ptr()), None)
+        if rc != 0:
+            raise RuntimeError(lib.cphnsw_b200_last_error().decode())
+
+    for _ in range(max(3, args.warmup)):
+        step_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    e2e_value = world * nq / (e2e_ms * 1e-3)
+    same = bool(np.array_equal(h_ids.numpy().astype(np.uint32), ids))
+
+    # ---- roofline of the dominant kernel (search): algorithmic HBM bytes per launch ----
+    exp_mean = float(stats[:, 0].mean())
+    evals_mean = float(stats[:, 1].mean())
+    code_row = K * cb
+    n_entry = min(w["entry_scan"], n)
+    rr = min(rerank_k, max(ef, rerank_k, k))
+    bytes_per_query = (exp_mean * M * (4 + code_row)      # adjacency ids + neighbour codes per expansion
+                       + n_entry * (4 + code_row)          # entry scan
+                       + K * idx.padded_dim * 4            # query table
+                       + rr * dim * 4 + k * 8)             # rerank gather + results
+    peak, peak_kind = measured_peaks()
+    search_ms_per_launch = search_ms / max(1, search_launches)
+    achieved = bytes_per_query * nq / (search_ms_per_launch * 1e-3) / 1e9
+    roofline = {"kernel": "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": "of " + peak_kind, "traffic": None,
+                "ms_per_launch": search_ms_per_launch, "algorithmic_bytes_per_query": bytes_per_query,
+                "expansions_per_query": exp_mean, "distance_evals_per_query": evals_mean,
+                "share_of_step": search_ms / (ms_total if ms_total else 1.0),
+                "query_encode_ms_per_step": qenc_ms / args.steps}
+
+    rows_s = lambda name: n / (stage_ms[name] * 1e-3)  # noqa: E731
+    build = {
+        "encode_vec_per_s": rows_s("encode"), "encode_ms": stage_ms["encode"],
+        "encode_fp32_addsub_per_s": rows_s("encode") * K * 3 * idx.padded_dim * np.log2(idx.padded_dim),
+        "knn_graph_vec_per_s": rows_s("knn_graph"), "knn_graph_ms": stage_ms["knn_graph"], "knn_k": knn_k,
+        "knn_pairs_per_s": rows_s("knn_graph") * n,
+        "knn_word_compares_per_s": rows_s("knn_graph") * n * (code_row / 4.0),
+        "select_neighbors_vec_per_s": rows_s("select_neighbors"), "select_neighbors_ms": stage_ms["select_neighbors"],
+        "allgather_codes_ms": stage_ms["allgather_codes"], "allgather_adjacency_ms": stage_ms["allgather_adjacency"],
+        "scaling": "strong",
+    }
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": w["name"], "n_base": n, "dim": dim, "queries_per_rank": nq, "k": k, "ef": ef,
+                       "rerank_k": rerank_k, "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry, "knn_k": knn_k,
+                       "l2": "index (vectors+codes+adjacency = %.0f MB) larger than L2" % (n * (dim * 4 + code_row + M * 4) / 1e6)},
+            "recall_at_10": recall, "recall_target_met": bool(recall >= 0.9),
+            "e2e": {"value": e2e_value, "unit": "queries/s", "h2d_bytes_per_step": int(world * nq * dim * 4),
+                    "d2h_bytes_per_step": int(world * nq * k * 8), "ms_per_step": e2e_ms, "same_ids_as_resident": same},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "build": build,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            _, qps, secs, crec, cores, desc = cpu_steps(args, 300, 2, 1)
+            line["cpu_baseline"] = {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": desc,
+                                    "recall_at_10": crec}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

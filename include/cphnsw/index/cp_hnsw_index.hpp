@@ -1,0 +1,203 @@
+// CPHNSWIndex<ComponentT, K>: header-only C++ front of the cphnsw_b200 C ABI with the surface of the
+// reference's legacy index class (its header is absent from the reference tree; the surface is the
+// one its evaluation programs call — evaluation/eval_sift.cpp:228-283,387,430,
+// evaluation/eval_master.cpp:89,145, evaluation/eval_main.cpp:42-43, evaluation/test_gpu_build.cpp:155-174,
+// evaluation/debug_code_storage.cpp:75).  Host pointers in, results by value, ascending by distance;
+// parameter errors throw std::invalid_argument like CPHNSWParams::finalize()
+// (include/cphnsw/core/types.hpp:403-469); any other failure throws std::runtime_error.
+//
+// All arithmetic runs on the GPU behind the C ABI; this header holds no algorithm.
+#pragma once
+
+#include <array>
+#include <cstddef>
+#include <cstdint>
+#include <limits>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+#include "../../cphnsw_b200.h"
+
+namespace cphnsw {
+
+using NodeId = uint32_t;                                                     // types.hpp:27
+constexpr NodeId INVALID_NODE = std::numeric_limits<NodeId>::max();          // types.hpp:29
+using Float = float;                                                         // types.hpp:41
+using AsymmetricDist = float;                                                // types.hpp:38
+using HammingDist = uint16_t;                                                // types.hpp:35
+
+// One result of a k-NN search (types.hpp:347-362).
+struct SearchResult {
+    NodeId id;
+    AsymmetricDist distance;
+    bool operator<(const SearchResult& o) const { return distance < o.distance; }
+    bool operator>(const SearchResult& o) const { return distance > o.distance; }
+    bool operator==(const SearchResult& o) const { return id == o.id && distance == o.distance; }
+};
+
+// K-component cross-polytope code; component = (argmax index << 1) | negative (types.hpp:68-106).
+// Only the components are stored by this implementation.
+template <typename ComponentT, size_t K>
+struct CPCode {
+    std::array<ComponentT, K> components;
+    static constexpr size_t decode_index(ComponentT c) { return c >> 1; }
+    static constexpr bool decode_sign_negative(ComponentT c) { return c & 1; }
+    static constexpr ComponentT encode(size_t index, bool is_negative) {
+        return static_cast<ComponentT>((index << 1) | (is_negative ? 1 : 0));
+    }
+};
+
+// Number of components in which two codes differ (the legacy hamming_distance(CPCode,CPCode);
+// use sites evaluation/debug_estimator.cpp:149,172).  Trivial host helper for single pairs; batches
+// go through CPHNSWIndex::code_distance.
+template <typename ComponentT, size_t K>
+inline HammingDist hamming_distance(const CPCode<ComponentT, K>& a, const CPCode<ComponentT, K>& b) {
+    HammingDist d = 0;
+    for (size_t r = 0; r < K; ++r) d += a.components[r] != b.components[r];
+    return d;
+}
+
+// Index parameters (types.hpp:374-470).  `k` is the code width and must equal the template K.
+struct CPHNSWParams {
+    size_t dim = 0;
+    size_t padded_dim = 0;
+    size_t k = 32;
+    size_t M = 32;
+    size_t ef_construction = 200;
+    bool keep_pruned = true;
+    uint64_t seed = 42;
+    size_t k_entry = 4;
+    float rank_pruning_alpha = 1.1f;
+    void finalize() {
+        if (dim == 0) throw std::invalid_argument("CPHNSWParams: dim must be > 0");
+        if (k == 0) throw std::invalid_argument("CPHNSWParams: k (code width) must be > 0");
+        if (k > 256) throw std::invalid_argument("CPHNSWParams: k (code width) must be <= 256");
+        if (M == 0) throw std::invalid_argument("CPHNSWParams: M (max connections) must be > 0");
+        if (M > 64) throw std::invalid_argument("CPHNSWParams: M must be <= 64 (FLASH_MAX_M limit)");
+        if (ef_construction < M) throw std::invalid_argument("CPHNSWParams: ef_construction must be >= M for good graph quality");
+        if (ef_construction > 10000) throw std::invalid_argument("CPHNSWParams: ef_construction must be <= 10000");
+        if (k_entry == 0) throw std::invalid_argument("CPHNSWParams: k_entry must be > 0");
+        if (k_entry > 100) throw std::invalid_argument("CPHNSWParams: k_entry must be <= 100");
+        if (rank_pruning_alpha < 1.0f) throw std::invalid_argument("CPHNSWParams: rank_pruning_alpha must be >= 1.0");
+        if (rank_pruning_alpha > 3.0f) throw std::invalid_argument("CPHNSWParams: rank_pruning_alpha must be <= 3.0");
+        padded_dim = 1;
+        while (padded_dim < dim) padded_dim *= 2;
+    }
+};
+
+template <typename ComponentT, size_t K>
+class CPHNSWIndex {
+    static_assert(std::is_same<ComponentT, uint8_t>::value || std::is_same<ComponentT, uint16_t>::value,
+                  "ComponentT must be uint8_t or uint16_t");
+
+public:
+    using Code = CPCode<ComponentT, K>;
+
+    CPHNSWIndex(size_t dim, size_t M = 32, size_t ef_construction = 200, uint64_t seed = 42,
+                int fht_convention = CPHNSW_B200_FHT_AVX512, int device = 0) {
+        check(cphnsw_b200_create(dim, uint32_t(K), uint32_t(sizeof(ComponentT)), uint32_t(M), uint32_t(ef_construction), seed,
+                                 fht_convention, device, &h_));
+    }
+    explicit CPHNSWIndex(const CPHNSWParams& p, int fht_convention = CPHNSW_B200_FHT_AVX512, int device = 0) {
+        if (p.k != K) throw std::invalid_argument("CPHNSWParams: k must equal the index's code width K");
+        check(cphnsw_b200_create(p.dim, uint32_t(K), uint32_t(sizeof(ComponentT)), uint32_t(p.M), uint32_t(p.ef_construction),
+                                 p.seed, fht_convention, device, &h_));
+        set_param("keep_pruned", p.keep_pruned ? 1.0 : 0.0);
+        set_param("k_entry", double(p.k_entry));
+    }
+    ~CPHNSWIndex() { cphnsw_b200_destroy(h_); }
+    CPHNSWIndex(const CPHNSWIndex&) = delete;
+    CPHNSWIndex& operator=(const CPHNSWIndex&) = delete;
+
+    cphnsw_b200_index* handle() const { return h_; }
+    void set_param(const char* name, double v) { check(cphnsw_b200_set_param(h_, name, v)); }
+    size_t dim() const { return cphnsw_b200_dim(h_); }
+    size_t padded_dim() const { return cphnsw_b200_padded_dim(h_); }
+    size_t size() const { return cphnsw_b200_size(h_); }
+
+    // ---- construction -------------------------------------------------------------------------
+    NodeId add(const Float* vec) {
+        NodeId id = NodeId(size());
+        add_batch_parallel(vec, 1);
+        return id;
+    }
+    void add_batch(const Float* vecs, size_t n) { add_batch_parallel(vecs, n); }
+    void add_batch_parallel(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch_parallel(h_, vecs, n)); }
+
+    // ---- search ---------------------------------------------------------------------------------
+    std::vector<SearchResult> search(const Float* q, size_t k, size_t ef) const {
+        return search_batch(q, 1, k, ef)[0];
+    }
+    std::vector<SearchResult> search_and_rerank(const Float* q, size_t k, size_t ef, size_t rerank_k) const {
+        return search_and_rerank_batch(q, 1, k, ef, rerank_k)[0];
+    }
+    std::vector<std::vector<SearchResult>> search_batch(const Float* q, size_t nq, size_t k, size_t ef) const {
+        std::vector<uint32_t> ids(nq * k);
+        std::vector<float> d(nq * k);
+        check(cphnsw_b200_search_batch(h_, q, nq, uint32_t(k), uint32_t(ef), ids.data(), d.data(), nullptr));
+        return unpack(ids, d, nq, k);
+    }
+    std::vector<std::vector<SearchResult>> search_and_rerank_batch(const Float* q, size_t nq, size_t k, size_t ef,
+                                                                   size_t rerank_k) const {
+        std::vector<uint32_t> ids(nq * k);
+        std::vector<float> d(nq * k);
+        check(cphnsw_b200_search_and_rerank_batch(h_, q, nq, uint32_t(k), uint32_t(ef), uint32_t(rerank_k), ids.data(),
+                                                  d.data(), nullptr));
+        return unpack(ids, d, nq, k);
+    }
+
+    // ---- stages ---------------------------------------------------------------------------------
+    std::vector<Code> encode(const Float* vecs, size_t n) const {
+        std::vector<Code> out(n);
+        static_assert(sizeof(Code) == K * sizeof(ComponentT), "CPCode must be a plain component array");
+        check(cphnsw_b200_encode(h_, vecs, n, out.data()));
+        return out;
+    }
+    Code get_code(NodeId id) const {
+        std::vector<Code> all(size());
+        check(cphnsw_b200_get_codes(h_, all.data()));
+        if (id >= all.size()) throw std::out_of_range("get_code: node id out of range");
+        return all[id];
+    }
+    std::vector<HammingDist> code_distance(const std::vector<Code>& a, const std::vector<Code>& b) const {
+        std::vector<HammingDist> out(a.size() * b.size());
+        check(cphnsw_b200_code_distance(h_, a.data(), a.size(), b.data(), b.size(), out.data()));
+        return out;
+    }
+    std::vector<NodeId> adjacency() const {
+        std::vector<NodeId> adj(size() * size_t(param("M")));
+        check(cphnsw_b200_get_adjacency(h_, adj.data()));
+        return adj;
+    }
+    double param(const char* name) const {
+        double v = 0;
+        check(cphnsw_b200_get_param(h_, name, &v));
+        return v;
+    }
+
+private:
+    cphnsw_b200_index* h_ = nullptr;
+
+    static void check(int rc) {
+        if (rc == 0) return;
+        std::string msg = cphnsw_b200_last_error();
+        if (rc == CPHNSW_B200_E_INVALID) throw std::invalid_argument(msg);
+        throw std::runtime_error(msg);
+    }
+    static std::vector<std::vector<SearchResult>> unpack(const std::vector<uint32_t>& ids, const std::vector<float>& d,
+                                                         size_t nq, size_t k) {
+        std::vector<std::vector<SearchResult>> out(nq);
+        for (size_t q = 0; q < nq; ++q)
+            for (size_t t = 0; t < k; ++t)
+                if (ids[q * k + t] != INVALID_NODE) out[q].push_back({ids[q * k + t], d[q * k + t]});
+        return out;
+    }
+};
+
+using CPHNSWIndex8 = CPHNSWIndex<uint8_t, 16>;    // evaluation/eval_main.cpp:42
+using CPHNSWIndex32 = CPHNSWIndex<uint8_t, 32>;   // evaluation/test_tiered.cpp:58
+using CPHNSWIndex16 = CPHNSWIndex<uint16_t, 16>;
+
+}  // namespace cphnsw

@@ -64,7 +64,7 @@ int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
 int cphnsw_b200_destroy(cphnsw_b200_index* h);
 
 /* Named tunables (CPHNSWParams fields, types.hpp:374-400, plus build/search knobs):
- *   "keep_pruned" (0/1, default 1), "k_entry" (1..100, default 4),
+ *   "keep_pruned" (0/1, default 1), "k_entry" (1..100, default 4), "profile" (0/1, see kernel_time),
  *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
  *   "entry_scan" (nodes scored per query to seed the beam; default = k_entry). */
 int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double value);
@@ -163,6 +163,13 @@ int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, 
                            void* stream);
 /* Reads and clears the device-side status word the kernels raise when a bounded wait runs out. */
 int cphnsw_b200_check_device_status(cphnsw_b200_index* h);
+
+/* Kernel timing for benchmarks (no counterpart in the reference, which times with a host clock,
+ * evaluation/metrics/recall.hpp:109-130).  With set_param("profile", 1) every launch of a kernel
+ * family is bracketed by CUDA events on its stream; this call waits for them, returns the summed
+ * device time and the number of launches since the last call, and resets the family's record.
+ * kind: 0 encode, 1 code distance, 2 kNN graph, 3 select_neighbors, 4 search. */
+int cphnsw_b200_kernel_time(cphnsw_b200_index* h, int kind, double* total_ms, uint64_t* launches);
 
 /* Number of kernel launches issued through this handle so far (for benchmark accounting). */
 uint64_t cphnsw_b200_launch_count(const cphnsw_b200_index* h);

@@ -33,6 +33,7 @@ EXPORTS = [
     "cphnsw_b200_search_and_rerank_batch", "cphnsw_b200_encode_dev", "cphnsw_b200_code_distance_dev",
     "cphnsw_b200_knn_graph_dev", "cphnsw_b200_select_neighbors_dev", "cphnsw_b200_install_dev",
     "cphnsw_b200_search_dev", "cphnsw_b200_check_device_status", "cphnsw_b200_launch_count",
+    "cphnsw_b200_kernel_time",
 ]
 
 
@@ -285,6 +286,15 @@ class CPHNSWIndex:
         _check(self._lib.cphnsw_b200_search_dev(self._h, C.c_void_p(d_q), _u64(nq), _u32(k), _u32(ef), _u32(rerank_k),
                                                 C.c_void_p(d_ids), C.c_void_p(d_dists), C.c_void_p(d_stats),
                                                 C.c_void_p(stream)))
+
+    KERNELS = {"encode": 0, "code_distance": 1, "knn_graph": 2, "select_neighbors": 3, "search": 4}
+
+    def kernel_time(self, kind):
+        """(summed device ms, launches) of a kernel family since the last call; needs set_param("profile", 1)."""
+        ms = C.c_double()
+        cnt = C.c_uint64()
+        _check(self._lib.cphnsw_b200_kernel_time(self._h, C.c_int(self.KERNELS[kind]), C.byref(ms), C.byref(cnt)))
+        return ms.value, int(cnt.value)
 
     def check_device_status(self):
         _check(self._lib.cphnsw_b200_check_device_status(self._h))

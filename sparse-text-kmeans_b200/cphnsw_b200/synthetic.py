@@ -13,16 +13,15 @@ def normalize(x):
     return (x * scale[:, None]).astype(np.float32)
 
 
-def gaussian_sphere(n, nq, dim, seed):
+def gaussian_sphere(n, nq, dim, seed, query_stream=0):
     """i.i.d. N(0,1) per coordinate, then normalised (the random-sphere generator of
-    dataset_loader.hpp:145-185 with a numpy stream)."""
-    rng = np.random.default_rng(seed)
-    base = normalize(rng.standard_normal((n, dim), dtype=np.float32))
-    queries = normalize(rng.standard_normal((nq, dim), dtype=np.float32))
+    dataset_loader.hpp:145-185 with numpy streams).  ``query_stream`` selects an independent query set."""
+    base = normalize(np.random.default_rng([seed, 1]).standard_normal((n, dim), dtype=np.float32))
+    queries = normalize(np.random.default_rng([seed, 2, query_stream]).standard_normal((nq, dim), dtype=np.float32))
     return base, queries
 
 
-def gaussian_mixture(n, nq, dim, n_clusters, sigma, seed, chunk=1 << 18):
+def gaussian_mixture(n, nq, dim, n_clusters, sigma, seed, query_stream=0, chunk=1 << 18):
     """Uniform-weight mixture: centres ~ N(0,1) per coordinate, points = centre + sigma*N(0,1),
     normalised; queries from the same mixture with an independent stream."""
     rng = np.random.default_rng(seed)
@@ -37,11 +36,11 @@ def gaussian_mixture(n, nq, dim, n_clusters, sigma, seed, chunk=1 << 18):
         return out
 
     base = draw(n, np.random.default_rng([seed, 1]))
-    queries = draw(nq, np.random.default_rng([seed, 2]))
+    queries = draw(nq, np.random.default_rng([seed, 2, query_stream]))
     return base, queries
 
 
-def abs_gaussian(n, nq, dim, seed, chunk=1 << 16):
+def abs_gaussian(n, nq, dim, seed, query_stream=0, chunk=1 << 16):
     """Non-negative |N(0,1)| coordinates, normalised (GIST-like value range)."""
     def draw(m, stream):
         out = np.empty((m, dim), np.float32)
@@ -50,35 +49,37 @@ def abs_gaussian(n, nq, dim, seed, chunk=1 << 16):
             out[i0:i1] = normalize(np.abs(stream.standard_normal((i1 - i0, dim), dtype=np.float32)))
         return out
 
-    return draw(n, np.random.default_rng([seed, 1])), draw(nq, np.random.default_rng([seed, 2]))
+    return draw(n, np.random.default_rng([seed, 1])), draw(nq, np.random.default_rng([seed, 2, query_stream]))
 
 
 # The five benchmark workloads (full sizes); ``scale`` shrinks base, queries and clusters together
 # so that cluster populations stay the same.
-def workload(name, scale=1.0):
+def workload(name, scale=1.0, query_stream=0):
+    """``query_stream`` picks an independent query set from the same distribution (one per rank)."""
     s = float(scale)
+    qs = query_stream
 
     def sz(v, lo=1):
         return max(lo, int(round(v * s)))
 
     if name == "C1":
-        base, q = gaussian_sphere(sz(100_000), sz(1_000, 10), 128, 0)
+        base, q = gaussian_sphere(sz(100_000), sz(1_000, 10), 128, 0, qs)
         return dict(name="C1", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
                     k=10, ef=100, rerank_k=500, entry_scan=4)
     if name == "C2":
-        base, q = gaussian_mixture(sz(1_000_000), sz(10_000, 10), 128, sz(1_000), 0.3, 1)
+        base, q = gaussian_mixture(sz(1_000_000), sz(10_000, 10), 128, sz(1_000), 0.3, 1, qs)
         return dict(name="C2", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
                     k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4))
     if name == "C3":
-        base, q = abs_gaussian(sz(1_000_000), sz(10_000, 10), 960, 2)
+        base, q = abs_gaussian(sz(1_000_000), sz(10_000, 10), 960, 2, qs)
         return dict(name="C3", base=base, queries=q, K=32, component_bytes=2, M=32, ef_construction=200,
                     k=10, ef=200, rerank_k=1000, entry_scan=4)
     if name == "C4":
-        base, q = gaussian_mixture(sz(10_000_000), sz(1_000, 10), 96, sz(10_000), 0.25, 3)
+        base, q = gaussian_mixture(sz(10_000_000), sz(1_000, 10), 96, sz(10_000), 0.25, 3, qs)
         return dict(name="C4", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
                     k=10, ef=100, rerank_k=500, knn_k=32, entry_scan=sz(65_536, 4))
     if name == "C5":
-        base, q = gaussian_mixture(sz(10_000_000), sz(100_000, 10), 128, sz(1_000), 0.3, 4)
+        base, q = gaussian_mixture(sz(10_000_000), sz(100_000, 10), 128, sz(1_000), 0.3, 4, qs)
         return dict(name="C5", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
                     k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4))
     raise ValueError("unknown workload %r" % name)

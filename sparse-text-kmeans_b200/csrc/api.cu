@@ -26,6 +26,22 @@ int cuda_fail(cudaError_t e, const char* what) {
     return CPHNSW_B200_E_CUDA;
 }
 
+LaunchTimer::LaunchTimer(cphnsw_b200_index* h_, int kind_, cudaStream_t st_) : h(h_), kind(kind_), st(st_) {
+    if (!h->profile) return;
+    auto& pool = h->events[kind];
+    size_t& used = h->events_used[kind];
+    if (used == pool.size()) {
+        EventPair e;
+        if (cudaEventCreate(&e.start) != cudaSuccess || cudaEventCreate(&e.stop) != cudaSuccess) return;
+        pool.push_back(e);
+    }
+    ev = &pool[used++];
+    cudaEventRecord(ev->start, st);
+}
+LaunchTimer::~LaunchTimer() {
+    if (ev) cudaEventRecord(ev->stop, st);
+}
+
 namespace {
 
 uint64_t next_pow2(uint64_t n) {
@@ -173,7 +189,34 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
 
 using namespace cpb;
 
+cphnsw_b200_index::~cphnsw_b200_index() {
+    for (auto& pool : events)
+        for (auto& e : pool) {
+            if (e.start) cudaEventDestroy(e.start);
+            if (e.stop) cudaEventDestroy(e.stop);
+        }
+}
+
 extern "C" {
+
+int cphnsw_b200_kernel_time(cphnsw_b200_index* h, int kind, double* total_ms, uint64_t* launches) {
+    CPB_TRY(bind(h));
+    if (kind < 0 || kind >= kKernelKinds || !total_ms || !launches) {
+        set_error("kernel_time: bad argument");
+        return CPHNSW_B200_E_INVALID;
+    }
+    double sum = 0.0;
+    for (size_t i = 0; i < h->events_used[kind]; ++i) {
+        float ms = 0.f;
+        CPB_CUDA(cudaEventSynchronize(h->events[kind][i].stop));
+        CPB_CUDA(cudaEventElapsedTime(&ms, h->events[kind][i].start, h->events[kind][i].stop));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = h->events_used[kind];
+    h->events_used[kind] = 0;
+    return 0;
+}
 
 const char* cphnsw_b200_last_error(void) { return g_error.c_str(); }
 
@@ -278,6 +321,7 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
     if (!h || !name) { set_error("set_param: null argument"); return CPHNSW_B200_E_INVALID; }
     std::string s(name);
     if (s == "keep_pruned") { h->keep_pruned = v != 0.0; return 0; }
+    if (s == "profile") { h->profile = v != 0.0; return 0; }
     if (s == "k_entry") {
         if (v < 1) { set_error("CPHNSWParams: k_entry must be > 0"); return CPHNSW_B200_E_INVALID; }
         if (v > 100) { set_error("CPHNSWParams: k_entry must be <= 100"); return CPHNSW_B200_E_INVALID; }
@@ -304,6 +348,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     if (!h || !name || !v) { set_error("get_param: null argument"); return CPHNSW_B200_E_INVALID; }
     std::string s(name);
     if (s == "keep_pruned") *v = h->keep_pruned;
+    else if (s == "profile") *v = h->profile;
     else if (s == "k_entry") *v = h->k_entry;
     else if (s == "knn_k") *v = h->knn_k;
     else if (s == "entry_scan") *v = h->entry_scan;

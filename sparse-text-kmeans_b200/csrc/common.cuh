@@ -33,6 +33,13 @@ int cuda_fail(cudaError_t e, const char* what);
         if (rc__ != 0) return rc__; \
     } while (0)
 
+// kernel families whose launches can be timed
+enum KernelKind { kKernelEncode = 0, kKernelCodeDistance = 1, kKernelKnn = 2, kKernelSelect = 3, kKernelSearch = 4 };
+constexpr int kKernelKinds = 5;
+struct EventPair {
+    cudaEvent_t start = nullptr, stop = nullptr;
+};
+
 // RAII device buffer (the library owns every scratch / index allocation through this).
 struct DevBuf {
     void* p = nullptr;
@@ -88,6 +95,12 @@ struct cphnsw_b200_index {
     cpb::DevBuf s_in, s_in2, s_out, s_out2, s_pad, s_pad2;
 
     uint64_t launches = 0;
+
+    // optional kernel timing ("profile" parameter): CUDA event pairs recorded around launches
+    int profile = 0;
+    std::vector<cpb::EventPair> events[cpb::kKernelKinds];
+    size_t events_used[cpb::kKernelKinds] = {0, 0, 0, 0, 0};
+    ~cphnsw_b200_index();
 };
 
 namespace cpb {
@@ -110,5 +123,15 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
                   cudaStream_t st);
 // scratch the search kernel needs for an index of n nodes (visited bitsets, expansion lists)
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam);
+
+// Brackets one kernel launch with an event pair when profiling is on (no-ops otherwise).
+struct LaunchTimer {
+    cphnsw_b200_index* h;
+    int kind;
+    cudaStream_t st;
+    EventPair* ev = nullptr;
+    LaunchTimer(cphnsw_b200_index* h_, int kind_, cudaStream_t st_);
+    ~LaunchTimer();
+};
 
 }  // namespace cpb

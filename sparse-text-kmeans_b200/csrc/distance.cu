@@ -474,6 +474,7 @@ int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, con
     CPB_TRY(padded_view(h, d_a, na, WC, h->s_pad, st, &pa));
     CPB_TRY(padded_view(h, d_b, nb, WC, h->s_pad2, st, &pb));
     dim3 grid(unsigned((nb + kCdThreads - 1) / kCdThreads), unsigned((na + kCdRowsA - 1) / kCdRowsA));
+    LaunchTimer timer(h, kKernelCodeDistance, st);
 #define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
@@ -490,6 +491,7 @@ static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n,
                                   int(smem)));
     const uint64_t rows = re - rb;
     const uint64_t blocks = (rows + kKnnWarps * Q - 1) / (kKnnWarps * Q);
+    LaunchTimer timer(h, kKernelKnn, st);
     knn_graph_kernel<WC, U16, SLOTS, Q><<<unsigned(blocks), kKnnThreads, smem, st>>>(
         codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>());
     h->launches++;
@@ -551,6 +553,7 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
     CPB_TRY(padded_view(h, d_codes, n, WC, h->s_pad, st, &pc));
     const uint64_t rows = row_end - row_begin;
     const unsigned grid = unsigned((rows + kSelWarps - 1) / kSelWarps);
+    LaunchTimer timer(h, kKernelSelect, st);
 #define CALL(W, U)                                                                                          \
     select_neighbors_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_cand, k, row_begin, row_end, M,    \
                                                                    keep_pruned, d_adj)

@@ -260,6 +260,7 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
     else if (h->convention >= CPHNSW_B200_FHT_AVX2 && P >= 8) w = 8;
     const int flip_mask = w - 1;
     const float* signs = h->d_signs.as<float>();
+    LaunchTimer timer(h, kKernelEncode, st);
 
     if (P == kP128) {
         size_t smem = size_t(kTileVecs) * kTileStride * sizeof(float) + size_t(kTileVecs) * K * h->comp_bytes;

@@ -439,6 +439,7 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.stats = d_stats;
     const unsigned grid = unsigned(h->sm_count);
     const bool u16 = h->comp_bytes == 2;
+    LaunchTimer timer(h, kKernelSearch, st);
 
 #define CPB_SEARCH(U, T)                                                                                   \
     do {                                                                                                   \

@@ -1,0 +1,32 @@
+"""The header-only C++ front (include/cphnsw/index/cp_hnsw_index.hpp): compiles and links against the
+C-ABI library on any machine; its QA program (modelled on the reference's evaluation/qa_protocol.cpp)
+runs on the GPU."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+EXE = os.path.join(ROOT, "tests", "cpp", "qa_protocol")
+
+
+def compile_qa():
+    lib_dir = os.path.join(ROOT, "sparse-text-kmeans_b200")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    cmd = [cxx, "-std=c++17", "-O2", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "qa_protocol.cpp"),
+           "-L", lib_dir, "-lcphnsw_b200", "-Wl,-rpath," + lib_dir, "-o", EXE]
+    subprocess.check_call(cmd)
+
+
+def test_cpp_front_compiles_and_links(cp):
+    compile_qa()
+    assert os.path.exists(EXE)
+
+
+@pytest.mark.gpu
+def test_cpp_qa_protocol(cp):
+    compile_qa()
+    out = subprocess.run([EXE], capture_output=True, text=True, timeout=600)
+    print(out.stdout[-3000:], out.stderr[-2000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "ALL PASS" in out.stdout
