@@ -161,6 +161,29 @@ int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const 
 int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, uint32_t k, uint32_t ef,
                            uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
                            void* stream);
+/* Code distance for callers that cannot allocate device memory.  No counterpart in the reference.
+ *
+ * Some hosts of this library run under a fixed memory plan: a serving process whose device memory
+ * was carved up at start-up, a plugin running inside another framework's allocator, or code on a
+ * latency path where cudaMalloc's implicit device synchronisation is not acceptable.  The ordinary
+ * entry points grow scratch buffers with cudaMalloc on demand; this one never allocates or frees
+ * anything (no cudaMalloc, cudaFree or allocating library routine).  It needs no index handle either
+ * (creating one allocates): it works on the CURRENT CUDA device and takes the code shape directly.
+ *
+ * Same result as cphnsw_b200_code_distance_dev: d_out[na][nb] = number of differing components
+ * between code rows d_a[na][K] and d_b[nb][K] (device pointers, caller-owned, asynchronous on `stream`).
+ * The padded copies of both operands that the kernel reads are kept in a 1 MiB array built into the
+ * library's device image (every GPU that loads the library holds it until the process exits), hence
+ * the limit: (na + nb) * R <= 1 MiB, where R is the row size K*component_bytes rounded up to 16, 32
+ * or 64 bytes (32,768 rows at K=32 uint8).  Larger inputs are rejected with CPHNSW_B200_E_INVALID.
+ *
+ * The first call on each device looks up the array's device address; make that first call outside
+ * any stream capture.  All calls share the one array: it is fully rewritten by each call (nothing
+ * from an earlier call is read), but two calls whose kernels can overlap on the GPU - different
+ * streams, or different threads - race on it; serialise them. */
+int cphnsw_b200_code_distance_noalloc(const void* d_a, uint64_t na, const void* d_b, uint64_t nb, uint32_t K,
+                                      uint32_t component_bytes, uint16_t* d_out, void* stream);
+
 /* Reads and clears the device-side status word the kernels raise when a bounded wait runs out. */
 int cphnsw_b200_check_device_status(cphnsw_b200_index* h);
 

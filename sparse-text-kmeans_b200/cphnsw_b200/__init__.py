@@ -33,7 +33,7 @@ EXPORTS = [
     "cphnsw_b200_search_and_rerank_batch", "cphnsw_b200_encode_dev", "cphnsw_b200_code_distance_dev",
     "cphnsw_b200_knn_graph_dev", "cphnsw_b200_select_neighbors_dev", "cphnsw_b200_install_dev",
     "cphnsw_b200_search_dev", "cphnsw_b200_check_device_status", "cphnsw_b200_launch_count",
-    "cphnsw_b200_kernel_time",
+    "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc",
 ]
 
 
@@ -82,6 +82,17 @@ def _u64(v):
 
 def _u32(v):
     return C.c_uint32(int(v))
+
+
+def code_distance_noalloc(d_a, na, d_b, nb, K, component_bytes, d_out, stream=0):
+    """Allocation-free code distance on the current CUDA device (raw device addresses in and out).
+
+    For hosts that may not allocate device memory once running; inputs are limited to what fits the
+    library's built-in 1 MiB scratch (see ``cphnsw_b200_code_distance_noalloc`` in the C header).
+    """
+    _check(load_library().cphnsw_b200_code_distance_noalloc(
+        C.c_void_p(d_a), _u64(na), C.c_void_p(d_b), _u64(nb), _u32(K), _u32(component_bytes), C.c_void_p(d_out),
+        C.c_void_p(stream)))
 
 
 class CPHNSWIndex:

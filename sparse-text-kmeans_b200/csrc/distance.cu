@@ -13,6 +13,8 @@
 // issued by one thread; the running k+1 best of each row live in registers, spread over the
 // warp in sorted order, and are updated by shuffles.  Ties go to the lower id because
 // candidates arrive in ascending id order and only a strictly smaller distance displaces.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cpb {
@@ -565,3 +567,82 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
 }
 
 }  // namespace cpb
+
+// ---- allocation-free code distance -------------------------------------------------------------------
+// For callers that must not allocate device memory (see the declaration in cphnsw_b200.h).
+// The padded copies of both operands, which the ordinary entry point keeps in buffers it
+// allocates on demand, live here in one statically sized device array that is part of the
+// loaded module on every GPU that loads the library.
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = size_t(1) << 20;  // padded copies of A and B together
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+uint32_t* g_noalloc_ptr[kNoAllocMaxDevices] = {};  // device address of the array, per device
+
+// `g_noalloc_scratch` in host code is only a stand-in for the symbol; the address a kernel can
+// use has to be asked for, once per device, with that device current.
+int noalloc_scratch(uint32_t** out) {
+    int dev = -1;
+    CPB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kNoAllocMaxDevices) {
+        cpb::set_error("code_distance_noalloc: device ordinal %d not supported", dev);
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        void* p = nullptr;
+        CPB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        g_noalloc_ptr[dev] = static_cast<uint32_t*>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int cphnsw_b200_code_distance_noalloc(const void* d_a, uint64_t na, const void* d_b, uint64_t nb,
+                                                 uint32_t K, uint32_t component_bytes, uint16_t* d_out,
+                                                 void* stream) {
+    using namespace cpb;
+    if (K == 0 || K > 256 || (component_bytes != 1 && component_bytes != 2)) {
+        set_error("code_distance_noalloc: need 1 <= K <= 256 and component_bytes 1 or 2");
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (na == 0 || nb == 0) return 0;
+    if (!d_a || !d_b || !d_out) {
+        set_error("code_distance_noalloc: null pointer");
+        return CPHNSW_B200_E_INVALID;
+    }
+    const int WC = code_row_words(K, component_bytes);
+    if (!WC) {
+        set_error("code_distance_noalloc: code rows wider than 64 bytes are not supported (K*component_bytes=%u)",
+                  K * component_bytes);
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    const uint64_t capacity_rows = kNoAllocScratchBytes / (uint64_t(WC) * 4);
+    if (na > capacity_rows || nb > capacity_rows || na + nb > capacity_rows) {
+        set_error("code_distance_noalloc: na + nb = %llu rows exceed the built-in scratch (%llu rows of %d bytes = %zu bytes); "
+                  "split the call or use cphnsw_b200_code_distance_dev",
+                  (unsigned long long)(na + nb), (unsigned long long)capacity_rows, WC * 4, kNoAllocScratchBytes);
+        return CPHNSW_B200_E_INVALID;
+    }
+    uint32_t* scratch = nullptr;
+    CPB_TRY(noalloc_scratch(&scratch));
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t* pa = scratch;
+    uint32_t* pb = scratch + na * WC;  // na*WC*4 is a multiple of 16: the 128-bit loads stay aligned
+    const int row_bytes = int(K * component_bytes);
+    // every word of both padded copies is rewritten here, so nothing left by an earlier call is read
+    pad_codes_kernel<<<unsigned((na * WC + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(d_a), na, row_bytes, WC, pa);
+    pad_codes_kernel<<<unsigned((nb * WC + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(d_b), nb, row_bytes, WC, pb);
+    const bool u16 = component_bytes == 2;
+    dim3 grid(unsigned((nb + kCdThreads - 1) / kCdThreads), unsigned((na + kCdRowsA - 1) / kCdRowsA));
+#define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out)
+    CPB_DISPATCH_WC(WC, u16, CALL);
+#undef CALL
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
