@@ -143,7 +143,7 @@ def cpu_steps(args, n_queries, steps, warmup):
 
     def step():
         _, rot, _ = O.encode(q, K, cb, signs, O.FHT_AVX512, want_rotated=True)
-        cands, _ = O.search(rot, codes, adj, entry, beam, w["rerank_k"])
+        cands, _ = O.search(rot, codes, adj, entry, beam, w["rerank_k"], n_seed=w.get("k_entry", 4))
         return O.rerank(q, base, cands, w["k"])
 
     for _ in range(warmup):
@@ -225,6 +225,7 @@ def run_b200(args):
 
     idx = cp.CPHNSWIndex(dim, M=M, ef_construction=w["ef_construction"], K=K, component_bytes=cb, device=local_rank)
     idx.set_param("entry_scan", w["entry_scan"])
+    idx.set_param("k_entry", w.get("k_entry", 4))
     idx.set_param("profile", 1)
 
     # ---- build (sharded by row block), each stage timed with CUDA events, max over ranks ----
@@ -370,7 +371,7 @@ def run_b200(args):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": w["name"], "n_base": n, "dim": dim, "queries_per_rank": nq, "k": k, "ef": ef,
-                       "rerank_k": rerank_k, "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry, "knn_k": knn_k,
+                       "rerank_k": rerank_k, "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry, "k_entry": w.get("k_entry", 4), "knn_k": knn_k,
                        "l2": "index (vectors+codes+adjacency = %.0f MB) larger than L2" % (n * (dim * 4 + code_row + M * 4) / 1e6)},
             "recall_at_10": recall, "recall_target_met": bool(recall >= 0.9),
             "e2e": {"value": e2e_value, "unit": "queries/s", "h2d_bytes_per_step": int(world * nq * dim * 4),

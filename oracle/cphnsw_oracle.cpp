@@ -269,12 +269,14 @@ int orc_select_neighbors(const void* codes, uint64_t n, uint64_t K, uint64_t com
 //  * the best k of W are returned ascending (the reference pops the k worst, :184-190; the
 //    legacy behaviour asserted by evaluation/qa_protocol.cpp:137-165 is ascending best-k).
 // Metric: legacy asymmetric distance against the query's K rotated vectors (table).
-// All entry ids are scored and offered to W first.  W capacity is ef.
-// out_ids/out_dist are [nq][k] padded with 0xFFFFFFFF / +inf; stats[nq][2] = expansions,
-// distance evaluations (optional).
+// Entry: every id of entry_ids is scored (the "entry scan"); the n_seed best under (distance, id)
+// seed the walk - the legacy index's k_entry entry points (types.hpp:396-397), chosen by score
+// instead of at random so that a query lands in its own cluster.  n_seed >= n_entry offers them all.
+// W capacity is ef.  out_ids/out_dist are [nq][k] padded with 0xFFFFFFFF / +inf; stats[nq][2] =
+// expansions, distance evaluations (scan + walk; optional).
 int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint64_t P,
                const void* codes, uint64_t comp_bytes, uint64_t n, const uint32_t* adj, uint64_t M,
-               const uint32_t* entry_ids, uint64_t n_entry, uint64_t ef, uint64_t k,
+               const uint32_t* entry_ids, uint64_t n_entry, uint64_t n_seed, uint64_t ef, uint64_t k,
                uint32_t* out_ids, float* out_dist, uint32_t* stats) {
 #pragma omp parallel
     {
@@ -303,7 +305,20 @@ int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint
                     C.insert(c);
                 }
             };
-            for (size_t e = 0; e < n_entry; ++e) offer(entry_ids[e]);  // :105-115
+            if (n_seed >= n_entry) {
+                for (size_t e = 0; e < n_entry; ++e) offer(entry_ids[e]);  // :105-115
+            } else {
+                std::vector<Cand> scan;
+                for (size_t e = 0; e < n_entry; ++e) {
+                    uint32_t id = entry_ids[e];
+                    if (id == kInvalid || id >= n) continue;
+                    scan.push_back({asym_dist(table, K, P, codes, comp_bytes, id), id});
+                    ++evals;
+                }
+                std::sort(scan.begin(), scan.end());
+                scan.erase(std::unique(scan.begin(), scan.end()), scan.end());
+                for (size_t e = 0; e < scan.size() && e < n_seed; ++e) offer(scan[e].second);
+            }
             while (!C.empty()) {  // :118-178; C only holds members of W, so the `c > worst` break
                 Cand c = *C.begin();  // of :130-132 is the emptiness of C
                 C.erase(C.begin());

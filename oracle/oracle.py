@@ -107,7 +107,8 @@ def select_neighbors(codes, cand, M, keep_pruned=True, row_begin=0):
     return adj
 
 
-def search(tables, codes, adj, entry_ids, ef, k, want_stats=False):
+def search(tables, codes, adj, entry_ids, ef, k, want_stats=False, n_seed=None):
+    """n_seed: how many of the scored entry ids seed the walk (None = all of them)."""
     tables = np.ascontiguousarray(tables, np.float32)
     codes = np.ascontiguousarray(codes)
     adj = np.ascontiguousarray(adj, np.uint32)
@@ -119,7 +120,8 @@ def search(tables, codes, adj, entry_ids, ef, k, want_stats=False):
     stats = np.zeros((nq, 2), np.uint32)
     lib().orc_search(_ptr(tables), C.c_uint64(nq), C.c_uint64(K), C.c_uint64(P), _ptr(codes),
                      C.c_uint64(codes.dtype.itemsize), C.c_uint64(n), _ptr(adj), C.c_uint64(M),
-                     _ptr(entry_ids), C.c_uint64(entry_ids.size), C.c_uint64(ef), C.c_uint64(k),
+                     _ptr(entry_ids), C.c_uint64(entry_ids.size),
+                     C.c_uint64(entry_ids.size if n_seed is None else n_seed), C.c_uint64(ef), C.c_uint64(k),
                      _ptr(ids), _ptr(dist), _ptr(stats))
     return (ids, dist, stats) if want_stats else (ids, dist)
 

@@ -69,7 +69,7 @@ def workload(name, scale=1.0, query_stream=0):
     if name == "C2":
         base, q = gaussian_mixture(sz(1_000_000), sz(10_000, 10), 128, sz(1_000), 0.3, 1, qs)
         return dict(name="C2", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
-                    k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4))
+                    k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4), k_entry=32)
     if name == "C3":
         base, q = abs_gaussian(sz(1_000_000), sz(10_000, 10), 960, 2, qs)
         return dict(name="C3", base=base, queries=q, K=32, component_bytes=2, M=32, ef_construction=200,
@@ -77,9 +77,9 @@ def workload(name, scale=1.0, query_stream=0):
     if name == "C4":
         base, q = gaussian_mixture(sz(10_000_000), sz(1_000, 10), 96, sz(10_000), 0.25, 3, qs)
         return dict(name="C4", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
-                    k=10, ef=100, rerank_k=500, knn_k=32, entry_scan=sz(65_536, 4))
+                    k=10, ef=100, rerank_k=500, knn_k=32, entry_scan=sz(65_536, 4), k_entry=32)
     if name == "C5":
         base, q = gaussian_mixture(sz(10_000_000), sz(100_000, 10), 128, sz(1_000), 0.3, 4, qs)
         return dict(name="C5", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
-                    k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4))
+                    k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4), k_entry=32)
     raise ValueError("unknown workload %r" % name)

@@ -86,7 +86,7 @@ struct cphnsw_b200_index {
     // index contents
     uint64_t n = 0;
     std::vector<float> h_vectors;  // host copy of everything added (rebuilds append to it)
-    cpb::DevBuf d_vectors, d_codes, d_adj, d_entry;
+    cpb::DevBuf d_vectors, d_codes, d_adj, d_entry, d_entry_codes;
     uint32_t n_entry = 0;
 
     // search scratch
@@ -123,6 +123,8 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
                   cudaStream_t st);
 // scratch the search kernel needs for an index of n nodes (visited bitsets, expansion lists)
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam);
+// copies the codes of the entry ids into one contiguous buffer (after d_entry / d_codes change)
+int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st);
 
 // Brackets one kernel launch with an event pair when profiling is on (no-ops otherwise).
 struct LaunchTimer {

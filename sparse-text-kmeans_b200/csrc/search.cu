@@ -28,6 +28,7 @@ namespace cpb {
 namespace {
 
 constexpr uint32_t kFull = 0xffffffffu;
+constexpr uint32_t kSeedSlots = 128;  // most seeds a query can have (k_entry <= 100)
 
 struct SearchArgs {
     const float* tables;   // [nq][K][P]
@@ -35,8 +36,9 @@ struct SearchArgs {
     const void* codes;     // [n][K] components
     const uint32_t* adj;   // [n][M]
     const float* vectors;  // [n][dim] (rerank only)
-    const uint32_t* entry;
-    uint32_t n_entry;
+    const uint32_t* entry;     // ids scored for every query before the walk
+    const void* entry_codes;   // their codes, gathered contiguously [n_entry][K]
+    uint32_t n_entry, n_seed;  // the n_seed best of the scan seed the walk
     uint64_t n;
     uint32_t nq;
     int K, P, dim, M, comp_bytes;
@@ -130,8 +132,11 @@ __global__ void search_kernel(SearchArgs a) {
 
     const uint32_t gwarp = blockIdx.x * warps + warp, total_warps = gridDim.x * warps;
     uint32_t* vis = a.visited + size_t(gwarp) * a.vis_words;
-    uint32_t* explist = a.explist + size_t(gwarp) * a.exp_cap;
+    // per-warp list in HBM: kSeedSlots seed ids, then the ids of expanded nodes
+    uint32_t* seedlist = a.explist + size_t(gwarp) * (a.exp_cap + kSeedSlots);
+    uint32_t* explist = seedlist + kSeedSlots;
     const uint32_t beam = a.beam;
+    const bool scan_mode = a.n_seed < a.n_entry;
 
     for (uint32_t q = gwarp; q < a.nq; q += total_warps) {
         const float* table = a.tables + size_t(q) * a.K * a.P;
@@ -152,7 +157,8 @@ __global__ void search_kernel(SearchArgs a) {
         if (lane < slots) expw[lane] = 0;
         __syncwarp();
 
-        uint32_t count = 0, nexp = 0, nevals = 0;
+        uint32_t count = 0, nexp = 0, nevals = 0, nseeds = 0;
+        uint32_t wcap = scan_mode ? a.n_seed : beam;  // capacity of W: the seeds first, then the beam
         bool exp_overflow = false;
         float wd = INFINITY;  // worst member of W once it is full
         uint32_t wi = kInvalidNode;
@@ -162,7 +168,7 @@ __global__ void search_kernel(SearchArgs a) {
             float ld = 0.0f;
             uint32_t li = 0;
             int lp = -1;
-            for (int p = lane; p < int(beam); p += 32) {
+            for (int p = lane; p < int(wcap); p += 32) {
                 const float d = sd[p];
                 const uint32_t i = sid[p];
                 if (lp < 0 || key_less(ld, li, d, i)) {
@@ -194,26 +200,17 @@ __global__ void search_kernel(SearchArgs a) {
             }
             __syncwarp();
         };
-        // offer one candidate per lane to W (search_engine.hpp:153-177 for a whole row at once)
-        auto offer = [&](uint32_t id, bool in_range) {
-            // a node listed twice in one row is offered once (the second copy would find it visited)
-            const uint32_t grp = __match_any_sync(kFull, id);
-            bool fresh = in_range && (__ffs(grp) - 1) == lane;
-            if (fresh) {
-                const uint32_t word = __ldcg(vis + (id >> 5));
-                if ((word >> (id & 31)) & 1u) fresh = false;
-                else atomicOr(vis + (id >> 5), 1u << (id & 31));
-            }
-            float dist = 0.0f;
-            if (fresh) dist = asym_distance<U16>(table, a.codes, id, a.K, a.P);
+        // admit one scored candidate per lane into W: W stays the wcap best seen so far
+        // (search_engine.hpp:166-176 for a whole row at once)
+        auto admit = [&](bool fresh, float dist, uint32_t id) {
             uint32_t m = __ballot_sync(kFull, fresh);
             nevals += __popc(m);
-            while (m && count < beam) {
+            while (m && count < wcap) {
                 const int src = __ffs(m) - 1;
                 m &= m - 1;
                 put(int(count), __shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src));
                 ++count;
-                if (count == beam) recompute_worst();
+                if (count == wcap) recompute_worst();
             }
             if (m) {
                 m &= __ballot_sync(kFull, fresh && key_less(dist, id, wd, wi));
@@ -230,11 +227,60 @@ __global__ void search_kernel(SearchArgs a) {
             }
             __syncwarp();
         };
+        // offer one node per lane: visited test-and-set, score, admit (search_engine.hpp:153-177)
+        auto offer = [&](uint32_t id, bool in_range) {
+            // a node listed twice in one row is offered once (the second copy would find it visited)
+            const uint32_t grp = __match_any_sync(kFull, id);
+            bool fresh = in_range && (__ffs(grp) - 1) == lane;
+            if (fresh) {
+                const uint32_t word = __ldcg(vis + (id >> 5));
+                if ((word >> (id & 31)) & 1u) fresh = false;
+                else atomicOr(vis + (id >> 5), 1u << (id & 31));
+            }
+            float dist = 0.0f;
+            if (fresh) dist = asym_distance<U16>(table, a.codes, id, a.K, a.P);
+            admit(fresh, dist, id);
+        };
 
-        for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
-            const uint32_t e = e0 + lane;
-            const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
-            offer(id, id < a.n);
+        if (scan_mode) {
+            // entry scan: score every entry node from the contiguous copy of its code, keep the
+            // n_seed best in W; nothing is marked visited until the seeds are known
+            for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {
+                const uint32_t e = e0 + lane;
+                const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
+                const bool ok = id < a.n;
+                float dist = 0.0f;
+                if (ok) dist = asym_distance<U16>(table, a.entry_codes, e, a.K, a.P);
+                admit(ok, dist, id);
+            }
+            // the seeds are now offered to the walk: mark them visited and remember them for the clean-up
+            nseeds = count;
+            nevals += nseeds;
+            for (uint32_t p = lane; p < nseeds; p += 32) {
+                const uint32_t id = sid[p];
+                atomicOr(vis + (id >> 5), 1u << (id & 31));
+                seedlist[p] = id;
+            }
+            __syncwarp();
+            if (nseeds > beam) {  // a beam narrower than the seed set keeps the best `beam` seeds
+                int ns = 32;
+                while (ns < int(nseeds)) ns <<= 1;
+                warp_sort_smem(sd, sid, ns, lane);
+                for (uint32_t p = beam + lane; p < uint32_t(cap); p += 32) {
+                    sd[p] = INFINITY;
+                    sid[p] = kInvalidNode;
+                }
+                count = beam;
+                __syncwarp();
+            }
+            wcap = beam;
+            if (count == wcap) recompute_worst();
+        } else {
+            for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
+                const uint32_t e = e0 + lane;
+                const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
+                offer(id, id < a.n);
+            }
         }
 
         while (true) {
@@ -284,9 +330,13 @@ __global__ void search_kernel(SearchArgs a) {
         if (exp_overflow) {
             for (uint64_t w = lane; w < a.vis_words; w += 32) vis[w] = 0;
         } else {
-            for (uint32_t e = lane; e < a.n_entry; e += 32) {
-                const uint32_t id = __ldg(a.entry + e);
-                if (id < a.n) vis[id >> 5] = 0;
+            if (scan_mode) {
+                for (uint32_t p = lane; p < nseeds; p += 32) vis[__ldcg(seedlist + p) >> 5] = 0;
+            } else {
+                for (uint32_t e = lane; e < a.n_entry; e += 32) {
+                    const uint32_t id = __ldg(a.entry + e);
+                    if (id < a.n) vis[id >> 5] = 0;
+                }
             }
             __syncwarp();
             for (uint32_t x = 0; x < nexp; ++x) {
@@ -357,6 +407,15 @@ __global__ void search_kernel(SearchArgs a) {
     }
 }
 
+__global__ void gather_rows_kernel(const unsigned char* __restrict__ src, int row_bytes,
+                                   const uint32_t* __restrict__ ids, uint32_t n_ids, uint64_t n,
+                                   unsigned char* __restrict__ dst) {
+    const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= uint64_t(n_ids) * row_bytes) return;
+    const uint32_t id = ids[i / row_bytes];
+    dst[i] = id < n ? src[uint64_t(id) * row_bytes + i % row_bytes] : 0;
+}
+
 struct LaunchCfg {
     uint32_t cap;
     int warps;
@@ -367,7 +426,7 @@ struct LaunchCfg {
 LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam) {
     LaunchCfg c;
     c.cap = 32;
-    while (c.cap < beam) c.cap <<= 1;
+    while (c.cap < beam || c.cap < h->k_entry) c.cap <<= 1;
     const size_t table_bytes = size_t(h->K) * h->P * 4;
     c.table_smem = table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
     const size_t dim_pad = (size_t(h->dim) + 3) & ~size_t(3);
@@ -384,6 +443,20 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam) {
 
 }  // namespace
 
+int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
+    const int row_bytes = int(h->K * h->comp_bytes);
+    CPB_TRY(h->d_entry_codes.reserve(size_t(h->n_entry) * row_bytes + 16));
+    const uint64_t total = uint64_t(h->n_entry) * row_bytes;
+    if (total) {
+        gather_rows_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(
+            h->d_codes.as<unsigned char>(), row_bytes, h->d_entry.as<uint32_t>(), h->n_entry, h->n,
+            h->d_entry_codes.as<unsigned char>());
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+    }
+    return 0;
+}
+
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
     const size_t total_warps = size_t(h->sm_count) * 16;  // the most warps a launch ever uses
     const size_t vis_words = (h->n + 31) / 32;
@@ -393,7 +466,7 @@ int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
         CPB_CUDA(cudaMemset(h->d_visited.p, 0, h->d_visited.bytes));
     }
     const size_t exp_cap = size_t(4) * beam + 64;
-    CPB_TRY(h->d_explist.reserve(total_warps * exp_cap * 4));
+    CPB_TRY(h->d_explist.reserve(total_warps * (exp_cap + kSeedSlots) * 4));
     return 0;
 }
 
@@ -418,7 +491,9 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.adj = h->d_adj.as<uint32_t>();
     a.vectors = h->d_vectors.as<float>();
     a.entry = h->d_entry.as<uint32_t>();
+    a.entry_codes = h->d_entry_codes.p;
     a.n_entry = h->n_entry;
+    a.n_seed = h->k_entry;
     a.n = h->n;
     a.nq = uint32_t(nq);
     a.K = int(h->K);

@@ -144,12 +144,15 @@ def oracle_index(oracle, base, K, cb, M, knn_k, conv=2):
     return signs, codes, oracle.select_neighbors(codes, cand, M, True)
 
 
-@pytest.mark.parametrize("n,dim,K,cb,M,scan", [(4000, 128, 32, 1, 32, 64), (3000, 96, 32, 1, 16, 4),
-                                               (1500, 200, 16, 2, 32, 32), (50, 128, 32, 1, 32, 4)])
-def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan):
+@pytest.mark.parametrize("n,dim,K,cb,M,scan,seeds", [(4000, 128, 32, 1, 32, 64, 4), (4000, 128, 32, 1, 32, 500, 32),
+                                                     (3000, 96, 32, 1, 16, 4, 4), (3000, 96, 32, 1, 16, 333, 100),
+                                                     (1500, 200, 16, 2, 32, 32, 8), (50, 128, 32, 1, 32, 4, 4),
+                                                     (50, 128, 32, 1, 32, 50, 1)])
+def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan, seeds):
     base, q = synthetic.gaussian_mixture(n, 60, dim, max(2, n // 250), 0.3, n)
     idx = make_index(cp, dim, K, cb, M=M)
     idx.set_param("entry_scan", scan)
+    idx.set_param("k_entry", seeds)
     idx.add_batch_parallel(base)
     assert idx.size() == n
     knn_k = min(64, 2 * M)
@@ -159,16 +162,16 @@ def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan):
     entry = idx.entry_ids()
     assert np.array_equal(entry, (np.arange(min(scan, n), dtype=np.uint64) * n // min(scan, n)).astype(np.uint32))
     _, rot, _ = oracle.encode(q, K, cb, signs, 2, want_rotated=True)
-    for k, ef in ((10, 10), (10, 100), (50, 20), (1, 300)):
+    for k, ef in ((10, 10), (10, 100), (50, 20), (1, 300), (1, 1), (3, 2)):
         ids, dist, stats = idx.search_batch(q, k, ef, want_stats=True)
-        wi, wd, ws = oracle.search(rot, codes, adj, entry, max(ef, k), k, want_stats=True)
+        wi, wd, ws = oracle.search(rot, codes, adj, entry, max(ef, k), k, want_stats=True, n_seed=seeds)
         assert np.array_equal(ids, wi), (k, ef)
         assert np.array_equal(dist, wd)
         assert np.array_equal(stats, ws)
     # search_and_rerank: the candidate set is bit-exact, reranked distances agree to 1e-5 relative
     for k, ef, rr in ((10, 50, 200), (10, 400, 100), (5, 10, 5)):
         ids, dist = idx.search_and_rerank_batch(q, k, ef, rr)
-        cand, _ = oracle.search(rot, codes, adj, entry, max(ef, rr), rr)
+        cand, _ = oracle.search(rot, codes, adj, entry, max(ef, rr), rr, n_seed=seeds)
         wi, wd = oracle.rerank(q, base, cand, k)
         valid = wi != INVALID
         assert np.array_equal(ids == INVALID, ~valid)
