@@ -128,14 +128,29 @@ inline uint32_t code_dist(const void* a, size_t ia, const void* b, size_t ib, si
 }
 
 // Legacy asymmetric_search_distance(CPQuery, CPCode), restated by hand in the reference at
-// evaluation/debug_estimator.cpp:47-55: score += neg ? -val : val over r = 0..K-1, distance = -score.
+// evaluation/debug_estimator.cpp:47-55: score = sum over r of (neg ? -val : val), distance = -score.
+// DECLARED SUMMATION ORDER: the reference's scalar form adds r = 0..K-1 in sequence and its SIMD
+// batch form adds in another order; the two agree only to 1e-5 (evaluation/qa_protocol.cpp:168-244).
+// This oracle fixes one order, the balanced tree a 32-lane reduction produces: within each block
+// of 32 rotations (missing terms are +0) term j is added to term j+16, then j+8, j+4, j+2, j+1;
+// the block sums are added in sequence.  Within 1e-5 relative of the sequential sum.
 inline float asym_dist(const float* table /*[K][P]*/, size_t K, size_t P, const void* codes,
                        size_t comp_bytes, size_t id) {
     float score = 0.0f;
-    for (size_t r = 0; r < K; ++r) {
-        uint32_t c = load_comp(codes, comp_bytes, id * K + r);
-        float val = table[r * P + (c >> 1)];
-        score += (c & 1) ? -val : val;
+    for (size_t c0 = 0; c0 < K; c0 += 32) {
+        float t[32];
+        for (size_t j = 0; j < 32; ++j) {
+            size_t r = c0 + j;
+            t[j] = 0.0f;
+            if (r < K) {
+                uint32_t c = load_comp(codes, comp_bytes, id * K + r);
+                float val = table[r * P + (c >> 1)];
+                t[j] = (c & 1) ? -val : val;
+            }
+        }
+        for (size_t step = 16; step >= 1; step >>= 1)
+            for (size_t j = 0; j < step; ++j) t[j] = t[j] + t[j + step];
+        score = score + t[0];
     }
     return -score;
 }

@@ -423,7 +423,7 @@ int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const 
                             uint64_t n, void* stream) {
     CPB_TRY(bind(h));
     if (n == 0 || !d_vectors || !d_codes || !d_adj) { set_error("install: null pointer or n == 0"); return CPHNSW_B200_E_INVALID; }
-    if (n >= 0xFFFFFFFFull) { set_error("install: n must be < 2^32-1"); return CPHNSW_B200_E_INVALID; }
+    if (n >= 0x80000000ull) { set_error("install: n must be < 2^31 (the top bit of a node id is used by the search)"); return CPHNSW_B200_E_INVALID; }
     cudaStream_t st = (cudaStream_t)stream;
     CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
     CPB_TRY(h->d_codes.reserve(n * code_row_bytes(h) + 16));
@@ -535,7 +535,7 @@ int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_
         set_error("add_batch_parallel: the index was installed from device buffers and cannot be extended");
         return CPHNSW_B200_E_STATE;
     }
-    if (h->n + n >= 0xFFFFFFFFull) { set_error("add_batch_parallel: at most 2^32-2 nodes"); return CPHNSW_B200_E_INVALID; }
+    if (h->n + n >= 0x80000000ull) { set_error("add_batch_parallel: at most 2^31-1 nodes"); return CPHNSW_B200_E_INVALID; }
     h->h_vectors.insert(h->h_vectors.end(), x, x + n * h->dim);
     const uint64_t total = h->n + n;
     CPB_TRY(h->d_vectors.reserve(total * h->dim * 4));

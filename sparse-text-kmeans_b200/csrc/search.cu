@@ -4,22 +4,26 @@
 // W keeps the `beam` best nodes seen so far, the closest not-yet-expanded member of W is
 // expanded next, and the walk ends when every member of W has been expanded (which is when the
 // reference's `c.distance > worst.distance` break fires).  Candidates are ordered by the total
-// order (distance, id), so the result is independent of the order in which the 32 neighbours of
-// a node are examined — that is what lets a warp score a whole adjacency row at once and still
-// return exactly what a sequential walk returns.
+// order (distance, id), so W after an expansion is the `beam` best of everything seen, whatever
+// the order in which the 32 neighbours of a node are examined — that is what lets a warp score a
+// whole adjacency row at once and still return exactly what a sequential walk returns.
 //
 // Metric: the legacy asymmetric CP score (restated at evaluation/debug_estimator.cpp:47-55):
-// dist = -sum_r (+-) table[r][index_r], accumulated for r = 0..K-1 in fp32.  The query's K
-// rotated vectors (CPQuery::rotated_vecs, include/cphnsw/core/types.hpp:324-337) are staged in
-// shared memory (16 KB at K=32, padded dim 128); for large padded dims they stay in global memory.
+// dist = -sum_r (+-) table[r][index_r] in fp32.  The K terms are added in a fixed balanced-tree
+// order (per block of 32 rotations: pairs 16 apart, then 8, 4, 2, 1; blocks added in sequence),
+// which is the order a warp shuffle reduction produces; the same order is used when one lane
+// scores a node alone, so every path yields the same float.  (The reference's scalar form adds
+// r = 0..K-1 in sequence and its SIMD batch form in yet another order; the two agree to 1e-5,
+// evaluation/qa_protocol.cpp:168-244.)  The query's K rotated vectors (CPQuery::rotated_vecs,
+// include/cphnsw/core/types.hpp:324-337) are staged in shared memory (16 KB at K=32, padded dim
+// 128); for large padded dims they stay in global memory.
 //
-// W lives in shared memory, unsorted, with the current worst member tracked in registers and a
-// bit per position marking expanded members; lane l scans positions l, l+32, ...  Visited nodes are tracked in a
-// per-warp bitset in global memory that the warp itself returns to all-zero after each query.
-// After the walk the beam is sorted by a bitonic network in shared memory; for
-// search_and_rerank the best rerank_k are re-scored with -<q,x> (replaces gather_vectors_kernel
-// + batch_dot_product_kernel + the host partial_sort of src/cuda/gpu_encoder.cu:605-664) and
-// sorted again.
+// W lives in shared memory, sorted ascending, the "expanded" flag in the top bit of the id; a
+// cursor tracks the first unexpanded member, an admission finds its rank with a two-round 32-ary
+// search and shifts the tail up by one.  Visited nodes are tracked in a per-warp bitset in global
+// memory that the warp itself returns to all-zero after each query.  For search_and_rerank the
+// best rerank_k are re-scored with -<q,x> (replaces gather_vectors_kernel + batch_dot_product_kernel
+// + the host partial_sort of src/cuda/gpu_encoder.cu:605-664) and sorted by a bitonic network.
 #include <cmath>
 
 #include "common.cuh"
@@ -28,7 +32,10 @@ namespace cpb {
 namespace {
 
 constexpr uint32_t kFull = 0xffffffffu;
-constexpr uint32_t kSeedSlots = 128;  // most seeds a query can have (k_entry <= 100)
+constexpr uint32_t kSeedSlots = 128;        // most seeds a query can have (k_entry <= 100)
+constexpr uint32_t kExpanded = 0x80000000u; // top bit of a stored id: the member has been expanded
+constexpr uint32_t kIdMask = 0x7fffffffu;
+constexpr int kCoopMax = 8;                 // up to this many fresh nodes are scored by the whole warp
 
 struct SearchArgs {
     const float* tables;   // [nq][K][P]
@@ -42,10 +49,11 @@ struct SearchArgs {
     uint64_t n;
     uint32_t nq;
     int K, P, dim, M, comp_bytes;
-    uint32_t beam, cap, k, rerank_k;  // cap: power of two >= max(32, beam), the size of W's arrays
+    uint32_t per_warp_smem;           // bytes of shared memory per warp (multiple of 16)
+    uint32_t beam, cap, k, rerank_k;  // cap: power of two >= max(32, beam, n_seed), the size of W's arrays
     uint32_t* visited;  // [total warps][vis_words], all zero between queries
     uint64_t vis_words;
-    uint32_t* explist;  // [total warps][exp_cap]
+    uint32_t* explist;  // [total warps][kSeedSlots + exp_cap]
     uint32_t exp_cap;
     uint32_t* out_ids;
     float* out_dist;
@@ -56,37 +64,71 @@ __device__ __forceinline__ bool key_less(float da, uint32_t ia, float db, uint32
     return da < db || (da == db && ia < ib);
 }
 
-// asymmetric distance of node `id` against the query table; r ascending, one add per rotation
 template <bool U16>
-__device__ __forceinline__ float asym_distance(const float* table, const void* codes, uint32_t id, int K,
-                                               int P) {
-    float acc = 0.0f;
+__device__ __forceinline__ uint32_t load_component(const unsigned char* row, int r) {
+    return U16 ? uint32_t(reinterpret_cast<const uint16_t*>(row)[r]) : uint32_t(row[r]);
+}
+
+// signed table value of rotation r for component `comp` (+0 for r >= K)
+__device__ __forceinline__ float signed_term(const float* table, int r, int K, int P, uint32_t comp) {
+    if (r >= K) return 0.0f;
+    const float val = table[r * P + int(comp >> 1)];
+    return (comp & 1u) ? -val : val;
+}
+
+// One lane scores one node: the 32 terms of each block are combined in the balanced-tree order
+// (j with j+16, then +8, +4, +2, +1), blocks are added in sequence.
+template <bool U16>
+__device__ __forceinline__ float asym_distance_lane(const float* table, const void* codes, uint32_t row_index,
+                                                    int K, int P) {
     const int row_bytes = K * (U16 ? 2 : 1);
-    const unsigned char* row = static_cast<const unsigned char*>(codes) + size_t(id) * row_bytes;
-    if ((row_bytes & 15) == 0) {
-        const uint4* r4 = reinterpret_cast<const uint4*>(row);
-        int r = 0;
-        for (int c = 0; c < row_bytes / 16; ++c) {
-            uint4 v = __ldg(r4 + c);
-            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const unsigned char* row = static_cast<const unsigned char*>(codes) + size_t(row_index) * row_bytes;
+    const bool vec = (row_bytes & 15) == 0;
+    float acc = 0.0f;
+    for (int c0 = 0; c0 < K; c0 += 32) {
+        float t[32];
+        if (vec) {
+            constexpr int kPerWord = U16 ? 2 : 4;           // components per 32-bit word
+            constexpr int kWords = 32 / kPerWord;           // words per block of 32 components
+            const uint4* r4 = reinterpret_cast<const uint4*>(row + size_t(c0) * (U16 ? 2 : 1));
+            uint32_t w[kWords];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < kWords / 4; ++i) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (c0 + i * 4 * kPerWord < K) v = __ldg(r4 + i);
+                w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+            }
 #pragma unroll
-                for (int b = 0; b < (U16 ? 2 : 4); ++b, ++r) {
-                    uint32_t comp = U16 ? ((w[i] >> (16 * b)) & 0xffffu) : ((w[i] >> (8 * b)) & 0xffu);
-                    float val = table[r * P + int(comp >> 1)];
-                    acc = __fadd_rn(acc, (comp & 1u) ? -val : val);
-                }
+            for (int j = 0; j < 32; ++j) {
+                const uint32_t word = w[j / kPerWord];
+                const uint32_t comp = U16 ? ((word >> (16 * (j % 2))) & 0xffffu) : ((word >> (8 * (j % 4))) & 0xffu);
+                t[j] = signed_term(table, c0 + j, K, P, comp);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int r = c0 + j;
+                t[j] = signed_term(table, r, K, P, r < K ? load_component<U16>(row, r) : 0u);
             }
         }
-    } else {
-        for (int r = 0; r < K; ++r) {
-            uint32_t comp = U16 ? uint32_t(reinterpret_cast<const uint16_t*>(row)[r]) : uint32_t(row[r]);
-            float val = table[r * P + int(comp >> 1)];
-            acc = __fadd_rn(acc, (comp & 1u) ? -val : val);
+#pragma unroll
+        for (int step = 16; step >= 1; step >>= 1) {
+#pragma unroll
+            for (int j = 0; j < step; ++j) t[j] = __fadd_rn(t[j], t[j + step]);
         }
+        acc = __fadd_rn(acc, t[0]);
     }
     return -acc;
+}
+
+// The whole warp scores one node: lane j owns rotation c0 + j of each block; the butterfly
+// reduction adds exactly the pairs the one-lane form adds.  `comp` is this lane's component of
+// block 0 (K <= 32 on this path).
+__device__ __forceinline__ float asym_distance_coop(const float* table, int K, int P, uint32_t comp, int lane) {
+    float t = signed_term(table, lane, K, P, comp);
+#pragma unroll
+    for (int step = 16; step >= 1; step >>= 1) t = __fadd_rn(t, __shfl_xor_sync(kFull, t, step));
+    return -__fadd_rn(0.0f, t);
 }
 
 // ---- warp-wide bitonic sort of n (a power of two) (distance, id) pairs in shared memory ------------
@@ -120,15 +162,12 @@ __global__ void search_kernel(SearchArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const size_t table_floats = TABLE_SMEM ? size_t(a.K) * a.P : 0;  // a multiple of 4 when staged
     const size_t dim_pad = (size_t(a.dim) + 3) & ~size_t(3);
-    const int cap = int(a.cap);  // power of two >= max(32, beam)
-    const int slots = cap >> 5;
-    const size_t per_warp = table_floats * 4 + size_t(cap) * 8 + size_t(slots) * 4 + dim_pad * 4;
-    unsigned char* mine = search_smem + ((per_warp + 15) & ~size_t(15)) * warp;
+    const int cap = int(a.cap);
+    unsigned char* mine = search_smem + size_t(a.per_warp_smem) * warp;
     float* table_sm = reinterpret_cast<float*>(mine);
     float* qsm = reinterpret_cast<float*>(mine + table_floats * 4);
-    uint32_t* sid = reinterpret_cast<uint32_t*>(qsm + dim_pad);  // W: node ids, position p
+    uint32_t* sid = reinterpret_cast<uint32_t*>(qsm + dim_pad);  // W: node ids (+ expanded bit), ascending
     float* sd = reinterpret_cast<float*>(sid + cap);             // W: distances
-    uint32_t* expw = reinterpret_cast<uint32_t*>(sd + cap);      // bit p&31 of word p>>5: p expanded
 
     const uint32_t gwarp = blockIdx.x * warps + warp, total_warps = gridDim.x * warps;
     uint32_t* vis = a.visited + size_t(gwarp) * a.vis_words;
@@ -137,6 +176,8 @@ __global__ void search_kernel(SearchArgs a) {
     uint32_t* explist = seedlist + kSeedSlots;
     const uint32_t beam = a.beam;
     const bool scan_mode = a.n_seed < a.n_entry;
+    const int row_bytes = a.K * (U16 ? 2 : 1);
+    const bool coop_ok = a.K <= 32;
 
     for (uint32_t q = gwarp; q < a.nq; q += total_warps) {
         const float* table = a.tables + size_t(q) * a.K * a.P;
@@ -154,79 +195,62 @@ __global__ void search_kernel(SearchArgs a) {
             sd[p] = INFINITY;
             sid[p] = kInvalidNode;
         }
-        if (lane < slots) expw[lane] = 0;
         __syncwarp();
 
         uint32_t count = 0, nexp = 0, nevals = 0, nseeds = 0;
         uint32_t wcap = scan_mode ? a.n_seed : beam;  // capacity of W: the seeds first, then the beam
+        uint32_t cur = 0;                             // first unexpanded position of W (== count when none)
         bool exp_overflow = false;
         float wd = INFINITY;  // worst member of W once it is full
         uint32_t wi = kInvalidNode;
-        int wpos = -1;
 
-        auto recompute_worst = [&]() {
-            float ld = 0.0f;
-            uint32_t li = 0;
-            int lp = -1;
-            for (int p = lane; p < int(wcap); p += 32) {
-                const float d = sd[p];
-                const uint32_t i = sid[p];
-                if (lp < 0 || key_less(ld, li, d, i)) {
-                    ld = d;
-                    li = i;
-                    lp = p;
-                }
+        // Admission of (d, id), known to every lane: W stays the wcap best seen so far, sorted
+        // (search_engine.hpp:166-176).
+        auto try_admit = [&](float d, uint32_t id) {
+            if (count == wcap && !key_less(d, id, wd, wi)) return;
+            // rank = number of members below (d, id): two rounds of a 32-ary search
+            uint32_t p = 0;
+            if (count) {
+                const uint32_t stride = (count + 31) >> 5;
+                const uint32_t e = min(count, (uint32_t(lane) + 1) * stride) - 1;
+                const bool in = uint32_t(lane) * stride < count;
+                const bool less = in && key_less(sd[e], sid[e] & kIdMask, d, id);
+                const uint32_t b = __popc(__ballot_sync(kFull, less));  // blocks entirely below
+                const uint32_t j = b * stride + lane;
+                const bool less2 = b < 32 && uint32_t(lane) < stride && j < count && key_less(sd[j], sid[j] & kIdMask, d, id);
+                p = min(count, b * stride) + __popc(__ballot_sync(kFull, less2));
             }
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                const float od = __shfl_xor_sync(kFull, ld, o);
-                const uint32_t oi = __shfl_xor_sync(kFull, li, o);
-                const int op = __shfl_xor_sync(kFull, lp, o);
-                if (op >= 0 && (lp < 0 || key_less(ld, li, od, oi))) {
-                    ld = od;
-                    li = oi;
-                    lp = op;
+            // shift [p, end) up by one, highest chunk first; a full W drops its last member
+            const int end = int(count == wcap ? wcap - 1 : count);
+            for (int top = end; top > int(p); top -= 32) {
+                const int i = top - 1 - lane;
+                const bool act = i >= int(p);
+                float md = 0.0f;
+                uint32_t mi = 0;
+                if (act) {
+                    md = sd[i];
+                    mi = sid[i];
                 }
+                __syncwarp();
+                if (act) {
+                    sd[i + 1] = md;
+                    sid[i + 1] = mi;
+                }
+                __syncwarp();
             }
-            wd = ld;
-            wi = li;
-            wpos = lp;
-        };
-        auto put = [&](int pos, float d, uint32_t id) {
             if (lane == 0) {
-                sd[pos] = d;
-                sid[pos] = id;
-                expw[pos >> 5] &= ~(1u << (pos & 31));
+                sd[p] = d;
+                sid[p] = id;
             }
             __syncwarp();
-        };
-        // admit one scored candidate per lane into W: W stays the wcap best seen so far
-        // (search_engine.hpp:166-176 for a whole row at once)
-        auto admit = [&](bool fresh, float dist, uint32_t id) {
-            uint32_t m = __ballot_sync(kFull, fresh);
-            nevals += __popc(m);
-            while (m && count < wcap) {
-                const int src = __ffs(m) - 1;
-                m &= m - 1;
-                put(int(count), __shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src));
-                ++count;
-                if (count == wcap) recompute_worst();
+            if (count < wcap) ++count;
+            if (p <= cur) cur = p;
+            if (count == wcap) {
+                wd = sd[wcap - 1];
+                wi = sid[wcap - 1] & kIdMask;
             }
-            if (m) {
-                m &= __ballot_sync(kFull, fresh && key_less(dist, id, wd, wi));
-                while (m) {
-                    const int src = __ffs(m) - 1;
-                    m &= m - 1;
-                    const float d = __shfl_sync(kFull, dist, src);
-                    const uint32_t i = __shfl_sync(kFull, id, src);
-                    if (key_less(d, i, wd, wi)) {
-                        put(wpos, d, i);
-                        recompute_worst();
-                    }
-                }
-            }
-            __syncwarp();
         };
+
         // offer one node per lane: visited test-and-set, score, admit (search_engine.hpp:153-177)
         auto offer = [&](uint32_t id, bool in_range) {
             // a node listed twice in one row is offered once (the second copy would find it visited)
@@ -237,9 +261,42 @@ __global__ void search_kernel(SearchArgs a) {
                 if ((word >> (id & 31)) & 1u) fresh = false;
                 else atomicOr(vis + (id >> 5), 1u << (id & 31));
             }
-            float dist = 0.0f;
-            if (fresh) dist = asym_distance<U16>(table, a.codes, id, a.K, a.P);
-            admit(fresh, dist, id);
+            uint32_t m = __ballot_sync(kFull, fresh);
+            const int nf = __popc(m);
+            nevals += nf;
+            if (nf == 0) return;
+            if (coop_ok && nf <= kCoopMax) {
+                // few fresh nodes: the whole warp scores each of them, one rotation per lane
+                uint32_t cid[kCoopMax], comp[kCoopMax];
+#pragma unroll
+                for (int f = 0; f < kCoopMax; ++f) {
+                    cid[f] = kInvalidNode;
+                    comp[f] = 0;
+                    if (f < nf) {
+                        const int src = __ffs(m) - 1;
+                        m &= m - 1;
+                        cid[f] = __shfl_sync(kFull, id, src);
+                        if (lane < a.K)
+                            comp[f] = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes, lane);
+                    }
+                }
+#pragma unroll
+                for (int f = 0; f < kCoopMax; ++f) {
+                    if (f < nf) {
+                        const float d = asym_distance_coop(table, a.K, a.P, comp[f], lane);
+                        try_admit(d, cid[f]);
+                    }
+                }
+            } else {
+                float dist = 0.0f;
+                if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
+                if (count == wcap) m &= __ballot_sync(kFull, fresh && key_less(dist, id, wd, wi));
+                while (m) {
+                    const int src = __ffs(m) - 1;
+                    m &= m - 1;
+                    try_admit(__shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src));
+                }
+            }
         };
 
         if (scan_mode) {
@@ -250,8 +307,15 @@ __global__ void search_kernel(SearchArgs a) {
                 const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
                 const bool ok = id < a.n;
                 float dist = 0.0f;
-                if (ok) dist = asym_distance<U16>(table, a.entry_codes, e, a.K, a.P);
-                admit(ok, dist, id);
+                if (ok) dist = asym_distance_lane<U16>(table, a.entry_codes, e, a.K, a.P);
+                uint32_t m = __ballot_sync(kFull, ok);
+                nevals += __popc(m);
+                if (count == wcap) m &= __ballot_sync(kFull, ok && key_less(dist, id, wd, wi));
+                while (m) {
+                    const int src = __ffs(m) - 1;
+                    m &= m - 1;
+                    try_admit(__shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src));
+                }
             }
             // the seeds are now offered to the walk: mark them visited and remember them for the clean-up
             nseeds = count;
@@ -261,20 +325,21 @@ __global__ void search_kernel(SearchArgs a) {
                 atomicOr(vis + (id >> 5), 1u << (id & 31));
                 seedlist[p] = id;
             }
-            __syncwarp();
             if (nseeds > beam) {  // a beam narrower than the seed set keeps the best `beam` seeds
-                int ns = 32;
-                while (ns < int(nseeds)) ns <<= 1;
-                warp_sort_smem(sd, sid, ns, lane);
+                __syncwarp();
                 for (uint32_t p = beam + lane; p < uint32_t(cap); p += 32) {
                     sd[p] = INFINITY;
                     sid[p] = kInvalidNode;
                 }
                 count = beam;
-                __syncwarp();
             }
+            __syncwarp();
             wcap = beam;
-            if (count == wcap) recompute_worst();
+            cur = 0;
+            if (count == wcap) {
+                wd = sd[wcap - 1];
+                wi = sid[wcap - 1] & kIdMask;
+            }
         } else {
             for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
                 const uint32_t e = e0 + lane;
@@ -283,41 +348,30 @@ __global__ void search_kernel(SearchArgs a) {
             }
         }
 
-        while (true) {
+        while (cur < count) {
             // closest member of W that has not been expanded (search_engine.hpp:121-123)
-            float ld = 0.0f;
-            uint32_t li = 0;
-            int lp = -1;
-            for (int p = lane; p < int(count); p += 32) {
-                if ((expw[p >> 5] >> lane) & 1u) continue;
-                const float d = sd[p];
-                const uint32_t i = sid[p];
-                if (lp < 0 || key_less(d, i, ld, li)) {
-                    ld = d;
-                    li = i;
-                    lp = p;
-                }
-            }
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                const float od = __shfl_xor_sync(kFull, ld, o);
-                const uint32_t oi = __shfl_xor_sync(kFull, li, o);
-                const int op = __shfl_xor_sync(kFull, lp, o);
-                if (op >= 0 && (lp < 0 || key_less(od, oi, ld, li))) {
-                    ld = od;
-                    li = oi;
-                    lp = op;
-                }
-            }
-            if (lp < 0) break;
+            const uint32_t node = sid[cur] & kIdMask;
+            __syncwarp();
             if (lane == 0) {
-                expw[lp >> 5] |= 1u << (lp & 31);
-                if (nexp < a.exp_cap) explist[nexp] = li;
+                sid[cur] = node | kExpanded;
+                if (nexp < a.exp_cap) explist[nexp] = node;
             }
             if (nexp >= a.exp_cap) exp_overflow = true;
             ++nexp;
             __syncwarp();
-            const uint32_t* row = a.adj + size_t(li) * a.M;
+            // advance the cursor to the next unexpanded member
+            uint32_t nxt = cur + 1;
+            while (nxt < count) {
+                const uint32_t j = nxt + lane;
+                const uint32_t un = __ballot_sync(kFull, j < count && !(sid[j] & kExpanded));
+                if (un) {
+                    nxt += __ffs(un) - 1;
+                    break;
+                }
+                nxt += 32;
+            }
+            cur = min(nxt, count);
+            const uint32_t* row = a.adj + size_t(node) * a.M;
             for (int m0 = 0; m0 < a.M; m0 += 32) {
                 const int j = m0 + lane;
                 const uint32_t id = j < a.M ? __ldg(row + j) : kInvalidNode;
@@ -325,8 +379,8 @@ __global__ void search_kernel(SearchArgs a) {
             }
         }
 
-        // return the visited bitset to all-zero: every marked node is an entry id or a neighbour
-        // of an expanded node
+        // return the visited bitset to all-zero: every marked node is a seed / entry id or a
+        // neighbour of an expanded node
         if (exp_overflow) {
             for (uint64_t w = lane; w < a.vis_words; w += 32) vis[w] = 0;
         } else {
@@ -348,12 +402,11 @@ __global__ void search_kernel(SearchArgs a) {
                 }
             }
         }
+        // W is sorted already; drop the expanded flags
+        for (uint32_t p = lane; p < count; p += 32) sid[p] &= kIdMask;
         __syncwarp();
-
-        // sort W ascending; positions past `count` hold (+inf, no node)
         int nsort = 32;
         while (nsort < int(count)) nsort <<= 1;
-        warp_sort_smem(sd, sid, nsort, lane);
 
         if (a.rerank_k) {
             const uint32_t ncand = min(a.rerank_k, count);
@@ -430,7 +483,7 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam) {
     const size_t table_bytes = size_t(h->K) * h->P * 4;
     c.table_smem = table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
     const size_t dim_pad = (size_t(h->dim) + 3) & ~size_t(3);
-    size_t per_warp = (c.table_smem ? table_bytes : 0) + size_t(c.cap) * 8 + size_t(c.cap / 32) * 4 + dim_pad * 4;
+    size_t per_warp = (c.table_smem ? table_bytes : 0) + size_t(c.cap) * 8 + dim_pad * 4;
     per_warp = (per_warp + 15) & ~size_t(15);
     const size_t budget = 220 * 1024;
     int w = int(budget / per_warp);
@@ -503,6 +556,7 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.comp_bytes = int(h->comp_bytes);
     a.beam = beam;
     a.cap = c.cap;
+    a.per_warp_smem = uint32_t(c.per_warp);
     a.k = k;
     a.rerank_k = rerank_k;
     a.visited = h->d_visited.as<uint32_t>();

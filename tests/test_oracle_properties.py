@@ -16,6 +16,22 @@ def small_index(oracle, n=600, nq=20, dim=32, K=16, seed=3, cb=1):
     return base, q, signs, codes
 
 
+def tree_score(terms):
+    """Sum of K term arrays in the oracle's declared order: blocks of 32, pairs 16/8/4/2/1 apart."""
+    K = len(terms)
+    zero = np.zeros_like(terms[0])
+    score = zero.copy()
+    for c0 in range(0, K, 32):
+        t = [terms[c0 + j] if c0 + j < K else zero for j in range(32)]
+        step = 16
+        while step >= 1:
+            for j in range(step):
+                t[j] = (t[j] + t[j + step]).astype(np.float32)
+            step //= 2
+        score = (score + t[0]).astype(np.float32)
+    return score
+
+
 def test_code_distance_counts_differing_components(oracle):
     rng = np.random.default_rng(0)
     for dt in (np.uint8, np.uint16):
@@ -90,10 +106,16 @@ def test_search_is_exhaustive_when_beam_covers_component(oracle):
     ids, dist = oracle.search(rot, codes, adj, np.array([0], np.uint32), n, 10)
     P = rot.shape[2]
     for qi in range(q.shape[0]):
-        score = np.zeros(n, np.float32)
+        terms = []
         for r in range(16):
             v = rot[qi, r, codes[:, r] >> 1]
-            score = score + np.where(codes[:, r] & 1, -v, v).astype(np.float32)
+            terms.append(np.where(codes[:, r] & 1, -v, v).astype(np.float32))
+        score = tree_score(terms)
+        # the declared tree order stays within 1e-5 relative of the reference's sequential sum
+        seq = np.zeros(n, np.float32)
+        for tm in terms:
+            seq = (seq + tm).astype(np.float32)
+        assert np.allclose(score, seq, rtol=1e-5, atol=1e-5 * float(np.abs(np.stack(terms)).sum(0).max()))
         order = sorted((float(-score[j]), j) for j in range(n))[:10]
         assert ids[qi].tolist() == [j for _, j in order]
         assert np.array_equal(dist[qi], np.array([d for d, _ in order], np.float32))
