@@ -58,7 +58,12 @@ struct SearchArgs {
     uint32_t* out_ids;
     float* out_dist;
     uint32_t* stats;
+    uint32_t* next_query;  // work counter, zero at launch
 };
+
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
 
 __device__ __forceinline__ bool key_less(float da, uint32_t ia, float db, uint32_t ib) {
     return da < db || (da == db && ia < ib);
@@ -169,7 +174,7 @@ __global__ void search_kernel(SearchArgs a) {
     uint32_t* sid = reinterpret_cast<uint32_t*>(qsm + dim_pad);  // W: node ids (+ expanded bit), ascending
     float* sd = reinterpret_cast<float*>(sid + cap);             // W: distances
 
-    const uint32_t gwarp = blockIdx.x * warps + warp, total_warps = gridDim.x * warps;
+    const uint32_t gwarp = blockIdx.x * warps + warp;
     uint32_t* vis = a.visited + size_t(gwarp) * a.vis_words;
     // per-warp list in HBM: kSeedSlots seed ids, then the ids of expanded nodes
     uint32_t* seedlist = a.explist + size_t(gwarp) * (a.exp_cap + kSeedSlots);
@@ -179,7 +184,13 @@ __global__ void search_kernel(SearchArgs a) {
     const int row_bytes = a.K * (U16 ? 2 : 1);
     const bool coop_ok = a.K <= 32;
 
-    for (uint32_t q = gwarp; q < a.nq; q += total_warps) {
+    // queries are handed out one at a time from a global counter, so that warps that draw short
+    // walks take more of them
+    while (true) {
+        uint32_t q = 0;
+        if (lane == 0) q = atomicAdd(a.next_query, 1u);
+        q = __shfl_sync(kFull, q, 0);
+        if (q >= a.nq) break;
         const float* table = a.tables + size_t(q) * a.K * a.P;
         if (TABLE_SMEM) {
             const float4* src = reinterpret_cast<const float4*>(table);
@@ -304,6 +315,10 @@ __global__ void search_kernel(SearchArgs a) {
             // n_seed best in W; nothing is marked visited until the seeds are known
             for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {
                 const uint32_t e = e0 + lane;
+                if (e + 32 < a.n_entry) {  // pull the next batch towards L1 while this one is scored
+                    prefetch_l1(a.entry + e + 32);
+                    prefetch_l1(static_cast<const unsigned char*>(a.entry_codes) + size_t(e + 32) * row_bytes);
+                }
                 const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
                 const bool ok = id < a.n;
                 float dist = 0.0f;
@@ -348,6 +363,7 @@ __global__ void search_kernel(SearchArgs a) {
             }
         }
 
+        uint32_t pre_node = kInvalidNode, pre_id = kInvalidNode;  // row loaded ahead for the predicted next node
         while (cur < count) {
             // closest member of W that has not been expanded (search_engine.hpp:121-123)
             const uint32_t node = sid[cur] & kIdMask;
@@ -372,7 +388,14 @@ __global__ void search_kernel(SearchArgs a) {
             }
             cur = min(nxt, count);
             const uint32_t* row = a.adj + size_t(node) * a.M;
-            for (int m0 = 0; m0 < a.M; m0 += 32) {
+            // first 32 neighbours: already on their way when the prediction of the last round held
+            const uint32_t first = node == pre_node ? pre_id : (lane < a.M ? __ldg(row + lane) : kInvalidNode);
+            // predict the next node (the cursor, unless this expansion admits something closer)
+            // and start loading its row now
+            pre_node = cur < count ? (sid[cur] & kIdMask) : kInvalidNode;
+            pre_id = (pre_node != kInvalidNode && lane < a.M) ? __ldg(a.adj + size_t(pre_node) * a.M + lane) : kInvalidNode;
+            offer(first, first < a.n);
+            for (int m0 = 32; m0 < a.M; m0 += 32) {
                 const int j = m0 + lane;
                 const uint32_t id = j < a.M ? __ldg(row + j) : kInvalidNode;
                 offer(id, id < a.n);
@@ -393,12 +416,18 @@ __global__ void search_kernel(SearchArgs a) {
                 }
             }
             __syncwarp();
-            for (uint32_t x = 0; x < nexp; ++x) {
-                const uint32_t node = __ldcg(explist + x);
-                const uint32_t* row = a.adj + size_t(node) * a.M;
-                for (int j = lane; j < a.M; j += 32) {
-                    const uint32_t id = __ldg(row + j);
-                    if (id < a.n) vis[id >> 5] = 0;
+            for (uint32_t x0 = 0; x0 < nexp; x0 += 32) {
+                // 32 expanded nodes at a time: their rows are independent loads
+                const uint32_t mine_node = x0 + lane < nexp ? __ldcg(explist + x0 + lane) : kInvalidNode;
+                const int nb = int(min(32u, nexp - x0));
+                for (int j0 = 0; j0 < a.M; j0 += 32) {
+                    const int j = j0 + lane;
+#pragma unroll 8
+                    for (int t = 0; t < nb; ++t) {
+                        const uint32_t node = __shfl_sync(kFull, mine_node, t);
+                        const uint32_t id = j < a.M ? __ldg(a.adj + size_t(node) * a.M + j) : kInvalidNode;
+                        if (id < a.n) vis[id >> 5] = 0;
+                    }
                 }
             }
         }
@@ -412,6 +441,7 @@ __global__ void search_kernel(SearchArgs a) {
             const uint32_t ncand = min(a.rerank_k, count);
             const int g = lane >> 3, j = lane & 7;
             const bool vec4 = (a.dim & 3) == 0;
+#pragma unroll 4
             for (uint32_t c0 = 0; c0 < ncand; c0 += 4) {
                 const uint32_t c = c0 + g;
                 float acc = 0.0f;
@@ -485,7 +515,7 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam) {
     const size_t dim_pad = (size_t(h->dim) + 3) & ~size_t(3);
     size_t per_warp = (c.table_smem ? table_bytes : 0) + size_t(c.cap) * 8 + dim_pad * 4;
     per_warp = (per_warp + 15) & ~size_t(15);
-    const size_t budget = 220 * 1024;
+    const size_t budget = 226 * 1024;  // of the 227 KB a block may use
     int w = int(budget / per_warp);
     if (w > 16) w = 16;
     if (w < 1) w = 1;
@@ -566,6 +596,8 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.out_ids = d_ids;
     a.out_dist = d_dists;
     a.stats = d_stats;
+    a.next_query = h->d_status.as<uint32_t>() + 1;
+    CPB_CUDA(cudaMemsetAsync(a.next_query, 0, 4, st));
     const unsigned grid = unsigned(h->sm_count);
     const bool u16 = h->comp_bytes == 2;
     LaunchTimer timer(h, kKernelSearch, st);
