@@ -302,8 +302,8 @@ int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
             for (uint64_t i = 0; i < P; ++i) h->signs[(size_t(r) * 3 + l) * P + i] = coin(rng) ? 1 : -1;
     }
     int rc = upload_signs(h);
-    if (rc == 0) rc = h->d_status.reserve(16);
-    if (rc == 0 && cudaMemset(h->d_status.p, 0, 16) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "memset status");
+    if (rc == 0) rc = h->d_status.reserve(256);
+    if (rc == 0 && cudaMemset(h->d_status.p, 0, 256) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "memset status");
     if (rc != 0) {
         delete h;
         return rc;

@@ -88,6 +88,7 @@ struct cphnsw_b200_index {
     std::vector<float> h_vectors;  // host copy of everything added (rebuilds append to it)
     cpb::DevBuf d_vectors, d_codes, d_adj, d_entry, d_entry_codes;
     uint32_t n_entry = 0;
+    uint64_t vis_stride = 0;  // bytes per warp slot of d_visited
 
     // search scratch
     cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;

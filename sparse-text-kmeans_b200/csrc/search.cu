@@ -20,8 +20,11 @@
 //
 // W lives in shared memory, sorted ascending, the "expanded" flag in the top bit of the id; a
 // cursor tracks the first unexpanded member, an admission finds its rank with a two-round 32-ary
-// search and shifts the tail up by one.  Visited nodes are tracked in a per-warp bitset in global
-// memory that the warp itself returns to all-zero after each query.  For search_and_rerank the
+// search and shifts the tail up by one.  Visited nodes are tracked in a per-warp array of one
+// byte per node in global memory holding the number ("epoch") of the last query of that warp
+// that visited the node, so nothing has to be cleared between queries (the array is zeroed when
+// the 8-bit epoch wraps).  The adjacency row and the visited bytes of the node expected to be
+// expanded next are loaded one expansion ahead.  For search_and_rerank the
 // best rerank_k are re-scored with -<q,x> (replaces gather_vectors_kernel + batch_dot_product_kernel
 // + the host partial_sort of src/cuda/gpu_encoder.cu:605-664) and sorted by a bitonic network.
 #include <cmath>
@@ -32,7 +35,6 @@ namespace cpb {
 namespace {
 
 constexpr uint32_t kFull = 0xffffffffu;
-constexpr uint32_t kSeedSlots = 128;        // most seeds a query can have (k_entry <= 100)
 constexpr uint32_t kExpanded = 0x80000000u; // top bit of a stored id: the member has been expanded
 constexpr uint32_t kIdMask = 0x7fffffffu;
 constexpr int kCoopMax = 8;                 // up to this many fresh nodes are scored by the whole warp
@@ -51,10 +53,9 @@ struct SearchArgs {
     int K, P, dim, M, comp_bytes;
     uint32_t per_warp_smem;           // bytes of shared memory per warp (multiple of 16)
     uint32_t beam, cap, k, rerank_k;  // cap: power of two >= max(32, beam, n_seed), the size of W's arrays
-    uint32_t* visited;  // [total warps][vis_words], all zero between queries
-    uint64_t vis_words;
-    uint32_t* explist;  // [total warps][kSeedSlots + exp_cap]
-    uint32_t exp_cap;
+    uint8_t* visited;    // [warp slots][vis_stride]: epoch of the last query that visited the node
+    uint64_t vis_stride; // bytes per warp slot (n rounded up to 16)
+    uint32_t* epochs;    // [warp slots]: last epoch used by the slot (persists across launches)
     uint32_t* out_ids;
     float* out_dist;
     uint32_t* stats;
@@ -175,10 +176,8 @@ __global__ void search_kernel(SearchArgs a) {
     float* sd = reinterpret_cast<float*>(sid + cap);             // W: distances
 
     const uint32_t gwarp = blockIdx.x * warps + warp;
-    uint32_t* vis = a.visited + size_t(gwarp) * a.vis_words;
-    // per-warp list in HBM: kSeedSlots seed ids, then the ids of expanded nodes
-    uint32_t* seedlist = a.explist + size_t(gwarp) * (a.exp_cap + kSeedSlots);
-    uint32_t* explist = seedlist + kSeedSlots;
+    uint8_t* vis = a.visited + size_t(gwarp) * a.vis_stride;
+    uint32_t epoch = a.epochs[gwarp];  // 1..255; 0 marks "never visited"
     const uint32_t beam = a.beam;
     const bool scan_mode = a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
@@ -206,12 +205,16 @@ __global__ void search_kernel(SearchArgs a) {
             sd[p] = INFINITY;
             sid[p] = kInvalidNode;
         }
+        if (++epoch == 256) {  // the 8-bit epoch wraps: forget every earlier query
+            uint4* v4 = reinterpret_cast<uint4*>(vis);
+            for (uint64_t i = lane; i < a.vis_stride / 16; i += 32) v4[i] = make_uint4(0u, 0u, 0u, 0u);
+            epoch = 1;
+        }
         __syncwarp();
 
-        uint32_t count = 0, nexp = 0, nevals = 0, nseeds = 0;
+        uint32_t count = 0, nexp = 0, nevals = 0;
         uint32_t wcap = scan_mode ? a.n_seed : beam;  // capacity of W: the seeds first, then the beam
         uint32_t cur = 0;                             // first unexpanded position of W (== count when none)
-        bool exp_overflow = false;
         float wd = INFINITY;  // worst member of W once it is full
         uint32_t wi = kInvalidNode;
 
@@ -263,19 +266,24 @@ __global__ void search_kernel(SearchArgs a) {
         };
 
         // offer one node per lane: visited test-and-set, score, admit (search_engine.hpp:153-177)
-        auto offer = [&](uint32_t id, bool in_range) {
+        // `have_vis`: the node's visited byte is already in `vbyte` (loaded one expansion ahead);
+        // `ahead()` runs once the visited marks of this row are made and its code loads issued
+        auto offer = [&](uint32_t id, bool in_range, bool have_vis, uint32_t vbyte, auto&& ahead) {
             // a node listed twice in one row is offered once (the second copy would find it visited)
             const uint32_t grp = __match_any_sync(kFull, id);
             bool fresh = in_range && (__ffs(grp) - 1) == lane;
             if (fresh) {
-                const uint32_t word = __ldcg(vis + (id >> 5));
-                if ((word >> (id & 31)) & 1u) fresh = false;
-                else atomicOr(vis + (id >> 5), 1u << (id & 31));
+                if (!have_vis) vbyte = __ldcg(vis + id);
+                if (vbyte == epoch) fresh = false;
+                else vis[id] = uint8_t(epoch);
             }
-            uint32_t m = __ballot_sync(kFull, fresh);
+            uint32_t m = __ballot_sync(kFull, fresh);  // (orders the marks before anything loaded below)
             const int nf = __popc(m);
             nevals += nf;
-            if (nf == 0) return;
+            if (nf == 0) {
+                ahead();
+                return;
+            }
             if (coop_ok && nf <= kCoopMax) {
                 // few fresh nodes: the whole warp scores each of them, one rotation per lane
                 uint32_t cid[kCoopMax], comp[kCoopMax];
@@ -291,6 +299,7 @@ __global__ void search_kernel(SearchArgs a) {
                             comp[f] = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes, lane);
                     }
                 }
+                ahead();
 #pragma unroll
                 for (int f = 0; f < kCoopMax; ++f) {
                     if (f < nf) {
@@ -299,6 +308,7 @@ __global__ void search_kernel(SearchArgs a) {
                     }
                 }
             } else {
+                ahead();
                 float dist = 0.0f;
                 if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
                 if (count == wcap) m &= __ballot_sync(kFull, fresh && key_less(dist, id, wd, wi));
@@ -309,6 +319,7 @@ __global__ void search_kernel(SearchArgs a) {
                 }
             }
         };
+        auto nothing = [] {};
 
         if (scan_mode) {
             // entry scan: score every entry node from the contiguous copy of its code, keep the
@@ -332,14 +343,10 @@ __global__ void search_kernel(SearchArgs a) {
                     try_admit(__shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src));
                 }
             }
-            // the seeds are now offered to the walk: mark them visited and remember them for the clean-up
-            nseeds = count;
+            // the seeds are now offered to the walk: mark them visited
+            const uint32_t nseeds = count;
             nevals += nseeds;
-            for (uint32_t p = lane; p < nseeds; p += 32) {
-                const uint32_t id = sid[p];
-                atomicOr(vis + (id >> 5), 1u << (id & 31));
-                seedlist[p] = id;
-            }
+            for (uint32_t p = lane; p < nseeds; p += 32) vis[sid[p]] = uint8_t(epoch);
             if (nseeds > beam) {  // a beam narrower than the seed set keeps the best `beam` seeds
                 __syncwarp();
                 for (uint32_t p = beam + lane; p < uint32_t(cap); p += 32) {
@@ -359,20 +366,19 @@ __global__ void search_kernel(SearchArgs a) {
             for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
                 const uint32_t e = e0 + lane;
                 const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
-                offer(id, id < a.n);
+                offer(id, id < a.n, false, 0u, nothing);
             }
         }
 
-        uint32_t pre_node = kInvalidNode, pre_id = kInvalidNode;  // row loaded ahead for the predicted next node
+        // row and visited bytes loaded one expansion ahead for the node predicted to be next
+        uint32_t pre_node = kInvalidNode, pre_id = kInvalidNode, pre_vis = 0;
+        bool pre_vis_ok = false;
+        const bool single_row = a.M <= 32;  // the visited bytes stay valid only if no later marks intervene
         while (cur < count) {
             // closest member of W that has not been expanded (search_engine.hpp:121-123)
             const uint32_t node = sid[cur] & kIdMask;
             __syncwarp();
-            if (lane == 0) {
-                sid[cur] = node | kExpanded;
-                if (nexp < a.exp_cap) explist[nexp] = node;
-            }
-            if (nexp >= a.exp_cap) exp_overflow = true;
+            if (lane == 0) sid[cur] = node | kExpanded;
             ++nexp;
             __syncwarp();
             // advance the cursor to the next unexpanded member
@@ -388,49 +394,29 @@ __global__ void search_kernel(SearchArgs a) {
             }
             cur = min(nxt, count);
             const uint32_t* row = a.adj + size_t(node) * a.M;
-            // first 32 neighbours: already on their way when the prediction of the last round held
-            const uint32_t first = node == pre_node ? pre_id : (lane < a.M ? __ldg(row + lane) : kInvalidNode);
+            const bool hit = node == pre_node;
+            const uint32_t first = hit ? pre_id : (lane < a.M ? __ldg(row + lane) : kInvalidNode);
+            const bool have_vis = hit && pre_vis_ok;
+            const uint32_t first_vis = pre_vis;
             // predict the next node (the cursor, unless this expansion admits something closer)
-            // and start loading its row now
+            // and start loading its row now; its visited bytes follow once this row's marks are made
             pre_node = cur < count ? (sid[cur] & kIdMask) : kInvalidNode;
             pre_id = (pre_node != kInvalidNode && lane < a.M) ? __ldg(a.adj + size_t(pre_node) * a.M + lane) : kInvalidNode;
-            offer(first, first < a.n);
+            pre_vis_ok = false;
+            offer(first, first < a.n, have_vis, first_vis, [&] {
+                if (single_row) {
+                    __syncwarp();  // this row's marks are ordered before the bytes read ahead
+                    pre_vis = pre_id < a.n ? uint32_t(__ldcg(vis + pre_id)) : 0u;
+                    pre_vis_ok = true;
+                }
+            });
             for (int m0 = 32; m0 < a.M; m0 += 32) {
                 const int j = m0 + lane;
                 const uint32_t id = j < a.M ? __ldg(row + j) : kInvalidNode;
-                offer(id, id < a.n);
+                offer(id, id < a.n, false, 0u, nothing);
             }
         }
 
-        // return the visited bitset to all-zero: every marked node is a seed / entry id or a
-        // neighbour of an expanded node
-        if (exp_overflow) {
-            for (uint64_t w = lane; w < a.vis_words; w += 32) vis[w] = 0;
-        } else {
-            if (scan_mode) {
-                for (uint32_t p = lane; p < nseeds; p += 32) vis[__ldcg(seedlist + p) >> 5] = 0;
-            } else {
-                for (uint32_t e = lane; e < a.n_entry; e += 32) {
-                    const uint32_t id = __ldg(a.entry + e);
-                    if (id < a.n) vis[id >> 5] = 0;
-                }
-            }
-            __syncwarp();
-            for (uint32_t x0 = 0; x0 < nexp; x0 += 32) {
-                // 32 expanded nodes at a time: their rows are independent loads
-                const uint32_t mine_node = x0 + lane < nexp ? __ldcg(explist + x0 + lane) : kInvalidNode;
-                const int nb = int(min(32u, nexp - x0));
-                for (int j0 = 0; j0 < a.M; j0 += 32) {
-                    const int j = j0 + lane;
-#pragma unroll 8
-                    for (int t = 0; t < nb; ++t) {
-                        const uint32_t node = __shfl_sync(kFull, mine_node, t);
-                        const uint32_t id = j < a.M ? __ldg(a.adj + size_t(node) * a.M + j) : kInvalidNode;
-                        if (id < a.n) vis[id >> 5] = 0;
-                    }
-                }
-            }
-        }
         // W is sorted already; drop the expanded flags
         for (uint32_t p = lane; p < count; p += 32) sid[p] &= kIdMask;
         __syncwarp();
@@ -488,6 +474,7 @@ __global__ void search_kernel(SearchArgs a) {
         }
         __syncwarp();
     }
+    if (lane == 0) a.epochs[gwarp] = epoch;
 }
 
 __global__ void gather_rows_kernel(const unsigned char* __restrict__ src, int row_bytes,
@@ -541,15 +528,17 @@ int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
 }
 
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
-    const size_t total_warps = size_t(h->sm_count) * 16;  // the most warps a launch ever uses
-    const size_t vis_words = (h->n + 31) / 32;
-    const size_t vis_bytes = total_warps * vis_words * 4;
-    if (vis_bytes > h->d_visited.bytes || !h->d_visited.p) {
+    (void)beam;
+    const size_t slots = size_t(h->sm_count) * 16;  // the most warps a launch ever uses
+    const size_t stride = (size_t(h->n) + 15) & ~size_t(15);
+    const size_t vis_bytes = slots * stride;
+    if (vis_bytes > h->d_visited.bytes || !h->d_visited.p || h->vis_stride != stride) {
         CPB_TRY(h->d_visited.reserve(vis_bytes));
         CPB_CUDA(cudaMemset(h->d_visited.p, 0, h->d_visited.bytes));
+        CPB_TRY(h->d_explist.reserve(slots * 4));  // per-slot epoch counters
+        CPB_CUDA(cudaMemset(h->d_explist.p, 0, h->d_explist.bytes));
+        h->vis_stride = stride;
     }
-    const size_t exp_cap = size_t(4) * beam + 64;
-    CPB_TRY(h->d_explist.reserve(total_warps * (exp_cap + kSeedSlots) * 4));
     return 0;
 }
 
@@ -589,10 +578,9 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.per_warp_smem = uint32_t(c.per_warp);
     a.k = k;
     a.rerank_k = rerank_k;
-    a.visited = h->d_visited.as<uint32_t>();
-    a.vis_words = (h->n + 31) / 32;
-    a.explist = h->d_explist.as<uint32_t>();
-    a.exp_cap = 4 * beam + 64;
+    a.visited = h->d_visited.as<uint8_t>();
+    a.vis_stride = h->vis_stride;
+    a.epochs = h->d_explist.as<uint32_t>();
     a.out_ids = d_ids;
     a.out_dist = d_dists;
     a.stats = d_stats;

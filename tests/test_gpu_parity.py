@@ -230,3 +230,21 @@ def test_errors_do_not_exit(cp):
         idx.set_param("k_entry", 0)
     ids, _ = idx.search_batch(base[:2], 10, 10)  # still usable
     assert ids.shape == (2, 10)
+
+
+def test_visited_epoch_wraps_without_losing_exactness(cp, oracle):
+    """Each warp stamps visited nodes with an 8-bit per-query epoch; far more than 255 queries per
+    warp must keep returning exactly the oracle's answers (the stamp array is zeroed at the wrap)."""
+    n, dim, K, M = 1500, 128, 32, 16
+    base, q = synthetic.gaussian_mixture(n, 40, dim, 6, 0.3, 321)
+    idx = make_index(cp, dim, K, 1, M=M)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 4)
+    idx.add_batch_parallel(base)
+    signs, codes, adj = oracle_index(oracle, base, K, 1, M, 32)
+    _, rot, _ = oracle.encode(q, K, 1, signs, 2, want_rotated=True)
+    wi, wd = oracle.search(rot, codes, adj, idx.entry_ids(), 24, 8, n_seed=4)
+    reps = 16000  # 640k queries over at most 148 x 16 warps: every warp passes several wraps
+    ids, dist = idx.search_batch(np.tile(q, (reps, 1)), 8, 24)
+    assert np.array_equal(ids.reshape(reps, 40, 8), np.broadcast_to(wi, (reps, 40, 8)))
+    assert np.array_equal(dist.reshape(reps, 40, 8), np.broadcast_to(wd, (reps, 40, 8)))
