@@ -109,11 +109,16 @@ class CPHNSWIndex:
         self.code_dtype = np.uint8 if component_bytes == 1 else np.uint16
 
     def close(self):
-        if getattr(self, "_h", None) and self._h.value:
-            self._lib.cphnsw_b200_destroy(self._h)
-            self._h = C.c_void_p()
+        h = getattr(self, "_h", None)
+        if h is not None and h.value:
+            self._lib.cphnsw_b200_destroy(h)
+            h.value = None
 
-    __del__ = close
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: module globals may already be gone
+            pass
 
     @property
     def handle(self):

@@ -324,6 +324,11 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
     std::string s(name);
     if (s == "keep_pruned") { h->keep_pruned = v != 0.0; return 0; }
     if (s == "profile") { h->profile = v != 0.0; return 0; }
+    if (s == "knn_kernel") {
+        if (v != 0 && v != 1 && v != 2) { set_error("knn_kernel must be 0 (pick), 1 (byte-wise) or 2 (bit-sliced)"); return CPHNSW_B200_E_INVALID; }
+        h->knn_kernel = int(v);
+        return 0;
+    }
     if (s == "k_entry") {
         if (v < 1) { set_error("CPHNSWParams: k_entry must be > 0"); return CPHNSW_B200_E_INVALID; }
         if (v > 100) { set_error("CPHNSWParams: k_entry must be <= 100"); return CPHNSW_B200_E_INVALID; }
@@ -351,6 +356,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     std::string s(name);
     if (s == "keep_pruned") *v = h->keep_pruned;
     else if (s == "profile") *v = h->profile;
+    else if (s == "knn_kernel") *v = h->knn_kernel;
     else if (s == "k_entry") *v = h->k_entry;
     else if (s == "knn_k") *v = h->knn_k;
     else if (s == "entry_scan") *v = h->entry_scan;

@@ -77,6 +77,7 @@ struct cphnsw_b200_index {
     int device = 0;
     int keep_pruned = 1;
     uint32_t k_entry = 4, knn_k = 0, entry_scan = 0;
+    int knn_kernel = 0;  // 0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance
     int sm_count = 0;
 
     std::vector<int8_t> signs;  // host [K][3][P]
@@ -93,7 +94,7 @@ struct cphnsw_b200_index {
     // search scratch
     cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
     // stage scratch for the host-pointer entry points
-    cpb::DevBuf s_in, s_in2, s_out, s_out2, s_pad, s_pad2;
+    cpb::DevBuf s_in, s_in2, s_out, s_out2, s_pad, s_pad2, s_sliced;
 
     uint64_t launches = 0;
 
@@ -116,6 +117,10 @@ int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, con
                          uint64_t nb, uint16_t* d_out, cudaStream_t st);
 int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
                      uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st);
+// bit-sliced variant of the kNN kernel (uint8 components, K = 16 or 32)
+bool knn_sliced_supported(const cphnsw_b200_index* h);
+int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                            uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st);
 int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
                             uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
                             uint32_t* d_adj, cudaStream_t st);

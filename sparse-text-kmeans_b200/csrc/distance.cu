@@ -16,11 +16,17 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "knn_common.cuh"
 
 namespace cpb {
 namespace {
 
-constexpr uint32_t kFull = 0xffffffffu;
+using knn::kFull;
+using knn::bulk_g2s;
+using knn::mbar_expect_tx;
+using knn::mbar_init;
+using knn::mbar_wait_bounded;
+using knn::kWaitLimit;
 
 // ---- SWAR component-mismatch count -------------------------------------------------------------
 template <int WC, bool U16>
@@ -93,48 +99,10 @@ code_distance_kernel(const uint32_t* __restrict__ a, uint64_t na, const uint32_t
     }
 }
 
-// ---- mbarrier / bulk-copy helpers -------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a short,
-// hardware-bounded time) and reports failure instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit) {
-    for (uint32_t i = 0; i < limit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// 1-D bulk asynchronous copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-            smem_u32(dst)),
-        "l"(src), "r"(bytes), "r"(smem_u32(bar))
-        : "memory");
-}
-
 // ---- kNN graph ---------------------------------------------------------------------------------------
 constexpr int kKnnWarps = 4;
 constexpr int kKnnThreads = kKnnWarps * 32;
-constexpr int kKnnTile = 1024;           // candidates per shared-memory stage
-constexpr uint32_t kWaitLimit = 1u << 22;  // polls before a wait is declared lost
+constexpr int kKnnTile = knn::kTile;  // candidates per shared-memory stage
 
 template <int WC, bool U16, int SLOTS, int Q>
 __global__ void __launch_bounds__(kKnnThreads)
@@ -241,39 +209,8 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
                         const uint32_t dd = __shfl_sync(kFull, d[q], src);
                         if (dd >= tau[q]) continue;  // tightened by an earlier lane
                         const uint32_t id = uint32_t(base + c0 + src);
-                        // rank = number of kept elements with distance <= dd (their ids are lower)
-                        int p = 0;
-#pragma unroll
-                        for (int s = 0; s < SLOTS; ++s) p += __popc(__ballot_sync(kFull, ld[q][s] <= dd));
-#pragma unroll
-                        for (int s = SLOTS - 1; s >= 0; --s) {
-                            uint32_t ud = __shfl_up_sync(kFull, ld[q][s], 1);
-                            uint32_t ui = __shfl_up_sync(kFull, li[q][s], 1);
-                            if (s > 0) {
-                                uint32_t cd = __shfl_sync(kFull, ld[q][s - 1], 31);
-                                uint32_t ci = __shfl_sync(kFull, li[q][s - 1], 31);
-                                if (lane == 0) {
-                                    ud = cd;
-                                    ui = ci;
-                                }
-                            }
-                            const int rank = s * 32 + lane;
-                            if (rank > p) {
-                                ld[q][s] = ud;
-                                li[q][s] = ui;
-                            } else if (rank == p) {
-                                ld[q][s] = dd;
-                                li[q][s] = id;
-                            }
-                        }
-                        // threshold = distance of the element of rank k (the (k+1)-th: room for self)
-                        uint32_t tk = kFull;
-#pragma unroll
-                        for (int s = 0; s < SLOTS; ++s) {
-                            const uint32_t v = __shfl_sync(kFull, ld[q][s], int(k & 31));
-                            if (s == int(k >> 5)) tk = v;
-                        }
-                        tau[q] = tk;
+                        knn::list_insert<SLOTS>(ld[q], li[q], dd, id, lane);
+                        tau[q] = knn::list_threshold<SLOTS>(ld[q], k);
                     }
                 }
             }
@@ -301,30 +238,8 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
     for (int q = 0; q < Q; ++q) {
         const uint64_t row = first_row + q;
         if (row >= row_end) continue;
-        int selfrank = 0x7fffffff, valid = 0;
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            uint32_t ms = __ballot_sync(kFull, li[q][s] == uint32_t(row));
-            if (ms && selfrank == 0x7fffffff) selfrank = s * 32 + __ffs(ms) - 1;
-            valid += __popc(__ballot_sync(kFull, li[q][s] != kInvalidNode));
-        }
-        uint32_t* out_n = nbrs + (row - row_begin) * uint64_t(k);
-        uint16_t* out_d = dists ? dists + (row - row_begin) * uint64_t(k) : nullptr;
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const int rank = s * 32 + lane;
-            if (li[q][s] == kInvalidNode || rank == selfrank) continue;
-            const int o = rank - (rank > selfrank ? 1 : 0);
-            if (o < int(k)) {
-                out_n[o] = li[q][s];
-                if (out_d) out_d[o] = uint16_t(ld[q][s]);
-            }
-        }
-        int n_out = valid - (selfrank != 0x7fffffff ? 1 : 0);
-        for (int o = n_out + lane; o < int(k); o += 32) {
-            out_n[o] = kInvalidNode;
-            if (out_d) out_d[o] = 0xFFFF;
-        }
+        knn::list_write<SLOTS>(ld[q], li[q], row, k, nbrs + (row - row_begin) * uint64_t(k),
+                               dists ? dists + (row - row_begin) * uint64_t(k) : nullptr, lane);
     }
 }
 
@@ -528,6 +443,12 @@ int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint
         set_error("code rows wider than 64 bytes are not supported by the distance kernels");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
+    if (h->knn_kernel == 2 && !knn_sliced_supported(h)) {
+        set_error("knn_kernel=2 (bit-sliced) needs uint8 components and K = 16 or 32");
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    if (h->knn_kernel != 1 && knn_sliced_supported(h))
+        return launch_knn_graph_sliced(h, d_codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
     const bool u16 = h->comp_bytes == 2;
     const uint32_t* pc;
     CPB_TRY(padded_view(h, d_codes, n, WC, h->s_pad, st, &pc));

@@ -1,0 +1,302 @@
+// Brute-force code-distance kNN graph with a bit-sliced distance (uint8 components, K = 16 or 32).
+//
+// Same result as knn_graph_kernel in distance.cu (k smallest under (distance, id), self excluded),
+// four times fewer integer instructions per pair.  The candidates are re-laid out once, 32 at a
+// time, as bit planes: word (r, b) of a group holds bit b of component r of its 32 candidates.
+// For a query with component q_r, the candidates that differ from it in rotation r are
+//      neq_r = OR_b ( plane(r,b) XOR mask(q_r,b) ),      mask = all ones if bit b of q_r is set,
+// eight 3-input logic instructions for 32 candidates; the K one-bit planes neq_r are then summed
+// with carry-save adders (two logic instructions per full adder, K - 6 adders for K = 32) into
+// six planes holding the 32 distances, which are compared with the row's admission threshold in
+// bit-sliced form as well.  Only candidates below the threshold (rare once the list has warmed
+// up) are unpacked and inserted into the row's running list.
+//
+// Work split: a warp owns Q query rows; their masks (1 KB each at K = 32) sit in shared memory
+// and are read with broadcast 128-bit loads.  A tile is 1024 candidates = 32 groups, one group
+// per lane, laid out [16-byte chunk][group] so that the lanes' 128-bit loads are conflict-free;
+// tiles arrive by bulk asynchronous copies (two stages, bounded waits), as in the byte-wise kernel.
+#include "knn_common.cuh"
+
+namespace cpb {
+namespace {
+
+using knn::kFull;
+constexpr int kSlWarps = 4;
+constexpr int kSlThreads = kSlWarps * 32;
+constexpr int kSlQ = 8;  // query rows per warp
+
+// full adder on bit planes: (carry, sum) of a + b + c
+__device__ __forceinline__ void csa(uint32_t& carry, uint32_t& sum, uint32_t a, uint32_t b, uint32_t c) {
+    const uint32_t u = a ^ b;
+    carry = (a & b) | (u & c);
+    sum = u ^ c;
+}
+
+// ---- layout transform: codes [n][K] bytes -> tiles [tile][chunk (2K)][group (32)][4 words] ----------
+// one warp per group of 32 candidates; candidates past n read as zero codes (masked out later)
+__global__ void slice_codes_kernel(const uint8_t* __restrict__ codes, uint64_t n, int K, uint32_t* __restrict__ out,
+                                   uint64_t n_groups) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t g = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (g >= n_groups) return;
+    const uint64_t cand = g * 32 + lane;
+    const uint64_t tile = g >> 5;
+    const int group = int(g & 31);
+    const int words_per_group = K * 8;            // bit planes per group
+    uint32_t* tile_out = out + tile * uint64_t(words_per_group) * 32;
+    for (int r = 0; r < K; ++r) {
+        const uint32_t byte = cand < n ? codes[cand * K + r] : 0u;
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const uint32_t plane = __ballot_sync(kFull, (byte >> b) & 1u);
+            const int w = r * 8 + b;  // plane index; chunk = w / 4, word in chunk = w % 4
+            if (lane == (w & 31)) tile_out[(size_t(w >> 2) * 32 + group) * 4 + (w & 3)] = plane;
+        }
+    }
+}
+
+template <int NBLK, int SLOTS>  // NBLK = K / 8 (2 or 4)
+__global__ void __launch_bounds__(kSlThreads)
+knn_sliced_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict__ codes, uint64_t n, uint32_t k,
+                  uint64_t row_begin, uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
+                  uint32_t* __restrict__ status) {
+    constexpr int K = NBLK * 8;
+    constexpr int CHUNKS = K * 2;                  // 16-byte chunks per group
+    constexpr uint32_t TILE_BYTES = CHUNKS * 32 * 16;
+    extern __shared__ __align__(128) unsigned char sl_smem[];
+    uint4* stage0 = reinterpret_cast<uint4*>(sl_smem);
+    uint4* stage1 = stage0 + CHUNKS * 32;
+    uint4* masks = stage1 + CHUNKS * 32;           // [warp][q][chunk]
+    __shared__ uint64_t full_bar[2];
+    __shared__ int abort_flag;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t tiles = (n + knn::kTile - 1) / knn::kTile;
+
+    if (threadIdx.x == 0) {
+        knn::mbar_init(&full_bar[0], 1);
+        knn::mbar_init(&full_bar[1], 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (uint64_t t = 0; t < 2 && t < tiles; ++t) {
+            knn::mbar_expect_tx(&full_bar[t], TILE_BYTES);
+            knn::bulk_g2s(t == 0 ? stage0 : stage1, sliced + t * (TILE_BYTES / 4), TILE_BYTES, &full_bar[t]);
+        }
+    }
+
+    // masks of this warp's Q rows: word (r, b) is all ones when bit b of the row's component r is set
+    const uint64_t first_row = row_begin + (uint64_t(blockIdx.x) * kSlWarps + warp) * kSlQ;
+    uint4* my_masks = masks + size_t(warp) * kSlQ * CHUNKS;
+    for (int q = 0; q < kSlQ; ++q) {
+        const uint64_t row = min(first_row + q, row_end - 1);
+        uint32_t* mw = reinterpret_cast<uint32_t*>(my_masks + q * CHUNKS);
+        for (int w = lane; w < K * 8; w += 32) {
+            const uint32_t byte = codes[row * K + (w >> 3)];
+            mw[w] = ((byte >> (w & 7)) & 1u) ? kFull : 0u;
+        }
+    }
+    __syncwarp();
+
+    uint32_t ld[kSlQ][SLOTS], li[kSlQ][SLOTS], tau[kSlQ];
+#pragma unroll
+    for (int q = 0; q < kSlQ; ++q) {
+        tau[q] = kFull;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            ld[q][s] = kFull;
+            li[q][s] = kInvalidNode;
+        }
+    }
+
+    bool lost = false;
+    for (uint64_t t = 0; t < tiles; ++t) {
+        const int st = int(t & 1);
+        const uint32_t parity = uint32_t((t >> 1) & 1);
+        if (!knn::mbar_wait_bounded(&full_bar[st], parity, knn::kWaitLimit)) abort_flag = 1;
+        __syncthreads();
+        if (abort_flag) {
+            lost = true;
+            break;
+        }
+        const uint4* tile = st == 0 ? stage0 : stage1;
+        const uint64_t group_base = t * knn::kTile + uint64_t(lane) * 32;  // id of this lane's first candidate
+        // candidates of this lane's group that exist
+        const uint32_t valid = group_base >= n ? 0u : (n - group_base >= 32 ? kFull : ((1u << (n - group_base)) - 1u));
+
+        // distance planes of the Q rows against this lane's 32 candidates
+        uint32_t ones[kSlQ], twos[kSlQ], fours[kSlQ], eights[kSlQ], sixteens[kSlQ], thirtytwos[kSlQ];
+        uint32_t pend8[kSlQ], pend16[kSlQ];
+#pragma unroll
+        for (int q = 0; q < kSlQ; ++q) ones[q] = twos[q] = fours[q] = eights[q] = sixteens[q] = thirtytwos[q] = pend8[q] = pend16[q] = 0;
+
+#pragma unroll 1
+        for (int blk = 0; blk < NBLK; ++blk) {
+            uint32_t twosA[kSlQ], twosB[kSlQ], foursA[kSlQ], foursB[kSlQ], prev[kSlQ];
+#pragma unroll
+            for (int rr = 0; rr < 8; ++rr) {
+                const int chunk = (blk * 8 + rr) * 2;
+                const uint4 s0 = tile[size_t(chunk) * 32 + lane];
+                const uint4 s1 = tile[size_t(chunk + 1) * 32 + lane];
+#pragma unroll
+                for (int q = 0; q < kSlQ; ++q) {
+                    const uint4 m0 = my_masks[q * CHUNKS + chunk];
+                    const uint4 m1 = my_masks[q * CHUNKS + chunk + 1];
+                    uint32_t x = s0.x ^ m0.x;
+                    x |= s0.y ^ m0.y;
+                    x |= s0.z ^ m0.z;
+                    x |= s0.w ^ m0.w;
+                    x |= s1.x ^ m1.x;
+                    x |= s1.y ^ m1.y;
+                    x |= s1.z ^ m1.z;
+                    x |= s1.w ^ m1.w;
+                    // carry-save accumulation of the 8 planes of this block
+                    if (rr & 1) {
+                        uint32_t& tw = (rr & 2) ? twosB[q] : twosA[q];
+                        csa(tw, ones[q], ones[q], prev[q], x);
+                        if ((rr & 3) == 3) {
+                            uint32_t& fo = (rr & 4) ? foursB[q] : foursA[q];
+                            csa(fo, twos[q], twos[q], twosA[q], twosB[q]);
+                            if (rr == 7) {
+                                uint32_t e8;
+                                csa(e8, fours[q], fours[q], foursA[q], foursB[q]);
+                                if (blk & 1) {
+                                    uint32_t s16;
+                                    csa(s16, eights[q], eights[q], pend8[q], e8);
+                                    if (NBLK == 2) {
+                                        sixteens[q] = s16;
+                                    } else if (blk & 2) {
+                                        csa(thirtytwos[q], sixteens[q], sixteens[q], pend16[q], s16);
+                                    } else {
+                                        pend16[q] = s16;
+                                    }
+                                } else {
+                                    pend8[q] = e8;
+                                }
+                            }
+                        }
+                    } else {
+                        prev[q] = x;
+                    }
+                }
+            }
+        }
+
+#pragma unroll
+        for (int q = 0; q < kSlQ; ++q) {
+            // candidates with distance < tau[q], bit-sliced compare against the warp-uniform threshold
+            uint32_t pass;
+            if (tau[q] > uint32_t(K)) {
+                pass = kFull;
+            } else {
+                const uint32_t plane[6] = {ones[q], twos[q], fours[q], eights[q], sixteens[q], thirtytwos[q]};
+                uint32_t lt = 0, eq = kFull;
+#pragma unroll
+                for (int b = 5; b >= 0; --b) {
+                    if ((tau[q] >> b) & 1u) {
+                        lt |= eq & ~plane[b];
+                        eq &= plane[b];
+                    } else {
+                        eq &= ~plane[b];
+                    }
+                }
+                pass = lt;
+            }
+            pass &= valid;
+            uint32_t lanes = __ballot_sync(kFull, pass != 0);
+            while (lanes) {
+                const int src = __ffs(lanes) - 1;
+                lanes &= lanes - 1;
+                uint32_t pm = __shfl_sync(kFull, pass, src);
+                const uint32_t p0 = __shfl_sync(kFull, ones[q], src), p1 = __shfl_sync(kFull, twos[q], src),
+                               p2 = __shfl_sync(kFull, fours[q], src), p3 = __shfl_sync(kFull, eights[q], src),
+                               p4 = __shfl_sync(kFull, sixteens[q], src), p5 = __shfl_sync(kFull, thirtytwos[q], src);
+                const uint64_t src_base = t * knn::kTile + uint64_t(src) * 32;
+                while (pm) {
+                    const int bit = __ffs(pm) - 1;
+                    pm &= pm - 1;
+                    const uint32_t dd = ((p0 >> bit) & 1u) | (((p1 >> bit) & 1u) << 1) | (((p2 >> bit) & 1u) << 2) |
+                                        (((p3 >> bit) & 1u) << 3) | (((p4 >> bit) & 1u) << 4) | (((p5 >> bit) & 1u) << 5);
+                    if (dd >= tau[q]) continue;  // tightened by an earlier candidate
+                    knn::list_insert<SLOTS>(ld[q], li[q], dd, uint32_t(src_base + bit), lane);
+                    tau[q] = knn::list_threshold<SLOTS>(ld[q], k);
+                }
+            }
+        }
+        __syncthreads();  // every warp is done with this stage
+        if (threadIdx.x == 0 && t + 2 < tiles) {
+            knn::mbar_expect_tx(&full_bar[st], TILE_BYTES);
+            knn::bulk_g2s(st == 0 ? stage0 : stage1, sliced + (t + 2) * (TILE_BYTES / 4), TILE_BYTES, &full_bar[st]);
+        }
+    }
+    if (lost) {
+        if (threadIdx.x == 0) {
+            atomicExch(status, kStatusWaitTimeout);
+            knn::mbar_wait_bounded(&full_bar[0], 0, knn::kWaitLimit);
+            knn::mbar_wait_bounded(&full_bar[1], 0, knn::kWaitLimit);
+        }
+        return;
+    }
+#pragma unroll
+    for (int q = 0; q < kSlQ; ++q) {
+        const uint64_t row = first_row + q;
+        if (row >= row_end) continue;
+        knn::list_write<SLOTS>(ld[q], li[q], row, k, nbrs + (row - row_begin) * uint64_t(k),
+                               dists ? dists + (row - row_begin) * uint64_t(k) : nullptr, lane);
+    }
+}
+
+template <int NBLK, int SLOTS>
+int launch_sliced_t(cphnsw_b200_index* h, const uint32_t* sliced, const uint8_t* codes, uint64_t n, uint32_t k,
+                    uint64_t rb, uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    constexpr int CHUNKS = NBLK * 16;
+    const size_t smem = size_t(2) * CHUNKS * 32 * 16 + size_t(kSlWarps) * kSlQ * CHUNKS * 16;
+    CPB_CUDA(cudaFuncSetAttribute(knn_sliced_kernel<NBLK, SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    const uint64_t rows = re - rb;
+    const uint64_t blocks = (rows + kSlWarps * kSlQ - 1) / (kSlWarps * kSlQ);
+    LaunchTimer timer(h, kKernelKnn, st);
+    knn_sliced_kernel<NBLK, SLOTS><<<unsigned(blocks), kSlThreads, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist,
+                                                                             h->d_status.as<uint32_t>());
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <int NBLK>
+int launch_sliced_slots(cphnsw_b200_index* h, const uint32_t* sliced, const uint8_t* codes, uint64_t n, uint32_t k,
+                        uint64_t rb, uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    const uint32_t need = k + 1;
+    if (need <= 64) return launch_sliced_t<NBLK, 2>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
+    if (need <= 96) return launch_sliced_t<NBLK, 3>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
+    return launch_sliced_t<NBLK, 4>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
+}
+
+}  // namespace
+
+bool knn_sliced_supported(const cphnsw_b200_index* h) {
+    return h->comp_bytes == 1 && (h->K == 16 || h->K == 32);
+}
+
+int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
+                            uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st) {
+    const int K = int(h->K);
+    const uint64_t tiles = (n + knn::kTile - 1) / knn::kTile;
+    const uint64_t n_groups = tiles * 32;
+    const size_t sliced_bytes = size_t(tiles) * K * 8 * 32 * 4;
+    CPB_TRY(h->s_sliced.reserve(sliced_bytes + 16));
+    {
+        const uint64_t threads = n_groups * 32;
+        slice_codes_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(d_codes), n, K,
+                                                                            h->s_sliced.as<uint32_t>(), n_groups);
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+    }
+    const uint32_t* sl = h->s_sliced.as<uint32_t>();
+    const uint8_t* codes = static_cast<const uint8_t*>(d_codes);
+    if (K == 16) return launch_sliced_slots<2>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    return launch_sliced_slots<4>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+}
+
+}  // namespace cpb

@@ -97,10 +97,17 @@ def clustered_codes(oracle, n, dim, K, cb, seed):
 @pytest.mark.parametrize("n,k,K,cb,dim", [(1, 4, 32, 1, 128), (2, 4, 32, 1, 128), (33, 40, 32, 1, 128),
                                           (1000, 32, 32, 1, 128), (2500, 64, 32, 1, 128), (3000, 10, 16, 1, 64),
                                           (1500, 32, 32, 2, 256), (1200, 100, 32, 1, 128), (900, 16, 12, 1, 32),
-                                          (5000, 32, 32, 1, 96)])
-def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim):
+                                          (5000, 32, 32, 1, 96), (2100, 20, 16, 1, 128), (1025, 64, 32, 1, 128)])
+@pytest.mark.parametrize("kernel", [1, 2])  # byte-wise and bit-sliced distance
+def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim, kernel):
     _, codes = clustered_codes(oracle, n, dim, K, cb, n + k)
     idx = make_index(cp, dim, K, cb)
+    if kernel == 2 and not (cb == 1 and K in (16, 32)):
+        idx.set_param("knn_kernel", 2)
+        with pytest.raises(cp.CPHNSWError):
+            idx.knn_graph(codes, k)
+        return
+    idx.set_param("knn_kernel", kernel)
     nbrs, dist = idx.knn_graph(codes, k)
     wn, wd = oracle.knn_graph(codes, k)
     assert np.array_equal(nbrs, wn)
@@ -111,10 +118,12 @@ def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim):
         assert np.array_equal(pn, wn[rb:re]) and np.array_equal(pd, wd[rb:re])
 
 
-def test_knn_graph_massive_ties_break_by_id(cp, oracle):
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_knn_graph_massive_ties_break_by_id(cp, oracle, kernel):
     codes = np.zeros((700, 32), np.uint8)
     codes[::7, 0] = 3  # two classes; within a class every distance is 0
     idx = make_index(cp, 128)
+    idx.set_param("knn_kernel", kernel)
     nbrs, dist = idx.knn_graph(codes, 20)
     wn, wd = oracle.knn_graph(codes, 20)
     assert np.array_equal(nbrs, wn) and np.array_equal(dist, wd)
