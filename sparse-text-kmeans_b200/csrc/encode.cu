@@ -41,12 +41,13 @@ __device__ __forceinline__ void butterfly_stage(float (&v)[kP128]) {
     }
 }
 
-// D then H on 128 registers.  `sg` points at 128 warp-uniform +-1 floats.
+// D then H on 128 registers.  `sg` points at 128 +-1 floats in shared memory, read by every
+// thread at the same address (broadcast).
 __device__ __forceinline__ void diag_fht128(float (&v)[kP128], const float* __restrict__ sg) {
     const float4* s4 = reinterpret_cast<const float4*>(sg);
 #pragma unroll
     for (int c = 0; c < kP128 / 4; ++c) {
-        float4 s = __ldg(s4 + c);
+        float4 s = s4[c];
         {
             float t = __fmul_rn(s.x, v[4 * c]);
             float y = v[4 * c + 1];
@@ -103,13 +104,14 @@ __device__ __forceinline__ uint32_t component_of(float win, int idx, int flip_ma
 
 // QUERY = true additionally writes the rotated vectors and winning magnitudes (CPQuery).
 template <typename CompT, bool QUERY>
-__global__ void __launch_bounds__(kTileVecs)
+__global__ void __launch_bounds__(kTileVecs, QUERY ? 2 : 3)
 encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
                    const float* __restrict__ signs /*[K][3][128]*/, int flip_mask,
                    CompT* __restrict__ codes, float* __restrict__ rotated, float* __restrict__ mags) {
     extern __shared__ float smem[];
     float* tile = smem;                                                 // [kTileVecs][kTileStride]
-    CompT* code_tile = reinterpret_cast<CompT*>(tile + kTileVecs * kTileStride);  // [kTileVecs][K]
+    float* sign_sm = tile + kTileVecs * kTileStride;                              // [2][3][128], double buffer
+    CompT* code_tile = reinterpret_cast<CompT*>(sign_sm + 2 * 3 * kP128);         // [kTileVecs][K]
 
     const uint64_t row0 = uint64_t(blockIdx.x) * kTileVecs;
     const int rows = int(min(uint64_t(kTileVecs), n - row0));
@@ -140,19 +142,24 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
             for (int c = 0; c < 4; ++c) dst[lane + 32 * c] = 0.0f;
         }
     }
+    // the three diagonals of one rotation are staged in shared memory one rotation ahead
+    const int t = threadIdx.x;
+    if (t < 3 * kP128 / 4)
+        reinterpret_cast<float4*>(sign_sm)[t] = __ldg(reinterpret_cast<const float4*>(signs) + t);
     __syncthreads();
 
-    const int t = threadIdx.x;
     const float* mine = tile + t * kTileStride;
     const uint64_t row = row0 + t;
     for (int r = 0; r < K; ++r) {
+        if (r + 1 < K && t < 3 * kP128 / 4)
+            reinterpret_cast<float4*>(sign_sm + ((r + 1) & 1) * 3 * kP128)[t] =
+                __ldg(reinterpret_cast<const float4*>(signs + size_t(r + 1) * 3 * kP128) + t);
         float v[kP128];
 #pragma unroll
         for (int i = 0; i < kP128; ++i) v[i] = mine[i];
-        const float* sg = signs + size_t(r) * 3 * kP128;
-        diag_fht128(v, sg);
-        diag_fht128(v, sg + kP128);
-        diag_fht128(v, sg + 2 * kP128);
+        const float* sg = sign_sm + (r & 1) * 3 * kP128;
+#pragma unroll 1
+        for (int layer = 0; layer < 3; ++layer) diag_fht128(v, sg + layer * kP128);
         float win;
         int idx;
         argmax128(v, win, idx);
@@ -172,8 +179,8 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
                 }
             }
         }
+        __syncthreads();  // the next rotation's diagonals are in place, this rotation's are free
     }
-    __syncthreads();
     // the tile's codes are contiguous in the output: write them back coalesced
     const int total = rows * K;
     CompT* dst = codes + row0 * uint64_t(K);
@@ -263,7 +270,8 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
     LaunchTimer timer(h, kKernelEncode, st);
 
     if (P == kP128) {
-        size_t smem = size_t(kTileVecs) * kTileStride * sizeof(float) + size_t(kTileVecs) * K * h->comp_bytes;
+        size_t smem = size_t(kTileVecs) * kTileStride * sizeof(float) + size_t(2) * 3 * kP128 * sizeof(float) +
+                      size_t(kTileVecs) * K * h->comp_bytes;
         unsigned grid = unsigned((n + kTileVecs - 1) / kTileVecs);
         const bool query = d_rot || d_mag;
 #define CPB_LAUNCH_P128(T, Q)                                                                              \
