@@ -148,6 +148,18 @@ public:
         return unpack(ids, d, nq, k);
     }
 
+    std::vector<SearchResult> search_multiprobe(const Float* q, size_t k, size_t ef, size_t num_probes) const {
+        return search_multiprobe_batch(q, 1, k, ef, num_probes)[0];
+    }
+    std::vector<std::vector<SearchResult>> search_multiprobe_batch(const Float* q, size_t nq, size_t k, size_t ef,
+                                                                   size_t num_probes) const {
+        std::vector<uint32_t> ids(nq * k);
+        std::vector<float> d(nq * k);
+        check(cphnsw_b200_search_multiprobe_batch(h_, q, nq, uint32_t(k), uint32_t(ef), uint32_t(num_probes), ids.data(),
+                                                  d.data()));
+        return unpack(ids, d, nq, k);
+    }
+
     // ---- stages ---------------------------------------------------------------------------------
     std::vector<Code> encode(const Float* vecs, size_t n) const {
         std::vector<Code> out(n);

@@ -64,9 +64,11 @@ int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
 int cphnsw_b200_destroy(cphnsw_b200_index* h);
 
 /* Named tunables (CPHNSWParams fields, types.hpp:374-400, plus build/search knobs):
- *   "keep_pruned" (0/1, default 1), "k_entry" (1..100, default 4), "profile" (0/1, see kernel_time),
+ *   "keep_pruned" (0/1, default 1), "profile" (0/1, see kernel_time),
  *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
- *   "entry_scan" (nodes scored per query to seed the beam; default = k_entry). */
+ *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; uint8 codes with K = 16/32 only),
+ *   "entry_scan" (evenly spaced nodes scored for every query before the walk; default = k_entry),
+ *   "k_entry" (1..100, default 4: how many of the scored nodes, the best, seed the walk). */
 int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double value);
 int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* value);
 
@@ -122,7 +124,8 @@ int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_
  * uint32[size][M] (FlatGraph neighbour ids, include/cphnsw/graph/flat_graph.hpp:179-181). */
 int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out);
 int cphnsw_b200_get_adjacency(const cphnsw_b200_index* h, uint32_t* adj_out);
-/* ids scored for every query before the graph walk (entry_scan evenly spaced node ids). */
+/* ids scored for every query before the graph walk (entry_scan evenly spaced node ids); the k_entry best of
+ * them seed the walk. */
 int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uint64_t* count);
 
 /* Batched CPHNSWIndex::search(q,k,ef) (evaluation/eval_sift.cpp:387; engine
@@ -139,6 +142,19 @@ int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, 
 int cphnsw_b200_search_and_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                                         uint32_t ef, uint32_t rerank_k, uint32_t* ids_out,
                                         float* dists_out, uint32_t* stats_out);
+
+/* Batched CPHNSWIndex::search_multiprobe(q,k,ef,num_probes) (evaluation/eval_sift.cpp:430,469).  The legacy
+ * source is absent; this follows the multiprobe scheme of the cross-polytope LSH paper
+ * (resources/cross-polytope-lsh/consolidated.tex:391-425) on the data CPQuery keeps for it
+ * (types.hpp:332-336): the num_probes (1..64) cheapest probe codes of the query are generated, the graph is
+ * walked once per probe code under the symmetric code distance (beam max(ef,k), seeds as for search), and
+ * the per-probe lists are merged: every node once with its smallest distance, ascending by (distance, id),
+ * best k.  dists are code distances as floats.  num_probes * k <= 2048. */
+int cphnsw_b200_search_multiprobe_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
+                                        uint32_t ef, uint32_t num_probes, uint32_t* ids_out, float* dists_out);
+/* The probe codes themselves, ComponentT[nq][num_probes][K], primary code first (legacy multiprobe.hpp). */
+int cphnsw_b200_probe_codes(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t num_probes,
+                            void* codes_out);
 
 /* ---- device-pointer variants (inputs already resident in HBM; used for sharded builds) ------- */
 

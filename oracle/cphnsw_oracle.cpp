@@ -289,17 +289,21 @@ int orc_select_neighbors(const void* codes, uint64_t n, uint64_t K, uint64_t com
 // instead of at random so that a query lands in its own cluster.  n_seed >= n_entry offers them all.
 // W capacity is ef.  out_ids/out_dist are [nq][k] padded with 0xFFFFFFFF / +inf; stats[nq][2] =
 // expansions, distance evaluations (scan + walk; optional).
-int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint64_t P,
-               const void* codes, uint64_t comp_bytes, uint64_t n, const uint32_t* adj, uint64_t M,
-               const uint32_t* entry_ids, uint64_t n_entry, uint64_t n_seed, uint64_t ef, uint64_t k,
-               uint32_t* out_ids, float* out_dist, uint32_t* stats) {
+}  // extern "C"
+
+namespace {
+// dist_of(q, id) is the metric: the asymmetric CP score for search / search_and_rerank, the
+// symmetric code distance to a probe code for search_multiprobe.
+template <class DistFn>
+int walk_all(uint64_t nq, uint64_t n, const uint32_t* adj, uint64_t M, const uint32_t* entry_ids, uint64_t n_entry,
+             uint64_t n_seed, uint64_t ef, uint64_t k, uint32_t* out_ids, float* out_dist, uint32_t* stats,
+             DistFn dist_of) {
 #pragma omp parallel
     {
         std::vector<uint8_t> visited(n);
         std::vector<uint32_t> touched;
 #pragma omp for schedule(dynamic, 4)
         for (int64_t q = 0; q < (int64_t)nq; ++q) {
-            const float* table = tables + (size_t)q * K * P;
             std::set<Cand> W;  // at most ef best seen so far
             std::set<Cand> C;  // members of W not yet expanded
             uint32_t expansions = 0, evals = 0;
@@ -307,7 +311,7 @@ int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint
                 if (id == kInvalid || id >= n || visited[id]) return;  // search_engine.hpp:154-160
                 visited[id] = 1;
                 touched.push_back(id);
-                Cand c{asym_dist(table, K, P, codes, comp_bytes, id), id};
+                Cand c{dist_of((size_t)q, id), id};
                 ++evals;
                 if (W.size() < ef) {  // search_engine.hpp:166-176
                     W.insert(c);
@@ -327,7 +331,7 @@ int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint
                 for (size_t e = 0; e < n_entry; ++e) {
                     uint32_t id = entry_ids[e];
                     if (id == kInvalid || id >= n) continue;
-                    scan.push_back({asym_dist(table, K, P, codes, comp_bytes, id), id});
+                    scan.push_back({dist_of((size_t)q, id), id});
                     ++evals;
                 }
                 std::sort(scan.begin(), scan.end());
@@ -356,6 +360,129 @@ int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint
             }
             for (uint32_t id : touched) visited[id] = 0;
             touched.clear();
+        }
+    }
+    return 0;
+}
+}  // namespace
+
+extern "C" {
+
+int orc_search(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint64_t P,
+               const void* codes, uint64_t comp_bytes, uint64_t n, const uint32_t* adj, uint64_t M,
+               const uint32_t* entry_ids, uint64_t n_entry, uint64_t n_seed, uint64_t ef, uint64_t k,
+               uint32_t* out_ids, float* out_dist, uint32_t* stats) {
+    return walk_all(nq, n, adj, M, entry_ids, n_entry, n_seed, ef, k, out_ids, out_dist, stats,
+                    [&](size_t q, uint32_t id) { return asym_dist(tables + q * K * P, K, P, codes, comp_bytes, id); });
+}
+
+// The same walk under the symmetric metric: distance = number of components in which the node's
+// code differs from the query's code qcodes[q] (legacy hamming_distance), as a float.
+int orc_search_codes(const void* qcodes /*[nq][K]*/, uint64_t nq, uint64_t K, const void* codes,
+                     uint64_t comp_bytes, uint64_t n, const uint32_t* adj, uint64_t M, const uint32_t* entry_ids,
+                     uint64_t n_entry, uint64_t n_seed, uint64_t ef, uint64_t k, uint32_t* out_ids, float* out_dist,
+                     uint32_t* stats) {
+    return walk_all(nq, n, adj, M, entry_ids, n_entry, n_seed, ef, k, out_ids, out_dist, stats,
+                    [&](size_t q, uint32_t id) { return (float)code_dist(qcodes, q, codes, id, K, comp_bytes); });
+}
+
+// Multiprobe sequence for the cross-polytope hash (resources/cross-polytope-lsh/consolidated.tex:391-425;
+// data kept for it in CPQuery, types.hpp:332-336).  Per rotation the coordinates are ranked by
+// (|x| descending, index ascending); replacing the winner by the coordinate of rank v costs
+// (|x|_(0) - |x|_(v))^2 (the paper's single-coordinate approximation); a probe is a choice of one
+// rank per rotation, scored by the sum of its costs over rotations in ascending rotation order
+// (fp32).  Probes are emitted in ascending (score, creation number) order, the primary code first:
+// after emitting a probe whose last modified rotation is j, its successors are "raise the rank of
+// rotation j by one" and "set rotation j' to rank 1" for every j' > j (each probe has exactly one
+// such derivation).  rotated is [nq][K][P]; probe codes out [nq][T][K].
+int orc_probe_codes(const float* rotated, uint64_t nq, uint64_t K, uint64_t P, uint64_t comp_bytes, uint64_t T,
+                    void* out) {
+    const size_t V = std::min<size_t>(P, T + 1);  // ranks that T probes can reach
+#pragma omp parallel for schedule(static)
+    for (int64_t q = 0; q < (int64_t)nq; ++q) {
+        std::vector<uint32_t> idx(K * V);
+        std::vector<float> cost(K * V);
+        for (size_t r = 0; r < K; ++r) {
+            const float* x = rotated + ((size_t)q * K + r) * P;
+            std::vector<std::pair<float, uint32_t>> key(P);
+            for (size_t i = 0; i < P; ++i) key[i] = {-std::fabs(x[i]), (uint32_t)i};
+            std::partial_sort(key.begin(), key.begin() + V, key.end());
+            const float top = -key[0].first;
+            for (size_t v = 0; v < V; ++v) {
+                idx[r * V + v] = key[v].second;
+                float d = top - (-key[v].first);
+                cost[r * V + v] = d * d;
+            }
+        }
+        struct Item { float score; uint32_t seq, parent, rot, rank; bool used; };
+        std::vector<Item> pool;
+        std::vector<std::vector<uint8_t>> ranks;  // emitted probes
+        std::vector<uint32_t> last;                // last modified rotation of each emitted probe
+        auto score_of = [&](const std::vector<uint8_t>& rk) {
+            float s = 0.0f;
+            for (size_t r = 0; r < K; ++r)
+                if (rk[r]) s = s + cost[r * V + rk[r]];
+            return s;
+        };
+        auto push_children = [&](uint32_t parent) {
+            const std::vector<uint8_t>& rk = ranks[parent];
+            const bool primary = parent == 0;
+            uint32_t j = primary ? 0 : last[parent];
+            if (!primary && (size_t)rk[j] + 1 < V) {
+                std::vector<uint8_t> c = rk;
+                c[j] = rk[j] + 1;
+                pool.push_back({score_of(c), (uint32_t)pool.size(), parent, j, (uint32_t)c[j], false});
+            }
+            for (uint32_t j2 = primary ? 0 : j + 1; j2 < K; ++j2) {
+                if (V < 2) break;
+                std::vector<uint8_t> c = rk;
+                c[j2] = 1;
+                pool.push_back({score_of(c), (uint32_t)pool.size(), parent, j2, 1u, false});
+            }
+        };
+        ranks.push_back(std::vector<uint8_t>(K, 0));
+        last.push_back(0);
+        push_children(0);
+        while (ranks.size() < T) {
+            int best = -1;
+            for (size_t i = 0; i < pool.size(); ++i)
+                if (!pool[i].used && (best < 0 || pool[i].score < pool[best].score)) best = (int)i;  // lowest seq wins ties
+            if (best < 0) break;  // fewer than T distinct probes exist
+            pool[best].used = true;
+            std::vector<uint8_t> rk = ranks[pool[best].parent];
+            rk[pool[best].rot] = (uint8_t)pool[best].rank;
+            ranks.push_back(rk);
+            last.push_back(pool[best].rot);
+            push_children((uint32_t)ranks.size() - 1);
+        }
+        for (size_t t = 0; t < T; ++t) {
+            const std::vector<uint8_t>& rk = ranks[std::min(t, ranks.size() - 1)];  // repeat the last probe if short
+            for (size_t r = 0; r < K; ++r) {
+                uint32_t i = idx[r * V + rk[r]];
+                float val = rotated[((size_t)q * K + r) * P + i];
+                store_comp(out, comp_bytes, ((size_t)q * T + t) * K + r, component(i, val < 0));
+            }
+        }
+    }
+    return 0;
+}
+
+// Merge of the per-probe result lists of search_multiprobe: per query, the union of T lists of k
+// (id, distance), each id kept once with its smallest distance, ascending by (distance, id), best k.
+int orc_merge_probes(const uint32_t* ids /*[nq][T][k]*/, const float* dist, uint64_t nq, uint64_t T, uint64_t k,
+                     uint32_t* out_ids, float* out_dist) {
+    for (size_t q = 0; q < nq; ++q) {
+        std::vector<std::pair<uint32_t, float>> all;
+        for (size_t i = 0; i < T * k; ++i)
+            if (ids[q * T * k + i] != kInvalid) all.push_back({ids[q * T * k + i], dist[q * T * k + i]});
+        std::sort(all.begin(), all.end());
+        std::vector<Cand> best;
+        for (size_t i = 0; i < all.size(); ++i)
+            if (i == 0 || all[i].first != all[i - 1].first) best.push_back({all[i].second, all[i].first});
+        std::sort(best.begin(), best.end());
+        for (size_t t = 0; t < k; ++t) {
+            out_ids[q * k + t] = t < best.size() ? best[t].second : kInvalid;
+            out_dist[q * k + t] = t < best.size() ? best[t].first : INFINITY;
         }
     }
     return 0;

@@ -126,6 +126,44 @@ def search(tables, codes, adj, entry_ids, ef, k, want_stats=False, n_seed=None):
     return (ids, dist, stats) if want_stats else (ids, dist)
 
 
+def search_codes(qcodes, codes, adj, entry_ids, ef, k, n_seed=None):
+    """The walk under the symmetric code distance to qcodes[q] (distances returned as floats)."""
+    qcodes = np.ascontiguousarray(qcodes)
+    codes = np.ascontiguousarray(codes)
+    adj = np.ascontiguousarray(adj, np.uint32)
+    entry_ids = np.ascontiguousarray(entry_ids, np.uint32)
+    nq, K = qcodes.shape
+    n, M = adj.shape
+    ids = np.empty((nq, k), np.uint32)
+    dist = np.empty((nq, k), np.float32)
+    lib().orc_search_codes(_ptr(qcodes), C.c_uint64(nq), C.c_uint64(K), _ptr(codes), C.c_uint64(codes.dtype.itemsize),
+                           C.c_uint64(n), _ptr(adj), C.c_uint64(M), _ptr(entry_ids), C.c_uint64(entry_ids.size),
+                           C.c_uint64(entry_ids.size if n_seed is None else n_seed), C.c_uint64(ef), C.c_uint64(k),
+                           _ptr(ids), _ptr(dist), None)
+    return ids, dist
+
+
+def probe_codes(rotated, comp_bytes, T):
+    """Multiprobe sequence: [nq][T][K] probe codes, the primary code first."""
+    rotated = np.ascontiguousarray(rotated, np.float32)
+    nq, K, P = rotated.shape
+    out = np.empty((nq, T, K), _comp_dtype(comp_bytes))
+    lib().orc_probe_codes(_ptr(rotated), C.c_uint64(nq), C.c_uint64(K), C.c_uint64(P), C.c_uint64(comp_bytes),
+                          C.c_uint64(T), _ptr(out))
+    return out
+
+
+def search_multiprobe(rotated, comp_bytes, codes, adj, entry_ids, ef, k, T, n_seed=None):
+    """search_multiprobe(q, k, ef, num_probes): one symmetric-distance walk per probe code, merged."""
+    pc = probe_codes(rotated, comp_bytes, T)
+    nq, _, K = pc.shape
+    ids, dist = search_codes(pc.reshape(nq * T, K), codes, adj, entry_ids, ef, k, n_seed)
+    oi = np.empty((nq, k), np.uint32)
+    od = np.empty((nq, k), np.float32)
+    lib().orc_merge_probes(_ptr(ids), _ptr(dist), C.c_uint64(nq), C.c_uint64(T), C.c_uint64(k), _ptr(oi), _ptr(od))
+    return oi, od
+
+
 def rerank(queries, base, cand, k):
     queries = np.ascontiguousarray(queries, np.float32)
     base = np.ascontiguousarray(base, np.float32)

@@ -33,7 +33,8 @@ EXPORTS = [
     "cphnsw_b200_search_and_rerank_batch", "cphnsw_b200_encode_dev", "cphnsw_b200_code_distance_dev",
     "cphnsw_b200_knn_graph_dev", "cphnsw_b200_select_neighbors_dev", "cphnsw_b200_install_dev",
     "cphnsw_b200_search_dev", "cphnsw_b200_check_device_status", "cphnsw_b200_launch_count",
-    "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc",
+    "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc", "cphnsw_b200_search_multiprobe_batch",
+    "cphnsw_b200_probe_codes",
 ]
 
 
@@ -260,6 +261,25 @@ class CPHNSWIndex:
         _check(self._lib.cphnsw_b200_search_and_rerank_batch(self._h, _p(q), _u64(nq), _u32(k), _u32(ef), _u32(rerank_k),
                                                              _p(ids), _p(dist), _p(stats)))
         return (ids, dist, stats) if want_stats else (ids, dist)
+
+    def search_multiprobe_batch(self, q, k, ef, num_probes):
+        q = self._vecs(q)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        _check(self._lib.cphnsw_b200_search_multiprobe_batch(self._h, _p(q), _u64(nq), _u32(k), _u32(ef),
+                                                             _u32(num_probes), _p(ids), _p(dist)))
+        return ids, dist
+
+    def search_multiprobe(self, q, k, ef, num_probes):
+        ids, dist = self.search_multiprobe_batch(q, k, ef, num_probes)
+        return self._results(ids[0], dist[0])
+
+    def probe_codes(self, q, num_probes):
+        q = self._vecs(q)
+        out = np.empty((q.shape[0], num_probes, self.K), self.code_dtype)
+        _check(self._lib.cphnsw_b200_probe_codes(self._h, _p(q), _u64(q.shape[0]), _u32(num_probes), _p(out)))
+        return out
 
     @staticmethod
     def _results(ids, dist):

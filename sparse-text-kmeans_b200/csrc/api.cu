@@ -186,6 +186,66 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
     return 0;
 }
 
+// search_multiprobe: probe codes from the rotated queries, one symmetric-distance walk per probe,
+// merge.  probe_codes_out (host, optional) receives the [nq][T][K] probe codes.
+int do_multiprobe(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef, uint32_t T,
+                  uint32_t* ids, float* dists, void* probe_codes_out, bool search) {
+    if (T == 0 || T > 64) {
+        set_error("search_multiprobe: num_probes must be in 1..64 (got %u)", T);
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (!q && nq) {
+        set_error("search_multiprobe: null query pointer");
+        return CPHNSW_B200_E_INVALID;
+    }
+    uint32_t beam = ef > k ? ef : k;
+    if (search) {
+        if (h->n == 0) {
+            set_error("search on an empty index");
+            return CPHNSW_B200_E_STATE;
+        }
+        if (k == 0 || !ids || !dists) {
+            set_error("search_multiprobe: k must be > 0 and output pointers non-null");
+            return CPHNSW_B200_E_INVALID;
+        }
+        if (beam > 1024 || uint64_t(T) * k > 2048) {
+            set_error("search_multiprobe: need max(ef,k) <= 1024 and num_probes*k <= 2048");
+            return CPHNSW_B200_E_INVALID;
+        }
+    }
+    const uint64_t chunk = 4096;
+    const size_t table_floats = size_t(h->K) * h->P;
+    const size_t rb = code_row_bytes(h);
+    cudaStream_t st = 0;
+    for (uint64_t q0 = 0; q0 < nq; q0 += chunk) {
+        const uint64_t m = nq - q0 < chunk ? nq - q0 : chunk;
+        CPB_TRY(h->d_q.reserve(m * h->dim * 4));
+        CPB_CUDA(cudaMemcpyAsync(h->d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
+        CPB_TRY(h->d_qtables.reserve(m * table_floats * 4));
+        CPB_TRY(h->d_qcodes.reserve(m * rb + 16));
+        CPB_TRY(launch_encode(h, h->d_q.as<float>(), m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
+        CPB_TRY(h->d_probe_codes.reserve(m * T * rb + 16));
+        CPB_TRY(launch_probe_codes(h, h->d_qtables.as<float>(), m, T, h->d_probe_codes.p, st));
+        if (probe_codes_out)
+            CPB_CUDA(cudaMemcpyAsync((char*)probe_codes_out + q0 * T * rb, h->d_probe_codes.p, m * T * rb,
+                                     cudaMemcpyDeviceToHost, st));
+        if (search) {
+            CPB_TRY(h->d_probe_ids.reserve(m * T * k * 4));
+            CPB_TRY(h->d_probe_dist.reserve(m * T * k * 4));
+            CPB_TRY(h->d_out_ids.reserve(m * k * 4));
+            CPB_TRY(h->d_out_dist.reserve(m * k * 4));
+            CPB_TRY(launch_search(h, nullptr, nullptr, m * T, k, beam, 0, h->d_probe_ids.as<uint32_t>(),
+                                  h->d_probe_dist.as<float>(), nullptr, st, h->d_probe_codes.p));
+            CPB_TRY(launch_merge_probes(h, h->d_probe_ids.as<uint32_t>(), h->d_probe_dist.as<float>(), m, T, k,
+                                        h->d_out_ids.as<uint32_t>(), h->d_out_dist.as<float>(), st));
+            CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, h->d_out_ids.p, m * k * 4, cudaMemcpyDeviceToHost, st));
+            CPB_CUDA(cudaMemcpyAsync(dists + q0 * k, h->d_out_dist.p, m * k * 4, cudaMemcpyDeviceToHost, st));
+        }
+        CPB_CUDA(cudaStreamSynchronize(st));
+    }
+    return 0;
+}
+
 }  // namespace
 }  // namespace cpb
 
@@ -578,6 +638,18 @@ int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, 
                              uint32_t* ids_out, float* dists_out, uint32_t* stats_out) {
     CPB_TRY(bind(h));
     return do_search(h, q, false, nq, k, ef, 0, ids_out, dists_out, stats_out, false, 0);
+}
+
+int cphnsw_b200_search_multiprobe_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
+                                        uint32_t num_probes, uint32_t* ids_out, float* dists_out) {
+    CPB_TRY(bind(h));
+    return do_multiprobe(h, q, nq, k, ef, num_probes, ids_out, dists_out, nullptr, true);
+}
+
+int cphnsw_b200_probe_codes(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t num_probes, void* codes_out) {
+    CPB_TRY(bind(h));
+    if (nq && !codes_out) { set_error("probe_codes: null output pointer"); return CPHNSW_B200_E_INVALID; }
+    return do_multiprobe(h, q, nq, 1, 1, num_probes, nullptr, nullptr, codes_out, false);
 }
 
 int cphnsw_b200_search_and_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,

@@ -93,6 +93,7 @@ struct cphnsw_b200_index {
 
     // search scratch
     cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
+    cpb::DevBuf d_probe_codes, d_probe_ids, d_probe_dist;  // search_multiprobe scratch
     // stage scratch for the host-pointer entry points
     cpb::DevBuf s_in, s_in2, s_out, s_out2, s_pad, s_pad2, s_sliced;
 
@@ -126,7 +127,12 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
                             uint32_t* d_adj, cudaStream_t st);
 int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
-                  cudaStream_t st);
+                  cudaStream_t st, const void* d_qcodes = nullptr);
+// multiprobe sequence of rotated queries [nq][K][P] -> probe codes [nq][T][K]; merge of per-probe results
+int launch_probe_codes(cphnsw_b200_index* h, const float* d_rotated, uint64_t nq, uint32_t T, void* d_out,
+                       cudaStream_t st);
+int launch_merge_probes(cphnsw_b200_index* h, const uint32_t* d_ids, const float* d_dist, uint64_t nq, uint32_t T,
+                        uint32_t k, uint32_t* d_out_ids, float* d_out_dist, cudaStream_t st);
 // scratch the search kernel needs for an index of n nodes (visited bitsets, expansion lists)
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam);
 // copies the codes of the entry ids into one contiguous buffer (after d_entry / d_codes change)

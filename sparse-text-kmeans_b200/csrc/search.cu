@@ -40,7 +40,8 @@ constexpr uint32_t kIdMask = 0x7fffffffu;
 constexpr int kCoopMax = 8;                 // up to this many fresh nodes are scored by the whole warp
 
 struct SearchArgs {
-    const float* tables;   // [nq][K][P]
+    const float* tables;   // [nq][K][P] (asymmetric metric)
+    const void* qcodes;    // [nq][K] query codes (symmetric metric)
     const float* queries;  // [nq][dim] (rerank only)
     const void* codes;     // [n][K] components
     const uint32_t* adj;   // [n][M]
@@ -51,6 +52,7 @@ struct SearchArgs {
     uint64_t n;
     uint32_t nq;
     int K, P, dim, M, comp_bytes;
+    uint32_t qsm_floats;              // size of the per-warp query area
     uint32_t per_warp_smem;           // bytes of shared memory per warp (multiple of 16)
     uint32_t beam, cap, k, rerank_k;  // cap: power of two >= max(32, beam, n_seed), the size of W's arrays
     uint8_t* visited;    // [warp slots][vis_stride]: epoch of the last query that visited the node
@@ -127,6 +129,28 @@ __device__ __forceinline__ float asym_distance_lane(const float* table, const vo
     return -acc;
 }
 
+// Symmetric metric (search_multiprobe): number of components in which the node's code differs
+// from the query code staged in shared memory, as a float.
+template <bool U16>
+__device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, const void* codes, uint32_t row_index,
+                                                   int K) {
+    const int row_bytes = K * (U16 ? 2 : 1);
+    const unsigned char* row = static_cast<const unsigned char*>(codes) + size_t(row_index) * row_bytes;
+    uint32_t d = 0;
+    if ((row_bytes & 3) == 0) {
+        constexpr uint32_t LO = U16 ? 0x7fff7fffu : 0x7f7f7f7fu;
+        const uint32_t* r32 = reinterpret_cast<const uint32_t*>(row);
+        const uint32_t* q32 = reinterpret_cast<const uint32_t*>(qcode);
+        for (int w = 0; w < row_bytes / 4; ++w) {
+            const uint32_t x = q32[w] ^ __ldg(r32 + w);
+            d += __popc((((x & LO) + LO) | x) & ~LO);  // one flag per differing byte / halfword
+        }
+    } else {
+        for (int r = 0; r < K; ++r) d += load_component<U16>(row, r) != load_component<U16>(qcode, r);
+    }
+    return float(d);
+}
+
 // The whole warp scores one node: lane j owns rotation c0 + j of each block; the butterfly
 // reduction adds exactly the pairs the one-lane form adds.  `comp` is this lane's component of
 // block 0 (K <= 32 on this path).
@@ -162,12 +186,12 @@ __device__ __forceinline__ void warp_sort_smem(float* d, uint32_t* id, int n, in
     }
 }
 
-template <bool U16, bool TABLE_SMEM>
+template <bool U16, bool TABLE_SMEM, bool SYM>
 __global__ void search_kernel(SearchArgs a) {
     extern __shared__ __align__(16) unsigned char search_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const size_t table_floats = TABLE_SMEM ? size_t(a.K) * a.P : 0;  // a multiple of 4 when staged
-    const size_t dim_pad = (size_t(a.dim) + 3) & ~size_t(3);
+    const size_t dim_pad = a.qsm_floats;  // floats of the query-vector / query-code area (multiple of 4)
     const int cap = int(a.cap);
     unsigned char* mine = search_smem + size_t(a.per_warp_smem) * warp;
     float* table_sm = reinterpret_cast<float*>(mine);
@@ -181,7 +205,8 @@ __global__ void search_kernel(SearchArgs a) {
     const uint32_t beam = a.beam;
     const bool scan_mode = a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
-    const bool coop_ok = a.K <= 32;
+    const bool coop_ok = !SYM && a.K <= 32;
+    const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm);  // symmetric metric only
 
     // queries are handed out one at a time from a global counter, so that warps that draw short
     // walks take more of them
@@ -190,14 +215,18 @@ __global__ void search_kernel(SearchArgs a) {
         if (lane == 0) q = atomicAdd(a.next_query, 1u);
         q = __shfl_sync(kFull, q, 0);
         if (q >= a.nq) break;
-        const float* table = a.tables + size_t(q) * a.K * a.P;
-        if (TABLE_SMEM) {
+        const float* table = SYM ? nullptr : a.tables + size_t(q) * a.K * a.P;
+        if (SYM) {
+            const unsigned char* src = static_cast<const unsigned char*>(a.qcodes) + size_t(q) * row_bytes;
+            for (int i = lane; i < row_bytes; i += 32) reinterpret_cast<unsigned char*>(qsm)[i] = src[i];
+        }
+        if (TABLE_SMEM && !SYM) {
             const float4* src = reinterpret_cast<const float4*>(table);
             float4* dst = reinterpret_cast<float4*>(table_sm);
             for (int i = lane; i < int(table_floats / 4); i += 32) dst[i] = __ldg(src + i);
             table = table_sm;
         }
-        if (a.rerank_k) {
+        if (a.rerank_k && !SYM) {
             const float* qv = a.queries + size_t(q) * a.dim;
             for (int i = lane; i < int(dim_pad); i += 32) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
         }
@@ -218,6 +247,11 @@ __global__ void search_kernel(SearchArgs a) {
         float wd = INFINITY;  // worst member of W once it is full
         uint32_t wi = kInvalidNode;
 
+        // one lane scores one node (row `row` of `code_base`) under the kernel's metric
+        auto score_lane = [&](const void* code_base, uint32_t row) -> float {
+            if (SYM) return sym_distance_lane<U16>(qcode_sm, code_base, row, a.K);
+            return asym_distance_lane<U16>(table, code_base, row, a.K, a.P);
+        };
         // Admission of (d, id), known to every lane: W stays the wcap best seen so far, sorted
         // (search_engine.hpp:166-176).
         auto try_admit = [&](float d, uint32_t id) {
@@ -310,7 +344,7 @@ __global__ void search_kernel(SearchArgs a) {
             } else {
                 ahead();
                 float dist = 0.0f;
-                if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
+                if (fresh) dist = score_lane(a.codes, id);
                 if (count == wcap) m &= __ballot_sync(kFull, fresh && key_less(dist, id, wd, wi));
                 while (m) {
                     const int src = __ffs(m) - 1;
@@ -333,7 +367,7 @@ __global__ void search_kernel(SearchArgs a) {
                 const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
                 const bool ok = id < a.n;
                 float dist = 0.0f;
-                if (ok) dist = asym_distance_lane<U16>(table, a.entry_codes, e, a.K, a.P);
+                if (ok) dist = score_lane(a.entry_codes, e);
                 uint32_t m = __ballot_sync(kFull, ok);
                 nevals += __popc(m);
                 if (count == wcap) m &= __ballot_sync(kFull, ok && key_less(dist, id, wd, wi));
@@ -423,7 +457,7 @@ __global__ void search_kernel(SearchArgs a) {
         int nsort = 32;
         while (nsort < int(count)) nsort <<= 1;
 
-        if (a.rerank_k) {
+        if (a.rerank_k && !SYM) {
             const uint32_t ncand = min(a.rerank_k, count);
             const int g = lane >> 3, j = lane & 7;
             const bool vec4 = (a.dim & 3) == 0;
@@ -490,16 +524,19 @@ struct LaunchCfg {
     uint32_t cap;
     int warps;
     size_t per_warp;
+    size_t qsm_floats;
     bool table_smem;
 };
 
-LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam) {
+LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
     LaunchCfg c;
     c.cap = 32;
     while (c.cap < beam || c.cap < h->k_entry) c.cap <<= 1;
     const size_t table_bytes = size_t(h->K) * h->P * 4;
-    c.table_smem = table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
-    const size_t dim_pad = (size_t(h->dim) + 3) & ~size_t(3);
+    c.table_smem = !sym && table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
+    size_t dim_pad = (size_t(h->dim) + 3) & ~size_t(3);
+    // the query-vector area doubles as the home of the query code under the symmetric metric
+    while (dim_pad * 4 < size_t(h->K) * h->comp_bytes) dim_pad += 4;
     size_t per_warp = (c.table_smem ? table_bytes : 0) + size_t(c.cap) * 8 + dim_pad * 4;
     per_warp = (per_warp + 15) & ~size_t(15);
     const size_t budget = 226 * 1024;  // of the 227 KB a block may use
@@ -508,6 +545,7 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam) {
     if (w < 1) w = 1;
     c.warps = w;
     c.per_warp = per_warp;
+    c.qsm_floats = dim_pad;
     return c;
 }
 
@@ -544,7 +582,8 @@ int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
 
 int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
-                  cudaStream_t st) {
+                  cudaStream_t st, const void* d_qcodes) {
+    const bool sym = d_qcodes != nullptr;  // symmetric code-distance walk (search_multiprobe)
     if (nq == 0) return 0;
     if (beam > 1024) {
         set_error("search: beam width max(ef, k, rerank_k) must be <= 1024 (got %u)", beam);
@@ -555,8 +594,10 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
         return CPHNSW_B200_E_INVALID;
     }
     CPB_TRY(prepare_search_scratch(h, beam));
-    LaunchCfg c = pick_cfg(h, beam);
+    LaunchCfg c = pick_cfg(h, beam, sym);
     SearchArgs a;
+    a.qcodes = d_qcodes;
+    a.qsm_floats = uint32_t(c.qsm_floats);
     a.tables = d_tables;
     a.queries = d_q;
     a.codes = h->d_codes.p;
@@ -590,21 +631,23 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     const bool u16 = h->comp_bytes == 2;
     LaunchTimer timer(h, kKernelSearch, st);
 
-#define CPB_SEARCH(U, T)                                                                                   \
+#define CPB_SEARCH(U, T, S)                                                                                \
     do {                                                                                                   \
         cudaFuncAttributes fa;                                                                             \
-        CPB_CUDA(cudaFuncGetAttributes(&fa, search_kernel<U, T>));                                         \
+        CPB_CUDA(cudaFuncGetAttributes(&fa, search_kernel<U, T, S>));                                      \
         int maxw = 65536 / (((fa.numRegs + 7) & ~7) * 32);                                                 \
         int w = c.warps < maxw ? c.warps : maxw;                                                           \
         size_t smem = c.per_warp * w;                                                                      \
-        CPB_CUDA(cudaFuncSetAttribute(search_kernel<U, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+        CPB_CUDA(cudaFuncSetAttribute(search_kernel<U, T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                       int(smem)));                                                         \
-        search_kernel<U, T><<<grid, w * 32, smem, st>>>(a);                                                \
+        search_kernel<U, T, S><<<grid, w * 32, smem, st>>>(a);                                             \
     } while (0)
-    if (u16 && c.table_smem) CPB_SEARCH(true, true);
-    else if (u16) CPB_SEARCH(true, false);
-    else if (c.table_smem) CPB_SEARCH(false, true);
-    else CPB_SEARCH(false, false);
+    if (sym && u16) CPB_SEARCH(true, false, true);
+    else if (sym) CPB_SEARCH(false, false, true);
+    else if (u16 && c.table_smem) CPB_SEARCH(true, true, false);
+    else if (u16) CPB_SEARCH(true, false, false);
+    else if (c.table_smem) CPB_SEARCH(false, true, false);
+    else CPB_SEARCH(false, false, false);
 #undef CPB_SEARCH
     h->launches++;
     CPB_CUDA(cudaGetLastError());

@@ -257,3 +257,40 @@ def test_visited_epoch_wraps_without_losing_exactness(cp, oracle):
     ids, dist = idx.search_batch(np.tile(q, (reps, 1)), 8, 24)
     assert np.array_equal(ids.reshape(reps, 40, 8), np.broadcast_to(wi, (reps, 40, 8)))
     assert np.array_equal(dist.reshape(reps, 40, 8), np.broadcast_to(wd, (reps, 40, 8)))
+
+
+# ---- multiprobe ----------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dim,K,cb,T", [(128, 32, 1, 1), (128, 32, 1, 4), (128, 32, 1, 16), (96, 16, 1, 16), (16, 8, 1, 40),
+                                        (200, 16, 2, 16), (128, 3, 1, 64)])
+def test_probe_codes_match_oracle(cp, oracle, dim, K, cb, T):
+    rng = np.random.default_rng(dim + T)
+    q = rng.standard_normal((50, dim)).astype(np.float32)
+    q[3] = 0
+    q[4, :] = 1.0  # ties everywhere
+    idx = make_index(cp, dim, K, cb)
+    signs = oracle.sign_tables(dim, K, 42)
+    _, rot, _ = oracle.encode(q, K, cb, signs, 2, want_rotated=True)
+    assert np.array_equal(idx.probe_codes(q, T), oracle.probe_codes(rot, cb, T))
+
+
+@pytest.mark.parametrize("n,dim,K,cb,M,T,k,ef", [(3000, 128, 32, 1, 32, 1, 10, 50), (3000, 128, 32, 1, 32, 4, 10, 50),
+                                                 (3000, 128, 32, 1, 32, 16, 10, 100), (2000, 96, 16, 1, 16, 16, 5, 20),
+                                                 (1500, 200, 16, 2, 32, 4, 10, 40), (1200, 100, 12, 1, 16, 8, 7, 30)])
+def test_search_multiprobe_matches_oracle(cp, oracle, n, dim, K, cb, M, T, k, ef):
+    base, q = synthetic.gaussian_mixture(n, 40, dim, max(2, n // 250), 0.3, n + T)
+    idx = make_index(cp, dim, K, cb, M=M)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 8)
+    idx.add_batch_parallel(base)
+    signs, codes, adj = oracle_index(oracle, base, K, cb, M, min(64, 2 * M))
+    _, rot, _ = oracle.encode(q, K, cb, signs, 2, want_rotated=True)
+    wi, wd = oracle.search_multiprobe(rot, cb, codes, adj, idx.entry_ids(), max(ef, k), k, T, n_seed=8)
+    ids, dist = idx.search_multiprobe_batch(q, k, ef, T)
+    assert np.array_equal(ids, wi)
+    assert np.array_equal(dist, wd)
+    one = idx.search_multiprobe(q[0], k, ef, T)
+    assert [i for i, _ in one] == [int(i) for i in wi[0] if i != INVALID]
+    with pytest.raises(ValueError):
+        idx.search_multiprobe_batch(q, k, ef, 0)
+    with pytest.raises(ValueError):
+        idx.search_multiprobe_batch(q, 100, 100, 64)  # num_probes * k too large

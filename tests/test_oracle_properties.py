@@ -166,3 +166,51 @@ def test_zero_vector_and_duplicates_do_not_break(oracle):
     assert (codes[0] == 0).all()  # all-zero rotation: index 0, positive
     assert np.array_equal(codes[1], codes[2])
     assert np.isfinite(rot).all()
+
+
+def test_probe_sequence_matches_exhaustive_enumeration(oracle):
+    """The multiprobe sequence must be the T cheapest rank combinations in ascending cost
+    (resources/cross-polytope-lsh/consolidated.tex:391-425), the primary code first."""
+    import itertools
+    rng = np.random.default_rng(5)
+    K, P, T = 3, 8, 12
+    rot = rng.standard_normal((6, K, P)).astype(np.float32)
+    pc = oracle.probe_codes(rot, 1, T)
+    V = min(P, T + 1)
+    for q in range(rot.shape[0]):
+        order = [sorted(range(P), key=lambda i: (-abs(rot[q, r, i]), i)) for r in range(K)]
+        cost = [[np.float32(np.float32(abs(rot[q, r, order[r][0]]) - abs(rot[q, r, order[r][v]])) ** 2) for v in range(V)]
+                for r in range(K)]
+        states = []
+        for rk in itertools.product(range(V), repeat=K):
+            s = np.float32(0)
+            for r in range(K):
+                if rk[r]:
+                    s = np.float32(s + cost[r][rk[r]])
+            states.append((float(s), rk))
+        states.sort()
+        for t in range(T):
+            rk = states[t][1]
+            want = [(order[r][rk[r]] << 1) | int(rot[q, r, order[r][rk[r]]] < 0) for r in range(K)]
+            assert pc[q, t].tolist() == want, (q, t)
+    # probe 0 is the ordinary code of the query
+    assert np.array_equal(pc[:, 0, :] >> 1, np.abs(rot).argmax(axis=2))
+
+
+def test_multiprobe_merge_and_monotone_recall(oracle):
+    base, q, signs, codes = small_index(oracle, n=1500, nq=30, dim=64, K=16)
+    _, rot, _ = oracle.encode(q, 16, 1, signs, want_rotated=True)
+    nbrs, _ = oracle.knn_graph(codes, 32)
+    adj = oracle.select_neighbors(codes, nbrs, 16)
+    entry = (np.arange(64) * 1500 // 64).astype(np.uint32)
+    one_i, one_d = oracle.search_multiprobe(rot, 1, codes, adj, entry, 40, 10, 1, n_seed=8)
+    qc = oracle.encode(q, 16, 1, signs)
+    ref_i, ref_d = oracle.search_codes(qc, codes, adj, entry, 40, 10, n_seed=8)
+    assert np.array_equal(one_i, ref_i) and np.array_equal(one_d, ref_d)  # one probe = plain symmetric search
+    many_i, many_d = oracle.search_multiprobe(rot, 1, codes, adj, entry, 40, 10, 8, n_seed=8)
+    assert (np.diff(many_d, axis=1) >= 0).all()
+    for row in many_i:
+        valid = row[row != 0xFFFFFFFF]
+        assert len(set(valid.tolist())) == len(valid)  # every id once
+    # distances are code distances to SOME probe, so they can only improve on the single-probe answer
+    assert (many_d[:, 0] <= one_d[:, 0]).all()
