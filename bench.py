@@ -29,6 +29,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "sparse-text-kmeans_b200"))
 
 METRIC = "batch-search QPS @ recall@10>=0.9 (search_and_rerank)"
+# DRAM bytes (read + written) per query of search_kernel, from the ncu capture summarised in
+# profiles/search_kernel_c2_quarter.md (C2 at 1/4 size, 2,500 queries: 1.215 GB + 0.080 GB per launch);
+# scaled to a launch by the number of queries it processes.
+NCU_SEARCH_DRAM_BYTES_PER_QUERY = 518e3
 
 
 def parse_args():
@@ -363,7 +367,9 @@ def run_b200(args):
     search_ms_per_launch = search_ms / max(1, search_launches)
     achieved = bytes_per_query * nq / (search_ms_per_launch * 1e-3) / 1e9
     roofline = {"kernel": "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_source": "of " + peak_kind, "traffic": None,
+                "frac": achieved / peak, "peak_source": "of " + peak_kind,
+                "traffic": NCU_SEARCH_DRAM_BYTES_PER_QUERY * nq if w["name"] == "C2" else None,
+                "traffic_note": "bytes per launch, scaled by queries from the ncu capture of C2 at 1/4 size",
                 "ms_per_launch": search_ms_per_launch, "algorithmic_bytes_per_query": bytes_per_query,
                 "expansions_per_query": exp_mean, "distance_evals_per_query": evals_mean,
                 "share_of_step": search_ms / (ms_total if ms_total else 1.0),
