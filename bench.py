@@ -251,6 +251,8 @@ def run_b200(args):
             torch.cuda.synchronize()
             stage_ms[self.name] = max_over_ranks(self.e0.elapsed_time(self.e1))
 
+    if world > 1:  # start NCCL before the timed build (its first collective sets the communicator up)
+        dist.all_reduce(torch.zeros(1, device=dev))
     stages = sharded.CudaStages(idx)
     # untimed warm pass of the encode kernel (first-launch overheads), then the timed build
     stages.encode(d_base[rb:min(re, rb + 4096)])
@@ -264,10 +266,12 @@ def run_b200(args):
     # ---- ground truth for this rank's queries: exact cosine top-k (fp32 matmul, measurement support) ----
     d_q = torch.from_numpy(queries).to(dev)
     torch.backends.cuda.matmul.allow_tf32 = False
-    gt = torch.empty((nq, k), dtype=torch.int64, device=dev)
-    for q0 in range(0, nq, 1024):
-        sims = d_q[q0:q0 + 1024] @ d_base.T
-        gt[q0:q0 + 1024] = sims.topk(k, dim=1).indices
+    n_gt = min(nq, 10_000)  # recall is measured on the first 10,000 queries of the rank
+    gt = torch.empty((n_gt, k), dtype=torch.int64, device=dev)
+    gt_chunk = 1024 if n <= 2_000_000 else 128
+    for q0 in range(0, n_gt, gt_chunk):
+        sims = d_q[q0:min(n_gt, q0 + gt_chunk)] @ d_base.T
+        gt[q0:q0 + sims.shape[0]] = sims.topk(k, dim=1).indices
     gt = gt.cpu().numpy()
     del sims
 
@@ -321,7 +325,7 @@ def run_b200(args):
 
     ids = d_ids.cpu().numpy().astype(np.uint32)
     stats = d_stats.cpu().numpy()
-    recall = sharded.recall_at_k(ids, gt, k)
+    recall = sharded.recall_at_k(ids[:n_gt], gt, k)
     if world > 1:
         t = torch.tensor([recall], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
