@@ -69,6 +69,21 @@ int upload_signs(cphnsw_b200_index* h) {
             }
     CPB_TRY(h->d_signs.reserve(f.size() * sizeof(float)));
     CPB_CUDA(cudaMemcpy(h->d_signs.p, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+    if (P == 1024) {
+        // bit-packed copy for the 1024-point kernel (a set bit negates): layer 0 in the consecutive
+        // layout (word w, bit b <-> element 32*w + b), layers 1 and 2 in the column layout
+        // (word l, bit j <-> element 32*j + l)
+        std::vector<uint32_t> bits(K * 3 * 32, 0u);
+        for (size_t r = 0; r < K; ++r)
+            for (size_t l = 0; l < 3; ++l)
+                for (size_t i = 0; i < P; ++i)
+                    if (f[(r * 3 + l) * P + i] < 0.0f) {
+                        if (l == 0) bits[(r * 3 + l) * 32 + i / 32] |= 1u << (i % 32);
+                        else bits[(r * 3 + l) * 32 + i % 32] |= 1u << (i / 32);
+                    }
+        CPB_TRY(h->d_signbits.reserve(bits.size() * 4));
+        CPB_CUDA(cudaMemcpy(h->d_signbits.p, bits.data(), bits.size() * 4, cudaMemcpyHostToDevice));
+    }
     return 0;
 }
 

@@ -82,6 +82,7 @@ struct cphnsw_b200_index {
 
     std::vector<int8_t> signs;  // host [K][3][P]
     cpb::DevBuf d_signs;        // float [K][3][P], +-1 with the FHT convention folded into layers 1,2
+    cpb::DevBuf d_signbits;     // padded dim 1024 only: the same diagonals bit-packed, uint32 [K][3][32]
     cpb::DevBuf d_status;       // uint32 status word
 
     // index contents

@@ -187,6 +187,130 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
     for (int i = threadIdx.x; i < total; i += kTileVecs) dst[i] = code_tile[i];
 }
 
+// ---- padded dim 1024 (d in 513..1024): one warp per vector, 32 elements per lane -------------------
+// The 10 stages of a 1024-point transform are done as two register passes of a 32-point transform:
+// stages h = 1..16 with the lane holding 32 consecutive elements (i = 32*lane + j), stages
+// h = 32..512 with the lane holding a stride-32 column (i = 32*j + lane), and a transpose through a
+// padded 32x33 shared-memory tile between the two layouts.  The stage order h = 1, 2, 4, ... and
+// the butterfly (lo = x + y, hi = x - y, x the lower index) are the reference's, so the result is
+// bit-identical.  The diagonals come bit-packed in the layout they are applied in (a set bit
+// negates), one word per lane and layer.
+constexpr int kP1024 = 1024;
+constexpr int kWarps1024 = 4;
+
+__device__ __forceinline__ void fht32_regs(float (&v)[32]) {
+#pragma unroll
+    for (int h = 1; h < 32; h <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if ((j & h) == 0) {
+                const float x = v[j], y = v[j + h];
+                v[j] = __fadd_rn(x, y);
+                v[j + h] = __fsub_rn(x, y);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void flip_signs32(float (&v)[32], uint32_t word) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+        v[j] = __int_as_float(__float_as_int(v[j]) ^ int((word << (31 - j)) & 0x80000000u));
+}
+
+template <typename CompT, bool QUERY>
+__global__ void __launch_bounds__(kWarps1024 * 32)
+encode_p1024_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
+                    const uint32_t* __restrict__ signbits /*[K][3][32]*/, int flip_mask,
+                    CompT* __restrict__ codes, float* __restrict__ rotated, float* __restrict__ mags) {
+    __shared__ float tiles[kWarps1024][32 * 33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* buf = tiles[warp];
+    const bool vec4 = (dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+    for (uint64_t row = uint64_t(blockIdx.x) * kWarps1024 + warp; row < n; row += uint64_t(gridDim.x) * kWarps1024) {
+        // the vector, zero-padded, in the consecutive layout: xin[j] = x[32*lane + j]
+        float xin[32];
+        const float* src = x + row * uint64_t(dim);
+        if (vec4) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int i = 32 * lane + 4 * c;
+                float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < dim) q = __ldg(reinterpret_cast<const float4*>(src + i));
+                xin[4 * c] = q.x, xin[4 * c + 1] = q.y, xin[4 * c + 2] = q.z, xin[4 * c + 3] = q.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int i = 32 * lane + j;
+                xin[j] = i < dim ? __ldg(src + i) : 0.0f;
+            }
+        }
+        for (int r = 0; r < K; ++r) {
+            const uint32_t* sb = signbits + size_t(r) * 3 * 32;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = xin[j];
+#pragma unroll 1
+            for (int layer = 0; layer < 3; ++layer) {
+                const uint32_t word = __ldg(sb + layer * 32 + lane);
+                flip_signs32(v, word);  // layer 0: consecutive layout; layers 1, 2: column layout
+                if (layer > 0) {        // column -> consecutive
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) buf[j * 33 + lane] = v[j];
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = buf[lane * 33 + j];
+                }
+                fht32_regs(v);  // stages h = 1..16
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) buf[lane * 33 + j] = v[j];  // consecutive -> column
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = buf[j * 33 + lane];
+                fht32_regs(v);  // stages h = 32..512
+            }
+            // column layout: v[j] is element 32*j + lane.  Lowest-index argmax of |v|.
+            float best = -1.0f, win = 0.0f;
+            int idx = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float av = fabsf(v[j]);
+                if (av > best) {
+                    best = av;
+                    win = v[j];
+                    idx = 32 * j + lane;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const float ow = __shfl_xor_sync(0xffffffffu, win, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ob > best || (ob == best && oi < idx)) {
+                    best = ob;
+                    win = ow;
+                    idx = oi;
+                }
+            }
+            if (lane == 0) {
+                codes[row * K + r] = CompT(component_of(win, idx, flip_mask));
+                if (QUERY && mags) mags[row * K + r] = best;
+            }
+            if (QUERY && rotated) {
+                float* out = rotated + (row * K + r) * uint64_t(kP1024);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int i = 32 * j + lane;
+                    out[i] = (__popc(i & flip_mask) & 1) ? -v[j] : v[j];
+                }
+            }
+        }
+    }
+}
+
 // ---- generic padded dim: one warp per vector, transform in shared memory ----------------------
 template <typename CompT>
 __global__ void encode_generic_kernel(const float* __restrict__ x, uint64_t n, int dim, int P, int K,
@@ -289,6 +413,21 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
             else CPB_LAUNCH_P128(uint16_t, false);
         }
 #undef CPB_LAUNCH_P128
+    } else if (P == kP1024 && h->d_signbits.p) {
+        const bool query = d_rot || d_mag;
+        const uint64_t blocks = (n + kWarps1024 - 1) / kWarps1024;
+        const unsigned grid = unsigned(blocks < uint64_t(h->sm_count) * 16 ? blocks : uint64_t(h->sm_count) * 16);
+        const uint32_t* sb = h->d_signbits.as<uint32_t>();
+#define CPB_LAUNCH_P1024(T, Q)                                                                              \
+    encode_p1024_kernel<T, Q><<<grid, kWarps1024 * 32, 0, st>>>(d_x, n, dim, K, sb, flip_mask, (T*)d_codes, d_rot, d_mag)
+        if (h->comp_bytes == 1) {  // (a 1-byte component cannot hold a 1024-wide index; kept for symmetry)
+            if (query) CPB_LAUNCH_P1024(uint8_t, true);
+            else CPB_LAUNCH_P1024(uint8_t, false);
+        } else {
+            if (query) CPB_LAUNCH_P1024(uint16_t, true);
+            else CPB_LAUNCH_P1024(uint16_t, false);
+        }
+#undef CPB_LAUNCH_P1024
     } else {
         int warps = 4;
         while (warps > 1 && size_t(warps) * P * sizeof(float) > 96 * 1024) warps >>= 1;

@@ -138,6 +138,21 @@ int main() {
         }
         CHECK(mono && last > 0.3, "recall non-decreasing in ef");
     }
+    // search_multiprobe (evaluation/eval_sift.cpp:430): ascending integer code distances, one probe equals
+    // a plain walk under the code distance, more probes can only lower the best distance
+    {
+        auto q = unit_vectors(20, dim, 11);
+        auto one = index.search_multiprobe_batch(q.data(), 20, 10, 100, 1);
+        auto many = index.search_multiprobe_batch(q.data(), 20, 10, 100, 16);
+        bool ok = true;
+        for (size_t qi = 0; qi < 20; ++qi) {
+            ok &= one[qi].size() == 10 && many[qi].size() == 10;
+            for (size_t t = 1; t < many[qi].size(); ++t) ok &= many[qi][t - 1].distance <= many[qi][t].distance;
+            for (auto& r : many[qi]) ok &= r.distance >= 0 && r.distance <= 32 && r.distance == std::floor(r.distance);
+            ok &= many[qi][0].distance <= one[qi][0].distance;
+        }
+        CHECK(ok, "search_multiprobe returns ascending code distances and improves with probes");
+    }
     // edge cases (qa_protocol.cpp:409-553): tiny index, duplicates, zero vector
     {
         CPHNSWIndex<uint8_t, 32> tiny(dim, 32, 200);
