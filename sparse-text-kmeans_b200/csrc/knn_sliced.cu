@@ -1,11 +1,12 @@
-// Brute-force code-distance kNN graph with a bit-sliced distance (uint8 components, K = 16 or 32).
+// Brute-force code-distance kNN graph with a bit-sliced distance (K = 16 or 32; uint8 components,
+// or uint16 components of an 11-bit code, i.e. padded dim 1024).
 //
 // Same result as knn_graph_kernel in distance.cu (k smallest under (distance, id), self excluded),
 // four times fewer integer instructions per pair.  The candidates are re-laid out once, 32 at a
 // time, as bit planes: word (r, b) of a group holds bit b of component r of its 32 candidates.
 // For a query with component q_r, the candidates that differ from it in rotation r are
 //      neq_r = OR_b ( plane(r,b) XOR mask(q_r,b) ),      mask = all ones if bit b of q_r is set,
-// eight 3-input logic instructions for 32 candidates; the K one-bit planes neq_r are then summed
+// one 3-input logic instruction per bit plane (8 or 11 per rotation) for 32 candidates; the K one-bit planes neq_r are then summed
 // with carry-save adders (two logic instructions per full adder, K - 6 adders for K = 32) into
 // six planes holding the 32 distances, which are compared with the row's admission threshold in
 // bit-sliced form as well.  Only candidates below the threshold (rare once the list has warmed
@@ -15,6 +16,8 @@
 // and are read with broadcast 128-bit loads.  A tile is 1024 candidates = 32 groups, one group
 // per lane, laid out [16-byte chunk][group] so that the lanes' 128-bit loads are conflict-free;
 // tiles arrive by bulk asynchronous copies (two stages, bounded waits), as in the byte-wise kernel.
+#include <utility>
+
 #include "knn_common.cuh"
 
 namespace cpb {
@@ -22,8 +25,17 @@ namespace {
 
 using knn::kFull;
 constexpr int kSlWarps = 4;
-constexpr int kSlThreads = kSlWarps * 32;
 constexpr int kSlQ = 8;  // query rows per warp
+
+// compile-time loop: calls f(integral_constant<int, 0>), ..., f(integral_constant<int, N-1>)
+template <class F, int... Is>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, Is...>) {
+    (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+    static_for_impl(static_cast<F&&>(f), std::make_integer_sequence<int, N>{});
+}
 
 // full adder on bit planes: (carry, sum) of a + b + c
 __device__ __forceinline__ void csa(uint32_t& carry, uint32_t& sum, uint32_t a, uint32_t b, uint32_t c) {
@@ -32,36 +44,37 @@ __device__ __forceinline__ void csa(uint32_t& carry, uint32_t& sum, uint32_t a, 
     sum = u ^ c;
 }
 
-// ---- layout transform: codes [n][K] bytes -> tiles [tile][chunk (2K)][group (32)][4 words] ----------
-// one warp per group of 32 candidates; candidates past n read as zero codes (masked out later)
-__global__ void slice_codes_kernel(const uint8_t* __restrict__ codes, uint64_t n, int K, uint32_t* __restrict__ out,
-                                   uint64_t n_groups) {
+// ---- layout transform: codes [n][K] components -> tiles [tile][chunk (K*NB/4)][group (32)][4 words] --
+// one warp per group of 32 candidates; plane index w = r*NB + b; candidates past n read as zero
+// codes (masked out later)
+template <typename CompT>
+__global__ void slice_codes_kernel(const CompT* __restrict__ codes, uint64_t n, int K, int NB,
+                                   uint32_t* __restrict__ out, uint64_t n_groups) {
     const int lane = threadIdx.x & 31;
     const uint64_t g = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (g >= n_groups) return;
     const uint64_t cand = g * 32 + lane;
     const uint64_t tile = g >> 5;
     const int group = int(g & 31);
-    const int words_per_group = K * 8;            // bit planes per group
+    const int words_per_group = K * NB;  // bit planes per group
     uint32_t* tile_out = out + tile * uint64_t(words_per_group) * 32;
     for (int r = 0; r < K; ++r) {
-        const uint32_t byte = cand < n ? codes[cand * K + r] : 0u;
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-            const uint32_t plane = __ballot_sync(kFull, (byte >> b) & 1u);
-            const int w = r * 8 + b;  // plane index; chunk = w / 4, word in chunk = w % 4
+        const uint32_t comp = cand < n ? uint32_t(codes[cand * K + r]) : 0u;
+        for (int b = 0; b < NB; ++b) {
+            const uint32_t plane = __ballot_sync(kFull, (comp >> b) & 1u);
+            const int w = r * NB + b;  // chunk = w / 4, word in chunk = w % 4
             if (lane == (w & 31)) tile_out[(size_t(w >> 2) * 32 + group) * 4 + (w & 3)] = plane;
         }
     }
 }
 
-template <int NBLK, int SLOTS>  // NBLK = K / 8 (2 or 4)
-__global__ void __launch_bounds__(kSlThreads)
-knn_sliced_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict__ codes, uint64_t n, uint32_t k,
+template <typename CompT, int NB, int NBLK, int SLOTS, int WARPS>  // NB bit planes per component, NBLK = K / 8
+__global__ void __launch_bounds__(WARPS * 32)
+knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__ codes, uint64_t n, uint32_t k,
                   uint64_t row_begin, uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
                   uint32_t* __restrict__ status) {
     constexpr int K = NBLK * 8;
-    constexpr int CHUNKS = K * 2;                  // 16-byte chunks per group
+    constexpr int CHUNKS = K * NB / 4;             // 16-byte chunks per group
     constexpr uint32_t TILE_BYTES = CHUNKS * 32 * 16;
     extern __shared__ __align__(128) unsigned char sl_smem[];
     uint4* stage0 = reinterpret_cast<uint4*>(sl_smem);
@@ -88,14 +101,14 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict
     }
 
     // masks of this warp's Q rows: word (r, b) is all ones when bit b of the row's component r is set
-    const uint64_t first_row = row_begin + (uint64_t(blockIdx.x) * kSlWarps + warp) * kSlQ;
+    const uint64_t first_row = row_begin + (uint64_t(blockIdx.x) * WARPS + warp) * kSlQ;
     uint4* my_masks = masks + size_t(warp) * kSlQ * CHUNKS;
     for (int q = 0; q < kSlQ; ++q) {
         const uint64_t row = min(first_row + q, row_end - 1);
         uint32_t* mw = reinterpret_cast<uint32_t*>(my_masks + q * CHUNKS);
-        for (int w = lane; w < K * 8; w += 32) {
-            const uint32_t byte = codes[row * K + (w >> 3)];
-            mw[w] = ((byte >> (w & 7)) & 1u) ? kFull : 0u;
+        for (int w = lane; w < K * NB; w += 32) {
+            const uint32_t comp = uint32_t(codes[row * K + w / NB]);
+            mw[w] = ((comp >> (w % NB)) & 1u) ? kFull : 0u;
         }
     }
     __syncwarp();
@@ -134,54 +147,58 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict
 
 #pragma unroll 1
         for (int blk = 0; blk < NBLK; ++blk) {
-            uint32_t twosA[kSlQ], twosB[kSlQ], foursA[kSlQ], foursB[kSlQ], prev[kSlQ];
-#pragma unroll
-            for (int rr = 0; rr < 8; ++rr) {
-                const int chunk = (blk * 8 + rr) * 2;
-                const uint4 s0 = tile[size_t(chunk) * 32 + lane];
-                const uint4 s1 = tile[size_t(chunk + 1) * 32 + lane];
+            uint32_t twosA[kSlQ], twosB[kSlQ], foursA[kSlQ], foursB[kSlQ], prev[kSlQ], x[kSlQ];
+            // the 8 rotations of this block span 8*NB planes = 2*NB chunks; the chunk index is a
+            // compile-time constant so that every plane's (rotation, bit) is resolved statically
+            static_for<2 * NB>([&](auto cc) {
+                constexpr int c = decltype(cc)::value;
+                const int chunk = blk * 2 * NB + c;
+                const uint4 s4 = tile[size_t(chunk) * 32 + lane];
+                const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                 for (int q = 0; q < kSlQ; ++q) {
-                    const uint4 m0 = my_masks[q * CHUNKS + chunk];
-                    const uint4 m1 = my_masks[q * CHUNKS + chunk + 1];
-                    uint32_t x = s0.x ^ m0.x;
-                    x |= s0.y ^ m0.y;
-                    x |= s0.z ^ m0.z;
-                    x |= s0.w ^ m0.w;
-                    x |= s1.x ^ m1.x;
-                    x |= s1.y ^ m1.y;
-                    x |= s1.z ^ m1.z;
-                    x |= s1.w ^ m1.w;
-                    // carry-save accumulation of the 8 planes of this block
-                    if (rr & 1) {
-                        uint32_t& tw = (rr & 2) ? twosB[q] : twosA[q];
-                        csa(tw, ones[q], ones[q], prev[q], x);
-                        if ((rr & 3) == 3) {
-                            uint32_t& fo = (rr & 4) ? foursB[q] : foursA[q];
-                            csa(fo, twos[q], twos[q], twosA[q], twosB[q]);
-                            if (rr == 7) {
-                                uint32_t e8;
-                                csa(e8, fours[q], fours[q], foursA[q], foursB[q]);
-                                if (blk & 1) {
-                                    uint32_t s16;
-                                    csa(s16, eights[q], eights[q], pend8[q], e8);
-                                    if (NBLK == 2) {
-                                        sixteens[q] = s16;
-                                    } else if (blk & 2) {
-                                        csa(thirtytwos[q], sixteens[q], sixteens[q], pend16[q], s16);
-                                    } else {
-                                        pend16[q] = s16;
+                    const uint4 m4 = my_masks[q * CHUNKS + chunk];
+                    const uint32_t mw[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int widx = c * 4 + i;  // plane within the block
+                        const int rr = widx / NB;    // rotation within the block (0..7)
+                        const int b = widx % NB;     // bit of the component
+                        const uint32_t t = sw[i] ^ mw[i];
+                        x[q] = b == 0 ? t : (x[q] | t);
+                        if (b == NB - 1) {
+                            // carry-save accumulation of this rotation's "differs" plane
+                            if (rr & 1) {
+                                uint32_t& tw = (rr & 2) ? twosB[q] : twosA[q];
+                                csa(tw, ones[q], ones[q], prev[q], x[q]);
+                                if ((rr & 3) == 3) {
+                                    uint32_t& fo = (rr & 4) ? foursB[q] : foursA[q];
+                                    csa(fo, twos[q], twos[q], twosA[q], twosB[q]);
+                                    if (rr == 7) {
+                                        uint32_t e8;
+                                        csa(e8, fours[q], fours[q], foursA[q], foursB[q]);
+                                        if (blk & 1) {
+                                            uint32_t s16;
+                                            csa(s16, eights[q], eights[q], pend8[q], e8);
+                                            if (NBLK == 2) {
+                                                sixteens[q] = s16;
+                                            } else if (blk & 2) {
+                                                csa(thirtytwos[q], sixteens[q], sixteens[q], pend16[q], s16);
+                                            } else {
+                                                pend16[q] = s16;
+                                            }
+                                        } else {
+                                            pend8[q] = e8;
+                                        }
                                     }
-                                } else {
-                                    pend8[q] = e8;
                                 }
+                            } else {
+                                prev[q] = x[q];
                             }
                         }
-                    } else {
-                        prev[q] = x;
                     }
                 }
-            }
+            });
         }
 
 #pragma unroll
@@ -248,55 +265,69 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict
     }
 }
 
-template <int NBLK, int SLOTS>
-int launch_sliced_t(cphnsw_b200_index* h, const uint32_t* sliced, const uint8_t* codes, uint64_t n, uint32_t k,
+template <typename CompT, int NB, int NBLK, int SLOTS, int WARPS>
+int launch_sliced_t(cphnsw_b200_index* h, const uint32_t* sliced, const CompT* codes, uint64_t n, uint32_t k,
                     uint64_t rb, uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
-    constexpr int CHUNKS = NBLK * 16;
-    const size_t smem = size_t(2) * CHUNKS * 32 * 16 + size_t(kSlWarps) * kSlQ * CHUNKS * 16;
-    CPB_CUDA(cudaFuncSetAttribute(knn_sliced_kernel<NBLK, SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    constexpr int CHUNKS = NBLK * 8 * NB / 4;
+    const size_t smem = size_t(2) * CHUNKS * 32 * 16 + size_t(WARPS) * kSlQ * CHUNKS * 16;
+    auto kernel = knn_sliced_kernel<CompT, NB, NBLK, SLOTS, WARPS>;
+    CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const uint64_t rows = re - rb;
-    const uint64_t blocks = (rows + kSlWarps * kSlQ - 1) / (kSlWarps * kSlQ);
+    const uint64_t blocks = (rows + WARPS * kSlQ - 1) / (WARPS * kSlQ);
     LaunchTimer timer(h, kKernelKnn, st);
-    knn_sliced_kernel<NBLK, SLOTS><<<unsigned(blocks), kSlThreads, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist,
-                                                                             h->d_status.as<uint32_t>());
+    kernel<<<unsigned(blocks), WARPS * 32, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>());
     h->launches++;
     CPB_CUDA(cudaGetLastError());
     return 0;
 }
 
-template <int NBLK>
-int launch_sliced_slots(cphnsw_b200_index* h, const uint32_t* sliced, const uint8_t* codes, uint64_t n, uint32_t k,
+template <typename CompT, int NB, int NBLK, int WARPS>
+int launch_sliced_slots(cphnsw_b200_index* h, const uint32_t* sliced, const CompT* codes, uint64_t n, uint32_t k,
                         uint64_t rb, uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
     const uint32_t need = k + 1;
-    if (need <= 64) return launch_sliced_t<NBLK, 2>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
-    if (need <= 96) return launch_sliced_t<NBLK, 3>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
-    return launch_sliced_t<NBLK, 4>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
+    if (need <= 64) return launch_sliced_t<CompT, NB, NBLK, 2, WARPS>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
+    if (need <= 96) return launch_sliced_t<CompT, NB, NBLK, 3, WARPS>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
+    return launch_sliced_t<CompT, NB, NBLK, 4, WARPS>(h, sliced, codes, n, k, rb, re, nbrs, dist, st);
 }
 
 }  // namespace
 
+// uint8 components (8 planes) or uint16 components of padded dim 1024 (10 index bits + sign = 11 planes)
 bool knn_sliced_supported(const cphnsw_b200_index* h) {
-    return h->comp_bytes == 1 && (h->K == 16 || h->K == 32);
+    if (h->K != 16 && h->K != 32) return false;
+    return h->comp_bytes == 1 || (h->comp_bytes == 2 && h->P == 1024);
 }
 
 int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
                             uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st) {
     const int K = int(h->K);
+    const bool u16 = h->comp_bytes == 2;
+    const int NB = u16 ? 11 : 8;
     const uint64_t tiles = (n + knn::kTile - 1) / knn::kTile;
     const uint64_t n_groups = tiles * 32;
-    const size_t sliced_bytes = size_t(tiles) * K * 8 * 32 * 4;
+    const size_t sliced_bytes = size_t(tiles) * K * NB * 32 * 4;
     CPB_TRY(h->s_sliced.reserve(sliced_bytes + 16));
     {
         const uint64_t threads = n_groups * 32;
-        slice_codes_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(d_codes), n, K,
-                                                                            h->s_sliced.as<uint32_t>(), n_groups);
+        const unsigned grid = unsigned((threads + 255) / 256);
+        if (u16)
+            slice_codes_kernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(d_codes), n, K, NB,
+                                                               h->s_sliced.as<uint32_t>(), n_groups);
+        else
+            slice_codes_kernel<uint8_t><<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(d_codes), n, K, NB,
+                                                              h->s_sliced.as<uint32_t>(), n_groups);
         h->launches++;
         CPB_CUDA(cudaGetLastError());
     }
     const uint32_t* sl = h->s_sliced.as<uint32_t>();
+    if (u16) {
+        const uint16_t* codes = static_cast<const uint16_t*>(d_codes);
+        if (K == 16) return launch_sliced_slots<uint16_t, 11, 2, 8>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+        return launch_sliced_slots<uint16_t, 11, 4, 8>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    }
     const uint8_t* codes = static_cast<const uint8_t*>(d_codes);
-    if (K == 16) return launch_sliced_slots<2>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
-    return launch_sliced_slots<4>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    if (K == 16) return launch_sliced_slots<uint8_t, 8, 2, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    return launch_sliced_slots<uint8_t, 8, 4, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
 }
 
 }  // namespace cpb

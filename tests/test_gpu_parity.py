@@ -97,12 +97,14 @@ def clustered_codes(oracle, n, dim, K, cb, seed):
 @pytest.mark.parametrize("n,k,K,cb,dim", [(1, 4, 32, 1, 128), (2, 4, 32, 1, 128), (33, 40, 32, 1, 128),
                                           (1000, 32, 32, 1, 128), (2500, 64, 32, 1, 128), (3000, 10, 16, 1, 64),
                                           (1500, 32, 32, 2, 256), (1200, 100, 32, 1, 128), (900, 16, 12, 1, 32),
-                                          (5000, 32, 32, 1, 96), (2100, 20, 16, 1, 128), (1025, 64, 32, 1, 128)])
+                                          (5000, 32, 32, 1, 96), (2100, 20, 16, 1, 128), (1025, 64, 32, 1, 128),
+                                          (1300, 32, 32, 2, 960), (1100, 70, 16, 2, 1000)])
 @pytest.mark.parametrize("kernel", [1, 2])  # byte-wise and bit-sliced distance
 def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim, kernel):
     _, codes = clustered_codes(oracle, n, dim, K, cb, n + k)
     idx = make_index(cp, dim, K, cb)
-    if kernel == 2 and not (cb == 1 and K in (16, 32)):
+    sliced_ok = K in (16, 32) and (cb == 1 or idx.padded_dim == 1024)
+    if kernel == 2 and not sliced_ok:
         idx.set_param("knn_kernel", 2)
         with pytest.raises(cp.CPHNSWError):
             idx.knn_graph(codes, k)
