@@ -66,7 +66,10 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
 /* Named tunables (CPHNSWParams fields, types.hpp:374-400, plus build/search knobs):
  *   "keep_pruned" (0/1, default 1), "profile" (0/1, see kernel_time),
  *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
- *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; uint8 codes with K = 16/32 only),
+ *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; K = 16/32 with uint8 codes,
+ *                 or uint16 codes of padded dim 1024),
+ *   "search_kernel" (0 = pick, 1 = one warp per query, 2 = two warps per query; the second needs
+ *                    K * padded_dim * 4 <= 32 KB and M <= 32; both return identical results),
  *   "entry_scan" (evenly spaced nodes scored for every query before the walk; default = k_entry),
  *   "k_entry" (1..100, default 4: how many of the scored nodes, the best, seed the walk). */
 int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double value);

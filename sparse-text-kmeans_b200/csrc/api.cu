@@ -404,6 +404,11 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         h->knn_kernel = int(v);
         return 0;
     }
+    if (s == "search_kernel") {
+        if (v != 0 && v != 1 && v != 2) { set_error("search_kernel must be 0 (pick), 1 (one warp per query) or 2 (two warps per query)"); return CPHNSW_B200_E_INVALID; }
+        h->search_kernel = int(v);
+        return 0;
+    }
     if (s == "k_entry") {
         if (v < 1) { set_error("CPHNSWParams: k_entry must be > 0"); return CPHNSW_B200_E_INVALID; }
         if (v > 100) { set_error("CPHNSWParams: k_entry must be <= 100"); return CPHNSW_B200_E_INVALID; }
@@ -432,6 +437,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     if (s == "keep_pruned") *v = h->keep_pruned;
     else if (s == "profile") *v = h->profile;
     else if (s == "knn_kernel") *v = h->knn_kernel;
+    else if (s == "search_kernel") *v = h->search_kernel;
     else if (s == "k_entry") *v = h->k_entry;
     else if (s == "knn_k") *v = h->knn_k;
     else if (s == "entry_scan") *v = h->entry_scan;

@@ -29,162 +29,12 @@
 // + the host partial_sort of src/cuda/gpu_encoder.cu:605-664) and sorted by a bitonic network.
 #include <cmath>
 
-#include "common.cuh"
+#include "search_common.cuh"
 
 namespace cpb {
 namespace {
 
-constexpr uint32_t kFull = 0xffffffffu;
-constexpr uint32_t kExpanded = 0x80000000u; // top bit of a stored id: the member has been expanded
-constexpr uint32_t kIdMask = 0x7fffffffu;
-constexpr int kCoopMax = 8;                 // up to this many fresh nodes are scored by the whole warp
-
-struct SearchArgs {
-    const float* tables;   // [nq][K][P] (asymmetric metric)
-    const void* qcodes;    // [nq][K] query codes (symmetric metric)
-    const float* queries;  // [nq][dim] (rerank only)
-    const void* codes;     // [n][K] components
-    const uint32_t* adj;   // [n][M]
-    const float* vectors;  // [n][dim] (rerank only)
-    const uint32_t* entry;     // ids scored for every query before the walk
-    const void* entry_codes;   // their codes, gathered contiguously [n_entry][K]
-    uint32_t n_entry, n_seed;  // the n_seed best of the scan seed the walk
-    uint64_t n;
-    uint32_t nq;
-    int K, P, dim, M, comp_bytes;
-    uint32_t qsm_floats;              // size of the per-warp query area
-    uint32_t per_warp_smem;           // bytes of shared memory per warp (multiple of 16)
-    uint32_t beam, cap, k, rerank_k;  // cap: power of two >= max(32, beam, n_seed), the size of W's arrays
-    uint8_t* visited;    // [warp slots][vis_stride]: epoch of the last query that visited the node
-    uint64_t vis_stride; // bytes per warp slot (n rounded up to 16)
-    uint32_t* epochs;    // [warp slots]: last epoch used by the slot (persists across launches)
-    uint32_t* out_ids;
-    float* out_dist;
-    uint32_t* stats;
-    uint32_t* next_query;  // work counter, zero at launch
-};
-
-__device__ __forceinline__ void prefetch_l1(const void* p) {
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
-}
-
-__device__ __forceinline__ bool key_less(float da, uint32_t ia, float db, uint32_t ib) {
-    return da < db || (da == db && ia < ib);
-}
-
-template <bool U16>
-__device__ __forceinline__ uint32_t load_component(const unsigned char* row, int r) {
-    return U16 ? uint32_t(reinterpret_cast<const uint16_t*>(row)[r]) : uint32_t(row[r]);
-}
-
-// signed table value of rotation r for component `comp` (+0 for r >= K)
-__device__ __forceinline__ float signed_term(const float* table, int r, int K, int P, uint32_t comp) {
-    if (r >= K) return 0.0f;
-    const float val = table[r * P + int(comp >> 1)];
-    return (comp & 1u) ? -val : val;
-}
-
-// One lane scores one node: the 32 terms of each block are combined in the balanced-tree order
-// (j with j+16, then +8, +4, +2, +1), blocks are added in sequence.
-template <bool U16>
-__device__ __forceinline__ float asym_distance_lane(const float* table, const void* codes, uint32_t row_index,
-                                                    int K, int P) {
-    const int row_bytes = K * (U16 ? 2 : 1);
-    const unsigned char* row = static_cast<const unsigned char*>(codes) + size_t(row_index) * row_bytes;
-    const bool vec = (row_bytes & 15) == 0;
-    float acc = 0.0f;
-    for (int c0 = 0; c0 < K; c0 += 32) {
-        float t[32];
-        if (vec) {
-            constexpr int kPerWord = U16 ? 2 : 4;           // components per 32-bit word
-            constexpr int kWords = 32 / kPerWord;           // words per block of 32 components
-            const uint4* r4 = reinterpret_cast<const uint4*>(row + size_t(c0) * (U16 ? 2 : 1));
-            uint32_t w[kWords];
-#pragma unroll
-            for (int i = 0; i < kWords / 4; ++i) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (c0 + i * 4 * kPerWord < K) v = __ldg(r4 + i);
-                w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const uint32_t word = w[j / kPerWord];
-                const uint32_t comp = U16 ? ((word >> (16 * (j % 2))) & 0xffffu) : ((word >> (8 * (j % 4))) & 0xffu);
-                t[j] = signed_term(table, c0 + j, K, P, comp);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int r = c0 + j;
-                t[j] = signed_term(table, r, K, P, r < K ? load_component<U16>(row, r) : 0u);
-            }
-        }
-#pragma unroll
-        for (int step = 16; step >= 1; step >>= 1) {
-#pragma unroll
-            for (int j = 0; j < step; ++j) t[j] = __fadd_rn(t[j], t[j + step]);
-        }
-        acc = __fadd_rn(acc, t[0]);
-    }
-    return -acc;
-}
-
-// Symmetric metric (search_multiprobe): number of components in which the node's code differs
-// from the query code staged in shared memory, as a float.
-template <bool U16>
-__device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, const void* codes, uint32_t row_index,
-                                                   int K) {
-    const int row_bytes = K * (U16 ? 2 : 1);
-    const unsigned char* row = static_cast<const unsigned char*>(codes) + size_t(row_index) * row_bytes;
-    uint32_t d = 0;
-    if ((row_bytes & 3) == 0) {
-        constexpr uint32_t LO = U16 ? 0x7fff7fffu : 0x7f7f7f7fu;
-        const uint32_t* r32 = reinterpret_cast<const uint32_t*>(row);
-        const uint32_t* q32 = reinterpret_cast<const uint32_t*>(qcode);
-        for (int w = 0; w < row_bytes / 4; ++w) {
-            const uint32_t x = q32[w] ^ __ldg(r32 + w);
-            d += __popc((((x & LO) + LO) | x) & ~LO);  // one flag per differing byte / halfword
-        }
-    } else {
-        for (int r = 0; r < K; ++r) d += load_component<U16>(row, r) != load_component<U16>(qcode, r);
-    }
-    return float(d);
-}
-
-// The whole warp scores one node: lane j owns rotation c0 + j of each block; the butterfly
-// reduction adds exactly the pairs the one-lane form adds.  `comp` is this lane's component of
-// block 0 (K <= 32 on this path).
-__device__ __forceinline__ float asym_distance_coop(const float* table, int K, int P, uint32_t comp, int lane) {
-    float t = signed_term(table, lane, K, P, comp);
-#pragma unroll
-    for (int step = 16; step >= 1; step >>= 1) t = __fadd_rn(t, __shfl_xor_sync(kFull, t, step));
-    return -__fadd_rn(0.0f, t);
-}
-
-// ---- warp-wide bitonic sort of n (a power of two) (distance, id) pairs in shared memory ------------
-// ascending by (distance, id); runtime loops keep the code small, each lane handles n/64 pairs
-// per stage.
-__device__ __forceinline__ void warp_sort_smem(float* d, uint32_t* id, int n, int lane) {
-    for (int k2 = 2; k2 <= n; k2 <<= 1) {
-        for (int j = k2 >> 1; j > 0; j >>= 1) {
-            for (int t = lane; t < n / 2; t += 32) {
-                const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));  // index with bit j clear
-                const int hi = lo | j;
-                const bool asc = (lo & k2) == 0;
-                const float dl = d[lo], dh = d[hi];
-                const uint32_t il = id[lo], ih = id[hi];
-                const bool hi_less = key_less(dh, ih, dl, il);
-                if (hi_less == asc) {
-                    d[lo] = dh;
-                    id[lo] = ih;
-                    d[hi] = dl;
-                    id[hi] = il;
-                }
-            }
-            __syncwarp();
-        }
-    }
-}
+using namespace srch;
 
 template <bool U16, bool TABLE_SMEM, bool SYM>
 __global__ void search_kernel(SearchArgs a) {
@@ -551,6 +401,10 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
 
 }  // namespace
 
+// two-warps-per-query kernel (search_team.cu)
+size_t search_team_extra_smem();
+int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st);
+
 int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
     const int row_bytes = int(h->K * h->comp_bytes);
     CPB_TRY(h->d_entry_codes.reserve(size_t(h->n_entry) * row_bytes + 16));
@@ -630,6 +484,20 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     const unsigned grid = unsigned(h->sm_count);
     const bool u16 = h->comp_bytes == 2;
     LaunchTimer timer(h, kKernelSearch, st);
+
+    // two warps per query: asymmetric metric, table in shared memory, one adjacency row per warp
+    const bool team_ok = !sym && c.table_smem && h->M <= 32 && h->k_entry <= 128;
+    if (h->search_kernel == 2 && !team_ok && !sym) {
+        set_error("search_kernel=2 needs the asymmetric metric, K*P*4 <= 32 KB and M <= 32");
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    if (team_ok && h->search_kernel != 1) {
+        const size_t per_team = (c.per_warp + search_team_extra_smem() + 15) & ~size_t(15);
+        CPB_TRY(launch_search_team(h, a, per_team, st));
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+        return 0;
+    }
 
 #define CPB_SEARCH(U, T, S)                                                                                \
     do {                                                                                                   \

@@ -1,0 +1,681 @@
+// Beam search with two warps per query ("team"): same algorithm and same results as
+// search_kernel (search.cu), arranged so that every expansion is a short chain of instructions.
+//
+// The walker warp owns W and the visited marks and performs the expansions in the exact
+// sequential order.  The scout warp prepares rows ahead of it.  Before each expansion the walker
+// announces the node it expands and the next three unexpanded members of W; the scout moves each
+// announced node one stage further per step: adjacency row towards L1; visited bytes read and the
+// codes of the unvisited neighbours towards L1; neighbours scored against the query table (which
+// the two warps share in shared memory) into a result slot.  When the walker selects a node that
+// has a result slot, it drops the neighbours it has marked itself since the scout read the
+// visited bytes (a ring of its latest marks tells which), marks the rest and admits them: no
+// global load is left on its path.  Without a slot it does the expansion itself, as the one-warp
+// kernel does.  Scores are a pure function of (query, node) and the set of neighbours offered is
+// the set unvisited at the walker's own sequential time either way, so the results do not
+// depend on how far the scout got.
+//
+// W is a tiered vector: buckets of 32 slots, each a circular buffer, globally sorted.  An
+// admission shifts inside one bucket (one load, two shuffles and one store per lane) and every
+// later bucket takes the element pushed out of its predecessor at its front in place of its
+// own last, all buckets at once (one lane per bucket).
+//
+// The two warps meet at a named barrier (bar.sync id, 64) once per expansion; every barrier sits
+// in control flow that depends only on values both warps read after the previous barrier, so the
+// two warps always execute the same sequence of barriers and nothing spins.  The entry scan and
+// the rerank are split between the two warps.
+//
+// Used for the asymmetric metric when the query table fits shared memory and M <= 32.
+#include "search_common.cuh"
+
+namespace cpb {
+namespace {
+
+using namespace srch;
+
+constexpr int kSeedCap = 128;  // scout's seed list; the same arrays hold the result slots during the walk
+constexpr int kSlots = 4;      // prepared rows kept for the walker (32 ids + 32 scores each)
+constexpr int kRing = 64;      // ids the walker marked most recently
+// mailbox words: 0 query, 8 scout evaluations, 9 scout seed count, 10 count; per result slot its
+// node, candidate mask and the walker's mark count when the visited bytes were read; two
+// announcement records {node, next three unexpanded, done, marks so far} used alternately
+constexpr int kKeyBase = 16, kMaskBase = 20, kSnapBase = 24, kPostBase = 32;
+constexpr int kMailWords = 48;
+static_assert(kSlots * 32 <= kSeedCap, "result slots live in the seed arrays");
+
+// ---- flat sorted list (the scout's share of the entry scan) ---------------------------------------
+struct BeamList {
+    float* d;
+    uint32_t* id;
+    uint32_t count, cap;
+    float wd;
+    uint32_t wi;
+};
+
+// Admission of (d, id), known to every lane, into a sorted list that keeps the cap best.
+__device__ __forceinline__ void beam_admit(BeamList& L, float d, uint32_t id, int lane) {
+    if (L.count == L.cap && !key_less(d, id, L.wd, L.wi)) return;
+    uint32_t p = 0;
+    if (L.count) {  // rank by a two-round 32-ary search
+        const uint32_t stride = (L.count + 31) >> 5;
+        const uint32_t e = min(L.count, (uint32_t(lane) + 1) * stride) - 1;
+        const bool in = uint32_t(lane) * stride < L.count;
+        const bool less = in && key_less(L.d[e], L.id[e], d, id);
+        const uint32_t b = __popc(__ballot_sync(kFull, less));
+        const uint32_t j = b * stride + lane;
+        const bool less2 = b < 32 && uint32_t(lane) < stride && j < L.count && key_less(L.d[j], L.id[j], d, id);
+        p = min(L.count, b * stride) + __popc(__ballot_sync(kFull, less2));
+    }
+    const int end = int(L.count == L.cap ? L.cap - 1 : L.count);
+    for (int top = end; top > int(p); top -= 32) {
+        const int i = top - 1 - lane;
+        const bool act = i >= int(p);
+        float md = 0.0f;
+        uint32_t mi = 0;
+        if (act) {
+            md = L.d[i];
+            mi = L.id[i];
+        }
+        __syncwarp();
+        if (act) {
+            L.d[i + 1] = md;
+            L.id[i + 1] = mi;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        L.d[p] = d;
+        L.id[p] = id;
+    }
+    __syncwarp();
+    if (L.count < L.cap) ++L.count;
+    if (L.count == L.cap) {
+        L.wd = L.d[L.cap - 1];
+        L.wi = L.id[L.cap - 1];
+    }
+}
+
+__device__ __forceinline__ void beam_admit_lanes(BeamList& L, uint32_t m, bool mine, float dist, uint32_t id, int lane) {
+    if (L.count == L.cap) m &= __ballot_sync(kFull, mine && key_less(dist, id, L.wd, L.wi));
+    while (m) {
+        const int src = __ffs(m) - 1;
+        m &= m - 1;
+        beam_admit(L, __shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src), lane);
+    }
+}
+
+// ---- tiered sorted list (W, walker only) -----------------------------------------------------------
+// Logical position p lives in bucket p >> 5 at slot (head + (p & 31)) & 31.  All nb * 32 logical
+// positions always hold something: live members first (count of them), then members pushed out of
+// a full list (still in ascending order, never looked at), then (+inf, invalid) fillers.  Lane b
+// keeps bucket b's head and a copy of its last (largest) element.
+struct TierList {
+    float* d;
+    uint32_t* id;    // expanded flag in the top bit
+    int nb;          // buckets (cap / 32 <= 32)
+    uint32_t count, wcap, cur;
+    float wd;        // worst live member once count == wcap
+    uint32_t wi;
+    int head;        // lane b: head of bucket b
+    float max_d;     // lane b: last logical element of bucket b
+    uint32_t max_i;
+};
+
+// heads to zero (the arrays are then read flat) and the per-bucket maxima re-read
+__device__ __forceinline__ void tier_reset_heads(TierList& T, int lane) {
+    T.head = 0;
+    T.max_d = INFINITY;
+    T.max_i = kInvalidNode;
+    if (lane < T.nb) {
+        T.max_d = T.d[lane * 32 + 31];
+        T.max_i = T.id[lane * 32 + 31];
+    }
+}
+
+__device__ __forceinline__ void tier_refresh_worst(TierList& T) {
+    if (T.count == T.wcap) {
+        const int wb = int(T.wcap - 1) >> 5;
+        const int hw = __shfl_sync(kFull, T.head, wb);
+        const int ws = wb * 32 + ((hw + int((T.wcap - 1) & 31)) & 31);
+        T.wd = T.d[ws];
+        T.wi = T.id[ws] & kIdMask;
+    }
+}
+
+// Admission of (d, id), known to every lane (search_engine.hpp:166-176).
+__device__ __forceinline__ void tier_admit(TierList& T, float d, uint32_t id, int lane) {
+    if (T.count == T.wcap && !key_less(d, id, T.wd, T.wi)) return;
+    // first bucket whose largest element is not below the key (fillers are +inf: there is one)
+    const bool below = lane < T.nb && key_less(T.max_d, T.max_i & kIdMask, d, id);
+    const int b = __popc(__ballot_sync(kFull, below));
+    const int hb = __shfl_sync(kFull, T.head, b);
+    const int slot = b * 32 + ((hb + lane) & 31);
+    const float ed = T.d[slot];  // logical element `lane` of bucket b
+    const uint32_t ei = T.id[slot];
+    const int r = __popc(__ballot_sync(kFull, key_less(ed, ei & kIdMask, d, id)));  // rank inside the bucket (<= 31)
+    const float pd = __shfl_up_sync(kFull, ed, 1);
+    const uint32_t pi = __shfl_up_sync(kFull, ei, 1);
+    const float nd = lane < r ? ed : (lane == r ? d : pd);
+    const uint32_t ni = lane < r ? ei : (lane == r ? id : pi);
+    if (lane >= r) {
+        T.d[slot] = nd;
+        T.id[slot] = ni;
+    }
+    const float out_d = __shfl_sync(kFull, ed, 31);  // pushed out of bucket b
+    const uint32_t out_i = __shfl_sync(kFull, ei, 31);
+    const float top_d = __shfl_sync(kFull, nd, 31);  // bucket b's new last element
+    const uint32_t top_i = __shfl_sync(kFull, ni, 31);
+    // later buckets, up to the one holding position wcap - 1: take the predecessor's last element
+    // at the front, in the slot of the own last element, which moves on
+    const int wb = int(T.wcap - 1) >> 5;
+    const bool casc = lane > b && lane <= wb;
+    const int last_slot = (lane & 31) * 32 + ((T.head + 31) & 31);
+    float ld = out_d;
+    uint32_t li = out_i;
+    if (casc) {
+        ld = T.d[last_slot];
+        li = T.id[last_slot];
+    }
+    const float in_d = __shfl_up_sync(kFull, ld, 1);  // lane b passes on out_d
+    const uint32_t in_i = __shfl_up_sync(kFull, li, 1);
+    if (casc) {
+        T.d[last_slot] = in_d;
+        T.id[last_slot] = in_i;
+        T.head = (T.head + 31) & 31;
+        const int nl = lane * 32 + ((T.head + 31) & 31);
+        T.max_d = T.d[nl];
+        T.max_i = T.id[nl];
+    }
+    if (lane == b) {
+        T.max_d = top_d;
+        T.max_i = top_i;
+    }
+    __syncwarp();
+    if (T.count < T.wcap) ++T.count;
+    const uint32_t p = uint32_t(b) * 32 + r;
+    if (p <= T.cur) T.cur = p;
+    tier_refresh_worst(T);
+}
+
+// admit the scored candidates of the lanes in mask m, lowest lane first
+__device__ __forceinline__ void tier_admit_lanes(TierList& T, uint32_t m, bool mine, float dist, uint32_t id, int lane) {
+    if (T.count == T.wcap) m &= __ballot_sync(kFull, mine && key_less(dist, id, T.wd, T.wi));
+    while (m) {
+        const int src = __ffs(m) - 1;
+        m &= m - 1;
+        tier_admit(T, __shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src), lane);
+    }
+}
+
+template <bool U16>
+__global__ void search_team_kernel(SearchArgs a) {
+    extern __shared__ __align__(16) unsigned char team_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int team = warp >> 1, role = warp & 1, teams = blockDim.x >> 6;
+    const int tl = role * 32 + lane;  // 0..63 within the team
+    const size_t table_floats = size_t(a.K) * a.P;
+    const size_t dim_pad = a.qsm_floats;
+    const int cap = int(a.cap);
+    unsigned char* mine = team_smem + size_t(a.per_warp_smem) * team;  // per-team area
+    float* table = reinterpret_cast<float*>(mine);
+    float* qsm = table + table_floats;
+    uint32_t* sid = reinterpret_cast<uint32_t*>(qsm + dim_pad);
+    float* sd = reinterpret_cast<float*>(sid + cap);
+    uint32_t* seed_id = reinterpret_cast<uint32_t*>(sd + cap);  // scout's seeds
+    float* seed_d = reinterpret_cast<float*>(seed_id + kSeedCap);
+    uint32_t* res_id = seed_id;  // [kSlots][32] rows prepared by the scout (after the entry scan)
+    float* res_d = seed_d;       // [kSlots][32]
+    uint32_t* ring = reinterpret_cast<uint32_t*>(seed_d + kSeedCap);
+    volatile uint32_t* mail = reinterpret_cast<volatile uint32_t*>(ring + kRing);
+
+    auto team_sync = [&]() {
+        __syncwarp();
+        asm volatile("bar.sync %0, 64;" ::"r"(team + 1) : "memory");
+    };
+
+    const uint32_t slot = blockIdx.x * teams + team;
+    uint8_t* vis = a.visited + size_t(slot) * a.vis_stride;
+    uint32_t epoch = a.epochs[slot];
+    const uint32_t beam = a.beam;
+    const bool scan_mode = a.n_seed < a.n_entry;
+    const int row_bytes = a.K * (U16 ? 2 : 1);
+    const bool coop_ok = a.K <= 32;
+
+    while (true) {
+        if (role == 0 && lane == 0) mail[0] = atomicAdd(a.next_query, 1u);
+        team_sync();
+        const uint32_t q = mail[0];
+        if (q >= a.nq) break;
+        {   // set-up by all 64 lanes
+            const float4* src = reinterpret_cast<const float4*>(a.tables + size_t(q) * table_floats);
+            float4* dst = reinterpret_cast<float4*>(table);
+            for (int i = tl; i < int(table_floats / 4); i += 64) dst[i] = __ldg(src + i);
+            if (a.rerank_k) {
+                const float* qv = a.queries + size_t(q) * a.dim;
+                for (int i = tl; i < int(dim_pad); i += 64) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
+            }
+            for (int p = tl; p < cap; p += 64) {
+                sd[p] = INFINITY;
+                sid[p] = kInvalidNode;
+            }
+            if (++epoch == 256) {  // the 8-bit epoch wraps: forget every earlier query
+                uint4* v4 = reinterpret_cast<uint4*>(vis);
+                for (uint64_t i = tl; i < a.vis_stride / 16; i += 64) v4[i] = make_uint4(0u, 0u, 0u, 0u);
+                epoch = 1;
+            }
+            if (tl < kSlots) mail[kKeyBase + tl] = kInvalidNode;
+        }
+        team_sync();
+
+        uint32_t nexp = 0, nevals = 0;
+        TierList T;  // the walker's W
+        T.d = sd;
+        T.id = sid;
+        T.nb = cap >> 5;
+        T.count = 0;
+        T.cur = 0;
+        T.wcap = scan_mode ? a.n_seed : beam;
+        T.wd = INFINITY;
+        T.wi = kInvalidNode;
+        T.head = 0;
+        T.max_d = INFINITY;
+        T.max_i = kInvalidNode;
+        uint32_t total_marks = 0;  // walker: nodes marked since the query began (ring write position)
+
+        // walker alone: visited test-and-set of one row, scoring, admission
+        // (search_engine.hpp:153-177); the marked ids go to the ring
+        auto offer = [&](uint32_t id, bool in_range) {
+            const uint32_t grp = __match_any_sync(kFull, id);
+            bool fresh = in_range && (__ffs(grp) - 1) == lane;
+            if (fresh) {
+                if (__ldcg(vis + id) == epoch) fresh = false;
+                else vis[id] = uint8_t(epoch);
+            }
+            uint32_t m = __ballot_sync(kFull, fresh);
+            if (fresh) ring[(total_marks + __popc(m & ((1u << lane) - 1u))) & (kRing - 1)] = id;
+            const int nf = __popc(m);
+            total_marks += nf;
+            nevals += nf;
+            if (nf == 0) return;
+            if (coop_ok && nf <= kCoopMax) {
+                uint32_t cid[kCoopMax], comp[kCoopMax];
+#pragma unroll
+                for (int f = 0; f < kCoopMax; ++f) {
+                    cid[f] = kInvalidNode;
+                    comp[f] = 0;
+                    if (f < nf) {
+                        const int src = __ffs(m) - 1;
+                        m &= m - 1;
+                        cid[f] = __shfl_sync(kFull, id, src);
+                        if (lane < a.K)
+                            comp[f] = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes, lane);
+                    }
+                }
+#pragma unroll
+                for (int f = 0; f < kCoopMax; ++f)
+                    if (f < nf) tier_admit(T, asym_distance_coop(table, a.K, a.P, comp[f], lane), cid[f], lane);
+            } else {
+                float dist = 0.0f;
+                if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
+                tier_admit_lanes(T, m, fresh, dist, id, lane);
+            }
+        };
+
+        if (scan_mode) {
+            // entry scan: the two warps take alternate batches and keep their own n_seed best
+            BeamList S;  // the scout's
+            S.d = seed_d;
+            S.id = seed_id;
+            S.count = 0;
+            S.cap = a.n_seed;
+            S.wd = INFINITY;
+            S.wi = kInvalidNode;
+            for (uint32_t e0 = 32u * role; e0 < a.n_entry; e0 += 64) {
+                const uint32_t e = e0 + lane;
+                if (e + 64 < a.n_entry) {
+                    prefetch_l1(a.entry + e + 64);
+                    prefetch_l1(static_cast<const unsigned char*>(a.entry_codes) + size_t(e + 64) * row_bytes);
+                }
+                const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
+                const bool ok = id < a.n;
+                float dist = 0.0f;
+                if (ok) dist = asym_distance_lane<U16>(table, a.entry_codes, e, a.K, a.P);
+                const uint32_t m = __ballot_sync(kFull, ok);
+                nevals += __popc(m);
+                if (role == 0) tier_admit_lanes(T, m, ok, dist, id, lane);
+                else beam_admit_lanes(S, m, ok, dist, id, lane);
+            }
+            if (role == 1 && lane == 0) {
+                mail[8] = nevals;
+                mail[9] = S.count;
+            }
+            team_sync();
+            if (role == 0) {
+                const uint32_t n1 = mail[9];
+                nevals += mail[8];
+                for (uint32_t i = 0; i < n1; ++i) tier_admit(T, seed_d[i], seed_id[i], lane);
+                // W now holds the seeds (within bucket (n_seed - 1) / 32 and before): bring it back
+                // to a flat list, fillers after the live members
+                const int wb = int(T.wcap - 1) >> 5;
+                for (int b = 0; b <= wb; ++b) {
+                    const int hb = __shfl_sync(kFull, T.head, b);
+                    const int from = b * 32 + ((hb + lane) & 31);
+                    float v = sd[from];
+                    uint32_t w = sid[from];
+                    if (uint32_t(b * 32 + lane) >= T.count) {
+                        v = INFINITY;
+                        w = kInvalidNode;
+                    }
+                    __syncwarp();
+                    sd[b * 32 + lane] = v;
+                    sid[b * 32 + lane] = w;
+                }
+                __syncwarp();
+                // the seeds are offered to the walk: mark them visited
+                const uint32_t nseeds = T.count;
+                nevals += nseeds;
+                for (uint32_t p = lane; p < nseeds; p += 32) vis[sid[p]] = uint8_t(epoch);
+                if (nseeds > beam) {  // a beam narrower than the seed set keeps the best `beam` seeds
+                    __syncwarp();
+                    for (uint32_t p = beam + lane; p < uint32_t(wb + 1) * 32; p += 32) {
+                        sd[p] = INFINITY;
+                        sid[p] = kInvalidNode;
+                    }
+                    T.count = beam;
+                }
+                __syncwarp();
+                T.wcap = beam;
+                T.cur = 0;
+                tier_reset_heads(T, lane);
+                tier_refresh_worst(T);
+            }
+        } else if (role == 0) {
+            for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
+                const uint32_t e = e0 + lane;
+                const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
+                offer(id, id < a.n);
+            }
+        }
+
+        // ---- walk
+        // Walker and scout meet at one barrier per expansion.  Before the barrier the walker selects
+        // the node to expand and announces it together with the next three unexpanded members of W;
+        // after it the walker consumes the prepared row of that node (if the scout has one) while the
+        // scout moves the announced nodes one stage further.
+        uint32_t rkey = kInvalidNode;  // scout: lane j < kSlots holds the node of result slot j
+        uint32_t c_key = kInvalidNode, c_id = kInvalidNode, c_mask = 0, c_snap = 0;  // scout: row with its visited bytes read
+        uint32_t step = 0;
+        while (true) {
+            volatile uint32_t* mb = mail + kPostBase + (step & 1) * 8;  // this step's announcement
+            if (role == 0) {
+                if (T.cur < T.count) {
+                    // closest member of W that has not been expanded (search_engine.hpp:121-123)
+                    const int cb = int(T.cur >> 5), cl = int(T.cur & 31);
+                    const int hb = __shfl_sync(kFull, T.head, cb);
+                    const int cslot = cb * 32 + ((hb + lane) & 31);
+                    uint32_t ei = sid[cslot];  // logical element `lane` of the cursor's bucket
+                    const uint32_t node = __shfl_sync(kFull, ei, cl) & kIdMask;
+                    if (lane == cl) sid[cslot] = ei | kExpanded;
+                    ++nexp;
+                    // the next unexpanded members: the first is the new cursor
+                    uint32_t base = uint32_t(cb) * 32;
+                    uint32_t un = __ballot_sync(kFull, !(ei & kExpanded) && lane > cl && base + lane < T.count);
+                    while (!un) {
+                        base += 32;
+                        if (base >= T.count) break;
+                        const int h2 = __shfl_sync(kFull, T.head, int(base >> 5));
+                        ei = sid[base + ((h2 + lane) & 31)];
+                        un = __ballot_sync(kFull, !(ei & kExpanded) && base + lane < T.count);
+                    }
+                    uint32_t p0 = kInvalidNode, p1 = kInvalidNode, p2 = kInvalidNode;
+                    T.cur = T.count;
+                    if (un) {
+                        int b = __ffs(un) - 1;
+                        T.cur = base + b;
+                        p0 = __shfl_sync(kFull, ei, b);
+                        un &= un - 1;
+                        if (un) {
+                            b = __ffs(un) - 1;
+                            p1 = __shfl_sync(kFull, ei, b);
+                            un &= un - 1;
+                            if (un) p2 = __shfl_sync(kFull, ei, __ffs(un) - 1);
+                        }
+                    }
+                    if (lane == 0) {
+                        mb[0] = node;
+                        mb[1] = p0;
+                        mb[2] = p1;
+                        mb[3] = p2;
+                        mb[4] = 0;
+                        mb[5] = total_marks;
+                    }
+                } else if (lane == 0) {
+                    mb[4] = 1;
+                }
+            }
+            team_sync();
+            if (mb[4]) break;
+            const uint32_t node = mb[0];
+            if (role == 0) {
+                // result slot of this node, if the scout got that far
+                uint32_t key = kInvalidNode;
+                if (lane < kSlots) key = mail[kKeyBase + lane];
+                const uint32_t match = __ballot_sync(kFull, key == node);
+                int s = match ? __ffs(match) - 1 : -1;
+                uint32_t snap = 0;
+                if (s >= 0) {
+                    snap = mail[kSnapBase + s];
+                    if (total_marks - snap > 32) s = -1;  // too many marks since the scout looked: do it here
+                }
+                if (s >= 0) {
+                    const uint32_t id = res_id[s * 32 + lane];
+                    const float dist = res_d[s * 32 + lane];
+                    bool fresh = (mail[kMaskBase + s] >> lane) & 1u;
+                    // neighbours marked since the scout read the visited bytes are no longer fresh
+                    const uint32_t cnt = total_marks - snap;
+                    const uint32_t rv = uint32_t(lane) < cnt ? ring[(snap + lane) & (kRing - 1)] : kInvalidNode;
+                    for (uint32_t j = 0; j < cnt; ++j)
+                        if (__shfl_sync(kFull, rv, int(j)) == id) fresh = false;
+                    if (fresh) vis[id] = uint8_t(epoch);
+                    const uint32_t fm = __ballot_sync(kFull, fresh);
+                    if (fresh) ring[(total_marks + __popc(fm & ((1u << lane) - 1u))) & (kRing - 1)] = id;
+                    total_marks += __popc(fm);
+                    nevals += __popc(fm);
+                    tier_admit_lanes(T, fm, fresh, dist, id, lane);
+                } else {
+                    const uint32_t id = lane < a.M ? __ldg(a.adj + size_t(node) * a.M + lane) : kInvalidNode;
+                    offer(id, id < a.n);
+                }
+            } else {
+                const uint32_t P0 = mb[1], P1 = mb[2], P2 = mb[3], snap = mb[5];
+                // stage 1: adjacency rows of the announced nodes towards L1
+                {
+                    const uint32_t p = lane == 0 ? P0 : lane == 1 ? P1 : lane == 2 ? P2 : kInvalidNode;
+                    if (p != kInvalidNode) {
+                        prefetch_l1(a.adj + size_t(p) * a.M);
+                        prefetch_l1(a.adj + size_t(p) * a.M + a.M - 1);
+                    }
+                }
+                auto in_r = [&](uint32_t x) { return __ballot_sync(kFull, rkey == x) != 0u; };
+                const bool c_wanted = c_key != kInvalidNode && (c_key == P0 || c_key == P1 || c_key == P2) && !in_r(c_key);
+                // stage 2, first half: the next announced node without results or visited bytes
+                // (P0 is selected at the next step; it is too late to start on it)
+                uint32_t target = kInvalidNode;
+                if (P1 != kInvalidNode && P1 != c_key && !in_r(P1)) target = P1;
+                else if (P2 != kInvalidNode && P2 != c_key && !in_r(P2)) target = P2;
+                uint32_t t_id = kInvalidNode, t_vis = 0;
+                bool t_first = false;
+                if (target != kInvalidNode) {
+                    t_id = lane < a.M ? __ldg(a.adj + size_t(target) * a.M + lane) : kInvalidNode;
+                    const uint32_t grp = __match_any_sync(kFull, t_id);
+                    t_first = t_id < a.n && (__ffs(grp) - 1) == lane;
+                    if (t_first) t_vis = __ldcg(vis + t_id);
+                }
+                // stage 3: score the row whose visited bytes were read during the previous step
+                if (c_wanted) {
+                    // a slot whose node is neither being consumed nor announced
+                    const bool keep = rkey != kInvalidNode && (rkey == node || rkey == P0 || rkey == P1 || rkey == P2);
+                    const uint32_t free_slots = __ballot_sync(kFull, lane < kSlots && !keep);
+                    const int s = __ffs(free_slots) - 1;  // at most three of the four are kept
+                    const bool cand = (c_mask >> lane) & 1u;
+                    const int nf = __popc(c_mask);
+                    float dist = 0.0f;
+                    if (coop_ok && nf <= kCoopMax) {
+                        uint32_t m = c_mask;
+                        for (int f = 0; f < nf; f += 2) {  // two candidates per round
+                            const int s0 = __ffs(m) - 1;
+                            m &= m - 1;
+                            const int s1 = m ? __ffs(m) - 1 : s0;
+                            m &= m - 1;
+                            const uint32_t id0 = __shfl_sync(kFull, c_id, s0), id1 = __shfl_sync(kFull, c_id, s1);
+                            uint32_t comp0 = 0, comp1 = 0;
+                            if (lane < a.K) {
+                                comp0 = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(id0) * row_bytes, lane);
+                                comp1 = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(id1) * row_bytes, lane);
+                            }
+                            const float d0 = asym_distance_coop(table, a.K, a.P, comp0, lane);
+                            const float d1 = asym_distance_coop(table, a.K, a.P, comp1, lane);
+                            if (lane == s0) dist = d0;
+                            if (lane == s1) dist = d1;
+                        }
+                    } else if (cand) {
+                        dist = asym_distance_lane<U16>(table, a.codes, c_id, a.K, a.P);
+                    }
+                    if (s >= 0) {
+                        res_id[s * 32 + lane] = c_id;
+                        res_d[s * 32 + lane] = dist;
+                        if (lane == 0) {
+                            mail[kMaskBase + s] = c_mask;
+                            mail[kSnapBase + s] = c_snap;
+                            mail[kKeyBase + s] = c_key;
+                        }
+                        if (lane == s) rkey = c_key;
+                    }
+                }
+                // stage 2, second half: codes of the unvisited neighbours towards L1
+                {
+                    const bool cand = t_first && t_vis != epoch;
+                    if (cand) {
+                        const unsigned char* row = static_cast<const unsigned char*>(a.codes) + size_t(t_id) * row_bytes;
+                        prefetch_l1(row);
+                        prefetch_l1(row + row_bytes - 1);
+                    }
+                    c_key = target;
+                    c_id = t_id;
+                    c_mask = __ballot_sync(kFull, cand);
+                    c_snap = snap;
+                }
+            }
+            ++step;
+        }
+
+        // ---- rerank (both warps) and output (walker)
+        if (role == 0) {
+            // back to a flat list, expanded flags dropped
+            const int nbl = int(T.count + 31) >> 5;
+            for (int b = 0; b < nbl; ++b) {
+                const int hb = __shfl_sync(kFull, T.head, b);
+                const int from = b * 32 + ((hb + lane) & 31);
+                const float v = sd[from];
+                const uint32_t w = sid[from];
+                __syncwarp();
+                sd[b * 32 + lane] = v;
+                sid[b * 32 + lane] = uint32_t(b * 32 + lane) < T.count ? (w & kIdMask) : kInvalidNode;
+            }
+            if (lane == 0) mail[10] = T.count;
+        }
+        team_sync();
+        const uint32_t count = mail[10];
+        int nsort = 32;
+        while (nsort < int(count)) nsort <<= 1;
+        uint32_t ncand = 0;
+        if (a.rerank_k) {
+            ncand = min(a.rerank_k, count);
+            const int g = lane >> 3, j = lane & 7;
+            const bool vec4 = (a.dim & 3) == 0;
+#pragma unroll 2
+            for (uint32_t c0 = 4u * role; c0 < ncand; c0 += 8) {
+                const uint32_t c = c0 + g;
+                float acc = 0.0f;
+                if (c < ncand) {
+                    const float* x = a.vectors + size_t(sid[c]) * a.dim;
+                    if (vec4) {
+                        for (int i = 4 * j; i < a.dim; i += 32) {
+                            const float4 xv = __ldg(reinterpret_cast<const float4*>(x + i));
+                            const float4 qv = *reinterpret_cast<const float4*>(qsm + i);
+                            acc = fmaf(xv.x, qv.x, acc);
+                            acc = fmaf(xv.y, qv.y, acc);
+                            acc = fmaf(xv.z, qv.z, acc);
+                            acc = fmaf(xv.w, qv.w, acc);
+                        }
+                    } else {
+                        for (int i = j; i < a.dim; i += 8) acc = fmaf(__ldg(x + i), qsm[i], acc);
+                    }
+                }
+                acc += __shfl_xor_sync(kFull, acc, 4);
+                acc += __shfl_xor_sync(kFull, acc, 2);
+                acc += __shfl_xor_sync(kFull, acc, 1);
+                if (c < ncand && j == 0) sd[c] = -acc;
+            }
+        }
+        team_sync();
+        if (role == 0) {
+            if (a.rerank_k) {
+                nsort = 32;
+                while (nsort < int(ncand)) nsort <<= 1;
+                for (int pos = int(ncand) + lane; pos < nsort; pos += 32) {
+                    sd[pos] = INFINITY;
+                    sid[pos] = kInvalidNode;
+                }
+                __syncwarp();
+                warp_sort_smem(sd, sid, nsort, lane);
+            }
+            uint32_t* oid = a.out_ids + size_t(q) * a.k;
+            float* od = a.out_dist + size_t(q) * a.k;
+            for (uint32_t pos = lane; pos < a.k; pos += 32) {
+                const bool have = pos < uint32_t(nsort) && sid[pos] != kInvalidNode;
+                oid[pos] = have ? sid[pos] : kInvalidNode;
+                od[pos] = have ? sd[pos] : INFINITY;
+            }
+            if (a.stats && lane == 0) {
+                a.stats[2 * size_t(q)] = nexp;
+                a.stats[2 * size_t(q) + 1] = nevals;
+            }
+        }
+        // the barrier at the top of the loop keeps the scout off the shared arrays until the
+        // walker is done with them
+    }
+    if (role == 0 && lane == 0) a.epochs[slot] = epoch;
+}
+
+}  // namespace
+
+// bytes of shared memory one team needs on top of the query table
+size_t search_team_extra_smem() { return size_t(kSeedCap) * 8 + kRing * 4 + kMailWords * 4; }
+
+// Teams per block: as many as shared memory allows (at most 15, one named barrier each), fewer if
+// the register file does not hold them.
+template <bool U16>
+static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st) {
+    auto kernel = search_team_kernel<U16>;
+    int teams = int((226 * 1024) / per_team);
+    if (teams > 15) teams = 15;
+    for (; teams >= 1; --teams) {
+        int blocks = 0;
+        CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(per_team * teams)));
+        CPB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, teams * 64, per_team * teams));
+        if (blocks >= 1) break;
+    }
+    if (teams < 1) {
+        set_error("search: no launch configuration fits the two-warp kernel");
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    kernel<<<unsigned(h->sm_count), teams * 64, per_team * teams, st>>>(a);
+    return 0;
+}
+
+int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st) {
+    a.per_warp_smem = uint32_t(per_team);
+    return h->comp_bytes == 2 ? launch_team_t<true>(h, a, per_team, st) : launch_team_t<false>(h, a, per_team, st);
+}
+
+}  // namespace cpb

@@ -159,9 +159,11 @@ def oracle_index(oracle, base, K, cb, M, knn_k, conv=2):
                                                      (3000, 96, 32, 1, 16, 4, 4), (3000, 96, 32, 1, 16, 333, 100),
                                                      (1500, 200, 16, 2, 32, 32, 8), (50, 128, 32, 1, 32, 4, 4),
                                                      (50, 128, 32, 1, 32, 50, 1)])
-def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan, seeds):
+@pytest.mark.parametrize("skernel", [1, 2])  # one warp per query, two warps per query
+def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan, seeds, skernel):
     base, q = synthetic.gaussian_mixture(n, 60, dim, max(2, n // 250), 0.3, n)
     idx = make_index(cp, dim, K, cb, M=M)
+    idx.set_param("search_kernel", skernel)
     idx.set_param("entry_scan", scan)
     idx.set_param("k_entry", seeds)
     idx.add_batch_parallel(base)
@@ -243,12 +245,37 @@ def test_errors_do_not_exit(cp):
     assert ids.shape == (2, 10)
 
 
-def test_visited_epoch_wraps_without_losing_exactness(cp, oracle):
+@pytest.mark.parametrize("skernel", [1, 2])
+def test_many_queries_match_oracle(cp, oracle, skernel):
+    """Enough queries on a graph large enough that every resident warp (or team of two warps) walks
+    many of them concurrently: ids, distances and the per-query expansion/evaluation counts are the
+    oracle's, whichever warp scored a neighbour."""
+    n, dim, K, M = 20000, 128, 32, 32
+    base, q = synthetic.gaussian_mixture(n, 3000, dim, 40, 0.3, 77)
+    idx = make_index(cp, dim, K, 1, M=M)
+    idx.set_param("search_kernel", skernel)
+    idx.set_param("entry_scan", 512)
+    idx.set_param("k_entry", 16)
+    idx.add_batch_parallel(base)
+    codes, adj = idx.codes(), idx.adjacency()
+    signs = oracle.sign_tables(dim, K, 42)
+    _, rot, _ = oracle.encode(q, K, 1, signs, 2, want_rotated=True)
+    for k, ef in ((10, 100), (10, 16)):
+        ids, dist, stats = idx.search_batch(q, k, ef, want_stats=True)
+        wi, wd, ws = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, k), k, want_stats=True, n_seed=16)
+        assert np.array_equal(ids, wi)
+        assert np.array_equal(dist, wd)
+        assert np.array_equal(stats, ws)
+
+
+@pytest.mark.parametrize("skernel", [1, 2])
+def test_visited_epoch_wraps_without_losing_exactness(cp, oracle, skernel):
     """Each warp stamps visited nodes with an 8-bit per-query epoch; far more than 255 queries per
     warp must keep returning exactly the oracle's answers (the stamp array is zeroed at the wrap)."""
     n, dim, K, M = 1500, 128, 32, 16
     base, q = synthetic.gaussian_mixture(n, 40, dim, 6, 0.3, 321)
     idx = make_index(cp, dim, K, 1, M=M)
+    idx.set_param("search_kernel", skernel)
     idx.set_param("entry_scan", 64)
     idx.set_param("k_entry", 4)
     idx.add_batch_parallel(base)
