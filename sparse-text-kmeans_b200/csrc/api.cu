@@ -118,6 +118,7 @@ int set_entry_ids(cphnsw_b200_index* h) {
     CPB_TRY(h->d_entry.reserve(s * 4 + 16));
     if (s) CPB_CUDA(cudaMemcpy(h->d_entry.p, ids.data(), s * 4, cudaMemcpyHostToDevice));
     CPB_TRY(gather_entry_codes(h, 0));
+    CPB_TRY(scan_adjacency_rows(h, 0));
     CPB_CUDA(cudaStreamSynchronize(0));
     return 0;
 }

@@ -92,6 +92,7 @@ struct cphnsw_b200_index {
     cpb::DevBuf d_vectors, d_codes, d_adj, d_entry, d_entry_codes;
     uint32_t n_entry = 0;
     uint64_t vis_stride = 0;  // bytes per warp slot of d_visited
+    int adj_rows_distinct = 0;  // no adjacency row lists a node twice (scan_adjacency_rows)
 
     // search scratch
     cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
@@ -137,6 +138,8 @@ int launch_merge_probes(cphnsw_b200_index* h, const uint32_t* d_ids, const float
                         uint32_t k, uint32_t* d_out_ids, float* d_out_dist, cudaStream_t st);
 // scratch the search kernel needs for an index of n nodes (visited bitsets, expansion lists)
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam);
+// looks for adjacency rows that list a node twice and sets h->adj_rows_distinct (after d_adj changes)
+int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st);
 // copies the codes of the entry ids into one contiguous buffer (after d_entry / d_codes change)
 int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st);
 

@@ -154,8 +154,11 @@ __global__ void search_kernel(SearchArgs a) {
         // `ahead()` runs once the visited marks of this row are made and its code loads issued
         auto offer = [&](uint32_t id, bool in_range, bool have_vis, uint32_t vbyte, auto&& ahead) {
             // a node listed twice in one row is offered once (the second copy would find it visited)
-            const uint32_t grp = __match_any_sync(kFull, id);
-            bool fresh = in_range && (__ffs(grp) - 1) == lane;
+            bool fresh = in_range;
+            if (!a.rows_distinct) {  // every lane takes part in the match, in range or not
+                const uint32_t grp = __match_any_sync(kFull, id);
+                fresh = fresh && (__ffs(grp) - 1) == lane;
+            }
             if (fresh) {
                 if (!have_vis) vbyte = __ldcg(vis + id);
                 if (vbyte == epoch) fresh = false;
@@ -370,6 +373,17 @@ __global__ void gather_rows_kernel(const unsigned char* __restrict__ src, int ro
     dst[i] = id < n ? src[uint64_t(id) * row_bytes + i % row_bytes] : 0;
 }
 
+// one warp per adjacency row (M <= 32): a valid id that appears twice raises the flag
+__global__ void adjacency_dup_kernel(const uint32_t* __restrict__ adj, uint64_t n, int M, uint32_t* __restrict__ flag) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t row = (uint64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= n) return;
+    const uint32_t id = lane < M ? adj[row * M + lane] : kInvalidNode;
+    const uint32_t grp = __match_any_sync(kFull, id);
+    const bool dup = id < n && (__ffs(grp) - 1) != lane;
+    if (__ballot_sync(kFull, dup) && lane == 0) atomicOr(flag, 1u);
+}
+
 struct LaunchCfg {
     uint32_t cap;
     int warps;
@@ -416,6 +430,22 @@ int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
         h->launches++;
         CPB_CUDA(cudaGetLastError());
     }
+    return 0;
+}
+
+int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st) {
+    h->adj_rows_distinct = 0;
+    if (h->n == 0 || h->M > 32 || !h->d_adj.p) return 0;  // wider rows: the search dedupes each batch of 32
+    uint32_t* flag = h->d_status.as<uint32_t>() + 2;
+    CPB_CUDA(cudaMemsetAsync(flag, 0, 4, st));
+    const uint64_t threads = h->n * 32;
+    adjacency_dup_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(h->d_adj.as<uint32_t>(), h->n, int(h->M), flag);
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    uint32_t dup = 1;
+    CPB_CUDA(cudaMemcpyAsync(&dup, flag, 4, cudaMemcpyDeviceToHost, st));
+    CPB_CUDA(cudaStreamSynchronize(st));
+    h->adj_rows_distinct = dup == 0;
     return 0;
 }
 
@@ -480,6 +510,7 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.out_dist = d_dists;
     a.stats = d_stats;
     a.next_query = h->d_status.as<uint32_t>() + 1;
+    a.rows_distinct = h->adj_rows_distinct;
     CPB_CUDA(cudaMemsetAsync(a.next_query, 0, 4, st));
     const unsigned grid = unsigned(h->sm_count);
     const bool u16 = h->comp_bytes == 2;

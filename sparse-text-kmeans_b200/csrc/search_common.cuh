@@ -38,10 +38,15 @@ struct SearchArgs {
     float* out_dist;
     uint32_t* stats;
     uint32_t* next_query;  // work counter, zero at launch
+    int rows_distinct;     // no adjacency row lists a node twice (checked when the adjacency is set)
 };
 
 __device__ __forceinline__ void prefetch_l1(const void* p) {
     asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 __device__ __forceinline__ bool key_less(float da, uint32_t ia, float db, uint32_t ib) {

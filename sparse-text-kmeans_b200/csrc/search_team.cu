@@ -284,8 +284,11 @@ __global__ void search_team_kernel(SearchArgs a) {
         // walker alone: visited test-and-set of one row, scoring, admission
         // (search_engine.hpp:153-177); the marked ids go to the ring
         auto offer = [&](uint32_t id, bool in_range) {
-            const uint32_t grp = __match_any_sync(kFull, id);
-            bool fresh = in_range && (__ffs(grp) - 1) == lane;
+            bool fresh = in_range;
+            if (!a.rows_distinct) {  // every lane takes part in the match, in range or not
+                const uint32_t grp = __match_any_sync(kFull, id);
+                fresh = fresh && (__ffs(grp) - 1) == lane;
+            }
             if (fresh) {
                 if (__ldcg(vis + id) == epoch) fresh = false;
                 else vis[id] = uint8_t(epoch);
@@ -402,7 +405,7 @@ __global__ void search_team_kernel(SearchArgs a) {
         // after it the walker consumes the prepared row of that node (if the scout has one) while the
         // scout moves the announced nodes one stage further.
         uint32_t rkey = kInvalidNode;  // scout: lane j < kSlots holds the node of result slot j
-        uint32_t c_key = kInvalidNode, c_id = kInvalidNode, c_mask = 0, c_snap = 0;  // scout: row with its visited bytes read
+        uint32_t held_key = kInvalidNode, held_id = kInvalidNode;  // scout: adjacency row loaded at the previous turn
         uint32_t step = 0;
         while (true) {
             volatile uint32_t* mb = mail + kPostBase + (step & 1) * 8;  // this step's announcement
@@ -487,46 +490,51 @@ __global__ void search_team_kernel(SearchArgs a) {
                 }
             } else {
                 const uint32_t P0 = mb[1], P1 = mb[2], P2 = mb[3], snap = mb[5];
-                // stage 1: adjacency rows of the announced nodes towards L1
-                {
-                    const uint32_t p = lane == 0 ? P0 : lane == 1 ? P1 : lane == 2 ? P2 : kInvalidNode;
-                    if (p != kInvalidNode) {
-                        prefetch_l1(a.adj + size_t(p) * a.M);
-                        prefetch_l1(a.adj + size_t(p) * a.M + a.M - 1);
-                    }
+                // adjacency row of the node three expansions away towards L2
+                if (lane == 0 && P2 != kInvalidNode) {
+                    prefetch_l2(a.adj + size_t(P2) * a.M);
+                    prefetch_l2(a.adj + size_t(P2) * a.M + a.M - 1);
                 }
                 auto in_r = [&](uint32_t x) { return __ballot_sync(kFull, rkey == x) != 0u; };
-                const bool c_wanted = c_key != kInvalidNode && (c_key == P0 || c_key == P1 || c_key == P2) && !in_r(c_key);
-                // stage 2, first half: the next announced node without results or visited bytes
-                // (P0 is selected at the next step; it is too late to start on it)
-                uint32_t target = kInvalidNode;
-                if (P1 != kInvalidNode && P1 != c_key && !in_r(P1)) target = P1;
-                else if (P2 != kInvalidNode && P2 != c_key && !in_r(P2)) target = P2;
-                uint32_t t_id = kInvalidNode, t_vis = 0;
-                bool t_first = false;
-                if (target != kInvalidNode) {
-                    t_id = lane < a.M ? __ldg(a.adj + size_t(target) * a.M + lane) : kInvalidNode;
-                    const uint32_t grp = __match_any_sync(kFull, t_id);
-                    t_first = t_id < a.n && (__ffs(grp) - 1) == lane;
-                    if (t_first) t_vis = __ldcg(vis + t_id);
+                const bool do_u = P0 != kInvalidNode && !in_r(P0);  // the node selected next: prepare it now
+                const bool do_v = P1 != kInvalidNode && !in_r(P1);  // the one after: bring its data closer
+                // the row of P1 is loaded now and kept for the next turn, when P1 has become P0
+                uint32_t u_id = kInvalidNode, v_id = kInvalidNode;
+                if (do_v) {
+                    if (held_key == P1) v_id = held_id;
+                    else if (lane < a.M) v_id = __ldg(a.adj + size_t(P1) * a.M + lane);
                 }
-                // stage 3: score the row whose visited bytes were read during the previous step
-                if (c_wanted) {
+                if (do_u) {
+                    if (held_key == P0) u_id = held_id;
+                    else if (lane < a.M) u_id = __ldg(a.adj + size_t(P0) * a.M + lane);
+                }
+                uint32_t u_vis = 0;
+                bool u_first = false;
+                if (do_u) {
+                    u_first = u_id < a.n;
+                    if (!a.rows_distinct) {
+                        const uint32_t grp = __match_any_sync(kFull, u_id);
+                        u_first = u_first && (__ffs(grp) - 1) == lane;
+                    }
+                    if (u_first) u_vis = __ldcg(vis + u_id);
+                }
+                if (do_u) {
                     // a slot whose node is neither being consumed nor announced
                     const bool keep = rkey != kInvalidNode && (rkey == node || rkey == P0 || rkey == P1 || rkey == P2);
                     const uint32_t free_slots = __ballot_sync(kFull, lane < kSlots && !keep);
                     const int s = __ffs(free_slots) - 1;  // at most three of the four are kept
-                    const bool cand = (c_mask >> lane) & 1u;
-                    const int nf = __popc(c_mask);
+                    const bool cand = u_first && u_vis != epoch;
+                    const uint32_t u_mask = __ballot_sync(kFull, cand);
+                    const int nf = __popc(u_mask);
                     float dist = 0.0f;
                     if (coop_ok && nf <= kCoopMax) {
-                        uint32_t m = c_mask;
+                        uint32_t m = u_mask;
                         for (int f = 0; f < nf; f += 2) {  // two candidates per round
                             const int s0 = __ffs(m) - 1;
                             m &= m - 1;
                             const int s1 = m ? __ffs(m) - 1 : s0;
                             m &= m - 1;
-                            const uint32_t id0 = __shfl_sync(kFull, c_id, s0), id1 = __shfl_sync(kFull, c_id, s1);
+                            const uint32_t id0 = __shfl_sync(kFull, u_id, s0), id1 = __shfl_sync(kFull, u_id, s1);
                             uint32_t comp0 = 0, comp1 = 0;
                             if (lane < a.K) {
                                 comp0 = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(id0) * row_bytes, lane);
@@ -538,31 +546,26 @@ __global__ void search_team_kernel(SearchArgs a) {
                             if (lane == s1) dist = d1;
                         }
                     } else if (cand) {
-                        dist = asym_distance_lane<U16>(table, a.codes, c_id, a.K, a.P);
+                        dist = asym_distance_lane<U16>(table, a.codes, u_id, a.K, a.P);
                     }
                     if (s >= 0) {
-                        res_id[s * 32 + lane] = c_id;
+                        res_id[s * 32 + lane] = u_id;
                         res_d[s * 32 + lane] = dist;
                         if (lane == 0) {
-                            mail[kMaskBase + s] = c_mask;
-                            mail[kSnapBase + s] = c_snap;
-                            mail[kKeyBase + s] = c_key;
+                            mail[kMaskBase + s] = u_mask;
+                            mail[kSnapBase + s] = snap;
+                            mail[kKeyBase + s] = P0;
                         }
-                        if (lane == s) rkey = c_key;
+                        if (lane == s) rkey = P0;
                     }
                 }
-                // stage 2, second half: codes of the unvisited neighbours towards L1
-                {
-                    const bool cand = t_first && t_vis != epoch;
-                    if (cand) {
-                        const unsigned char* row = static_cast<const unsigned char*>(a.codes) + size_t(t_id) * row_bytes;
-                        prefetch_l1(row);
-                        prefetch_l1(row + row_bytes - 1);
+                if (do_v) {  // visited bytes and codes of the next row towards L2
+                    if (v_id < a.n && held_key != P1) {
+                        prefetch_l2(vis + v_id);
+                        prefetch_l2(static_cast<const unsigned char*>(a.codes) + size_t(v_id) * row_bytes);
                     }
-                    c_key = target;
-                    c_id = t_id;
-                    c_mask = __ballot_sync(kFull, cand);
-                    c_snap = snap;
+                    held_key = P1;
+                    held_id = v_id;
                 }
             }
             ++step;

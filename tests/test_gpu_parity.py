@@ -269,6 +269,57 @@ def test_many_queries_match_oracle(cp, oracle, skernel):
 
 
 @pytest.mark.parametrize("skernel", [1, 2])
+def test_rows_with_repeated_neighbours_are_offered_once(cp, oracle, skernel):
+    """An adjacency installed from outside may list a node twice in a row (the graph builder never
+    does): each copy is offered once, as in the sequential walk."""
+    import torch
+    n, dim, K, M = 5000, 128, 32, 32
+    base, q = synthetic.gaussian_mixture(n, 200, dim, 20, 0.3, 13)
+    src = make_index(cp, dim, K, 1, M=M)
+    src.add_batch_parallel(base)
+    codes, adj = src.codes(), src.adjacency().copy()
+    rng = np.random.default_rng(3)
+    rows = rng.choice(n, n // 2, replace=False)
+    adj[rows, 1] = adj[rows, 0]                       # adjacent copies
+    adj[rows[: n // 4], 31] = adj[rows[: n // 4], 5]  # distant copies
+    adj[rows[: n // 8], 7] = INVALID                  # holes
+    idx = make_index(cp, dim, K, 1, M=M)
+    idx.set_param("search_kernel", skernel)
+    idx.set_param("entry_scan", 256)
+    idx.set_param("k_entry", 8)
+    dv, dc, da = (torch.from_numpy(x).cuda() for x in (base, codes, adj.view(np.int32)))
+    idx.install_dev(dv.data_ptr(), dc.data_ptr(), da.data_ptr(), n)
+    signs = oracle.sign_tables(dim, K, 42)
+    _, rot, _ = oracle.encode(q, K, 1, signs, 2, want_rotated=True)
+    ids, dist, stats = idx.search_batch(q, 10, 200, want_stats=True)
+    wi, wd, ws = oracle.search(rot, codes, adj, idx.entry_ids(), 200, 10, want_stats=True, n_seed=8)
+    assert np.array_equal(ids, wi) and np.array_equal(dist, wd) and np.array_equal(stats, ws)
+
+
+@pytest.mark.parametrize("reps", [1, 6000])
+def test_two_warp_kernel_wide_beam_on_small_graph(cp, oracle, reps):
+    """A beam of 1000 on an unclustered graph of 8000 nodes visits most of it; with many
+    repetitions every team of the two-warp kernel passes the wrap of its 8-bit visited epoch
+    several times."""
+    n, dim, K, M = 8000, 128, 32, 32
+    base, q = synthetic.gaussian_sphere(n, 40, dim, 5)
+    idx = make_index(cp, dim, K, 1, M=M)
+    idx.set_param("search_kernel", 2)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 4)
+    idx.add_batch_parallel(base)
+    codes, adj = idx.codes(), idx.adjacency()
+    signs = oracle.sign_tables(dim, K, 42)
+    _, rot, _ = oracle.encode(q, K, 1, signs, 2, want_rotated=True)
+    wi, wd, ws = oracle.search(rot, codes, adj, idx.entry_ids(), 1000, 10, want_stats=True, n_seed=4)
+    assert ws[:, 1].min() > 5000  # far more marks than any shared-memory set holds
+    ids, dist, stats = idx.search_batch(np.tile(q, (reps, 1)), 10, 1000, want_stats=True)
+    assert np.array_equal(ids.reshape(reps, 40, 10), np.broadcast_to(wi, (reps, 40, 10)))
+    assert np.array_equal(dist.reshape(reps, 40, 10), np.broadcast_to(wd, (reps, 40, 10)))
+    assert np.array_equal(stats.reshape(reps, 40, 2), np.broadcast_to(ws, (reps, 40, 2)))
+
+
+@pytest.mark.parametrize("skernel", [1, 2])
 def test_visited_epoch_wraps_without_losing_exactness(cp, oracle, skernel):
     """Each warp stamps visited nodes with an 8-bit per-query epoch; far more than 255 queries per
     warp must keep returning exactly the oracle's answers (the stamp array is zeroed at the wrap)."""
