@@ -29,10 +29,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "sparse-text-kmeans_b200"))
 
 METRIC = "batch-search QPS @ recall@10>=0.9 (search_and_rerank)"
-# DRAM bytes (read + written) per query of search_kernel, from the ncu capture summarised in
-# profiles/search_kernel_c2_quarter.md (C2 at 1/4 size, 2,500 queries: 1.215 GB + 0.080 GB per launch);
-# scaled to a launch by the number of queries it processes.
-NCU_SEARCH_DRAM_BYTES_PER_QUERY = 518e3
+# DRAM bytes (read + written) per query of search_team_kernel, from the ncu capture summarised in
+# profiles/search_team_kernel_c2_quarter.md (C2 at 1/4 size, 2,500 queries: 1.269 GB + 0.079 GB per launch);
+# the traffic per query does not depend on the number of queries, so a launch of nq queries moves nq times this
+NCU_SEARCH_DRAM_BYTES_PER_QUERY = 539e3
+# the same for the one-warp search_kernel (profiles/search_kernel_c2_quarter.md: 1.215 GB + 0.080 GB per launch)
+NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP = 518e3
 
 
 def parse_args():
@@ -47,6 +49,8 @@ def parse_args():
     ap.add_argument("--rerank-k", type=int, default=None)
     ap.add_argument("--entry-scan", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--search-kernel", type=int, default=0, choices=[0, 1, 2],
+                    help="0 = the library's choice, 1 = one warp per query, 2 = two warps per query")
     return ap.parse_args()
 
 
@@ -231,6 +235,7 @@ def run_b200(args):
     idx.set_param("entry_scan", w["entry_scan"])
     idx.set_param("k_entry", w.get("k_entry", 4))
     idx.set_param("profile", 1)
+    idx.set_param("search_kernel", args.search_kernel)
 
     # ---- build (sharded by row block), each stage timed with CUDA events, max over ranks ----
     rb, re = sharded.shard_range(n, rank, world)
@@ -370,9 +375,12 @@ def run_b200(args):
     peak, peak_kind = measured_peaks()
     search_ms_per_launch = search_ms / max(1, search_launches)
     achieved = bytes_per_query * nq / (search_ms_per_launch * 1e-3) / 1e9
-    roofline = {"kernel": "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    # the library takes the two-warp kernel when the query table fits shared memory and M <= 32
+    team = args.search_kernel != 1 and K * idx.padded_dim * 4 <= 32 * 1024 and M <= 32
+    dram_per_query = NCU_SEARCH_DRAM_BYTES_PER_QUERY if team else NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP
+    roofline = {"kernel": "search_team_kernel" if team else "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": "of " + peak_kind,
-                "traffic": NCU_SEARCH_DRAM_BYTES_PER_QUERY * nq if w["name"] == "C2" else None,
+                "traffic": dram_per_query * nq if w["name"] == "C2" else None,
                 "traffic_note": "bytes per launch, scaled by queries from the ncu capture of C2 at 1/4 size",
                 "ms_per_launch": search_ms_per_launch, "algorithmic_bytes_per_query": bytes_per_query,
                 "expansions_per_query": exp_mean, "distance_evals_per_query": evals_mean,

@@ -3,16 +3,19 @@
 //
 // The walker warp owns W and the visited marks and performs the expansions in the exact
 // sequential order.  The scout warp prepares rows ahead of it.  Before each expansion the walker
-// announces the node it expands and the next three unexpanded members of W; the scout moves each
-// announced node one stage further per step: adjacency row towards L1; visited bytes read and the
-// codes of the unvisited neighbours towards L1; neighbours scored against the query table (which
-// the two warps share in shared memory) into a result slot.  When the walker selects a node that
-// has a result slot, it drops the neighbours it has marked itself since the scout read the
-// visited bytes (a ring of its latest marks tells which), marks the rest and admits them: no
-// global load is left on its path.  Without a slot it does the expansion itself, as the one-warp
-// kernel does.  Scores are a pure function of (query, node) and the set of neighbours offered is
-// the set unvisited at the walker's own sequential time either way, so the results do not
-// depend on how far the scout got.
+// announces the node it expands and the next three unexpanded members of W.  During that
+// expansion the scout prepares the first of them, the node the walker will select next unless
+// this expansion admits something closer (about 3 % of the steps): it reads the visited bytes of
+// the node's neighbours, scores the unvisited ones against the query table (which the two warps
+// share in shared memory) and leaves ids, scores and a candidate mask in a result slot.  For the
+// second announced node it loads the adjacency row, which it keeps in registers for its next
+// turn, and asks for that row's visited bytes and codes to be brought into L2; the row of the third
+// goes towards L2 as well.  When the walker selects a node that has a result slot, it drops the
+// neighbours it has marked itself since the scout read the visited bytes (a ring of its latest
+// marks tells which), marks the rest and admits them: no global load is left on its path.
+// Without a slot it does the expansion itself, as the one-warp kernel does.  Scores are a pure
+// function of (query, node) and the set of neighbours offered is the set unvisited at the
+// walker's own sequential time either way, so the results do not depend on how far the scout got.
 //
 // W is a tiered vector: buckets of 32 slots, each a circular buffer, globally sorted.  An
 // admission shifts inside one bucket (one load, two shuffles and one store per lane) and every
