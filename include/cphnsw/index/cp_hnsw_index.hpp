@@ -160,6 +160,44 @@ public:
         return unpack(ids, d, nq, k);
     }
 
+    // ---- diagnostics (evaluation/eval_sift.cpp:266-283, evaluation/eval_main.cpp:52,128-189) -------
+    struct Calibration {  // exact distance ~ alpha * CP score + beta over sampled node pairs
+        float alpha = 1.0f, beta = 0.0f, r_squared = 0.0f;
+        size_t num_samples = 0;
+    };
+    std::vector<SearchResult> brute_force_search(const Float* q, size_t k) const {
+        std::vector<uint32_t> ids(k);
+        std::vector<float> d(k);
+        check(cphnsw_b200_brute_force_search_batch(h_, q, 1, uint32_t(k), ids.data(), d.data()));
+        return unpack(ids, d, 1, k)[0];
+    }
+    size_t verify_connectivity() const {
+        uint64_t r = 0;
+        check(cphnsw_b200_verify_connectivity(h_, &r));
+        return size_t(r);
+    }
+    Calibration calibrate(size_t num_samples = 1000, uint64_t seed = 42) {
+        check(cphnsw_b200_calibrate(h_, num_samples, seed, nullptr, nullptr, nullptr));
+        return get_calibration();
+    }
+    Calibration get_calibration() const {
+        double a = 1, b = 0, r = 0;
+        uint64_t m = 0;
+        check(cphnsw_b200_get_calibration(h_, &a, &b, &r, &m));
+        Calibration c;
+        c.alpha = float(a), c.beta = float(b), c.r_squared = float(r), c.num_samples = size_t(m);
+        return c;
+    }
+    std::vector<SearchResult> search_calibrated(const Float* q, size_t k, size_t ef) const {
+        return search_calibrated_and_rerank(q, k, ef, 0);
+    }
+    std::vector<SearchResult> search_calibrated_and_rerank(const Float* q, size_t k, size_t ef, size_t rerank_k) const {
+        std::vector<uint32_t> ids(k);
+        std::vector<float> d(k);
+        check(cphnsw_b200_search_calibrated_batch(h_, q, 1, uint32_t(k), uint32_t(ef), uint32_t(rerank_k), ids.data(), d.data()));
+        return unpack(ids, d, 1, k)[0];
+    }
+
     // ---- stages ---------------------------------------------------------------------------------
     std::vector<Code> encode(const Float* vecs, size_t n) const {
         std::vector<Code> out(n);

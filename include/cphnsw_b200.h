@@ -155,6 +155,33 @@ int cphnsw_b200_search_and_rerank_batch(cphnsw_b200_index* h, const float* q, ui
  * best k.  dists are code distances as floats.  num_probes * k <= 2048. */
 int cphnsw_b200_search_multiprobe_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                                         uint32_t ef, uint32_t num_probes, uint32_t* ids_out, float* dists_out);
+/* Diagnostics the reference's evaluation programs call around the hot path.  The legacy sources
+ * are absent; behaviour follows the call sites.
+ *
+ * Batched CPHNSWIndex::brute_force_search(q,k) (evaluation/eval_sift.cpp:283,329;
+ * evaluation/test_k_variants.cpp:79): the k (<= 1024) nodes with the smallest asymmetric CP score
+ * among all stored nodes, ascending by (score, id); no graph involved. */
+int cphnsw_b200_brute_force_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
+                                         uint32_t* ids_out, float* dists_out);
+/* CPHNSWIndex::verify_connectivity() (evaluation/eval_main.cpp:52, eval_sift.cpp:266): number of
+ * nodes reachable from the entry nodes along the directed adjacency, entry nodes included. */
+int cphnsw_b200_verify_connectivity(cphnsw_b200_index* h, uint64_t* reachable_out);
+/* CPHNSWIndex::calibrate(num_samples, seed) (evaluation/eval_main.cpp:128-135, qa_protocol.cpp:263-270):
+ * num_samples (1..65536) pairs (u,v) of stored nodes from std::mt19937_64(seed) (u = next() % n, then
+ * v = next() % n); least-squares fit  -<x_u,x_v> ~ alpha * score(u,v) + beta  of the exact distance
+ * against the asymmetric CP score, r_squared = squared correlation.  The fit is kept in the handle
+ * (get_calibration) and used by search_calibrated. */
+int cphnsw_b200_calibrate(cphnsw_b200_index* h, uint64_t num_samples, uint64_t seed, double* alpha_out,
+                          double* beta_out, double* r_squared_out);
+int cphnsw_b200_get_calibration(const cphnsw_b200_index* h, double* alpha_out, double* beta_out,
+                                double* r_squared_out, uint64_t* num_samples_out);
+/* Batched CPHNSWIndex::search_calibrated(q,k,ef) and search_calibrated_and_rerank(q,k,ef,rerank_k)
+ * (evaluation/eval_main.cpp:170,189): the walk of search / search_and_rerank; with rerank_k == 0
+ * the returned distances are alpha * score + beta (an estimate of the exact distance; alpha > 0
+ * keeps the order), with rerank_k > 0 they are the exact reranked distances. */
+int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
+                                        uint32_t ef, uint32_t rerank_k, uint32_t* ids_out, float* dists_out);
+
 /* The probe codes themselves, ComponentT[nq][num_probes][K], primary code first (legacy multiprobe.hpp). */
 int cphnsw_b200_probe_codes(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t num_probes,
                             void* codes_out);

@@ -532,6 +532,96 @@ int orc_ground_truth(const float* queries, uint64_t nq, const float* base, uint6
     return 0;
 }
 
+// Diagnostics of the legacy index.  Their sources are absent from the reference tree; the
+// behaviour is restated from the call sites.
+//
+// brute_force_search (evaluation/eval_sift.cpp:283,329; test_k_variants.cpp:79): the k nodes with
+// the smallest asymmetric CP score among all n, ascending by (score, id).
+int orc_brute_force(const float* tables /*[nq][K][P]*/, uint64_t nq, uint64_t K, uint64_t P, const void* codes,
+                    uint64_t comp_bytes, uint64_t n, uint64_t k, uint32_t* out_ids, float* out_dist) {
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t q = 0; q < (int64_t)nq; ++q) {
+        const float* table = tables + (size_t)q * K * P;
+        std::vector<Cand> best;
+        for (size_t i = 0; i < n; ++i) {
+            Cand c{asym_dist(table, K, P, codes, comp_bytes, i), (uint32_t)i};
+            if (best.size() == k && !(c < best.back())) continue;
+            best.insert(std::upper_bound(best.begin(), best.end(), c), c);
+            if (best.size() > k) best.pop_back();
+        }
+        for (size_t t = 0; t < k; ++t) {
+            out_ids[(size_t)q * k + t] = t < best.size() ? best[t].second : kInvalid;
+            out_dist[(size_t)q * k + t] = t < best.size() ? best[t].first : INFINITY;
+        }
+    }
+    return 0;
+}
+
+// calibrate(num_samples, seed) (evaluation/eval_main.cpp:128-135, qa_protocol.cpp:263-270): pairs
+// (u, v) of stored nodes drawn with std::mt19937_64(seed) (u = next() % n, then v = next() % n);
+// x = asymmetric CP score of v's code for u as the query, y = -<x_u, x_v> accumulated in d order
+// in fp32.  Outputs the pairs and the samples; the least-squares fit is orc_linear_fit.
+int orc_calibration_samples(const float* tables /*[num_samples][K][P] of the u vectors, in sample order*/,
+                            uint64_t K, uint64_t P, const void* codes, uint64_t comp_bytes, const float* base,
+                            uint64_t n, uint64_t dim, uint64_t num_samples, const uint32_t* u, const uint32_t* v,
+                            float* x, float* y) {
+#pragma omp parallel for schedule(static)
+    for (int64_t s = 0; s < (int64_t)num_samples; ++s) {
+        x[s] = asym_dist(tables + (size_t)s * K * P, K, P, codes, comp_bytes, v[s]);
+        float dot = 0.0f;
+        for (size_t d = 0; d < dim; ++d) dot += base[(size_t)u[s] * dim + d] * base[(size_t)v[s] * dim + d];
+        y[s] = -dot;
+    }
+    (void)n;
+    return 0;
+}
+
+int orc_calibration_pairs(uint64_t n, uint64_t num_samples, uint64_t seed, uint32_t* u, uint32_t* v) {
+    std::mt19937_64 rng(seed);
+    for (uint64_t s = 0; s < num_samples; ++s) {
+        u[s] = (uint32_t)(rng() % n);
+        v[s] = (uint32_t)(rng() % n);
+    }
+    return 0;
+}
+
+// y ~ alpha * x + beta by least squares in double; r_squared = squared correlation (0 when x or y
+// is constant).  out = {alpha, beta, r_squared}.
+int orc_linear_fit(const float* x, const float* y, uint64_t m, double* out) {
+    double sx = 0, sy = 0;
+    for (uint64_t i = 0; i < m; ++i) sx += x[i], sy += y[i];
+    const double mx = m ? sx / m : 0, my = m ? sy / m : 0;
+    double sxx = 0, sxy = 0, syy = 0;
+    for (uint64_t i = 0; i < m; ++i) {
+        const double dx = x[i] - mx, dy = y[i] - my;
+        sxx += dx * dx, sxy += dx * dy, syy += dy * dy;
+    }
+    const double alpha = sxx > 0 ? sxy / sxx : 0.0;
+    out[0] = alpha;
+    out[1] = my - alpha * mx;
+    out[2] = (sxx > 0 && syy > 0) ? (sxy * sxy) / (sxx * syy) : 0.0;
+    return 0;
+}
+
+// verify_connectivity() (evaluation/eval_main.cpp:52, eval_sift.cpp:266): number of nodes reachable
+// from the entry nodes along the directed adjacency (the entry nodes included).
+uint64_t orc_connectivity(const uint32_t* adj, uint64_t n, uint64_t M, const uint32_t* entry_ids, uint64_t n_entry) {
+    std::vector<uint8_t> seen(n, 0);
+    std::vector<uint32_t> stack;
+    uint64_t count = 0;
+    for (uint64_t e = 0; e < n_entry; ++e)
+        if (entry_ids[e] < n && !seen[entry_ids[e]]) seen[entry_ids[e]] = 1, stack.push_back(entry_ids[e]), ++count;
+    while (!stack.empty()) {
+        const uint32_t v = stack.back();
+        stack.pop_back();
+        for (uint64_t j = 0; j < M; ++j) {
+            const uint32_t w = adj[(size_t)v * M + j];
+            if (w < n && !seen[w]) seen[w] = 1, stack.push_back(w), ++count;
+        }
+    }
+    return count;
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -185,6 +185,56 @@ def ground_truth(queries, base, k):
     return ids
 
 
+def brute_force(rotated, codes, k):
+    """Exhaustive top-k by asymmetric CP score; rotated is float32 [nq][K][P]."""
+    rotated = np.ascontiguousarray(rotated, np.float32)
+    nq, K, P = rotated.shape
+    codes = np.ascontiguousarray(codes)
+    ids = np.empty((nq, k), np.uint32)
+    dist = np.empty((nq, k), np.float32)
+    lib().orc_brute_force(_ptr(rotated), C.c_uint64(nq), C.c_uint64(K), C.c_uint64(P), _ptr(codes),
+                          C.c_uint64(codes.dtype.itemsize), C.c_uint64(codes.shape[0]), C.c_uint64(k), _ptr(ids), _ptr(dist))
+    return ids, dist
+
+
+def calibration_pairs(n, num_samples, seed):
+    u = np.empty(num_samples, np.uint32)
+    v = np.empty(num_samples, np.uint32)
+    lib().orc_calibration_pairs(C.c_uint64(n), C.c_uint64(num_samples), C.c_uint64(seed), _ptr(u), _ptr(v))
+    return u, v
+
+
+def linear_fit(x, y):
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.ascontiguousarray(y, np.float32)
+    out = np.empty(3, np.float64)
+    lib().orc_linear_fit(_ptr(x), _ptr(y), C.c_uint64(x.size), _ptr(out))
+    return float(out[0]), float(out[1]), float(out[2])
+
+
+def calibrate(base, codes, signs, K, comp_bytes, convention, num_samples, seed):
+    """(alpha, beta, r_squared, x, y) of the legacy index's calibrate(num_samples, seed)."""
+    base = np.ascontiguousarray(base, np.float32)
+    codes = np.ascontiguousarray(codes)
+    n, dim = base.shape
+    u, v = calibration_pairs(n, num_samples, seed)
+    _, rot, _ = encode(base[u], K, comp_bytes, signs, convention, want_rotated=True)
+    x = np.empty(num_samples, np.float32)
+    y = np.empty(num_samples, np.float32)
+    lib().orc_calibration_samples(_ptr(rot), C.c_uint64(K), C.c_uint64(rot.shape[2]), _ptr(codes),
+                                  C.c_uint64(codes.dtype.itemsize), _ptr(base), C.c_uint64(n), C.c_uint64(dim),
+                                  C.c_uint64(num_samples), _ptr(u), _ptr(v), _ptr(x), _ptr(y))
+    return linear_fit(x, y) + (x, y)
+
+
+def connectivity(adj, entry_ids):
+    adj = np.ascontiguousarray(adj, np.uint32)
+    entry_ids = np.ascontiguousarray(entry_ids, np.uint32)
+    f = lib().orc_connectivity
+    f.restype = C.c_uint64
+    return int(f(_ptr(adj), C.c_uint64(adj.shape[0]), C.c_uint64(adj.shape[1]), _ptr(entry_ids), C.c_uint64(entry_ids.size)))
+
+
 def recall_at_k(found, truth, k):
     """|retrieved ∩ truth| / k averaged over queries (evaluation/metrics/recall.hpp:22-39)."""
     hits = 0

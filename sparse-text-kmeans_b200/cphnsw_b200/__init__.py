@@ -34,7 +34,8 @@ EXPORTS = [
     "cphnsw_b200_knn_graph_dev", "cphnsw_b200_select_neighbors_dev", "cphnsw_b200_install_dev",
     "cphnsw_b200_search_dev", "cphnsw_b200_check_device_status", "cphnsw_b200_launch_count",
     "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc", "cphnsw_b200_search_multiprobe_batch",
-    "cphnsw_b200_probe_codes",
+    "cphnsw_b200_probe_codes", "cphnsw_b200_brute_force_search_batch", "cphnsw_b200_verify_connectivity",
+    "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
 ]
 
 
@@ -261,6 +262,46 @@ class CPHNSWIndex:
         _check(self._lib.cphnsw_b200_search_and_rerank_batch(self._h, _p(q), _u64(nq), _u32(k), _u32(ef), _u32(rerank_k),
                                                              _p(ids), _p(dist), _p(stats)))
         return (ids, dist, stats) if want_stats else (ids, dist)
+
+    def brute_force_search_batch(self, q, k):
+        """The k nodes with the smallest asymmetric CP score among all stored nodes (no graph)."""
+        q = self._vecs(q)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        _check(self._lib.cphnsw_b200_brute_force_search_batch(self._h, _p(q), _u64(nq), _u32(k), _p(ids), _p(dist)))
+        return ids, dist
+
+    def brute_force_search(self, q, k):
+        ids, dist = self.brute_force_search_batch(np.asarray(q, np.float32)[None, :], k)
+        return [(int(i), float(d)) for i, d in zip(ids[0], dist[0]) if i != INVALID_NODE]
+
+    def verify_connectivity(self):
+        """Number of nodes reachable from the entry nodes along the directed adjacency."""
+        out = C.c_uint64()
+        _check(self._lib.cphnsw_b200_verify_connectivity(self._h, C.byref(out)))
+        return int(out.value)
+
+    def calibrate(self, num_samples=1000, seed=42):
+        """Least-squares fit of the exact distance against the CP score over sampled node pairs:
+        (alpha, beta, r_squared)."""
+        a, b, r = C.c_double(), C.c_double(), C.c_double()
+        _check(self._lib.cphnsw_b200_calibrate(self._h, _u64(num_samples), _u64(seed), C.byref(a), C.byref(b), C.byref(r)))
+        return a.value, b.value, r.value
+
+    def get_calibration(self):
+        a, b, r, m = C.c_double(), C.c_double(), C.c_double(), C.c_uint64()
+        _check(self._lib.cphnsw_b200_get_calibration(self._h, C.byref(a), C.byref(b), C.byref(r), C.byref(m)))
+        return a.value, b.value, r.value, int(m.value)
+
+    def search_calibrated_batch(self, q, k, ef, rerank_k=0):
+        q = self._vecs(q)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        _check(self._lib.cphnsw_b200_search_calibrated_batch(self._h, _p(q), _u64(nq), _u32(k), _u32(ef), _u32(rerank_k),
+                                                             _p(ids), _p(dist)))
+        return ids, dist
 
     def search_multiprobe_batch(self, q, k, ef, num_probes):
         q = self._vecs(q)

@@ -139,9 +139,10 @@ int build_graph(cphnsw_b200_index* h, cudaStream_t st) {
     return set_entry_ids(h);
 }
 
+// scan_only: brute_force_search (every node scored, no walk); calibrated: distances mapped through the fit
 int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t nq, uint32_t k, uint32_t ef,
               uint32_t rerank_k, uint32_t* ids, float* dists, uint32_t* stats, bool out_on_device,
-              cudaStream_t st) {
+              cudaStream_t st, int scan_only = 0, bool calibrated = false) {
     if (h->n == 0) {
         set_error("search on an empty index");
         return CPHNSW_B200_E_STATE;
@@ -191,7 +192,9 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
                 o_stats = h->d_stats.as<uint32_t>();
             }
         }
-        CPB_TRY(launch_search(h, dq, h->d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st));
+        CPB_TRY(launch_search(h, dq, h->d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st, nullptr,
+                              scan_only));
+        if (calibrated && rerank_k == 0) CPB_TRY(launch_affine(h, o_d, m * k, float(h->calib_alpha), float(h->calib_beta), st));
         if (!out_on_device) {
             CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, o_ids, m * k * 4, cudaMemcpyDeviceToHost, st));
             CPB_CUDA(cudaMemcpyAsync(dists + q0 * k, o_d, m * k * 4, cudaMemcpyDeviceToHost, st));
@@ -199,6 +202,58 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
             CPB_CUDA(cudaStreamSynchronize(st));
         }
     }
+    return 0;
+}
+
+int do_calibrate(cphnsw_b200_index* h, uint64_t num_samples, uint64_t seed) {
+    if (h->n == 0) {
+        set_error("calibrate on an empty index");
+        return CPHNSW_B200_E_STATE;
+    }
+    if (num_samples == 0 || num_samples > 65536) {
+        set_error("calibrate: num_samples must be in 1..65536");
+        return CPHNSW_B200_E_INVALID;
+    }
+    const uint32_t m = uint32_t(num_samples);
+    std::vector<uint32_t> uv(size_t(m) * 2);
+    std::mt19937_64 rng(seed);
+    for (uint32_t s = 0; s < m; ++s) {
+        uv[s] = uint32_t(rng() % h->n);
+        uv[m + s] = uint32_t(rng() % h->n);
+    }
+    cudaStream_t st = 0;
+    const size_t table_floats = size_t(h->K) * h->P;
+    CPB_TRY(h->s_in.reserve(size_t(m) * 8 + 16));       // u, v
+    CPB_TRY(h->s_out.reserve(size_t(m) * 8 + 16));      // x, y
+    CPB_TRY(h->d_q.reserve(size_t(m) * h->dim * 4));    // the u vectors
+    CPB_TRY(h->d_qtables.reserve(size_t(m) * table_floats * 4));
+    CPB_TRY(h->d_qcodes.reserve(size_t(m) * code_row_bytes(h) + 16));
+    uint32_t* d_u = h->s_in.as<uint32_t>();
+    uint32_t* d_v = d_u + m;
+    float* d_x = h->s_out.as<float>();
+    float* d_y = d_x + m;
+    CPB_CUDA(cudaMemcpyAsync(d_u, uv.data(), size_t(m) * 8, cudaMemcpyHostToDevice, st));
+    CPB_TRY(gather_rows(h, h->d_vectors.p, h->dim * 4, d_u, m, h->d_q.p, st));
+    CPB_TRY(launch_encode(h, h->d_q.as<float>(), m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
+    CPB_TRY(launch_calibration_samples(h, h->d_qtables.as<float>(), d_u, d_v, m, d_x, d_y, st));
+    std::vector<float> xy(size_t(m) * 2);
+    CPB_CUDA(cudaMemcpyAsync(xy.data(), d_x, size_t(m) * 8, cudaMemcpyDeviceToHost, st));
+    CPB_CUDA(cudaStreamSynchronize(st));
+    // least squares in double on the host: 2 * num_samples floats
+    const float* x = xy.data();
+    const float* y = x + m;
+    double sx = 0, sy = 0;
+    for (uint32_t i = 0; i < m; ++i) sx += x[i], sy += y[i];
+    const double mx = sx / m, my = sy / m;
+    double sxx = 0, sxy = 0, syy = 0;
+    for (uint32_t i = 0; i < m; ++i) {
+        const double dx = x[i] - mx, dy = y[i] - my;
+        sxx += dx * dx, sxy += dx * dy, syy += dy * dy;
+    }
+    h->calib_alpha = sxx > 0 ? sxy / sxx : 0.0;
+    h->calib_beta = my - h->calib_alpha * mx;
+    h->calib_r2 = (sxx > 0 && syy > 0) ? (sxy * sxy) / (sxx * syy) : 0.0;
+    h->calib_samples = m;
     return 0;
 }
 
@@ -530,6 +585,46 @@ int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, 
                            uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats, void* stream) {
     CPB_TRY(bind(h));
     return do_search(h, d_q, true, nq, k, ef, rerank_k, d_ids, d_dists, d_stats, true, (cudaStream_t)stream);
+}
+
+int cphnsw_b200_brute_force_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t* ids_out,
+                                         float* dists_out) {
+    CPB_TRY(bind(h));
+    return do_search(h, q, false, nq, k, k, 0, ids_out, dists_out, nullptr, false, 0, 1);
+}
+
+int cphnsw_b200_verify_connectivity(cphnsw_b200_index* h, uint64_t* reachable_out) {
+    CPB_TRY(bind(h));
+    if (!reachable_out) { set_error("verify_connectivity: null pointer"); return CPHNSW_B200_E_INVALID; }
+    *reachable_out = 0;
+    if (h->n == 0) return 0;
+    return launch_connectivity(h, reachable_out, 0);
+}
+
+int cphnsw_b200_calibrate(cphnsw_b200_index* h, uint64_t num_samples, uint64_t seed, double* alpha_out, double* beta_out,
+                          double* r_squared_out) {
+    CPB_TRY(bind(h));
+    CPB_TRY(do_calibrate(h, num_samples, seed));
+    if (alpha_out) *alpha_out = h->calib_alpha;
+    if (beta_out) *beta_out = h->calib_beta;
+    if (r_squared_out) *r_squared_out = h->calib_r2;
+    return 0;
+}
+
+int cphnsw_b200_get_calibration(const cphnsw_b200_index* h, double* alpha_out, double* beta_out, double* r_squared_out,
+                                uint64_t* num_samples_out) {
+    if (!h) { set_error("null index handle"); return CPHNSW_B200_E_INVALID; }
+    if (alpha_out) *alpha_out = h->calib_alpha;
+    if (beta_out) *beta_out = h->calib_beta;
+    if (r_squared_out) *r_squared_out = h->calib_r2;
+    if (num_samples_out) *num_samples_out = h->calib_samples;
+    return 0;
+}
+
+int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
+                                        uint32_t rerank_k, uint32_t* ids_out, float* dists_out) {
+    CPB_TRY(bind(h));
+    return do_search(h, q, false, nq, k, ef, rerank_k, ids_out, dists_out, nullptr, false, 0, 0, true);
 }
 
 // ---- host-pointer entry points -------------------------------------------------------------------------

@@ -93,6 +93,9 @@ struct cphnsw_b200_index {
     uint32_t n_entry = 0;
     uint64_t vis_stride = 0;  // bytes per warp slot of d_visited
     int adj_rows_distinct = 0;  // no adjacency row lists a node twice (scan_adjacency_rows)
+    // calibrate(): true distance ~ alpha * CP score + beta (identity until calibrate is called)
+    double calib_alpha = 1.0, calib_beta = 0.0, calib_r2 = 0.0;
+    uint64_t calib_samples = 0;
 
     // search scratch
     cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
@@ -130,7 +133,14 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
                             uint32_t* d_adj, cudaStream_t st);
 int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
-                  cudaStream_t st, const void* d_qcodes = nullptr);
+                  cudaStream_t st, const void* d_qcodes = nullptr, int scan_only = 0);
+int gather_rows(cphnsw_b200_index* h, const void* src, size_t row_bytes, const uint32_t* d_ids, uint32_t n_ids, void* dst,
+                cudaStream_t st);
+// diagnostics (diagnostics.cu)
+int launch_connectivity(cphnsw_b200_index* h, uint64_t* reachable, cudaStream_t st);
+int launch_calibration_samples(cphnsw_b200_index* h, const float* d_tables, const uint32_t* d_u, const uint32_t* d_v,
+                               uint32_t m, float* d_x, float* d_y, cudaStream_t st);
+int launch_affine(cphnsw_b200_index* h, float* d_dist, uint64_t n, float alpha, float beta, cudaStream_t st);
 // multiprobe sequence of rotated queries [nq][K][P] -> probe codes [nq][T][K]; merge of per-probe results
 int launch_probe_codes(cphnsw_b200_index* h, const float* d_rotated, uint64_t nq, uint32_t T, void* d_out,
                        cudaStream_t st);

@@ -53,7 +53,7 @@ __global__ void search_kernel(SearchArgs a) {
     uint8_t* vis = a.visited + size_t(gwarp) * a.vis_stride;
     uint32_t epoch = a.epochs[gwarp];  // 1..255; 0 marks "never visited"
     const uint32_t beam = a.beam;
-    const bool scan_mode = a.n_seed < a.n_entry;
+    const bool scan_mode = a.scan_only || a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
     const bool coop_ok = !SYM && a.K <= 32;
     const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm);  // symmetric metric only
@@ -214,10 +214,10 @@ __global__ void search_kernel(SearchArgs a) {
             for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {
                 const uint32_t e = e0 + lane;
                 if (e + 32 < a.n_entry) {  // pull the next batch towards L1 while this one is scored
-                    prefetch_l1(a.entry + e + 32);
+                    if (a.entry) prefetch_l1(a.entry + e + 32);
                     prefetch_l1(static_cast<const unsigned char*>(a.entry_codes) + size_t(e + 32) * row_bytes);
                 }
-                const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
+                const uint32_t id = e < a.n_entry ? (a.entry ? __ldg(a.entry + e) : e) : kInvalidNode;
                 const bool ok = id < a.n;
                 float dist = 0.0f;
                 if (ok) dist = score_lane(a.entry_codes, e);
@@ -230,6 +230,9 @@ __global__ void search_kernel(SearchArgs a) {
                     try_admit(__shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src));
                 }
             }
+            if (a.scan_only) {
+                cur = count;  // nothing to expand: the best of the scan are the result
+            } else {
             // the seeds are now offered to the walk: mark them visited
             const uint32_t nseeds = count;
             nevals += nseeds;
@@ -248,6 +251,7 @@ __global__ void search_kernel(SearchArgs a) {
             if (count == wcap) {
                 wd = sd[wcap - 1];
                 wi = sid[wcap - 1] & kIdMask;
+            }
             }
         } else {
             for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
@@ -433,6 +437,18 @@ int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
     return 0;
 }
 
+// dst[i] = row ids[i] of src (rows of row_bytes bytes; ids >= n give zero rows)
+int gather_rows(cphnsw_b200_index* h, const void* src, size_t row_bytes, const uint32_t* d_ids, uint32_t n_ids, void* dst,
+                cudaStream_t st) {
+    const uint64_t total = uint64_t(n_ids) * row_bytes;
+    if (total == 0) return 0;
+    gather_rows_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(static_cast<const unsigned char*>(src), int(row_bytes),
+                                                                     d_ids, n_ids, h->n, static_cast<unsigned char*>(dst));
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st) {
     h->adj_rows_distinct = 0;
     if (h->n == 0 || h->M > 32 || !h->d_adj.p) return 0;  // wider rows: the search dedupes each batch of 32
@@ -466,7 +482,7 @@ int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
 
 int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
-                  cudaStream_t st, const void* d_qcodes) {
+                  cudaStream_t st, const void* d_qcodes, int scan_only) {
     const bool sym = d_qcodes != nullptr;  // symmetric code-distance walk (search_multiprobe)
     if (nq == 0) return 0;
     if (beam > 1024) {
@@ -511,13 +527,20 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.stats = d_stats;
     a.next_query = h->d_status.as<uint32_t>() + 1;
     a.rows_distinct = h->adj_rows_distinct;
+    a.scan_only = scan_only;
+    if (scan_only) {  // every node is an "entry", read from the code array itself; the k best are the result
+        a.entry = nullptr;
+        a.entry_codes = h->d_codes.p;
+        a.n_entry = uint32_t(h->n);
+        a.n_seed = k;
+    }
     CPB_CUDA(cudaMemsetAsync(a.next_query, 0, 4, st));
     const unsigned grid = unsigned(h->sm_count);
     const bool u16 = h->comp_bytes == 2;
     LaunchTimer timer(h, kKernelSearch, st);
 
     // two warps per query: asymmetric metric, table in shared memory, one adjacency row per warp
-    const bool team_ok = !sym && c.table_smem && h->M <= 32 && h->k_entry <= 128;
+    const bool team_ok = !sym && !scan_only && c.table_smem && h->M <= 32 && h->k_entry <= 128;
     if (h->search_kernel == 2 && !team_ok && !sym) {
         set_error("search_kernel=2 needs the asymmetric metric, K*P*4 <= 32 KB and M <= 32");
         return CPHNSW_B200_E_UNSUPPORTED;

@@ -39,6 +39,7 @@ struct SearchArgs {
     uint32_t* stats;
     uint32_t* next_query;  // work counter, zero at launch
     int rows_distinct;     // no adjacency row lists a node twice (checked when the adjacency is set)
+    int scan_only;         // brute_force_search: score all n nodes (entry == nullptr: ids 0..n-1), keep the n_seed best, no walk
 };
 
 __device__ __forceinline__ void prefetch_l1(const void* p) {

@@ -153,6 +153,30 @@ int main() {
         }
         CHECK(ok, "search_multiprobe returns ascending code distances and improves with probes");
     }
+    // diagnostics: connectivity (eval_main.cpp:52), brute force by CP score (eval_sift.cpp:283),
+    // calibration sign (qa_protocol.cpp:263-282) and calibrated search (eval_main.cpp:170-189)
+    {
+        const size_t reach = index.verify_connectivity();
+        CHECK(reach > n * 9 / 10 && reach <= n, "verify_connectivity reaches (nearly) every node");
+        auto bf = index.brute_force_search(base.data() + 7 * dim, 10);
+        bool asc = bf.size() == 10 && bf[0].id == 7;
+        for (size_t t = 1; t < bf.size(); ++t) asc &= bf[t - 1].distance <= bf[t].distance;
+        CHECK(asc, "brute_force_search finds the stored vector first, ascending scores");
+        auto calib = index.calibrate(1000);
+        CHECK(calib.alpha > 0 && calib.r_squared > 0.3f && calib.num_samples == 1000, "calibrate: alpha > 0 (positive correlation)");
+        auto plain = index.search(base.data() + 7 * dim, 10, 100);
+        auto cal = index.search_calibrated(base.data() + 7 * dim, 10, 100);
+        bool same = plain.size() == cal.size();
+        for (size_t t = 0; same && t < plain.size(); ++t)
+            same &= plain[t].id == cal[t].id && std::fabs(cal[t].distance - (calib.alpha * plain[t].distance + calib.beta)) < 1e-4f;
+        CHECK(same, "search_calibrated returns the ids of search with distances alpha * score + beta");
+        CHECK(cal[0].distance < -0.5f, "calibrated distance of a stored vector to itself is near -1");
+        auto rr = index.search_and_rerank(base.data() + 7 * dim, 10, 100, 50);
+        auto crr = index.search_calibrated_and_rerank(base.data() + 7 * dim, 10, 100, 50);
+        bool eq = rr.size() == crr.size();
+        for (size_t t = 0; eq && t < rr.size(); ++t) eq &= rr[t] == crr[t];
+        CHECK(eq, "search_calibrated_and_rerank equals search_and_rerank");
+    }
     // edge cases (qa_protocol.cpp:409-553): tiny index, duplicates, zero vector
     {
         CPHNSWIndex<uint8_t, 32> tiny(dim, 32, 200);

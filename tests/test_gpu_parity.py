@@ -374,3 +374,75 @@ def test_search_multiprobe_matches_oracle(cp, oracle, n, dim, K, cb, M, T, k, ef
         idx.search_multiprobe_batch(q, k, ef, 0)
     with pytest.raises(ValueError):
         idx.search_multiprobe_batch(q, 100, 100, 64)  # num_probes * k too large
+
+
+# ---- diagnostics around the hot path ---------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,dim,K,cb,k", [(3000, 128, 32, 1, 10), (3000, 128, 32, 1, 100), (700, 200, 16, 2, 37),
+                                          (50, 128, 32, 1, 64), (2500, 960, 16, 2, 5)])
+def test_brute_force_search_matches_oracle(cp, oracle, n, dim, K, cb, k):
+    base, q = synthetic.gaussian_mixture(n, 30, dim, max(2, n // 300), 0.3, n + k)
+    idx = make_index(cp, dim, K, cb)
+    idx.add_batch_parallel(base)
+    signs = oracle.sign_tables(dim, K, 42)
+    _, rot, _ = oracle.encode(q, K, cb, signs, 2, want_rotated=True)
+    ids, dist = idx.brute_force_search_batch(q, k)
+    wi, wd = oracle.brute_force(rot, idx.codes(), k)
+    assert np.array_equal(ids, wi) and np.array_equal(dist, wd)  # k > n: padded with invalid / +inf on both sides
+    assert idx.brute_force_search(q[0], k)[0][0] == int(wi[0, 0])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,M,scan", [(4000, 32, 64), (4000, 8, 1), (300, 4, 2), (1, 32, 4)])
+def test_verify_connectivity_matches_oracle(cp, oracle, n, M, scan):
+    base, _ = synthetic.gaussian_mixture(n, 1, 128, max(2, n // 100), 0.1, 5 * n + M)  # tight clusters: islands at small M
+    idx = make_index(cp, 128, M=M)
+    idx.set_param("entry_scan", scan)
+    idx.set_param("k_entry", 1)
+    idx.add_batch_parallel(base)
+    want = oracle.connectivity(idx.adjacency(), idx.entry_ids())
+    assert idx.verify_connectivity() == want
+    assert 1 <= want <= n
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,K,cb,m,seed", [(128, 32, 1, 1000, 42), (128, 32, 1, 1, 7), (200, 16, 2, 4096, 1), (64, 8, 1, 333, 99)])
+def test_calibrate_matches_oracle(cp, oracle, dim, K, cb, m, seed):
+    n = 3000
+    base, q = synthetic.gaussian_mixture(n, 50, dim, 10, 0.3, dim + K)
+    idx = make_index(cp, dim, K, cb)
+    idx.add_batch_parallel(base)
+    alpha, beta, r2 = idx.calibrate(m, seed)
+    wa, wb, wr, x, y = oracle.calibrate(base, idx.codes(), oracle.sign_tables(dim, K, 42), K, cb, 2, m, seed)
+    # samples are bit-exact (same add order on both sides), so the double-precision fits agree to rounding
+    assert np.isclose(alpha, wa, rtol=1e-9, atol=1e-12) and np.isclose(beta, wb, rtol=1e-9, atol=1e-12)
+    assert np.isclose(r2, wr, rtol=1e-9, atol=1e-12)
+    assert idx.get_calibration() == (alpha, beta, r2, m)
+    if m >= 333:
+        assert alpha > 0 and r2 > 0.2  # the score is positively correlated with the exact distance
+    # search_calibrated: ids of search, distances mapped through the fit in fp32
+    ids, dist = idx.search_batch(q, 10, 50)
+    cids, cdist = idx.search_calibrated_batch(q, 10, 50)
+    assert np.array_equal(ids, cids)
+    want = np.float32(alpha) * dist + np.float32(beta)
+    assert np.array_equal(cdist, want.astype(np.float32))
+    # with a rerank the distances are the exact ones
+    rids, rdist = idx.search_and_rerank_batch(q, 10, 50, 30)
+    crids, crdist = idx.search_calibrated_batch(q, 10, 50, 30)
+    assert np.array_equal(rids, crids) and np.array_equal(rdist, crdist)
+
+
+@pytest.mark.gpu
+def test_diagnostics_errors(cp):
+    idx = make_index(cp, 128)
+    with pytest.raises(cp.CPHNSWError):
+        idx.calibrate(100)  # empty index
+    assert idx.verify_connectivity() == 0
+    base, _ = synthetic.gaussian_sphere(200, 1, 128, 3)
+    idx.add_batch_parallel(base)
+    with pytest.raises((cp.CPHNSWError, ValueError)):
+        idx.calibrate(0)
+    with pytest.raises((cp.CPHNSWError, ValueError)):
+        idx.brute_force_search_batch(base[:2], 5000)
+    assert idx.get_calibration() == (1.0, 0.0, 0.0, 0)
+

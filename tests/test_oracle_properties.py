@@ -214,3 +214,58 @@ def test_multiprobe_merge_and_monotone_recall(oracle):
         assert len(set(valid.tolist())) == len(valid)  # every id once
     # distances are code distances to SOME probe, so they can only improve on the single-probe answer
     assert (many_d[:, 0] <= one_d[:, 0]).all()
+
+
+# ---- diagnostics ------------------------------------------------------------------------------------------
+def test_brute_force_is_the_sorted_prefix_of_all_scores(oracle):
+    rng = np.random.default_rng(5)
+    base = rng.standard_normal((400, 64)).astype(np.float32)
+    q = rng.standard_normal((6, 64)).astype(np.float32)
+    signs = oracle.sign_tables(64, 16, 42)
+    codes = oracle.encode(base, 16, 1, signs, 2)
+    _, rot, _ = oracle.encode(q, 16, 1, signs, 2, want_rotated=True)
+    ids, dist = oracle.brute_force(rot, codes, 400)  # everything, ascending by (score, id)
+    assert all(sorted(r.tolist()) == list(range(400)) for r in ids)
+    key = [list(zip(d.tolist(), i.tolist())) for d, i in zip(dist, ids)]
+    assert all(k == sorted(k) for k in key)
+    top, _ = oracle.brute_force(rot, codes, 7)
+    assert np.array_equal(top, ids[:, :7])
+    over, od = oracle.brute_force(rot, codes[:3], 5)  # k > n pads
+    assert (over[:, 3:] == 0xFFFFFFFF).all() and np.isinf(od[:, 3:]).all()
+
+
+def test_linear_fit_and_calibration_pairs(oracle):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal(500).astype(np.float32)
+    y = (0.37 * x - 1.25 + 0.05 * rng.standard_normal(500)).astype(np.float32)
+    a, b, r2 = oracle.linear_fit(x, y)
+    pa, pb = np.polyfit(x.astype(np.float64), y.astype(np.float64), 1)
+    assert np.isclose(a, pa, rtol=1e-9) and np.isclose(b, pb, rtol=1e-9)
+    assert np.isclose(r2, np.corrcoef(x, y)[0, 1] ** 2, rtol=1e-9)
+    assert oracle.linear_fit(np.ones(10, np.float32), y[:10]) == (0.0, float(np.float64(y[:10].astype(np.float64).mean())), 0.0)
+    u, v = oracle.calibration_pairs(1000, 64, 42)
+    u2, v2 = oracle.calibration_pairs(1000, 64, 42)
+    assert np.array_equal(u, u2) and np.array_equal(v, v2) and u.max() < 1000 and v.max() < 1000
+    assert not np.array_equal(u, oracle.calibration_pairs(1000, 64, 43)[0])
+
+
+def test_calibration_has_positive_slope_on_clustered_data(oracle):
+    rng = np.random.default_rng(1)
+    centres = rng.standard_normal((8, 128)).astype(np.float32)
+    base = centres[rng.integers(0, 8, 1500)] + 0.3 * rng.standard_normal((1500, 128)).astype(np.float32)
+    base /= np.linalg.norm(base, axis=1, keepdims=True)
+    signs = oracle.sign_tables(128, 32, 42)
+    codes = oracle.encode(base, 32, 1, signs, 2)
+    a, b, r2, x, y = oracle.calibrate(base, codes, signs, 32, 1, 2, 1000, 42)
+    assert a > 0 and r2 > 0.5 and x.shape == (1000,) and (y >= -1.0001).all() and (y <= 1.0001).all()
+
+
+def test_connectivity_counts_reachable_nodes(oracle):
+    inv = 0xFFFFFFFF
+    adj = np.array([[1, inv], [2, 0], [inv, inv], [4, inv], [3, 3], [0, inv]], np.uint32)  # {0,1,2} <- 5, {3,4} island
+    assert oracle.connectivity(adj, np.array([0], np.uint32)) == 3
+    assert oracle.connectivity(adj, np.array([5], np.uint32)) == 4
+    assert oracle.connectivity(adj, np.array([3, 0, 0], np.uint32)) == 5
+    assert oracle.connectivity(adj, np.array([], np.uint32)) == 0
+    assert oracle.connectivity(adj, np.array([2, inv], np.uint32)) == 1
+
