@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--rerank-k", type=int, default=None)
     ap.add_argument("--entry-scan", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fvecs", nargs=2, metavar=("BASE", "QUERY"), default=None,
+                    help="run on fvecs files (rows are normalised) instead of a synthetic workload")
     ap.add_argument("--search-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="0 = the library's choice, 1 = one warp per query, 2 = two warps per query")
     return ap.parse_args()
@@ -223,7 +225,10 @@ def run_b200(args):
 
     # weak scaling of the search: every rank answers its own batch of queries (an independent stream
     # of the same distribution) against the replicated index
-    w = overrides(synthetic.workload(args.workload, args.scale, query_stream=rank), args)
+    if args.fvecs:
+        w = overrides(synthetic.workload_from_files(args.fvecs[0], args.fvecs[1], rank=rank, world=world), args)
+    else:
+        w = overrides(synthetic.workload(args.workload, args.scale, query_stream=rank), args)
     base, K, cb, M, dim = w["base"], w["K"], w["component_bytes"], w["M"], w["base"].shape[1]
     n = base.shape[0]
     queries = w["queries"]
@@ -403,7 +408,7 @@ def run_b200(args):
         line = {
             "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
+            "data": "files" if args.fvecs else "synthetic",
             "config": {"workload": w["name"], "n_base": n, "dim": dim, "queries_per_rank": nq, "k": k, "ef": ef,
                        "rerank_k": rerank_k, "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry, "k_entry": w.get("k_entry", 4), "knn_k": knn_k,
                        "l2": "index (vectors+codes+adjacency = %.0f MB) larger than L2" % (n * (dim * 4 + code_row + M * 4) / 1e6)},

@@ -110,6 +110,22 @@ public:
     ~CPHNSWIndex() { cphnsw_b200_destroy(h_); }
     CPHNSWIndex(const CPHNSWIndex&) = delete;
     CPHNSWIndex& operator=(const CPHNSWIndex&) = delete;
+    CPHNSWIndex(CPHNSWIndex&& o) noexcept : h_(o.h_) { o.h_ = nullptr; }
+
+    // ---- index file (the reference has no save/load) ---------------------------------------------
+    void save(const std::string& path) const { check(cphnsw_b200_save(h_, path.c_str())); }
+    static CPHNSWIndex load(const std::string& path, int device = 0) {
+        cphnsw_b200_index* h = nullptr;
+        check(cphnsw_b200_load(path.c_str(), device, &h));
+        double k = 0, cb = 0;
+        cphnsw_b200_get_param(h, "K", &k);
+        cphnsw_b200_get_param(h, "component_bytes", &cb);
+        if (size_t(k) != K || size_t(cb) != sizeof(ComponentT)) {
+            cphnsw_b200_destroy(h);
+            throw std::invalid_argument("index file holds another code type than this CPHNSWIndex<ComponentT,K>");
+        }
+        return CPHNSWIndex(h, Adopt{});
+    }
 
     cphnsw_b200_index* handle() const { return h_; }
     void set_param(const char* name, double v) { check(cphnsw_b200_set_param(h_, name, v)); }
@@ -228,6 +244,8 @@ public:
     }
 
 private:
+    struct Adopt {};
+    CPHNSWIndex(cphnsw_b200_index* h, Adopt) : h_(h) {}
     cphnsw_b200_index* h_ = nullptr;
 
     static void check(int rc) {

@@ -182,6 +182,15 @@ int cphnsw_b200_get_calibration(const cphnsw_b200_index* h, double* alpha_out, d
 int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                                         uint32_t ef, uint32_t rerank_k, uint32_t* ids_out, float* dists_out);
 
+/* Index file (the reference has no save/load, SURVEY of its tree: rotation.hpp's get_signs() exists "for
+ * serialization" only).  One little-endian file: magic "CPHNSWB2", format version, the constructor
+ * arguments, the tunables, the calibration, then sign tables int8[K][3][padded_dim], vectors
+ * float[n][dim], codes ComponentT[n][K], adjacency uint32[n][M].  load creates a new handle on `device`
+ * holding exactly the saved index (no re-encoding, no graph rebuild); it can be searched at once and
+ * extended with add_batch_parallel. */
+int cphnsw_b200_save(cphnsw_b200_index* h, const char* path);
+int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out);
+
 /* The probe codes themselves, ComponentT[nq][num_probes][K], primary code first (legacy multiprobe.hpp). */
 int cphnsw_b200_probe_codes(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t num_probes,
                             void* codes_out);

@@ -19,6 +19,10 @@
 #include "cphnsw/encoder/cp_encoder.hpp"
 #include "cphnsw/encoder/rotation.hpp"
 #include "cphnsw/encoder/transform/fht.hpp"
+#ifdef CPHNSW_REF_EVAL_DIR
+// the reference's dataset readers (evaluation/datasets/dataset_loader.hpp), included in place
+#include "datasets/dataset_loader.hpp"
+#endif
 
 extern "C" {
 
@@ -102,3 +106,40 @@ int ref_encode_batch_signbits32(const float* x, uint64_t n, uint64_t dim, uint64
 }
 
 }  // extern "C"
+
+#ifdef CPHNSW_REF_EVAL_DIR
+extern "C" {
+
+// the reference's load_fvecs / load_ivecs / normalize_vectors; out may be null to query the shape
+int ref_load_fvecs(const char* path, float* out, uint64_t cap, uint64_t* dim, uint64_t* count) {
+    try {
+        size_t d = 0, c = 0;
+        auto v = cphnsw::eval::load_fvecs(path, d, c);
+        *dim = d, *count = c;
+        if (out && v.size() <= cap) std::memcpy(out, v.data(), v.size() * sizeof(float));
+        return 0;
+    } catch (const std::exception&) {
+        return -1;
+    }
+}
+
+int ref_load_ivecs(const char* path, uint32_t* out, uint64_t cap, uint64_t* k, uint64_t* count) {
+    try {
+        size_t kk = 0, c = 0;
+        auto v = cphnsw::eval::load_ivecs(path, kk, c);
+        *k = kk, *count = c;
+        if (out && kk * c <= cap)
+            for (size_t i = 0; i < c; ++i) std::memcpy(out + i * kk, v[i].data(), kk * sizeof(uint32_t));
+        return 0;
+    } catch (const std::exception&) {
+        return -1;
+    }
+}
+
+int ref_normalize_vectors(float* v, uint64_t count, uint64_t dim) {
+    cphnsw::eval::normalize_vectors(v, count, dim);
+    return 0;
+}
+
+}  // extern "C"
+#endif

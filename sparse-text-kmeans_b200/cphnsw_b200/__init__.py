@@ -36,6 +36,7 @@ EXPORTS = [
     "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc", "cphnsw_b200_search_multiprobe_batch",
     "cphnsw_b200_probe_codes", "cphnsw_b200_brute_force_search_batch", "cphnsw_b200_verify_connectivity",
     "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
+    "cphnsw_b200_save", "cphnsw_b200_load",
 ]
 
 
@@ -109,6 +110,23 @@ class CPHNSWIndex:
         self.dim, self.K, self.M, self.component_bytes = dim, K, M, component_bytes
         self.padded_dim = int(self._lib.cphnsw_b200_padded_dim(self._h))
         self.code_dtype = np.uint8 if component_bytes == 1 else np.uint16
+
+    def save(self, path):
+        """Writes the whole index (parameters, sign tables, vectors, codes, adjacency) to one file."""
+        _check(self._lib.cphnsw_b200_save(self._h, os.fsencode(path)))
+
+    @classmethod
+    def load(cls, path, device=0):
+        """A new index holding exactly what ``save`` wrote; nothing is re-encoded or rebuilt."""
+        self = cls.__new__(cls)
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        _check(self._lib.cphnsw_b200_load(os.fsencode(path), C.c_int(device), C.byref(self._h)))
+        self.dim = int(self._lib.cphnsw_b200_dim(self._h))
+        self.K, self.M, self.component_bytes = (int(self.get_param(n)) for n in ("K", "M", "component_bytes"))
+        self.padded_dim = int(self._lib.cphnsw_b200_padded_dim(self._h))
+        self.code_dtype = np.uint8 if self.component_bytes == 1 else np.uint16
+        return self
 
     def close(self):
         h = getattr(self, "_h", None)

@@ -3,6 +3,8 @@
 no item of them is reproduced.  All vectors are float32 and L2-normalised with the
 ``norm > 1e-10`` guard of evaluation/datasets/dataset_loader.hpp:225-240.
 """
+import os
+
 import numpy as np
 
 
@@ -83,3 +85,21 @@ def workload(name, scale=1.0, query_stream=0):
         return dict(name="C5", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
                     k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4), k_entry=32)
     raise ValueError("unknown workload %r" % name)
+
+
+def workload_from_files(base_path, query_path, max_base=0, max_queries=0, rank=0, world=1):
+    """A workload from fvecs files (e.g. sift_base.fvecs / sift_query.fvecs when they are available):
+    rows normalised to unit length like the reference's load_*_normalized loaders do
+    (evaluation/datasets/dataset_loader.hpp:225-240), parameters of the C2 configuration (uint16
+    components when the padded dimension exceeds 128).  Queries are split across ranks."""
+    from . import vecs_io
+    base = vecs_io.normalize_rows(vecs_io.read_fvecs(base_path, max_base))
+    q = vecs_io.normalize_rows(vecs_io.read_fvecs(query_path, max_queries))
+    if q.shape[1] != base.shape[1]:
+        raise ValueError("Query dimension mismatch")  # dataset_loader.hpp:130-132
+    q = np.ascontiguousarray(q[rank::world])
+    wide = base.shape[1] > 128
+    return dict(name="files:" + os.path.basename(base_path), base=base, queries=q, K=32, component_bytes=2 if wide else 1,
+                M=32, ef_construction=200, k=10, ef=200 if wide else 100, rerank_k=1000 if wide else 500,
+                entry_scan=8192, k_entry=32)
+

@@ -627,6 +627,111 @@ int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, ui
     return do_search(h, q, false, nq, k, ef, rerank_k, ids_out, dists_out, nullptr, false, 0, 0, true);
 }
 
+// ---- index file -------------------------------------------------------------------------------------------
+namespace {
+constexpr char kFileMagic[8] = {'C', 'P', 'H', 'N', 'S', 'W', 'B', '2'};
+constexpr uint32_t kFileVersion = 1;
+struct FileHeader {  // after the magic; all little-endian, naturally aligned
+    uint32_t version, K, comp_bytes, M, ef_construction, keep_pruned, k_entry, knn_k, entry_scan;
+    int32_t convention;
+    uint64_t dim, seed, n, calib_samples;
+    double calib_alpha, calib_beta, calib_r2;
+};
+struct FileCloser {
+    std::FILE* f;
+    ~FileCloser() { if (f) std::fclose(f); }
+};
+// device -> file in pieces through a host buffer
+int write_device(std::FILE* f, const void* d, size_t bytes, std::vector<char>& buf) {
+    for (size_t off = 0; off < bytes; off += buf.size()) {
+        const size_t m = bytes - off < buf.size() ? bytes - off : buf.size();
+        CPB_CUDA(cudaMemcpy(buf.data(), static_cast<const char*>(d) + off, m, cudaMemcpyDeviceToHost));
+        if (std::fwrite(buf.data(), 1, m, f) != m) { set_error("save: write failed"); return CPHNSW_B200_E_INVALID; }
+    }
+    return 0;
+}
+int read_device(std::FILE* f, void* d, size_t bytes, std::vector<char>& buf) {
+    for (size_t off = 0; off < bytes; off += buf.size()) {
+        const size_t m = bytes - off < buf.size() ? bytes - off : buf.size();
+        if (std::fread(buf.data(), 1, m, f) != m) { set_error("load: file is shorter than its header says"); return CPHNSW_B200_E_INVALID; }
+        CPB_CUDA(cudaMemcpy(static_cast<char*>(d) + off, buf.data(), m, cudaMemcpyHostToDevice));
+    }
+    return 0;
+}
+}  // namespace
+
+int cphnsw_b200_save(cphnsw_b200_index* h, const char* path) {
+    CPB_TRY(bind(h));
+    if (!path) { set_error("save: null path"); return CPHNSW_B200_E_INVALID; }
+    FileCloser fc{std::fopen(path, "wb")};
+    if (!fc.f) { set_error("save: cannot create %s", path); return CPHNSW_B200_E_INVALID; }
+    FileHeader hd{};
+    hd.version = kFileVersion, hd.K = h->K, hd.comp_bytes = h->comp_bytes, hd.M = h->M, hd.ef_construction = h->ef_construction;
+    hd.keep_pruned = uint32_t(h->keep_pruned), hd.k_entry = h->k_entry, hd.knn_k = h->knn_k, hd.entry_scan = h->entry_scan;
+    hd.convention = h->convention, hd.dim = h->dim, hd.seed = h->seed, hd.n = h->n, hd.calib_samples = h->calib_samples;
+    hd.calib_alpha = h->calib_alpha, hd.calib_beta = h->calib_beta, hd.calib_r2 = h->calib_r2;
+    bool ok = std::fwrite(kFileMagic, 1, 8, fc.f) == 8 && std::fwrite(&hd, sizeof(hd), 1, fc.f) == 1 &&
+              std::fwrite(h->signs.data(), 1, h->signs.size(), fc.f) == h->signs.size();
+    if (!ok) { set_error("save: write failed"); return CPHNSW_B200_E_INVALID; }
+    std::vector<char> buf(size_t(64) << 20);
+    if (h->n) {
+        CPB_TRY(write_device(fc.f, h->d_vectors.p, h->n * h->dim * 4, buf));
+        CPB_TRY(write_device(fc.f, h->d_codes.p, h->n * code_row_bytes(h), buf));
+        CPB_TRY(write_device(fc.f, h->d_adj.p, h->n * h->M * 4, buf));
+    }
+    std::FILE* f = fc.f;
+    fc.f = nullptr;
+    if (std::fclose(f) != 0) { set_error("save: write failed"); return CPHNSW_B200_E_INVALID; }
+    return 0;
+}
+
+int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
+    if (!path || !out) { set_error("load: null argument"); return CPHNSW_B200_E_INVALID; }
+    *out = nullptr;
+    FileCloser fc{std::fopen(path, "rb")};
+    if (!fc.f) { set_error("load: cannot open %s", path); return CPHNSW_B200_E_INVALID; }
+    char magic[8];
+    FileHeader hd{};
+    if (std::fread(magic, 1, 8, fc.f) != 8 || std::memcmp(magic, kFileMagic, 8) != 0) {
+        set_error("load: %s is not a cphnsw_b200 index file", path);
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (std::fread(&hd, sizeof(hd), 1, fc.f) != 1 || hd.version != kFileVersion) {
+        set_error("load: unsupported index file version");
+        return CPHNSW_B200_E_INVALID;
+    }
+    if (hd.n >= 0x80000000ull) { set_error("load: corrupt header (n)"); return CPHNSW_B200_E_INVALID; }
+    cphnsw_b200_index* h = nullptr;
+    CPB_TRY(cphnsw_b200_create(hd.dim, hd.K, hd.comp_bytes, hd.M, hd.ef_construction, hd.seed, hd.convention, device, &h));
+    struct Guard {
+        cphnsw_b200_index* h;
+        ~Guard() { delete h; }
+    } guard{h};
+    std::vector<int8_t> signs(h->signs.size());
+    if (std::fread(signs.data(), 1, signs.size(), fc.f) != signs.size()) { set_error("load: file is shorter than its header says"); return CPHNSW_B200_E_INVALID; }
+    CPB_TRY(cphnsw_b200_set_sign_tables(h, signs.data()));
+    if (hd.k_entry < 1 || hd.k_entry > 100 || hd.knn_k > 64 || hd.entry_scan > 1048576) { set_error("load: corrupt header (tunables)"); return CPHNSW_B200_E_INVALID; }
+    h->keep_pruned = hd.keep_pruned != 0, h->k_entry = hd.k_entry, h->knn_k = hd.knn_k, h->entry_scan = hd.entry_scan;
+    h->calib_alpha = hd.calib_alpha, h->calib_beta = hd.calib_beta, h->calib_r2 = hd.calib_r2, h->calib_samples = hd.calib_samples;
+    if (hd.n) {
+        const uint64_t n = hd.n;
+        h->h_vectors.resize(n * h->dim);
+        if (std::fread(h->h_vectors.data(), 4, n * h->dim, fc.f) != n * h->dim) { set_error("load: file is shorter than its header says"); return CPHNSW_B200_E_INVALID; }
+        CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
+        CPB_TRY(h->d_codes.reserve(n * code_row_bytes(h) + 16));
+        CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
+        CPB_CUDA(cudaMemcpy(h->d_vectors.p, h->h_vectors.data(), n * h->dim * 4, cudaMemcpyHostToDevice));
+        std::vector<char> buf(size_t(64) << 20);
+        CPB_TRY(read_device(fc.f, h->d_codes.p, n * code_row_bytes(h), buf));
+        CPB_TRY(read_device(fc.f, h->d_adj.p, n * h->M * 4, buf));
+        h->n = n;
+        CPB_TRY(set_entry_ids(h));
+    }
+    guard.h = nullptr;
+    *out = h;
+    return 0;
+}
+
 // ---- host-pointer entry points -------------------------------------------------------------------------
 int cphnsw_b200_encode(cphnsw_b200_index* h, const float* x, uint64_t n, void* codes_out) {
     return cphnsw_b200_encode_queries(h, x, n, codes_out, nullptr, nullptr);

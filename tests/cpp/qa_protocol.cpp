@@ -177,6 +177,20 @@ int main() {
         for (size_t t = 0; eq && t < rr.size(); ++t) eq &= rr[t] == crr[t];
         CHECK(eq, "search_calibrated_and_rerank equals search_and_rerank");
     }
+    // index file: a loaded index answers like the one that was saved
+    {
+        const std::string path = "/tmp/cphnsw_b200_qa_index.bin";
+        index.save(path);
+        auto copy = CPHNSWIndex<uint8_t, 32>::load(path);
+        auto q = unit_vectors(5, dim, 99);
+        auto r1 = index.search_and_rerank_batch(q.data(), 5, 10, 100, 50);
+        auto r2 = copy.search_and_rerank_batch(q.data(), 5, 10, 100, 50);
+        CHECK(copy.size() == n && r1 == r2, "load(save(index)) returns the same results");
+        bool threw = false;
+        try { auto wrong = CPHNSWIndex<uint16_t, 16>::load(path); } catch (const std::invalid_argument&) { threw = true; }
+        CHECK(threw, "loading into another CPHNSWIndex<ComponentT,K> throws");
+        std::remove(path.c_str());
+    }
     // edge cases (qa_protocol.cpp:409-553): tiny index, duplicates, zero vector
     {
         CPHNSWIndex<uint8_t, 32> tiny(dim, 32, 200);

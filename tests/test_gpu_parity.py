@@ -446,3 +446,59 @@ def test_diagnostics_errors(cp):
         idx.brute_force_search_batch(base[:2], 5000)
     assert idx.get_calibration() == (1.0, 0.0, 0.0, 0)
 
+
+# ---- index file -------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,K,cb,M,n", [(128, 32, 1, 32, 3000), (200, 16, 2, 16, 700), (128, 32, 1, 8, 1)])
+def test_save_and_load_round_trip(cp, oracle, tmp_path, dim, K, cb, M, n):
+    base, q = synthetic.gaussian_mixture(n, 40, dim, max(2, n // 300), 0.3, n + dim)
+    a = make_index(cp, dim, K, cb, M=M, seed=7, conv=0)
+    a.set_param("entry_scan", 200)
+    a.set_param("k_entry", 16)
+    a.set_param("keep_pruned", 0)
+    a.add_batch_parallel(base)
+    if n > 1:
+        a.calibrate(500, 3)
+    path = str(tmp_path / "index.cphnsw")
+    a.save(path)
+    assert os.path.getsize(path) == 8 + 96 + K * 3 * a.padded_dim + n * (dim * 4 + K * cb + M * 4)
+    b = cp.CPHNSWIndex.load(path)
+    assert (b.dim, b.K, b.M, b.component_bytes, b.size()) == (dim, K, M, cb, n)
+    assert np.array_equal(a.sign_tables(), b.sign_tables())
+    assert np.array_equal(a.codes(), b.codes()) and np.array_equal(a.adjacency(), b.adjacency())
+    assert np.array_equal(a.entry_ids(), b.entry_ids())
+    assert a.get_calibration() == b.get_calibration()
+    assert all(a.get_param(p) == b.get_param(p) for p in ("keep_pruned", "k_entry", "knn_k", "entry_scan", "ef_construction"))
+    for k, ef, rr in ((10, 50, 0), (5, 20, 30)):
+        k = min(k, n)
+        ra = a.search_and_rerank_batch(q, k, ef, max(rr, k)) if rr else a.search_batch(q, k, ef)
+        rb = b.search_and_rerank_batch(q, k, ef, max(rr, k)) if rr else b.search_batch(q, k, ef)
+        assert np.array_equal(ra[0], rb[0]) and np.array_equal(ra[1], rb[1])
+    # a loaded index can be extended like the one that was saved
+    extra, _ = synthetic.gaussian_sphere(50, 1, dim, 5)
+    a.add_batch_parallel(extra)
+    b.add_batch_parallel(extra)
+    assert b.size() == n + 50 and np.array_equal(a.adjacency(), b.adjacency())
+
+
+@pytest.mark.gpu
+def test_load_rejects_bad_files(cp, tmp_path):
+    idx = make_index(cp, 128)
+    base, _ = synthetic.gaussian_sphere(100, 1, 128, 1)
+    idx.add_batch_parallel(base)
+    path = str(tmp_path / "i.cphnsw")
+    idx.save(path)
+    raw = open(path, "rb").read()
+    cases = {"magic": b"NOTANIDX" + raw[8:], "version": raw[:8] + (99).to_bytes(4, "little") + raw[12:], "short": raw[:-100],
+             "empty": b""}
+    for name, data in cases.items():
+        p = str(tmp_path / name)
+        open(p, "wb").write(data)
+        with pytest.raises(ValueError):
+            cp.CPHNSWIndex.load(p)
+    with pytest.raises(ValueError):
+        cp.CPHNSWIndex.load(str(tmp_path / "missing"))
+    with pytest.raises(ValueError):
+        idx.save(str(tmp_path / "no_such_dir" / "x"))
+    assert idx.search_batch(base[:1], 5, 10)[0].shape == (1, 5)  # still usable
+
