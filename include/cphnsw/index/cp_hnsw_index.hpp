@@ -134,12 +134,14 @@ public:
     size_t size() const { return cphnsw_b200_size(h_); }
 
     // ---- construction -------------------------------------------------------------------------
+    // add / add_batch insert into the existing graph (new links + reverse links); add_batch_parallel
+    // rebuilds the graph over everything added so far.  On an empty index all three are the bulk build.
     NodeId add(const Float* vec) {
         NodeId id = NodeId(size());
-        add_batch_parallel(vec, 1);
+        add_batch(vec, 1);
         return id;
     }
-    void add_batch(const Float* vecs, size_t n) { add_batch_parallel(vecs, n); }
+    void add_batch(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch(h_, vecs, n)); }
     void add_batch_parallel(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch_parallel(h_, vecs, n)); }
 
     // ---- search ---------------------------------------------------------------------------------

@@ -123,6 +123,16 @@ int cphnsw_b200_select_neighbors(cphnsw_b200_index* h, const void* codes, uint64
  * graph over everything added so far: encode -> code-distance kNN graph (knn_k) -> select_neighbors. */
 int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_t n);
 
+/* Replaces CPHNSWIndex::add / add_batch (unified form include/cphnsw/api/index.hpp:98-164; legacy use
+ * evaluation/qa_protocol.cpp:262): incremental insertion into the existing graph, batched.  The n
+ * vectors are appended (ids continue from size()) in pieces no larger than the graph they join;
+ * for every piece: encode; candidates of a new node = the 64 best of a walk of the EXISTING graph
+ * under the code distance (beam ef_construction, seeds as for search; nodes of one piece do not see
+ * each other); select_neighbors gives its M links; every old node chosen by new nodes re-selects
+ * its row from (current row + the new nodes that chose it), the 64 closest by (distance, id).
+ * On an empty index this is add_batch_parallel. */
+int cphnsw_b200_add_batch(cphnsw_b200_index* h, const float* x, uint64_t n);
+
 /* CPHNSWIndex::get_code (evaluation/debug_code_storage.cpp:75) for all nodes, and the adjacency
  * uint32[size][M] (FlatGraph neighbour ids, include/cphnsw/graph/flat_graph.hpp:179-181). */
 int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out);

@@ -36,7 +36,7 @@ EXPORTS = [
     "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc", "cphnsw_b200_search_multiprobe_batch",
     "cphnsw_b200_probe_codes", "cphnsw_b200_brute_force_search_batch", "cphnsw_b200_verify_connectivity",
     "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
-    "cphnsw_b200_save", "cphnsw_b200_load",
+    "cphnsw_b200_save", "cphnsw_b200_load", "cphnsw_b200_add_batch",
 ]
 
 
@@ -234,12 +234,15 @@ class CPHNSWIndex:
         x = self._vecs(x)
         _check(self._lib.cphnsw_b200_add_batch_parallel(self._h, _p(x), _u64(x.shape[0])))
 
-    add_batch = add_batch_parallel
+    def add_batch(self, x):
+        """Incremental insertion into the existing graph (bulk build on an empty index)."""
+        x = self._vecs(x)
+        _check(self._lib.cphnsw_b200_add_batch(self._h, _p(x), _u64(x.shape[0])))
 
     def add(self, vec):
-        """Appends one vector and returns its id (CPHNSWIndex::add, evaluation/eval_sift.cpp:239)."""
+        """Inserts one vector and returns its id (CPHNSWIndex::add, evaluation/eval_sift.cpp:239)."""
         nid = self.size()
-        self.add_batch_parallel(self._vecs(vec))
+        self.add_batch(self._vecs(vec))
         return nid
 
     def codes(self):

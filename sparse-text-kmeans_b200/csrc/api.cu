@@ -835,6 +835,67 @@ int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_
     return build_graph(h, 0);
 }
 
+namespace {
+// grows a device buffer to new_bytes keeping its first keep_bytes
+int grow_keep(cpb::DevBuf& b, size_t keep_bytes, size_t new_bytes) {
+    if (b.p && new_bytes <= b.bytes) return 0;
+    void* p = nullptr;
+    const size_t cap = new_bytes + new_bytes / 2;
+    CPB_CUDA(cudaMalloc(&p, cap));
+    if (b.p && keep_bytes) {
+        cudaError_t e = cudaMemcpy(p, b.p, keep_bytes, cudaMemcpyDeviceToDevice);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            CPB_CUDA(e);
+        }
+    }
+    b.release();
+    b.p = p;
+    b.bytes = cap;
+    return 0;
+}
+}  // namespace
+
+int cphnsw_b200_add_batch(cphnsw_b200_index* h, const float* x, uint64_t n) {
+    CPB_TRY(bind(h));
+    if (n == 0) return 0;
+    if (!x) { set_error("add_batch: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (h->n == 0) return cphnsw_b200_add_batch_parallel(h, x, n);  // nothing to insert into: bulk build
+    if (h->n + n >= 0x80000000ull) { set_error("add_batch: at most 2^31-1 nodes"); return CPHNSW_B200_E_INVALID; }
+    const bool track_host = h->h_vectors.size() == h->n * h->dim;
+    const size_t rb = code_row_bytes(h);
+    cudaStream_t st = 0;
+    for (uint64_t done = 0; done < n;) {
+        const uint64_t n_old = h->n;
+        const uint64_t m = n - done < n_old ? n - done : n_old;  // a piece never outnumbers the graph it joins
+        CPB_TRY(grow_keep(h->d_vectors, n_old * h->dim * 4, (n_old + m) * h->dim * 4));
+        CPB_TRY(grow_keep(h->d_codes, n_old * rb, (n_old + m) * rb + 16));
+        CPB_TRY(grow_keep(h->d_adj, n_old * h->M * 4, (n_old + m) * h->M * 4 + 16));
+        float* d_new = h->d_vectors.as<float>() + n_old * h->dim;
+        unsigned char* d_new_codes = h->d_codes.as<unsigned char>() + n_old * rb;
+        CPB_CUDA(cudaMemcpyAsync(d_new, x + done * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
+        CPB_TRY(launch_encode(h, d_new, m, d_new_codes, nullptr, nullptr, st));
+        // candidates: a walk of the existing graph under the code distance from the usual seeds
+        const uint32_t k_c = uint32_t(n_old < 64 ? n_old : 64);
+        uint32_t beam = h->ef_construction > k_c ? h->ef_construction : k_c;
+        if (beam > 1024) beam = 1024;
+        CPB_TRY(h->d_out_ids.reserve(m * k_c * 4));
+        CPB_TRY(h->d_out_dist.reserve(m * k_c * 4));
+        CPB_TRY(launch_search(h, nullptr, nullptr, m, k_c, beam, 0, h->d_out_ids.as<uint32_t>(), h->d_out_dist.as<float>(),
+                              nullptr, st, d_new_codes));
+        CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n_old + m, h->d_out_ids.as<uint32_t>(), k_c, n_old, n_old + m, h->M,
+                                        h->keep_pruned, h->d_adj.as<uint32_t>() + n_old * h->M, st));
+        CPB_TRY(launch_reverse_edges(h, h->d_codes.p, n_old, m, h->d_adj.as<uint32_t>(), h->M, h->keep_pruned, st));
+        CPB_CUDA(cudaStreamSynchronize(st));
+        CPB_TRY(check_status(h));
+        if (track_host) h->h_vectors.insert(h->h_vectors.end(), x + done * h->dim, x + (done + m) * h->dim);
+        h->n = n_old + m;
+        CPB_TRY(set_entry_ids(h));
+        done += m;
+    }
+    return 0;
+}
+
 int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out) {
     CPB_TRY(bind(h));
     if (!codes_out) { set_error("get_codes: null pointer"); return CPHNSW_B200_E_INVALID; }

@@ -130,7 +130,10 @@ int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t 
                             uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st);
 int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
                             uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
-                            uint32_t* d_adj, cudaStream_t st);
+                            uint32_t* d_adj, cudaStream_t st, const uint32_t* d_row_ids = nullptr);
+// incremental insertion: old nodes chosen by the new rows [n_old, n_old + m) of d_adj re-select their rows
+int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_old, uint64_t m, uint32_t* d_adj,
+                         uint32_t M, int keep_pruned, cudaStream_t st);
 int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
                   cudaStream_t st, const void* d_qcodes = nullptr, int scan_only = 0);

@@ -254,12 +254,15 @@ template <int WC, bool U16>
 __global__ void __launch_bounds__(kSelWarps * 32)
 select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ cand, uint32_t k,
                         uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
-                        uint32_t* __restrict__ adj) {
+                        uint32_t* __restrict__ adj, const uint32_t* __restrict__ row_ids) {
+    // row_ids == nullptr: rows [row_begin, row_end), output row i at adj[i - row_begin];
+    // otherwise rows row_ids[0 .. row_end - row_begin) and the output goes to adj[row] (in place)
     __shared__ uint32_t csm[kSelWarps][kSelMaxK][WC];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint64_t row = row_begin + uint64_t(blockIdx.x) * kSelWarps + warp;
-    if (row >= row_end) return;
-    const uint32_t* crow = cand + (row - row_begin) * uint64_t(k);
+    const uint64_t slot = row_begin + uint64_t(blockIdx.x) * kSelWarps + warp;
+    if (slot >= row_end) return;
+    const uint64_t row = row_ids ? uint64_t(row_ids[slot - row_begin]) : slot;
+    const uint32_t* crow = cand + (slot - row_begin) * uint64_t(k);
     uint32_t cid[2];
     cid[0] = lane < int(k) ? crow[lane] : kInvalidNode;
     cid[1] = lane + 32 < int(k) ? crow[lane + 32] : kInvalidNode;
@@ -312,7 +315,7 @@ select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __re
             ++rsize;
         }
     }
-    uint32_t* out = adj + (row - row_begin) * uint64_t(M);
+    uint32_t* out = adj + (row_ids ? row : slot - row_begin) * uint64_t(M);
     const uint32_t n_disc = keep_pruned ? uint32_t(__popcll(disc)) : 0u;
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
@@ -325,6 +328,95 @@ select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __re
     }
     const uint32_t total = min(M, rsize + n_disc);
     for (uint32_t o = total + lane; o < M; o += 32) out[o] = kInvalidNode;
+}
+
+// ---- reverse edges of an incremental insertion ---------------------------------------------------------------
+// New nodes (ids >= n_old) have chosen their neighbours among the old nodes; every old node v that
+// was chosen gets the choosers as candidates for its own row.
+// in-degree of every old node from the new rows
+__global__ void rev_count_kernel(const uint32_t* __restrict__ new_adj, uint64_t m, int M, uint64_t n_old,
+                                 uint32_t* __restrict__ cnt) {
+    const uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= m * M) return;
+    const uint32_t v = new_adj[t];
+    if (v < n_old) atomicAdd(cnt + v, 1u);
+}
+// a segment of the incoming list for every old node with incoming edges; the list of those nodes
+// (counters[0] = entries used in the incoming list, counters[1] = affected nodes)
+__global__ void rev_alloc_kernel(const uint32_t* __restrict__ cnt, uint64_t n_old, uint32_t* __restrict__ seg,
+                                 uint32_t* __restrict__ aff, uint32_t* __restrict__ counters) {
+    const uint64_t v = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (v >= n_old || cnt[v] == 0) return;
+    seg[v] = atomicAdd(counters, cnt[v]);
+    aff[atomicAdd(counters + 1, 1u)] = uint32_t(v);
+}
+__global__ void rev_fill_kernel(const uint32_t* __restrict__ new_adj, uint64_t m, int M, uint64_t n_old,
+                                const uint32_t* __restrict__ seg, uint32_t* __restrict__ fill, uint32_t* __restrict__ inc) {
+    const uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= m * M) return;
+    const uint32_t v = new_adj[t];
+    if (v < n_old) inc[seg[v] + atomicAdd(fill + v, 1u)] = uint32_t(n_old + t / M);
+}
+// One warp per affected old node v: its current neighbours and the new nodes that chose it, the 64
+// closest to v by (code distance, id) in ascending order -> cand_out[i][64] (the order in which
+// the incoming list was filled does not matter).
+template <int WC, bool U16>
+__global__ void __launch_bounds__(kSelWarps * 32)
+rev_merge_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ adj, int M,
+                 const uint32_t* __restrict__ aff, uint32_t n_aff, const uint32_t* __restrict__ cnt,
+                 const uint32_t* __restrict__ seg, const uint32_t* __restrict__ inc, uint32_t* __restrict__ cand_out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t i = blockIdx.x * kSelWarps + warp;
+    if (i >= n_aff) return;
+    const uint32_t v = aff[i];
+    uint32_t qc[WC];
+#pragma unroll
+    for (int w = 0; w < WC; w += 4) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(codes + uint64_t(v) * WC + w));
+        qc[w] = c.x, qc[w + 1] = c.y, qc[w + 2] = c.z, qc[w + 3] = c.w;
+    }
+    uint32_t ld[2] = {kFull, kFull}, li[2] = {kInvalidNode, kInvalidNode};
+    const uint32_t total = uint32_t(M) + cnt[v];
+    for (uint32_t c0 = 0; c0 < total; c0 += 32) {
+        const uint32_t c = c0 + lane;
+        uint32_t w = kInvalidNode;
+        if (c < uint32_t(M)) w = adj[uint64_t(v) * M + c];
+        else if (c < total) w = inc[seg[v] + (c - M)];
+        uint32_t dd = kFull;
+        if (w != kInvalidNode) {
+            uint32_t wc[WC];
+#pragma unroll
+            for (int x = 0; x < WC; x += 4) {
+                const uint4 cc = __ldg(reinterpret_cast<const uint4*>(codes + uint64_t(w) * WC + x));
+                wc[x] = cc.x, wc[x + 1] = cc.y, wc[x + 2] = cc.z, wc[x + 3] = cc.w;
+            }
+            dd = mismatch_count<WC, U16>(wc, qc);
+        }
+        uint32_t live = __ballot_sync(kFull, w != kInvalidNode);
+        while (live) {
+            const int src = __ffs(live) - 1;
+            live &= live - 1;
+            const uint32_t d1 = __shfl_sync(kFull, dd, src), w1 = __shfl_sync(kFull, w, src);
+            // rank = members below (d1, w1); whatever moves past place 63 falls off
+            int p = 0;
+#pragma unroll
+            for (int s = 0; s < 2; ++s) p += __popc(__ballot_sync(kFull, ld[s] < d1 || (ld[s] == d1 && li[s] < w1)));
+            if (p >= 64) continue;
+#pragma unroll
+            for (int s = 1; s >= 0; --s) {
+                uint32_t ud = __shfl_up_sync(kFull, ld[s], 1), ui = __shfl_up_sync(kFull, li[s], 1);
+                if (s > 0) {
+                    const uint32_t cd = __shfl_sync(kFull, ld[s - 1], 31), ci = __shfl_sync(kFull, li[s - 1], 31);
+                    if (lane == 0) ud = cd, ui = ci;
+                }
+                const int rank = s * 32 + lane;
+                if (rank > p) ld[s] = ud, li[s] = ui;
+                else if (rank == p) ld[s] = d1, li[s] = w1;
+            }
+        }
+    }
+    cand_out[uint64_t(i) * 64 + lane] = li[0];
+    cand_out[uint64_t(i) * 64 + 32 + lane] = li[1];
 }
 
 // ---- host-side dispatch ----------------------------------------------------------------------------------
@@ -460,7 +552,7 @@ int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint
 
 int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
                             uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
-                            uint32_t* d_adj, cudaStream_t st) {
+                            uint32_t* d_adj, cudaStream_t st, const uint32_t* d_row_ids) {
     if (row_end <= row_begin) return 0;
     if (k == 0 || k > kSelMaxK || M == 0 || M > 64) {
         set_error("select_neighbors: need 1 <= k <= 64 and 1 <= M <= 64 (got k=%u M=%u)", k, M);
@@ -479,12 +571,59 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
     LaunchTimer timer(h, kKernelSelect, st);
 #define CALL(W, U)                                                                                          \
     select_neighbors_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_cand, k, row_begin, row_end, M,    \
-                                                                   keep_pruned, d_adj)
+                                                                   keep_pruned, d_adj, d_row_ids)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
     h->launches++;
     CPB_CUDA(cudaGetLastError());
     return 0;
+}
+
+// Reverse edges after the rows [n_old, n_old + m) of d_adj have been chosen among the old nodes:
+// every old node with incoming new edges re-selects its row from (current row + choosers).
+int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_old, uint64_t m, uint32_t* d_adj,
+                         uint32_t M, int keep_pruned, cudaStream_t st) {
+    if (m == 0 || n_old == 0) return 0;
+    const int WC = code_row_words(h->K, h->comp_bytes);
+    if (!WC) {
+        set_error("code rows wider than 64 bytes are not supported by the distance kernels");
+        return CPHNSW_B200_E_UNSUPPORTED;
+    }
+    const bool u16 = h->comp_bytes == 2;
+    const uint64_t edges = m * M;
+    // scratch: cnt, seg, fill [n_old]; aff [n_old]; inc [edges]
+    CPB_TRY(h->s_in.reserve((size_t(n_old) * 4 + edges) * 4 + 64));
+    uint32_t* cnt = h->s_in.as<uint32_t>();
+    uint32_t* seg = cnt + n_old;
+    uint32_t* fill = seg + n_old;
+    uint32_t* aff = fill + n_old;
+    uint32_t* inc = aff + n_old;
+    uint32_t* counters = h->d_status.as<uint32_t>() + 6;  // two words
+    CPB_CUDA(cudaMemsetAsync(cnt, 0, size_t(n_old) * 4, st));
+    CPB_CUDA(cudaMemsetAsync(fill, 0, size_t(n_old) * 4, st));
+    CPB_CUDA(cudaMemsetAsync(counters, 0, 8, st));
+    const uint32_t* new_adj = d_adj + n_old * M;
+    rev_count_kernel<<<unsigned((edges + 255) / 256), 256, 0, st>>>(new_adj, m, int(M), n_old, cnt);
+    rev_alloc_kernel<<<unsigned((n_old + 255) / 256), 256, 0, st>>>(cnt, n_old, seg, aff, counters);
+    rev_fill_kernel<<<unsigned((edges + 255) / 256), 256, 0, st>>>(new_adj, m, int(M), n_old, seg, fill, inc);
+    h->launches += 3;
+    CPB_CUDA(cudaGetLastError());
+    uint32_t host_counters[2] = {0, 0};
+    CPB_CUDA(cudaMemcpyAsync(host_counters, counters, 8, cudaMemcpyDeviceToHost, st));
+    CPB_CUDA(cudaStreamSynchronize(st));
+    const uint32_t n_aff = host_counters[1];
+    if (n_aff == 0) return 0;
+    CPB_TRY(h->s_in2.reserve(size_t(n_aff) * 64 * 4 + 16));
+    uint32_t* cand = h->s_in2.as<uint32_t>();
+    const uint32_t* pc;
+    CPB_TRY(padded_view(h, d_codes, n_old + m, WC, h->s_pad, st, &pc));
+    const unsigned grid = (n_aff + kSelWarps - 1) / kSelWarps;
+#define CALL(W, U) rev_merge_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_adj, int(M), aff, n_aff, cnt, seg, inc, cand)
+    CPB_DISPATCH_WC(WC, u16, CALL);
+#undef CALL
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return launch_select_neighbors(h, d_codes, n_old + m, cand, 64, 0, n_aff, M, keep_pruned, d_adj, st, aff);
 }
 
 }  // namespace cpb

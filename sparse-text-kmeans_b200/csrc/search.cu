@@ -468,9 +468,13 @@ int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st) {
 int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
     (void)beam;
     const size_t slots = size_t(h->sm_count) * 16;  // the most warps a launch ever uses
-    const size_t stride = (size_t(h->n) + 15) & ~size_t(15);
+    size_t stride = (size_t(h->n) + 15) & ~size_t(15);
+    // an array laid out for more nodes than the index holds stays valid (an index that grows by
+    // incremental insertion gets a quarter of slack so that not every insertion reallocates)
+    if (h->d_visited.p && h->vis_stride >= stride && slots * h->vis_stride <= h->d_visited.bytes) return 0;
+    if (h->d_visited.p) stride = (stride + stride / 4 + 15) & ~size_t(15);
     const size_t vis_bytes = slots * stride;
-    if (vis_bytes > h->d_visited.bytes || !h->d_visited.p || h->vis_stride != stride) {
+    {
         CPB_TRY(h->d_visited.reserve(vis_bytes));
         CPB_CUDA(cudaMemset(h->d_visited.p, 0, h->d_visited.bytes));
         CPB_TRY(h->d_explist.reserve(slots * 4));  // per-slot epoch counters

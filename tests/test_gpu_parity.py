@@ -215,16 +215,83 @@ def test_identity_queries_and_ordering(cp):
     assert (ids[:, 0] == np.arange(50)).all() and (dist[:, 0] < 0).all()
 
 
-def test_add_batch_appends_and_rebuilds(cp, oracle):
+def test_add_batch_parallel_appends_and_rebuilds(cp, oracle):
     base, _ = synthetic.gaussian_mixture(1200, 1, 128, 5, 0.3, 9)
     a = make_index(cp, 128)
-    a.add_batch(base[:500])
-    a.add_batch_parallel(base[500:])
-    nid = a.add(base[0])
-    assert nid == 1200 and a.size() == 1201
+    a.add_batch(base[:500])            # empty index: the bulk build
+    a.add_batch_parallel(base[500:])   # rebuild over everything
+    assert a.size() == 1200
     b = make_index(cp, 128)
-    b.add_batch_parallel(np.concatenate([base, base[:1]]))
+    b.add_batch_parallel(base)
     assert np.array_equal(a.codes(), b.codes()) and np.array_equal(a.adjacency(), b.adjacency())
+
+
+def oracle_insert(oracle, codes, adj, n_old, m, M, keep, ef_c, entry, n_seed):
+    """The declared incremental insertion, step by step with the oracle's pieces: candidates of a new
+    node = 64 best of a code-distance walk of the old graph; select_neighbors; every old node chosen
+    by new nodes re-selects from (its row + the choosers), the 64 closest by (distance, id)."""
+    n = n_old + m
+    k_c = min(64, n_old)
+    beam = min(1024, max(ef_c, k_c))
+    cand, _ = oracle.search_codes(codes[n_old:n], codes[:n_old], adj[:n_old], entry, beam, k_c, n_seed=n_seed)
+    full = np.full((n, k_c), INVALID, np.uint32)
+    full[n_old:] = cand
+    new_rows = oracle.select_neighbors(codes[:n], full, M, keep)[n_old:]
+    out = np.concatenate([adj[:n_old], new_rows])
+    incoming = {}
+    for u in range(n_old, n):
+        for v in new_rows[u - n_old]:
+            if v < n_old:
+                incoming.setdefault(int(v), []).append(u)
+    rev = np.full((n, 64), INVALID, np.uint32)
+    for v, us in incoming.items():
+        ids = [int(w) for w in adj[v] if w != INVALID] + us
+        d = oracle.code_distance(codes[v:v + 1], codes[ids])[0]
+        order = sorted(zip(d.tolist(), ids))[:64]
+        rev[v, :len(order)] = [w for _, w in order]
+    sel = oracle.select_neighbors(codes[:n], rev, M, keep)
+    for v in incoming:
+        out[v] = sel[v]
+    return out
+
+
+@pytest.mark.parametrize("n0,adds,dim,K,cb,M,keep", [(2000, (1, 1, 300, 2500), 128, 32, 1, 32, True),
+                                                       (500, (700, 40), 96, 16, 1, 8, False),
+                                                       (40, (5, 100), 200, 16, 2, 16, True), (1, (1, 2, 4), 128, 32, 1, 32, True)])
+def test_incremental_add_matches_oracle(cp, oracle, n0, adds, dim, K, cb, M, keep):
+    total = n0 + sum(adds)
+    base, q = synthetic.gaussian_mixture(total, 30, dim, max(2, total // 300), 0.3, total)
+    idx = make_index(cp, dim, K, cb, M=M)
+    idx.set_param("keep_pruned", int(keep))
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 8)
+    idx.add_batch(base[:n0])
+    signs = oracle.sign_tables(dim, K, 42)
+    codes = oracle.encode(base, K, cb, signs, 2)
+    adj = idx.adjacency()
+    n = n0
+    for a in adds:
+        first = idx.add(base[n]) if a == 1 else None
+        if a != 1:
+            idx.add_batch(base[n:n + a])
+        assert first is None or first == n
+        # pieces no larger than the graph they join
+        done = 0
+        while done < a:
+            m = min(a - done, n)
+            entry = (np.arange(min(64, n), dtype=np.uint64) * n // min(64, n)).astype(np.uint32)
+            adj = oracle_insert(oracle, codes, adj, n, m, M, keep, max(200, M), entry, 8)
+            n += m
+            done += m
+        assert idx.size() == n
+        assert np.array_equal(idx.codes(), codes[:n])
+        assert np.array_equal(idx.adjacency(), adj), (n, a)
+    # the grown index searches like any other: ids, distances and counts equal to the oracle's on the same graph
+    _, rot, _ = oracle.encode(q, K, cb, signs, 2, want_rotated=True)
+    ids, dist, stats = idx.search_batch(q, 5, 40, want_stats=True)
+    wi, wd, ws = oracle.search(rot, codes[:n], adj, idx.entry_ids(), 40, 5, want_stats=True, n_seed=8)
+    assert np.array_equal(ids, wi) and np.array_equal(dist, wd) and np.array_equal(stats, ws)
+    assert idx.verify_connectivity() == oracle.connectivity(adj, idx.entry_ids())
 
 
 def test_errors_do_not_exit(cp):
