@@ -70,6 +70,9 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *                 or uint16 codes of padded dim 1024),
  *   "search_kernel" (0 = pick, 1 = one warp per query, 2 = two warps per query; the second needs
  *                    K * padded_dim * 4 <= 32 KB and M <= 32; both return identical results),
+ *   "build_seed" (0 = add_batch_parallel builds the exact code-distance kNN graph over everything, the
+ *                 default; s > 0 = on an empty index only the first s vectors get the exact graph and
+ *                 the others are inserted as add_batch does: O(n) instead of O(n^2) candidate search),
  *   "entry_scan" (evenly spaced nodes scored for every query before the walk; default = k_entry),
  *   "k_entry" (1..100, default 4: how many of the scored nodes, the best, seed the walk). */
 int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double value);

@@ -465,6 +465,11 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         h->search_kernel = int(v);
         return 0;
     }
+    if (s == "build_seed") {
+        if (v < 0 || v > 2147483647.0) { set_error("build_seed must be in 0..2^31-1 (0 = exact kNN graph over everything)"); return CPHNSW_B200_E_INVALID; }
+        h->build_seed = uint32_t(v);
+        return 0;
+    }
     if (s == "k_entry") {
         if (v < 1) { set_error("CPHNSWParams: k_entry must be > 0"); return CPHNSW_B200_E_INVALID; }
         if (v > 100) { set_error("CPHNSWParams: k_entry must be <= 100"); return CPHNSW_B200_E_INVALID; }
@@ -494,6 +499,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "profile") *v = h->profile;
     else if (s == "knn_kernel") *v = h->knn_kernel;
     else if (s == "search_kernel") *v = h->search_kernel;
+    else if (s == "build_seed") *v = h->build_seed;
     else if (s == "k_entry") *v = h->k_entry;
     else if (s == "knn_k") *v = h->knn_k;
     else if (s == "entry_scan") *v = h->entry_scan;
@@ -824,6 +830,15 @@ int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_
         return CPHNSW_B200_E_STATE;
     }
     if (h->n + n >= 0x80000000ull) { set_error("add_batch_parallel: at most 2^31-1 nodes"); return CPHNSW_B200_E_INVALID; }
+    if (h->build_seed && h->n == 0 && n > h->build_seed) {
+        // the exact kNN graph of the first build_seed vectors, the others inserted into it
+        const uint32_t seed_n = h->build_seed;
+        h->build_seed = 0;
+        int rc = cphnsw_b200_add_batch_parallel(h, x, seed_n);
+        h->build_seed = seed_n;
+        CPB_TRY(rc);
+        return cphnsw_b200_add_batch(h, x + uint64_t(seed_n) * h->dim, n - seed_n);
+    }
     h->h_vectors.insert(h->h_vectors.end(), x, x + n * h->dim);
     const uint64_t total = h->n + n;
     CPB_TRY(h->d_vectors.reserve(total * h->dim * 4));

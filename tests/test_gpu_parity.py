@@ -226,6 +226,28 @@ def test_add_batch_parallel_appends_and_rebuilds(cp, oracle):
     assert np.array_equal(a.codes(), b.codes()) and np.array_equal(a.adjacency(), b.adjacency())
 
 
+def test_seeded_build_is_bulk_seed_plus_insertion(cp):
+    """build_seed = s: add_batch_parallel on an empty index builds the exact kNN graph of the first s
+    vectors and inserts the others, i.e. exactly add_batch_parallel(x[:s]) followed by add_batch(x[s:])."""
+    base, q = synthetic.gaussian_mixture(3000, 20, 128, 12, 0.3, 31)
+    a = make_index(cp, 128)
+    a.set_param("build_seed", 400)
+    a.add_batch_parallel(base)
+    b = make_index(cp, 128)
+    b.add_batch_parallel(base[:400])
+    b.add_batch(base[400:])
+    assert a.size() == 3000 and a.get_param("build_seed") == 400
+    assert np.array_equal(a.codes(), b.codes()) and np.array_equal(a.adjacency(), b.adjacency())
+    c = make_index(cp, 128)
+    c.set_param("build_seed", 5000)  # more than there is: the exact graph over everything
+    c.add_batch_parallel(base)
+    d = make_index(cp, 128)
+    d.add_batch_parallel(base)
+    assert np.array_equal(c.adjacency(), d.adjacency())
+    with pytest.raises(ValueError):
+        a.set_param("build_seed", -1)
+
+
 def oracle_insert(oracle, codes, adj, n_old, m, M, keep, ef_c, entry, n_seed):
     """The declared incremental insertion, step by step with the oracle's pieces: candidates of a new
     node = 64 best of a code-distance walk of the old graph; select_neighbors; every old node chosen
