@@ -70,6 +70,12 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *                 or uint16 codes of padded dim 1024),
  *   "search_kernel" (0 = pick, 1 = one warp per query, 2 = two warps per query; the second needs
  *                    K * padded_dim * 4 <= 32 KB and M <= 32; both return identical results),
+ *   "binary_codes" (0/1, before any vector is added: 1 = the unified index's primary binary code
+ *                   (include/cphnsw/core/codes.hpp:76-129 with R = 0): a component keeps only its sign bit, so
+ *                   code distance = Hamming distance and the graph is built under it; search / search_and_rerank
+ *                   walk under the Hamming distance to the query's code (unified search, include/cphnsw/api/index.hpp:177-214),
+ *                   distances returned are Hamming distances (exact -<q,x> after a rerank); brute_force_search ranks by
+ *                   Hamming distance; calibrate and search_multiprobe are not available),
  *   "build_seed" (0 = add_batch_parallel builds the exact code-distance kNN graph over everything, the
  *                 default; s > 0 = on an empty index only the first s vectors get the exact graph and
  *                 the others are inserted as add_batch does: O(n) instead of O(n^2) candidate search),
@@ -194,6 +200,11 @@ int cphnsw_b200_get_calibration(const cphnsw_b200_index* h, double* alpha_out, d
  * keeps the order), with rerank_k > 0 they are the exact reranked distances. */
 int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                                         uint32_t ef, uint32_t rerank_k, uint32_t* ids_out, float* dists_out);
+
+/* Sign bits of all stored codes packed like the unified index's ResidualCode<K,0>::primary
+ * (include/cphnsw/core/codes.hpp:21-52): uint64[size][(K+63)/64], bit r of a row = 1 iff the winning
+ * coordinate of rotation r is negative.  Works in both code modes (it is bit 0 of every component). */
+int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out);
 
 /* Index file (the reference has no save/load, SURVEY of its tree: rotation.hpp's get_signs() exists "for
  * serialization" only).  One little-endian file: magic "CPHNSWB2", format version, the constructor

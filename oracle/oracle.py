@@ -307,6 +307,21 @@ class Ref:
                           C.c_uint64(seed), _ptr(codes), _ptr(rot), _ptr(mag))
         return (codes, rot, mag) if want_rotated else codes
 
+    def encode_batch_signbits64(self, x, seed=42):
+        """The unified encoder CPEncoder<64,0>: one uint64 of sign bits per vector."""
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty(x.shape[0], np.uint64)
+        self.l.ref_encode_batch_signbits64(_ptr(x), C.c_uint64(x.shape[0]), C.c_uint64(x.shape[1]), C.c_uint64(seed), _ptr(out))
+        return out
+
+    def hamming64(self, a, b):
+        """The reference's hamming_primary_scalar<64> between packed codes (scalar build only)."""
+        a = np.ascontiguousarray(a, np.uint64)
+        b = np.ascontiguousarray(b, np.uint64)
+        out = np.empty((a.size, b.size), np.uint32)
+        self.l.ref_hamming64(_ptr(a), C.c_uint64(a.size), _ptr(b), C.c_uint64(b.size), _ptr(out))
+        return out
+
     def encode_batch_signbits32(self, x, seed=42):
         x = np.ascontiguousarray(x, np.float32)
         out = np.empty(x.shape[0], np.uint32)

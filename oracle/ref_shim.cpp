@@ -22,6 +22,8 @@
 #ifdef CPHNSW_REF_EVAL_DIR
 // the reference's dataset readers (evaluation/datasets/dataset_loader.hpp), included in place
 #include "datasets/dataset_loader.hpp"
+// the unified distance kernels compile in the scalar build only
+#include "cphnsw/distance/metric_policy.hpp"
 #endif
 
 extern "C" {
@@ -105,10 +107,31 @@ int ref_encode_batch_signbits32(const float* x, uint64_t n, uint64_t dim, uint64
     return 0;
 }
 
+// The unified encoder with 64 sign bits, and the reference's own Hamming distance between two of
+// its primary codes (include/cphnsw/distance/detail/scalar_kernels.hpp:37-47).
+int ref_encode_batch_signbits64(const float* x, uint64_t n, uint64_t dim, uint64_t seed, uint64_t* out) {
+    cphnsw::CPEncoder<64, 0> enc(dim, seed);
+    std::vector<cphnsw::ResidualCode<64, 0>> codes(n);
+    enc.encode_batch(x, n, codes.data());
+    for (uint64_t i = 0; i < n; ++i) out[i] = codes[i].primary.signs[0];
+    return 0;
+}
+
 }  // extern "C"
 
 #ifdef CPHNSW_REF_EVAL_DIR
 extern "C" {
+
+int ref_hamming64(const uint64_t* a, uint64_t na, const uint64_t* b, uint64_t nb, uint32_t* out) {
+    for (uint64_t i = 0; i < na; ++i)
+        for (uint64_t j = 0; j < nb; ++j) {
+            cphnsw::BinaryCodeStorage<64> ca, cb;
+            ca.signs[0] = a[i];
+            cb.signs[0] = b[j];
+            out[i * nb + j] = cphnsw::detail::hamming_primary_scalar<64>(ca, cb);
+        }
+    return 0;
+}
 
 // the reference's load_fvecs / load_ivecs / normalize_vectors; out may be null to query the shape
 int ref_load_fvecs(const char* path, float* out, uint64_t cap, uint64_t* dim, uint64_t* count) {

@@ -36,7 +36,7 @@ EXPORTS = [
     "cphnsw_b200_kernel_time", "cphnsw_b200_code_distance_noalloc", "cphnsw_b200_search_multiprobe_batch",
     "cphnsw_b200_probe_codes", "cphnsw_b200_brute_force_search_batch", "cphnsw_b200_verify_connectivity",
     "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
-    "cphnsw_b200_save", "cphnsw_b200_load", "cphnsw_b200_add_batch",
+    "cphnsw_b200_save", "cphnsw_b200_load", "cphnsw_b200_add_batch", "cphnsw_b200_get_binary_codes",
 ]
 
 
@@ -252,6 +252,12 @@ class CPHNSWIndex:
 
     def get_code(self, node_id):
         return self.codes()[node_id]
+
+    def binary_codes(self):
+        """Sign bits of the stored codes, uint64 [size][(K+63)//64] (the unified index's primary code)."""
+        out = np.zeros((self.size(), (self.K + 63) // 64), np.uint64)
+        _check(self._lib.cphnsw_b200_get_binary_codes(self._h, _p(out)))
+        return out
 
     def adjacency(self):
         out = np.empty((self.size(), self.M), np.uint32)

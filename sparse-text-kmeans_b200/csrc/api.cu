@@ -173,9 +173,14 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
             CPB_CUDA(cudaMemcpyAsync(h->d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
             dq = h->d_q.as<float>();
         }
-        CPB_TRY(h->d_qtables.reserve(m * table_floats * 4));
         CPB_TRY(h->d_qcodes.reserve(m * code_row_bytes(h) + 16));
-        CPB_TRY(launch_encode(h, dq, m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
+        if (h->binary_codes) {
+            // binary-code mode: the walk compares sign-bit codes (Hamming distance), no query table
+            CPB_TRY(launch_encode(h, dq, m, h->d_qcodes.p, nullptr, nullptr, st));
+        } else {
+            CPB_TRY(h->d_qtables.reserve(m * table_floats * 4));
+            CPB_TRY(launch_encode(h, dq, m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
+        }
         uint32_t *o_ids, *o_stats = nullptr;
         float* o_d;
         if (out_on_device) {
@@ -192,8 +197,8 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
                 o_stats = h->d_stats.as<uint32_t>();
             }
         }
-        CPB_TRY(launch_search(h, dq, h->d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st, nullptr,
-                              scan_only));
+        CPB_TRY(launch_search(h, dq, h->d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st,
+                              h->binary_codes ? h->d_qcodes.p : nullptr, scan_only));
         if (calibrated && rerank_k == 0) CPB_TRY(launch_affine(h, o_d, m * k, float(h->calib_alpha), float(h->calib_beta), st));
         if (!out_on_device) {
             CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, o_ids, m * k * 4, cudaMemcpyDeviceToHost, st));
@@ -209,6 +214,10 @@ int do_calibrate(cphnsw_b200_index* h, uint64_t num_samples, uint64_t seed) {
     if (h->n == 0) {
         set_error("calibrate on an empty index");
         return CPHNSW_B200_E_STATE;
+    }
+    if (h->binary_codes) {
+        set_error("calibrate: not available in binary-code mode (the distance is the Hamming distance itself)");
+        return CPHNSW_B200_E_UNSUPPORTED;
     }
     if (num_samples == 0 || num_samples > 65536) {
         set_error("calibrate: num_samples must be in 1..65536");
@@ -264,6 +273,10 @@ int do_multiprobe(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
     if (T == 0 || T > 64) {
         set_error("search_multiprobe: num_probes must be in 1..64 (got %u)", T);
         return CPHNSW_B200_E_INVALID;
+    }
+    if (h->binary_codes) {
+        set_error("search_multiprobe: not available in binary-code mode");
+        return CPHNSW_B200_E_UNSUPPORTED;
     }
     if (!q && nq) {
         set_error("search_multiprobe: null query pointer");
@@ -465,6 +478,12 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         h->search_kernel = int(v);
         return 0;
     }
+    if (s == "binary_codes") {
+        if (v != 0 && v != 1) { set_error("binary_codes must be 0 or 1"); return CPHNSW_B200_E_INVALID; }
+        if (h->n && int(v) != h->binary_codes) { set_error("binary_codes cannot change once vectors have been added"); return CPHNSW_B200_E_STATE; }
+        h->binary_codes = int(v);
+        return 0;
+    }
     if (s == "build_seed") {
         if (v < 0 || v > 2147483647.0) { set_error("build_seed must be in 0..2^31-1 (0 = exact kNN graph over everything)"); return CPHNSW_B200_E_INVALID; }
         h->build_seed = uint32_t(v);
@@ -500,6 +519,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "knn_kernel") *v = h->knn_kernel;
     else if (s == "search_kernel") *v = h->search_kernel;
     else if (s == "build_seed") *v = h->build_seed;
+    else if (s == "binary_codes") *v = h->binary_codes;
     else if (s == "k_entry") *v = h->k_entry;
     else if (s == "knn_k") *v = h->knn_k;
     else if (s == "entry_scan") *v = h->entry_scan;
@@ -633,6 +653,20 @@ int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, ui
     return do_search(h, q, false, nq, k, ef, rerank_k, ids_out, dists_out, nullptr, false, 0, 0, true);
 }
 
+int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out) {
+    if (!h || (!words_out && h->n)) { set_error("get_binary_codes: null argument"); return CPHNSW_B200_E_INVALID; }
+    CPB_TRY(bind(h));
+    const size_t rb = code_row_bytes(h), nw = (h->K + 63) / 64;
+    std::vector<unsigned char> codes(h->n * rb);
+    if (h->n) CPB_CUDA(cudaMemcpy(codes.data(), h->d_codes.p, codes.size(), cudaMemcpyDeviceToHost));
+    for (uint64_t i = 0; i < h->n; ++i) {
+        for (size_t w = 0; w < nw; ++w) words_out[i * nw + w] = 0;
+        for (uint32_t r = 0; r < h->K; ++r)  // the low byte of a component holds its sign bit
+            if (codes[i * rb + size_t(r) * h->comp_bytes] & 1u) words_out[i * nw + r / 64] |= uint64_t(1) << (r % 64);
+    }
+    return 0;
+}
+
 // ---- index file -------------------------------------------------------------------------------------------
 namespace {
 constexpr char kFileMagic[8] = {'C', 'P', 'H', 'N', 'S', 'W', 'B', '2'};
@@ -640,6 +674,7 @@ constexpr uint32_t kFileVersion = 1;
 struct FileHeader {  // after the magic; all little-endian, naturally aligned
     uint32_t version, K, comp_bytes, M, ef_construction, keep_pruned, k_entry, knn_k, entry_scan;
     int32_t convention;
+    uint32_t binary_codes, reserved;
     uint64_t dim, seed, n, calib_samples;
     double calib_alpha, calib_beta, calib_r2;
 };
@@ -674,6 +709,7 @@ int cphnsw_b200_save(cphnsw_b200_index* h, const char* path) {
     FileHeader hd{};
     hd.version = kFileVersion, hd.K = h->K, hd.comp_bytes = h->comp_bytes, hd.M = h->M, hd.ef_construction = h->ef_construction;
     hd.keep_pruned = uint32_t(h->keep_pruned), hd.k_entry = h->k_entry, hd.knn_k = h->knn_k, hd.entry_scan = h->entry_scan;
+    hd.binary_codes = uint32_t(h->binary_codes);
     hd.convention = h->convention, hd.dim = h->dim, hd.seed = h->seed, hd.n = h->n, hd.calib_samples = h->calib_samples;
     hd.calib_alpha = h->calib_alpha, hd.calib_beta = h->calib_beta, hd.calib_r2 = h->calib_r2;
     bool ok = std::fwrite(kFileMagic, 1, 8, fc.f) == 8 && std::fwrite(&hd, sizeof(hd), 1, fc.f) == 1 &&
@@ -717,6 +753,7 @@ int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
     if (std::fread(signs.data(), 1, signs.size(), fc.f) != signs.size()) { set_error("load: file is shorter than its header says"); return CPHNSW_B200_E_INVALID; }
     CPB_TRY(cphnsw_b200_set_sign_tables(h, signs.data()));
     if (hd.k_entry < 1 || hd.k_entry > 100 || hd.knn_k > 64 || hd.entry_scan > 1048576) { set_error("load: corrupt header (tunables)"); return CPHNSW_B200_E_INVALID; }
+    h->binary_codes = hd.binary_codes != 0;
     h->keep_pruned = hd.keep_pruned != 0, h->k_entry = hd.k_entry, h->knn_k = hd.knn_k, h->entry_scan = hd.entry_scan;
     h->calib_alpha = hd.calib_alpha, h->calib_beta = hd.calib_beta, h->calib_r2 = hd.calib_r2, h->calib_samples = hd.calib_samples;
     if (hd.n) {

@@ -79,6 +79,7 @@ struct cphnsw_b200_index {
     uint32_t k_entry = 4, knn_k = 0, entry_scan = 0;
     int knn_kernel = 0;  // 0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance
     int search_kernel = 0;  // 0 = pick, 1 = one warp per query, 2 = two warps per query
+    int binary_codes = 0;  // 1: components keep only the sign bit (Hamming metric), search walks under the code distance
     uint32_t build_seed = 0;  // 0: add_batch_parallel builds the exact kNN graph; else only of this many nodes, the rest inserted
     int sm_count = 0;
 

@@ -380,6 +380,16 @@ __global__ void encode_generic_kernel(const float* __restrict__ x, uint64_t n, i
 
 }  // namespace
 
+// binary-code mode: every component reduced to its sign bit; 32-bit words where the buffer allows
+__global__ void sign_only_kernel(uint32_t* __restrict__ codes, uint64_t words, uint32_t mask) {
+    const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < words) codes[i] &= mask;
+}
+__global__ void sign_only_bytes_kernel(unsigned char* __restrict__ codes, uint64_t bytes, int comp_bytes) {
+    const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < bytes) codes[i] &= (comp_bytes == 2 && (i & 1)) ? 0u : 1u;  // little-endian halfwords: the high byte is cleared
+}
+
 int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_codes, float* d_rot,
                   float* d_mag, cudaStream_t st) {
     if (n == 0) return 0;
@@ -446,6 +456,19 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
     }
     h->launches++;
     CPB_CUDA(cudaGetLastError());
+    if (h->binary_codes && d_codes) {
+        // binary-code mode: a component keeps only its sign bit (the unified encoder's primary code,
+        // include/cphnsw/encoder/cp_encoder.hpp:165-176)
+        const uint64_t bytes = n * uint64_t(K) * h->comp_bytes;
+        if ((reinterpret_cast<uintptr_t>(d_codes) & 3) == 0 && (bytes & 3) == 0)
+            sign_only_kernel<<<unsigned((bytes / 4 + 255) / 256), 256, 0, st>>>(static_cast<uint32_t*>(d_codes), bytes / 4,
+                                                                              h->comp_bytes == 2 ? 0x00010001u : 0x01010101u);
+        else
+            sign_only_bytes_kernel<<<unsigned((bytes + 255) / 256), 256, 0, st>>>(static_cast<unsigned char*>(d_codes), bytes,
+                                                                                 int(h->comp_bytes));
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+    }
     return 0;
 }
 

@@ -56,7 +56,7 @@ __global__ void search_kernel(SearchArgs a) {
     const bool scan_mode = a.scan_only || a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
     const bool coop_ok = !SYM && a.K <= 32;
-    const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm);  // symmetric metric only
+    const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm + a.qvec_floats);  // symmetric metric only
 
     // queries are handed out one at a time from a global counter, so that warps that draw short
     // walks take more of them
@@ -68,7 +68,7 @@ __global__ void search_kernel(SearchArgs a) {
         const float* table = SYM ? nullptr : a.tables + size_t(q) * a.K * a.P;
         if (SYM) {
             const unsigned char* src = static_cast<const unsigned char*>(a.qcodes) + size_t(q) * row_bytes;
-            for (int i = lane; i < row_bytes; i += 32) reinterpret_cast<unsigned char*>(qsm)[i] = src[i];
+            for (int i = lane; i < row_bytes; i += 32) reinterpret_cast<unsigned char*>(qsm + a.qvec_floats)[i] = src[i];
         }
         if (TABLE_SMEM && !SYM) {
             const float4* src = reinterpret_cast<const float4*>(table);
@@ -76,9 +76,9 @@ __global__ void search_kernel(SearchArgs a) {
             for (int i = lane; i < int(table_floats / 4); i += 32) dst[i] = __ldg(src + i);
             table = table_sm;
         }
-        if (a.rerank_k && !SYM) {
+        if (a.rerank_k) {
             const float* qv = a.queries + size_t(q) * a.dim;
-            for (int i = lane; i < int(dim_pad); i += 32) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
+            for (int i = lane; i < int(a.qvec_floats); i += 32) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
         }
         for (int p = lane; p < cap; p += 32) {
             sd[p] = INFINITY;
@@ -314,7 +314,7 @@ __global__ void search_kernel(SearchArgs a) {
         int nsort = 32;
         while (nsort < int(count)) nsort <<= 1;
 
-        if (a.rerank_k && !SYM) {
+        if (a.rerank_k) {
             const uint32_t ncand = min(a.rerank_k, count);
             const int g = lane >> 3, j = lane & 7;
             const bool vec4 = (a.dim & 3) == 0;
@@ -392,7 +392,7 @@ struct LaunchCfg {
     uint32_t cap;
     int warps;
     size_t per_warp;
-    size_t qsm_floats;
+    size_t qsm_floats, qvec_floats;
     bool table_smem;
 };
 
@@ -402,9 +402,10 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
     while (c.cap < beam || c.cap < h->k_entry) c.cap <<= 1;
     const size_t table_bytes = size_t(h->K) * h->P * 4;
     c.table_smem = !sym && table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
-    size_t dim_pad = (size_t(h->dim) + 3) & ~size_t(3);
-    // the query-vector area doubles as the home of the query code under the symmetric metric
-    while (dim_pad * 4 < size_t(h->K) * h->comp_bytes) dim_pad += 4;
+    const size_t qvec = (size_t(h->dim) + 3) & ~size_t(3);
+    // under the symmetric metric the query code follows the query vector
+    size_t dim_pad = qvec + (sym ? ((size_t(h->K) * h->comp_bytes + 15) / 16) * 4 : 0);
+    c.qvec_floats = qvec;
     size_t per_warp = (c.table_smem ? table_bytes : 0) + size_t(c.cap) * 8 + dim_pad * 4;
     per_warp = (per_warp + 15) & ~size_t(15);
     const size_t budget = 226 * 1024;  // of the 227 KB a block may use
@@ -502,6 +503,7 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     SearchArgs a;
     a.qcodes = d_qcodes;
     a.qsm_floats = uint32_t(c.qsm_floats);
+    a.qvec_floats = uint32_t(c.qvec_floats);
     a.tables = d_tables;
     a.queries = d_q;
     a.codes = h->d_codes.p;

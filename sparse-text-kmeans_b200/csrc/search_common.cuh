@@ -28,7 +28,8 @@ struct SearchArgs {
     uint64_t n;
     uint32_t nq;
     int K, P, dim, M, comp_bytes;
-    uint32_t qsm_floats;              // size of the per-warp query area
+    uint32_t qsm_floats;              // size of the per-warp query area: the query vector, then (symmetric metric) the query code
+    uint32_t qvec_floats;             // its first part: the query vector padded to a multiple of 4 floats
     uint32_t per_warp_smem;           // bytes of shared memory per warp (multiple of 16)
     uint32_t beam, cap, k, rerank_k;  // cap: power of two >= max(32, beam, n_seed), the size of W's arrays
     uint8_t* visited;    // [warp slots][vis_stride]: epoch of the last query that visited the node

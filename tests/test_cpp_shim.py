@@ -30,3 +30,28 @@ def test_cpp_qa_protocol(cp):
     print(out.stdout[-3000:], out.stderr[-2000:])
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "ALL PASS" in out.stdout
+
+
+BIN_EXE = os.path.join(ROOT, "tests", "cpp", "binary_check")
+
+
+def compile_binary():
+    lib_dir = os.path.join(ROOT, "sparse-text-kmeans_b200")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    subprocess.check_call([cxx, "-std=c++17", "-O2", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "binary_check.cpp"),
+                           "-L", lib_dir, "-lcphnsw_b200", "-Wl,-rpath," + lib_dir, "-o", BIN_EXE])
+
+
+def test_binary_front_compiles_and_links(cp):
+    compile_binary()
+    assert os.path.exists(BIN_EXE)
+
+
+@pytest.mark.gpu
+def test_binary_front_runs(cp):
+    compile_binary()
+    out = subprocess.run([BIN_EXE], capture_output=True, text=True, timeout=600)
+    print(out.stdout[-3000:], out.stderr[-2000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "ALL PASS" in out.stdout
+

@@ -550,7 +550,7 @@ def test_save_and_load_round_trip(cp, oracle, tmp_path, dim, K, cb, M, n):
         a.calibrate(500, 3)
     path = str(tmp_path / "index.cphnsw")
     a.save(path)
-    assert os.path.getsize(path) == 8 + 96 + K * 3 * a.padded_dim + n * (dim * 4 + K * cb + M * 4)
+    assert os.path.getsize(path) == 8 + 104 + K * 3 * a.padded_dim + n * (dim * 4 + K * cb + M * 4)
     b = cp.CPHNSWIndex.load(path)
     assert (b.dim, b.K, b.M, b.component_bytes, b.size()) == (dim, K, M, cb, n)
     assert np.array_equal(a.sign_tables(), b.sign_tables())
@@ -590,4 +590,79 @@ def test_load_rejects_bad_files(cp, tmp_path):
     with pytest.raises(ValueError):
         idx.save(str(tmp_path / "no_such_dir" / "x"))
     assert idx.search_batch(base[:1], 5, 10)[0].shape == (1, 5)  # still usable
+
+
+# ---- binary-code mode (the unified index's primary sign-bit code, Hamming metric) -------------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,dim,K,cb,M", [(3000, 128, 32, 1, 32), (2000, 96, 64, 1, 16), (800, 200, 16, 2, 8), (40, 128, 7, 1, 32)])
+def test_binary_mode_matches_oracle(cp, oracle, n, dim, K, cb, M):
+    base, q = synthetic.gaussian_mixture(n, 40, dim, max(2, n // 300), 0.3, n + K)
+    idx = make_index(cp, dim, K, cb, M=M)
+    idx.set_param("binary_codes", 1)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 8)
+    idx.add_batch_parallel(base)
+    signs = oracle.sign_tables(dim, K, 42)
+    codes = (oracle.encode(base, K, cb, signs, 2) & 1).astype(idx.code_dtype)
+    qcodes = (oracle.encode(q, K, cb, signs, 2) & 1).astype(idx.code_dtype)
+    assert np.array_equal(idx.codes(), codes)            # components are sign bits
+    assert np.array_equal(idx.encode(q), qcodes)
+    # packed like the unified index's ResidualCode<K,0>::primary.signs
+    packed = np.zeros((n, (K + 63) // 64), np.uint64)
+    for r in range(K):
+        packed[:, r // 64] |= codes[:, r].astype(np.uint64) << np.uint64(r % 64)
+    assert np.array_equal(idx.binary_codes(), packed)
+    # code distance = Hamming distance; the graph is the oracle's under that distance
+    ham = (codes[:50, None, :] != codes[None, :60, :]).sum(axis=2)
+    assert np.array_equal(idx.code_distance(codes[:50], codes[:60]), ham)
+    knn_k = min(64, 2 * M)
+    cand, _ = oracle.knn_graph(codes, knn_k)
+    adj = oracle.select_neighbors(codes, cand, M, True)
+    assert np.array_equal(idx.adjacency(), adj)
+    entry = idx.entry_ids()
+    for k, ef in ((10, 50), (5, 5), (1, 200)):
+        k = min(k, n)
+        ids, dist, stats = idx.search_batch(q, k, ef, want_stats=True)
+        wi, wd = oracle.search_codes(qcodes, codes, adj, entry, max(ef, k), k, n_seed=8)
+        assert np.array_equal(ids, wi) and np.array_equal(dist, wd)
+    # search_and_rerank: Hamming walk, exact rerank of its best rerank_k
+    k, ef, rr = min(10, n), 60, min(40, n)
+    ids, dist = idx.search_and_rerank_batch(q, k, ef, rr)
+    cands, _ = oracle.search_codes(qcodes, codes, adj, entry, max(ef, rr), rr, n_seed=8)
+    wi, wd = oracle.rerank(q, base, cands, k)
+    valid = wi != INVALID
+    assert np.allclose(dist[valid], wd[valid], rtol=1e-5, atol=1e-6) and (ids == wi).mean() > 0.99
+    # brute force ranks all nodes by Hamming distance, ties by id
+    bi, bd = idx.brute_force_search_batch(q[:10], min(20, n))
+    for qi in range(10):
+        d = (codes != qcodes[qi]).sum(axis=1)
+        order = np.lexsort((np.arange(n), d))[: min(20, n)]
+        assert np.array_equal(bi[qi], order.astype(np.uint32)) and np.array_equal(bd[qi], d[order].astype(np.float32))
+    # incremental insertion works on sign-bit codes too
+    extra, _ = synthetic.gaussian_sphere(30, 1, dim, 8)
+    idx.add_batch(extra)
+    assert idx.size() == n + 30 and set(np.unique(idx.codes())) <= {0, 1}
+    with pytest.raises(cp.CPHNSWError):
+        idx.calibrate(100)
+    with pytest.raises(cp.CPHNSWError):
+        idx.search_multiprobe_batch(q, 5, 10, 4)
+    with pytest.raises(cp.CPHNSWError):
+        idx.set_param("binary_codes", 0)  # not once vectors have been added
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("conv", [0, 1, 2])
+@pytest.mark.parametrize("dim", [128, 96, 20])
+def test_binary_codes_match_reference_golden(cp, dim, conv):
+    """Packed sign codes against the fixture written from the reference's own unified encoder
+    (CPEncoder<64,0>, all three FHT builds) and its Hamming kernel (tests/golden/make_binary_golden.py)."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "binary_golden.npz"))
+    x = g["x_%d" % dim]
+    idx = make_index(cp, dim, 64, 1, conv=conv)
+    idx.set_param("binary_codes", 1)
+    idx.add_batch_parallel(x)
+    assert np.array_equal(idx.binary_codes()[:, 0], g["bits_%d_c%d" % (dim, conv)])
+    if dim == 128 and conv == 2:
+        codes = idx.codes()
+        assert np.array_equal(idx.code_distance(codes[:20], codes), g["hamming_128_c2"].astype(np.uint16))
 

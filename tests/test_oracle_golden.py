@@ -81,3 +81,29 @@ def test_live_reference_when_available(oracle, conv):
     bits = ((codes & 1).astype(np.uint64) << np.arange(32, dtype=np.uint64)).sum(axis=1).astype(np.uint32)
     # the reference's shipped encoder keeps exactly the sign bit of each component
     assert np.array_equal(bits, R.encode_batch_signbits32(x, 42))
+
+
+BIN = np.load(os.path.join(os.path.dirname(__file__), "golden", "binary_golden.npz"))
+
+
+def pack64(codes):
+    return ((codes & 1).astype(np.uint64) << np.arange(64, dtype=np.uint64)).sum(axis=1).astype(np.uint64)
+
+
+@pytest.mark.parametrize("conv", CONVS)
+@pytest.mark.parametrize("dim", [128, 96, 20])
+def test_sign_bits_are_the_unified_encoders_code(oracle, dim, conv):
+    """Bit 0 of every component = the primary binary code of the reference's unified encoder
+    (CPEncoder<64,0>, include/cphnsw/encoder/cp_encoder.hpp:161-184), for every FHT build."""
+    x = BIN["x_%d" % dim]
+    codes = oracle.encode(x, 64, 1 if dim <= 128 else 2, oracle.sign_tables(dim, 64, 42), conv)
+    assert np.array_equal(pack64(codes), BIN["bits_%d_c%d" % (dim, conv)])
+
+
+def test_component_mismatch_of_sign_codes_is_the_unified_hamming_distance(oracle):
+    """code_distance on sign-only components = hamming_primary_scalar<64> of the packed codes
+    (include/cphnsw/distance/detail/scalar_kernels.hpp:37-47)."""
+    x = BIN["x_128"]
+    codes = (oracle.encode(x, 64, 1, oracle.sign_tables(128, 64, 42), 2) & 1).astype(np.uint8)
+    assert np.array_equal(oracle.code_distance(codes[:20], codes), BIN["hamming_128_c2"].astype(np.uint16))
+
