@@ -656,14 +656,12 @@ int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, ui
 int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out) {
     if (!h || (!words_out && h->n)) { set_error("get_binary_codes: null argument"); return CPHNSW_B200_E_INVALID; }
     CPB_TRY(bind(h));
-    const size_t rb = code_row_bytes(h), nw = (h->K + 63) / 64;
-    std::vector<unsigned char> codes(h->n * rb);
-    if (h->n) CPB_CUDA(cudaMemcpy(codes.data(), h->d_codes.p, codes.size(), cudaMemcpyDeviceToHost));
-    for (uint64_t i = 0; i < h->n; ++i) {
-        for (size_t w = 0; w < nw; ++w) words_out[i * nw + w] = 0;
-        for (uint32_t r = 0; r < h->K; ++r)  // the low byte of a component holds its sign bit
-            if (codes[i * rb + size_t(r) * h->comp_bytes] & 1u) words_out[i * nw + r / 64] |= uint64_t(1) << (r % 64);
-    }
+    if (h->n == 0) return 0;
+    cphnsw_b200_index* m = const_cast<cphnsw_b200_index*>(h);  // scratch and launch counter only
+    const size_t bytes = h->n * ((h->K + 63) / 64) * 8;
+    CPB_TRY(m->s_out.reserve(bytes));
+    CPB_TRY(launch_pack_sign_bits(m, h->d_codes.p, h->n, m->s_out.as<uint64_t>(), 0));
+    CPB_CUDA(cudaMemcpy(words_out, m->s_out.p, bytes, cudaMemcpyDeviceToHost));
     return 0;
 }
 

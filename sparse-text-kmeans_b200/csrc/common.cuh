@@ -86,7 +86,9 @@ struct cphnsw_b200_index {
     std::vector<int8_t> signs;  // host [K][3][P]
     cpb::DevBuf d_signs;        // float [K][3][P], +-1 with the FHT convention folded into layers 1,2
     cpb::DevBuf d_signbits;     // padded dim 1024 only: the same diagonals bit-packed, uint32 [K][3][32]
-    cpb::DevBuf d_status;       // uint32 status word
+    // uint32 words: 0 status of bounded device waits, 1 query counter of a search launch, 2 "an adjacency
+    // row repeats an id", 4-5 frontier sizes of the connectivity BFS, 6-7 counters of the reverse-edge pass
+    cpb::DevBuf d_status;
 
     // index contents
     uint64_t n = 0;
@@ -146,6 +148,7 @@ int launch_connectivity(cphnsw_b200_index* h, uint64_t* reachable, cudaStream_t 
 int launch_calibration_samples(cphnsw_b200_index* h, const float* d_tables, const uint32_t* d_u, const uint32_t* d_v,
                                uint32_t m, float* d_x, float* d_y, cudaStream_t st);
 int launch_affine(cphnsw_b200_index* h, float* d_dist, uint64_t n, float alpha, float beta, cudaStream_t st);
+int launch_pack_sign_bits(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint64_t* d_out, cudaStream_t st);
 // multiprobe sequence of rotated queries [nq][K][P] -> probe codes [nq][T][K]; merge of per-probe results
 int launch_probe_codes(cphnsw_b200_index* h, const float* d_rotated, uint64_t nq, uint32_t T, void* d_out,
                        cudaStream_t st);

@@ -64,7 +64,33 @@ __global__ void affine_kernel(float* __restrict__ d, uint64_t n, float alpha, fl
     if (v != INFINITY) d[i] = __fadd_rn(__fmul_rn(alpha, v), beta);
 }
 
+// ---- packed sign bits: one thread per (node, 64-bit word); bit r = bit 0 of component r ---------------
+__global__ void pack_sign_bits_kernel(const unsigned char* __restrict__ codes, uint64_t n, int K, int comp_bytes,
+                                      unsigned long long* __restrict__ out) {
+    const int nw = (K + 63) / 64;
+    const uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= n * nw) return;
+    const uint64_t node = t / nw;
+    const int w = int(t % nw);
+    const unsigned char* row = codes + node * uint64_t(K) * comp_bytes;
+    unsigned long long bits = 0;
+    for (int b = 0; b < 64 && w * 64 + b < K; ++b)
+        if (row[size_t(w * 64 + b) * comp_bytes] & 1u) bits |= 1ull << b;  // the low byte of a component holds the sign
+    out[t] = bits;
+}
+
 }  // namespace
+
+int launch_pack_sign_bits(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint64_t* d_out, cudaStream_t st) {
+    const uint64_t threads = n * ((h->K + 63) / 64);
+    if (threads == 0) return 0;
+    pack_sign_bits_kernel<<<unsigned((threads + 255) / 256), 256, 0, st>>>(static_cast<const unsigned char*>(d_codes), n, int(h->K),
+                                                                          int(h->comp_bytes),
+                                                                          reinterpret_cast<unsigned long long*>(d_out));
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
 
 // Number of nodes reachable from the entry nodes (the entry nodes included).
 int launch_connectivity(cphnsw_b200_index* h, uint64_t* reachable, cudaStream_t st) {
