@@ -206,8 +206,7 @@ int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, ui
  * coordinate of rotation r is negative.  Works in both code modes (it is bit 0 of every component). */
 int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out);
 
-/* Index file (the reference has no save/load, SURVEY of its tree: rotation.hpp's get_signs() exists "for
- * serialization" only).  One little-endian file: magic "CPHNSWB2", format version, the constructor
+/* Index file (the reference has no save/load; its rotation.hpp get_signs() exists "for serialization" only).  One little-endian file: magic "CPHNSWB2", format version, the constructor
  * arguments, the tunables, the calibration, then sign tables int8[K][3][padded_dim], vectors
  * float[n][dim], codes ComponentT[n][K], adjacency uint32[n][M].  load creates a new handle on `device`
  * holding exactly the saved index (no re-encoding, no graph rebuild); it can be searched at once and
