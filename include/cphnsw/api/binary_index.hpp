@@ -62,10 +62,8 @@ public:
     static constexpr size_t NUM_WORDS = (K + 63) / 64;  // BinaryCodeStorage<K>::NUM_WORDS, codes.hpp:24
 
     explicit BinaryCPHNSWIndex(const IndexParams& p, int device = 0) : params_(p) {
-        const size_t P = next_pow2(p.dim);
-        check(cphnsw_b200_create(p.dim, uint32_t(K), P > 128 ? 2u : 1u, uint32_t(p.M), uint32_t(p.ef_construction), p.seed,
-                                 CPHNSW_B200_FHT_AVX512, device, &h_));
-        check(cphnsw_b200_set_param(h_, "binary_codes", 1.0));
+        check(cphnsw_b200_create_binary(p.dim, uint32_t(K), uint32_t(p.M), uint32_t(p.ef_construction), p.seed,
+                                        CPHNSW_B200_FHT_AVX512, device, &h_));
     }
     explicit BinaryCPHNSWIndex(size_t dim) : BinaryCPHNSWIndex(IndexParams().set_dim(dim)) {}
     ~BinaryCPHNSWIndex() { cphnsw_b200_destroy(h_); }
@@ -122,11 +120,6 @@ private:
     IndexParams params_;
     cphnsw_b200_index* h_ = nullptr;
 
-    static size_t next_pow2(size_t n) {
-        size_t p = 1;
-        while (p < n) p <<= 1;
-        return p;
-    }
     static void check(int rc) {
         if (rc == 0) return;
         const std::string msg = cphnsw_b200_last_error();

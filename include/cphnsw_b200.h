@@ -61,13 +61,18 @@ int cphnsw_b200_device_count(void);
 int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M,
                        uint32_t ef_construction, uint64_t seed, int fht_convention, int device,
                        cphnsw_b200_index** out);
+/* The same for the unified index's binary codes (CPHNSWIndex<K, 0>, include/cphnsw/api/index.hpp:71-90):
+ * "binary_codes" is on from the start and a component is one byte whatever the dimension (it
+ * holds a sign bit only). */
+int cphnsw_b200_create_binary(uint64_t dim, uint32_t K, uint32_t M, uint32_t ef_construction, uint64_t seed,
+                              int fht_convention, int device, cphnsw_b200_index** out);
 int cphnsw_b200_destroy(cphnsw_b200_index* h);
 
 /* Named tunables (CPHNSWParams fields, types.hpp:374-400, plus build/search knobs):
  *   "keep_pruned" (0/1, default 1), "profile" (0/1, see kernel_time),
  *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
- *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; K = 16/32 with uint8 codes,
- *                 or uint16 codes of padded dim 1024),
+ *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; K = 16/32/64 with uint8 codes or
+ *                 in binary-code mode, K = 16/32 with uint16 codes of padded dim 1024),
  *   "search_kernel" (0 = pick, 1 = one warp per query, 2 = two warps per query; the second needs
  *                    K * padded_dim * 4 <= 32 KB and M <= 32; both return identical results),
  *   "binary_codes" (0/1, before any vector is added: 1 = the unified index's primary binary code

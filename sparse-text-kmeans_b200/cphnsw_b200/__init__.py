@@ -37,6 +37,7 @@ EXPORTS = [
     "cphnsw_b200_probe_codes", "cphnsw_b200_brute_force_search_batch", "cphnsw_b200_verify_connectivity",
     "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
     "cphnsw_b200_save", "cphnsw_b200_load", "cphnsw_b200_add_batch", "cphnsw_b200_get_binary_codes",
+    "cphnsw_b200_create_binary",
 ]
 
 
@@ -110,6 +111,20 @@ class CPHNSWIndex:
         self.dim, self.K, self.M, self.component_bytes = dim, K, M, component_bytes
         self.padded_dim = int(self._lib.cphnsw_b200_padded_dim(self._h))
         self.code_dtype = np.uint8 if component_bytes == 1 else np.uint16
+
+    @classmethod
+    def binary(cls, dim, M=32, ef_construction=200, K=64, seed=42, fht_convention=FHT_AVX512, device=0):
+        """The unified index's binary-code variant: K sign bits per vector, Hamming metric (one-byte
+        components whatever the dimension)."""
+        self = cls.__new__(cls)
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        _check(self._lib.cphnsw_b200_create_binary(_u64(dim), _u32(K), _u32(M), _u32(ef_construction), _u64(seed),
+                                                   C.c_int(fht_convention), C.c_int(device), C.byref(self._h)))
+        self.dim, self.K, self.M, self.component_bytes = dim, K, M, 1
+        self.padded_dim = int(self._lib.cphnsw_b200_padded_dim(self._h))
+        self.code_dtype = np.uint8
+        return self
 
     def save(self, path):
         """Writes the whole index (parameters, sign tables, vectors, codes, adjacency) to one file."""

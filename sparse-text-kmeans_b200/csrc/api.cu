@@ -380,8 +380,8 @@ int cphnsw_b200_device_count(void) {
     return ok;
 }
 
-int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M, uint32_t ef_construction,
-                       uint64_t seed, int fht_convention, int device, cphnsw_b200_index** out) {
+static int create_impl(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M, uint32_t ef_construction,
+                       uint64_t seed, int fht_convention, int device, bool binary, cphnsw_b200_index** out) {
     if (!out) {
         set_error("create: out is null");
         return CPHNSW_B200_E_INVALID;
@@ -405,7 +405,7 @@ int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
     if (fht_convention < 0 || fht_convention > 2) { set_error("unknown fht_convention %d", fht_convention); return CPHNSW_B200_E_INVALID; }
     const uint64_t P = next_pow2(dim);
     // a component holds (index << 1) | sign (types.hpp:88-90)
-    if ((component_bytes == 1 && P > 128) || (component_bytes == 2 && P > 32768)) {
+    if (!binary && ((component_bytes == 1 && P > 128) || (component_bytes == 2 && P > 32768))) {
         set_error("padded dim %llu does not fit a %u-byte component (max %d)", (unsigned long long)P,
                   component_bytes, component_bytes == 1 ? 128 : 32768);
         return CPHNSW_B200_E_INVALID;
@@ -434,6 +434,7 @@ int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
     h->seed = seed;
     h->convention = fht_convention;
     h->device = device;
+    h->binary_codes = binary ? 1 : 0;
     h->sm_count = prop.multiProcessorCount;
     // RotationChain: rotation r is seeded seed + r (include/cphnsw/encoder/rotation.hpp:173-178);
     // each table is drawn layer by layer from mt19937_64 through uniform_int_distribution<int>(0,1)
@@ -454,6 +455,17 @@ int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
     }
     *out = h;
     return 0;
+}
+
+int cphnsw_b200_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M, uint32_t ef_construction,
+                       uint64_t seed, int fht_convention, int device, cphnsw_b200_index** out) {
+    return create_impl(dim, K, component_bytes, M, ef_construction, seed, fht_convention, device, false, out);
+}
+
+// binary-code mode from the start: a component holds a sign bit only, so one byte does for every dimension
+int cphnsw_b200_create_binary(uint64_t dim, uint32_t K, uint32_t M, uint32_t ef_construction, uint64_t seed,
+                              int fht_convention, int device, cphnsw_b200_index** out) {
+    return create_impl(dim, K, 1, M, ef_construction, seed, fht_convention, device, true, out);
 }
 
 int cphnsw_b200_destroy(cphnsw_b200_index* h) {
@@ -742,7 +754,8 @@ int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
     }
     if (hd.n >= 0x80000000ull) { set_error("load: corrupt header (n)"); return CPHNSW_B200_E_INVALID; }
     cphnsw_b200_index* h = nullptr;
-    CPB_TRY(cphnsw_b200_create(hd.dim, hd.K, hd.comp_bytes, hd.M, hd.ef_construction, hd.seed, hd.convention, device, &h));
+    CPB_TRY(create_impl(hd.dim, hd.K, hd.comp_bytes, hd.M, hd.ef_construction, hd.seed, hd.convention, device,
+                        hd.binary_codes != 0, &h));
     struct Guard {
         cphnsw_b200_index* h;
         ~Guard() { delete h; }

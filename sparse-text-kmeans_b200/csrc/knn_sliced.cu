@@ -1,5 +1,6 @@
-// Brute-force code-distance kNN graph with a bit-sliced distance (K = 16 or 32; uint8 components,
-// or uint16 components of an 11-bit code, i.e. padded dim 1024).
+// Brute-force code-distance kNN graph with a bit-sliced distance (K = 16, 32 or 64; uint8 components,
+// uint16 components of an 11-bit code, i.e. padded dim 1024 (K = 16 or 32), or sign-bit codes of the
+// binary-code mode: one plane per component).
 //
 // Same result as knn_graph_kernel in distance.cu (k smallest under (distance, id), self excluded),
 // four times fewer integer instructions per pair.  The candidates are re-laid out once, 32 at a
@@ -140,10 +141,11 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
         const uint32_t valid = group_base >= n ? 0u : (n - group_base >= 32 ? kFull : ((1u << (n - group_base)) - 1u));
 
         // distance planes of the Q rows against this lane's 32 candidates
-        uint32_t ones[kSlQ], twos[kSlQ], fours[kSlQ], eights[kSlQ], sixteens[kSlQ], thirtytwos[kSlQ];
+        uint32_t ones[kSlQ], twos[kSlQ], fours[kSlQ], eights[kSlQ], sixteens[kSlQ], thirtytwos[kSlQ], sixtyfours[kSlQ];
         uint32_t pend8[kSlQ], pend16[kSlQ];
 #pragma unroll
-        for (int q = 0; q < kSlQ; ++q) ones[q] = twos[q] = fours[q] = eights[q] = sixteens[q] = thirtytwos[q] = pend8[q] = pend16[q] = 0;
+        for (int q = 0; q < kSlQ; ++q)
+            ones[q] = twos[q] = fours[q] = eights[q] = sixteens[q] = thirtytwos[q] = sixtyfours[q] = pend8[q] = pend16[q] = 0;
 
 #pragma unroll 1
         for (int blk = 0; blk < NBLK; ++blk) {
@@ -177,7 +179,17 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
                                     if (rr == 7) {
                                         uint32_t e8;
                                         csa(e8, fours[q], fours[q], foursA[q], foursB[q]);
-                                        if (blk & 1) {
+                                        if (NBLK == 8) {
+                                            // 64 rotations: the weight-8 carry of every block ripples into the
+                                            // 8 / 16 / 32 / 64 planes
+                                            const uint32_t c16 = eights[q] & e8;
+                                            eights[q] ^= e8;
+                                            const uint32_t c32 = sixteens[q] & c16;
+                                            sixteens[q] ^= c16;
+                                            const uint32_t c64 = thirtytwos[q] & c32;
+                                            thirtytwos[q] ^= c32;
+                                            sixtyfours[q] ^= c64;
+                                        } else if (blk & 1) {
                                             uint32_t s16;
                                             csa(s16, eights[q], eights[q], pend8[q], e8);
                                             if (NBLK == 2) {
@@ -208,10 +220,10 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
             if (tau[q] > uint32_t(K)) {
                 pass = kFull;
             } else {
-                const uint32_t plane[6] = {ones[q], twos[q], fours[q], eights[q], sixteens[q], thirtytwos[q]};
+                const uint32_t plane[7] = {ones[q], twos[q], fours[q], eights[q], sixteens[q], thirtytwos[q], sixtyfours[q]};
                 uint32_t lt = 0, eq = kFull;
 #pragma unroll
-                for (int b = 5; b >= 0; --b) {
+                for (int b = (NBLK == 8 ? 6 : 5); b >= 0; --b) {
                     if ((tau[q] >> b) & 1u) {
                         lt |= eq & ~plane[b];
                         eq &= plane[b];
@@ -229,13 +241,15 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
                 uint32_t pm = __shfl_sync(kFull, pass, src);
                 const uint32_t p0 = __shfl_sync(kFull, ones[q], src), p1 = __shfl_sync(kFull, twos[q], src),
                                p2 = __shfl_sync(kFull, fours[q], src), p3 = __shfl_sync(kFull, eights[q], src),
-                               p4 = __shfl_sync(kFull, sixteens[q], src), p5 = __shfl_sync(kFull, thirtytwos[q], src);
+                               p4 = __shfl_sync(kFull, sixteens[q], src), p5 = __shfl_sync(kFull, thirtytwos[q], src),
+                               p6 = NBLK == 8 ? __shfl_sync(kFull, sixtyfours[q], src) : 0u;
                 const uint64_t src_base = t * knn::kTile + uint64_t(src) * 32;
                 while (pm) {
                     const int bit = __ffs(pm) - 1;
                     pm &= pm - 1;
                     const uint32_t dd = ((p0 >> bit) & 1u) | (((p1 >> bit) & 1u) << 1) | (((p2 >> bit) & 1u) << 2) |
-                                        (((p3 >> bit) & 1u) << 3) | (((p4 >> bit) & 1u) << 4) | (((p5 >> bit) & 1u) << 5);
+                                        (((p3 >> bit) & 1u) << 3) | (((p4 >> bit) & 1u) << 4) | (((p5 >> bit) & 1u) << 5) |
+                                        (((p6 >> bit) & 1u) << 6);
                     if (dd >= tau[q]) continue;  // tightened by an earlier candidate
                     knn::list_insert<SLOTS>(ld[q], li[q], dd, uint32_t(src_base + bit), lane);
                     tau[q] = knn::list_threshold<SLOTS>(ld[q], k);
@@ -292,17 +306,32 @@ int launch_sliced_slots(cphnsw_b200_index* h, const uint32_t* sliced, const Comp
 
 }  // namespace
 
-// uint8 components (8 planes) or uint16 components of padded dim 1024 (10 index bits + sign = 11 planes)
+// Planes per component: 8 for uint8 codes, 11 for uint16 codes of padded dim 1024 (10 index bits +
+// sign), 1 in binary-code mode (a component is its sign bit).  K = 16, 32 or 64 (64: not with 11 planes).
 bool knn_sliced_supported(const cphnsw_b200_index* h) {
-    if (h->K != 16 && h->K != 32) return false;
-    return h->comp_bytes == 1 || (h->comp_bytes == 2 && h->P == 1024);
+    if (h->K != 16 && h->K != 32 && h->K != 64) return false;
+    if (h->binary_codes) return true;
+    if (h->comp_bytes == 1) return true;
+    return h->comp_bytes == 2 && h->P == 1024 && h->K != 64;
 }
+
+namespace {
+template <typename CompT, int NB, int WARPS>
+int launch_sliced_k(cphnsw_b200_index* h, const uint32_t* sl, const CompT* codes, uint64_t n, uint32_t k, uint64_t rb,
+                    uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    if (h->K == 16) return launch_sliced_slots<CompT, NB, 2, WARPS>(h, sl, codes, n, k, rb, re, nbrs, dist, st);
+    if (h->K == 32) return launch_sliced_slots<CompT, NB, 4, WARPS>(h, sl, codes, n, k, rb, re, nbrs, dist, st);
+    if constexpr (NB <= 8) return launch_sliced_slots<CompT, NB, 8, WARPS>(h, sl, codes, n, k, rb, re, nbrs, dist, st);
+    set_error("bit-sliced kNN: K = 64 is not available with 11-plane components");
+    return CPHNSW_B200_E_UNSUPPORTED;
+}
+}  // namespace
 
 int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
                             uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, cudaStream_t st) {
     const int K = int(h->K);
     const bool u16 = h->comp_bytes == 2;
-    const int NB = u16 ? 11 : 8;
+    const int NB = h->binary_codes ? 1 : (u16 ? 11 : 8);
     const uint64_t tiles = (n + knn::kTile - 1) / knn::kTile;
     const uint64_t n_groups = tiles * 32;
     const size_t sliced_bytes = size_t(tiles) * K * NB * 32 * 4;
@@ -322,12 +351,12 @@ int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t 
     const uint32_t* sl = h->s_sliced.as<uint32_t>();
     if (u16) {
         const uint16_t* codes = static_cast<const uint16_t*>(d_codes);
-        if (K == 16) return launch_sliced_slots<uint16_t, 11, 2, 8>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
-        return launch_sliced_slots<uint16_t, 11, 4, 8>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+        if (NB == 1) return launch_sliced_k<uint16_t, 1, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+        return launch_sliced_k<uint16_t, 11, 8>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
     }
     const uint8_t* codes = static_cast<const uint8_t*>(d_codes);
-    if (K == 16) return launch_sliced_slots<uint8_t, 8, 2, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
-    return launch_sliced_slots<uint8_t, 8, 4, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    if (NB == 1) return launch_sliced_k<uint8_t, 1, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    return launch_sliced_k<uint8_t, 8, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
 }
 
 }  // namespace cpb

@@ -98,12 +98,13 @@ def clustered_codes(oracle, n, dim, K, cb, seed):
                                           (1000, 32, 32, 1, 128), (2500, 64, 32, 1, 128), (3000, 10, 16, 1, 64),
                                           (1500, 32, 32, 2, 256), (1200, 100, 32, 1, 128), (900, 16, 12, 1, 32),
                                           (5000, 32, 32, 1, 96), (2100, 20, 16, 1, 128), (1025, 64, 32, 1, 128),
-                                          (1300, 32, 32, 2, 960), (1100, 70, 16, 2, 1000)])
+                                          (1300, 32, 32, 2, 960), (1100, 70, 16, 2, 1000), (2300, 64, 64, 1, 128),
+                                          (700, 100, 64, 1, 100)])
 @pytest.mark.parametrize("kernel", [1, 2])  # byte-wise and bit-sliced distance
 def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim, kernel):
     _, codes = clustered_codes(oracle, n, dim, K, cb, n + k)
     idx = make_index(cp, dim, K, cb)
-    sliced_ok = K in (16, 32) and (cb == 1 or idx.padded_dim == 1024)
+    sliced_ok = (K in (16, 32, 64) and cb == 1) or (K in (16, 32) and idx.padded_dim == 1024)
     if kernel == 2 and not sliced_ok:
         idx.set_param("knn_kernel", 2)
         with pytest.raises(cp.CPHNSWError):
@@ -665,4 +666,49 @@ def test_binary_codes_match_reference_golden(cp, dim, conv):
     if dim == 128 and conv == 2:
         codes = idx.codes()
         assert np.array_equal(idx.code_distance(codes[:20], codes), g["hamming_128_c2"].astype(np.uint16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("K,cb,dim", [(16, 1, 64), (32, 1, 128), (64, 1, 128), (32, 2, 300), (32, 2, 1024), (24, 1, 128)])
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_binary_knn_graph_both_kernels(cp, oracle, K, cb, dim, kernel):
+    """Sign-bit codes: the bit-sliced kernel runs with one plane per component (K = 16, 32, 64)."""
+    n, k = 2200, 48
+    _, codes = clustered_codes(oracle, n, dim, K, cb, 7 * K + dim)
+    codes = (codes & 1).astype(codes.dtype)
+    idx = make_index(cp, dim, K, cb)
+    idx.set_param("binary_codes", 1)
+    idx.set_param("knn_kernel", kernel)
+    if kernel == 2 and K not in (16, 32, 64):
+        with pytest.raises(cp.CPHNSWError):
+            idx.knn_graph(codes, k)
+        return
+    nbrs, dist = idx.knn_graph(codes, k)
+    wn, wd = oracle.knn_graph(codes, k)
+    assert np.array_equal(nbrs, wn) and np.array_equal(dist, wd)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,K", [(300, 64), (960, 32), (128, 64)])
+def test_binary_index_any_dimension(cp, oracle, dim, K):
+    """create_binary: one-byte sign components whatever the padded dimension; codes, graph and walk
+    equal the oracle's on sign codes."""
+    n = 1500
+    base, q = synthetic.gaussian_mixture(n, 20, dim, 6, 0.3, dim + K)
+    idx = cp.CPHNSWIndex.binary(dim, K=K, M=16)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 8)
+    assert idx.get_param("binary_codes") == 1 and idx.get_param("component_bytes") == 1
+    idx.add_batch(base)
+    signs = oracle.sign_tables(dim, K, 42)
+    cb = 1 if idx.padded_dim <= 128 else 2
+    codes = (oracle.encode(base, K, cb, signs, 2) & 1).astype(np.uint8)
+    qcodes = (oracle.encode(q, K, cb, signs, 2) & 1).astype(np.uint8)
+    assert np.array_equal(idx.codes(), codes)
+    cand, _ = oracle.knn_graph(codes, 32)
+    adj = oracle.select_neighbors(codes, cand, 16, True)
+    assert np.array_equal(idx.adjacency(), adj)
+    ids, dist = idx.search_batch(q, 10, 80)
+    wi, wd = oracle.search_codes(qcodes, codes, adj, idx.entry_ids(), 80, 10, n_seed=8)
+    assert np.array_equal(ids, wi) and np.array_equal(dist, wd)
 
