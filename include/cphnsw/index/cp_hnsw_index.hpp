@@ -143,6 +143,25 @@ public:
     }
     void add_batch(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch(h_, vecs, n)); }
     void add_batch_parallel(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch_parallel(h_, vecs, n)); }
+    // build_with_gpu_knn (evaluation/test_gpu_build.cpp:168-174): bulk build from a k-candidate kNN graph
+    // (CP-code distance), pruned to M links by select_neighbors or, with prune = false, cut to the M
+    // nearest.  alpha is the legacy detour threshold (types.hpp:399-400); its pruning rule is not in the
+    // reference tree, so it is range-checked like CPHNSWParams::finalize() does and select_neighbors
+    // (the HNSW heuristic with keep_pruned) decides the links.
+    void build_with_gpu_knn(const Float* vecs, size_t n, size_t k = 64, bool prune = true, float alpha = 1.1f) {
+        if (alpha < 1.0f || alpha > 3.0f) throw std::invalid_argument("build_with_gpu_knn: alpha must be in [1.0, 3.0]");
+        if (k == 0 || k > 64) throw std::invalid_argument("build_with_gpu_knn: k must be in 1..64");
+        if (size() != 0) throw std::invalid_argument("build_with_gpu_knn: the index must be empty");
+        double old_k = 0, old_prune = 1;
+        check(cphnsw_b200_get_param(h_, "knn_k", &old_k));
+        check(cphnsw_b200_get_param(h_, "prune", &old_prune));
+        check(cphnsw_b200_set_param(h_, "knn_k", double(k)));
+        check(cphnsw_b200_set_param(h_, "prune", prune ? 1.0 : 0.0));
+        const int rc = cphnsw_b200_add_batch_parallel(h_, vecs, n);
+        cphnsw_b200_set_param(h_, "knn_k", old_k);
+        cphnsw_b200_set_param(h_, "prune", old_prune);
+        check(rc);
+    }
 
     // ---- search ---------------------------------------------------------------------------------
     std::vector<SearchResult> search(const Float* q, size_t k, size_t ef) const {

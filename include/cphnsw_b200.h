@@ -70,6 +70,8 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
 
 /* Named tunables (CPHNSWParams fields, types.hpp:374-400, plus build/search knobs):
  *   "keep_pruned" (0/1, default 1), "profile" (0/1, see kernel_time),
+ *   "prune" (0/1, default 1: the bulk build runs select_neighbors on the kNN candidates; 0 = the M nearest
+ *            candidates are the links, build_with_gpu_knn(..., prune = false), evaluation/test_gpu_build.cpp:168-174),
  *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
  *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; K = 16/32/64 with uint8 codes or
  *                 in binary-code mode, K = 16/32 with uint16 codes of padded dim 1024),

@@ -129,8 +129,15 @@ int build_graph(cphnsw_b200_index* h, cudaStream_t st) {
     uint32_t k = h->knn_k ? h->knn_k : (2 * h->M < 64 ? 2 * h->M : 64);
     if (k < h->M) k = h->M;
     if (k > 64) k = 64;
-    CPB_TRY(h->s_out.reserve(size_t(n) * k * 4 + 16));
     CPB_TRY(h->d_adj.reserve(size_t(n) * h->M * 4 + 16));
+    if (!h->prune) {
+        // build_with_gpu_knn(..., prune = false): the M nearest by (code distance, id) are the links
+        CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, h->M, 0, n, h->d_adj.as<uint32_t>(), nullptr, st));
+        CPB_CUDA(cudaStreamSynchronize(st));
+        CPB_TRY(check_status(h));
+        return set_entry_ids(h);
+    }
+    CPB_TRY(h->s_out.reserve(size_t(n) * k * 4 + 16));
     CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, k, 0, n, h->s_out.as<uint32_t>(), nullptr, st));
     CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n, h->s_out.as<uint32_t>(), k, 0, n, h->M, h->keep_pruned,
                                     h->d_adj.as<uint32_t>(), st));
@@ -479,6 +486,7 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
     if (!h || !name) { set_error("set_param: null argument"); return CPHNSW_B200_E_INVALID; }
     std::string s(name);
     if (s == "keep_pruned") { h->keep_pruned = v != 0.0; return 0; }
+    if (s == "prune") { h->prune = v != 0.0; return 0; }
     if (s == "profile") { h->profile = v != 0.0; return 0; }
     if (s == "knn_kernel") {
         if (v != 0 && v != 1 && v != 2) { set_error("knn_kernel must be 0 (pick), 1 (byte-wise) or 2 (bit-sliced)"); return CPHNSW_B200_E_INVALID; }
@@ -527,6 +535,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     if (!h || !name || !v) { set_error("get_param: null argument"); return CPHNSW_B200_E_INVALID; }
     std::string s(name);
     if (s == "keep_pruned") *v = h->keep_pruned;
+    else if (s == "prune") *v = h->prune;
     else if (s == "profile") *v = h->profile;
     else if (s == "knn_kernel") *v = h->knn_kernel;
     else if (s == "search_kernel") *v = h->search_kernel;

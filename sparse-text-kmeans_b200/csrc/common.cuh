@@ -76,6 +76,7 @@ struct cphnsw_b200_index {
     int convention = CPHNSW_B200_FHT_AVX512;
     int device = 0;
     int keep_pruned = 1;
+    int prune = 1;  // 0: the bulk build keeps the M nearest kNN candidates instead of running select_neighbors
     uint32_t k_entry = 4, knn_k = 0, entry_scan = 0;
     int knn_kernel = 0;  // 0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance
     int search_kernel = 0;  // 0 = pick, 1 = one warp per query, 2 = two warps per query

@@ -712,3 +712,21 @@ def test_binary_index_any_dimension(cp, oracle, dim, K):
     wi, wd = oracle.search_codes(qcodes, codes, adj, idx.entry_ids(), 80, 10, n_seed=8)
     assert np.array_equal(ids, wi) and np.array_equal(dist, wd)
 
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,M", [(1200, 16), (20, 32)])
+def test_bulk_build_without_pruning_keeps_the_nearest(cp, oracle, n, M):
+    """prune = 0 (build_with_gpu_knn(..., prune = false)): the links are the M nearest by (code distance, id)."""
+    base, q = synthetic.gaussian_mixture(n, 10, 64, 5, 0.3, 77)
+    idx = cp.CPHNSWIndex(64, K=16, M=M)
+    idx.set_param("prune", 0)
+    assert idx.get_param("prune") == 0
+    idx.add_batch_parallel(base)
+    codes = oracle.encode(base, 16, 1, oracle.sign_tables(64, 16, 42), 2)
+    cand, _ = oracle.knn_graph(codes, M)
+    assert np.array_equal(idx.adjacency(), cand)
+    _, rot, _ = idx.encode_queries(q)
+    ids, dist = idx.search_batch(q, 5, 40)
+    wi, wd = oracle.search(rot, codes, cand, idx.entry_ids(), 40, 5, n_seed=min(4, n))
+    assert np.array_equal(ids, wi) and np.array_equal(dist, wd)
