@@ -273,17 +273,15 @@ def run_b200(args):
     for kind in ("encode", "knn_graph", "select_neighbors"):
         idx.kernel_time(kind)  # reset the per-kernel records
 
-    # ---- ground truth for this rank's queries: exact cosine top-k (fp32 matmul, measurement support) ----
+    # ---- ground truth for this rank's queries: exact top-k by (-<q,x>, id) (exact_topk_kernel; measurement support) ----
     d_q = torch.from_numpy(queries).to(dev)
-    torch.backends.cuda.matmul.allow_tf32 = False
     n_gt = min(nq, 10_000)  # recall is measured on the first 10,000 queries of the rank
-    gt = torch.empty((n_gt, k), dtype=torch.int64, device=dev)
-    gt_chunk = 1024 if n <= 2_000_000 else 128
-    for q0 in range(0, n_gt, gt_chunk):
-        sims = d_q[q0:min(n_gt, q0 + gt_chunk)] @ d_base.T
-        gt[q0:q0 + sims.shape[0]] = sims.topk(k, dim=1).indices
-    gt = gt.cpu().numpy()
-    del sims
+    d_gt = torch.empty((n_gt, k), dtype=torch.int32, device=dev)
+    d_gt_dist = torch.empty((n_gt, k), dtype=torch.float32, device=dev)
+    idx.exact_search_dev(d_base.data_ptr(), n, d_q.data_ptr(), n_gt, k, d_gt.data_ptr(), d_gt_dist.data_ptr())
+    torch.cuda.synchronize()
+    gt = d_gt.cpu().numpy().view(np.uint32).astype(np.int64)
+    del d_gt, d_gt_dist
 
     d_ids = torch.empty((nq, k), dtype=torch.int32, device=dev)
     d_dist = torch.empty((nq, k), dtype=torch.float32, device=dev)

@@ -189,6 +189,19 @@ int cphnsw_b200_search_multiprobe_batch(cphnsw_b200_index* h, const float* q, ui
  * among all stored nodes, ascending by (score, id); no graph involved. */
 int cphnsw_b200_brute_force_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                                          uint32_t* ids_out, float* dists_out);
+/* Exact search and rerank on fp32 vectors: GPUBruteForce (include/cphnsw/cuda/gpu_encoder.cuh:101-156;
+ * src/cuda/gpu_encoder.cu:554-664) and the harness's compute_ground_truth
+ * (evaluation/datasets/dataset_loader.hpp:187-212).  distance = -<q,x>, the dot product accumulated in
+ * fp32 in d order; results ascending by (distance, id), rows padded with (CPHNSW_B200_INVALID_NODE, +inf);
+ * k <= 128.  They run over the index's stored vectors unless set_exact_base gave others
+ * (GPUBruteForce::set_base_vectors; float[n][dim] with the handle's dim, copied to the device; n = 0
+ * drops them again).  rerank (GPUBruteForce::rerank): the k best of cand[nq][num_cand]; ids >= n and
+ * CPHNSW_B200_INVALID_NODE are skipped. */
+int cphnsw_b200_set_exact_base(cphnsw_b200_index* h, const float* base, uint64_t n);
+int cphnsw_b200_exact_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
+                                   uint32_t* ids_out, float* dists_out);
+int cphnsw_b200_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, const uint32_t* cand,
+                             uint32_t num_cand, uint32_t k, uint32_t* ids_out, float* dists_out);
 /* CPHNSWIndex::verify_connectivity() (evaluation/eval_main.cpp:52, eval_sift.cpp:266): number of
  * nodes reachable from the entry nodes along the directed adjacency, entry nodes included. */
 int cphnsw_b200_verify_connectivity(cphnsw_b200_index* h, uint64_t* reachable_out);
@@ -246,6 +259,9 @@ int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const 
 int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, uint32_t k, uint32_t ef,
                            uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
                            void* stream);
+/* exact_search over d_base float[n][dim] (device) for d_q float[nq][dim]; outputs device uint32[nq][k] / float[nq][k]. */
+int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint64_t n, const float* d_q,
+                                 uint64_t nq, uint32_t k, uint32_t* d_ids, float* d_dists, void* stream);
 /* Code distance for callers that cannot allocate device memory.  No counterpart in the reference.
  *
  * Some hosts of this library run under a fixed memory plan: a serving process whose device memory

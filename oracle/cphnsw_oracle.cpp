@@ -512,10 +512,10 @@ int orc_rerank(const float* queries, uint64_t nq, uint64_t dim, const float* bas
     return 0;
 }
 
-// Exact cosine ground truth for unit vectors (evaluation/datasets/dataset_loader.hpp:187-212):
-// top-k by (-dot, id).
+// Exact cosine ground truth for unit vectors (evaluation/datasets/dataset_loader.hpp:187-212;
+// GPUBruteForce::search, src/cuda/gpu_encoder.cu:554-603): top-k by (-dot, id); out_dist may be null.
 int orc_ground_truth(const float* queries, uint64_t nq, const float* base, uint64_t n, uint64_t dim,
-                     uint64_t k, uint32_t* out_ids) {
+                     uint64_t k, uint32_t* out_ids, float* out_dist) {
 #pragma omp parallel for schedule(dynamic, 1)
     for (int64_t q = 0; q < (int64_t)nq; ++q) {
         std::vector<Cand> best;
@@ -527,7 +527,10 @@ int orc_ground_truth(const float* queries, uint64_t nq, const float* base, uint6
             best.insert(std::upper_bound(best.begin(), best.end(), c), c);
             if (best.size() > k) best.pop_back();
         }
-        for (size_t t = 0; t < k; ++t) out_ids[(size_t)q * k + t] = t < best.size() ? best[t].second : kInvalid;
+        for (size_t t = 0; t < k; ++t) {
+            out_ids[(size_t)q * k + t] = t < best.size() ? best[t].second : kInvalid;
+            if (out_dist) out_dist[(size_t)q * k + t] = t < best.size() ? best[t].first : INFINITY;
+        }
     }
     return 0;
 }

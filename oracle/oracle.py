@@ -176,13 +176,15 @@ def rerank(queries, base, cand, k):
     return ids, dist
 
 
-def ground_truth(queries, base, k):
+def ground_truth(queries, base, k, want_dist=False):
     queries = np.ascontiguousarray(queries, np.float32)
     base = np.ascontiguousarray(base, np.float32)
     ids = np.empty((queries.shape[0], k), np.uint32)
+    dist = np.empty((queries.shape[0], k), np.float32) if want_dist else None
     lib().orc_ground_truth(_ptr(queries), C.c_uint64(queries.shape[0]), _ptr(base),
-                           C.c_uint64(base.shape[0]), C.c_uint64(base.shape[1]), C.c_uint64(k), _ptr(ids))
-    return ids
+                           C.c_uint64(base.shape[0]), C.c_uint64(base.shape[1]), C.c_uint64(k), _ptr(ids),
+                           _ptr(dist) if want_dist else None)
+    return (ids, dist) if want_dist else ids
 
 
 def brute_force(rotated, codes, k):

@@ -37,7 +37,8 @@ EXPORTS = [
     "cphnsw_b200_probe_codes", "cphnsw_b200_brute_force_search_batch", "cphnsw_b200_verify_connectivity",
     "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
     "cphnsw_b200_save", "cphnsw_b200_load", "cphnsw_b200_add_batch", "cphnsw_b200_get_binary_codes",
-    "cphnsw_b200_create_binary",
+    "cphnsw_b200_create_binary", "cphnsw_b200_set_exact_base", "cphnsw_b200_exact_search_batch",
+    "cphnsw_b200_rerank_batch", "cphnsw_b200_exact_search_dev",
 ]
 
 
@@ -317,6 +318,40 @@ class CPHNSWIndex:
     def brute_force_search(self, q, k):
         ids, dist = self.brute_force_search_batch(np.asarray(q, np.float32)[None, :], k)
         return [(int(i), float(d)) for i, d in zip(ids[0], dist[0]) if i != INVALID_NODE]
+
+    def set_exact_base(self, base):
+        """Vectors for exact_search / rerank to run over instead of the index's own (None drops them)."""
+        if base is None:
+            _check(self._lib.cphnsw_b200_set_exact_base(self._h, None, _u64(0)))
+            return
+        base = self._vecs(base)
+        _check(self._lib.cphnsw_b200_set_exact_base(self._h, _p(base), _u64(base.shape[0])))
+
+    def exact_search_batch(self, q, k):
+        """Exact top-k by (-<q,x>, id) over the stored vectors (or the exact base): ground truth."""
+        q = self._vecs(q)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        _check(self._lib.cphnsw_b200_exact_search_batch(self._h, _p(q), _u64(nq), _u32(k), _p(ids), _p(dist)))
+        return ids, dist
+
+    def rerank_batch(self, q, cand, k):
+        """The k best of cand[nq][num_cand] by (-<q,x>, id)."""
+        q = self._vecs(q)
+        cand = np.ascontiguousarray(cand, np.uint32)
+        nq = q.shape[0]
+        if cand.ndim != 2 or cand.shape[0] != nq:
+            raise ValueError("cand must be [nq][num_cand]")
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        _check(self._lib.cphnsw_b200_rerank_batch(self._h, _p(q), _u64(nq), _p(cand), _u32(cand.shape[1]), _u32(k), _p(ids),
+                                                  _p(dist)))
+        return ids, dist
+
+    def exact_search_dev(self, d_base, n, d_q, nq, k, d_ids, d_dists, stream=0):
+        _check(self._lib.cphnsw_b200_exact_search_dev(self._h, C.c_void_p(d_base), _u64(n), C.c_void_p(d_q), _u64(nq), _u32(k),
+                                                      C.c_void_p(d_ids), C.c_void_p(d_dists), C.c_void_p(stream)))
 
     def verify_connectivity(self):
         """Number of nodes reachable from the entry nodes along the directed adjacency."""

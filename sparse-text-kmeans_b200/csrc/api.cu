@@ -640,6 +640,80 @@ int cphnsw_b200_brute_force_search_batch(cphnsw_b200_index* h, const float* q, u
     return do_search(h, q, false, nq, k, k, 0, ids_out, dists_out, nullptr, false, 0, 1);
 }
 
+// the vectors exact_search / rerank run over: those of set_exact_base if any, else the index's own
+static const float* exact_vectors(cphnsw_b200_index* h, uint64_t* n) {
+    if (h->n_exact) {
+        *n = h->n_exact;
+        return h->d_exact_base.as<float>();
+    }
+    *n = h->n;
+    return h->d_vectors.as<float>();
+}
+
+int cphnsw_b200_set_exact_base(cphnsw_b200_index* h, const float* base, uint64_t n) {
+    CPB_TRY(bind(h));
+    if (n == 0) {
+        h->d_exact_base.release();
+        h->n_exact = 0;
+        return 0;
+    }
+    if (!base) { set_error("set_exact_base: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (n >= kInvalidNode) { set_error("set_exact_base: at most 2^32 - 2 vectors"); return CPHNSW_B200_E_INVALID; }
+    h->n_exact = 0;
+    CPB_TRY(h->d_exact_base.reserve(n * h->dim * sizeof(float)));
+    CPB_CUDA(cudaMemcpy(h->d_exact_base.p, base, n * h->dim * sizeof(float), cudaMemcpyHostToDevice));
+    h->n_exact = n;
+    return 0;
+}
+
+int cphnsw_b200_exact_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t* ids_out,
+                                   float* dists_out) {
+    CPB_TRY(bind(h));
+    if (nq == 0) return 0;
+    if (!q || !ids_out || !dists_out) { set_error("exact_search: null pointer"); return CPHNSW_B200_E_INVALID; }
+    uint64_t n = 0;
+    const float* base = exact_vectors(h, &n);
+    if (n == 0) { set_error("exact_search: no vectors (empty index and no exact base)"); return CPHNSW_B200_E_STATE; }
+    CPB_TRY(h->s_in.reserve(nq * h->dim * sizeof(float)));
+    CPB_TRY(h->s_out.reserve(nq * k * 4 + 16));
+    CPB_TRY(h->s_out2.reserve(nq * k * 4 + 16));
+    CPB_CUDA(cudaMemcpy(h->s_in.p, q, nq * h->dim * sizeof(float), cudaMemcpyHostToDevice));
+    CPB_TRY(launch_exact_search(h, base, n, h->s_in.as<float>(), nq, k, h->s_out.as<uint32_t>(), h->s_out2.as<float>(), 0));
+    CPB_CUDA(cudaMemcpy(ids_out, h->s_out.p, nq * k * 4, cudaMemcpyDeviceToHost));
+    CPB_CUDA(cudaMemcpy(dists_out, h->s_out2.p, nq * k * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint64_t n, const float* d_q, uint64_t nq,
+                                 uint32_t k, uint32_t* d_ids, float* d_dists, void* stream) {
+    CPB_TRY(bind(h));
+    if (nq == 0) return 0;
+    if ((n && !d_base) || !d_q || !d_ids || !d_dists) { set_error("exact_search: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (n >= kInvalidNode) { set_error("exact_search: at most 2^32 - 2 vectors"); return CPHNSW_B200_E_INVALID; }
+    return launch_exact_search(h, d_base, n, d_q, nq, k, d_ids, d_dists, (cudaStream_t)stream);
+}
+
+int cphnsw_b200_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, const uint32_t* cand, uint32_t num_cand,
+                             uint32_t k, uint32_t* ids_out, float* dists_out) {
+    CPB_TRY(bind(h));
+    if (nq == 0) return 0;
+    if (!q || (num_cand && !cand) || !ids_out || !dists_out) { set_error("rerank: null pointer"); return CPHNSW_B200_E_INVALID; }
+    uint64_t n = 0;
+    const float* base = exact_vectors(h, &n);
+    if (n == 0) { set_error("rerank: no vectors (empty index and no exact base)"); return CPHNSW_B200_E_STATE; }
+    CPB_TRY(h->s_in.reserve(nq * h->dim * sizeof(float)));
+    CPB_TRY(h->s_in2.reserve(nq * uint64_t(num_cand) * 4 + 16));
+    CPB_TRY(h->s_out.reserve(nq * k * 4 + 16));
+    CPB_TRY(h->s_out2.reserve(nq * k * 4 + 16));
+    CPB_CUDA(cudaMemcpy(h->s_in.p, q, nq * h->dim * sizeof(float), cudaMemcpyHostToDevice));
+    if (num_cand) CPB_CUDA(cudaMemcpy(h->s_in2.p, cand, nq * uint64_t(num_cand) * 4, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_rerank(h, base, n, h->s_in.as<float>(), nq, h->s_in2.as<uint32_t>(), num_cand, k, h->s_out.as<uint32_t>(),
+                          h->s_out2.as<float>(), 0));
+    CPB_CUDA(cudaMemcpy(ids_out, h->s_out.p, nq * k * 4, cudaMemcpyDeviceToHost));
+    CPB_CUDA(cudaMemcpy(dists_out, h->s_out2.p, nq * k * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 int cphnsw_b200_verify_connectivity(cphnsw_b200_index* h, uint64_t* reachable_out) {
     CPB_TRY(bind(h));
     if (!reachable_out) { set_error("verify_connectivity: null pointer"); return CPHNSW_B200_E_INVALID; }

@@ -95,6 +95,8 @@ struct cphnsw_b200_index {
     uint64_t n = 0;
     std::vector<float> h_vectors;  // host copy of everything added (rebuilds append to it)
     cpb::DevBuf d_vectors, d_codes, d_adj, d_entry, d_entry_codes;
+    cpb::DevBuf d_exact_base;  // vectors given to set_exact_base (exact_search / rerank run over them instead of d_vectors)
+    uint64_t n_exact = 0;
     uint32_t n_entry = 0;
     uint64_t vis_stride = 0;  // bytes per warp slot of d_visited
     int adj_rows_distinct = 0;  // no adjacency row lists a node twice (scan_adjacency_rows)
@@ -150,6 +152,11 @@ int launch_calibration_samples(cphnsw_b200_index* h, const float* d_tables, cons
                                uint32_t m, float* d_x, float* d_y, cudaStream_t st);
 int launch_affine(cphnsw_b200_index* h, float* d_dist, uint64_t n, float alpha, float beta, cudaStream_t st);
 int launch_pack_sign_bits(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint64_t* d_out, cudaStream_t st);
+// exact inner-product top-k and rerank over fp32 vectors (exact.cu)
+int launch_exact_search(cphnsw_b200_index* h, const float* d_base, uint64_t n, const float* d_q, uint64_t nq, uint32_t k,
+                        uint32_t* d_ids, float* d_dist, cudaStream_t st);
+int launch_rerank(cphnsw_b200_index* h, const float* d_base, uint64_t n, const float* d_q, uint64_t nq, const uint32_t* d_cand,
+                  uint32_t num_cand, uint32_t k, uint32_t* d_ids, float* d_dist, cudaStream_t st);
 // multiprobe sequence of rotated queries [nq][K][P] -> probe codes [nq][T][K]; merge of per-probe results
 int launch_probe_codes(cphnsw_b200_index* h, const float* d_rotated, uint64_t nq, uint32_t T, void* d_out,
                        cudaStream_t st);

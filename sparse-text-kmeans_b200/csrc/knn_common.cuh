@@ -50,15 +50,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // The running list of one query row: element of rank (s*32 + lane) sits in slot s of lane
 // `lane`, ascending by (distance, id); unused places hold (0xFFFFFFFF, no node).
-// Inserts (dd, id), known to every lane, where id is larger than every id already kept (rows are
-// swept in ascending candidate order): its rank is the number of kept elements with distance
-// <= dd.  The last element falls off.
+// list_place puts (dd, id), known to every lane, at rank p (warp-uniform) and moves the elements
+// of rank >= p one place down; the last element falls off.
 template <int SLOTS>
-__device__ __forceinline__ void list_insert(uint32_t (&ld)[SLOTS], uint32_t (&li)[SLOTS], uint32_t dd, uint32_t id,
-                                            int lane) {
-    int p = 0;
-#pragma unroll
-    for (int s = 0; s < SLOTS; ++s) p += __popc(__ballot_sync(kFull, ld[s] <= dd));
+__device__ __forceinline__ void list_place(uint32_t (&ld)[SLOTS], uint32_t (&li)[SLOTS], int p, uint32_t dd, uint32_t id,
+                                           int lane) {
 #pragma unroll
     for (int s = SLOTS - 1; s >= 0; --s) {
         uint32_t ud = __shfl_up_sync(kFull, ld[s], 1);
@@ -80,6 +76,27 @@ __device__ __forceinline__ void list_insert(uint32_t (&ld)[SLOTS], uint32_t (&li
             li[s] = id;
         }
     }
+}
+
+// Inserts (dd, id) where id is larger than every id already kept (rows are swept in ascending
+// candidate order): its rank is the number of kept elements with distance <= dd.
+template <int SLOTS>
+__device__ __forceinline__ void list_insert(uint32_t (&ld)[SLOTS], uint32_t (&li)[SLOTS], uint32_t dd, uint32_t id,
+                                            int lane) {
+    int p = 0;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) p += __popc(__ballot_sync(kFull, ld[s] <= dd));
+    list_place<SLOTS>(ld, li, p, dd, id, lane);
+}
+
+// The same for ids in any order: the rank is the number of kept elements below (dd, id).
+template <int SLOTS>
+__device__ __forceinline__ int list_rank_keyed(const uint32_t (&ld)[SLOTS], const uint32_t (&li)[SLOTS], uint32_t dd,
+                                               uint32_t id) {
+    int p = 0;
+#pragma unroll
+    for (int s = 0; s < SLOTS; ++s) p += __popc(__ballot_sync(kFull, ld[s] < dd || (ld[s] == dd && li[s] < id)));
+    return p;
 }
 
 // Admission threshold: the distance of the element of rank k (the (k+1)-th: one place is kept

@@ -55,3 +55,30 @@ def test_binary_front_runs(cp):
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "ALL PASS" in out.stdout
 
+
+FRONT_EXE = os.path.join(ROOT, "tests", "cpp", "gpu_front_check")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def compile_gpu_fronts():
+    lib_dir = os.path.join(ROOT, "sparse-text-kmeans_b200")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    subprocess.check_call([cxx, "-std=c++17", "-O2", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA_HOME, "include"),
+                           os.path.join(ROOT, "tests", "cpp", "gpu_front_check.cpp"), "-L", lib_dir, "-lcphnsw_b200",
+                           "-L", os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-Wl,-rpath," + lib_dir, "-o", FRONT_EXE])
+
+
+def test_gpu_class_fronts_compile_and_link(cp):
+    """include/cphnsw/cuda/gpu_encoder.cuh and gpu_knn_graph.cuh (GPUEncoder, GPUBruteForce, GPUKNNGraphBuilder)."""
+    compile_gpu_fronts()
+    assert os.path.exists(FRONT_EXE)
+
+
+@pytest.mark.gpu
+def test_gpu_class_fronts_run(cp):
+    compile_gpu_fronts()
+    out = subprocess.run([FRONT_EXE], capture_output=True, text=True, timeout=600)
+    print(out.stdout[-3000:], out.stderr[-2000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "ALL PASS" in out.stdout
+

@@ -730,3 +730,57 @@ def test_bulk_build_without_pruning_keeps_the_nearest(cp, oracle, n, M):
     ids, dist = idx.search_batch(q, 5, 40)
     wi, wd = oracle.search(rot, codes, cand, idx.entry_ids(), 40, 5, n_seed=min(4, n))
     assert np.array_equal(ids, wi) and np.array_equal(dist, wd)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,nq,dim,k", [(5000, 70, 128, 10), (3000, 33, 100, 40), (2600, 9, 960, 100), (700, 300, 17, 128),
+                                        (5, 3, 64, 10), (40000, 1000, 64, 1)])
+def test_exact_search_equals_cpu_ground_truth(cp, oracle, n, nq, dim, k):
+    """exact_search (GPUBruteForce::search, the harness's ground truth): ids and distances of the k smallest
+    (-<q,x>, id), bit for bit, for every k class, a dimension that is not a multiple of 4, a split base and
+    an index smaller than k."""
+    base, q = synthetic.gaussian_mixture(n, nq, dim, max(1, n // 200), 0.3, 5 + dim)
+    base[1] = base[0]  # equal distances: ties go to the lower id
+    idx = cp.CPHNSWIndex(dim, K=16, M=8, component_bytes=1 if dim <= 128 else 2)
+    idx.set_exact_base(base)
+    ids, dist = idx.exact_search_batch(q, k)
+    wi, wd = oracle.ground_truth(q, base, k, want_dist=True)
+    assert np.array_equal(ids, wi)
+    assert np.array_equal(dist, wd)
+    # queries equal to base rows: the row itself comes first with distance -|x|^2
+    ids2, _ = idx.exact_search_batch(base[:4], 1)
+    assert list(ids2[:, 0]) == [0, 0, 2, 3]
+    idx.set_exact_base(None)
+    with pytest.raises(cp.CPHNSWError):
+        idx.exact_search_batch(q, k)  # no vectors left
+
+
+@pytest.mark.gpu
+def test_exact_search_runs_over_the_index_vectors_by_default(cp, oracle):
+    base, q = synthetic.gaussian_mixture(3000, 50, 128, 10, 0.3, 9)
+    idx = cp.CPHNSWIndex(128, K=16, M=16)
+    idx.add_batch_parallel(base)
+    ids, dist = idx.exact_search_batch(q, 10)
+    wi, wd = oracle.ground_truth(q, base, 10, want_dist=True)
+    assert np.array_equal(ids, wi) and np.array_equal(dist, wd)
+    with pytest.raises(ValueError):
+        idx.exact_search_batch(q, 129)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim,k,ncand", [(128, 10, 200), (100, 5, 33), (64, 100, 150), (64, 20, 7)])
+def test_rerank_batch_equals_cpu(cp, oracle, dim, k, ncand):
+    """rerank (GPUBruteForce::rerank): candidates in any order, with holes and repeats."""
+    n, nq = 4000, 37
+    base, q = synthetic.gaussian_mixture(n, nq, dim, 20, 0.3, 3 + k)
+    rng = np.random.default_rng(k)
+    cand = rng.integers(0, n, size=(nq, ncand)).astype(np.uint32)
+    cand[:, ::7] = 0xFFFFFFFF
+    cand[:, 1] = cand[:, 2]
+    idx = cp.CPHNSWIndex(dim, K=16, M=8)
+    idx.set_exact_base(base)
+    ids, dist = idx.rerank_batch(q, cand, k)
+    wi, wd = oracle.rerank(q, base, cand, k)
+    assert np.array_equal(ids, wi)
+    assert np.array_equal(dist, wd)
+
