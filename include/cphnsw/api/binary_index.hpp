@@ -1,7 +1,8 @@
 // cphnsw::binary::BinaryCPHNSWIndex<K>: the reference's unified index CPHNSWIndex<K, 0> (sign-bit
 // codes, Hamming metric; include/cphnsw/api/index.hpp:60-260, include/cphnsw/api/config.hpp:17-100)
 // on the B200 library.  Same parameter structs and method names; header-only, holds no algorithm.
-// Residual codes (R > 0) are not provided.
+// BinaryCPHNSWIndex<K, R, Shift> is CPHNSWIndex<K, R, Shift>: R residual bits, combined distance
+// (h_primary << Shift) + h_residual (include/cphnsw/core/types.hpp:284-302); K + R <= 64.
 #pragma once
 
 #include <cstdint>
@@ -54,16 +55,23 @@ struct SearchParams {  // config.hpp:74-100
     SearchParams& set_rerank(bool r, size_t rk = 200) { rerank = r; rerank_k = rk; return *this; }
 };
 
-template <size_t K>
+template <size_t K, size_t R = 0, int Shift = 2>
 class BinaryCPHNSWIndex {
     static_assert(K >= 1 && K <= 256, "1 <= K <= 256 sign bits");
+    static_assert(R == 0 || (K % 4 == 0 && K + R <= 64 && Shift >= 0 && Shift <= 4),
+                  "residual codes: K a multiple of 4, K + R <= 64, 0 <= Shift <= 4");
 
 public:
-    static constexpr size_t NUM_WORDS = (K + 63) / 64;  // BinaryCodeStorage<K>::NUM_WORDS, codes.hpp:24
+    // words per node returned by codes(): bits 0..K-1 primary, K..K+R-1 residual (BinaryCodeStorage, codes.hpp:24)
+    static constexpr size_t NUM_WORDS = (K + R + 63) / 64;
 
     explicit BinaryCPHNSWIndex(const IndexParams& p, int device = 0) : params_(p) {
-        check(cphnsw_b200_create_binary(p.dim, uint32_t(K), uint32_t(p.M), uint32_t(p.ef_construction), p.seed,
+        check(cphnsw_b200_create_binary(p.dim, uint32_t(K + R), uint32_t(p.M), uint32_t(p.ef_construction), p.seed,
                                         CPHNSW_B200_FHT_AVX512, device, &h_));
+        if (R) {
+            check(cphnsw_b200_set_param(h_, "residual_bits", double(R)));
+            check(cphnsw_b200_set_param(h_, "residual_shift", double(Shift)));
+        }
     }
     explicit BinaryCPHNSWIndex(size_t dim) : BinaryCPHNSWIndex(IndexParams().set_dim(dim)) {}
     ~BinaryCPHNSWIndex() { cphnsw_b200_destroy(h_); }
@@ -103,7 +111,7 @@ public:
         return out;
     }
 
-    // the packed codes, NUM_WORDS uint64 per node (ResidualCode<K,0>::primary.signs)
+    // the packed codes, NUM_WORDS uint64 per node (ResidualCode<K,R>: primary bits, then residual bits)
     std::vector<uint64_t> codes() const {
         std::vector<uint64_t> w(size() * NUM_WORDS);
         check(cphnsw_b200_get_binary_codes(h_, w.data()));

@@ -83,6 +83,13 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *                   walk under the Hamming distance to the query's code (unified search, include/cphnsw/api/index.hpp:177-214),
  *                   distances returned are Hamming distances (exact -<q,x> after a rerank); brute_force_search ranks by
  *                   Hamming distance; calibrate and search_multiprobe are not available),
+ *   "residual_bits" / "residual_shift" (binary-code mode only, before any vector is added: the unified index's
+ *                   residual codes, ResidualCode<K, R> (include/cphnsw/core/codes.hpp:76-129).  The handle's K
+ *                   counts primary + residual bits; the last residual_bits components are the residual bits (the
+ *                   reference seeds its residual rotations seed + K_primary + r, i.e. rotations K_primary.. of one
+ *                   chain) and every code distance becomes (h_primary << residual_shift) + h_residual
+ *                   (include/cphnsw/core/types.hpp:284-302; shift 0..4).  (K - residual_bits) * component_bytes must
+ *                   be a multiple of 4; the kNN graph then runs on the byte-wise kernel),
  *   "build_seed" (0 = add_batch_parallel builds the exact code-distance kNN graph over everything, the
  *                 default; s > 0 = on an empty index only the first s vectors get the exact graph and
  *                 the others are inserted as add_batch does: O(n) instead of O(n^2) candidate search),

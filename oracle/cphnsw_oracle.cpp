@@ -119,11 +119,20 @@ inline void store_comp(void* codes, size_t comp_bytes, size_t i, uint32_t c) {
 
 // Legacy hamming_distance(CPCode, CPCode): number of the K components that differ
 // (use sites: evaluation/debug_estimator.cpp:149,172; evaluation/debug_code_storage.cpp:81).
+// Residual codes of the unified index (include/cphnsw/core/types.hpp:284-302;
+// hamming_combined_scalar, include/cphnsw/distance/detail/scalar_kernels.hpp:57-76): with the first
+// g_primary components the primary bits and the others the residual bits, the distance is
+// (h_primary << g_shift) + h_residual.  g_primary = 0 (the default) is the plain count.  A setting
+// of the whole oracle (orc_set_residual_weighting), so that every function built on code_dist follows it.
+static size_t g_primary = 0;
+static uint32_t g_shift = 0;
 inline uint32_t code_dist(const void* a, size_t ia, const void* b, size_t ib, size_t K,
                           size_t comp_bytes) {
     uint32_t d = 0;
-    for (size_t r = 0; r < K; ++r)
-        d += load_comp(a, comp_bytes, ia * K + r) != load_comp(b, comp_bytes, ib * K + r);
+    for (size_t r = 0; r < K; ++r) {
+        const uint32_t ne = load_comp(a, comp_bytes, ia * K + r) != load_comp(b, comp_bytes, ib * K + r);
+        d += r < g_primary ? ne << g_shift : ne;
+    }
     return d;
 }
 
@@ -202,6 +211,12 @@ int orc_encode(const float* x, uint64_t n, uint64_t dim, uint64_t K, uint64_t co
                 if (magnitudes) magnitudes[(size_t)i * K + r] = mag;
             }
     }
+    return 0;
+}
+
+int orc_set_residual_weighting(uint64_t primary_components, uint32_t shift) {
+    g_primary = primary_components;
+    g_shift = shift;
     return 0;
 }
 

@@ -74,6 +74,22 @@ def encode(x, K, comp_bytes, signs, convention=FHT_AVX512, want_rotated=False):
     return (codes, rot, mag) if want_rotated else codes
 
 
+class residual_weighting:
+    """Context manager: inside it every code distance of the oracle is the combined distance of
+    residual codes, (h_primary << shift) + h_residual, the first `primary` components being primary."""
+
+    def __init__(self, primary, shift):
+        self.primary, self.shift = primary, shift
+
+    def __enter__(self):
+        lib().orc_set_residual_weighting(C.c_uint64(self.primary), C.c_uint32(self.shift))
+        return self
+
+    def __exit__(self, *exc):
+        lib().orc_set_residual_weighting(C.c_uint64(0), C.c_uint32(0))
+        return False
+
+
 def code_distance(a, b):
     a = np.ascontiguousarray(a)
     b = np.ascontiguousarray(b)
@@ -314,6 +330,23 @@ class Ref:
         x = np.ascontiguousarray(x, np.float32)
         out = np.empty(x.shape[0], np.uint64)
         self.l.ref_encode_batch_signbits64(_ptr(x), C.c_uint64(x.shape[0]), C.c_uint64(x.shape[1]), C.c_uint64(seed), _ptr(out))
+        return out
+
+    def encode_batch_residual_32_16(self, x, seed=42):
+        """The unified encoder CPEncoder<32,16>: (primary uint64 word, residual uint64 word) per vector."""
+        x = np.ascontiguousarray(x, np.float32)
+        prim = np.empty(x.shape[0], np.uint64)
+        res = np.empty(x.shape[0], np.uint64)
+        self.l.ref_encode_batch_residual_32_16(_ptr(x), C.c_uint64(x.shape[0]), C.c_uint64(x.shape[1]), C.c_uint64(seed),
+                                               _ptr(prim), _ptr(res))
+        return prim, res
+
+    def hamming_combined_32_16_s2(self, pa, ra, pb, rb):
+        """The reference's hamming_combined_scalar<32,16,2> between codes given as (primary, residual) words."""
+        pa, ra, pb, rb = (np.ascontiguousarray(v, np.uint64) for v in (pa, ra, pb, rb))
+        out = np.empty((pa.size, pb.size), np.uint32)
+        self.l.ref_hamming_combined_32_16_s2(_ptr(pa), _ptr(ra), C.c_uint64(pa.size), _ptr(pb), _ptr(rb), C.c_uint64(pb.size),
+                                             _ptr(out))
         return out
 
     def hamming64(self, a, b):

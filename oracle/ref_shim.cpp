@@ -117,10 +117,40 @@ int ref_encode_batch_signbits64(const float* x, uint64_t n, uint64_t dim, uint64
     return 0;
 }
 
+// The unified encoder with residual bits, CPEncoder<32, 16> (include/cphnsw/encoder/cp_encoder.hpp:161-184,282-300)
+int ref_encode_batch_residual_32_16(const float* x, uint64_t n, uint64_t dim, uint64_t seed, uint64_t* primary,
+                                    uint64_t* residual) {
+    // one vector at a time through encode(): the reference's encode_batch runs encode_residual on a
+    // buffer shared by all OpenMP threads (cp_encoder.hpp:286-300), so its residual bits are only
+    // defined single-threaded
+    cphnsw::CPEncoder<32, 16> enc(dim, seed);
+    for (uint64_t i = 0; i < n; ++i) {
+        const cphnsw::ResidualCode<32, 16> c = enc.encode(x + i * dim);
+        primary[i] = c.primary.signs[0];
+        residual[i] = c.residual.signs[0];
+    }
+    return 0;
+}
+
 }  // extern "C"
 
 #ifdef CPHNSW_REF_EVAL_DIR
 extern "C" {
+
+// the reference's combined distance (primary << 2) + residual
+// (include/cphnsw/distance/detail/scalar_kernels.hpp:57-76)
+int ref_hamming_combined_32_16_s2(const uint64_t* pa, const uint64_t* ra, uint64_t na, const uint64_t* pb, const uint64_t* rb,
+                                  uint64_t nb, uint32_t* out) {
+    for (uint64_t i = 0; i < na; ++i)
+        for (uint64_t j = 0; j < nb; ++j) {
+            cphnsw::ResidualCode<32, 16> a, b;
+            a.clear(), b.clear();
+            a.primary.signs[0] = pa[i], a.residual.signs[0] = ra[i];
+            b.primary.signs[0] = pb[j], b.residual.signs[0] = rb[j];
+            out[i * nb + j] = cphnsw::detail::hamming_combined_scalar<32, 16, 2>(a, b);
+        }
+    return 0;
+}
 
 int ref_hamming64(const uint64_t* a, uint64_t na, const uint64_t* b, uint64_t nb, uint32_t* out) {
     for (uint64_t i = 0; i < na; ++i)

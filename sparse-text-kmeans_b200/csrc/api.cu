@@ -501,7 +501,26 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
     if (s == "binary_codes") {
         if (v != 0 && v != 1) { set_error("binary_codes must be 0 or 1"); return CPHNSW_B200_E_INVALID; }
         if (h->n && int(v) != h->binary_codes) { set_error("binary_codes cannot change once vectors have been added"); return CPHNSW_B200_E_STATE; }
+        if (v == 0 && h->residual_bits) { set_error("binary_codes cannot be switched off while residual_bits is set"); return CPHNSW_B200_E_INVALID; }
         h->binary_codes = int(v);
+        return 0;
+    }
+    if (s == "residual_bits" || s == "residual_shift") {
+        // residual codes of the unified index (ResidualCode<K, R>, include/cphnsw/core/codes.hpp:76-129;
+        // combined distance include/cphnsw/core/types.hpp:284-302)
+        if (h->n) { set_error("%s cannot change once vectors have been added", name); return CPHNSW_B200_E_STATE; }
+        if (s == "residual_shift") {
+            if (v < 0 || v > 4 || v != double(int(v))) { set_error("residual_shift must be in 0..4"); return CPHNSW_B200_E_INVALID; }
+            h->residual_shift = uint32_t(v);
+            return 0;
+        }
+        if (v != 0 && !h->binary_codes) { set_error("residual_bits needs binary_codes = 1"); return CPHNSW_B200_E_INVALID; }
+        if (v < 0 || v >= h->K || v != double(int(v))) { set_error("residual_bits must be in 0..K-1 (K = primary + residual bits = %u)", h->K); return CPHNSW_B200_E_INVALID; }
+        if (v != 0 && ((h->K - uint32_t(v)) * h->comp_bytes) % 4 != 0) {
+            set_error("residual_bits: the primary part (K - residual_bits components) must fill whole 32-bit words");
+            return CPHNSW_B200_E_INVALID;
+        }
+        h->residual_bits = uint32_t(v);
         return 0;
     }
     if (s == "build_seed") {
@@ -541,6 +560,8 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "search_kernel") *v = h->search_kernel;
     else if (s == "build_seed") *v = h->build_seed;
     else if (s == "binary_codes") *v = h->binary_codes;
+    else if (s == "residual_bits") *v = h->residual_bits;
+    else if (s == "residual_shift") *v = h->residual_shift;
     else if (s == "k_entry") *v = h->k_entry;
     else if (s == "knn_k") *v = h->knn_k;
     else if (s == "entry_scan") *v = h->entry_scan;
@@ -767,7 +788,7 @@ constexpr uint32_t kFileVersion = 1;
 struct FileHeader {  // after the magic; all little-endian, naturally aligned
     uint32_t version, K, comp_bytes, M, ef_construction, keep_pruned, k_entry, knn_k, entry_scan;
     int32_t convention;
-    uint32_t binary_codes, reserved;
+    uint32_t binary_codes, residual;  // residual = residual_bits | residual_shift << 16
     uint64_t dim, seed, n, calib_samples;
     double calib_alpha, calib_beta, calib_r2;
 };
@@ -803,6 +824,7 @@ int cphnsw_b200_save(cphnsw_b200_index* h, const char* path) {
     hd.version = kFileVersion, hd.K = h->K, hd.comp_bytes = h->comp_bytes, hd.M = h->M, hd.ef_construction = h->ef_construction;
     hd.keep_pruned = uint32_t(h->keep_pruned), hd.k_entry = h->k_entry, hd.knn_k = h->knn_k, hd.entry_scan = h->entry_scan;
     hd.binary_codes = uint32_t(h->binary_codes);
+    hd.residual = h->residual_bits | (h->residual_shift << 16);
     hd.convention = h->convention, hd.dim = h->dim, hd.seed = h->seed, hd.n = h->n, hd.calib_samples = h->calib_samples;
     hd.calib_alpha = h->calib_alpha, hd.calib_beta = h->calib_beta, hd.calib_r2 = h->calib_r2;
     bool ok = std::fwrite(kFileMagic, 1, 8, fc.f) == 8 && std::fwrite(&hd, sizeof(hd), 1, fc.f) == 1 &&
@@ -848,6 +870,11 @@ int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
     CPB_TRY(cphnsw_b200_set_sign_tables(h, signs.data()));
     if (hd.k_entry < 1 || hd.k_entry > 100 || hd.knn_k > 64 || hd.entry_scan > 1048576) { set_error("load: corrupt header (tunables)"); return CPHNSW_B200_E_INVALID; }
     h->binary_codes = hd.binary_codes != 0;
+    {
+        const uint32_t rb = hd.residual & 0xffffu, rs = hd.residual >> 16;
+        if (rb >= hd.K || rs > 4 || (rb && (!hd.binary_codes || ((hd.K - rb) * hd.comp_bytes) % 4 != 0))) { set_error("load: corrupt header (residual codes)"); return CPHNSW_B200_E_INVALID; }
+        h->residual_bits = rb, h->residual_shift = rs;
+    }
     h->keep_pruned = hd.keep_pruned != 0, h->k_entry = hd.k_entry, h->knn_k = hd.knn_k, h->entry_scan = hd.entry_scan;
     h->calib_alpha = hd.calib_alpha, h->calib_beta = hd.calib_beta, h->calib_r2 = hd.calib_r2, h->calib_samples = hd.calib_samples;
     if (hd.n) {

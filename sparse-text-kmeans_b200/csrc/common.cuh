@@ -81,6 +81,9 @@ struct cphnsw_b200_index {
     int knn_kernel = 0;  // 0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance
     int search_kernel = 0;  // 0 = pick, 1 = one warp per query, 2 = two warps per query
     int binary_codes = 0;  // 1: components keep only the sign bit (Hamming metric), search walks under the code distance
+    // residual codes of the binary mode: the last residual_bits components are residual bits, a primary mismatch
+    // counts 2^residual_shift (combined distance (h_p << shift) + h_r, include/cphnsw/core/types.hpp:284-302)
+    uint32_t residual_bits = 0, residual_shift = 0;
     uint32_t build_seed = 0;  // 0: add_batch_parallel builds the exact kNN graph; else only of this many nodes, the rest inserted
     int sm_count = 0;
 

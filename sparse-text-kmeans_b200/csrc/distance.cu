@@ -29,11 +29,38 @@ using knn::mbar_wait_bounded;
 using knn::kWaitLimit;
 
 // ---- SWAR component-mismatch count -------------------------------------------------------------
+// Weighted form for residual codes (combined distance (h_primary << shift) + h_residual,
+// include/cphnsw/core/types.hpp:284-302): a component of the first wp words of a row counts
+// 1 + mul = 2^shift, the others 1.  CodeWeights{0, 0} is the plain count.
+struct CodeWeights {
+    uint32_t wp = 0, mul = 0;
+};
+template <bool U16>
+struct FlagGroups {
+    static constexpr int G = U16 ? 16 : 8;  // words whose flags fit one accumulator
+};
+// pm[g]: the flag bits of group g that belong to primary words.  Array word i holds the row's word
+// 4 * (((i >> 2) + rot) & (WC / 4 - 1)) + (i & 3) (rot = 0: in order).
 template <int WC, bool U16>
-__device__ __forceinline__ uint32_t mismatch_count(const uint32_t (&a)[WC], const uint32_t (&b)[WC]) {
+__device__ __forceinline__ void primary_masks(CodeWeights cw, int rot, uint32_t (&pm)[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G]) {
+    constexpr uint32_t HI = U16 ? 0x80008000u : 0x80808080u;
+    constexpr int G = FlagGroups<U16>::G;
+#pragma unroll
+    for (int g = 0; g < (WC + G - 1) / G; ++g) pm[g] = 0;
+#pragma unroll
+    for (int w = 0; w < WC; ++w) {
+        const uint32_t truew = 4u * (((w >> 2) + rot) & (WC / 4 - 1)) + (w & 3);
+        if (truew < cw.wp) pm[w / G] |= HI >> (w % G);
+    }
+}
+
+template <int WC, bool U16>
+__device__ __forceinline__ uint32_t mismatch_count(const uint32_t (&a)[WC], const uint32_t (&b)[WC],
+                                                   const uint32_t (&pm)[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G],
+                                                   uint32_t mul) {
     constexpr uint32_t LO = U16 ? 0x7fff7fffu : 0x7f7f7f7fu;
     constexpr uint32_t HI = ~LO;
-    constexpr int G = U16 ? 16 : 8;  // words whose flags fit one accumulator
+    constexpr int G = FlagGroups<U16>::G;
     uint32_t d = 0;
 #pragma unroll
     for (int g = 0; g < (WC + G - 1) / G; ++g) {
@@ -46,6 +73,7 @@ __device__ __forceinline__ uint32_t mismatch_count(const uint32_t (&a)[WC], cons
             acc |= (y >> (w - g * G)) & (HI >> (w - g * G));
         }
         d += __popc(acc);
+        if (mul) d += mul * __popc(acc & pm[g]);  // warp-uniform branch
     }
     return d;
 }
@@ -74,7 +102,9 @@ constexpr int kCdRowsA = 32;
 template <int WC, bool U16>
 __global__ void __launch_bounds__(kCdThreads)
 code_distance_kernel(const uint32_t* __restrict__ a, uint64_t na, const uint32_t* __restrict__ b,
-                     uint64_t nb, uint16_t* __restrict__ out) {
+                     uint64_t nb, uint16_t* __restrict__ out, CodeWeights cwt) {
+    uint32_t pm[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G];
+    primary_masks<WC, U16>(cwt, 0, pm);
     __shared__ uint32_t atile[kCdRowsA][WC];
     const uint64_t a0 = uint64_t(blockIdx.y) * kCdRowsA;
     const uint64_t j = uint64_t(blockIdx.x) * kCdThreads + threadIdx.x;
@@ -95,7 +125,7 @@ code_distance_kernel(const uint32_t* __restrict__ a, uint64_t na, const uint32_t
         uint32_t other[WC];
 #pragma unroll
         for (int w = 0; w < WC; ++w) other[w] = atile[i][w];
-        out[(a0 + i) * nb + j] = uint16_t(mismatch_count<WC, U16>(other, mine));
+        out[(a0 + i) * nb + j] = uint16_t(mismatch_count<WC, U16>(other, mine, pm, cwt.mul));
     }
 }
 
@@ -108,7 +138,7 @@ template <int WC, bool U16, int SLOTS, int Q>
 __global__ void __launch_bounds__(kKnnThreads)
 knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uint64_t row_begin,
                  uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
-                 uint32_t* __restrict__ status) {
+                 uint32_t* __restrict__ status, CodeWeights cwt) {
     constexpr int CH = WC / 4;  // 16-byte chunks per code row
     constexpr int CHLOG = CH == 1 ? 0 : (CH == 2 ? 1 : 2);
     extern __shared__ __align__(128) unsigned char knn_smem[];
@@ -142,6 +172,8 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
     // of a quarter-warp fall into distinct banks
     const int rot = CH == 1 ? 0 : (lane >> (3 - CHLOG)) & (CH - 1);
     const uint64_t first_row = row_begin + (uint64_t(blockIdx.x) * kKnnWarps + warp) * Q;
+    uint32_t pm[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G];
+    primary_masks<WC, U16>(cwt, rot, pm);
     uint32_t qw[Q][WC];
 #pragma unroll
     for (int q = 0; q < Q; ++q) {
@@ -196,7 +228,7 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
             bool any = false;
 #pragma unroll
             for (int q = 0; q < Q; ++q) {
-                d[q] = c < rows ? mismatch_count<WC, U16>(qw[q], cw) : kFull;
+                d[q] = c < rows ? mismatch_count<WC, U16>(qw[q], cw, pm, cwt.mul) : kFull;
                 any |= d[q] < tau[q];
             }
             if (__any_sync(kFull, any)) {
@@ -254,7 +286,7 @@ template <int WC, bool U16>
 __global__ void __launch_bounds__(kSelWarps * 32)
 select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ cand, uint32_t k,
                         uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
-                        uint32_t* __restrict__ adj, const uint32_t* __restrict__ row_ids) {
+                        uint32_t* __restrict__ adj, const uint32_t* __restrict__ row_ids, CodeWeights cwt) {
     // row_ids == nullptr: rows [row_begin, row_end), output row i at adj[i - row_begin];
     // otherwise rows row_ids[0 .. row_end - row_begin) and the output goes to adj[row] (in place)
     __shared__ uint32_t csm[kSelWarps][kSelMaxK][WC];
@@ -263,6 +295,8 @@ select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __re
     if (slot >= row_end) return;
     const uint64_t row = row_ids ? uint64_t(row_ids[slot - row_begin]) : slot;
     const uint32_t* crow = cand + (slot - row_begin) * uint64_t(k);
+    uint32_t pm[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G];
+    primary_masks<WC, U16>(cwt, 0, pm);
     uint32_t cid[2];
     cid[0] = lane < int(k) ? crow[lane] : kInvalidNode;
     cid[1] = lane + 32 < int(k) ? crow[lane + 32] : kInvalidNode;
@@ -295,12 +329,12 @@ select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __re
         uint32_t ec[WC];
 #pragma unroll
         for (int w = 0; w < WC; ++w) ec[w] = csm[warp][t][w];
-        const uint32_t d_eq = mismatch_count<WC, U16>(ec, qc);
+        const uint32_t d_eq = mismatch_count<WC, U16>(ec, qc, pm, cwt.mul);
         bool viol = false;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
             const uint32_t m = uint32_t(lane + 32 * s);
-            if (m < rsize) viol |= !(d_eq < mismatch_count<WC, U16>(ec, rc[s]));
+            if (m < rsize) viol |= !(d_eq < mismatch_count<WC, U16>(ec, rc[s], pm, cwt.mul));
         }
         if (__any_sync(kFull, viol)) {
             disc |= 1ull << t;
@@ -364,10 +398,13 @@ template <int WC, bool U16>
 __global__ void __launch_bounds__(kSelWarps * 32)
 rev_merge_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ adj, int M,
                  const uint32_t* __restrict__ aff, uint32_t n_aff, const uint32_t* __restrict__ cnt,
-                 const uint32_t* __restrict__ seg, const uint32_t* __restrict__ inc, uint32_t* __restrict__ cand_out) {
+                 const uint32_t* __restrict__ seg, const uint32_t* __restrict__ inc, uint32_t* __restrict__ cand_out,
+                 CodeWeights cwt) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t i = blockIdx.x * kSelWarps + warp;
     if (i >= n_aff) return;
+    uint32_t pm[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G];
+    primary_masks<WC, U16>(cwt, 0, pm);
     const uint32_t v = aff[i];
     uint32_t qc[WC];
 #pragma unroll
@@ -390,7 +427,7 @@ rev_merge_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict_
                 const uint4 cc = __ldg(reinterpret_cast<const uint4*>(codes + uint64_t(w) * WC + x));
                 wc[x] = cc.x, wc[x + 1] = cc.y, wc[x + 2] = cc.z, wc[x + 3] = cc.w;
             }
-            dd = mismatch_count<WC, U16>(wc, qc);
+            dd = mismatch_count<WC, U16>(wc, qc, pm, cwt.mul);
         }
         uint32_t live = __ballot_sync(kFull, w != kInvalidNode);
         while (live) {
@@ -451,6 +488,16 @@ int padded_view(cphnsw_b200_index* h, const void* d_codes, uint64_t n, int WC, D
 
 }  // namespace
 
+// weights of the handle's code distance (plain unless residual bits are set)
+static CodeWeights code_weights(const cphnsw_b200_index* h) {
+    CodeWeights w;
+    if (h->residual_bits) {
+        w.wp = (h->K - h->residual_bits) * h->comp_bytes / 4;
+        w.mul = (1u << h->residual_shift) - 1u;
+    }
+    return w;
+}
+
 int code_row_words(uint32_t K, uint32_t comp_bytes) {
     uint32_t bytes = K * comp_bytes;
     if (bytes <= 16) return 4;
@@ -484,7 +531,8 @@ int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, con
     CPB_TRY(padded_view(h, d_b, nb, WC, h->s_pad2, st, &pb));
     dim3 grid(unsigned((nb + kCdThreads - 1) / kCdThreads), unsigned((na + kCdRowsA - 1) / kCdRowsA));
     LaunchTimer timer(h, kKernelCodeDistance, st);
-#define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out)
+    const CodeWeights cwt = code_weights(h);
+#define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out, cwt)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
     h->launches++;
@@ -502,7 +550,7 @@ static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n,
     const uint64_t blocks = (rows + kKnnWarps * Q - 1) / (kKnnWarps * Q);
     LaunchTimer timer(h, kKernelKnn, st);
     knn_graph_kernel<WC, U16, SLOTS, Q><<<unsigned(blocks), kKnnThreads, smem, st>>>(
-        codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>());
+        codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), code_weights(h));
     h->launches++;
     CPB_CUDA(cudaGetLastError());
     return 0;
@@ -569,9 +617,10 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
     const uint64_t rows = row_end - row_begin;
     const unsigned grid = unsigned((rows + kSelWarps - 1) / kSelWarps);
     LaunchTimer timer(h, kKernelSelect, st);
+    const CodeWeights cwt = code_weights(h);
 #define CALL(W, U)                                                                                          \
     select_neighbors_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_cand, k, row_begin, row_end, M,    \
-                                                                   keep_pruned, d_adj, d_row_ids)
+                                                                   keep_pruned, d_adj, d_row_ids, cwt)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
     h->launches++;
@@ -618,7 +667,8 @@ int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_o
     const uint32_t* pc;
     CPB_TRY(padded_view(h, d_codes, n_old + m, WC, h->s_pad, st, &pc));
     const unsigned grid = (n_aff + kSelWarps - 1) / kSelWarps;
-#define CALL(W, U) rev_merge_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_adj, int(M), aff, n_aff, cnt, seg, inc, cand)
+    const CodeWeights cwt = code_weights(h);
+#define CALL(W, U) rev_merge_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_adj, int(M), aff, n_aff, cnt, seg, inc, cand, cwt)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
     h->launches++;
@@ -700,7 +750,7 @@ extern "C" int cphnsw_b200_code_distance_noalloc(const void* d_a, uint64_t na, c
     pad_codes_kernel<<<unsigned((nb * WC + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(d_b), nb, row_bytes, WC, pb);
     const bool u16 = component_bytes == 2;
     dim3 grid(unsigned((nb + kCdThreads - 1) / kCdThreads), unsigned((na + kCdRowsA - 1) / kCdRowsA));
-#define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out)
+#define CALL(W, U) code_distance_kernel<W, U><<<grid, kCdThreads, 0, st>>>(pa, na, pb, nb, d_out, CodeWeights{})
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
     CPB_CUDA(cudaGetLastError());

@@ -309,6 +309,7 @@ int launch_sliced_slots(cphnsw_b200_index* h, const uint32_t* sliced, const Comp
 // Planes per component: 8 for uint8 codes, 11 for uint16 codes of padded dim 1024 (10 index bits +
 // sign), 1 in binary-code mode (a component is its sign bit).  K = 16, 32 or 64 (64: not with 11 planes).
 bool knn_sliced_supported(const cphnsw_b200_index* h) {
+    if (h->residual_bits) return false;  // weighted (combined) distance: the byte-wise kernel
     if (h->K != 16 && h->K != 32 && h->K != 64) return false;
     if (h->binary_codes) return true;
     if (h->comp_bytes == 1) return true;

@@ -99,7 +99,7 @@ __global__ void search_kernel(SearchArgs a) {
 
         // one lane scores one node (row `row` of `code_base`) under the kernel's metric
         auto score_lane = [&](const void* code_base, uint32_t row) -> float {
-            if (SYM) return sym_distance_lane<U16>(qcode_sm, code_base, row, a.K);
+            if (SYM) return sym_distance_lane<U16>(qcode_sm, code_base, row, a.K, a.resid_kp, a.resid_mul);
             return asym_distance_lane<U16>(table, code_base, row, a.K, a.P);
         };
         // Admission of (d, id), known to every lane: W stays the wcap best seen so far, sorted
@@ -534,6 +534,8 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.next_query = h->d_status.as<uint32_t>() + 1;
     a.rows_distinct = h->adj_rows_distinct;
     a.scan_only = scan_only;
+    a.resid_kp = h->residual_bits ? int(h->K - h->residual_bits) : 0;
+    a.resid_mul = h->residual_bits ? int((1u << h->residual_shift) - 1u) : 0;
     if (scan_only) {  // every node is an "entry", read from the code array itself; the k best are the result
         a.entry = nullptr;
         a.entry_codes = h->d_codes.p;

@@ -40,6 +40,8 @@ struct SearchArgs {
     uint32_t* stats;
     uint32_t* next_query;  // work counter, zero at launch
     int rows_distinct;     // no adjacency row lists a node twice (checked when the adjacency is set)
+    int resid_kp;          // residual codes: the first resid_kp components are primary and count 1 + resid_mul
+    int resid_mul;         //   in the symmetric distance (0: plain count)
     int scan_only;         // brute_force_search: score all n nodes (entry == nullptr: ids 0..n-1), keep the n_seed best, no walk
 };
 
@@ -116,7 +118,7 @@ __device__ __forceinline__ float asym_distance_lane(const float* table, const vo
 // from the query code staged in shared memory, as a float.
 template <bool U16>
 __device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, const void* codes, uint32_t row_index,
-                                                   int K) {
+                                                   int K, int kp = 0, int mul = 0) {
     const int row_bytes = K * (U16 ? 2 : 1);
     const unsigned char* row = static_cast<const unsigned char*>(codes) + size_t(row_index) * row_bytes;
     uint32_t d = 0;
@@ -124,12 +126,15 @@ __device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, c
         constexpr uint32_t LO = U16 ? 0x7fff7fffu : 0x7f7f7f7fu;
         const uint32_t* r32 = reinterpret_cast<const uint32_t*>(row);
         const uint32_t* q32 = reinterpret_cast<const uint32_t*>(qcode);
+        const int wp = mul ? kp * (U16 ? 2 : 1) / 4 : 0;  // primary words (kp * component size is a multiple of 4)
         for (int w = 0; w < row_bytes / 4; ++w) {
             const uint32_t x = q32[w] ^ __ldg(r32 + w);
-            d += __popc((((x & LO) + LO) | x) & ~LO);  // one flag per differing byte / halfword
+            const uint32_t c = __popc((((x & LO) + LO) | x) & ~LO);  // one flag per differing byte / halfword
+            d += w < wp ? c * uint32_t(1 + mul) : c;
         }
     } else {
-        for (int r = 0; r < K; ++r) d += load_component<U16>(row, r) != load_component<U16>(qcode, r);
+        for (int r = 0; r < K; ++r)
+            d += (load_component<U16>(row, r) != load_component<U16>(qcode, r)) ? (r < kp ? 1 + mul : 1) : 0;
     }
     return float(d);
 }

@@ -48,6 +48,27 @@ int main() {
     bool same = batch.size() == 20;
     for (size_t i = 0; same && i < 20; ++i) same &= batch[i] == index.search(base.data() + i * dim, SearchParams().set_k(3));
     CHECK(same, "search_batch equals search");
+    {
+        // residual codes: CPHNSWIndex<32, 16, 2> of the reference (K = 32 primary bits, R = 16, shift 2)
+        BinaryCPHNSWIndex<32, 16, 2> res(IndexParams().set_dim(dim).set_M(16).set_ef_construction(200));
+        res.add_batch(base.data(), n);
+        auto rw = res.codes();
+        BinaryCPHNSWIndex<32> prim(IndexParams().set_dim(dim).set_M(16).set_ef_construction(200));
+        prim.add_batch(base.data(), 200);
+        auto pw = prim.codes();
+        bool same_primary = rw.size() == n;
+        for (size_t i = 0; i < 200 && same_primary; ++i) same_primary = (rw[i] & 0xFFFFFFFFull) == pw[i] && (rw[i] >> 48) == 0;
+        CHECK(same_primary, "residual index: bits 0..31 are the primary code of the K = 32 index, bits 32..47 the residual");
+        size_t self = 0;
+        for (size_t i = 0; i < 50; ++i) {
+            auto r = res.search(base.data() + i * dim, SearchParams().set_k(5).set_ef(100).set_rerank(false));
+            self += !r.empty() && r[0].distance == 0.0f;
+            bool fits = true;
+            for (auto& x : r) fits &= x.distance >= 0.f && x.distance <= float((32 << 2) + 16);
+            self += fits ? 0 : 1000;
+        }
+        CHECK(self == 50, "residual index: self at combined distance 0, distances within (32 << 2) + 16");
+    }
     std::printf("%s (%d failures)\n", failures ? "FAILED" : "ALL PASS", failures);
     return failures ? 1 : 0;
 }

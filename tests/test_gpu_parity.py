@@ -784,3 +784,98 @@ def test_rerank_batch_equals_cpu(cp, oracle, dim, k, ncand):
     assert np.array_equal(ids, wi)
     assert np.array_equal(dist, wd)
 
+
+def residual_index(cp, dim, Kp, R, shift, M=16, conv=2):
+    idx = cp.CPHNSWIndex.binary(dim, K=Kp + R, M=M, fht_convention=conv)
+    idx.set_param("residual_bits", R)
+    idx.set_param("residual_shift", shift)
+    return idx
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("conv", [0, 1, 2])
+@pytest.mark.parametrize("dim", [128, 100, 24])
+def test_residual_codes_match_reference_golden(cp, dim, conv):
+    """Codes against the reference's CPEncoder<32,16> and the distance against its
+    hamming_combined_scalar<32,16,2> (tests/golden/make_residual_golden.py)."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "residual_golden.npz"))
+    x = g["x_%d" % dim]
+    idx = residual_index(cp, dim, 32, 16, 2, conv=conv)
+    idx.add_batch_parallel(x)
+    words = idx.binary_codes()[:, 0]
+    assert np.array_equal(words & np.uint64(0xFFFFFFFF), g["primary_%d_c%d" % (dim, conv)])
+    assert np.array_equal(words >> np.uint64(32), g["residual_%d_c%d" % (dim, conv)])
+    if dim == 128 and conv == 2:
+        codes = idx.codes()
+        assert np.array_equal(idx.code_distance(codes[:16], codes), g["combined_128_c2"].astype(np.uint16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("Kp,R,shift,dim,M", [(32, 16, 2, 128, 16), (32, 32, 1, 100, 32), (16, 16, 3, 300, 8), (8, 4, 0, 64, 16)])
+def test_residual_index_matches_oracle(cp, oracle, Kp, R, shift, dim, M):
+    """Residual codes end to end: combined distance in the kNN graph, select_neighbors, the walk,
+    brute force, incremental insertion and a save/load round trip."""
+    n0, n1, K = 1800, 300, Kp + R
+    base, q = synthetic.gaussian_mixture(n0 + n1, 25, dim, 8, 0.3, Kp * 100 + R)
+    idx = residual_index(cp, dim, Kp, R, shift, M=M)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 8)
+    assert idx.get_param("residual_bits") == R and idx.get_param("residual_shift") == shift
+    idx.add_batch_parallel(base[:n0])
+    signs = oracle.sign_tables(dim, K, 42)
+    cb = 1 if idx.padded_dim <= 128 else 2
+    codes = (oracle.encode(base, K, cb, signs, 2) & 1).astype(np.uint8)
+    qcodes = (oracle.encode(q, K, cb, signs, 2) & 1).astype(np.uint8)
+    assert np.array_equal(idx.codes(), codes[:n0])
+    with oracle.residual_weighting(Kp, shift):
+        assert np.array_equal(idx.code_distance(codes[:40], codes[:70]), oracle.code_distance(codes[:40], codes[:70]))
+        knn_k = min(64, 2 * M)
+        wn, wd = oracle.knn_graph(codes[:n0], knn_k)
+        nbrs, dist = idx.knn_graph(codes[:n0], knn_k)
+        assert np.array_equal(nbrs, wn) and np.array_equal(dist, wd)
+        adj = oracle.select_neighbors(codes[:n0], wn, M, True)
+        assert np.array_equal(idx.adjacency(), adj)
+        entry = idx.entry_ids()
+        ids, dd = idx.search_batch(q, 10, 80)
+        wi, wdd = oracle.search_codes(qcodes, codes[:n0], adj, entry, 80, 10, n_seed=8)
+        assert np.array_equal(ids, wi) and np.array_equal(dd, wdd)
+        bi, bd = idx.brute_force_search_batch(q[:5], 15)
+        full = oracle.code_distance(qcodes[:5], codes[:n0]).astype(np.int64)
+        for qi in range(5):
+            order = np.lexsort((np.arange(n0), full[qi]))[:15]
+            assert np.array_equal(bi[qi], order.astype(np.uint32)) and np.array_equal(bd[qi], full[qi][order].astype(np.float32))
+        # incremental insertion under the combined distance
+        idx.add_batch(base[n0:])
+        want = oracle_insert(oracle, codes, adj, n0, n1, M, True, 200, entry, 8)
+        assert np.array_equal(idx.adjacency(), want)
+    # the kNN kernel choice does not matter (the bit-sliced kernel declines weighted distances)
+    idx.set_param("knn_kernel", 2)
+    with pytest.raises(cp.CPHNSWError):
+        idx.knn_graph(codes[:n0], 16)
+    idx.set_param("knn_kernel", 0)
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "res.cphnsw")
+        idx.save(path)
+        again = cp.CPHNSWIndex.load(path)
+        assert again.get_param("residual_bits") == R and again.get_param("residual_shift") == shift
+        a, b = idx.search_batch(q, 5, 40), again.search_batch(q, 5, 40)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+@pytest.mark.gpu
+def test_residual_parameters_are_validated(cp):
+    idx = cp.CPHNSWIndex(128, K=32, M=16)
+    with pytest.raises(ValueError):
+        idx.set_param("residual_bits", 8)       # needs binary codes
+    b = cp.CPHNSWIndex.binary(128, K=48, M=16)
+    with pytest.raises(ValueError):
+        b.set_param("residual_bits", 48)        # no primary part left
+    with pytest.raises(ValueError):
+        b.set_param("residual_bits", 15)        # primary part must fill whole words
+    with pytest.raises(ValueError):
+        b.set_param("residual_shift", 5)
+    b.set_param("residual_bits", 16)
+    with pytest.raises(ValueError):
+        b.set_param("binary_codes", 0)
+

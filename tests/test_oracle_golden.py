@@ -107,3 +107,34 @@ def test_component_mismatch_of_sign_codes_is_the_unified_hamming_distance(oracle
     codes = (oracle.encode(x, 64, 1, oracle.sign_tables(128, 64, 42), 2) & 1).astype(np.uint8)
     assert np.array_equal(oracle.code_distance(codes[:20], codes), BIN["hamming_128_c2"].astype(np.uint16))
 
+
+RES = np.load(os.path.join(os.path.dirname(__file__), "golden", "residual_golden.npz"))
+
+
+def pack_bits(codes, first, count):
+    return ((codes[:, first:first + count] & 1).astype(np.uint64) << np.arange(count, dtype=np.uint64)).sum(axis=1).astype(np.uint64)
+
+
+@pytest.mark.parametrize("conv", CONVS)
+@pytest.mark.parametrize("dim", [128, 100, 24])
+def test_residual_bits_are_rotations_K_onwards(oracle, dim, conv):
+    """CPEncoder<32,16> (include/cphnsw/encoder/cp_encoder.hpp:161-184,282-300): the residual chain is
+    seeded seed + K, so its bits are the sign bits of rotations 32..47 of one chain of 48."""
+    x = RES["x_%d" % dim]
+    codes = oracle.encode(x, 48, 1, oracle.sign_tables(dim, 48, 42), conv)
+    assert np.array_equal(pack_bits(codes, 0, 32), RES["primary_%d_c%d" % (dim, conv)])
+    assert np.array_equal(pack_bits(codes, 32, 16), RES["residual_%d_c%d" % (dim, conv)])
+
+
+def test_weighted_code_distance_is_the_combined_hamming_distance(oracle):
+    """(h_primary << 2) + h_residual = hamming_combined_scalar<32,16,2>
+    (include/cphnsw/distance/detail/scalar_kernels.hpp:57-76)."""
+    x = RES["x_128"]
+    codes = (oracle.encode(x, 48, 1, oracle.sign_tables(128, 48, 42), 2) & 1).astype(np.uint8)
+    with oracle.residual_weighting(32, 2):
+        d = oracle.code_distance(codes[:16], codes)
+    assert np.array_equal(d.astype(np.uint32), RES["combined_128_c2"])
+    # the setting does not outlive the block
+    plain = (codes[:16, None, :] != codes[None, :, :]).sum(axis=2)
+    assert np.array_equal(oracle.code_distance(codes[:16], codes), plain)
+
