@@ -548,9 +548,10 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     LaunchTimer timer(h, kKernelSearch, st);
 
     // two warps per query: asymmetric metric, table in shared memory, one adjacency row per warp
-    const bool team_ok = !sym && !scan_only && c.table_smem && h->M <= 32 && h->k_entry <= 128;
+    const bool team_ok = !sym && !scan_only && (c.table_smem || h->K <= 32) && h->M <= 32 && h->k_entry <= 128;
+    a.table_in_smem = c.table_smem ? 1 : 0;
     if (h->search_kernel == 2 && !team_ok && !sym) {
-        set_error("search_kernel=2 needs the asymmetric metric, K*P*4 <= 32 KB and M <= 32");
+        set_error("search_kernel=2 needs the asymmetric metric, M <= 32 and K*P*4 <= 32 KB or K <= 32");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     if (team_ok && h->search_kernel != 1) {

@@ -40,6 +40,7 @@ struct SearchArgs {
     uint32_t* stats;
     uint32_t* next_query;  // work counter, zero at launch
     int rows_distinct;     // no adjacency row lists a node twice (checked when the adjacency is set)
+    int table_in_smem;     // two-warp kernel: the query table is copied to shared memory (else read from global memory)
     int resid_kp;          // residual codes: the first resid_kp components are primary and count 1 + resid_mul
     int resid_mul;         //   in the symmetric distance (0: plain count)
     int scan_only;         // brute_force_search: score all n nodes (entry == nullptr: ids 0..n-1), keep the n_seed best, no walk

@@ -27,7 +27,8 @@
 // two warps always execute the same sequence of barriers and nothing spins.  The entry scan and
 // the rerank are split between the two warps.
 //
-// Used for the asymmetric metric when the query table fits shared memory and M <= 32.
+// Used for the asymmetric metric with M <= 32; the query table sits in shared memory when it is at
+// most 32 KB and is read in place (global memory, through L1 / L2) otherwise.
 #include "search_common.cuh"
 
 namespace cpb {
@@ -219,8 +220,8 @@ __global__ void search_team_kernel(SearchArgs a) {
     const size_t dim_pad = a.qsm_floats;
     const int cap = int(a.cap);
     unsigned char* mine = team_smem + size_t(a.per_warp_smem) * team;  // per-team area
-    float* table = reinterpret_cast<float*>(mine);
-    float* qsm = table + table_floats;
+    float* table_sm = reinterpret_cast<float*>(mine);  // the query table, when it fits
+    float* qsm = table_sm + (a.table_in_smem ? table_floats : 0);
     uint32_t* sid = reinterpret_cast<uint32_t*>(qsm + dim_pad);
     float* sd = reinterpret_cast<float*>(sid + cap);
     uint32_t* seed_id = reinterpret_cast<uint32_t*>(sd + cap);  // scout's seeds
@@ -248,10 +249,14 @@ __global__ void search_team_kernel(SearchArgs a) {
         team_sync();
         const uint32_t q = mail[0];
         if (q >= a.nq) break;
+        // a table too large for shared memory is read in place (through L1 / L2)
+        const float* table = a.table_in_smem ? table_sm : a.tables + size_t(q) * table_floats;
         {   // set-up by all 64 lanes
-            const float4* src = reinterpret_cast<const float4*>(a.tables + size_t(q) * table_floats);
-            float4* dst = reinterpret_cast<float4*>(table);
-            for (int i = tl; i < int(table_floats / 4); i += 64) dst[i] = __ldg(src + i);
+            if (a.table_in_smem) {
+                const float4* src = reinterpret_cast<const float4*>(a.tables + size_t(q) * table_floats);
+                float4* dst = reinterpret_cast<float4*>(table_sm);
+                for (int i = tl; i < int(table_floats / 4); i += 64) dst[i] = __ldg(src + i);
+            }
             if (a.rerank_k) {
                 const float* qv = a.queries + size_t(q) * a.dim;
                 for (int i = tl; i < int(dim_pad); i += 64) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
