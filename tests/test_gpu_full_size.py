@@ -80,3 +80,24 @@ def test_full_size_search_parity_and_properties(c2, oracle):
     pid, pd, ps = idx.search_batch(q[sample], k, ef, want_stats=True)
     oi, od, os_ = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, k), k, want_stats=True, n_seed=w["k_entry"])
     assert np.array_equal(pid, oi) and np.array_equal(pd, od) and np.array_equal(ps, os_)
+
+
+def test_full_size_exact_search(c2, oracle):
+    """exact_search over all 1M stored vectors: a sample of queries against the CPU loop (bit-exact), and for
+    all 10k queries the size-independent properties (ascending, distinct, distances equal the dot products,
+    search_and_rerank never beats the exact k-th distance)."""
+    w, idx, codes, adj = c2
+    base, q = w["base"], w["queries"]
+    ids, dist = idx.exact_search_batch(q, 10)
+    assert (ids < base.shape[0]).all() and (np.diff(dist, axis=1) >= 0).all()
+    assert all(len(set(r.tolist())) == 10 for r in ids[:2000])
+    sample = np.arange(0, q.shape[0], 400)
+    wi, wd = oracle.ground_truth(q[sample], base, 10, want_dist=True)
+    assert np.array_equal(ids[sample], wi) and np.array_equal(dist[sample], wd)
+    exact = -np.einsum("qd,qkd->qk", q[:500], base[ids[:500]])
+    assert np.allclose(dist[:500], exact, rtol=1e-5, atol=1e-6)
+    ai, ad = idx.search_and_rerank_batch(q, 10, w["ef"], w["rerank_k"])
+    assert (ad[:, 9] >= dist[:, 9] - 1e-6).all()          # an approximate top-10 cannot be closer than the exact one
+    # rerank of the exact ids gives them back
+    ri, rd = idx.rerank_batch(q[:1000], ids[:1000, ::-1].copy(), 10)
+    assert np.array_equal(ri, ids[:1000]) and np.array_equal(rd, dist[:1000])
