@@ -2,7 +2,7 @@
 // codes, Hamming metric; include/cphnsw/api/index.hpp:60-260, include/cphnsw/api/config.hpp:17-100)
 // on the B200 library.  Same parameter structs and method names; header-only, holds no algorithm.
 // BinaryCPHNSWIndex<K, R, Shift> is CPHNSWIndex<K, R, Shift>: R residual bits, combined distance
-// (h_primary << Shift) + h_residual (include/cphnsw/core/types.hpp:284-302); K + R <= 64.
+// (h_primary << Shift) + h_residual (include/cphnsw/core/types.hpp:284-302); K + R <= 128.
 #pragma once
 
 #include <cstdint>
@@ -58,8 +58,8 @@ struct SearchParams {  // config.hpp:74-100
 template <size_t K, size_t R = 0, int Shift = 2>
 class BinaryCPHNSWIndex {
     static_assert(K >= 1 && K <= 256, "1 <= K <= 256 sign bits");
-    static_assert(R == 0 || (K % 4 == 0 && K + R <= 64 && Shift >= 0 && Shift <= 4),
-                  "residual codes: K a multiple of 4, K + R <= 64, 0 <= Shift <= 4");
+    static_assert(R == 0 || (K % 4 == 0 && K + R <= 128 && Shift >= 0 && Shift <= 4),
+                  "residual codes: K a multiple of 4, K + R <= 128, 0 <= Shift <= 4");
 
 public:
     // words per node returned by codes(): bits 0..K-1 primary, K..K+R-1 residual (BinaryCodeStorage, codes.hpp:24)

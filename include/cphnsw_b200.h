@@ -282,8 +282,8 @@ int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint
  * between code rows d_a[na][K] and d_b[nb][K] (device pointers, caller-owned, asynchronous on `stream`).
  * The padded copies of both operands that the kernel reads are kept in a 1 MiB array built into the
  * library's device image (every GPU that loads the library holds it until the process exits), hence
- * the limit: (na + nb) * R <= 1 MiB, where R is the row size K*component_bytes rounded up to 16, 32
- * or 64 bytes (32,768 rows at K=32 uint8).  Larger inputs are rejected with CPHNSW_B200_E_INVALID.
+ * the limit: (na + nb) * R <= 1 MiB, where R is the row size K*component_bytes rounded up to 16, 32,
+ * 64 or 128 bytes (32,768 rows at K=32 uint8).  Larger inputs are rejected with CPHNSW_B200_E_INVALID.
  *
  * The first call on each device looks up the array's device address; make that first call outside
  * any stream capture.  All calls share the one array: it is fully rewritten by each call (nothing

@@ -124,7 +124,7 @@ struct cphnsw_b200_index {
 
 namespace cpb {
 
-// padded code row width (32-bit words) used by the distance kernels: 4, 8 or 16; 0 = unsupported
+// padded code row width (32-bit words) used by the distance kernels: 4, 8, 16 or 32; 0 = unsupported
 int code_row_words(uint32_t K, uint32_t comp_bytes);
 
 // ---- launchers (each returns 0 or a negative status and counts its launches in h) ----

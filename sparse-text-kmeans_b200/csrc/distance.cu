@@ -132,7 +132,11 @@ code_distance_kernel(const uint32_t* __restrict__ a, uint64_t na, const uint32_t
 // ---- kNN graph ---------------------------------------------------------------------------------------
 constexpr int kKnnWarps = 4;
 constexpr int kKnnThreads = kKnnWarps * 32;
-constexpr int kKnnTile = knn::kTile;  // candidates per shared-memory stage
+// candidates per shared-memory stage: 1024, or 512 for 128-byte rows (two stages must fit shared memory)
+template <int WC>
+struct KnnTile {
+    static constexpr int value = WC == 32 ? knn::kTile / 2 : knn::kTile;
+};
 
 template <int WC, bool U16, int SLOTS, int Q>
 __global__ void __launch_bounds__(kKnnThreads)
@@ -140,7 +144,8 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
                  uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
                  uint32_t* __restrict__ status, CodeWeights cwt) {
     constexpr int CH = WC / 4;  // 16-byte chunks per code row
-    constexpr int CHLOG = CH == 1 ? 0 : (CH == 2 ? 1 : 2);
+    constexpr int CHLOG = CH == 1 ? 0 : (CH == 2 ? 1 : (CH == 4 ? 2 : 3));
+    constexpr int kKnnTile = KnnTile<WC>::value;
     extern __shared__ __align__(128) unsigned char knn_smem[];
     uint4* stage0 = reinterpret_cast<uint4*>(knn_smem);
     uint4* stage1 = stage0 + size_t(kKnnTile) * CH;
@@ -503,6 +508,7 @@ int code_row_words(uint32_t K, uint32_t comp_bytes) {
     if (bytes <= 16) return 4;
     if (bytes <= 32) return 8;
     if (bytes <= 64) return 16;
+    if (bytes <= 128) return 32;
     return 0;
 }
 
@@ -512,8 +518,10 @@ int code_row_words(uint32_t K, uint32_t comp_bytes) {
         else if (WCV == 4) { CALL(4, true); }                              \
         else if (WCV == 8 && !(U16V)) { CALL(8, false); }                  \
         else if (WCV == 8) { CALL(8, true); }                              \
-        else if (!(U16V)) { CALL(16, false); }                             \
-        else { CALL(16, true); }                                           \
+        else if (WCV == 16 && !(U16V)) { CALL(16, false); }                \
+        else if (WCV == 16) { CALL(16, true); }                            \
+        else if (!(U16V)) { CALL(32, false); }                             \
+        else { CALL(32, true); }                                           \
     } while (0)
 
 int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, const void* d_b, uint64_t nb,
@@ -521,7 +529,7 @@ int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, con
     if (na == 0 || nb == 0) return 0;
     const int WC = code_row_words(h->K, h->comp_bytes);
     if (!WC) {
-        set_error("code rows wider than 64 bytes are not supported by the distance kernels (K*component_bytes=%u)",
+        set_error("code rows wider than 128 bytes are not supported by the distance kernels (K*component_bytes=%u)",
                   h->K * h->comp_bytes);
         return CPHNSW_B200_E_UNSUPPORTED;
     }
@@ -543,7 +551,7 @@ int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, con
 template <int WC, bool U16, int SLOTS, int Q>
 static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
                         uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
-    const size_t smem = size_t(2) * kKnnTile * WC * 4;
+    const size_t smem = size_t(2) * KnnTile<WC>::value * WC * 4;
     CPB_CUDA(cudaFuncSetAttribute(knn_graph_kernel<WC, U16, SLOTS, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   int(smem)));
     const uint64_t rows = re - rb;
@@ -559,7 +567,7 @@ static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n,
 template <int WC, bool U16>
 static int launch_knn_slots(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
                             uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
-    constexpr int Q = WC == 16 ? 4 : 8;
+    constexpr int Q = WC == 32 ? 2 : (WC == 16 ? 4 : 8);
     const uint32_t need = k + 1;  // the row's own id may occupy one place
     if (need <= 64) return launch_knn_t<WC, U16, 2, Q>(h, codes, n, k, rb, re, nbrs, dist, st);
     if (need <= 96) return launch_knn_t<WC, U16, 3, Q>(h, codes, n, k, rb, re, nbrs, dist, st);
@@ -580,7 +588,7 @@ int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint
     }
     const int WC = code_row_words(h->K, h->comp_bytes);
     if (!WC) {
-        set_error("code rows wider than 64 bytes are not supported by the distance kernels");
+        set_error("code rows wider than 128 bytes are not supported by the distance kernels");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     if (h->knn_kernel == 2 && !knn_sliced_supported(h)) {
@@ -608,7 +616,7 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
     }
     const int WC = code_row_words(h->K, h->comp_bytes);
     if (!WC) {
-        set_error("code rows wider than 64 bytes are not supported by the distance kernels");
+        set_error("code rows wider than 128 bytes are not supported by the distance kernels");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     const bool u16 = h->comp_bytes == 2;
@@ -635,7 +643,7 @@ int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_o
     if (m == 0 || n_old == 0) return 0;
     const int WC = code_row_words(h->K, h->comp_bytes);
     if (!WC) {
-        set_error("code rows wider than 64 bytes are not supported by the distance kernels");
+        set_error("code rows wider than 128 bytes are not supported by the distance kernels");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     const bool u16 = h->comp_bytes == 2;
@@ -728,7 +736,7 @@ extern "C" int cphnsw_b200_code_distance_noalloc(const void* d_a, uint64_t na, c
     }
     const int WC = code_row_words(K, component_bytes);
     if (!WC) {
-        set_error("code_distance_noalloc: code rows wider than 64 bytes are not supported (K*component_bytes=%u)",
+        set_error("code_distance_noalloc: code rows wider than 128 bytes are not supported (K*component_bytes=%u)",
                   K * component_bytes);
         return CPHNSW_B200_E_UNSUPPORTED;
     }

@@ -75,7 +75,7 @@ def test_encode_empty_and_custom_signs(cp, oracle):
 
 
 # ---- code distance ---------------------------------------------------------------------------------
-@pytest.mark.parametrize("K,cb", [(32, 1), (16, 1), (64, 1), (32, 2), (16, 2), (5, 1), (7, 2), (1, 1)])
+@pytest.mark.parametrize("K,cb", [(32, 1), (16, 1), (64, 1), (32, 2), (16, 2), (5, 1), (7, 2), (1, 1), (64, 2), (100, 1), (128, 1), (40, 2)])
 def test_code_distance_matches_oracle(cp, oracle, K, cb):
     rng = np.random.default_rng(K * 10 + cb)
     dt = np.uint8 if cb == 1 else np.uint16
@@ -99,7 +99,8 @@ def clustered_codes(oracle, n, dim, K, cb, seed):
                                           (1500, 32, 32, 2, 256), (1200, 100, 32, 1, 128), (900, 16, 12, 1, 32),
                                           (5000, 32, 32, 1, 96), (2100, 20, 16, 1, 128), (1025, 64, 32, 1, 128),
                                           (1300, 32, 32, 2, 960), (1100, 70, 16, 2, 1000), (2300, 64, 64, 1, 128),
-                                          (700, 100, 64, 1, 100)])
+                                          (700, 100, 64, 1, 100), (1400, 64, 64, 2, 300), (1300, 40, 100, 1, 128),
+                                          (1030, 20, 128, 1, 64)])  # the last three: 128-byte rows
 @pytest.mark.parametrize("kernel", [1, 2])  # byte-wise and bit-sliced distance
 def test_knn_graph_matches_oracle(cp, oracle, n, k, K, cb, dim, kernel):
     _, codes = clustered_codes(oracle, n, dim, K, cb, n + k)
@@ -136,7 +137,8 @@ def test_knn_graph_massive_ties_break_by_id(cp, oracle, kernel):
 @pytest.mark.parametrize("n,k,M,K,cb,dim,keep", [(1500, 64, 32, 32, 1, 128, True), (1500, 64, 32, 32, 1, 128, False),
                                                  (800, 32, 32, 32, 1, 128, True), (800, 40, 16, 16, 1, 64, True),
                                                  (600, 64, 64, 32, 2, 256, True), (40, 64, 32, 32, 1, 128, True),
-                                                 (500, 20, 8, 12, 1, 32, False)])
+                                                 (500, 20, 8, 12, 1, 32, False), (700, 64, 32, 64, 2, 300, True),
+                                                 (600, 48, 16, 96, 1, 128, False)])
 def test_select_neighbors_matches_oracle(cp, oracle, n, k, M, K, cb, dim, keep):
     _, codes = clustered_codes(oracle, n, dim, K, cb, n + M)
     cand, _ = oracle.knn_graph(codes, k)
@@ -160,6 +162,7 @@ def oracle_index(oracle, base, K, cb, M, knn_k, conv=2):
                                                      (3000, 96, 32, 1, 16, 4, 4), (3000, 96, 32, 1, 16, 333, 100),
                                                      (1500, 200, 16, 2, 32, 32, 8), (50, 128, 32, 1, 32, 4, 4),
                                                      (1200, 300, 32, 2, 16, 32, 8), (900, 960, 32, 2, 32, 16, 4),  # table > 32 KB
+                                                     (1000, 100, 64, 2, 16, 32, 8),  # 128-byte code rows
                                                      (50, 128, 32, 1, 32, 50, 1)])
 @pytest.mark.parametrize("skernel", [1, 2])  # one warp per query, two warps per query
 def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan, seeds, skernel):
@@ -279,7 +282,7 @@ def oracle_insert(oracle, codes, adj, n_old, m, M, keep, ef_c, entry, n_seed):
     return out
 
 
-@pytest.mark.parametrize("n0,adds,dim,K,cb,M,keep", [(2000, (1, 1, 300, 2500), 128, 32, 1, 32, True),
+@pytest.mark.parametrize("n0,adds,dim,K,cb,M,keep", [(2000, (1, 1, 300, 2500), 128, 32, 1, 32, True), (600, (200,), 300, 64, 2, 16, True),
                                                        (500, (700, 40), 96, 16, 1, 8, False),
                                                        (40, (5, 100), 200, 16, 2, 16, True), (1, (1, 2, 4), 128, 32, 1, 32, True)])
 def test_incremental_add_matches_oracle(cp, oracle, n0, adds, dim, K, cb, M, keep):
@@ -812,7 +815,8 @@ def test_residual_codes_match_reference_golden(cp, dim, conv):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("Kp,R,shift,dim,M", [(32, 16, 2, 128, 16), (32, 32, 1, 100, 32), (16, 16, 3, 300, 8), (8, 4, 0, 64, 16)])
+@pytest.mark.parametrize("Kp,R,shift,dim,M", [(32, 16, 2, 128, 16), (32, 32, 1, 100, 32), (16, 16, 3, 300, 8), (8, 4, 0, 64, 16),
+                                              (64, 32, 2, 128, 16), (64, 16, 3, 200, 32)])  # the reference's K = 64 configurations
 def test_residual_index_matches_oracle(cp, oracle, Kp, R, shift, dim, M):
     """Residual codes end to end: combined distance in the kNN graph, select_neighbors, the walk,
     brute force, incremental insertion and a save/load round trip."""
