@@ -74,7 +74,8 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *            candidates are the links, build_with_gpu_knn(..., prune = false), evaluation/test_gpu_build.cpp:168-174),
  *   "knn_k" (candidates per node fed to select_neighbors, default min(2*M, 64)),
  *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; K = 16/32/64 with uint8 codes or
- *                 in binary-code mode, K = 16/32 with uint16 codes of padded dim 1024),
+ *                 in binary-code mode, K = 16/32 with uint16 codes of padded dim 1024, and one-byte binary codes of
+ *                 any K <= 120 that is a multiple of 8, residual bits included when the primary part is one too),
  *   "search_kernel" (0 = pick, 1 = one warp per query, 2 = two warps per query; the second needs
  *                    M <= 32 and either K * padded_dim * 4 <= 32 KB or K <= 32; both return identical results),
  *   "binary_codes" (0/1, before any vector is added: 1 = the unified index's primary binary code
@@ -89,7 +90,8 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *                   reference seeds its residual rotations seed + K_primary + r, i.e. rotations K_primary.. of one
  *                   chain) and every code distance becomes (h_primary << residual_shift) + h_residual
  *                   (include/cphnsw/core/types.hpp:284-302; shift 0..4).  (K - residual_bits) * component_bytes must
- *                   be a multiple of 4; the kNN graph then runs on the byte-wise kernel),
+ *                   be a multiple of 4; the kNN graph runs on the bit-sliced kernel when K and K - residual_bits are
+ *                   multiples of 8 and K <= 120, else on the byte-wise kernel),
  *   "build_seed" (0 = add_batch_parallel builds the exact code-distance kNN graph over everything, the
  *                 default; s > 0 = on an empty index only the first s vectors get the exact graph and
  *                 the others are inserted as add_batch does: O(n) instead of O(n^2) candidate search),

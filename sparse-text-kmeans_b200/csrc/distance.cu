@@ -592,7 +592,7 @@ int launch_knn_graph(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     if (h->knn_kernel == 2 && !knn_sliced_supported(h)) {
-        set_error("knn_kernel=2 (bit-sliced) needs K = 16, 32 or 64 with uint8 components or sign-bit codes, or K = 16 / 32 with padded dim 1024");
+        set_error("knn_kernel=2 (bit-sliced) needs K = 16, 32 or 64 with uint8 components, K = 16 / 32 with padded dim 1024, or one-byte sign-bit codes of whole blocks of 8 components (K <= 120)");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     if (h->knn_kernel != 1 && knn_sliced_supported(h))

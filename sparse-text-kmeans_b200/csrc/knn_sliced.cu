@@ -279,6 +279,212 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
     }
 }
 
+// ---- sign-bit codes of any width, with or without residual weighting -----------------------------------
+// One plane per component (binary-code mode), K = 8 * nblk <= 120 components.  The first 8 * nblk_p
+// components are primary bits: the distance is (h_primary << shift) + h_residual
+// (include/cphnsw/core/types.hpp:284-302); nblk_p = 0 is the plain count.  Same list machinery as
+// knn_sliced_kernel; the counts are kept as seven planes each and added in bit-sliced form.
+constexpr int kWPlanes = 11;  // (120 << 4) + 120 < 2048
+
+template <int SLOTS>
+__global__ void __launch_bounds__(kSlWarps * 32)
+knn_sliced_binary_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict__ codes, uint64_t n, uint32_t k,
+                         uint64_t row_begin, uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
+                         uint32_t* __restrict__ status, int nblk, int nblk_p, int shift) {
+    const int K = nblk * 8, CHUNKS = nblk * 2;
+    const uint32_t TILE_BYTES = uint32_t(CHUNKS) * 32 * 16;
+    extern __shared__ __align__(128) unsigned char sl_smem[];
+    uint4* stage0 = reinterpret_cast<uint4*>(sl_smem);
+    uint4* stage1 = stage0 + CHUNKS * 32;
+    uint4* masks = stage1 + CHUNKS * 32;  // [warp][q][chunk]
+    __shared__ uint64_t full_bar[2];
+    __shared__ int abort_flag;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t tiles = (n + knn::kTile - 1) / knn::kTile;
+    if (threadIdx.x == 0) {
+        knn::mbar_init(&full_bar[0], 1);
+        knn::mbar_init(&full_bar[1], 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (uint64_t t = 0; t < 2 && t < tiles; ++t) {
+            knn::mbar_expect_tx(&full_bar[t], TILE_BYTES);
+            knn::bulk_g2s(t == 0 ? stage0 : stage1, sliced + t * (TILE_BYTES / 4), TILE_BYTES, &full_bar[t]);
+        }
+    }
+    const uint64_t first_row = row_begin + (uint64_t(blockIdx.x) * kSlWarps + warp) * kSlQ;
+    uint4* my_masks = masks + size_t(warp) * kSlQ * CHUNKS;
+    for (int q = 0; q < kSlQ; ++q) {
+        const uint64_t row = min(first_row + q, row_end - 1);
+        uint32_t* mw = reinterpret_cast<uint32_t*>(my_masks + q * CHUNKS);
+        for (int w = lane; w < K; w += 32) mw[w] = (codes[row * K + w] & 1u) ? kFull : 0u;
+    }
+    __syncwarp();
+
+    uint32_t ld[kSlQ][SLOTS], li[kSlQ][SLOTS], tau[kSlQ];
+#pragma unroll
+    for (int q = 0; q < kSlQ; ++q) {
+        tau[q] = kFull;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) ld[q][s] = kFull, li[q][s] = kInvalidNode;
+    }
+
+    bool lost = false;
+    for (uint64_t t = 0; t < tiles; ++t) {
+        const int st = int(t & 1);
+        const uint32_t parity = uint32_t((t >> 1) & 1);
+        if (!knn::mbar_wait_bounded(&full_bar[st], parity, knn::kWaitLimit)) abort_flag = 1;
+        __syncthreads();
+        if (abort_flag) {
+            lost = true;
+            break;
+        }
+        const uint4* tile = st == 0 ? stage0 : stage1;
+        const uint64_t group_base = t * knn::kTile + uint64_t(lane) * 32;
+        const uint32_t valid = group_base >= n ? 0u : (n - group_base >= 32 ? kFull : ((1u << (n - group_base)) - 1u));
+
+        // S: count planes of the part being summed (weights 1, 2, .., 64); P: those of the primary part
+        uint32_t S[kSlQ][7], P[kSlQ][7];
+#pragma unroll
+        for (int q = 0; q < kSlQ; ++q)
+#pragma unroll
+            for (int b = 0; b < 7; ++b) S[q][b] = P[q][b] = 0;
+
+#pragma unroll 1
+        for (int blk = 0; blk < nblk; ++blk) {
+            if (blk == nblk_p) {  // the primary part ends here (nblk_p = 0: there is none)
+#pragma unroll
+                for (int q = 0; q < kSlQ; ++q)
+#pragma unroll
+                    for (int b = 0; b < 7; ++b) P[q][b] = S[q][b], S[q][b] = 0;
+            }
+            const uint4 sa = tile[size_t(blk * 2) * 32 + lane], sb = tile[size_t(blk * 2 + 1) * 32 + lane];
+#pragma unroll
+            for (int q = 0; q < kSlQ; ++q) {
+                const uint4 ma = my_masks[q * CHUNKS + blk * 2], mb = my_masks[q * CHUNKS + blk * 2 + 1];
+                // "differs" planes of the block's 8 components, carry-save added into the running count
+                uint32_t twosA, twosB, foursA, foursB, e8;
+                csa(twosA, S[q][0], S[q][0], sa.x ^ ma.x, sa.y ^ ma.y);
+                csa(twosB, S[q][0], S[q][0], sa.z ^ ma.z, sa.w ^ ma.w);
+                csa(foursA, S[q][1], S[q][1], twosA, twosB);
+                csa(twosA, S[q][0], S[q][0], sb.x ^ mb.x, sb.y ^ mb.y);
+                csa(twosB, S[q][0], S[q][0], sb.z ^ mb.z, sb.w ^ mb.w);
+                csa(foursB, S[q][1], S[q][1], twosA, twosB);
+                csa(e8, S[q][2], S[q][2], foursA, foursB);
+                // the weight-8 carry ripples into the 8 / 16 / 32 / 64 planes
+                const uint32_t c16 = S[q][3] & e8;
+                S[q][3] ^= e8;
+                const uint32_t c32 = S[q][4] & c16;
+                S[q][4] ^= c16;
+                const uint32_t c64 = S[q][5] & c32;
+                S[q][5] ^= c32;
+                S[q][6] ^= c64;
+            }
+        }
+
+#pragma unroll
+        for (int q = 0; q < kSlQ; ++q) {
+            // D = (P << shift) + S, bit-sliced
+            uint32_t D[kWPlanes];
+#pragma unroll
+            for (int b = 0; b < kWPlanes; ++b) D[b] = b < 7 ? P[q][b] : 0u;
+#pragma unroll 1
+            for (int s = 0; s < shift; ++s) {
+#pragma unroll
+                for (int b = kWPlanes - 1; b >= 1; --b) D[b] = D[b - 1];
+                D[0] = 0;
+            }
+            uint32_t carry = 0;
+#pragma unroll
+            for (int b = 0; b < kWPlanes; ++b) {
+                const uint32_t r = b < 7 ? S[q][b] : 0u;
+                const uint32_t u = D[b] ^ r;
+                const uint32_t sum = u ^ carry;
+                carry = (D[b] & r) | (u & carry);
+                D[b] = sum;
+            }
+            // candidates with distance < tau[q]
+            uint32_t pass;
+            if (tau[q] >= (1u << kWPlanes)) {
+                pass = kFull;
+            } else {
+                uint32_t lt = 0, eq = kFull;
+#pragma unroll
+                for (int b = kWPlanes - 1; b >= 0; --b) {
+                    if ((tau[q] >> b) & 1u) {
+                        lt |= eq & ~D[b];
+                        eq &= D[b];
+                    } else {
+                        eq &= ~D[b];
+                    }
+                }
+                pass = lt;
+            }
+            pass &= valid;
+            uint32_t lanes = __ballot_sync(kFull, pass != 0);
+            while (lanes) {
+                const int src = __ffs(lanes) - 1;
+                lanes &= lanes - 1;
+                uint32_t pm = __shfl_sync(kFull, pass, src);
+                uint32_t pl[kWPlanes];
+#pragma unroll
+                for (int b = 0; b < kWPlanes; ++b) pl[b] = __shfl_sync(kFull, D[b], src);
+                const uint64_t src_base = t * knn::kTile + uint64_t(src) * 32;
+                while (pm) {
+                    const int bit = __ffs(pm) - 1;
+                    pm &= pm - 1;
+                    uint32_t dd = 0;
+#pragma unroll
+                    for (int b = 0; b < kWPlanes; ++b) dd |= ((pl[b] >> bit) & 1u) << b;
+                    if (dd >= tau[q]) continue;  // tightened by an earlier candidate
+                    knn::list_insert<SLOTS>(ld[q], li[q], dd, uint32_t(src_base + bit), lane);
+                    tau[q] = knn::list_threshold<SLOTS>(ld[q], k);
+                }
+            }
+        }
+        __syncthreads();  // every warp is done with this stage
+        if (threadIdx.x == 0 && t + 2 < tiles) {
+            knn::mbar_expect_tx(&full_bar[st], TILE_BYTES);
+            knn::bulk_g2s(st == 0 ? stage0 : stage1, sliced + (t + 2) * (TILE_BYTES / 4), TILE_BYTES, &full_bar[st]);
+        }
+    }
+    if (lost) {
+        if (threadIdx.x == 0) {
+            atomicExch(status, kStatusWaitTimeout);
+            knn::mbar_wait_bounded(&full_bar[0], 0, knn::kWaitLimit);
+            knn::mbar_wait_bounded(&full_bar[1], 0, knn::kWaitLimit);
+        }
+        return;
+    }
+#pragma unroll
+    for (int q = 0; q < kSlQ; ++q) {
+        const uint64_t row = first_row + q;
+        if (row >= row_end) continue;
+        knn::list_write<SLOTS>(ld[q], li[q], row, k, nbrs + (row - row_begin) * uint64_t(k),
+                               dists ? dists + (row - row_begin) * uint64_t(k) : nullptr, lane);
+    }
+}
+
+template <int SLOTS>
+int launch_sliced_binary_t(cphnsw_b200_index* h, const uint32_t* sliced, const uint8_t* codes, uint64_t n, uint32_t k,
+                           uint64_t rb, uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    const int nblk = int(h->K / 8), chunks = nblk * 2;
+    const int nblk_p = h->residual_bits ? int((h->K - h->residual_bits) / 8) : 0;
+    const size_t smem = size_t(2) * chunks * 32 * 16 + size_t(kSlWarps) * kSlQ * chunks * 16;
+    auto kernel = knn_sliced_binary_kernel<SLOTS>;
+    CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    const uint64_t blocks = (re - rb + kSlWarps * kSlQ - 1) / (kSlWarps * kSlQ);
+    LaunchTimer timer(h, kKernelKnn, st);
+    kernel<<<unsigned(blocks), kSlWarps * 32, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), nblk,
+                                                         nblk_p, int(h->residual_bits ? h->residual_shift : 0));
+    h->launches++;
+    CPB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 template <typename CompT, int NB, int NBLK, int SLOTS, int WARPS>
 int launch_sliced_t(cphnsw_b200_index* h, const uint32_t* sliced, const CompT* codes, uint64_t n, uint32_t k,
                     uint64_t rb, uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
@@ -306,10 +512,19 @@ int launch_sliced_slots(cphnsw_b200_index* h, const uint32_t* sliced, const Comp
 
 }  // namespace
 
+// Sign-bit codes that take knn_sliced_binary_kernel: one-byte components, whole blocks of 8 components
+// in the code and in its primary part, at most 120 components.
+static bool knn_sliced_binary_general(const cphnsw_b200_index* h) {
+    if (h->K % 8 != 0 || h->K > 120) return false;
+    if (h->residual_bits) return (h->K - h->residual_bits) % 8 == 0;
+    return h->K != 16 && h->K != 32 && h->K != 64;  // those widths have their own instantiations
+}
+
 // Planes per component: 8 for uint8 codes, 11 for uint16 codes of padded dim 1024 (10 index bits +
 // sign), 1 in binary-code mode (a component is its sign bit).  K = 16, 32 or 64 (64: not with 11 planes).
 bool knn_sliced_supported(const cphnsw_b200_index* h) {
-    if (h->residual_bits) return false;  // weighted (combined) distance: the byte-wise kernel
+    if (h->binary_codes && h->comp_bytes == 1 && knn_sliced_binary_general(h)) return true;
+    if (h->residual_bits) return false;  // weighted (combined) distance of wider components: the byte-wise kernel
     if (h->K != 16 && h->K != 32 && h->K != 64) return false;
     if (h->binary_codes) return true;
     if (h->comp_bytes == 1) return true;
@@ -356,6 +571,12 @@ int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t 
         return launch_sliced_k<uint16_t, 11, 8>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
     }
     const uint8_t* codes = static_cast<const uint8_t*>(d_codes);
+    if (NB == 1 && knn_sliced_binary_general(h)) {
+        const uint32_t need = k + 1;
+        if (need <= 64) return launch_sliced_binary_t<2>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+        if (need <= 96) return launch_sliced_binary_t<3>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+        return launch_sliced_binary_t<4>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
+    }
     if (NB == 1) return launch_sliced_k<uint8_t, 1, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
     return launch_sliced_k<uint8_t, 8, kSlWarps>(h, sl, codes, n, k, row_begin, row_end, d_nbrs, d_dist, st);
 }

@@ -673,7 +673,8 @@ def test_binary_codes_match_reference_golden(cp, dim, conv):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("K,cb,dim", [(16, 1, 64), (32, 1, 128), (64, 1, 128), (32, 2, 300), (32, 2, 1024), (24, 1, 128)])
+@pytest.mark.parametrize("K,cb,dim", [(16, 1, 64), (32, 1, 128), (64, 1, 128), (32, 2, 300), (32, 2, 1024), (24, 1, 128),
+                                      (96, 1, 128), (120, 1, 64), (8, 1, 32), (20, 1, 128)])
 @pytest.mark.parametrize("kernel", [1, 2])
 def test_binary_knn_graph_both_kernels(cp, oracle, K, cb, dim, kernel):
     """Sign-bit codes: the bit-sliced kernel runs with one plane per component (K = 16, 32, 64)."""
@@ -683,7 +684,7 @@ def test_binary_knn_graph_both_kernels(cp, oracle, K, cb, dim, kernel):
     idx = make_index(cp, dim, K, cb)
     idx.set_param("binary_codes", 1)
     idx.set_param("knn_kernel", kernel)
-    if kernel == 2 and K not in (16, 32, 64):
+    if kernel == 2 and K not in (16, 32, 64) and not (cb == 1 and K % 8 == 0):
         with pytest.raises(cp.CPHNSWError):
             idx.knn_graph(codes, k)
         return
@@ -853,10 +854,17 @@ def test_residual_index_matches_oracle(cp, oracle, Kp, R, shift, dim, M):
         idx.add_batch(base[n0:])
         want = oracle_insert(oracle, codes, adj, n0, n1, M, True, 200, entry, 8)
         assert np.array_equal(idx.adjacency(), want)
-    # the kNN kernel choice does not matter (the bit-sliced kernel declines weighted distances)
-    idx.set_param("knn_kernel", 2)
-    with pytest.raises(cp.CPHNSWError):
-        idx.knn_graph(codes[:n0], 16)
+    # both kNN kernels give the same lists; the bit-sliced one needs whole blocks of 8 components
+    with oracle.residual_weighting(Kp, shift):
+        wn, wd = oracle.knn_graph(codes, 70)
+    for kern in (1, 2):
+        idx.set_param("knn_kernel", kern)
+        if kern == 2 and (K % 8 or Kp % 8):
+            with pytest.raises(cp.CPHNSWError):
+                idx.knn_graph(codes, 70)
+            continue
+        nbrs, dist = idx.knn_graph(codes, 70)
+        assert np.array_equal(nbrs, wn) and np.array_equal(dist, wd)
     idx.set_param("knn_kernel", 0)
     import tempfile
     with tempfile.TemporaryDirectory() as tmp:
