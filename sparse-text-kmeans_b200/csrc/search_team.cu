@@ -210,7 +210,9 @@ __device__ __forceinline__ void tier_admit_lanes(TierList& T, uint32_t m, bool m
     }
 }
 
-template <bool U16>
+// TSM: the query table is copied to shared memory (a compile-time fact, so that its reads stay
+// shared-memory loads); otherwise it is read in place.
+template <bool U16, bool TSM>
 __global__ void search_team_kernel(SearchArgs a) {
     extern __shared__ __align__(16) unsigned char team_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -221,7 +223,7 @@ __global__ void search_team_kernel(SearchArgs a) {
     const int cap = int(a.cap);
     unsigned char* mine = team_smem + size_t(a.per_warp_smem) * team;  // per-team area
     float* table_sm = reinterpret_cast<float*>(mine);  // the query table, when it fits
-    float* qsm = table_sm + (a.table_in_smem ? table_floats : 0);
+    float* qsm = table_sm + (TSM ? table_floats : 0);
     uint32_t* sid = reinterpret_cast<uint32_t*>(qsm + dim_pad);
     float* sd = reinterpret_cast<float*>(sid + cap);
     uint32_t* seed_id = reinterpret_cast<uint32_t*>(sd + cap);  // scout's seeds
@@ -250,9 +252,9 @@ __global__ void search_team_kernel(SearchArgs a) {
         const uint32_t q = mail[0];
         if (q >= a.nq) break;
         // a table too large for shared memory is read in place (through L1 / L2)
-        const float* table = a.table_in_smem ? table_sm : a.tables + size_t(q) * table_floats;
+        const float* table = TSM ? table_sm : a.tables + size_t(q) * table_floats;
         {   // set-up by all 64 lanes
-            if (a.table_in_smem) {
+            if (TSM) {
                 const float4* src = reinterpret_cast<const float4*>(a.tables + size_t(q) * table_floats);
                 float4* dst = reinterpret_cast<float4*>(table_sm);
                 for (int i = tl; i < int(table_floats / 4); i += 64) dst[i] = __ldg(src + i);
@@ -665,9 +667,9 @@ size_t search_team_extra_smem() { return size_t(kSeedCap) * 8 + kRing * 4 + kMai
 
 // Teams per block: as many as shared memory allows (at most 15, one named barrier each), fewer if
 // the register file does not hold them.
-template <bool U16>
+template <bool U16, bool TSM>
 static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st) {
-    auto kernel = search_team_kernel<U16>;
+    auto kernel = search_team_kernel<U16, TSM>;
     int teams = int((226 * 1024) / per_team);
     if (teams > 15) teams = 15;
     for (; teams >= 1; --teams) {
@@ -686,7 +688,8 @@ static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cu
 
 int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st) {
     a.per_warp_smem = uint32_t(per_team);
-    return h->comp_bytes == 2 ? launch_team_t<true>(h, a, per_team, st) : launch_team_t<false>(h, a, per_team, st);
+    if (a.table_in_smem) return h->comp_bytes == 2 ? launch_team_t<true, true>(h, a, per_team, st) : launch_team_t<false, true>(h, a, per_team, st);
+    return h->comp_bytes == 2 ? launch_team_t<true, false>(h, a, per_team, st) : launch_team_t<false, false>(h, a, per_team, st);
 }
 
 }  // namespace cpb
