@@ -54,7 +54,7 @@ __device__ __forceinline__ void primary_masks(CodeWeights cw, int rot, uint32_t 
     }
 }
 
-template <int WC, bool U16>
+template <int WC, bool U16, bool WEIGHTED = true>
 __device__ __forceinline__ uint32_t mismatch_count(const uint32_t (&a)[WC], const uint32_t (&b)[WC],
                                                    const uint32_t (&pm)[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G],
                                                    uint32_t mul) {
@@ -73,7 +73,7 @@ __device__ __forceinline__ uint32_t mismatch_count(const uint32_t (&a)[WC], cons
             acc |= (y >> (w - g * G)) & (HI >> (w - g * G));
         }
         d += __popc(acc);
-        if (mul) d += mul * __popc(acc & pm[g]);  // warp-uniform branch
+        if (WEIGHTED && mul) d += mul * __popc(acc & pm[g]);  // warp-uniform branch
     }
     return d;
 }
@@ -138,7 +138,7 @@ struct KnnTile {
     static constexpr int value = WC == 32 ? knn::kTile / 2 : knn::kTile;
 };
 
-template <int WC, bool U16, int SLOTS, int Q>
+template <int WC, bool U16, int SLOTS, int Q, bool WEIGHTED>
 __global__ void __launch_bounds__(kKnnThreads)
 knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uint64_t row_begin,
                  uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
@@ -233,7 +233,7 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
             bool any = false;
 #pragma unroll
             for (int q = 0; q < Q; ++q) {
-                d[q] = c < rows ? mismatch_count<WC, U16>(qw[q], cw, pm, cwt.mul) : kFull;
+                d[q] = c < rows ? mismatch_count<WC, U16, WEIGHTED>(qw[q], cw, pm, cwt.mul) : kFull;
                 any |= d[q] < tau[q];
             }
             if (__any_sync(kFull, any)) {
@@ -548,20 +548,28 @@ int launch_code_distance(cphnsw_b200_index* h, const void* d_a, uint64_t na, con
     return 0;
 }
 
-template <int WC, bool U16, int SLOTS, int Q>
-static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
+template <int WC, bool U16, int SLOTS, int Q, bool WEIGHTED>
+static int launch_knn_w(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
                         uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
     const size_t smem = size_t(2) * KnnTile<WC>::value * WC * 4;
-    CPB_CUDA(cudaFuncSetAttribute(knn_graph_kernel<WC, U16, SLOTS, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  int(smem)));
+    auto kernel = knn_graph_kernel<WC, U16, SLOTS, Q, WEIGHTED>;
+    CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const uint64_t rows = re - rb;
     const uint64_t blocks = (rows + kKnnWarps * Q - 1) / (kKnnWarps * Q);
     LaunchTimer timer(h, kKernelKnn, st);
-    knn_graph_kernel<WC, U16, SLOTS, Q><<<unsigned(blocks), kKnnThreads, smem, st>>>(
-        codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), code_weights(h));
+    kernel<<<unsigned(blocks), kKnnThreads, smem, st>>>(codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(),
+                                                       code_weights(h));
     h->launches++;
     CPB_CUDA(cudaGetLastError());
     return 0;
+}
+
+// the weighted (residual-code) distance is a separate instantiation: the plain count pays nothing for it
+template <int WC, bool U16, int SLOTS, int Q>
+static int launch_knn_t(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n, uint32_t k, uint64_t rb,
+                        uint64_t re, uint32_t* nbrs, uint16_t* dist, cudaStream_t st) {
+    if (h->residual_bits) return launch_knn_w<WC, U16, SLOTS, Q, true>(h, codes, n, k, rb, re, nbrs, dist, st);
+    return launch_knn_w<WC, U16, SLOTS, Q, false>(h, codes, n, k, rb, re, nbrs, dist, st);
 }
 
 template <int WC, bool U16>
