@@ -127,11 +127,18 @@ __device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, c
         constexpr uint32_t LO = U16 ? 0x7fff7fffu : 0x7f7f7f7fu;
         const uint32_t* r32 = reinterpret_cast<const uint32_t*>(row);
         const uint32_t* q32 = reinterpret_cast<const uint32_t*>(qcode);
-        const int wp = mul ? kp * (U16 ? 2 : 1) / 4 : 0;  // primary words (kp * component size is a multiple of 4)
-        for (int w = 0; w < row_bytes / 4; ++w) {
-            const uint32_t x = q32[w] ^ __ldg(r32 + w);
-            const uint32_t c = __popc((((x & LO) + LO) | x) & ~LO);  // one flag per differing byte / halfword
-            d += w < wp ? c * uint32_t(1 + mul) : c;
+        if (!mul) {
+            for (int w = 0; w < row_bytes / 4; ++w) {
+                const uint32_t x = q32[w] ^ __ldg(r32 + w);
+                d += __popc((((x & LO) + LO) | x) & ~LO);  // one flag per differing byte / halfword
+            }
+        } else {  // residual codes: a primary word counts 1 + mul (kp * component size is a multiple of 4)
+            const int wp = kp * (U16 ? 2 : 1) / 4;
+            for (int w = 0; w < row_bytes / 4; ++w) {
+                const uint32_t x = q32[w] ^ __ldg(r32 + w);
+                const uint32_t c = __popc((((x & LO) + LO) | x) & ~LO);
+                d += w < wp ? c * uint32_t(1 + mul) : c;
+            }
         }
     } else {
         for (int r = 0; r < K; ++r)
