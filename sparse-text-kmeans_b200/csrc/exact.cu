@@ -281,8 +281,8 @@ int launch_exact_t(cphnsw_b200_index* h, const float* d_base, uint64_t n, const 
     const size_t smem = size_t(2) * (TILE + kExWarps * kExQ) * kExRow * sizeof(float);
     const uint64_t blocks = (nq + uint64_t(kExWarps) * kExQ - 1) / (uint64_t(kExWarps) * kExQ);
     const uint64_t tiles = (n + TILE - 1) / TILE;
-    // enough blocks for two waves; every range holds at least four tiles
-    uint64_t S = (2 * uint64_t(h->sm_count) * 4 + blocks - 1) / blocks;
+    // enough blocks for four waves of four blocks per SM (a short tail); every range holds at least four tiles
+    uint64_t S = (4 * uint64_t(h->sm_count) * 4 + blocks - 1) / blocks;
     if (S > tiles / 4) S = tiles / 4;
     if (S > kExMaxSplit) S = kExMaxSplit;
     if (S < 1) S = 1;
