@@ -106,6 +106,7 @@ public:
                                  p.seed, fht_convention, device, &h_));
         set_param("keep_pruned", p.keep_pruned ? 1.0 : 0.0);
         set_param("k_entry", double(p.k_entry));
+        set_param("rank_pruning_alpha", double(p.rank_pruning_alpha));
     }
     ~CPHNSWIndex() { cphnsw_b200_destroy(h_); }
     CPHNSWIndex(const CPHNSWIndex&) = delete;
@@ -144,23 +145,26 @@ public:
     void add_batch(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch(h_, vecs, n)); }
     void add_batch_parallel(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch_parallel(h_, vecs, n)); }
     // build_with_gpu_knn (evaluation/test_gpu_build.cpp:168-174): bulk build from a k-candidate kNN graph
-    // (CP-code distance), pruned to M links by select_neighbors or, with prune = false, cut to the M
-    // nearest.  alpha is the legacy detour threshold (types.hpp:399-400); its pruning rule is not in the
-    // reference tree, so it is range-checked like CPHNSWParams::finalize() does and select_neighbors
-    // (the HNSW heuristic with keep_pruned) decides the links.
+    // (CP-code distance).  prune = true prunes it by rank with the detour threshold alpha, the CAGRA graph
+    // optimisation the parameter is documented for (types.hpp:399-400; rule in cphnsw_b200.h at
+    // cphnsw_b200_rank_prune); prune = false keeps the M nearest candidates.  add_batch_parallel is the
+    // build that prunes with select_neighbors (the HNSW heuristic).
     void build_with_gpu_knn(const Float* vecs, size_t n, size_t k = 64, bool prune = true, float alpha = 1.1f) {
-        if (alpha < 1.0f || alpha > 3.0f) throw std::invalid_argument("build_with_gpu_knn: alpha must be in [1.0, 3.0]");
+        if (!(alpha >= 1.0f) || alpha > 3.0f) throw std::invalid_argument("build_with_gpu_knn: alpha must be in [1.0, 3.0]");
         if (k == 0 || k > 64) throw std::invalid_argument("build_with_gpu_knn: k must be in 1..64");
         if (size() != 0) throw std::invalid_argument("build_with_gpu_knn: the index must be empty");
-        double old_k = 0, old_prune = 1;
-        check(cphnsw_b200_get_param(h_, "knn_k", &old_k));
-        check(cphnsw_b200_get_param(h_, "prune", &old_prune));
-        check(cphnsw_b200_set_param(h_, "knn_k", double(k)));
-        check(cphnsw_b200_set_param(h_, "prune", prune ? 1.0 : 0.0));
-        const int rc = cphnsw_b200_add_batch_parallel(h_, vecs, n);
-        cphnsw_b200_set_param(h_, "knn_k", old_k);
-        cphnsw_b200_set_param(h_, "prune", old_prune);
-        check(rc);
+        const char* names[4] = {"knn_k", "prune", "rank_prune", "rank_pruning_alpha"};
+        const double want[4] = {double(k), 1.0, prune ? 1.0 : 0.0, double(alpha)};
+        double old[4] = {0, 1, 0, 1.1};
+        for (int i = 0; i < 4; ++i) check(cphnsw_b200_get_param(h_, names[i], &old[i]));
+        int rc = 0;
+        for (int i = 0; i < 4 && rc == 0; ++i) rc = cphnsw_b200_set_param(h_, names[i], want[i]);
+        if (rc == 0 && !prune) rc = cphnsw_b200_set_param(h_, "prune", 0.0);
+        if (rc == 0) rc = cphnsw_b200_add_batch_parallel(h_, vecs, n);
+        // last_error() belongs to the failing call: restore the tunables only after reading it
+        std::string msg = rc ? cphnsw_b200_last_error() : "";
+        for (int i = 0; i < 4; ++i) cphnsw_b200_set_param(h_, names[i], old[i]);
+        if (rc) fail(rc, msg);
     }
 
     // ---- search ---------------------------------------------------------------------------------
@@ -243,10 +247,10 @@ public:
         return out;
     }
     Code get_code(NodeId id) const {
-        std::vector<Code> all(size());
-        check(cphnsw_b200_get_codes(h_, all.data()));
-        if (id >= all.size()) throw std::out_of_range("get_code: node id out of range");
-        return all[id];
+        if (id >= size()) throw std::out_of_range("get_code: node id out of range");
+        Code c;
+        check(cphnsw_b200_get_code(h_, id, &c));
+        return c;
     }
     std::vector<HammingDist> code_distance(const std::vector<Code>& a, const std::vector<Code>& b) const {
         std::vector<HammingDist> out(a.size() * b.size());
@@ -269,11 +273,12 @@ private:
     CPHNSWIndex(cphnsw_b200_index* h, Adopt) : h_(h) {}
     cphnsw_b200_index* h_ = nullptr;
 
-    static void check(int rc) {
-        if (rc == 0) return;
-        std::string msg = cphnsw_b200_last_error();
+    static void fail(int rc, const std::string& msg) {
         if (rc == CPHNSW_B200_E_INVALID) throw std::invalid_argument(msg);
         throw std::runtime_error(msg);
+    }
+    static void check(int rc) {
+        if (rc != 0) fail(rc, cphnsw_b200_last_error());
     }
     static std::vector<std::vector<SearchResult>> unpack(const std::vector<uint32_t>& ids, const std::vector<float>& d,
                                                          size_t nq, size_t k) {

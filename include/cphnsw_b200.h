@@ -12,7 +12,15 @@
  *     (include/cphnsw/cuda/gpu_encoder.cuh:24-93, include/cphnsw/cuda/gpu_knn_graph.cuh:28-101).
  *   - "_dev" entry points take DEVICE pointers on the index's device and a cudaStream_t passed
  *     as void*; they are asynchronous on that stream and allocate no output.
- *   - a handle is bound to one CUDA device and is thread-compatible (one thread at a time).
+ *   - a handle is bound to one CUDA device and is thread-safe.  The search entry points (search_batch,
+ *     search_and_rerank_batch, search_multiprobe_batch, brute_force_search_batch, search_calibrated_batch,
+ *     search_codes_batch, search_dev) run concurrently from any number of host threads, as the reference's
+ *     callers do from OpenMP loops (evaluation/eval_sift.cpp:279-283,380-387,423-430): each call works in a
+ *     search context of its own (stream, staging buffers, visited slots) taken from a pool in the handle.
+ *     Calls of up to 32 queries get one thread block per query and up to 64 of them run side by side; larger
+ *     batches fill the GPU and take turns.  Every other entry point (add*, install, set_param, the stage
+ *     calls, save) excludes all others while it runs, like the mutex of the reference's add
+ *     (include/cphnsw/graph/flat_graph.hpp:80-98).
  *   - code layout is row-major ComponentT[n][K], component = (argmax_index << 1) | negative
  *     (include/cphnsw/core/types.hpp:68-106).  Node ids are uint32, 0xFFFFFFFF is "no node"
  *     (types.hpp:28-30).
@@ -95,6 +103,11 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *   "build_seed" (0 = add_batch_parallel builds the exact code-distance kNN graph over everything, the
  *                 default; s > 0 = on an empty index only the first s vectors get the exact graph and
  *                 the others are inserted as add_batch does: O(n) instead of O(n^2) candidate search),
+ *   "rank_prune" (0/1, default 0: the bulk build prunes the kNN lists by rank, see cphnsw_b200_rank_prune, instead of
+ *                 running select_neighbors) and "rank_pruning_alpha" (1.0..3.0, default 1.1; CPHNSWParams::rank_pruning_alpha,
+ *                 types.hpp:399-400,459-466),
+ *   "first_wait_polls" (0..2^22, default 2^22: polls granted to the FIRST bounded wait of a kNN-graph launch; a test
+ *                 sets 0 to make that wait give up, which the call reports as CPHNSW_B200_E_DEVICE_WAIT),
  *   "entry_scan" (evenly spaced nodes scored for every query before the walk; default = k_entry),
  *   "k_entry" (1..100, default 4: how many of the scored nodes, the best, seed the walk). */
 int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double value);
@@ -141,6 +154,20 @@ int cphnsw_b200_select_neighbors(cphnsw_b200_index* h, const void* codes, uint64
                                  const uint32_t* cand, uint32_t k, uint64_t row_begin, uint64_t row_end,
                                  uint32_t M, int keep_pruned, uint32_t* adj_out);
 
+/* Rank-based pruning of kNN lists: the graph optimisation of CAGRA that the legacy index ran behind
+ * build_with_gpu_knn(base, N, k, prune = true, alpha) (evaluation/test_gpu_build.cpp:168-174; parameter
+ * "Detour threshold for rank-based pruning (CAGRA)", include/cphnsw/core/types.hpp:399-400).  The legacy source is
+ * absent; the rule is the paper's (resources/arXiv-2308.15136v2/consolidated.tex:298-340), no distance involved:
+ *   reorder  a route X -> Z -> Y (Z, Y in X's list, Y in Z's list) is a detour of the edge X -> Y when
+ *            alpha * max(rank_X(Z), rank_Z(Y)) < rank_X(Y), ranks = 1-based list positions, compared in fp32
+ *            (alpha = 1: the paper's condition); X keeps its M candidates with the fewest detours, ties by rank;
+ *   reverse  P receives every X that kept P, ordered by (position of P in X's kept list, X);
+ *   merge    kept list and reverse list of P are interleaved, kept list first, each id once, until M links are
+ *            chosen; when one list runs out the other goes on alone.
+ * cand uint32[n][k] (k <= 64) for ALL n nodes in ascending (distance, id) order -> adj_out uint32[n][M]. */
+int cphnsw_b200_rank_prune(cphnsw_b200_index* h, const uint32_t* cand, uint64_t n, uint32_t k, uint32_t M, float alpha,
+                           uint32_t* adj_out);
+
 /* ---- index build and search, host pointers -------------------------------------------------- */
 
 /* Replaces CPHNSWIndex::add_batch_parallel / add_batch (use sites evaluation/eval_master.cpp:89,
@@ -158,8 +185,9 @@ int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_
  * On an empty index this is add_batch_parallel. */
 int cphnsw_b200_add_batch(cphnsw_b200_index* h, const float* x, uint64_t n);
 
-/* CPHNSWIndex::get_code (evaluation/debug_code_storage.cpp:75) for all nodes, and the adjacency
- * uint32[size][M] (FlatGraph neighbour ids, include/cphnsw/graph/flat_graph.hpp:179-181). */
+/* CPHNSWIndex::get_code (evaluation/debug_code_storage.cpp:75) for one node (ComponentT[K]) and for all nodes,
+ * and the adjacency uint32[size][M] (FlatGraph neighbour ids, include/cphnsw/graph/flat_graph.hpp:179-181). */
+int cphnsw_b200_get_code(const cphnsw_b200_index* h, uint32_t id, void* code_out);
 int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out);
 int cphnsw_b200_get_adjacency(const cphnsw_b200_index* h, uint32_t* adj_out);
 /* ids scored for every query before the graph walk (entry_scan evenly spaced node ids); the k_entry best of
@@ -172,6 +200,13 @@ int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uin
  * Beam width is max(ef, k).  stats (optional) uint32[nq][2] = expansions, distance evaluations. */
 int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                              uint32_t ef, uint32_t* ids_out, float* dists_out, uint32_t* stats_out);
+
+/* The same walk under the symmetric code distance to given query CODES (ComponentT[nq][K]): the unified index's
+ * search, SearchEngine<Policy>::search over FlatGraph (include/cphnsw/search/search_engine.hpp:86-193) with
+ * distance = code distance (Hamming distance in binary-code mode, residual weighting included); also the walk
+ * search_multiprobe runs per probe code and add_batch runs per new node.  Distances are returned as floats. */
+int cphnsw_b200_search_codes_batch(cphnsw_b200_index* h, const void* qcodes, uint64_t nq, uint32_t k, uint32_t ef,
+                                   uint32_t* ids_out, float* dists_out, uint32_t* stats_out);
 
 /* Batched CPHNSWIndex::search_and_rerank(q,k,ef,rerank_k) (evaluation/eval_master.cpp:145;
  * steps shown by hand at evaluation/eval_sift.cpp:539-563; replaces GPUBruteForce::rerank,
@@ -264,6 +299,16 @@ int cphnsw_b200_select_neighbors_dev(cphnsw_b200_index* h, const void* d_codes, 
  * codes [n][K], adjacency uint32[n][M].  Used after a sharded build has all-gathered its rows. */
 int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const void* d_codes,
                             const uint32_t* d_adj, uint64_t n, void* stream);
+/* The same from host buffers (FlatGraph::add_node + add_neighbor for every node,
+ * include/cphnsw/graph/flat_graph.hpp:80-98,204-208). */
+int cphnsw_b200_install(cphnsw_b200_index* h, const float* vectors, const void* codes, const uint32_t* adj, uint64_t n);
+/* The two halves of cphnsw_b200_rank_prune for row-block sharded builds: reorder writes the M kept ids of rows
+ * [row_begin, row_end) from the candidate lists of ALL n nodes; merge needs the kept rows of all n nodes (gathered
+ * in between) and writes the final rows of the range. */
+int cphnsw_b200_rank_reorder_dev(cphnsw_b200_index* h, const uint32_t* d_cand, uint64_t n, uint32_t k, uint64_t row_begin,
+                                 uint64_t row_end, uint32_t M, float alpha, uint32_t* d_kept, void* stream);
+int cphnsw_b200_rank_merge_dev(cphnsw_b200_index* h, const uint32_t* d_kept, uint64_t n, uint32_t M, uint64_t row_begin,
+                               uint64_t row_end, uint32_t* d_adj, void* stream);
 /* d_q float[nq][dim]; outputs device uint32[nq][k] / float[nq][k]; rerank_k = 0 means plain search. */
 int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, uint32_t k, uint32_t ef,
                            uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
@@ -290,7 +335,10 @@ int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint
  * The first call on each device looks up the array's device address; make that first call outside
  * any stream capture.  All calls share the one array: it is fully rewritten by each call (nothing
  * from an earlier call is read), but two calls whose kernels can overlap on the GPU - different
- * streams, or different threads - race on it; serialise them. */
+ * streams, or different threads - race on it; serialise them.
+ *
+ * The plain count only: the residual weighting of a binary-code index ("residual_bits", "residual_shift") belongs
+ * to a handle and is not applied here. */
 int cphnsw_b200_code_distance_noalloc(const void* d_a, uint64_t na, const void* d_b, uint64_t nb, uint32_t K,
                                       uint32_t component_bytes, uint16_t* d_out, void* stream);
 

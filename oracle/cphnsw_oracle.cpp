@@ -640,6 +640,80 @@ uint64_t orc_connectivity(const uint32_t* adj, uint64_t n, uint64_t M, const uin
     return count;
 }
 
+// Rank-based pruning of kNN lists (CAGRA graph optimisation; the legacy build_with_gpu_knn(..., prune,
+// alpha), evaluation/test_gpu_build.cpp:168-174, parameter include/cphnsw/core/types.hpp:399-400; rule
+// resources/arXiv-2308.15136v2/consolidated.tex:298-340).  cand[n][k] in ascending (distance, id) order.
+//   reorder: detours of edge X -> Y = #{Z in L_X : Y in L_Z and alpha * max(rank_X(Z), rank_Z(Y)) < rank_X(Y)},
+//            ranks 1-based, the product in fp32; keep the M first by (detours, rank).
+//   reverse: P receives the X that kept P, ordered by (position of P in X's kept list, X), at most M.
+//   merge:   interleave kept and reverse list, kept first, each id once, until M; an exhausted list
+//            passes its turns to the other.
+int orc_rank_prune(const uint32_t* cand, uint64_t n, uint64_t k, uint64_t M, float alpha, uint32_t* adj) {
+    std::vector<uint32_t> kept(n * M, kInvalid);
+#pragma omp parallel for schedule(static)
+    for (int64_t x = 0; x < (int64_t)n; ++x) {
+        const uint32_t* lx = cand + (size_t)x * k;
+        std::vector<std::pair<uint32_t, uint32_t>> order;  // (detours, position)
+        for (size_t j = 0; j < k; ++j) {
+            const uint32_t y = lx[j];
+            if (y >= n) continue;
+            uint32_t detours = 0;
+            for (size_t i = 0; i < k; ++i) {
+                const uint32_t z = lx[i];
+                if (z >= n) continue;
+                const uint32_t* lz = cand + (size_t)z * k;
+                for (size_t p = 0; p < k; ++p)
+                    if (lz[p] == y) {
+                        const float thr = alpha * (float)(std::max(i, p) + 1);
+                        if (thr < (float)(j + 1)) ++detours;
+                    }
+            }
+            order.push_back({detours, (uint32_t)j});
+        }
+        std::sort(order.begin(), order.end());
+        for (size_t t = 0; t < order.size() && t < M; ++t) kept[(size_t)x * M + t] = lx[order[t].second];
+    }
+    std::vector<std::vector<std::pair<uint32_t, uint32_t>>> rev(n);  // (position in the chooser's list, chooser)
+    for (size_t x = 0; x < n; ++x)
+        for (size_t r = 0; r < M; ++r) {
+            const uint32_t p = kept[x * M + r];
+            if (p < n) rev[p].push_back({(uint32_t)r, (uint32_t)x});
+        }
+#pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < (int64_t)n; ++p) {
+        std::sort(rev[p].begin(), rev[p].end());
+        if (rev[p].size() > M) rev[p].resize(M);
+        std::vector<uint32_t> a, b, out;
+        for (size_t r = 0; r < M; ++r)
+            if (kept[(size_t)p * M + r] < n) a.push_back(kept[(size_t)p * M + r]);
+        for (auto& e : rev[p]) b.push_back(e.second);
+        size_t ia = 0, ib = 0;
+        int turn = 0;
+        auto taken = [&](uint32_t id) { return std::find(out.begin(), out.end(), id) != out.end(); };
+        while (out.size() < M) {
+            while (ia < a.size() && taken(a[ia])) ++ia;
+            while (ib < b.size() && taken(b[ib])) ++ib;
+            if (ia >= a.size() && ib >= b.size()) break;
+            const bool from_a = ib >= b.size() || (ia < a.size() && turn == 0);
+            out.push_back(from_a ? a[ia++] : b[ib++]);
+            turn ^= 1;
+        }
+        for (size_t t = 0; t < M; ++t) adj[(size_t)p * M + t] = t < out.size() ? out[t] : kInvalid;
+    }
+    return 0;
+}
+
+// Thread count of every parallel region from now on (launchers such as torchrun export OMP_NUM_THREADS=1).
+int orc_set_threads(int threads) {
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+    return omp_get_max_threads();
+#else
+    (void)threads;
+    return 1;
+#endif
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

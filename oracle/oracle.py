@@ -123,6 +123,20 @@ def select_neighbors(codes, cand, M, keep_pruned=True, row_begin=0):
     return adj
 
 
+def rank_prune(cand, M, alpha=1.1):
+    """Rank-based (CAGRA) pruning of the kNN lists of all nodes: cand [n][k] -> adjacency [n][M]."""
+    cand = np.ascontiguousarray(cand, np.uint32)
+    n, k = cand.shape
+    adj = np.empty((n, M), np.uint32)
+    lib().orc_rank_prune(_ptr(cand), C.c_uint64(n), C.c_uint64(k), C.c_uint64(M), C.c_float(alpha), _ptr(adj))
+    return adj
+
+
+def set_threads(threads):
+    """Sets the OpenMP thread count of the oracle (returns the count now in force)."""
+    return int(lib().orc_set_threads(C.c_int(int(threads))))
+
+
 def search(tables, codes, adj, entry_ids, ef, k, want_stats=False, n_seed=None):
     """n_seed: how many of the scored entry ids seed the walk (None = all of them)."""
     tables = np.ascontiguousarray(tables, np.float32)
@@ -363,3 +377,51 @@ class Ref:
         self.l.ref_encode_batch_signbits32(_ptr(x), C.c_uint64(x.shape[0]), C.c_uint64(x.shape[1]),
                                            C.c_uint64(seed), _ptr(out))
         return out
+
+
+def ref_search_available():
+    return os.path.exists(os.path.join(_HERE, "_ref", "libcphnsw_ref_search.so"))
+
+
+class RefSearch:
+    """The reference's own graph walk (include/cphnsw/search/search_engine.hpp:86-193), built by
+    `make -C oracle ref` from a throw-away patched copy of its headers (see ref_search_shim.cpp).
+    Codes are packed sign bits; every call returns W in full (k = ef), ascending by distance."""
+
+    def __init__(self):
+        self.l = C.CDLL(os.path.join(_HERE, "_ref", "libcphnsw_ref_search.so"))
+
+    def _out(self, nq, ef):
+        return np.empty((nq, ef), np.uint32), np.empty((nq, ef), np.float32), np.empty(nq, np.uint32)
+
+    def search_64(self, codes, adj, qcodes, entry, ef):
+        codes = np.ascontiguousarray(codes, np.uint64)
+        qcodes = np.ascontiguousarray(qcodes, np.uint64)
+        adj = np.ascontiguousarray(adj, np.uint32)
+        entry = np.ascontiguousarray(entry, np.uint32)
+        ids, dist, cnt = self._out(qcodes.shape[0], ef)
+        self.l.ref_search_64(_ptr(codes), C.c_uint64(codes.shape[0]), _ptr(adj), C.c_uint64(adj.shape[1]), _ptr(qcodes),
+                             C.c_uint64(qcodes.shape[0]), _ptr(entry), C.c_uint64(entry.size), C.c_uint64(ef),
+                             _ptr(ids), _ptr(dist), _ptr(cnt))
+        return ids, dist, cnt
+
+    def search_32_16_s2(self, primary, residual, adj, q_primary, q_residual, entry, ef):
+        arrs = [np.ascontiguousarray(a, np.uint64) for a in (primary, residual, q_primary, q_residual)]
+        adj = np.ascontiguousarray(adj, np.uint32)
+        entry = np.ascontiguousarray(entry, np.uint32)
+        ids, dist, cnt = self._out(arrs[2].shape[0], ef)
+        self.l.ref_search_32_16_s2(_ptr(arrs[0]), _ptr(arrs[1]), C.c_uint64(arrs[0].shape[0]), _ptr(adj),
+                                   C.c_uint64(adj.shape[1]), _ptr(arrs[2]), _ptr(arrs[3]), C.c_uint64(arrs[2].shape[0]),
+                                   _ptr(entry), C.c_uint64(entry.size), C.c_uint64(ef), _ptr(ids), _ptr(dist), _ptr(cnt))
+        return ids, dist, cnt
+
+
+def pack_sign_bits(codes):
+    """One-byte sign components [n][K <= 64] -> uint64[n], bit r = component r (core/codes.hpp:21-52)."""
+    codes = np.asarray(codes)
+    return ((codes.astype(np.uint64) & np.uint64(1)) << np.arange(codes.shape[1], dtype=np.uint64)).sum(axis=1).astype(np.uint64)
+
+
+def unpack_sign_bits(words, K):
+    words = np.asarray(words, np.uint64)
+    return ((words[:, None] >> np.arange(K, dtype=np.uint64)) & np.uint64(1)).astype(np.uint8)

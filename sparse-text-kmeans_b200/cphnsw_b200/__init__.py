@@ -38,7 +38,9 @@ EXPORTS = [
     "cphnsw_b200_calibrate", "cphnsw_b200_get_calibration", "cphnsw_b200_search_calibrated_batch",
     "cphnsw_b200_save", "cphnsw_b200_load", "cphnsw_b200_add_batch", "cphnsw_b200_get_binary_codes",
     "cphnsw_b200_create_binary", "cphnsw_b200_set_exact_base", "cphnsw_b200_exact_search_batch",
-    "cphnsw_b200_rerank_batch", "cphnsw_b200_exact_search_dev",
+    "cphnsw_b200_rerank_batch", "cphnsw_b200_exact_search_dev", "cphnsw_b200_rank_prune",
+    "cphnsw_b200_rank_reorder_dev", "cphnsw_b200_rank_merge_dev", "cphnsw_b200_install",
+    "cphnsw_b200_search_codes_batch", "cphnsw_b200_get_code",
 ]
 
 
@@ -267,7 +269,38 @@ class CPHNSWIndex:
         return out
 
     def get_code(self, node_id):
-        return self.codes()[node_id]
+        """CPHNSWIndex::get_code (evaluation/debug_code_storage.cpp:75): the K components of one node."""
+        out = np.empty(self.K, self.code_dtype)
+        _check(self._lib.cphnsw_b200_get_code(self._h, _u32(node_id), _p(out)))
+        return out
+
+    def install(self, vectors, codes, adj):
+        """A complete index from host arrays: vectors [n][dim], codes [n][K], adjacency uint32 [n][M]."""
+        vectors = self._vecs(vectors)
+        codes = self._codes(codes)
+        adj = np.ascontiguousarray(adj, np.uint32)
+        assert codes.shape[0] == vectors.shape[0] == adj.shape[0] and adj.shape[1] == self.M
+        _check(self._lib.cphnsw_b200_install(self._h, _p(vectors), _p(codes), _p(adj), _u64(vectors.shape[0])))
+
+    def rank_prune(self, cand, M=None, alpha=1.1):
+        """Rank-based (CAGRA) pruning of the kNN lists of ALL nodes: cand uint32 [n][k] -> adjacency [n][M]."""
+        cand = np.ascontiguousarray(cand, np.uint32)
+        M = self.M if M is None else M
+        adj = np.empty((cand.shape[0], M), np.uint32)
+        _check(self._lib.cphnsw_b200_rank_prune(self._h, _p(cand), _u64(cand.shape[0]), _u32(cand.shape[1]), _u32(M),
+                                                C.c_float(alpha), _p(adj)))
+        return adj
+
+    def search_codes_batch(self, qcodes, k, ef, want_stats=False):
+        """The walk under the symmetric code distance to the given query codes [nq][K]."""
+        qcodes = self._codes(qcodes)
+        nq = qcodes.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        stats = np.zeros((nq, 2), np.uint32) if want_stats else None
+        _check(self._lib.cphnsw_b200_search_codes_batch(self._h, _p(qcodes), _u64(nq), _u32(k), _u32(ef), _p(ids), _p(dist),
+                                                        _p(stats)))
+        return (ids, dist, stats) if want_stats else (ids, dist)
 
     def binary_codes(self):
         """Sign bits of the stored codes, uint64 [size][(K+63)//64] (the unified index's primary code)."""
@@ -431,6 +464,15 @@ class CPHNSWIndex:
                                                           _u32(k), _u64(row_begin), _u64(row_end), _u32(M),
                                                           C.c_int(int(keep_pruned)), C.c_void_p(d_adj),
                                                           C.c_void_p(stream)))
+
+    def rank_reorder_dev(self, d_cand, n, k, row_begin, row_end, M, alpha, d_kept, stream=0):
+        _check(self._lib.cphnsw_b200_rank_reorder_dev(self._h, C.c_void_p(d_cand), _u64(n), _u32(k), _u64(row_begin),
+                                                      _u64(row_end), _u32(M), C.c_float(alpha), C.c_void_p(d_kept),
+                                                      C.c_void_p(stream)))
+
+    def rank_merge_dev(self, d_kept, n, M, row_begin, row_end, d_adj, stream=0):
+        _check(self._lib.cphnsw_b200_rank_merge_dev(self._h, C.c_void_p(d_kept), _u64(n), _u32(M), _u64(row_begin),
+                                                    _u64(row_end), C.c_void_p(d_adj), C.c_void_p(stream)))
 
     def install_dev(self, d_vectors, d_codes, d_adj, n, stream=0):
         _check(self._lib.cphnsw_b200_install_dev(self._h, C.c_void_p(d_vectors), C.c_void_p(d_codes),

@@ -28,9 +28,11 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 LaunchTimer::LaunchTimer(cphnsw_b200_index* h_, int kind_, cudaStream_t st_) : h(h_), kind(kind_), st(st_) {
     if (!h->profile) return;
+    std::lock_guard<std::mutex> lock(h->ev_mu);
     auto& pool = h->events[kind];
     size_t& used = h->events_used[kind];
     if (used == pool.size()) {
+        if (pool.size() == pool.capacity()) return;  // growing would move the pairs other timers point at
         EventPair e;
         if (cudaEventCreate(&e.start) != cudaSuccess || cudaEventCreate(&e.stop) != cudaSuccess) return;
         pool.push_back(e);
@@ -123,38 +125,117 @@ int set_entry_ids(cphnsw_b200_index* h) {
     return 0;
 }
 
-// codes already in d_codes, vectors in d_vectors: build adjacency and entry ids
-int build_graph(cphnsw_b200_index* h, cudaStream_t st) {
-    const uint64_t n = h->n;
+// grows a device buffer to new_bytes keeping its first keep_bytes
+int grow_keep(DevBuf& b, size_t keep_bytes, size_t new_bytes) {
+    if (b.p && new_bytes <= b.bytes) return 0;
+    void* p = nullptr;
+    const size_t cap = new_bytes + new_bytes / 2;
+    CPB_CUDA(cudaMalloc(&p, cap));
+    if (b.p && keep_bytes) {
+        cudaError_t e = cudaMemcpy(p, b.p, keep_bytes, cudaMemcpyDeviceToDevice);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            CPB_CUDA(e);
+        }
+    }
+    b.release();
+    b.p = p;
+    b.bytes = cap;
+    return 0;
+}
+
+// adjacency of the first n nodes (codes in d_codes) into `adj`: kNN candidates, then pruning.  The
+// handle's own adjacency and node count are left alone; the caller commits them on success.
+int build_graph(cphnsw_b200_index* h, uint64_t n, DevBuf& adj, cudaStream_t st) {
     uint32_t k = h->knn_k ? h->knn_k : (2 * h->M < 64 ? 2 * h->M : 64);
     if (k < h->M) k = h->M;
     if (k > 64) k = 64;
-    CPB_TRY(h->d_adj.reserve(size_t(n) * h->M * 4 + 16));
+    CPB_TRY(adj.reserve(size_t(n) * h->M * 4 + 16));
     if (!h->prune) {
         // build_with_gpu_knn(..., prune = false): the M nearest by (code distance, id) are the links
-        CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, h->M, 0, n, h->d_adj.as<uint32_t>(), nullptr, st));
+        CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, h->M, 0, n, adj.as<uint32_t>(), nullptr, st));
         CPB_CUDA(cudaStreamSynchronize(st));
-        CPB_TRY(check_status(h));
-        return set_entry_ids(h);
+        return check_status(h);
     }
     CPB_TRY(h->s_out.reserve(size_t(n) * k * 4 + 16));
     CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, k, 0, n, h->s_out.as<uint32_t>(), nullptr, st));
-    CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n, h->s_out.as<uint32_t>(), k, 0, n, h->M, h->keep_pruned,
-                                    h->d_adj.as<uint32_t>(), st));
+    if (h->rank_prune)
+        CPB_TRY(launch_rank_prune(h, n, h->s_out.as<uint32_t>(), k, h->M, h->rank_pruning_alpha, adj.as<uint32_t>(), st));
+    else
+        CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n, h->s_out.as<uint32_t>(), k, 0, n, h->M, h->keep_pruned,
+                                        adj.as<uint32_t>(), st));
     CPB_CUDA(cudaStreamSynchronize(st));
-    CPB_TRY(check_status(h));
-    return set_entry_ids(h);
+    return check_status(h);
 }
 
-// scan_only: brute_force_search (every node scored, no walk); calibrated: distances mapped through the fit
+// A search call's lease on one of the handle's contexts: a free one of the right kind, a new one while
+// the pool may grow, else the call waits for one to come back.
+constexpr size_t kMaxWideCtx = 1;     // launches that fill the GPU gain nothing from running side by side
+constexpr size_t kMaxNarrowCtx = 64;  // single-query calls from as many host threads
+struct CtxLease {
+    cphnsw_b200_index* h = nullptr;
+    SearchCtx* cx = nullptr;
+    int acquire(cphnsw_b200_index* h_, bool wide) {
+        h = h_;
+        std::unique_lock<std::mutex> lock(h->ctx_mu);
+        for (;;) {
+            size_t have = 0;
+            for (auto& c : h->ctxs) {
+                if (c->wide != wide) continue;
+                ++have;
+                if (!c->busy) {
+                    c->busy = true;
+                    cx = c.get();
+                    return 0;
+                }
+            }
+            if (have < (wide ? kMaxWideCtx : kMaxNarrowCtx)) {
+                std::unique_ptr<SearchCtx> c(new SearchCtx());
+                c->wide = wide;
+                CPB_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+                CPB_CUDA(cudaEventCreateWithFlags(&c->done, cudaEventDisableTiming));
+                CPB_TRY(c->d_counter.reserve(16));
+                c->busy = true;
+                cx = c.get();
+                h->ctxs.push_back(std::move(c));
+                return 0;
+            }
+            h->ctx_cv.wait(lock);
+        }
+    }
+    // work of this call goes to stream `st`: it must start behind whatever last used the scratch
+    int begin(cudaStream_t st) {
+        if (cx->pending) CPB_CUDA(cudaStreamWaitEvent(st, cx->done, 0));
+        return 0;
+    }
+    // the call returns without having waited for `st`: the next user of the scratch has to
+    int leave_pending(cudaStream_t st) {
+        CPB_CUDA(cudaEventRecord(cx->done, st));
+        cx->pending = true;
+        return 0;
+    }
+    ~CtxLease() {
+        if (!cx) return;
+        {
+            std::lock_guard<std::mutex> lock(h->ctx_mu);
+            cx->busy = false;
+        }
+        h->ctx_cv.notify_one();
+    }
+};
+
+// scan_only: brute_force_search (every node scored, no walk); calibrated: distances mapped through the fit;
+// q_codes: the walk runs under the symmetric code distance to these query codes ([nq][K], same place as q).
+// `st` is the caller's stream for device-pointer calls and nullptr for host-pointer calls, which run on the
+// context's own stream and return with the results copied out.
 int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t nq, uint32_t k, uint32_t ef,
               uint32_t rerank_k, uint32_t* ids, float* dists, uint32_t* stats, bool out_on_device,
-              cudaStream_t st, int scan_only = 0, bool calibrated = false) {
+              cudaStream_t st, int scan_only = 0, bool calibrated = false, const void* q_codes = nullptr) {
     if (h->n == 0) {
         set_error("search on an empty index");
         return CPHNSW_B200_E_STATE;
     }
-    if (k == 0 || (!q && nq) || !ids || !dists) {
+    if (k == 0 || (!q && !q_codes && nq) || !ids || !dists) {
         set_error("search: k must be > 0 and query/output pointers non-null");
         return CPHNSW_B200_E_INVALID;
     }
@@ -168,25 +249,48 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
         set_error("search: beam width max(ef, k, rerank_k) must be <= 1024 (got %u)", beam);
         return CPHNSW_B200_E_INVALID;
     }
+    if (nq == 0) return 0;
+    CtxLease lease;
+    CPB_TRY(lease.acquire(h, nq > kNarrowQueries));
+    SearchCtx& cx = *lease.cx;
+    const bool own_stream = !(q_on_device || out_on_device);
+    if (own_stream) st = cx.stream;
+    CPB_TRY(lease.begin(st));
     const uint64_t chunk = 16384;  // queries per launch: bounds the rotated-table scratch
     const size_t table_floats = size_t(h->K) * h->P;
+    const size_t rb = code_row_bytes(h);
+    bool synced = false;
     for (uint64_t q0 = 0; q0 < nq; q0 += chunk) {
         const uint64_t m = nq - q0 < chunk ? nq - q0 : chunk;
-        const float* dq;
-        if (q_on_device) {
-            dq = q + q0 * h->dim;
+        synced = false;
+        const float* dq = nullptr;
+        const void* dqc = nullptr;  // query codes of a symmetric walk
+        if (q_codes) {
+            if (q_on_device) {
+                dqc = static_cast<const unsigned char*>(q_codes) + q0 * rb;
+            } else {
+                CPB_TRY(cx.d_qcodes.reserve(m * rb + 16));
+                CPB_CUDA(cudaMemcpyAsync(cx.d_qcodes.p, static_cast<const unsigned char*>(q_codes) + q0 * rb, m * rb,
+                                         cudaMemcpyHostToDevice, st));
+                dqc = cx.d_qcodes.p;
+            }
         } else {
-            CPB_TRY(h->d_q.reserve(m * h->dim * 4));
-            CPB_CUDA(cudaMemcpyAsync(h->d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
-            dq = h->d_q.as<float>();
-        }
-        CPB_TRY(h->d_qcodes.reserve(m * code_row_bytes(h) + 16));
-        if (h->binary_codes) {
-            // binary-code mode: the walk compares sign-bit codes (Hamming distance), no query table
-            CPB_TRY(launch_encode(h, dq, m, h->d_qcodes.p, nullptr, nullptr, st));
-        } else {
-            CPB_TRY(h->d_qtables.reserve(m * table_floats * 4));
-            CPB_TRY(launch_encode(h, dq, m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
+            if (q_on_device) {
+                dq = q + q0 * h->dim;
+            } else {
+                CPB_TRY(cx.d_q.reserve(m * h->dim * 4));
+                CPB_CUDA(cudaMemcpyAsync(cx.d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
+                dq = cx.d_q.as<float>();
+            }
+            CPB_TRY(cx.d_qcodes.reserve(m * rb + 16));
+            if (h->binary_codes) {
+                // binary-code mode: the walk compares sign-bit codes (Hamming distance), no query table
+                CPB_TRY(launch_encode(h, dq, m, cx.d_qcodes.p, nullptr, nullptr, st));
+                dqc = cx.d_qcodes.p;
+            } else {
+                CPB_TRY(cx.d_qtables.reserve(m * table_floats * 4));
+                CPB_TRY(launch_encode(h, dq, m, cx.d_qcodes.p, cx.d_qtables.as<float>(), nullptr, st));
+            }
         }
         uint32_t *o_ids, *o_stats = nullptr;
         float* o_d;
@@ -195,25 +299,28 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
             o_d = dists + q0 * k;
             if (stats) o_stats = stats + q0 * 2;
         } else {
-            CPB_TRY(h->d_out_ids.reserve(m * k * 4));
-            CPB_TRY(h->d_out_dist.reserve(m * k * 4));
-            o_ids = h->d_out_ids.as<uint32_t>();
-            o_d = h->d_out_dist.as<float>();
+            CPB_TRY(cx.d_out_ids.reserve(m * k * 4));
+            CPB_TRY(cx.d_out_dist.reserve(m * k * 4));
+            o_ids = cx.d_out_ids.as<uint32_t>();
+            o_d = cx.d_out_dist.as<float>();
             if (stats) {
-                CPB_TRY(h->d_stats.reserve(m * 8));
-                o_stats = h->d_stats.as<uint32_t>();
+                CPB_TRY(cx.d_stats.reserve(m * 8));
+                o_stats = cx.d_stats.as<uint32_t>();
             }
         }
-        CPB_TRY(launch_search(h, dq, h->d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st,
-                              h->binary_codes ? h->d_qcodes.p : nullptr, scan_only));
+        CPB_TRY(launch_search(h, cx, dq, cx.d_qtables.as<float>(), m, k, beam, rerank_k, o_ids, o_d, o_stats, st, dqc,
+                              scan_only));
         if (calibrated && rerank_k == 0) CPB_TRY(launch_affine(h, o_d, m * k, float(h->calib_alpha), float(h->calib_beta), st));
         if (!out_on_device) {
             CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, o_ids, m * k * 4, cudaMemcpyDeviceToHost, st));
             CPB_CUDA(cudaMemcpyAsync(dists + q0 * k, o_d, m * k * 4, cudaMemcpyDeviceToHost, st));
             if (stats) CPB_CUDA(cudaMemcpyAsync(stats + q0 * 2, o_stats, m * 8, cudaMemcpyDeviceToHost, st));
             CPB_CUDA(cudaStreamSynchronize(st));
+            synced = true;
         }
     }
+    if (synced) cx.pending = false;
+    else CPB_TRY(lease.leave_pending(st));
     return 0;
 }
 
@@ -304,36 +411,42 @@ int do_multiprobe(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
             return CPHNSW_B200_E_INVALID;
         }
     }
+    if (nq == 0) return 0;
     const uint64_t chunk = 4096;
     const size_t table_floats = size_t(h->K) * h->P;
     const size_t rb = code_row_bytes(h);
-    cudaStream_t st = 0;
+    CtxLease lease;
+    CPB_TRY(lease.acquire(h, (nq < chunk ? nq : chunk) * T > kNarrowQueries));
+    SearchCtx& cx = *lease.cx;
+    cudaStream_t st = cx.stream;
+    CPB_TRY(lease.begin(st));
     for (uint64_t q0 = 0; q0 < nq; q0 += chunk) {
         const uint64_t m = nq - q0 < chunk ? nq - q0 : chunk;
-        CPB_TRY(h->d_q.reserve(m * h->dim * 4));
-        CPB_CUDA(cudaMemcpyAsync(h->d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
-        CPB_TRY(h->d_qtables.reserve(m * table_floats * 4));
-        CPB_TRY(h->d_qcodes.reserve(m * rb + 16));
-        CPB_TRY(launch_encode(h, h->d_q.as<float>(), m, h->d_qcodes.p, h->d_qtables.as<float>(), nullptr, st));
-        CPB_TRY(h->d_probe_codes.reserve(m * T * rb + 16));
-        CPB_TRY(launch_probe_codes(h, h->d_qtables.as<float>(), m, T, h->d_probe_codes.p, st));
+        CPB_TRY(cx.d_q.reserve(m * h->dim * 4));
+        CPB_CUDA(cudaMemcpyAsync(cx.d_q.p, q + q0 * h->dim, m * h->dim * 4, cudaMemcpyHostToDevice, st));
+        CPB_TRY(cx.d_qtables.reserve(m * table_floats * 4));
+        CPB_TRY(cx.d_qcodes.reserve(m * rb + 16));
+        CPB_TRY(launch_encode(h, cx.d_q.as<float>(), m, cx.d_qcodes.p, cx.d_qtables.as<float>(), nullptr, st));
+        CPB_TRY(cx.d_probe_codes.reserve(m * T * rb + 16));
+        CPB_TRY(launch_probe_codes(h, cx.d_qtables.as<float>(), m, T, cx.d_probe_codes.p, st));
         if (probe_codes_out)
-            CPB_CUDA(cudaMemcpyAsync((char*)probe_codes_out + q0 * T * rb, h->d_probe_codes.p, m * T * rb,
+            CPB_CUDA(cudaMemcpyAsync((char*)probe_codes_out + q0 * T * rb, cx.d_probe_codes.p, m * T * rb,
                                      cudaMemcpyDeviceToHost, st));
         if (search) {
-            CPB_TRY(h->d_probe_ids.reserve(m * T * k * 4));
-            CPB_TRY(h->d_probe_dist.reserve(m * T * k * 4));
-            CPB_TRY(h->d_out_ids.reserve(m * k * 4));
-            CPB_TRY(h->d_out_dist.reserve(m * k * 4));
-            CPB_TRY(launch_search(h, nullptr, nullptr, m * T, k, beam, 0, h->d_probe_ids.as<uint32_t>(),
-                                  h->d_probe_dist.as<float>(), nullptr, st, h->d_probe_codes.p));
-            CPB_TRY(launch_merge_probes(h, h->d_probe_ids.as<uint32_t>(), h->d_probe_dist.as<float>(), m, T, k,
-                                        h->d_out_ids.as<uint32_t>(), h->d_out_dist.as<float>(), st));
-            CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, h->d_out_ids.p, m * k * 4, cudaMemcpyDeviceToHost, st));
-            CPB_CUDA(cudaMemcpyAsync(dists + q0 * k, h->d_out_dist.p, m * k * 4, cudaMemcpyDeviceToHost, st));
+            CPB_TRY(cx.d_probe_ids.reserve(m * T * k * 4));
+            CPB_TRY(cx.d_probe_dist.reserve(m * T * k * 4));
+            CPB_TRY(cx.d_out_ids.reserve(m * k * 4));
+            CPB_TRY(cx.d_out_dist.reserve(m * k * 4));
+            CPB_TRY(launch_search(h, cx, nullptr, nullptr, m * T, k, beam, 0, cx.d_probe_ids.as<uint32_t>(),
+                                  cx.d_probe_dist.as<float>(), nullptr, st, cx.d_probe_codes.p));
+            CPB_TRY(launch_merge_probes(h, cx.d_probe_ids.as<uint32_t>(), cx.d_probe_dist.as<float>(), m, T, k,
+                                        cx.d_out_ids.as<uint32_t>(), cx.d_out_dist.as<float>(), st));
+            CPB_CUDA(cudaMemcpyAsync(ids + q0 * k, cx.d_out_ids.p, m * k * 4, cudaMemcpyDeviceToHost, st));
+            CPB_CUDA(cudaMemcpyAsync(dists + q0 * k, cx.d_out_dist.p, m * k * 4, cudaMemcpyDeviceToHost, st));
         }
         CPB_CUDA(cudaStreamSynchronize(st));
     }
+    cx.pending = false;
     return 0;
 }
 
@@ -358,6 +471,7 @@ int cphnsw_b200_kernel_time(cphnsw_b200_index* h, int kind, double* total_ms, ui
         set_error("kernel_time: bad argument");
         return CPHNSW_B200_E_INVALID;
     }
+    std::lock_guard<std::mutex> lock(h->ev_mu);
     double sum = 0.0;
     for (size_t i = 0; i < h->events_used[kind]; ++i) {
         float ms = 0.f;
@@ -410,6 +524,11 @@ static int create_impl(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
         return CPHNSW_B200_E_INVALID;
     }
     if (fht_convention < 0 || fht_convention > 2) { set_error("unknown fht_convention %d", fht_convention); return CPHNSW_B200_E_INVALID; }
+    // the encode kernels serve padded dims up to 32768 (a uint16 component holds no more), 65536 for sign-bit codes
+    if (dim > (binary ? 65536u : 32768u)) {
+        set_error("dim %llu is too large (max %u)", (unsigned long long)dim, binary ? 65536u : 32768u);
+        return CPHNSW_B200_E_INVALID;
+    }
     const uint64_t P = next_pow2(dim);
     // a component holds (index << 1) | sign (types.hpp:88-90)
     if (!binary && ((component_bytes == 1 && P > 128) || (component_bytes == 2 && P > 32768))) {
@@ -454,6 +573,8 @@ static int create_impl(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
             for (uint64_t i = 0; i < P; ++i) h->signs[(size_t(r) * 3 + l) * P + i] = coin(rng) ? 1 : -1;
     }
     int rc = upload_signs(h);
+    h->events[0].reserve(1024);  // LaunchTimer keeps pointers into these pools
+    for (int kk = 1; kk < kKernelKinds; ++kk) h->events[kk].reserve(1024);
     if (rc == 0) rc = h->d_status.reserve(256);
     if (rc == 0 && cudaMemset(h->d_status.p, 0, 256) != cudaSuccess) rc = cuda_fail(cudaGetLastError(), "memset status");
     if (rc != 0) {
@@ -502,6 +623,11 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         if (v != 0 && v != 1) { set_error("binary_codes must be 0 or 1"); return CPHNSW_B200_E_INVALID; }
         if (h->n && int(v) != h->binary_codes) { set_error("binary_codes cannot change once vectors have been added"); return CPHNSW_B200_E_STATE; }
         if (v == 0 && h->residual_bits) { set_error("binary_codes cannot be switched off while residual_bits is set"); return CPHNSW_B200_E_INVALID; }
+        // a full component holds (index << 1) | sign: the bound create checks for the K-byte codes
+        if (v == 0 && ((h->comp_bytes == 1 && h->P > 128) || (h->comp_bytes == 2 && h->P > 32768))) {
+            set_error("binary_codes cannot be switched off: padded dim %llu does not fit a %u-byte component", (unsigned long long)h->P, h->comp_bytes);
+            return CPHNSW_B200_E_INVALID;
+        }
         h->binary_codes = int(v);
         return 0;
     }
@@ -521,6 +647,19 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
             return CPHNSW_B200_E_INVALID;
         }
         h->residual_bits = uint32_t(v);
+        return 0;
+    }
+    if (s == "first_wait_polls") {
+        if (v < 0 || v > 4194304.0) { set_error("first_wait_polls must be in 0..2^22"); return CPHNSW_B200_E_INVALID; }
+        h->first_wait_polls = uint32_t(v);
+        return 0;
+    }
+    if (s == "rank_prune") { h->rank_prune = v != 0.0; return 0; }
+    if (s == "rank_pruning_alpha") {
+        // bounds of CPHNSWParams::finalize (include/cphnsw/core/types.hpp:459-466)
+        if (!(v >= 1.0)) { set_error("CPHNSWParams: rank_pruning_alpha must be >= 1.0"); return CPHNSW_B200_E_INVALID; }
+        if (v > 3.0) { set_error("CPHNSWParams: rank_pruning_alpha must be <= 3.0"); return CPHNSW_B200_E_INVALID; }
+        h->rank_pruning_alpha = float(v);
         return 0;
     }
     if (s == "build_seed") {
@@ -545,6 +684,7 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
     }
     if (h->n) {
         CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
         return set_entry_ids(h);
     }
     return 0;
@@ -559,6 +699,9 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "knn_kernel") *v = h->knn_kernel;
     else if (s == "search_kernel") *v = h->search_kernel;
     else if (s == "build_seed") *v = h->build_seed;
+    else if (s == "first_wait_polls") *v = h->first_wait_polls;
+    else if (s == "rank_prune") *v = h->rank_prune;
+    else if (s == "rank_pruning_alpha") *v = h->rank_pruning_alpha;
     else if (s == "binary_codes") *v = h->binary_codes;
     else if (s == "residual_bits") *v = h->residual_bits;
     else if (s == "residual_shift") *v = h->residual_shift;
@@ -576,7 +719,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
 uint64_t cphnsw_b200_dim(const cphnsw_b200_index* h) { return h ? h->dim : 0; }
 uint64_t cphnsw_b200_padded_dim(const cphnsw_b200_index* h) { return h ? h->P : 0; }
 uint64_t cphnsw_b200_size(const cphnsw_b200_index* h) { return h ? h->n : 0; }
-uint64_t cphnsw_b200_launch_count(const cphnsw_b200_index* h) { return h ? h->launches : 0; }
+uint64_t cphnsw_b200_launch_count(const cphnsw_b200_index* h) { return h ? h->launches.load() : uint64_t(0); }
 
 int cphnsw_b200_get_sign_tables(const cphnsw_b200_index* h, int8_t* out) {
     if (!h || !out) { set_error("get_sign_tables: null argument"); return CPHNSW_B200_E_INVALID; }
@@ -589,12 +732,14 @@ int cphnsw_b200_set_sign_tables(cphnsw_b200_index* h, const int8_t* signs) {
     for (size_t i = 0; i < h->signs.size(); ++i)
         if (signs[i] != 1 && signs[i] != -1) { set_error("sign tables must hold +1/-1 only"); return CPHNSW_B200_E_INVALID; }
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     std::memcpy(h->signs.data(), signs, h->signs.size());
     return upload_signs(h);
 }
 
 int cphnsw_b200_check_device_status(cphnsw_b200_index* h) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     return check_status(h);
 }
 
@@ -602,6 +747,7 @@ int cphnsw_b200_check_device_status(cphnsw_b200_index* h) {
 int cphnsw_b200_encode_dev(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_codes, float* d_rotated,
                            float* d_magnitudes, void* stream) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (n && (!d_x || !d_codes)) { set_error("encode: null pointer"); return CPHNSW_B200_E_INVALID; }
     return launch_encode(h, d_x, n, d_codes, d_rotated, d_magnitudes, (cudaStream_t)stream);
 }
@@ -609,6 +755,7 @@ int cphnsw_b200_encode_dev(cphnsw_b200_index* h, const float* d_x, uint64_t n, v
 int cphnsw_b200_code_distance_dev(cphnsw_b200_index* h, const void* d_a, uint64_t na, const void* d_b, uint64_t nb,
                                   uint16_t* d_out, void* stream) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (na && nb && (!d_a || !d_b || !d_out)) { set_error("code_distance: null pointer"); return CPHNSW_B200_E_INVALID; }
     return launch_code_distance(h, d_a, na, d_b, nb, d_out, (cudaStream_t)stream);
 }
@@ -616,6 +763,7 @@ int cphnsw_b200_code_distance_dev(cphnsw_b200_index* h, const void* d_a, uint64_
 int cphnsw_b200_knn_graph_dev(cphnsw_b200_index* h, const void* d_codes, uint64_t n, uint32_t k, uint64_t row_begin,
                               uint64_t row_end, uint32_t* d_nbrs, uint16_t* d_dist, void* stream) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (row_end > row_begin && (!d_codes || !d_nbrs)) { set_error("knn_graph: null pointer"); return CPHNSW_B200_E_INVALID; }
     return launch_knn_graph(h, d_codes, n, k, row_begin, row_end, d_nbrs, d_dist, (cudaStream_t)stream);
 }
@@ -624,6 +772,7 @@ int cphnsw_b200_select_neighbors_dev(cphnsw_b200_index* h, const void* d_codes, 
                                      uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
                                      uint32_t* d_adj, void* stream) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (row_end > row_begin && (!d_codes || !d_cand || !d_adj)) { set_error("select_neighbors: null pointer"); return CPHNSW_B200_E_INVALID; }
     if (row_end > n) { set_error("select_neighbors: row range exceeds n"); return CPHNSW_B200_E_INVALID; }
     return launch_select_neighbors(h, d_codes, n, d_cand, k, row_begin, row_end, M, keep_pruned, d_adj,
@@ -633,6 +782,7 @@ int cphnsw_b200_select_neighbors_dev(cphnsw_b200_index* h, const void* d_codes, 
 int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const void* d_codes, const uint32_t* d_adj,
                             uint64_t n, void* stream) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (n == 0 || !d_vectors || !d_codes || !d_adj) { set_error("install: null pointer or n == 0"); return CPHNSW_B200_E_INVALID; }
     if (n >= 0x80000000ull) { set_error("install: n must be < 2^31 (the top bit of a node id is used by the search)"); return CPHNSW_B200_E_INVALID; }
     cudaStream_t st = (cudaStream_t)stream;
@@ -644,20 +794,55 @@ int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const 
     CPB_CUDA(cudaMemcpyAsync(h->d_adj.p, d_adj, n * h->M * 4, cudaMemcpyDeviceToDevice, st));
     CPB_CUDA(cudaStreamSynchronize(st));
     h->n = n;
-    h->h_vectors.clear();  // a later add_batch_parallel cannot extend an index installed from device buffers
-    h->d_visited.release();
+    drop_search_scratch(h);
     return set_entry_ids(h);
+}
+
+int cphnsw_b200_install(cphnsw_b200_index* h, const float* vectors, const void* codes, const uint32_t* adj, uint64_t n) {
+    CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
+    if (n == 0 || !vectors || !codes || !adj) { set_error("install: null pointer or n == 0"); return CPHNSW_B200_E_INVALID; }
+    if (n >= 0x80000000ull) { set_error("install: n must be < 2^31 (the top bit of a node id is used by the search)"); return CPHNSW_B200_E_INVALID; }
+    const size_t rb = code_row_bytes(h);
+    CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
+    CPB_TRY(h->d_codes.reserve(n * rb + 16));
+    CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
+    CPB_CUDA(cudaMemcpy(h->d_vectors.p, vectors, n * h->dim * 4, cudaMemcpyHostToDevice));
+    CPB_CUDA(cudaMemcpy(h->d_codes.p, codes, n * rb, cudaMemcpyHostToDevice));
+    CPB_CUDA(cudaMemcpy(h->d_adj.p, adj, n * h->M * 4, cudaMemcpyHostToDevice));
+    h->n = n;
+    drop_search_scratch(h);
+    return set_entry_ids(h);
+}
+
+int cphnsw_b200_search_codes_batch(cphnsw_b200_index* h, const void* qcodes, uint64_t nq, uint32_t k, uint32_t ef,
+                                   uint32_t* ids_out, float* dists_out, uint32_t* stats_out) {
+    CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
+    return do_search(h, nullptr, false, nq, k, ef, 0, ids_out, dists_out, stats_out, false, nullptr, 0, false, qcodes);
+}
+
+int cphnsw_b200_get_code(const cphnsw_b200_index* h, uint32_t id, void* code_out) {
+    CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
+    if (!code_out) { set_error("get_code: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (id >= h->n) { set_error("get_code: node %u does not exist (size %llu)", id, (unsigned long long)h->n); return CPHNSW_B200_E_INVALID; }
+    const size_t rb = code_row_bytes(h);
+    CPB_CUDA(cudaMemcpy(code_out, h->d_codes.as<unsigned char>() + size_t(id) * rb, rb, cudaMemcpyDeviceToHost));
+    return 0;
 }
 
 int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, uint32_t k, uint32_t ef,
                            uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats, void* stream) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     return do_search(h, d_q, true, nq, k, ef, rerank_k, d_ids, d_dists, d_stats, true, (cudaStream_t)stream);
 }
 
 int cphnsw_b200_brute_force_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t* ids_out,
                                          float* dists_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     return do_search(h, q, false, nq, k, k, 0, ids_out, dists_out, nullptr, false, 0, 1);
 }
 
@@ -673,6 +858,7 @@ static const float* exact_vectors(cphnsw_b200_index* h, uint64_t* n) {
 
 int cphnsw_b200_set_exact_base(cphnsw_b200_index* h, const float* base, uint64_t n) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (n == 0) {
         h->d_exact_base.release();
         h->n_exact = 0;
@@ -690,6 +876,7 @@ int cphnsw_b200_set_exact_base(cphnsw_b200_index* h, const float* base, uint64_t
 int cphnsw_b200_exact_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t* ids_out,
                                    float* dists_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (nq == 0) return 0;
     if (!q || !ids_out || !dists_out) { set_error("exact_search: null pointer"); return CPHNSW_B200_E_INVALID; }
     uint64_t n = 0;
@@ -708,6 +895,7 @@ int cphnsw_b200_exact_search_batch(cphnsw_b200_index* h, const float* q, uint64_
 int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint64_t n, const float* d_q, uint64_t nq,
                                  uint32_t k, uint32_t* d_ids, float* d_dists, void* stream) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (nq == 0) return 0;
     if ((n && !d_base) || !d_q || !d_ids || !d_dists) { set_error("exact_search: null pointer"); return CPHNSW_B200_E_INVALID; }
     if (n >= kInvalidNode) { set_error("exact_search: at most 2^32 - 2 vectors"); return CPHNSW_B200_E_INVALID; }
@@ -717,6 +905,7 @@ int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint
 int cphnsw_b200_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, const uint32_t* cand, uint32_t num_cand,
                              uint32_t k, uint32_t* ids_out, float* dists_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (nq == 0) return 0;
     if (!q || (num_cand && !cand) || !ids_out || !dists_out) { set_error("rerank: null pointer"); return CPHNSW_B200_E_INVALID; }
     uint64_t n = 0;
@@ -737,6 +926,7 @@ int cphnsw_b200_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, 
 
 int cphnsw_b200_verify_connectivity(cphnsw_b200_index* h, uint64_t* reachable_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (!reachable_out) { set_error("verify_connectivity: null pointer"); return CPHNSW_B200_E_INVALID; }
     *reachable_out = 0;
     if (h->n == 0) return 0;
@@ -746,6 +936,7 @@ int cphnsw_b200_verify_connectivity(cphnsw_b200_index* h, uint64_t* reachable_ou
 int cphnsw_b200_calibrate(cphnsw_b200_index* h, uint64_t num_samples, uint64_t seed, double* alpha_out, double* beta_out,
                           double* r_squared_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     CPB_TRY(do_calibrate(h, num_samples, seed));
     if (alpha_out) *alpha_out = h->calib_alpha;
     if (beta_out) *beta_out = h->calib_beta;
@@ -766,12 +957,14 @@ int cphnsw_b200_get_calibration(const cphnsw_b200_index* h, double* alpha_out, d
 int cphnsw_b200_search_calibrated_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
                                         uint32_t rerank_k, uint32_t* ids_out, float* dists_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     return do_search(h, q, false, nq, k, ef, rerank_k, ids_out, dists_out, nullptr, false, 0, 0, true);
 }
 
 int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out) {
     if (!h || (!words_out && h->n)) { set_error("get_binary_codes: null argument"); return CPHNSW_B200_E_INVALID; }
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (h->n == 0) return 0;
     cphnsw_b200_index* m = const_cast<cphnsw_b200_index*>(h);  // scratch and launch counter only
     const size_t bytes = h->n * ((h->K + 63) / 64) * 8;
@@ -817,6 +1010,7 @@ int read_device(std::FILE* f, void* d, size_t bytes, std::vector<char>& buf) {
 
 int cphnsw_b200_save(cphnsw_b200_index* h, const char* path) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (!path) { set_error("save: null path"); return CPHNSW_B200_E_INVALID; }
     FileCloser fc{std::fopen(path, "wb")};
     if (!fc.f) { set_error("save: cannot create %s", path); return CPHNSW_B200_E_INVALID; }
@@ -879,13 +1073,11 @@ int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
     h->calib_alpha = hd.calib_alpha, h->calib_beta = hd.calib_beta, h->calib_r2 = hd.calib_r2, h->calib_samples = hd.calib_samples;
     if (hd.n) {
         const uint64_t n = hd.n;
-        h->h_vectors.resize(n * h->dim);
-        if (std::fread(h->h_vectors.data(), 4, n * h->dim, fc.f) != n * h->dim) { set_error("load: file is shorter than its header says"); return CPHNSW_B200_E_INVALID; }
         CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
         CPB_TRY(h->d_codes.reserve(n * code_row_bytes(h) + 16));
         CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
-        CPB_CUDA(cudaMemcpy(h->d_vectors.p, h->h_vectors.data(), n * h->dim * 4, cudaMemcpyHostToDevice));
         std::vector<char> buf(size_t(64) << 20);
+        CPB_TRY(read_device(fc.f, h->d_vectors.p, n * h->dim * 4, buf));
         CPB_TRY(read_device(fc.f, h->d_codes.p, n * code_row_bytes(h), buf));
         CPB_TRY(read_device(fc.f, h->d_adj.p, n * h->M * 4, buf));
         h->n = n;
@@ -904,6 +1096,7 @@ int cphnsw_b200_encode(cphnsw_b200_index* h, const float* x, uint64_t n, void* c
 int cphnsw_b200_encode_queries(cphnsw_b200_index* h, const float* q, uint64_t nq, void* codes_out, float* rotated_out,
                                float* magnitudes_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (nq == 0) return 0;
     if (!q || !codes_out) { set_error("encode: null pointer"); return CPHNSW_B200_E_INVALID; }
     const size_t rb = code_row_bytes(h);
@@ -929,6 +1122,7 @@ int cphnsw_b200_encode_queries(cphnsw_b200_index* h, const float* q, uint64_t nq
 int cphnsw_b200_code_distance(cphnsw_b200_index* h, const void* a, uint64_t na, const void* b, uint64_t nb,
                               uint16_t* out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (na == 0 || nb == 0) return 0;
     if (!a || !b || !out) { set_error("code_distance: null pointer"); return CPHNSW_B200_E_INVALID; }
     const size_t rb = code_row_bytes(h);
@@ -945,6 +1139,7 @@ int cphnsw_b200_code_distance(cphnsw_b200_index* h, const void* a, uint64_t na, 
 int cphnsw_b200_knn_graph(cphnsw_b200_index* h, const void* codes, uint64_t n, uint32_t k, uint64_t row_begin,
                           uint64_t row_end, uint32_t* nbrs_out, uint16_t* dist_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (row_end <= row_begin) return 0;
     if (!codes || !nbrs_out) { set_error("knn_graph: null pointer"); return CPHNSW_B200_E_INVALID; }
     const size_t rb = code_row_bytes(h);
@@ -963,6 +1158,7 @@ int cphnsw_b200_knn_graph(cphnsw_b200_index* h, const void* codes, uint64_t n, u
 int cphnsw_b200_select_neighbors(cphnsw_b200_index* h, const void* codes, uint64_t n, const uint32_t* cand, uint32_t k,
                                  uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned, uint32_t* adj_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
     if (row_end <= row_begin) return 0;
     if (!codes || !cand || !adj_out) { set_error("select_neighbors: null pointer"); return CPHNSW_B200_E_INVALID; }
     if (row_end > n) { set_error("select_neighbors: row range exceeds n"); return CPHNSW_B200_E_INVALID; }
@@ -979,63 +1175,89 @@ int cphnsw_b200_select_neighbors(cphnsw_b200_index* h, const void* codes, uint64
     return 0;
 }
 
-int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_t n) {
+int cphnsw_b200_rank_prune(cphnsw_b200_index* h, const uint32_t* cand, uint64_t n, uint32_t k, uint32_t M, float alpha,
+                           uint32_t* adj_out) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
+    if (n == 0) return 0;
+    if (!cand || !adj_out) { set_error("rank_prune: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (!(alpha >= 1.0f) || alpha > 3.0f) { set_error("rank_prune: alpha must be in 1.0..3.0"); return CPHNSW_B200_E_INVALID; }
+    CPB_TRY(h->s_in2.reserve(n * k * 4 + 16));
+    CPB_TRY(h->s_out.reserve(n * M * 4 + 16));
+    CPB_CUDA(cudaMemcpy(h->s_in2.p, cand, n * k * 4, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_rank_prune(h, n, h->s_in2.as<uint32_t>(), k, M, alpha, h->s_out.as<uint32_t>(), 0));
+    CPB_CUDA(cudaMemcpy(adj_out, h->s_out.p, n * M * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int cphnsw_b200_rank_reorder_dev(cphnsw_b200_index* h, const uint32_t* d_cand, uint64_t n, uint32_t k, uint64_t row_begin,
+                                 uint64_t row_end, uint32_t M, float alpha, uint32_t* d_kept, void* stream) {
+    CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
+    if (row_end > row_begin && (!d_cand || !d_kept)) { set_error("rank_reorder: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (!(alpha >= 1.0f) || alpha > 3.0f) { set_error("rank_reorder: alpha must be in 1.0..3.0"); return CPHNSW_B200_E_INVALID; }
+    return launch_rank_reorder(h, n, d_cand, k, row_begin, row_end, M, alpha, d_kept, (cudaStream_t)stream);
+}
+
+int cphnsw_b200_rank_merge_dev(cphnsw_b200_index* h, const uint32_t* d_kept, uint64_t n, uint32_t M, uint64_t row_begin,
+                               uint64_t row_end, uint32_t* d_adj, void* stream) {
+    CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
+    if (row_end > row_begin && (!d_kept || !d_adj)) { set_error("rank_merge: null pointer"); return CPHNSW_B200_E_INVALID; }
+    return launch_rank_merge(h, n, d_kept, M, row_begin, row_end, d_adj, (cudaStream_t)stream);
+}
+
+static int add_batch_impl(cphnsw_b200_index* h, const float* x, uint64_t n);
+
+// callers hold the handle's lock exclusively
+static int add_batch_parallel_impl(cphnsw_b200_index* h, const float* x, uint64_t n) {
     if (n == 0) return 0;
     if (!x) { set_error("add_batch_parallel: null pointer"); return CPHNSW_B200_E_INVALID; }
-    if (h->n && h->h_vectors.size() != h->n * h->dim) {
-        set_error("add_batch_parallel: the index was installed from device buffers and cannot be extended");
-        return CPHNSW_B200_E_STATE;
-    }
     if (h->n + n >= 0x80000000ull) { set_error("add_batch_parallel: at most 2^31-1 nodes"); return CPHNSW_B200_E_INVALID; }
     if (h->build_seed && h->n == 0 && n > h->build_seed) {
         // the exact kNN graph of the first build_seed vectors, the others inserted into it
         const uint32_t seed_n = h->build_seed;
         h->build_seed = 0;
-        int rc = cphnsw_b200_add_batch_parallel(h, x, seed_n);
+        int rc = add_batch_parallel_impl(h, x, seed_n);
         h->build_seed = seed_n;
         CPB_TRY(rc);
-        return cphnsw_b200_add_batch(h, x + uint64_t(seed_n) * h->dim, n - seed_n);
+        return add_batch_impl(h, x + uint64_t(seed_n) * h->dim, n - seed_n);
     }
-    h->h_vectors.insert(h->h_vectors.end(), x, x + n * h->dim);
-    const uint64_t total = h->n + n;
-    CPB_TRY(h->d_vectors.reserve(total * h->dim * 4));
-    CPB_TRY(h->d_codes.reserve(total * code_row_bytes(h) + 16));
-    CPB_CUDA(cudaMemcpy(h->d_vectors.p, h->h_vectors.data(), total * h->dim * 4, cudaMemcpyHostToDevice));
-    CPB_TRY(launch_encode(h, h->d_vectors.as<float>(), total, h->d_codes.p, nullptr, nullptr, 0));
+    // the new adjacency is built beside the old one and the handle (n, adjacency) changes only once
+    // everything has succeeded: a failure on the way leaves the index as it was
+    const uint64_t old_n = h->n, total = h->n + n;
+    const size_t rb = code_row_bytes(h);
+    CPB_TRY(grow_keep(h->d_vectors, old_n * h->dim * 4, total * h->dim * 4));
+    CPB_TRY(grow_keep(h->d_codes, old_n * rb, total * rb + 16));
+    float* d_new = h->d_vectors.as<float>() + old_n * h->dim;
+    CPB_CUDA(cudaMemcpy(d_new, x, n * h->dim * 4, cudaMemcpyHostToDevice));
+    CPB_TRY(launch_encode(h, d_new, n, h->d_codes.as<unsigned char>() + old_n * rb, nullptr, nullptr, 0));
+    DevBuf adj;
+    CPB_TRY(build_graph(h, total, adj, 0));
+    h->d_adj.swap(adj);
     h->n = total;
-    h->d_visited.release();  // sized by n
-    return build_graph(h, 0);
+    drop_search_scratch(h);  // visited arrays are sized by n
+    return set_entry_ids(h);
 }
 
-namespace {
-// grows a device buffer to new_bytes keeping its first keep_bytes
-int grow_keep(cpb::DevBuf& b, size_t keep_bytes, size_t new_bytes) {
-    if (b.p && new_bytes <= b.bytes) return 0;
-    void* p = nullptr;
-    const size_t cap = new_bytes + new_bytes / 2;
-    CPB_CUDA(cudaMalloc(&p, cap));
-    if (b.p && keep_bytes) {
-        cudaError_t e = cudaMemcpy(p, b.p, keep_bytes, cudaMemcpyDeviceToDevice);
-        if (e != cudaSuccess) {
-            cudaFree(p);
-            CPB_CUDA(e);
-        }
-    }
-    b.release();
-    b.p = p;
-    b.bytes = cap;
-    return 0;
+
+int cphnsw_b200_add_batch_parallel(cphnsw_b200_index* h, const float* x, uint64_t n) {
+    CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
+    return add_batch_parallel_impl(h, x, n);
 }
-}  // namespace
 
 int cphnsw_b200_add_batch(cphnsw_b200_index* h, const float* x, uint64_t n) {
     CPB_TRY(bind(h));
+    std::unique_lock<std::shared_mutex> guard(h->rw);
+    return add_batch_impl(h, x, n);
+}
+
+static int add_batch_impl(cphnsw_b200_index* h, const float* x, uint64_t n) {
     if (n == 0) return 0;
     if (!x) { set_error("add_batch: null pointer"); return CPHNSW_B200_E_INVALID; }
-    if (h->n == 0) return cphnsw_b200_add_batch_parallel(h, x, n);  // nothing to insert into: bulk build
+    if (h->n == 0) return add_batch_parallel_impl(h, x, n);  // nothing to insert into: bulk build
     if (h->n + n >= 0x80000000ull) { set_error("add_batch: at most 2^31-1 nodes"); return CPHNSW_B200_E_INVALID; }
-    const bool track_host = h->h_vectors.size() == h->n * h->dim;
     const size_t rb = code_row_bytes(h);
     cudaStream_t st = 0;
     for (uint64_t done = 0; done < n;) {
@@ -1052,16 +1274,19 @@ int cphnsw_b200_add_batch(cphnsw_b200_index* h, const float* x, uint64_t n) {
         const uint32_t k_c = uint32_t(n_old < 64 ? n_old : 64);
         uint32_t beam = h->ef_construction > k_c ? h->ef_construction : k_c;
         if (beam > 1024) beam = 1024;
-        CPB_TRY(h->d_out_ids.reserve(m * k_c * 4));
-        CPB_TRY(h->d_out_dist.reserve(m * k_c * 4));
-        CPB_TRY(launch_search(h, nullptr, nullptr, m, k_c, beam, 0, h->d_out_ids.as<uint32_t>(), h->d_out_dist.as<float>(),
+        CtxLease lease;
+        CPB_TRY(lease.acquire(h, true));
+        SearchCtx& cx = *lease.cx;
+        CPB_TRY(lease.begin(st));
+        CPB_TRY(cx.d_out_ids.reserve(m * k_c * 4));
+        CPB_TRY(cx.d_out_dist.reserve(m * k_c * 4));
+        CPB_TRY(launch_search(h, cx, nullptr, nullptr, m, k_c, beam, 0, cx.d_out_ids.as<uint32_t>(), cx.d_out_dist.as<float>(),
                               nullptr, st, d_new_codes));
-        CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n_old + m, h->d_out_ids.as<uint32_t>(), k_c, n_old, n_old + m, h->M,
+        CPB_TRY(launch_select_neighbors(h, h->d_codes.p, n_old + m, cx.d_out_ids.as<uint32_t>(), k_c, n_old, n_old + m, h->M,
                                         h->keep_pruned, h->d_adj.as<uint32_t>() + n_old * h->M, st));
         CPB_TRY(launch_reverse_edges(h, h->d_codes.p, n_old, m, h->d_adj.as<uint32_t>(), h->M, h->keep_pruned, st));
         CPB_CUDA(cudaStreamSynchronize(st));
         CPB_TRY(check_status(h));
-        if (track_host) h->h_vectors.insert(h->h_vectors.end(), x + done * h->dim, x + (done + m) * h->dim);
         h->n = n_old + m;
         CPB_TRY(set_entry_ids(h));
         done += m;
@@ -1071,6 +1296,7 @@ int cphnsw_b200_add_batch(cphnsw_b200_index* h, const float* x, uint64_t n) {
 
 int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     if (!codes_out) { set_error("get_codes: null pointer"); return CPHNSW_B200_E_INVALID; }
     if (h->n) CPB_CUDA(cudaMemcpy(codes_out, h->d_codes.p, h->n * code_row_bytes(h), cudaMemcpyDeviceToHost));
     return 0;
@@ -1078,6 +1304,7 @@ int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out) {
 
 int cphnsw_b200_get_adjacency(const cphnsw_b200_index* h, uint32_t* adj_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     if (!adj_out) { set_error("get_adjacency: null pointer"); return CPHNSW_B200_E_INVALID; }
     if (h->n) CPB_CUDA(cudaMemcpy(adj_out, h->d_adj.p, h->n * h->M * 4, cudaMemcpyDeviceToHost));
     return 0;
@@ -1085,6 +1312,7 @@ int cphnsw_b200_get_adjacency(const cphnsw_b200_index* h, uint32_t* adj_out) {
 
 int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uint64_t* count) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     if (count) *count = h->n_entry;
     if (ids_out && h->n_entry) CPB_CUDA(cudaMemcpy(ids_out, h->d_entry.p, size_t(h->n_entry) * 4, cudaMemcpyDeviceToHost));
     return 0;
@@ -1093,17 +1321,20 @@ int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uin
 int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
                              uint32_t* ids_out, float* dists_out, uint32_t* stats_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     return do_search(h, q, false, nq, k, ef, 0, ids_out, dists_out, stats_out, false, 0);
 }
 
 int cphnsw_b200_search_multiprobe_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
                                         uint32_t num_probes, uint32_t* ids_out, float* dists_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     return do_multiprobe(h, q, nq, k, ef, num_probes, ids_out, dists_out, nullptr, true);
 }
 
 int cphnsw_b200_probe_codes(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t num_probes, void* codes_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     if (nq && !codes_out) { set_error("probe_codes: null output pointer"); return CPHNSW_B200_E_INVALID; }
     return do_multiprobe(h, q, nq, 1, 1, num_probes, nullptr, nullptr, codes_out, false);
 }
@@ -1111,6 +1342,7 @@ int cphnsw_b200_probe_codes(cphnsw_b200_index* h, const float* q, uint64_t nq, u
 int cphnsw_b200_search_and_rerank_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
                                         uint32_t rerank_k, uint32_t* ids_out, float* dists_out, uint32_t* stats_out) {
     CPB_TRY(bind(h));
+    std::shared_lock<std::shared_mutex> guard(h->rw);
     if (rerank_k == 0) { set_error("search_and_rerank: rerank_k must be > 0"); return CPHNSW_B200_E_INVALID; }
     return do_search(h, q, false, nq, k, ef, rerank_k, ids_out, dists_out, stats_out, false, 0);
 }

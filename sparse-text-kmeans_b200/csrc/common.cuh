@@ -4,7 +4,12 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <condition_variable>
 #include <cstdint>
+#include <memory>
+#include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <vector>
 
@@ -62,8 +67,37 @@ struct DevBuf {
         bytes = n;
         return 0;
     }
+    void swap(DevBuf& o) {
+        void* tp = p;
+        size_t tb = bytes;
+        p = o.p, bytes = o.bytes;
+        o.p = tp, o.bytes = tb;
+    }
     template <class T>
     T* as() const { return reinterpret_cast<T*>(p); }
+};
+
+// Everything one search call writes besides its outputs: a stream, the staging and result buffers, the
+// work counter and the visited slots of its launch.  A handle keeps a pool of these so that search calls from
+// several host threads run side by side (the reference's callers search from OpenMP loops,
+// evaluation/eval_sift.cpp:380-387).  `wide` contexts own visited slots for a launch that fills the GPU,
+// narrow ones for launches of up to kNarrowQueries queries, one block per query.
+constexpr uint32_t kNarrowQueries = 32;
+struct SearchCtx {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t done = nullptr;  // recorded behind the last work that used this scratch on a caller's stream
+    bool pending = false;        // `done` has to be waited for before the scratch is reused
+    bool busy = false;
+    bool wide = false;
+    DevBuf d_visited, d_epochs, d_counter;
+    uint64_t vis_stride = 0;
+    size_t vis_slots = 0;
+    DevBuf d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
+    DevBuf d_probe_codes, d_probe_ids, d_probe_dist;  // search_multiprobe
+    ~SearchCtx() {
+        if (done) cudaEventDestroy(done);
+        if (stream) cudaStreamDestroy(stream);
+    }
 };
 
 }  // namespace cpb
@@ -86,6 +120,11 @@ struct cphnsw_b200_index {
     uint32_t residual_bits = 0, residual_shift = 0;
     uint32_t build_seed = 0;  // 0: add_batch_parallel builds the exact kNN graph; else only of this many nodes, the rest inserted
     int sm_count = 0;
+    // polls the kNN kernels grant their FIRST tile wait ("first_wait_polls"; every other wait keeps the full
+    // limit).  0 makes that wait give up at once: the way a test reaches the lost-wait path.
+    uint32_t first_wait_polls = 1u << 22;
+    int rank_prune = 0;               // bulk build prunes by detourable-route count instead of select_neighbors
+    float rank_pruning_alpha = 1.1f;  // CPHNSWParams::rank_pruning_alpha (include/cphnsw/core/types.hpp:399-400)
 
     std::vector<int8_t> signs;  // host [K][3][P]
     cpb::DevBuf d_signs;        // float [K][3][P], +-1 with the FHT convention folded into layers 1,2
@@ -96,27 +135,32 @@ struct cphnsw_b200_index {
 
     // index contents
     uint64_t n = 0;
-    std::vector<float> h_vectors;  // host copy of everything added (rebuilds append to it)
     cpb::DevBuf d_vectors, d_codes, d_adj, d_entry, d_entry_codes;
     cpb::DevBuf d_exact_base;  // vectors given to set_exact_base (exact_search / rerank run over them instead of d_vectors)
     uint64_t n_exact = 0;
     uint32_t n_entry = 0;
-    uint64_t vis_stride = 0;  // bytes per warp slot of d_visited
     int adj_rows_distinct = 0;  // no adjacency row lists a node twice (scan_adjacency_rows)
     // calibrate(): true distance ~ alpha * CP score + beta (identity until calibrate is called)
     double calib_alpha = 1.0, calib_beta = 0.0, calib_r2 = 0.0;
     uint64_t calib_samples = 0;
 
-    // search scratch
-    cpb::DevBuf d_visited, d_explist, d_qtables, d_qcodes, d_q, d_out_ids, d_out_dist, d_stats;
-    cpb::DevBuf d_probe_codes, d_probe_ids, d_probe_dist;  // search_multiprobe scratch
+    // Locking: search* calls hold `rw` shared and work in a SearchCtx of their own; every call that changes the
+    // index or uses the stage scratch below holds it exclusively.
+    mutable std::shared_mutex rw;
+    std::mutex ctx_mu;
+    std::condition_variable ctx_cv;
+    std::vector<std::unique_ptr<cpb::SearchCtx>> ctxs;
+    // scratch of calibrate / encode_queries (rotated vectors)
+    cpb::DevBuf d_qtables, d_qcodes, d_q;
     // stage scratch for the host-pointer entry points
     cpb::DevBuf s_in, s_in2, s_out, s_out2, s_pad, s_pad2, s_sliced;
+    cpb::DevBuf s_rank, s_kept;  // rank-based pruning: reverse lists, kept rows
 
-    uint64_t launches = 0;
+    std::atomic<uint64_t> launches{0};
 
     // optional kernel timing ("profile" parameter): CUDA event pairs recorded around launches
     int profile = 0;
+    std::mutex ev_mu;
     std::vector<cpb::EventPair> events[cpb::kKernelKinds];
     size_t events_used[cpb::kKernelKinds] = {0, 0, 0, 0, 0};
     ~cphnsw_b200_index();
@@ -141,10 +185,18 @@ int launch_knn_graph_sliced(cphnsw_b200_index* h, const void* d_codes, uint64_t 
 int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t n, const uint32_t* d_cand,
                             uint32_t k, uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
                             uint32_t* d_adj, cudaStream_t st, const uint32_t* d_row_ids = nullptr);
+// rank-based pruning of kNN lists (rank_prune.cu): d_cand uint32[n][k] for ALL n nodes; reorder writes the M kept
+// ids of rows [row_begin, row_end); merge needs the kept rows of all n nodes and writes the final rows of the range
+int launch_rank_reorder(cphnsw_b200_index* h, uint64_t n, const uint32_t* d_cand, uint32_t k, uint64_t row_begin,
+                        uint64_t row_end, uint32_t M, float alpha, uint32_t* d_kept, cudaStream_t st);
+int launch_rank_merge(cphnsw_b200_index* h, uint64_t n, const uint32_t* d_kept, uint32_t M, uint64_t row_begin,
+                      uint64_t row_end, uint32_t* d_adj, cudaStream_t st);
+int launch_rank_prune(cphnsw_b200_index* h, uint64_t n, const uint32_t* d_cand, uint32_t k, uint32_t M, float alpha,
+                      uint32_t* d_adj, cudaStream_t st);
 // incremental insertion: old nodes chosen by the new rows [n_old, n_old + m) of d_adj re-select their rows
 int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_old, uint64_t m, uint32_t* d_adj,
                          uint32_t M, int keep_pruned, cudaStream_t st);
-int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
+int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
                   cudaStream_t st, const void* d_qcodes = nullptr, int scan_only = 0);
 int gather_rows(cphnsw_b200_index* h, const void* src, size_t row_bytes, const uint32_t* d_ids, uint32_t n_ids, void* dst,
@@ -165,8 +217,10 @@ int launch_probe_codes(cphnsw_b200_index* h, const float* d_rotated, uint64_t nq
                        cudaStream_t st);
 int launch_merge_probes(cphnsw_b200_index* h, const uint32_t* d_ids, const float* d_dist, uint64_t nq, uint32_t T,
                         uint32_t k, uint32_t* d_out_ids, float* d_out_dist, cudaStream_t st);
-// scratch the search kernel needs for an index of n nodes (visited bitsets, expansion lists)
-int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam);
+// visited slots and epoch counters of a context for an index of n nodes
+int prepare_search_scratch(cphnsw_b200_index* h, SearchCtx& cx, cudaStream_t st);
+// after n changed: every context's visited array is dropped (sized by n)
+void drop_search_scratch(cphnsw_b200_index* h);
 // looks for adjacency rows that list a node twice and sets h->adj_rows_distinct (after d_adj changes)
 int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st);
 // copies the codes of the entry ids into one contiguous buffer (after d_entry / d_codes change)

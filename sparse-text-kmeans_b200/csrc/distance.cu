@@ -142,7 +142,7 @@ template <int WC, bool U16, int SLOTS, int Q, bool WEIGHTED>
 __global__ void __launch_bounds__(kKnnThreads)
 knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uint64_t row_begin,
                  uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
-                 uint32_t* __restrict__ status, CodeWeights cwt) {
+                 uint32_t* __restrict__ status, uint32_t first_wait_polls, CodeWeights cwt) {
     constexpr int CH = WC / 4;  // 16-byte chunks per code row
     constexpr int CHLOG = CH == 1 ? 0 : (CH == 2 ? 1 : (CH == 4 ? 2 : 3));
     constexpr int kKnnTile = KnnTile<WC>::value;
@@ -206,13 +206,15 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
     }
 
     bool lost = false;
+    uint64_t lost_tile = 0;
     for (uint64_t t = 0; t < tiles; ++t) {
         const int st = int(t & 1);
         const uint32_t parity = uint32_t((t >> 1) & 1);
-        if (!mbar_wait_bounded(&full_bar[st], parity, kWaitLimit)) abort_flag = 1;
+        if (!mbar_wait_bounded(&full_bar[st], parity, t == 0 ? first_wait_polls : kWaitLimit)) abort_flag = 1;
         __syncthreads();
         if (abort_flag) {
             lost = true;
+            lost_tile = t;
             break;
         }
         const uint4* tile = st == 0 ? stage0 : stage1;
@@ -264,8 +266,7 @@ knn_graph_kernel(const uint32_t* __restrict__ codes, uint64_t n, uint32_t k, uin
         // (and its shared memory) goes away
         if (threadIdx.x == 0) {
             atomicExch(status, kStatusWaitTimeout);
-            mbar_wait_bounded(&full_bar[0], 0, kWaitLimit);
-            mbar_wait_bounded(&full_bar[1], 0, kWaitLimit);
+            knn::drain_after_loss(full_bar, lost_tile, tiles);
         }
         return;
     }
@@ -289,7 +290,7 @@ constexpr int kSelMaxK = 64;
 
 template <int WC, bool U16>
 __global__ void __launch_bounds__(kSelWarps * 32)
-select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ cand, uint32_t k,
+select_neighbors_kernel(const uint32_t* __restrict__ codes, uint64_t n, const uint32_t* __restrict__ cand, uint32_t k,
                         uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned,
                         uint32_t* __restrict__ adj, const uint32_t* __restrict__ row_ids, CodeWeights cwt) {
     // row_ids == nullptr: rows [row_begin, row_end), output row i at adj[i - row_begin];
@@ -302,9 +303,12 @@ select_neighbors_kernel(const uint32_t* __restrict__ codes, const uint32_t* __re
     const uint32_t* crow = cand + (slot - row_begin) * uint64_t(k);
     uint32_t pm[(WC + FlagGroups<U16>::G - 1) / FlagGroups<U16>::G];
     primary_masks<WC, U16>(cwt, 0, pm);
+    // candidate ids come from the caller: an id that names no code row counts as "no node"
     uint32_t cid[2];
     cid[0] = lane < int(k) ? crow[lane] : kInvalidNode;
     cid[1] = lane + 32 < int(k) ? crow[lane + 32] : kInvalidNode;
+    if (cid[0] >= n) cid[0] = kInvalidNode;
+    if (cid[1] >= n) cid[1] = kInvalidNode;
     uint32_t qc[WC];
 #pragma unroll
     for (int w = 0; w < WC; w += 4) {
@@ -401,7 +405,7 @@ __global__ void rev_fill_kernel(const uint32_t* __restrict__ new_adj, uint64_t m
 // the incoming list was filled does not matter).
 template <int WC, bool U16>
 __global__ void __launch_bounds__(kSelWarps * 32)
-rev_merge_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict__ adj, int M,
+rev_merge_kernel(const uint32_t* __restrict__ codes, uint64_t n, const uint32_t* __restrict__ adj, int M,
                  const uint32_t* __restrict__ aff, uint32_t n_aff, const uint32_t* __restrict__ cnt,
                  const uint32_t* __restrict__ seg, const uint32_t* __restrict__ inc, uint32_t* __restrict__ cand_out,
                  CodeWeights cwt) {
@@ -424,6 +428,7 @@ rev_merge_kernel(const uint32_t* __restrict__ codes, const uint32_t* __restrict_
         uint32_t w = kInvalidNode;
         if (c < uint32_t(M)) w = adj[uint64_t(v) * M + c];
         else if (c < total) w = inc[seg[v] + (c - M)];
+        if (w >= n) w = kInvalidNode;  // rows installed or loaded from outside may hold anything
         uint32_t dd = kFull;
         if (w != kInvalidNode) {
             uint32_t wc[WC];
@@ -557,7 +562,7 @@ static int launch_knn_w(cphnsw_b200_index* h, const uint32_t* codes, uint64_t n,
     const uint64_t rows = re - rb;
     const uint64_t blocks = (rows + kKnnWarps * Q - 1) / (kKnnWarps * Q);
     LaunchTimer timer(h, kKernelKnn, st);
-    kernel<<<unsigned(blocks), kKnnThreads, smem, st>>>(codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(),
+    kernel<<<unsigned(blocks), kKnnThreads, smem, st>>>(codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), h->first_wait_polls,
                                                        code_weights(h));
     h->launches++;
     CPB_CUDA(cudaGetLastError());
@@ -635,7 +640,7 @@ int launch_select_neighbors(cphnsw_b200_index* h, const void* d_codes, uint64_t 
     LaunchTimer timer(h, kKernelSelect, st);
     const CodeWeights cwt = code_weights(h);
 #define CALL(W, U)                                                                                          \
-    select_neighbors_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_cand, k, row_begin, row_end, M,    \
+    select_neighbors_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, n, d_cand, k, row_begin, row_end, M, \
                                                                    keep_pruned, d_adj, d_row_ids, cwt)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
@@ -684,7 +689,7 @@ int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_o
     CPB_TRY(padded_view(h, d_codes, n_old + m, WC, h->s_pad, st, &pc));
     const unsigned grid = (n_aff + kSelWarps - 1) / kSelWarps;
     const CodeWeights cwt = code_weights(h);
-#define CALL(W, U) rev_merge_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, d_adj, int(M), aff, n_aff, cnt, seg, inc, cand, cwt)
+#define CALL(W, U) rev_merge_kernel<W, U><<<grid, kSelWarps * 32, 0, st>>>(pc, n_old + m, d_adj, int(M), aff, n_aff, cnt, seg, inc, cand, cwt)
     CPB_DISPATCH_WC(WC, u16, CALL);
 #undef CALL
     h->launches++;

@@ -39,6 +39,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// After a wait for tile t was lost: the copies that can still be in flight are those of tiles t and
+// t + 1 (tile u lands in stage u & 1 and completes that barrier's phase of parity (u >> 1) & 1).
+// They get the full poll limit to land before the block and its shared memory go away.
+__device__ __forceinline__ void drain_after_loss(uint64_t* full_bar, uint64_t t, uint64_t tiles) {
+    for (uint64_t u = t; u < t + 2 && u < tiles; ++u)
+        mbar_wait_bounded(&full_bar[u & 1], uint32_t((u >> 1) & 1), kWaitLimit);
+}
 // 1-D bulk asynchronous copy global -> shared; both addresses 16-byte aligned, bytes % 16 == 0.
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile(

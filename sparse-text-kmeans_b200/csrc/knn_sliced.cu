@@ -73,7 +73,7 @@ template <typename CompT, int NB, int NBLK, int SLOTS, int WARPS>  // NB bit pla
 __global__ void __launch_bounds__(WARPS * 32)
 knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__ codes, uint64_t n, uint32_t k,
                   uint64_t row_begin, uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
-                  uint32_t* __restrict__ status) {
+                  uint32_t* __restrict__ status, uint32_t first_wait_polls) {
     constexpr int K = NBLK * 8;
     constexpr int CHUNKS = K * NB / 4;             // 16-byte chunks per group
     constexpr uint32_t TILE_BYTES = CHUNKS * 32 * 16;
@@ -126,13 +126,15 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
     }
 
     bool lost = false;
+    uint64_t lost_tile = 0;
     for (uint64_t t = 0; t < tiles; ++t) {
         const int st = int(t & 1);
         const uint32_t parity = uint32_t((t >> 1) & 1);
-        if (!knn::mbar_wait_bounded(&full_bar[st], parity, knn::kWaitLimit)) abort_flag = 1;
+        if (!knn::mbar_wait_bounded(&full_bar[st], parity, t == 0 ? first_wait_polls : knn::kWaitLimit)) abort_flag = 1;
         __syncthreads();
         if (abort_flag) {
             lost = true;
+            lost_tile = t;
             break;
         }
         const uint4* tile = st == 0 ? stage0 : stage1;
@@ -265,8 +267,7 @@ knn_sliced_kernel(const uint32_t* __restrict__ sliced, const CompT* __restrict__
     if (lost) {
         if (threadIdx.x == 0) {
             atomicExch(status, kStatusWaitTimeout);
-            knn::mbar_wait_bounded(&full_bar[0], 0, knn::kWaitLimit);
-            knn::mbar_wait_bounded(&full_bar[1], 0, knn::kWaitLimit);
+            knn::drain_after_loss(full_bar, lost_tile, tiles);
         }
         return;
     }
@@ -290,7 +291,7 @@ template <int SLOTS>
 __global__ void __launch_bounds__(kSlWarps * 32)
 knn_sliced_binary_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __restrict__ codes, uint64_t n, uint32_t k,
                          uint64_t row_begin, uint64_t row_end, uint32_t* __restrict__ nbrs, uint16_t* __restrict__ dists,
-                         uint32_t* __restrict__ status, int nblk, int nblk_p, int shift) {
+                         uint32_t* __restrict__ status, uint32_t first_wait_polls, int nblk, int nblk_p, int shift) {
     const int K = nblk * 8, CHUNKS = nblk * 2;
     const uint32_t TILE_BYTES = uint32_t(CHUNKS) * 32 * 16;
     extern __shared__ __align__(128) unsigned char sl_smem[];
@@ -333,13 +334,15 @@ knn_sliced_binary_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __r
     }
 
     bool lost = false;
+    uint64_t lost_tile = 0;
     for (uint64_t t = 0; t < tiles; ++t) {
         const int st = int(t & 1);
         const uint32_t parity = uint32_t((t >> 1) & 1);
-        if (!knn::mbar_wait_bounded(&full_bar[st], parity, knn::kWaitLimit)) abort_flag = 1;
+        if (!knn::mbar_wait_bounded(&full_bar[st], parity, t == 0 ? first_wait_polls : knn::kWaitLimit)) abort_flag = 1;
         __syncthreads();
         if (abort_flag) {
             lost = true;
+            lost_tile = t;
             break;
         }
         const uint4* tile = st == 0 ? stage0 : stage1;
@@ -454,8 +457,7 @@ knn_sliced_binary_kernel(const uint32_t* __restrict__ sliced, const uint8_t* __r
     if (lost) {
         if (threadIdx.x == 0) {
             atomicExch(status, kStatusWaitTimeout);
-            knn::mbar_wait_bounded(&full_bar[0], 0, knn::kWaitLimit);
-            knn::mbar_wait_bounded(&full_bar[1], 0, knn::kWaitLimit);
+            knn::drain_after_loss(full_bar, lost_tile, tiles);
         }
         return;
     }
@@ -478,7 +480,7 @@ int launch_sliced_binary_t(cphnsw_b200_index* h, const uint32_t* sliced, const u
     CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     const uint64_t blocks = (re - rb + kSlWarps * kSlQ - 1) / (kSlWarps * kSlQ);
     LaunchTimer timer(h, kKernelKnn, st);
-    kernel<<<unsigned(blocks), kSlWarps * 32, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), nblk,
+    kernel<<<unsigned(blocks), kSlWarps * 32, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), h->first_wait_polls, nblk,
                                                          nblk_p, int(h->residual_bits ? h->residual_shift : 0));
     h->launches++;
     CPB_CUDA(cudaGetLastError());
@@ -495,7 +497,7 @@ int launch_sliced_t(cphnsw_b200_index* h, const uint32_t* sliced, const CompT* c
     const uint64_t rows = re - rb;
     const uint64_t blocks = (rows + WARPS * kSlQ - 1) / (WARPS * kSlQ);
     LaunchTimer timer(h, kKernelKnn, st);
-    kernel<<<unsigned(blocks), WARPS * 32, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>());
+    kernel<<<unsigned(blocks), WARPS * 32, smem, st>>>(sliced, codes, n, k, rb, re, nbrs, dist, h->d_status.as<uint32_t>(), h->first_wait_polls);
     h->launches++;
     CPB_CUDA(cudaGetLastError());
     return 0;

@@ -422,7 +422,7 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
 
 // two-warps-per-query kernel (search_team.cu)
 size_t search_team_extra_smem();
-int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st);
+int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st);
 
 int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
     const int row_bytes = int(h->K * h->comp_bytes);
@@ -466,26 +466,32 @@ int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st) {
     return 0;
 }
 
-int prepare_search_scratch(cphnsw_b200_index* h, uint32_t beam) {
-    (void)beam;
-    const size_t slots = size_t(h->sm_count) * 16;  // the most warps a launch ever uses
+int prepare_search_scratch(cphnsw_b200_index* h, SearchCtx& cx, cudaStream_t st) {
+    // the most slots a launch of this context uses: one per query (narrow) or 16 per SM (wide)
+    const size_t slots = cx.wide ? size_t(h->sm_count) * 16 : size_t(kNarrowQueries);
     size_t stride = (size_t(h->n) + 15) & ~size_t(15);
     // an array laid out for more nodes than the index holds stays valid (an index that grows by
     // incremental insertion gets a quarter of slack so that not every insertion reallocates)
-    if (h->d_visited.p && h->vis_stride >= stride && slots * h->vis_stride <= h->d_visited.bytes) return 0;
-    if (h->d_visited.p) stride = (stride + stride / 4 + 15) & ~size_t(15);
-    const size_t vis_bytes = slots * stride;
-    {
-        CPB_TRY(h->d_visited.reserve(vis_bytes));
-        CPB_CUDA(cudaMemset(h->d_visited.p, 0, h->d_visited.bytes));
-        CPB_TRY(h->d_explist.reserve(slots * 4));  // per-slot epoch counters
-        CPB_CUDA(cudaMemset(h->d_explist.p, 0, h->d_explist.bytes));
-        h->vis_stride = stride;
-    }
+    if (cx.d_visited.p && cx.vis_stride >= stride && slots * cx.vis_stride <= cx.d_visited.bytes) return 0;
+    if (cx.d_visited.p) stride = (stride + stride / 4 + 15) & ~size_t(15);
+    CPB_TRY(cx.d_visited.reserve(slots * stride));
+    CPB_CUDA(cudaMemsetAsync(cx.d_visited.p, 0, cx.d_visited.bytes, st));
+    CPB_TRY(cx.d_epochs.reserve(slots * 4));  // per-slot epoch counters
+    CPB_CUDA(cudaMemsetAsync(cx.d_epochs.p, 0, cx.d_epochs.bytes, st));
+    cx.vis_stride = stride;
+    cx.vis_slots = slots;
     return 0;
 }
 
-int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
+void drop_search_scratch(cphnsw_b200_index* h) {
+    std::lock_guard<std::mutex> lock(h->ctx_mu);
+    for (auto& c : h->ctxs) {
+        c->d_visited.release();
+        c->vis_stride = 0;
+    }
+}
+
+int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const float* d_tables, uint64_t nq, uint32_t k,
                   uint32_t beam, uint32_t rerank_k, uint32_t* d_ids, float* d_dists, uint32_t* d_stats,
                   cudaStream_t st, const void* d_qcodes, int scan_only) {
     const bool sym = d_qcodes != nullptr;  // symmetric code-distance walk (search_multiprobe)
@@ -498,7 +504,11 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
         set_error("search: at most 2^32-1 queries per call");
         return CPHNSW_B200_E_INVALID;
     }
-    CPB_TRY(prepare_search_scratch(h, beam));
+    if (!cx.wide && nq > kNarrowQueries) {
+        set_error("search: internal error (a narrow context was given %llu queries)", (unsigned long long)nq);
+        return CPHNSW_B200_E_STATE;
+    }
+    CPB_TRY(prepare_search_scratch(h, cx, st));
     LaunchCfg c = pick_cfg(h, beam, sym);
     SearchArgs a;
     a.qcodes = d_qcodes;
@@ -525,13 +535,13 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     a.per_warp_smem = uint32_t(c.per_warp);
     a.k = k;
     a.rerank_k = rerank_k;
-    a.visited = h->d_visited.as<uint8_t>();
-    a.vis_stride = h->vis_stride;
-    a.epochs = h->d_explist.as<uint32_t>();
+    a.visited = cx.d_visited.as<uint8_t>();
+    a.vis_stride = cx.vis_stride;
+    a.epochs = cx.d_epochs.as<uint32_t>();
     a.out_ids = d_ids;
     a.out_dist = d_dists;
     a.stats = d_stats;
-    a.next_query = h->d_status.as<uint32_t>() + 1;
+    a.next_query = cx.d_counter.as<uint32_t>();
     a.rows_distinct = h->adj_rows_distinct;
     a.scan_only = scan_only;
     a.resid_kp = h->residual_bits ? int(h->K - h->residual_bits) : 0;
@@ -543,7 +553,10 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
         a.n_seed = k;
     }
     CPB_CUDA(cudaMemsetAsync(a.next_query, 0, 4, st));
-    const unsigned grid = unsigned(h->sm_count);
+    // a narrow launch gives every query a block of its own (one warp or one team), so a handful of
+    // queries spread over as many SMs and need as many visited slots
+    const bool narrow = !cx.wide;
+    const unsigned grid = narrow ? unsigned(nq) : unsigned(h->sm_count);
     const bool u16 = h->comp_bytes == 2;
     LaunchTimer timer(h, kKernelSearch, st);
 
@@ -556,7 +569,7 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
     }
     if (team_ok && h->search_kernel != 1) {
         const size_t per_team = (c.per_warp + search_team_extra_smem() + 15) & ~size_t(15);
-        CPB_TRY(launch_search_team(h, a, per_team, st));
+        CPB_TRY(launch_search_team(h, a, per_team, narrow ? int(nq) : 0, st));
         h->launches++;
         CPB_CUDA(cudaGetLastError());
         return 0;
@@ -567,7 +580,7 @@ int launch_search(cphnsw_b200_index* h, const float* d_q, const float* d_tables,
         cudaFuncAttributes fa;                                                                             \
         CPB_CUDA(cudaFuncGetAttributes(&fa, search_kernel<U, T, S>));                                      \
         int maxw = 65536 / (((fa.numRegs + 7) & ~7) * 32);                                                 \
-        int w = c.warps < maxw ? c.warps : maxw;                                                           \
+        int w = narrow ? 1 : (c.warps < maxw ? c.warps : maxw);                                            \
         size_t smem = c.per_warp * w;                                                                      \
         CPB_CUDA(cudaFuncSetAttribute(search_kernel<U, T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                       int(smem)));                                                         \

@@ -668,10 +668,11 @@ size_t search_team_extra_smem() { return size_t(kSeedCap) * 8 + kRing * 4 + kMai
 // Teams per block: as many as shared memory allows (at most 15, one named barrier each), fewer if
 // the register file does not hold them.
 template <bool U16, bool TSM>
-static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st) {
+static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
     auto kernel = search_team_kernel<U16, TSM>;
     int teams = int((226 * 1024) / per_team);
     if (teams > 15) teams = 15;
+    if (narrow_blocks) teams = 1;  // one query per block
     for (; teams >= 1; --teams) {
         int blocks = 0;
         CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(per_team * teams)));
@@ -682,14 +683,14 @@ static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cu
         set_error("search: no launch configuration fits the two-warp kernel");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
-    kernel<<<unsigned(h->sm_count), teams * 64, per_team * teams, st>>>(a);
+    kernel<<<narrow_blocks ? unsigned(narrow_blocks) : unsigned(h->sm_count), teams * 64, per_team * teams, st>>>(a);
     return 0;
 }
 
-int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, cudaStream_t st) {
+int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
     a.per_warp_smem = uint32_t(per_team);
-    if (a.table_in_smem) return h->comp_bytes == 2 ? launch_team_t<true, true>(h, a, per_team, st) : launch_team_t<false, true>(h, a, per_team, st);
-    return h->comp_bytes == 2 ? launch_team_t<true, false>(h, a, per_team, st) : launch_team_t<false, false>(h, a, per_team, st);
+    if (a.table_in_smem) return h->comp_bytes == 2 ? launch_team_t<true, true>(h, a, per_team, narrow_blocks, st) : launch_team_t<false, true>(h, a, per_team, narrow_blocks, st);
+    return h->comp_bytes == 2 ? launch_team_t<true, false>(h, a, per_team, narrow_blocks, st) : launch_team_t<false, false>(h, a, per_team, narrow_blocks, st);
 }
 
 }  // namespace cpb

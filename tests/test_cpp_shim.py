@@ -82,3 +82,29 @@ def test_gpu_class_fronts_run(cp):
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert "ALL PASS" in out.stdout
 
+
+
+OMP_EXE = os.path.join(ROOT, "tests", "cpp", "omp_search")
+
+
+def compile_omp():
+    lib_dir = os.path.join(ROOT, "sparse-text-kmeans_b200")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    subprocess.check_call([cxx, "-std=c++17", "-O2", "-fopenmp", "-I", os.path.join(ROOT, "include"),
+                           os.path.join(ROOT, "tests", "cpp", "omp_search.cpp"), "-L", lib_dir, "-lcphnsw_b200",
+                           "-Wl,-rpath," + lib_dir, "-o", OMP_EXE])
+
+
+def test_omp_search_compiles_and_links(cp):
+    """Searches from an OpenMP loop over one shared index (the loop shape of evaluation/eval_sift.cpp:380-387)."""
+    compile_omp()
+    assert os.path.exists(OMP_EXE)
+
+
+@pytest.mark.gpu
+def test_omp_search_runs(cp):
+    compile_omp()
+    out = subprocess.run([OMP_EXE], capture_output=True, text=True, timeout=600)
+    print(out.stdout[-3000:], out.stderr[-2000:])
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "ALL PASS" in out.stdout

@@ -32,7 +32,8 @@ def test_full_size_encode_knn_select_rows(c2, oracle):
         got, gd = idx.knn_graph(codes, 64, r0, r0 + 40)
         assert np.array_equal(got, want) and np.array_equal(gd, wd)
         sel = idx.select_neighbors(codes, got, 32, True, r0)
-        assert np.array_equal(sel, adj[r0:r0 + 40])
+        assert np.array_equal(sel, oracle.select_neighbors(codes, want, 32, True, r0))  # the pruning against the oracle's
+        assert np.array_equal(sel, adj[r0:r0 + 40])                                    # and the build kept exactly that
 
 
 def test_full_size_adjacency_properties(c2):

@@ -1,0 +1,224 @@
+"""GPU tests of the pieces around the hot path: rank-based pruning against the oracle, candidate ids that
+name no node, the bounded-wait exit of the kNN kernels, the library's code-distance walk against the
+reference's own walk, concurrent searches on one handle, installation from host buffers."""
+import os
+import threading
+
+import numpy as np
+import pytest
+
+from cphnsw_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+INVALID = 0xFFFFFFFF
+WALK = np.load(os.path.join(os.path.dirname(__file__), "golden", "walk_golden.npz"))
+
+
+def make_index(cp, dim, K=32, cb=1, M=32):
+    return cp.CPHNSWIndex(dim, M=M, ef_construction=max(200, M), K=K, component_bytes=cb)
+
+
+# ---- rank-based pruning ------------------------------------------------------------------------------
+@pytest.mark.parametrize("n,k,M,alpha", [(1, 8, 4, 1.0), (40, 64, 32, 1.1), (700, 64, 32, 1.1), (1500, 32, 16, 1.0),
+                                         (1500, 64, 32, 1.5), (900, 20, 32, 1.1), (2000, 64, 64, 3.0), (1200, 48, 8, 1.1)])
+def test_rank_prune_matches_oracle(cp, oracle, n, k, M, alpha):
+    base, _ = synthetic.gaussian_mixture(n, 1, 64, max(2, n // 200), 0.3, n + k)
+    codes = oracle.encode(base, 32, 1, oracle.sign_tables(64, 32, 42))
+    cand, _ = oracle.knn_graph(codes, k)
+    idx = make_index(cp, 64, M=min(M, 64))
+    got = idx.rank_prune(cand, M, alpha)
+    want = oracle.rank_prune(cand, M, alpha)
+    assert np.array_equal(got, want)
+    valid = got != INVALID
+    assert (got[valid] < n).all() and not (got == np.arange(n, dtype=np.uint32)[:, None]).any()
+    s = np.sort(got, axis=1)
+    assert not ((s[:, 1:] == s[:, :-1]) & (s[:, 1:] != INVALID)).any()  # each id once in a row
+
+
+def test_rank_prune_build_matches_oracle_and_searches(cp, oracle):
+    n, dim, K, M = 4000, 128, 32, 32
+    base, q = synthetic.gaussian_mixture(n, 100, dim, 16, 0.3, 5)
+    idx = make_index(cp, dim, K, 1, M)
+    idx.set_param("entry_scan", 128)
+    idx.set_param("rank_prune", 1)
+    idx.set_param("rank_pruning_alpha", 1.1)
+    idx.add_batch_parallel(base)
+    codes = oracle.encode(base, K, 1, oracle.sign_tables(dim, K, 42))
+    cand, _ = oracle.knn_graph(codes, 64)
+    assert np.array_equal(idx.adjacency(), oracle.rank_prune(cand, M, 1.1))
+    ids, _ = idx.search_and_rerank_batch(q, 10, 100, 200)
+    gt = oracle.ground_truth(q, base, 10)
+    assert oracle.recall_at_k(ids, gt, 10) > 0.8
+    with pytest.raises(ValueError):
+        idx.set_param("rank_pruning_alpha", 0.5)
+    with pytest.raises(ValueError):
+        idx.set_param("rank_pruning_alpha", 3.5)
+
+
+# ---- ids that name no node are skipped, never read -----------------------------------------------------
+def test_select_neighbors_skips_out_of_range_candidates(cp, oracle):
+    n, k, M = 600, 32, 16
+    base, _ = synthetic.gaussian_mixture(n, 1, 128, 4, 0.3, 9)
+    codes = oracle.encode(base, 32, 1, oracle.sign_tables(128, 32, 42))
+    cand, _ = oracle.knn_graph(codes, k)
+    bad = cand.copy()
+    rng = np.random.default_rng(1)
+    for row in range(0, n, 3):  # a few ids >= n among the candidates, the largest legal-looking ones included
+        for col in rng.choice(k, 3, replace=False):
+            bad[row, col] = rng.choice([n, n + 7, 0x7FFFFFFF, 0xFFFFFFFE])
+    idx = make_index(cp, 128, M=M)
+    got = idx.select_neighbors(codes, bad, M, True)
+    clean = np.where(bad >= n, INVALID, bad).astype(np.uint32)
+    assert np.array_equal(got, oracle.select_neighbors(codes, clean, M, True))
+    assert (got[got != INVALID] < n).all()
+
+
+# ---- the bounded wait of the kNN kernels ----------------------------------------------------------------
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_lost_wait_is_reported_and_the_handle_stays_usable(cp, oracle, kernel):
+    # nothing is made to hang: the first wait of the launch is given zero polls, so it gives up at once,
+    # the blocks let their copies in flight land (full poll limit) and return, the call reports the status
+    n, k = 3000, 16
+    base, _ = synthetic.gaussian_mixture(n, 1, 128, 8, 0.3, 3)
+    codes = oracle.encode(base, 32, 1, oracle.sign_tables(128, 32, 42))
+    idx = make_index(cp, 128)
+    idx.set_param("knn_kernel", kernel)
+    idx.set_param("first_wait_polls", 0)
+    with pytest.raises(cp.CPHNSWError) as err:
+        idx.knn_graph(codes, k)
+    assert "[%d]" % cp.E_DEVICE_WAIT in str(err.value)
+    idx.check_device_status()  # the status word was cleared by the failing call
+    idx.set_param("first_wait_polls", 1 << 22)
+    got, gd = idx.knn_graph(codes, k)
+    want, wd = oracle.knn_graph(codes, k)
+    assert np.array_equal(got, want) and np.array_equal(gd, wd)
+    # a bulk build that loses its wait leaves the index as it was
+    idx.add_batch_parallel(base[:1000])
+    adj = idx.adjacency()
+    idx.set_param("first_wait_polls", 0)
+    with pytest.raises(cp.CPHNSWError):
+        idx.add_batch_parallel(base[1000:2000])
+    idx.set_param("first_wait_polls", 1 << 22)
+    assert idx.size() == 1000 and np.array_equal(idx.adjacency(), adj)
+    idx.add_batch_parallel(base[1000:2000])
+    assert idx.size() == 2000
+
+
+# ---- the code-distance walk against the reference's SearchEngine (tie-free cases: exact) --------------
+def _entries(row):
+    return row[row != INVALID]
+
+
+def _entries_first(n, entry, adj):
+    """Entry ids of an index are evenly spaced node ids; renumber the nodes so that the wanted entry
+    points are exactly those.  Returns perm (perm[new] = old) and the renumbered adjacency."""
+    ne = len(entry)
+    slots = (np.arange(ne, dtype=np.uint64) * n // ne).astype(np.int64)
+    rest = np.setdiff1d(np.arange(n), slots)
+    perm = np.empty(n, np.uint32)
+    perm[slots] = entry
+    perm[rest] = np.setdiff1d(np.arange(n, dtype=np.uint32), entry)
+    inv = np.empty(n, np.uint32)
+    inv[perm] = np.arange(n, dtype=np.uint32)
+    adj2 = np.where(adj[perm] == INVALID, INVALID, inv[np.minimum(adj[perm], n - 1)]).astype(np.uint32)
+    return perm, adj2
+
+
+def test_walk_equals_reference_walk_tie_free(cp, oracle):
+    for c in range(WALK["tf64_q"].shape[0]):
+        ef = int(WALK["tf64_ef"][c])
+        codes = oracle.unpack_sign_bits(WALK["tf64_codes"][c], 64)
+        q = oracle.unpack_sign_bits(WALK["tf64_q"][c:c + 1], 64)
+        entry = _entries(WALK["tf64_entry"][c])
+        n = codes.shape[0]
+        perm, adj2 = _entries_first(n, entry, WALK["tf64_adj"][c])
+        idx = cp.CPHNSWIndex.binary(64, M=6, ef_construction=200, K=64)
+        idx.install(np.zeros((n, 64), np.float32), codes[perm], adj2)
+        assert np.array_equal(idx.get_code(5), codes[perm][5])
+        # the walk is seeded with exactly the reference's entry points: all scanned ids seed it
+        idx.set_param("entry_scan", len(entry))
+        idx.set_param("k_entry", len(entry))
+        assert np.array_equal(perm[idx.entry_ids()], entry)
+        ids, dist = idx.search_codes_batch(q, ef, ef)
+        got = np.where(ids[0] == INVALID, INVALID, perm[np.minimum(ids[0], n - 1)])
+        assert np.array_equal(got, WALK["tf64_ids"][c, :ef]), c
+        assert np.array_equal(dist[0], WALK["tf64_dist"][c, :ef]), c
+
+
+def test_walk_equals_reference_walk_residual_tie_free(cp, oracle):
+    for c in range(WALK["tfr_qp"].shape[0]):
+        ef = int(WALK["tfr_ef"][c])
+        codes = np.concatenate([oracle.unpack_sign_bits(WALK["tfr_prim"][c], 32), oracle.unpack_sign_bits(WALK["tfr_resi"][c], 16)], axis=1)
+        q = np.concatenate([oracle.unpack_sign_bits(WALK["tfr_qp"][c:c + 1], 32), oracle.unpack_sign_bits(WALK["tfr_qr"][c:c + 1], 16)], axis=1)
+        entry = _entries(WALK["tfr_entry"][c])
+        n = codes.shape[0]
+        adj = WALK["tfr_adj"][c]
+        perm, adj2 = _entries_first(n, entry, adj)
+        idx = cp.CPHNSWIndex.binary(64, M=6, ef_construction=200, K=48)
+        idx.set_param("residual_bits", 16)
+        idx.set_param("residual_shift", 2)
+        idx.install(np.zeros((n, 64), np.float32), codes[perm], adj2)
+        idx.set_param("entry_scan", len(entry))
+        idx.set_param("k_entry", len(entry))
+        ids, dist = idx.search_codes_batch(q, ef, ef)
+        got = np.where(ids[0] == INVALID, INVALID, perm[np.minimum(ids[0], n - 1)])
+        assert np.array_equal(got, WALK["tfr_ids"][c, :ef]), c
+        assert np.array_equal(dist[0], WALK["tfr_dist"][c, :ef]), c
+
+
+# ---- concurrent searches on one handle -------------------------------------------------------------------
+def test_concurrent_single_query_searches_equal_the_batch(cp):
+    # the reference's callers search from OpenMP loops, one query per call (evaluation/eval_sift.cpp:380-387)
+    n, nq, dim = 20000, 256, 128
+    base, q = synthetic.gaussian_mixture(n, nq, dim, 40, 0.3, 21)
+    idx = make_index(cp, dim)
+    idx.set_param("entry_scan", 512)
+    idx.set_param("k_entry", 8)
+    idx.add_batch_parallel(base)
+    want_i, want_d = idx.search_and_rerank_batch(q, 10, 100, 200)
+    ws_i, ws_d = idx.search_batch(q, 10, 64)
+    got_i = np.zeros_like(want_i)
+    got_d = np.zeros_like(want_d)
+    gs_i = np.zeros_like(ws_i)
+    gs_d = np.zeros_like(ws_d)
+    errors = []
+
+    def worker(t, nthreads):
+        try:
+            for i in range(t, nq, nthreads):
+                a, b = idx.search_and_rerank_batch(q[i:i + 1], 10, 100, 200)
+                got_i[i], got_d[i] = a[0], b[0]
+                a, b = idx.search_batch(q[i:i + 1], 10, 64)
+                gs_i[i], gs_d[i] = a[0], b[0]
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=worker, args=(t, 16)) for t in range(16)]
+    for t in threads:
+        t.start()
+    # a large batch takes its turn on the wide context while the single-query calls run
+    big_i, big_d = idx.search_and_rerank_batch(q, 10, 100, 200)
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert np.array_equal(got_i, want_i) and np.array_equal(got_d, want_d)
+    assert np.array_equal(gs_i, ws_i) and np.array_equal(gs_d, ws_d)
+    assert np.array_equal(big_i, want_i) and np.array_equal(big_d, want_d)
+
+
+def test_narrow_launch_equals_wide_launch(cp):
+    # up to 32 queries run one block per query, more fill the GPU: same results either way
+    n, dim = 12000, 96
+    base, q = synthetic.gaussian_mixture(n, 200, dim, 24, 0.3, 4)
+    for kern in (1, 2):
+        idx = make_index(cp, dim)
+        idx.set_param("entry_scan", 256)
+        idx.set_param("search_kernel", kern)
+        idx.add_batch_parallel(base)
+        wide = idx.search_and_rerank_batch(q, 10, 80, 150, want_stats=True)
+        for lo, hi in ((0, 1), (1, 33), (33, 40), (40, 72)):
+            part = idx.search_and_rerank_batch(q[lo:hi], 10, 80, 150, want_stats=True)
+            assert all(np.array_equal(a, b[lo:hi]) for a, b in zip(part, wide))
+        mp = idx.search_multiprobe_batch(q[:64], 10, 50, 4)
+        one = idx.search_multiprobe_batch(q[3:4], 10, 50, 4)
+        assert np.array_equal(one[0][0], mp[0][3]) and np.array_equal(one[1][0], mp[1][3])

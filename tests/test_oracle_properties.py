@@ -269,3 +269,49 @@ def test_connectivity_counts_reachable_nodes(oracle):
     assert oracle.connectivity(adj, np.array([], np.uint32)) == 0
     assert oracle.connectivity(adj, np.array([2, inv], np.uint32)) == 1
 
+
+
+def rank_prune_py(cand, M, alpha):
+    """Rank-based pruning written from the paper's text with Python sets and lists (1-based ranks)."""
+    n, k = cand.shape
+    lists = [[int(v) for v in row if v < n] for row in cand]
+    pos = [{y: j + 1 for j, y in enumerate(row) if y < n} for row in cand.tolist()]
+    kept = []
+    for x in range(n):
+        scored = []
+        for y, ry in pos[x].items():
+            detours = sum(1 for z, rz in pos[x].items()
+                          if y in pos[z] and np.float32(alpha) * np.float32(max(rz, pos[z][y])) < np.float32(ry))
+            scored.append((detours, ry, y))
+        kept.append([y for _, _, y in sorted(scored)[:M]])
+    rev = [[] for _ in range(n)]
+    for x in range(n):
+        for r, p in enumerate(kept[x]):
+            rev[p].append((r, x))
+    out = np.full((n, M), INVALID, np.uint32)
+    for p in range(n):
+        a, b = list(kept[p]), [x for _, x in sorted(rev[p])[:M]]
+        row, turn = [], 0
+        while len(row) < M:
+            a = [v for v in a if v not in row]
+            b = [v for v in b if v not in row]
+            if not a and not b:
+                break
+            src = a if (not b or (a and turn == 0)) else b
+            row.append(src.pop(0))
+            turn ^= 1
+        out[p, :len(row)] = row
+    return out
+
+
+@pytest.mark.parametrize("alpha", [1.0, 1.1, 2.0])
+def test_rank_prune_matches_python(oracle, alpha):
+    base, q, signs, codes = small_index(oracle, n=260)
+    cand, _ = oracle.knn_graph(codes, 20)
+    cand[7, 15:] = INVALID
+    for M in (8, 20, 32):
+        assert np.array_equal(oracle.rank_prune(cand, M, alpha), rank_prune_py(cand, M, alpha)), M
+    # alpha = 1 is the paper's condition max(rank_XZ, rank_ZY) < rank_XY; a larger alpha can only remove detours,
+    # so the nearest candidate (rank 1, never detourable) is always kept first
+    adj = oracle.rank_prune(cand, 8, alpha)
+    assert np.array_equal(adj[:, 0], cand[:, 0])

@@ -22,7 +22,7 @@ def _device_arrays(torch, a, b):
     return ta, tb, out
 
 
-def _both_ways(cp, torch, K, cb, na, nb, seed):
+def _both_ways(cp, torch, K, cb, na, nb, seed, check_memory=False):
     rng = np.random.default_rng(seed)
     dt = np.uint8 if cb == 1 else np.uint16
     hi = 256 if cb == 1 else 2048
@@ -35,8 +35,13 @@ def _both_ways(cp, torch, K, cb, na, nb, seed):
     idx = cp.CPHNSWIndex(128 if cb == 1 else 1024, K=K, component_bytes=cb)
     idx.code_distance_dev(ta.data_ptr(), na, tb.data_ptr(), nb, out_ref.data_ptr())
     torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(0)[0] if check_memory else None
     cp.code_distance_noalloc(ta.data_ptr(), na, tb.data_ptr(), nb, K, cb, out_new.data_ptr())
     torch.cuda.synchronize()
+    if check_memory:
+        # the device's free memory is what it was: the call allocated nothing (the first call on a device may
+        # make the driver load the kernels it uses, so the claim is checked from the second call on)
+        assert torch.cuda.mem_get_info(0)[0] == free_before
     want = (a[:, None, :] != b[None, :, :]).sum(-1).astype(np.int16)
     return out_new.cpu().numpy(), out_ref.cpu().numpy(), want
 
@@ -49,7 +54,7 @@ def test_noalloc_matches_existing_entry_point_twice_in_a_row(cp):
     assert np.array_equal(new1, ref1)
     assert np.array_equal(new1, want1)
     # second call straight after: smaller, other component type and width
-    new2, ref2, want2 = _both_ways(cp, torch, K=32, cb=1, na=257, nb=1000, seed=2)
+    new2, ref2, want2 = _both_ways(cp, torch, K=32, cb=1, na=257, nb=1000, seed=2, check_memory=True)
     assert np.array_equal(new2, ref2)
     assert np.array_equal(new2, want2)
 
