@@ -38,6 +38,21 @@ int cuda_fail(cudaError_t e, const char* what);
         if (rc__ != 0) return rc__; \
     } while (0)
 
+// Lets a kernel use as much dynamic shared memory as the device grants a block.  The attribute belongs to the
+// function, not to the launch: concurrent callers that each set "what my launch needs" would lower it under one
+// another's feet, so every caller sets the same, largest value (the device's opt-in limit less the kernel's static
+// shared memory).
+template <class F>
+inline cudaError_t allow_max_dynamic_smem(F* kernel) {
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+    if (e != cudaSuccess) return e;
+    int dev = 0, optin = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - int(fa.sharedSizeBytes));
+}
+
 // kernel families whose launches can be timed
 enum KernelKind { kKernelEncode = 0, kKernelCodeDistance = 1, kKernelKnn = 2, kKernelSelect = 3, kKernelSearch = 4 };
 constexpr int kKernelKinds = 5;

@@ -410,8 +410,7 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
         const bool query = d_rot || d_mag;
 #define CPB_LAUNCH_P128(T, Q)                                                                              \
     do {                                                                                                   \
-        CPB_CUDA(cudaFuncSetAttribute(encode_p128_kernel<T, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                      int(smem)));                                                         \
+        CPB_CUDA(allow_max_dynamic_smem(encode_p128_kernel<T, Q>));                                        \
         encode_p128_kernel<T, Q><<<grid, kTileVecs, smem, st>>>(d_x, n, dim, K, signs, flip_mask,           \
                                                                (T*)d_codes, d_rot, d_mag);                  \
     } while (0)
@@ -445,11 +444,11 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
         uint64_t blocks = (n + warps - 1) / warps;
         unsigned grid = unsigned(blocks < uint64_t(h->sm_count) * 16 ? blocks : uint64_t(h->sm_count) * 16);
         if (h->comp_bytes == 1) {
-            CPB_CUDA(cudaFuncSetAttribute(encode_generic_kernel<uint8_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+            CPB_CUDA(allow_max_dynamic_smem(encode_generic_kernel<uint8_t>));
             encode_generic_kernel<uint8_t><<<grid, warps * 32, smem, st>>>(d_x, n, dim, P, K, signs, flip_mask,
                                                                           (uint8_t*)d_codes, d_rot, d_mag);
         } else {
-            CPB_CUDA(cudaFuncSetAttribute(encode_generic_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+            CPB_CUDA(allow_max_dynamic_smem(encode_generic_kernel<uint16_t>));
             encode_generic_kernel<uint16_t><<<grid, warps * 32, smem, st>>>(d_x, n, dim, P, K, signs, flip_mask,
                                                                            (uint16_t*)d_codes, d_rot, d_mag);
         }

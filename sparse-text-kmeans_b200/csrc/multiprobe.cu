@@ -251,10 +251,10 @@ int launch_probe_codes(cphnsw_b200_index* h, const float* d_rotated, uint64_t nq
     }
     const unsigned grid = unsigned(nq < uint64_t(h->sm_count) * 8 ? nq : uint64_t(h->sm_count) * 8);
     if (h->comp_bytes == 2) {
-        CPB_CUDA(cudaFuncSetAttribute(probe_codes_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        CPB_CUDA(allow_max_dynamic_smem(probe_codes_kernel<true>));
         probe_codes_kernel<true><<<grid, 32, smem, st>>>(a);
     } else {
-        CPB_CUDA(cudaFuncSetAttribute(probe_codes_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        CPB_CUDA(allow_max_dynamic_smem(probe_codes_kernel<false>));
         probe_codes_kernel<false><<<grid, 32, smem, st>>>(a);
     }
     h->launches++;
@@ -268,7 +268,7 @@ int launch_merge_probes(cphnsw_b200_index* h, const uint32_t* d_ids, const float
     int npad = 32;
     while (npad < int(T * k)) npad <<= 1;
     const size_t smem = size_t(npad) * 8 + size_t(k) * 4;
-    CPB_CUDA(cudaFuncSetAttribute(merge_probes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    CPB_CUDA(allow_max_dynamic_smem(merge_probes_kernel));
     const unsigned grid = unsigned(nq < uint64_t(h->sm_count) * 8 ? nq : uint64_t(h->sm_count) * 8);
     merge_probes_kernel<<<grid, 32, smem, st>>>(d_ids, d_dist, uint32_t(nq), int(T), int(k), npad, d_out_ids, d_out_dist);
     h->launches++;

@@ -582,8 +582,7 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
         int maxw = 65536 / (((fa.numRegs + 7) & ~7) * 32);                                                 \
         int w = narrow ? 1 : (c.warps < maxw ? c.warps : maxw);                                            \
         size_t smem = c.per_warp * w;                                                                      \
-        CPB_CUDA(cudaFuncSetAttribute(search_kernel<U, T, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                      int(smem)));                                                         \
+        CPB_CUDA(allow_max_dynamic_smem(search_kernel<U, T, S>));                                          \
         search_kernel<U, T, S><<<grid, w * 32, smem, st>>>(a);                                             \
     } while (0)
     if (sym && u16) CPB_SEARCH(true, false, true);

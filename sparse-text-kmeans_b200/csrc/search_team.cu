@@ -675,7 +675,7 @@ static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, in
     if (narrow_blocks) teams = 1;  // one query per block
     for (; teams >= 1; --teams) {
         int blocks = 0;
-        CPB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(per_team * teams)));
+        CPB_CUDA(allow_max_dynamic_smem(kernel));
         CPB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, teams * 64, per_team * teams));
         if (blocks >= 1) break;
     }

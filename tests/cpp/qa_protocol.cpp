@@ -211,19 +211,22 @@ int main() {
         CHECK(!r.empty() && r[0].id == 0, "uint16_t components, padded dim 512");
     }
     {
-        // build_with_gpu_knn (evaluation/test_gpu_build.cpp:168-174): same graph as add_batch_parallel with knn_k = k
+        // build_with_gpu_knn (evaluation/test_gpu_build.cpp:168-174): k candidates per node, pruned by rank with the
+        // detour threshold alpha = the bulk build with knn_k = k, rank_prune = 1 and that alpha
         auto b = unit_vectors(3000, dim, 11);
         CPHNSWIndex<uint8_t, 32> g(dim, 32, 200), ref(dim, 32, 200), cut(dim, 32, 200);
         g.build_with_gpu_knn(b.data(), 3000, 64, true, 1.1f);
         ref.set_param("knn_k", 64);
+        ref.set_param("rank_prune", 1);
+        ref.set_param("rank_pruning_alpha", 1.1);
         ref.add_batch_parallel(b.data(), 3000);
-        bool same = g.size() == 3000;
+        bool same = g.size() == 3000 && g.adjacency() == ref.adjacency() && g.param("rank_prune") == 0.0;
         for (size_t q = 0; q < 20 && same; ++q) {
             auto x = g.search_and_rerank(b.data() + q * dim, 5, 50, 50), y = ref.search_and_rerank(b.data() + q * dim, 5, 50, 50);
             same = x.size() == y.size();
             for (size_t t = 0; t < x.size() && same; ++t) same = x[t] == y[t];
         }
-        CHECK(same, "build_with_gpu_knn(k=64, prune) answers like add_batch_parallel with knn_k = 64");
+        CHECK(same, "build_with_gpu_knn(k=64, prune, alpha) is the bulk build with rank-based pruning");
         CHECK(g.verify_connectivity() > 2900, "build_with_gpu_knn graph is connected from the entry nodes");
         cut.build_with_gpu_knn(b.data(), 3000, 64, false, 1.1f);
         auto r = cut.search_and_rerank(b.data() + 7 * dim, 5, 50, 50);
