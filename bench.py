@@ -53,6 +53,8 @@ def parse_args():
                     help="run on fvecs files (rows are normalised) instead of a synthetic workload")
     ap.add_argument("--search-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="0 = the library's choice, 1 = one warp per query, 2 = two warps per query")
+    ap.add_argument("--search-table-smem", type=int, default=1, choices=[0, 1],
+                    help="0 = the search kernels read the query table in place (global memory) even when it fits shared memory")
     return ap.parse_args()
 
 
@@ -118,8 +120,42 @@ def overrides(w, args):
     return w
 
 
+def host_info():
+    """CPU model, usable cores and the vector ISA flags the CPU baselines can use."""
+    model, flags = "unknown", []
+    try:
+        with open("/proc/cpuinfo") as f:
+            txt = f.read()
+        for ln in txt.splitlines():
+            if ln.startswith("model name"):
+                model = ln.split(":", 1)[1].strip()
+                break
+        have = set(txt.split("flags", 1)[1].split("\n", 1)[0].split())
+        flags = [fl for fl in ("avx2", "fma", "avx512f", "avx512bw", "avx512vl", "avx512_vpopcntdq") if fl in have]
+    except Exception:
+        pass
+    try:
+        usable = len(os.sched_getaffinity(0))
+    except Exception:
+        usable = os.cpu_count() or 1
+    return {"cpu_model": model, "nproc": os.cpu_count(), "usable_cores": usable, "isa": flags}
+
+
+def load_cpu_oracle():
+    """The oracle for the CPU legs: the tuned build where it compiles on this host (the plain build otherwise),
+    on every usable core whatever OMP_NUM_THREADS says (launchers such as torchrun export 1)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+    tuned = O.use_tuned_build()
+    info = host_info()
+    info["threads"] = O.set_threads(info["usable_cores"])
+    info["build"] = ("tuned: -O3 -march=native, sorted-array beam, AVX-512 gather score / byte compare where the host has them"
+                     if tuned else "plain checker build (-O3 -march=x86-64-v3): the tuned build did not compile here")
+    return O, info
+
+
 def oracle_index(O, w):
-    """Builds the workload's index with the CPU oracle (setup for the CPU arms; untimed)."""
+    """Builds the workload's index with the CPU oracle (setup for the CPU search leg; untimed except where noted)."""
     base = w["base"]
     K, cb, M = w["K"], w["component_bytes"], w["M"]
     signs = O.sign_tables(base.shape[1], K, 42)
@@ -129,58 +165,165 @@ def oracle_index(O, w):
     n = base.shape[0]
     scan = min(w["entry_scan"], n)
     entry = (np.arange(scan, dtype=np.uint64) * n // scan).astype(np.uint32)
-    return signs, codes, adj, entry
+    return signs, codes, cand, adj, entry
+
+
+CPU_INDEX_POINTS = 100_000  # the CPU search leg's index: what the O(n^2) CPU graph build finishes in well under a minute
 
 
 def cpu_sample(args, n_queries):
-    """The bounded CPU sample of the workload: the same generator scaled so that the oracle's
-    O(n^2) graph build stays within a minute (cluster population, entry scan and beam unchanged)."""
+    """The bounded CPU sample of the workload: the same generator scaled down (cluster population, entry scan
+    and beam unchanged, so the work per query is the full configuration's)."""
     from cphnsw_b200 import synthetic
-    scale = min(args.scale, 50_000.0 / full_base_size(args.workload))
+    scale = min(args.scale, float(CPU_INDEX_POINTS) / full_base_size(args.workload))
     w = overrides(synthetic.workload(args.workload, scale), args)
     w["entry_scan"] = min(full_entry_scan(args), w["base"].shape[0])
-    w["queries"] = w["queries"][:n_queries]
+    if w["queries"].shape[0] < n_queries:  # more queries of the same distribution
+        extra = [synthetic.workload(args.workload, scale, query_stream=100 + i)["queries"]
+                 for i in range((n_queries - 1) // w["queries"].shape[0])]
+        w["queries"] = np.concatenate([w["queries"]] + extra)
+    w["queries"] = np.ascontiguousarray(w["queries"][:n_queries])
     return w, scale
 
 
-def cpu_steps(args, n_queries, steps, warmup):
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import oracle as O
+def step_stats(ms):
+    ms = [float(v) for v in ms]
+    return {"min": min(ms), "median": float(np.median(ms)), "max": max(ms)}
+
+
+def cpu_steps(args, n_queries, steps, warmup, build_stages=False):
+    """Times the CPU arm.  Returns the search leg's numbers and, with build_stages, the build stages too
+    (encode = the reference's own CPEncoder::encode_batch where its AVX-512 build runs on this host)."""
+    O, info = load_cpu_oracle()
     w, scale = cpu_sample(args, n_queries)
-    signs, codes, adj, entry = oracle_index(O, w)
+    signs, codes, cand, adj, entry = oracle_index(O, w)
     base, q, K, cb = w["base"], w["queries"], w["K"], w["component_bytes"]
     beam = max(w["ef"], w["rerank_k"], w["k"])
+    n_seed = w.get("k_entry", 4)
 
     def step():
         _, rot, _ = O.encode(q, K, cb, signs, O.FHT_AVX512, want_rotated=True)
-        cands, _ = O.search(rot, codes, adj, entry, beam, w["rerank_k"], n_seed=w.get("k_entry", 4))
+        cands, _ = O.search(rot, codes, adj, entry, beam, w["rerank_k"], n_seed=n_seed)
         return O.rerank(q, base, cands, w["k"])
 
     for _ in range(warmup):
         step()
-    t0 = time.perf_counter()
+    times = []
     for _ in range(steps):
+        t0 = time.perf_counter()
         ids, _ = step()
-    dt = (time.perf_counter() - t0) / steps
+        times.append(time.perf_counter() - t0)
+    dt = sum(times) / steps
     recall = O.recall_at_k(ids, O.ground_truth(q, base, w["k"]), w["k"])
-    sample = ("%d queries per step on an index of %d points (%s at %.3g of its size, same cluster population; "
-              "entry_scan=%d, beam=%d, rerank_k=%d); CPU oracle with OpenMP - the reference's legacy search sources are "
-              "absent from its tree" % (q.shape[0], base.shape[0], w["name"], scale, entry.size, beam, w["rerank_k"]))
-    return w, q.shape[0] / dt, dt, recall, O.num_threads(), sample
+    # the tuned build against the plain checker on the first queries: identical ids or the number means nothing
+    identical = None
+    if O.is_tuned():
+        m = min(50, q.shape[0])
+        O.use_plain_build()
+        _, rot, _ = O.encode(q[:m], K, cb, signs, O.FHT_AVX512, want_rotated=True)
+        want, _ = O.search(rot, codes, adj, entry, beam, w["rerank_k"], n_seed=n_seed)
+        wi, _ = O.rerank(q[:m], base, want, w["k"])
+        identical = bool(np.array_equal(wi, ids[:m]))
+        O.use_tuned_build()
+        O.set_threads(info["usable_cores"])
+    sample = ("%d queries per step on an index of %d points (%s at %.3g of its size: the CPU cannot build the full "
+              "O(n^2) graph in the time of a benchmark run; same cluster population, entry_scan=%d, beam=%d, rerank_k=%d, "
+              "so the same work per query); the oracle's restatement with OpenMP - the reference's legacy search sources "
+              "are absent from its tree" % (q.shape[0], base.shape[0], w["name"], scale, entry.size, beam, w["rerank_k"]))
+    out = {"w": w, "qps": q.shape[0] / dt, "dt": dt, "times_ms": [t * 1e3 for t in times], "recall": recall,
+           "info": info, "sample": sample, "identical": identical, "index_points": int(base.shape[0]), "scale": scale}
+    if build_stages:
+        out["stages"] = cpu_build_stages(O, info, args, w, codes, cand)
+    return out
+
+
+def cpu_build_stages(O, info, args, w, codes, cand):
+    """CPU numbers for the three build stages of the metric, each on a bounded sample."""
+    base, K, cb, M = w["base"], w["K"], w["component_bytes"], w["M"]
+    n = base.shape[0]
+    n_full = int(full_base_size(args.workload) * args.scale)
+    stages = {}
+    # encode: the reference's own CPEncoder<32,0>::encode_batch (include/cphnsw/encoder/cp_encoder.hpp:244-260) from
+    # its AVX-512 build: the same rotations, transforms and argmax as the K-byte code, it keeps the sign bit only
+    enc = None
+    if K == 32 and O.ref_available(O.FHT_AVX512):
+        try:
+            R = O.Ref(O.FHT_AVX512)
+            R.encode_batch_signbits32(base[:4096])
+            t0 = time.perf_counter()
+            R.encode_batch_signbits32(base)
+            dt = time.perf_counter() - t0
+            enc = {"value": n / dt, "unit": "vectors/s", "kind": "reference", "cores": info["threads"],
+                   "sample": "%d vectors of dim %d through the reference's CPEncoder<32,0>::encode_batch, built "
+                             "-mavx512f -mavx512bw -mavx512vl -fopenmp" % (n, base.shape[1])}
+        except Exception:
+            enc = None
+    if enc is None:
+        signs = O.sign_tables(base.shape[1], K, 42)
+        t0 = time.perf_counter()
+        O.encode(base, K, cb, signs, O.FHT_AVX512)
+        dt = time.perf_counter() - t0
+        enc = {"value": n / dt, "unit": "vectors/s", "kind": "port", "cores": info["threads"],
+               "sample": "%d vectors of dim %d through the oracle's encode (scalar transform; the reference's AVX-512 "
+                         "build is not available on this host)" % (n, base.shape[1])}
+    stages["encode"] = enc
+    # kNN graph: sampled rows against all codes of the sample index, scaled to rows/s against the FULL index
+    k = w.get("knn_k", min(64, 2 * M))
+    rows = min(n, 4000)
+    O.knn_graph(codes, k, 0, min(rows, 256))
+    t0 = time.perf_counter()
+    O.knn_graph(codes, k, 0, rows)
+    dt = time.perf_counter() - t0
+    pairs = rows * float(n) / dt
+    stages["knn_graph"] = {"value": pairs / n_full, "unit": "vectors/s", "pairs_per_s": pairs, "kind": "port", "sampled": True,
+                           "cores": info["threads"],
+                           "sample": "%d rows against %d codes, k=%d; vectors/s = measured pairs/s / %d (rows/s the same "
+                                     "code would reach against the full index)" % (rows, n, k, n_full)}
+    t0 = time.perf_counter()
+    O.select_neighbors(codes, cand, M, True)
+    dt = time.perf_counter() - t0
+    stages["select_neighbors"] = {"value": n / dt, "unit": "vectors/s", "kind": "port", "cores": info["threads"],
+                                  "sample": "%d rows of %d candidates" % (n, cand.shape[1])}
+    return stages
+
+
+def cpu_baseline_object(r):
+    obj = {"value": r["qps"], "unit": "queries/s", "cores": r["info"]["threads"], "kind": "port", "sample": r["sample"],
+           "recall_at_10": r["recall"], "index_points": r["index_points"], "ms_per_step": step_stats(r["times_ms"]),
+           "build_flags": r["info"]["build"], "identical_to_checker": r["identical"], "cpu_model": r["info"]["cpu_model"],
+           "nproc": r["info"]["nproc"], "usable_cores": r["info"]["usable_cores"], "isa": r["info"]["isa"]}
+    for name, st in r.get("stages", {}).items():
+        obj[name] = st
+    return obj
+
+
+def b200_config(args, w, n, dim, nq, n_entry, knn_k):
+    """The `config` object of both arms: the workload the line is quoted on."""
+    K, cb, M = w["K"], w["component_bytes"], w["M"]
+    return {"workload": w["name"], "n_base": n, "dim": dim, "queries_per_rank": nq, "k": w["k"], "ef": w["ef"],
+            "rerank_k": w["rerank_k"], "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry,
+            "k_entry": w.get("k_entry", 4), "knn_k": knn_k,
+            "l2": "index (vectors+codes+adjacency = %.0f MB) larger than L2" % (n * (dim * 4 + K * cb + M * 4) / 1e6)}
 
 
 def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    w, qps, dt, recall, cores, sample = cpu_steps(args, 500, args.steps, args.warmup)
+    r = cpu_steps(args, 2000, args.steps, args.warmup, build_stages=True)
+    w = r["w"]
+    # the arm's config is the b200 arm's: the full workload; what the CPU actually ran is the bounded sample below
+    from cphnsw_b200 import synthetic  # noqa: F401  (generators only; no GPU code is touched by this arm)
+    n_full = int(full_base_size(args.workload) * args.scale)
+    nq_full = {"C1": 1000, "C2": 10_000, "C3": 10_000, "C4": 1000, "C5": 100_000}[args.workload]
+    cfg = b200_config(args, w, n_full, w["base"].shape[1], max(10, int(round(nq_full * args.scale))),
+                      min(full_entry_scan(args), n_full), w.get("knn_k", min(64, 2 * w["M"])))
+    cfg["cpu_sample"] = {"index_points": r["index_points"], "scale_of_workload": r["scale"], "queries_per_step": 2000}
     line = {
-        "impl": "reference", "metric": METRIC, "value": qps, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["name"], "k": w["k"], "ef": w["ef"], "rerank_k": w["rerank_k"], "K": w["K"], "M": w["M"]},
-        "recall_at_10": recall,
-        "cpu_baseline": {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": qps, "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRIC, "value": r["qps"], "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": r["dt"] * 1e3, "ms_per_step_stats": step_stats(r["times_ms"]),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": cfg, "recall_at_10": r["recall"], "cpu_baseline": cpu_baseline_object(r),
+        "e2e": {"value": r["qps"], "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
@@ -237,10 +380,12 @@ def run_b200(args):
     knn_k = w.get("knn_k", min(64, 2 * M))
 
     idx = cp.CPHNSWIndex(dim, M=M, ef_construction=w["ef_construction"], K=K, component_bytes=cb, device=local_rank)
+    idx_sm_count = torch.cuda.get_device_properties(local_rank).multi_processor_count
     idx.set_param("entry_scan", w["entry_scan"])
     idx.set_param("k_entry", w.get("k_entry", 4))
     idx.set_param("profile", 1)
     idx.set_param("search_kernel", args.search_kernel)
+    idx.set_param("search_table_smem", args.search_table_smem)
 
     # ---- build (sharded by row block), each stage timed with CUDA events, max over ranks ----
     rb, re = sharded.shard_range(n, rank, world)
@@ -261,8 +406,16 @@ def run_b200(args):
             torch.cuda.synchronize()
             stage_ms[self.name] = max_over_ranks(self.e0.elapsed_time(self.e1))
 
-    if world > 1:  # start NCCL before the timed build (its first collective sets the communicator up)
+    if world > 1:
+        # start NCCL before the timed build: the first collective sets the communicator up and the first
+        # all-gather of each size sets its channels up, so both gathers of the build are rehearsed at full size
         dist.all_reduce(torch.zeros(1, device=dev))
+        for nbytes in (n * K * cb, n * M * 4):
+            part = torch.zeros((nbytes + world - 1) // world, dtype=torch.uint8, device=dev)
+            full = torch.empty(part.numel() * world, dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(full, part)
+        torch.cuda.synchronize()
+        del part, full
     stages = sharded.CudaStages(idx)
     # untimed warm pass of the three build kernels on a few thousand rows (first launches load the kernels and
     # allocate the library's scratch), then the timed build
@@ -276,6 +429,18 @@ def run_b200(args):
     codes_all, adj_all = sharded.build_sharded(stages, d_base[rb:re], n, rank, world, dist if world > 1 else None, knn_k, M,
                                                True, timers=Timer)
     idx.check_device_status()
+    # rows computed by other ranks against rows this GPU computes alone from the gathered codes: 8 blocks of 250 rows
+    # spread over all shards
+    sharded_equals_single = None
+    if world > 1 and rank == 0:
+        sharded_equals_single = True
+        blk = min(250, n)
+        for b in range(8):
+            r0 = min(n - blk, (n // 8) * b + (n // 16))
+            cand_s = stages.knn(codes_all, knn_k, r0, r0 + blk)
+            adj_s = stages.select(codes_all, cand_s, knn_k, r0, r0 + blk, M, True)
+            sharded_equals_single &= bool(torch.equal(adj_s, adj_all[r0:r0 + blk]))
+        torch.cuda.synchronize()
     idx.install_dev(d_base.data_ptr(), codes_all.data_ptr(), adj_all.data_ptr(), n)
     for kind in ("encode", "knn_graph", "select_neighbors"):
         idx.kernel_time(kind)  # reset the per-kernel records
@@ -317,23 +482,27 @@ def run_b200(args):
         idx.kernel_time("search")
         idx.kernel_time("encode")
         l0 = idx.launch_count()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
         barrier()
-        e0.record()
-        for _ in range(args.steps):
+        ev[0].record()
+        for i in range(args.steps):
             step_resident()
-        e1.record()
+            ev[i + 1].record()
         barrier()
-        total = max_over_ranks(e0.elapsed_time(e1))
+        total = max_over_ranks(ev[0].elapsed_time(ev[-1]))
+        per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
         s_ms, s_n = idx.kernel_time("search")
         q_ms, _ = idx.kernel_time("encode")
-        return total, idx.launch_count() - l0, s_ms, s_n, q_ms
+        return total, idx.launch_count() - l0, s_ms, s_n, q_ms, per_step
 
-    ms_total, launches, search_ms, search_launches, qenc_ms = timed_region()
-    remeasured = False
+    ms_total, launches, search_ms, search_launches, qenc_ms, per_step_ms = timed_region()
+    remeasured = None
     if ms_total / args.steps > 2.0 * max_over_ranks(min(warm_ms)):
-        # a timed step far slower than every warm-up step is interference, not the kernel: take it once more
-        remeasured = True
-        ms_total, launches, search_ms, search_launches, qenc_ms = timed_region()
+        # a timed region far slower than every warm-up step is interference, not the kernel: it is taken once more
+        # and BOTH totals are reported
+        first_total = ms_total
+        ms_total, launches, search_ms, search_launches, qenc_ms, per_step_ms = timed_region()
+        remeasured = {"first_ms_total": first_total, "second_ms_total": ms_total, "reported": "second"}
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms_total / args.steps
     value = world * nq / (ms_per_step * 1e-3)
@@ -363,9 +532,12 @@ def run_b200(args):
     for _ in range(max(3, args.warmup)):
         step_e2e()
     barrier()
+    e2e_steps = []
     e0.record()
     for _ in range(args.steps):
-        step_e2e()
+        t0 = time.perf_counter()
+        step_e2e()  # returns with the results in host memory: the host clock sees the whole step
+        e2e_steps.append((time.perf_counter() - t0) * 1e3)
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
@@ -386,11 +558,15 @@ def run_b200(args):
     search_ms_per_launch = search_ms / max(1, search_launches)
     achieved = bytes_per_query * nq / (search_ms_per_launch * 1e-3) / 1e9
     # the library takes the two-warp kernel when the query table fits shared memory and M <= 32
-    team = args.search_kernel != 1 and K * idx.padded_dim * 4 <= 32 * 1024 and M <= 32
+    team = args.search_kernel != 1 and (K * idx.padded_dim * 4 <= 32 * 1024 or K <= 32) and M <= 32
     dram_per_query = NCU_SEARCH_DRAM_BYTES_PER_QUERY if team else NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP
+    traffic = dram_per_query * nq if w["name"] == "C2" else None
     roofline = {"kernel": "search_team_kernel" if team else "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": "of " + peak_kind,
-                "traffic": dram_per_query * nq if w["name"] == "C2" else None,
+                "traffic": traffic,
+                # the same fraction on the DRAM bytes ncu measured instead of the algorithmic bytes: what the kernel
+                # really asks of HBM (it is bound by dependent latencies, not by bandwidth)
+                "frac_measured_dram": (traffic / (search_ms_per_launch * 1e-3) / 1e9 / peak) if traffic else None,
                 "traffic_note": "bytes per launch, scaled by queries from the ncu capture of C2 at 1/4 size",
                 "ms_per_launch": search_ms_per_launch, "algorithmic_bytes_per_query": bytes_per_query,
                 "expansions_per_query": exp_mean, "distance_evals_per_query": evals_mean,
@@ -409,23 +585,44 @@ def run_b200(args):
         "scaling": "strong",
     }
 
+    sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
+    lanes = idx_sm_count * 128 * sm_mhz * 1e6  # fp32 add lanes of the GPU per second at the sampled clock
+    roofline_build = {
+        "encode": {"bound": "fp32-add pipe", "achieved": build["encode_fp32_addsub_per_s"], "peak": lanes, "unit": "add/s",
+                   "frac": build["encode_fp32_addsub_per_s"] / lanes,
+                   "note": "K*3*P*log2(P) butterflies per vector over the measured stage time; peak = SMs x 128 lanes x sampled SM clock"},
+        "knn_graph": None, "select_neighbors": None}
+    if K == 32 and cb == 1:
+        # bit-sliced kernel: 330 integer instructions per (row, 32 candidates) = 10.3 per pair on the ALU pipe, which
+        # issues 64 lanes per SM and clock
+        alu = idx_sm_count * 64 * sm_mhz * 1e6
+        roofline_build["knn_graph"] = {"bound": "integer ALU pipe", "achieved": build["knn_pairs_per_s"] * 330.0 / 32.0, "peak": alu,
+                                       "unit": "instr/s", "frac": build["knn_pairs_per_s"] * 330.0 / 32.0 / alu,
+                                       "note": "10.3 integer instructions per pair (kernel source count); ncu sm__pipe_alu_cycles_active "
+                                               "67.5 % on C2 at 1/4 size (profiles/knn_sliced_kernel_c2_quarter.md)"}
+    sel_bytes = n * (knn_k * 4 + knn_k * code_row + M * 4.0)
+    roofline_build["select_neighbors"] = {"bound": "hbm gather", "achieved": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9, "peak": peak,
+                                          "unit": "GB/s", "frac": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9 / peak,
+                                          "note": "k*4 + k*code_row gathered + M*4 written per node; gather-latency bound, 1 % of the build"}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "ms_per_step": ms_per_step, "ms_per_step_stats": step_stats(per_step_ms),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "files" if args.fvecs else "synthetic",
-            "config": {"workload": w["name"], "n_base": n, "dim": dim, "queries_per_rank": nq, "k": k, "ef": ef,
-                       "rerank_k": rerank_k, "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry, "k_entry": w.get("k_entry", 4), "knn_k": knn_k,
-                       "l2": "index (vectors+codes+adjacency = %.0f MB) larger than L2" % (n * (dim * 4 + code_row + M * 4) / 1e6)},
+            "config": b200_config(args, w, n, dim, nq, n_entry, knn_k),
             "recall_at_10": recall, "recall_target_met": bool(recall >= 0.9),
             "e2e": {"value": e2e_value, "unit": "queries/s", "h2d_bytes_per_step": int(world * nq * dim * 4),
-                    "d2h_bytes_per_step": int(world * nq * k * 8), "ms_per_step": e2e_ms, "same_ids_as_resident": same},
+                    "d2h_bytes_per_step": int(world * nq * k * 8), "ms_per_step": e2e_ms,
+                    "ms_per_step_stats": step_stats(e2e_steps), "same_ids_as_resident": same},
             "gpu_launches": int(launches), "remeasured": remeasured, "clocks": clocks, "roofline": roofline, "build": build,
+            "roofline_build": roofline_build,
         }
+        if world > 1:
+            line["sharded_equals_single"] = sharded_equals_single
         if world == 1 and not args.no_cpu_baseline:
-            _, qps, secs, crec, cores, desc = cpu_steps(args, 300, 2, 1)
-            line["cpu_baseline"] = {"value": qps, "unit": "queries/s", "cores": cores, "kind": "port", "sample": desc,
-                                    "recall_at_10": crec}
+            line["cpu_baseline"] = cpu_baseline_object(cpu_steps(args, 2000, 3, 1, build_stages=True))
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

@@ -32,6 +32,9 @@
 #ifdef _OPENMP
 #include <omp.h>
 #endif
+#if defined(CPHNSW_ORACLE_TUNED) && defined(__AVX512F__)
+#include <immintrin.h>
+#endif
 
 namespace {
 
@@ -128,6 +131,30 @@ static size_t g_primary = 0;
 static uint32_t g_shift = 0;
 inline uint32_t code_dist(const void* a, size_t ia, const void* b, size_t ib, size_t K,
                           size_t comp_bytes) {
+#ifdef CPHNSW_ORACLE_TUNED
+    // the tuned build (CPU baseline of the benchmark): byte codes of whole 8-byte words without residual
+    // weighting are compared a word at a time - 32 bytes at a time where the host has AVX-512BW/VL
+    if (comp_bytes == 1 && g_primary == 0 && (K & 7) == 0) {
+        const uint8_t* pa = (const uint8_t*)a + ia * K;
+        const uint8_t* pb = (const uint8_t*)b + ib * K;
+        uint32_t dd = 0;
+        size_t r = 0;
+#if defined(__AVX512BW__) && defined(__AVX512VL__)
+        for (; r + 32 <= K; r += 32)
+            dd += (uint32_t)__builtin_popcount(_mm256_cmpneq_epi8_mask(_mm256_loadu_si256((const __m256i*)(pa + r)),
+                                                                       _mm256_loadu_si256((const __m256i*)(pb + r))));
+#endif
+        for (; r < K; r += 8) {
+            uint64_t x, y;
+            std::memcpy(&x, pa + r, 8);
+            std::memcpy(&y, pb + r, 8);
+            x ^= y;
+            const uint64_t lo = 0x7f7f7f7f7f7f7f7full;
+            dd += (uint32_t)__builtin_popcountll((((x & lo) + lo) | x) & ~lo);  // one flag per differing byte
+        }
+        return dd;
+    }
+#endif
     uint32_t d = 0;
     for (size_t r = 0; r < K; ++r) {
         const uint32_t ne = load_comp(a, comp_bytes, ia * K + r) != load_comp(b, comp_bytes, ib * K + r);
@@ -145,6 +172,30 @@ inline uint32_t code_dist(const void* a, size_t ia, const void* b, size_t ib, si
 // the block sums are added in sequence.  Within 1e-5 relative of the sequential sum.
 inline float asym_dist(const float* table /*[K][P]*/, size_t K, size_t P, const void* codes,
                        size_t comp_bytes, size_t id) {
+#if defined(CPHNSW_ORACLE_TUNED) && defined(__AVX512F__) && defined(__AVX512BW__) && defined(__AVX512VL__)
+    // tuned build, 32 one-byte components: two 16-lane gathers and the same add tree (term j with j+16 is the sum
+    // of the two vectors, then upper half onto lower half down to one lane), so the float is the plain build's
+    if (K == 32 && comp_bytes == 1) {
+        const __m256i c = _mm256_loadu_si256((const __m256i*)((const uint8_t*)codes + id * 32));
+        const __m512i lo = _mm512_cvtepu8_epi32(_mm256_castsi256_si128(c));
+        const __m512i hi = _mm512_cvtepu8_epi32(_mm256_extracti128_si256(c, 1));
+        const __m512i lane = _mm512_set_epi32(15, 14, 13, 12, 11, 10, 9, 8, 7, 6, 5, 4, 3, 2, 1, 0);
+        const __m512i p = _mm512_set1_epi32((int)P);
+        const __m512i i0 = _mm512_add_epi32(_mm512_mullo_epi32(lane, p), _mm512_srli_epi32(lo, 1));
+        const __m512i i1 = _mm512_add_epi32(_mm512_mullo_epi32(_mm512_add_epi32(lane, _mm512_set1_epi32(16)), p),
+                                            _mm512_srli_epi32(hi, 1));
+        __m512i v0 = _mm512_castps_si512(_mm512_i32gather_ps(i0, table, 4));
+        __m512i v1 = _mm512_castps_si512(_mm512_i32gather_ps(i1, table, 4));
+        v0 = _mm512_xor_si512(v0, _mm512_slli_epi32(lo, 31));  // odd component: negated
+        v1 = _mm512_xor_si512(v1, _mm512_slli_epi32(hi, 31));
+        const __m512 s16 = _mm512_add_ps(_mm512_castsi512_ps(v0), _mm512_castsi512_ps(v1));
+        const __m256 s8 = _mm256_add_ps(_mm512_castps512_ps256(s16), _mm512_extractf32x8_ps(s16, 1));
+        const __m128 s4 = _mm_add_ps(_mm256_castps256_ps128(s8), _mm256_extractf128_ps(s8, 1));
+        const __m128 s2 = _mm_add_ps(s4, _mm_movehl_ps(s4, s4));
+        const __m128 s1 = _mm_add_ss(s2, _mm_shuffle_ps(s2, s2, 1));
+        return -(0.0f + _mm_cvtss_f32(s1));
+    }
+#endif
     float score = 0.0f;
     for (size_t c0 = 0; c0 < K; c0 += 32) {
         float t[32];
@@ -313,6 +364,95 @@ template <class DistFn>
 int walk_all(uint64_t nq, uint64_t n, const uint32_t* adj, uint64_t M, const uint32_t* entry_ids, uint64_t n_entry,
              uint64_t n_seed, uint64_t ef, uint64_t k, uint32_t* out_ids, float* out_dist, uint32_t* stats,
              DistFn dist_of) {
+#ifdef CPHNSW_ORACLE_TUNED
+    // Tuned build: the same walk with W as one sorted array (binary search + shift on admission, an
+    // "expanded" flag per member, a cursor on the first unexpanded member) and an epoch-stamped visited
+    // array, instead of two std::set.  Same total order, so the same results; the plain build is the checker.
+#pragma omp parallel
+    {
+        std::vector<uint32_t> stamp(n, 0u);
+        uint32_t epoch = 0;
+        struct Member {
+            float d;
+            uint32_t id;
+            bool expanded;
+        };
+        std::vector<Member> W;
+        W.reserve(ef + 1);
+#pragma omp for schedule(dynamic, 4)
+        for (int64_t q = 0; q < (int64_t)nq; ++q) {
+            if (++epoch == 0) {
+                std::fill(stamp.begin(), stamp.end(), 0u);
+                epoch = 1;
+            }
+            W.clear();
+            size_t cur = 0;  // no unexpanded member before this position
+            uint32_t expansions = 0, evals = 0;
+            auto offer = [&](uint32_t id) {
+                if (id == kInvalid || id >= n || stamp[id] == epoch) return;
+                stamp[id] = epoch;
+                const float d = dist_of((size_t)q, id);
+                ++evals;
+                if (W.size() == ef && !(Cand{d, id} < Cand{W.back().d, W.back().id})) return;
+                size_t lo = 0, hi = W.size();
+                while (lo < hi) {
+                    const size_t mid = (lo + hi) / 2;
+                    if (Cand{W[mid].d, W[mid].id} < Cand{d, id}) lo = mid + 1;
+                    else hi = mid;
+                }
+                if (W.size() == ef) W.pop_back();
+                W.insert(W.begin() + lo, Member{d, id, false});
+                if (lo < cur) cur = lo;
+            };
+            if (n_seed >= n_entry) {
+                for (size_t e = 0; e < n_entry; ++e) offer(entry_ids[e]);
+            } else {
+                std::vector<Cand> scan;
+                scan.reserve(n_entry);
+                for (size_t e = 0; e < n_entry; ++e) {
+                    const uint32_t id = entry_ids[e];
+                    if (id == kInvalid || id >= n) continue;
+                    scan.push_back({dist_of((size_t)q, id), id});
+                    ++evals;
+                }
+                // the n_seed best without sorting everything; a full sort only if repeated ids ate the margin
+                size_t keep = std::min<size_t>(scan.size(), 2 * n_seed + 8);
+                std::partial_sort(scan.begin(), scan.begin() + keep, scan.end());
+                std::vector<Cand> head(scan.begin(), scan.begin() + keep);
+                head.erase(std::unique(head.begin(), head.end()), head.end());
+                if (head.size() < n_seed && keep < scan.size()) {
+                    std::sort(scan.begin(), scan.end());
+                    scan.erase(std::unique(scan.begin(), scan.end()), scan.end());
+                } else {
+                    scan.swap(head);
+                }
+                for (size_t e = 0; e < scan.size() && e < n_seed; ++e) offer(scan[e].second);
+            }
+            for (;;) {
+                while (cur < W.size() && W[cur].expanded) ++cur;
+                if (cur == W.size()) break;
+                W[cur].expanded = true;
+                ++expansions;
+                const uint32_t* row = adj + (size_t)W[cur].id * M;
+                for (size_t t = 0; t < M; ++t) offer(row[t]);
+            }
+            const size_t o = (size_t)q * k;
+            size_t t = 0;
+            for (; t < k && t < W.size(); ++t) {
+                out_ids[o + t] = W[t].id;
+                out_dist[o + t] = W[t].d;
+            }
+            for (; t < k; ++t) {
+                out_ids[o + t] = kInvalid;
+                out_dist[o + t] = INFINITY;
+            }
+            if (stats) {
+                stats[2 * q] = expansions;
+                stats[2 * q + 1] = evals;
+            }
+        }
+    }
+#else
 #pragma omp parallel
     {
         std::vector<uint8_t> visited(n);
@@ -377,6 +517,7 @@ int walk_all(uint64_t nq, uint64_t n, const uint32_t* adj, uint64_t M, const uin
             touched.clear();
         }
     }
+#endif
     return 0;
 }
 }  // namespace
@@ -711,6 +852,15 @@ int orc_set_threads(int threads) {
 #else
     (void)threads;
     return 1;
+#endif
+}
+
+// 1 when this library is the tuned build (the benchmark's CPU baseline), 0 for the plain checker.
+int orc_is_tuned() {
+#ifdef CPHNSW_ORACLE_TUNED
+    return 1;
+#else
+    return 0;
 #endif
 }
 

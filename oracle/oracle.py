@@ -43,6 +43,34 @@ def lib():
     return _lib
 
 
+def use_tuned_build():
+    """Switches this module to the tuned build of the same source (`make -C oracle native`: -O3 -march=native,
+    AVX-512 gather score and byte compare where the host has them, sorted-array beam) - the benchmark's CPU
+    baseline.  Built on the host it runs on; returns False (and keeps the plain build) when that fails."""
+    global _lib
+    import subprocess
+    path = os.path.join(_HERE, "_native", "liboracle_tuned.so")
+    try:
+        subprocess.run(["make", "-C", _HERE, "native"], check=True, capture_output=True, timeout=300)
+        tuned = C.CDLL(path)
+        if tuned.orc_is_tuned() != 1:
+            return False
+    except Exception:
+        return False
+    _lib = tuned
+    return True
+
+
+def use_plain_build():
+    global _lib
+    _lib = None
+    lib()
+
+
+def is_tuned():
+    return bool(lib().orc_is_tuned())
+
+
 def num_threads():
     return lib().orc_num_threads()
 

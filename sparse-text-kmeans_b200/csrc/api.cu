@@ -619,6 +619,7 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         h->search_kernel = int(v);
         return 0;
     }
+    if (s == "search_table_smem") { h->search_table_smem = v != 0.0; return 0; }
     if (s == "binary_codes") {
         if (v != 0 && v != 1) { set_error("binary_codes must be 0 or 1"); return CPHNSW_B200_E_INVALID; }
         if (h->n && int(v) != h->binary_codes) { set_error("binary_codes cannot change once vectors have been added"); return CPHNSW_B200_E_STATE; }
@@ -698,6 +699,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "profile") *v = h->profile;
     else if (s == "knn_kernel") *v = h->knn_kernel;
     else if (s == "search_kernel") *v = h->search_kernel;
+    else if (s == "search_table_smem") *v = h->search_table_smem;
     else if (s == "build_seed") *v = h->build_seed;
     else if (s == "first_wait_polls") *v = h->first_wait_polls;
     else if (s == "rank_prune") *v = h->rank_prune;

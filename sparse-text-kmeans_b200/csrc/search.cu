@@ -401,7 +401,7 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
     c.cap = 32;
     while (c.cap < beam || c.cap < h->k_entry) c.cap <<= 1;
     const size_t table_bytes = size_t(h->K) * h->P * 4;
-    c.table_smem = !sym && table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
+    c.table_smem = !sym && h->search_table_smem && table_bytes <= 32 * 1024 && (table_bytes % 16) == 0;
     const size_t qvec = (size_t(h->dim) + 3) & ~size_t(3);
     // under the symmetric metric the query code follows the query vector
     size_t dim_pad = qvec + (sym ? ((size_t(h->K) * h->comp_bytes + 15) / 16) * 4 : 0);
