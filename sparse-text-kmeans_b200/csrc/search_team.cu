@@ -212,10 +212,10 @@ __device__ __forceinline__ void tier_admit_lanes(TierList& T, uint32_t m, bool m
 
 // TSM: the query table is copied to shared memory (a compile-time fact, so that its reads stay
 // shared-memory loads); otherwise it is read in place.
-// Without the table in shared memory a team needs little of it, so the register file decides how many teams an
-// SM holds: that instantiation is held to 64 registers (15 teams instead of 11).
+// No register cap: holding the kernel to 64 registers (15 teams per SM instead of 11 when the table is read in
+// place) spills inside the walk and was measured slower on every configuration.
 template <bool U16, bool TSM>
-__global__ void __launch_bounds__(TSM ? 640 : 960) search_team_kernel(SearchArgs a) {
+__global__ void search_team_kernel(SearchArgs a) {
     extern __shared__ __align__(16) unsigned char team_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int team = warp >> 1, role = warp & 1, teams = blockDim.x >> 6;
