@@ -95,41 +95,47 @@ class CPHNSWIndex {
 public:
     using Code = CPCode<ComponentT, K>;
 
+    // `device` >= 0 binds the index to that GPU; ALL_GPUS (the default) spreads it over every usable GPU of the box:
+    // one replica per device, the bulk build sharded by row block, batched searches by query block, single-query
+    // calls going round the replicas (cphnsw_b200_sharded_* in cphnsw_b200.h).  On a one-GPU box both are the same.
+    static constexpr int ALL_GPUS = -1;
     CPHNSWIndex(size_t dim, size_t M = 32, size_t ef_construction = 200, uint64_t seed = 42,
-                int fht_convention = CPHNSW_B200_FHT_AVX512, int device = 0) {
-        check(cphnsw_b200_create(dim, uint32_t(K), uint32_t(sizeof(ComponentT)), uint32_t(M), uint32_t(ef_construction), seed,
-                                 fht_convention, device, &h_));
+                int fht_convention = CPHNSW_B200_FHT_AVX512, int device = ALL_GPUS) {
+        create(dim, M, ef_construction, seed, fht_convention, device);
     }
-    explicit CPHNSWIndex(const CPHNSWParams& p, int fht_convention = CPHNSW_B200_FHT_AVX512, int device = 0) {
+    explicit CPHNSWIndex(const CPHNSWParams& p, int fht_convention = CPHNSW_B200_FHT_AVX512, int device = ALL_GPUS) {
         if (p.k != K) throw std::invalid_argument("CPHNSWParams: k must equal the index's code width K");
-        check(cphnsw_b200_create(p.dim, uint32_t(K), uint32_t(sizeof(ComponentT)), uint32_t(p.M), uint32_t(p.ef_construction),
-                                 p.seed, fht_convention, device, &h_));
+        create(p.dim, p.M, p.ef_construction, p.seed, fht_convention, device);
         set_param("keep_pruned", p.keep_pruned ? 1.0 : 0.0);
         set_param("k_entry", double(p.k_entry));
         set_param("rank_pruning_alpha", double(p.rank_pruning_alpha));
     }
-    ~CPHNSWIndex() { cphnsw_b200_destroy(h_); }
+    ~CPHNSWIndex() { cphnsw_b200_sharded_destroy(s_); }
     CPHNSWIndex(const CPHNSWIndex&) = delete;
     CPHNSWIndex& operator=(const CPHNSWIndex&) = delete;
-    CPHNSWIndex(CPHNSWIndex&& o) noexcept : h_(o.h_) { o.h_ = nullptr; }
+    CPHNSWIndex(CPHNSWIndex&& o) noexcept : s_(o.s_), h_(o.h_) { o.s_ = nullptr, o.h_ = nullptr; }
 
     // ---- index file (the reference has no save/load) ---------------------------------------------
     void save(const std::string& path) const { check(cphnsw_b200_save(h_, path.c_str())); }
-    static CPHNSWIndex load(const std::string& path, int device = 0) {
-        cphnsw_b200_index* h = nullptr;
-        check(cphnsw_b200_load(path.c_str(), device, &h));
+    static CPHNSWIndex load(const std::string& path, int device = ALL_GPUS) {
+        cphnsw_b200_sharded* s = nullptr;
+        check(cphnsw_b200_sharded_load(path.c_str(), device < 0 ? 0 : 1, device < 0 ? nullptr : &device, &s));
+        cphnsw_b200_index* h = cphnsw_b200_sharded_replica(s, 0);
         double k = 0, cb = 0;
         cphnsw_b200_get_param(h, "K", &k);
         cphnsw_b200_get_param(h, "component_bytes", &cb);
         if (size_t(k) != K || size_t(cb) != sizeof(ComponentT)) {
-            cphnsw_b200_destroy(h);
+            cphnsw_b200_sharded_destroy(s);
             throw std::invalid_argument("index file holds another code type than this CPHNSWIndex<ComponentT,K>");
         }
-        return CPHNSWIndex(h, Adopt{});
+        return CPHNSWIndex(s, Adopt{});
     }
 
+    // replica 0: every read-only call and every stage call of this class goes to it
     cphnsw_b200_index* handle() const { return h_; }
-    void set_param(const char* name, double v) { check(cphnsw_b200_set_param(h_, name, v)); }
+    cphnsw_b200_sharded* sharded() const { return s_; }
+    int gpus() const { return cphnsw_b200_sharded_gpus(s_); }
+    void set_param(const char* name, double v) { check(cphnsw_b200_sharded_set_param(s_, name, v)); }
     size_t dim() const { return cphnsw_b200_dim(h_); }
     size_t padded_dim() const { return cphnsw_b200_padded_dim(h_); }
     size_t size() const { return cphnsw_b200_size(h_); }
@@ -142,8 +148,8 @@ public:
         add_batch(vec, 1);
         return id;
     }
-    void add_batch(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch(h_, vecs, n)); }
-    void add_batch_parallel(const Float* vecs, size_t n) { check(cphnsw_b200_add_batch_parallel(h_, vecs, n)); }
+    void add_batch(const Float* vecs, size_t n) { check(cphnsw_b200_sharded_add_batch(s_, vecs, n)); }
+    void add_batch_parallel(const Float* vecs, size_t n) { check(cphnsw_b200_sharded_add_batch_parallel(s_, vecs, n)); }
     // build_with_gpu_knn (evaluation/test_gpu_build.cpp:168-174): bulk build from a k-candidate kNN graph
     // (CP-code distance).  prune = true prunes it by rank with the detour threshold alpha, the CAGRA graph
     // optimisation the parameter is documented for (types.hpp:399-400; rule in cphnsw_b200.h at
@@ -158,12 +164,12 @@ public:
         double old[4] = {0, 1, 0, 1.1};
         for (int i = 0; i < 4; ++i) check(cphnsw_b200_get_param(h_, names[i], &old[i]));
         int rc = 0;
-        for (int i = 0; i < 4 && rc == 0; ++i) rc = cphnsw_b200_set_param(h_, names[i], want[i]);
-        if (rc == 0 && !prune) rc = cphnsw_b200_set_param(h_, "prune", 0.0);
-        if (rc == 0) rc = cphnsw_b200_add_batch_parallel(h_, vecs, n);
+        for (int i = 0; i < 4 && rc == 0; ++i) rc = cphnsw_b200_sharded_set_param(s_, names[i], want[i]);
+        if (rc == 0 && !prune) rc = cphnsw_b200_sharded_set_param(s_, "prune", 0.0);
+        if (rc == 0) rc = cphnsw_b200_sharded_add_batch_parallel(s_, vecs, n);
         // last_error() belongs to the failing call: restore the tunables only after reading it
         std::string msg = rc ? cphnsw_b200_last_error() : "";
-        for (int i = 0; i < 4; ++i) cphnsw_b200_set_param(h_, names[i], old[i]);
+        for (int i = 0; i < 4; ++i) cphnsw_b200_sharded_set_param(s_, names[i], old[i]);
         if (rc) fail(rc, msg);
     }
 
@@ -177,15 +183,15 @@ public:
     std::vector<std::vector<SearchResult>> search_batch(const Float* q, size_t nq, size_t k, size_t ef) const {
         std::vector<uint32_t> ids(nq * k);
         std::vector<float> d(nq * k);
-        check(cphnsw_b200_search_batch(h_, q, nq, uint32_t(k), uint32_t(ef), ids.data(), d.data(), nullptr));
+        check(cphnsw_b200_sharded_search(s_, 0, q, nq, uint32_t(k), uint32_t(ef), 0, ids.data(), d.data(), nullptr));
         return unpack(ids, d, nq, k);
     }
     std::vector<std::vector<SearchResult>> search_and_rerank_batch(const Float* q, size_t nq, size_t k, size_t ef,
                                                                    size_t rerank_k) const {
         std::vector<uint32_t> ids(nq * k);
         std::vector<float> d(nq * k);
-        check(cphnsw_b200_search_and_rerank_batch(h_, q, nq, uint32_t(k), uint32_t(ef), uint32_t(rerank_k), ids.data(),
-                                                  d.data(), nullptr));
+        check(cphnsw_b200_sharded_search(s_, 1, q, nq, uint32_t(k), uint32_t(ef), uint32_t(rerank_k), ids.data(), d.data(),
+                                         nullptr));
         return unpack(ids, d, nq, k);
     }
 
@@ -196,8 +202,8 @@ public:
                                                                    size_t num_probes) const {
         std::vector<uint32_t> ids(nq * k);
         std::vector<float> d(nq * k);
-        check(cphnsw_b200_search_multiprobe_batch(h_, q, nq, uint32_t(k), uint32_t(ef), uint32_t(num_probes), ids.data(),
-                                                  d.data()));
+        check(cphnsw_b200_sharded_search(s_, 2, q, nq, uint32_t(k), uint32_t(ef), uint32_t(num_probes), ids.data(), d.data(),
+                                         nullptr));
         return unpack(ids, d, nq, k);
     }
 
@@ -209,7 +215,7 @@ public:
     std::vector<SearchResult> brute_force_search(const Float* q, size_t k) const {
         std::vector<uint32_t> ids(k);
         std::vector<float> d(k);
-        check(cphnsw_b200_brute_force_search_batch(h_, q, 1, uint32_t(k), ids.data(), d.data()));
+        check(cphnsw_b200_sharded_search(s_, 3, q, 1, uint32_t(k), uint32_t(k), 0, ids.data(), d.data(), nullptr));
         return unpack(ids, d, 1, k)[0];
     }
     size_t verify_connectivity() const {
@@ -218,7 +224,9 @@ public:
         return size_t(r);
     }
     Calibration calibrate(size_t num_samples = 1000, uint64_t seed = 42) {
-        check(cphnsw_b200_calibrate(h_, num_samples, seed, nullptr, nullptr, nullptr));
+        // the fit is kept in the handle: every replica computes it (same samples, same result)
+        for (int g = 0; g < gpus(); ++g)
+            check(cphnsw_b200_calibrate(cphnsw_b200_sharded_replica(s_, g), num_samples, seed, nullptr, nullptr, nullptr));
         return get_calibration();
     }
     Calibration get_calibration() const {
@@ -235,7 +243,7 @@ public:
     std::vector<SearchResult> search_calibrated_and_rerank(const Float* q, size_t k, size_t ef, size_t rerank_k) const {
         std::vector<uint32_t> ids(k);
         std::vector<float> d(k);
-        check(cphnsw_b200_search_calibrated_batch(h_, q, 1, uint32_t(k), uint32_t(ef), uint32_t(rerank_k), ids.data(), d.data()));
+        check(cphnsw_b200_sharded_search(s_, 4, q, 1, uint32_t(k), uint32_t(ef), uint32_t(rerank_k), ids.data(), d.data(), nullptr));
         return unpack(ids, d, 1, k)[0];
     }
 
@@ -270,8 +278,14 @@ public:
 
 private:
     struct Adopt {};
-    CPHNSWIndex(cphnsw_b200_index* h, Adopt) : h_(h) {}
-    cphnsw_b200_index* h_ = nullptr;
+    CPHNSWIndex(cphnsw_b200_sharded* s, Adopt) : s_(s), h_(cphnsw_b200_sharded_replica(s, 0)) {}
+    void create(size_t dim, size_t M, size_t ef_construction, uint64_t seed, int fht_convention, int device) {
+        check(cphnsw_b200_sharded_create(dim, uint32_t(K), uint32_t(sizeof(ComponentT)), uint32_t(M), uint32_t(ef_construction),
+                                         seed, fht_convention, 0, device < 0 ? 0 : 1, device < 0 ? nullptr : &device, &s_));
+        h_ = cphnsw_b200_sharded_replica(s_, 0);
+    }
+    cphnsw_b200_sharded* s_ = nullptr;  // owns the replicas
+    cphnsw_b200_index* h_ = nullptr;    // replica 0
 
     static void fail(int rc, const std::string& msg) {
         if (rc == CPHNSW_B200_E_INVALID) throw std::invalid_argument(msg);

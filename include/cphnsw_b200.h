@@ -316,6 +316,45 @@ int cphnsw_b200_search_dev(cphnsw_b200_index* h, const float* d_q, uint64_t nq, 
 /* exact_search over d_base float[n][dim] (device) for d_q float[nq][dim]; outputs device uint32[nq][k] / float[nq][k]. */
 int cphnsw_b200_exact_search_dev(cphnsw_b200_index* h, const float* d_base, uint64_t n, const float* d_q,
                                  uint64_t nq, uint32_t k, uint32_t* d_ids, float* d_dists, void* stream);
+/* ---- one index over several GPUs of one box -------------------------------------------------------------
+ * The reference is single-device (BuildParams::gpu_device is declared and never read, include/cphnsw/api/config.hpp:55-56);
+ * this is the multi-GPU form of the same calls: one process, one replica of the index per device.
+ * add_batch_parallel shards the rows into contiguous blocks: every device encodes its block, the codes are
+ * all-gathered with NCCL, every device computes the kNN rows and the pruned rows of its block against all codes, the
+ * adjacency and vector blocks are all-gathered and every device installs the complete index - the adjacency is the
+ * one a single device builds, bit for bit.  search splits the query batch across the replicas (batches smaller than
+ * 32 queries per device go to one replica whole, successive calls going round the replicas, so that single-query
+ * calls from many host threads use all devices).  n_gpus = 0 takes every usable device; devices = NULL means
+ * ordinals 0..n_gpus-1.  NCCL (libnccl.so.2) is loaded at run time, and only when n_gpus > 1.
+ * Thread safety is that of the plain handle: searches from any number of threads, builds exclude one another. */
+typedef struct cphnsw_b200_sharded cphnsw_b200_sharded;
+int cphnsw_b200_sharded_create(uint64_t dim, uint32_t K, uint32_t component_bytes, uint32_t M, uint32_t ef_construction,
+                               uint64_t seed, int fht_convention, int binary_codes, int n_gpus, const int* devices,
+                               cphnsw_b200_sharded** out);
+/* a saved index (cphnsw_b200_save) loaded onto every device */
+int cphnsw_b200_sharded_load(const char* path, int n_gpus, const int* devices, cphnsw_b200_sharded** out);
+int cphnsw_b200_sharded_destroy(cphnsw_b200_sharded* s);
+int cphnsw_b200_sharded_gpus(const cphnsw_b200_sharded* s);
+uint64_t cphnsw_b200_sharded_size(const cphnsw_b200_sharded* s);
+/* The replica on the g-th device: an ordinary handle, owned by the sharded index.  Read-only calls (get_codes,
+ * get_adjacency, save, verify_connectivity, the stage calls) may use any replica; calls that change a handle must be
+ * made on every replica alike (set_param and the add calls below do that). */
+cphnsw_b200_index* cphnsw_b200_sharded_replica(const cphnsw_b200_sharded* s, int g);
+int cphnsw_b200_sharded_set_param(cphnsw_b200_sharded* s, const char* name, double value);
+/* CPHNSWIndex::add_batch_parallel over all devices (an index that already holds nodes, a seeded build or fewer than
+ * 64 rows per device: every replica runs the whole call instead) and add_batch (every replica inserts the same rows). */
+int cphnsw_b200_sharded_add_batch_parallel(cphnsw_b200_sharded* s, const float* x, uint64_t n);
+int cphnsw_b200_sharded_add_batch(cphnsw_b200_sharded* s, const float* x, uint64_t n);
+/* The batched searches over all replicas.  mode: 0 search_batch, 1 search_and_rerank_batch (arg = rerank_k),
+ * 2 search_multiprobe_batch (arg = num_probes), 3 brute_force_search_batch, 4 search_calibrated_batch (arg = rerank_k);
+ * arguments and outputs as in the call of that name (stats_out: modes 0 and 1, else NULL). */
+int cphnsw_b200_sharded_search(cphnsw_b200_sharded* s, int mode, const float* q, uint64_t nq, uint32_t k, uint32_t ef,
+                               uint32_t arg, uint32_t* ids_out, float* dists_out, uint32_t* stats_out);
+/* Host-clock milliseconds of the stages of the last sharded build: encode (with the upload), all-gather of codes,
+ * kNN rows, pruning, all-gather of adjacency and vectors, installation.  ms_out double[CPHNSW_B200_SHARDED_STAGES]. */
+#define CPHNSW_B200_SHARDED_STAGES 6
+int cphnsw_b200_sharded_stage_times(const cphnsw_b200_sharded* s, double* ms_out);
+
 /* Code distance for callers that cannot allocate device memory.  No counterpart in the reference.
  *
  * Some hosts of this library run under a fixed memory plan: a serving process whose device memory

@@ -40,7 +40,10 @@ EXPORTS = [
     "cphnsw_b200_create_binary", "cphnsw_b200_set_exact_base", "cphnsw_b200_exact_search_batch",
     "cphnsw_b200_rerank_batch", "cphnsw_b200_exact_search_dev", "cphnsw_b200_rank_prune",
     "cphnsw_b200_rank_reorder_dev", "cphnsw_b200_rank_merge_dev", "cphnsw_b200_install",
-    "cphnsw_b200_search_codes_batch", "cphnsw_b200_get_code",
+    "cphnsw_b200_search_codes_batch", "cphnsw_b200_get_code", "cphnsw_b200_sharded_create", "cphnsw_b200_sharded_load",
+    "cphnsw_b200_sharded_destroy", "cphnsw_b200_sharded_gpus", "cphnsw_b200_sharded_size", "cphnsw_b200_sharded_replica",
+    "cphnsw_b200_sharded_set_param", "cphnsw_b200_sharded_add_batch_parallel", "cphnsw_b200_sharded_add_batch",
+    "cphnsw_b200_sharded_search", "cphnsw_b200_sharded_stage_times",
 ]
 
 
@@ -59,9 +62,12 @@ def load_library():
             raise CPHNSWError("%s not found: run `python sparse-text-kmeans_b200/build.py`" % LIB_PATH)
         lib = C.CDLL(LIB_PATH)
         lib.cphnsw_b200_last_error.restype = C.c_char_p
-        for name in ("cphnsw_b200_dim", "cphnsw_b200_padded_dim", "cphnsw_b200_size", "cphnsw_b200_launch_count"):
+        for name in ("cphnsw_b200_dim", "cphnsw_b200_padded_dim", "cphnsw_b200_size", "cphnsw_b200_launch_count",
+                     "cphnsw_b200_sharded_size"):
             getattr(lib, name).restype = C.c_uint64
             getattr(lib, name).argtypes = [C.c_void_p]
+        lib.cphnsw_b200_sharded_replica.restype = C.c_void_p
+        lib.cphnsw_b200_sharded_replica.argtypes = [C.c_void_p, C.c_int]
         _lib = lib
     return _lib
 
@@ -149,7 +155,8 @@ class CPHNSWIndex:
     def close(self):
         h = getattr(self, "_h", None)
         if h is not None and h.value:
-            self._lib.cphnsw_b200_destroy(h)
+            if not getattr(self, "_borrowed", False):  # a replica of a ShardedIndex belongs to it
+                self._lib.cphnsw_b200_destroy(h)
             h.value = None
 
     def __del__(self):
@@ -494,3 +501,82 @@ class CPHNSWIndex:
 
     def check_device_status(self):
         _check(self._lib.cphnsw_b200_check_device_status(self._h))
+
+
+class ShardedIndex:
+    """One index over several GPUs of one box in one process (``cphnsw_b200_sharded_*``): the bulk build
+    sharded by row block with NCCL all-gathers in between, batched searches by query block, one replica
+    per device.  ``n_gpus = 0`` takes every usable device."""
+
+    SEARCH, RERANK, MULTIPROBE, BRUTE_FORCE, CALIBRATED = range(5)
+    STAGES = ("encode", "allgather_codes", "knn_graph", "prune", "allgather_adjacency_vectors", "install")
+
+    def __init__(self, dim, M=32, ef_construction=200, K=32, component_bytes=1, seed=42, fht_convention=FHT_AVX512,
+                 n_gpus=0, devices=None, binary=False):
+        self._lib = load_library()
+        self._s = C.c_void_p()
+        dev = None if devices is None else (C.c_int * len(devices))(*devices)
+        _check(self._lib.cphnsw_b200_sharded_create(_u64(dim), _u32(K), _u32(component_bytes), _u32(M), _u32(ef_construction),
+                                                    _u64(seed), C.c_int(fht_convention), C.c_int(int(binary)), C.c_int(n_gpus),
+                                                    dev, C.byref(self._s)))
+        self.dim, self.K, self.M, self.component_bytes = dim, K, M, component_bytes
+
+    def close(self):
+        if getattr(self, "_s", None) is not None and self._s.value:
+            self._lib.cphnsw_b200_sharded_destroy(self._s)
+            self._s = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def gpus(self):
+        return int(self._lib.cphnsw_b200_sharded_gpus(self._s))
+
+    def size(self):
+        return int(self._lib.cphnsw_b200_sharded_size(self._s))
+
+    def replica(self, g=0):
+        """The replica on the g-th device as a (non-owning) CPHNSWIndex."""
+        idx = CPHNSWIndex.__new__(CPHNSWIndex)
+        idx._lib = self._lib
+        idx._h = C.c_void_p(self._lib.cphnsw_b200_sharded_replica(self._s, C.c_int(g)))
+        idx._borrowed = True
+        idx.dim, idx.K, idx.M, idx.component_bytes = self.dim, self.K, self.M, self.component_bytes
+        idx.padded_dim = int(self._lib.cphnsw_b200_padded_dim(idx._h))
+        idx.code_dtype = np.uint8 if self.component_bytes == 1 else np.uint16
+        return idx
+
+    def set_param(self, name, value):
+        _check(self._lib.cphnsw_b200_sharded_set_param(self._s, name.encode(), C.c_double(value)))
+
+    def add_batch_parallel(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        _check(self._lib.cphnsw_b200_sharded_add_batch_parallel(self._s, _p(x), _u64(x.shape[0])))
+
+    def add_batch(self, x):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, self.dim)
+        _check(self._lib.cphnsw_b200_sharded_add_batch(self._s, _p(x), _u64(x.shape[0])))
+
+    def stage_times(self):
+        ms = (C.c_double * len(self.STAGES))()
+        _check(self._lib.cphnsw_b200_sharded_stage_times(self._s, ms))
+        return dict(zip(self.STAGES, [float(v) for v in ms]))
+
+    def search(self, mode, q, k, ef, arg=0, want_stats=False):
+        q = np.ascontiguousarray(q, np.float32).reshape(-1, self.dim)
+        nq = q.shape[0]
+        ids = np.empty((nq, k), np.uint32)
+        dist = np.empty((nq, k), np.float32)
+        stats = np.zeros((nq, 2), np.uint32) if want_stats else None
+        _check(self._lib.cphnsw_b200_sharded_search(self._s, C.c_int(mode), _p(q), _u64(nq), _u32(k), _u32(ef), _u32(arg),
+                                                    _p(ids), _p(dist), _p(stats)))
+        return (ids, dist, stats) if want_stats else (ids, dist)
+
+    def search_and_rerank_batch(self, q, k, ef, rerank_k, want_stats=False):
+        return self.search(self.RERANK, q, k, ef, rerank_k, want_stats)
+
+    def search_batch(self, q, k, ef, want_stats=False):
+        return self.search(self.SEARCH, q, k, ef, 0, want_stats)
