@@ -30,9 +30,9 @@ sys.path.insert(0, os.path.join(ROOT, "sparse-text-kmeans_b200"))
 
 METRIC = "batch-search QPS @ recall@10>=0.9 (search_and_rerank)"
 # DRAM bytes (read + written) per query of search_team_kernel, from the ncu capture summarised in
-# profiles/search_team_kernel_c2_quarter.md (C2 at 1/4 size, 2,500 queries: 1.269 GB + 0.079 GB per launch);
+# profiles/search_team_kernel_c2_quarter.md (C2 at 1/4 size, 2,500 queries: 1.281 GB + 0.080 GB per launch);
 # the traffic per query does not depend on the number of queries, so a launch of nq queries moves nq times this
-NCU_SEARCH_DRAM_BYTES_PER_QUERY = 539e3
+NCU_SEARCH_DRAM_BYTES_PER_QUERY = 544e3
 # the same for the one-warp search_kernel (profiles/search_kernel_c2_quarter.md: 1.215 GB + 0.080 GB per launch)
 NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP = 518e3
 
@@ -53,6 +53,9 @@ def parse_args():
                     help="run on fvecs files (rows are normalised) instead of a synthetic workload")
     ap.add_argument("--search-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="0 = the library's choice, 1 = one warp per query, 2 = two warps per query")
+    ap.add_argument("--single-process", action="store_true",
+                    help="drive all --gpus devices from this one process through the sharded C ABI (cphnsw_b200_sharded_*: "
+                         "NCCL inside the library) instead of one torchrun rank per GPU; host pointers in and out")
     ap.add_argument("--search-table-smem", type=int, default=1, choices=[0, 1],
                     help="0 = the search kernels read the query table in place (global memory) even when it fits shared memory")
     return ap.parse_args()
@@ -629,10 +632,85 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_single_process(args):
+    """All devices from one process through the sharded C ABI: the path a C++ caller of CPHNSWIndex gets.  Inputs and
+    outputs are host buffers, so `value` here IS the end-to-end number (copies inside the timed region); the build
+    stages are the library's own host-clock laps."""
+    import torch
+    import cphnsw_b200 as cp
+    from cphnsw_b200 import sharded, synthetic
+    G = args.gpus
+    w = overrides(synthetic.workload(args.workload, args.scale), args)
+    base, K, cb, M, dim = w["base"], w["K"], w["component_bytes"], w["M"], w["base"].shape[1]
+    n = base.shape[0]
+    # weak scaling like the torchrun arm: every device answers a batch of the rank's size
+    queries = np.concatenate([synthetic.workload(args.workload, args.scale, query_stream=g)["queries"] for g in range(G)])
+    nq = queries.shape[0]
+    k, ef, rerank_k = w["k"], w["ef"], w["rerank_k"]
+    knn_k = w.get("knn_k", min(64, 2 * M))
+    sh = cp.ShardedIndex(dim, M=M, ef_construction=w["ef_construction"], K=K, component_bytes=cb, n_gpus=G)
+    sh.set_param("entry_scan", w["entry_scan"])
+    sh.set_param("k_entry", w.get("k_entry", 4))
+    sh.set_param("knn_k", knn_k)
+    sh.set_param("search_kernel", args.search_kernel)
+    # rehearsal on a slice (kernel loading, NCCL channels), then the timed build
+    warm = cp.ShardedIndex(dim, M=M, ef_construction=w["ef_construction"], K=K, component_bytes=cb, n_gpus=G)
+    warm.add_batch_parallel(base[: min(n, 4096 * G)])
+    warm.close()
+    t0 = time.perf_counter()
+    sh.add_batch_parallel(base)
+    build_s = time.perf_counter() - t0
+    stages = sh.stage_times()
+    h_q = torch.from_numpy(queries).pin_memory()
+    qv = h_q.numpy()
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(max(3, args.warmup)):
+        ids, dist, stats = sh.search_and_rerank_batch(qv, k, ef, rerank_k, want_stats=True)
+    steps = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        ids, dist = sh.search_and_rerank_batch(qv, k, ef, rerank_k)
+        steps.append((time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop()
+    ms = float(np.mean(steps))
+    # recall against the exact top-k (replica 0's exact search; measurement support)
+    n_gt = min(nq, 10_000)
+    gt, _ = sh.replica(0).exact_search_batch(queries[:n_gt], k)
+    recall = sharded.recall_at_k(ids[:n_gt], gt.astype(np.int64), k)
+    # the same build on one device: the sharded adjacency must be that one bit for bit (sampled rows)
+    equal = None
+    if G > 1:
+        rep = sh.replica(0)
+        codes = rep.codes()
+        adj = rep.adjacency()
+        equal = True
+        for b in range(8):
+            r0 = min(n - 250, (n // 8) * b + (n // 16)) if n > 250 else 0
+            r1 = min(n, r0 + 250)
+            cand, _ = rep.knn_graph(codes, knn_k, r0, r1)
+            equal &= bool(np.array_equal(rep.select_neighbors(codes, cand, M, True, r0), adj[r0:r1]))
+    line = {
+        "metric": METRIC, "value": nq / (ms * 1e-3), "unit": "queries/s", "n_gpus": G, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms, "ms_per_step_stats": step_stats(steps), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "mode": "single process, sharded C ABI (host pointers; value is end to end)",
+        "config": b200_config(args, w, n, dim, nq // G, min(w["entry_scan"], n), knn_k),
+        "recall_at_10": recall, "recall_target_met": bool(recall >= 0.9),
+        "e2e": {"value": nq / (ms * 1e-3), "unit": "queries/s", "h2d_bytes_per_step": int(nq * dim * 4), "d2h_bytes_per_step": int(nq * k * 8),
+                "ms_per_step": ms},
+        "gpu_launches": int(sum(sh.replica(g).launch_count() for g in range(G))), "clocks": clocks,
+        "build": {"seconds_from_host_memory": build_s, "stage_ms": stages, "vec_per_s": n / build_s, "scaling": "strong"},
+        "sharded_equals_single": equal,
+    }
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.single_process:
+        run_single_process(args)
     else:
         run_b200(args)
 
