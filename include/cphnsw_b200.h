@@ -296,7 +296,10 @@ int cphnsw_b200_select_neighbors_dev(cphnsw_b200_index* h, const void* d_codes, 
                                      uint64_t row_end, uint32_t M, int keep_pruned, uint32_t* d_adj,
                                      void* stream);
 /* Install a complete index from device buffers (copied, not retained): vectors float[n][dim],
- * codes [n][K], adjacency uint32[n][M].  Used after a sharded build has all-gathered its rows. */
+ * codes [n][K], adjacency uint32[n][M].  Used after a sharded build has all-gathered its rows.
+ * The rows are taken as they are: an id that names no node (>= n) is treated as CPHNSW_B200_INVALID_NODE
+ * by every kernel that reads the adjacency (search, connectivity, the reverse-edge pass of add_batch),
+ * never dereferenced.  The same holds for candidate ids given to select_neighbors and for loaded files. */
 int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const void* d_codes,
                             const uint32_t* d_adj, uint64_t n, void* stream);
 /* The same from host buffers (FlatGraph::add_node + add_neighbor for every node,

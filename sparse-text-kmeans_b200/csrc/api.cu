@@ -550,7 +550,15 @@ static int create_impl(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
         return CPHNSW_B200_E_CUDA;
     }
     CPB_CUDA(cudaSetDevice(device));
-    auto* h = new cphnsw_b200_index();
+    cphnsw_b200_index* h = nullptr;
+    try {
+        h = new cphnsw_b200_index();
+        h->signs.resize(size_t(K) * 3 * P);
+    } catch (const std::exception&) {  // nothing may leave an extern "C" entry point as an exception
+        delete h;
+        set_error("create: out of host memory");
+        return CPHNSW_B200_E_INVALID;
+    }
     h->dim = dim;
     h->P = P;
     h->K = K;
@@ -565,7 +573,6 @@ static int create_impl(uint64_t dim, uint32_t K, uint32_t component_bytes, uint3
     // RotationChain: rotation r is seeded seed + r (include/cphnsw/encoder/rotation.hpp:173-178);
     // each table is drawn layer by layer from mt19937_64 through uniform_int_distribution<int>(0,1)
     // (rotation.hpp:134-144) — the standard library does the draw, as in the reference.
-    h->signs.resize(size_t(K) * 3 * P);
     for (uint32_t r = 0; r < K; ++r) {
         std::mt19937_64 rng(seed + r);
         std::uniform_int_distribution<int> coin(0, 1);
@@ -620,6 +627,7 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         return 0;
     }
     if (s == "search_table_smem") { h->search_table_smem = v != 0.0; return 0; }
+    if (s == "encode_variant") { h->encode_variant = v < 0 ? 0 : (v > 2 ? 2 : int(v)); return 0; }
     if (s == "binary_codes") {
         if (v != 0 && v != 1) { set_error("binary_codes must be 0 or 1"); return CPHNSW_B200_E_INVALID; }
         if (h->n && int(v) != h->binary_codes) { set_error("binary_codes cannot change once vectors have been added"); return CPHNSW_B200_E_STATE; }
@@ -1054,6 +1062,24 @@ int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
         return CPHNSW_B200_E_INVALID;
     }
     if (hd.n >= 0x80000000ull) { set_error("load: corrupt header (n)"); return CPHNSW_B200_E_INVALID; }
+    // the payload the header promises must be what the file holds, before anything is allocated for it
+    if (hd.dim == 0 || hd.dim > 65536 || hd.K == 0 || hd.K > 256 || (hd.comp_bytes != 1 && hd.comp_bytes != 2) || hd.M == 0 ||
+        hd.M > 64) {
+        set_error("load: corrupt header (shape)");
+        return CPHNSW_B200_E_INVALID;
+    }
+    {
+        const uint64_t P = next_pow2(hd.dim);
+        const uint64_t want = 8 + sizeof(hd) + uint64_t(hd.K) * 3 * P +
+                              hd.n * (hd.dim * 4 + uint64_t(hd.K) * hd.comp_bytes + uint64_t(hd.M) * 4);
+        const long here = std::ftell(fc.f);
+        if (here < 0 || std::fseek(fc.f, 0, SEEK_END) != 0) { set_error("load: cannot size %s", path); return CPHNSW_B200_E_INVALID; }
+        const long size = std::ftell(fc.f);
+        if (size < 0 || uint64_t(size) != want || std::fseek(fc.f, here, SEEK_SET) != 0) {
+            set_error("load: %s holds %ld bytes, its header promises %llu", path, size, (unsigned long long)want);
+            return CPHNSW_B200_E_INVALID;
+        }
+    }
     cphnsw_b200_index* h = nullptr;
     CPB_TRY(create_impl(hd.dim, hd.K, hd.comp_bytes, hd.M, hd.ef_construction, hd.seed, hd.convention, device,
                         hd.binary_codes != 0, &h));

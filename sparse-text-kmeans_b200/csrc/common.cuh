@@ -129,6 +129,7 @@ struct cphnsw_b200_index {
     uint32_t k_entry = 4, knn_k = 0, entry_scan = 0;
     int knn_kernel = 0;  // 0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance
     int search_kernel = 0;  // 0 = pick, 1 = one warp per query, 2 = two warps per query
+    int encode_variant = 1;  // 128-point encode kernel: 0, 1, 2 (see encode.cu)
     int search_table_smem = 1;  // 0: the query table is read in place even when it would fit shared memory
     int binary_codes = 0;  // 1: components keep only the sign bit (Hamming metric), search walks under the code distance
     // residual codes of the binary mode: the last residual_bits components are residual bits, a primary mismatch

@@ -18,7 +18,9 @@
 //   encode_p128_kernel   padded dim 128 (d in 65..128): one thread owns one vector, the whole
 //                        128-point transform lives in registers (no shuffles, no barriers in the
 //                        inner loop); the bound is the fp32 add pipe.
-//   encode_generic_kernel any power-of-two padded dim: one warp owns one vector in shared memory.
+//   encode_warp_kernel   padded dims 32, 64, 256, 512: one warp per vector, P/32 consecutive elements per lane,
+//                        low stages in registers, high stages by shuffles.
+//   encode_generic_kernel any other power-of-two padded dim: one warp owns one vector in shared memory.
 #include "common.cuh"
 
 namespace cpb {
@@ -26,7 +28,13 @@ namespace {
 
 constexpr int kP128 = 128;
 constexpr int kTileVecs = 128;          // vectors per block = threads per block
-constexpr int kTileStride = kP128 + 1;  // padded row: thread t reads bank (t + i) & 31
+// Row stride of the staged tile.  132 floats: rows start on 16-byte boundaries, so a thread reloads its vector with
+// 128-bit loads, and the eight threads of a quarter-warp read eight distinct 16-byte bank groups (4t mod 32).
+// (Variant 0, kept for comparison: 129 floats, 32-bit loads, thread t reads bank (t + i) & 31.)
+template <int V>
+struct TileStride {
+    static constexpr int value = V == 0 ? kP128 + 1 : kP128 + 4;
+};
 
 template <int H>
 __device__ __forceinline__ void butterfly_stage(float (&v)[kP128]) {
@@ -43,11 +51,26 @@ __device__ __forceinline__ void butterfly_stage(float (&v)[kP128]) {
 
 // D then H on 128 registers.  `sg` points at 128 +-1 floats in shared memory, read by every
 // thread at the same address (broadcast).
+template <bool XORSIGN>
 __device__ __forceinline__ void diag_fht128(float (&v)[kP128], const float* __restrict__ sg) {
     const float4* s4 = reinterpret_cast<const float4*>(sg);
 #pragma unroll
     for (int c = 0; c < kP128 / 4; ++c) {
         float4 s = s4[c];
+        if (XORSIGN) {
+            // a -1 of the diagonal flips the sign bit (integer pipe), then the plain butterfly: exact, and two
+            // operations on the fp32 pipe per pair instead of three
+            const uint32_t m = 0x80000000u;
+            const float a = __uint_as_float(__float_as_uint(v[4 * c]) ^ (__float_as_uint(s.x) & m));
+            const float b = __uint_as_float(__float_as_uint(v[4 * c + 1]) ^ (__float_as_uint(s.y) & m));
+            const float cc = __uint_as_float(__float_as_uint(v[4 * c + 2]) ^ (__float_as_uint(s.z) & m));
+            const float d = __uint_as_float(__float_as_uint(v[4 * c + 3]) ^ (__float_as_uint(s.w) & m));
+            v[4 * c] = __fadd_rn(a, b);
+            v[4 * c + 1] = __fsub_rn(a, b);
+            v[4 * c + 2] = __fadd_rn(cc, d);
+            v[4 * c + 3] = __fsub_rn(cc, d);
+            continue;
+        }
         {
             float t = __fmul_rn(s.x, v[4 * c]);
             float y = v[4 * c + 1];
@@ -103,12 +126,13 @@ __device__ __forceinline__ uint32_t component_of(float win, int idx, int flip_ma
 }
 
 // QUERY = true additionally writes the rotated vectors and winning magnitudes (CPQuery).
-template <typename CompT, bool QUERY>
+template <typename CompT, bool QUERY, int V>
 __global__ void __launch_bounds__(kTileVecs, QUERY ? 2 : 3)
 encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
                    const float* __restrict__ signs /*[K][3][128]*/, int flip_mask,
                    CompT* __restrict__ codes, float* __restrict__ rotated, float* __restrict__ mags) {
-    extern __shared__ float smem[];
+    constexpr int kTileStride = TileStride<V>::value;
+    extern __shared__ __align__(16) float smem[];
     float* tile = smem;                                                 // [kTileVecs][kTileStride]
     float* sign_sm = tile + kTileVecs * kTileStride;                              // [2][3][128], double buffer
     CompT* code_tile = reinterpret_cast<CompT*>(sign_sm + 2 * 3 * kP128);         // [kTileVecs][K]
@@ -126,10 +150,14 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
             if (vec4) {
                 float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (4 * lane < dim) q = __ldg(reinterpret_cast<const float4*>(src) + lane);
-                dst[4 * lane] = q.x;
-                dst[4 * lane + 1] = q.y;
-                dst[4 * lane + 2] = q.z;
-                dst[4 * lane + 3] = q.w;
+                if (V != 0) {
+                    reinterpret_cast<float4*>(dst)[lane] = q;
+                } else {
+                    dst[4 * lane] = q.x;
+                    dst[4 * lane + 1] = q.y;
+                    dst[4 * lane + 2] = q.z;
+                    dst[4 * lane + 3] = q.w;
+                }
             } else {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -155,11 +183,19 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
             reinterpret_cast<float4*>(sign_sm + ((r + 1) & 1) * 3 * kP128)[t] =
                 __ldg(reinterpret_cast<const float4*>(signs + size_t(r + 1) * 3 * kP128) + t);
         float v[kP128];
+        if (V != 0) {
 #pragma unroll
-        for (int i = 0; i < kP128; ++i) v[i] = mine[i];
+            for (int c = 0; c < kP128 / 4; ++c) {
+                const float4 q = reinterpret_cast<const float4*>(mine)[c];
+                v[4 * c] = q.x, v[4 * c + 1] = q.y, v[4 * c + 2] = q.z, v[4 * c + 3] = q.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kP128; ++i) v[i] = mine[i];
+        }
         const float* sg = sign_sm + (r & 1) * 3 * kP128;
 #pragma unroll 1
-        for (int layer = 0; layer < 3; ++layer) diag_fht128(v, sg + layer * kP128);
+        for (int layer = 0; layer < 3; ++layer) diag_fht128<V == 2>(v, sg + layer * kP128);
         float win;
         int idx;
         argmax128(v, win, idx);
@@ -311,6 +347,89 @@ encode_p1024_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
     }
 }
 
+// ---- padded dims 32, 64, 256, 512: one warp per vector, E = P / 32 consecutive elements per lane -------------
+// Lane L holds elements E*L .. E*L + E - 1.  Stages h < E pair elements of one lane (registers), stages
+// h = E * 2^t pair lane L with lane L ^ 2^t (one shuffle per element): the lower index computes x + y, the upper
+// x - y with x the lower element, in ascending h like the reference's loop (fht.hpp:56-69), so the result is
+// bit-identical.  Nothing goes through shared memory.
+template <typename CompT, bool QUERY, int E>
+__global__ void __launch_bounds__(128)
+encode_warp_kernel(const float* __restrict__ x, uint64_t n, int dim, int K, const float* __restrict__ signs /*[K][3][P]*/,
+                   int flip_mask, CompT* __restrict__ codes, float* __restrict__ rotated, float* __restrict__ mags) {
+    constexpr int P = 32 * E;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int first = E * lane;
+    for (uint64_t row = uint64_t(blockIdx.x) * warps + warp; row < n; row += uint64_t(gridDim.x) * warps) {
+        const float* src = x + row * uint64_t(dim);
+        float in[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) in[j] = first + j < dim ? __ldg(src + first + j) : 0.0f;
+        for (int r = 0; r < K; ++r) {
+            float v[E];
+#pragma unroll
+            for (int j = 0; j < E; ++j) v[j] = in[j];
+            const float* sg = signs + size_t(r) * 3 * P + first;
+#pragma unroll 1
+            for (int layer = 0; layer < 3; ++layer) {
+#pragma unroll
+                for (int j = 0; j < E; ++j) v[j] = __fmul_rn(v[j], __ldg(sg + layer * P + j));
+#pragma unroll
+                for (int h = 1; h < E; h <<= 1) {
+#pragma unroll
+                    for (int j = 0; j < E; ++j)
+                        if ((j & h) == 0) {
+                            const float a = v[j], b = v[j + h];
+                            v[j] = __fadd_rn(a, b);
+                            v[j + h] = __fsub_rn(a, b);
+                        }
+                }
+#pragma unroll
+                for (int t = 1; t < 32; t <<= 1) {
+                    const bool upper = lane & t;
+#pragma unroll
+                    for (int j = 0; j < E; ++j) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[j], t);
+                        v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+                    }
+                }
+            }
+            // lowest-index argmax: ascending scan of the lane's own elements, then a warp reduction that prefers
+            // the lower index on equal magnitude (cp_encoder.hpp:82-88)
+            float best = -1.0f, win = 0.0f;
+            int idx = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                const float a = fabsf(v[j]);
+                if (a > best) {
+                    best = a;
+                    win = v[j];
+                    idx = first + j;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const float ow = __shfl_xor_sync(0xffffffffu, win, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ob > best || (ob == best && oi < idx)) {
+                    best = ob;
+                    win = ow;
+                    idx = oi;
+                }
+            }
+            if (lane == 0) {
+                codes[row * K + r] = CompT(component_of(win, idx, flip_mask));
+                if (QUERY && mags) mags[row * K + r] = best;
+            }
+            if (QUERY && rotated) {
+                float* out = rotated + (row * K + r) * uint64_t(P) + first;
+#pragma unroll
+                for (int j = 0; j < E; ++j) out[j] = (__popc((first + j) & flip_mask) & 1) ? -v[j] : v[j];
+            }
+        }
+    }
+}
+
 // ---- generic padded dim: one warp per vector, transform in shared memory ----------------------
 template <typename CompT>
 __global__ void encode_generic_kernel(const float* __restrict__ x, uint64_t n, int dim, int P, int K,
@@ -404,15 +523,22 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
     LaunchTimer timer(h, kKernelEncode, st);
 
     if (P == kP128) {
-        size_t smem = size_t(kTileVecs) * kTileStride * sizeof(float) + size_t(2) * 3 * kP128 * sizeof(float) +
-                      size_t(kTileVecs) * K * h->comp_bytes;
+        const int variant = h->encode_variant;
+        size_t smem = size_t(kTileVecs) * (variant == 0 ? TileStride<0>::value : TileStride<1>::value) * sizeof(float) +
+                      size_t(2) * 3 * kP128 * sizeof(float) + size_t(kTileVecs) * K * h->comp_bytes;
         unsigned grid = unsigned((n + kTileVecs - 1) / kTileVecs);
         const bool query = d_rot || d_mag;
-#define CPB_LAUNCH_P128(T, Q)                                                                              \
+#define CPB_LAUNCH_P128_V(T, Q, VV)                                                                        \
     do {                                                                                                   \
-        CPB_CUDA(allow_max_dynamic_smem(encode_p128_kernel<T, Q>));                                        \
-        encode_p128_kernel<T, Q><<<grid, kTileVecs, smem, st>>>(d_x, n, dim, K, signs, flip_mask,           \
-                                                               (T*)d_codes, d_rot, d_mag);                  \
+        CPB_CUDA(allow_max_dynamic_smem(encode_p128_kernel<T, Q, VV>));                                    \
+        encode_p128_kernel<T, Q, VV><<<grid, kTileVecs, smem, st>>>(d_x, n, dim, K, signs, flip_mask,       \
+                                                                   (T*)d_codes, d_rot, d_mag);              \
+    } while (0)
+#define CPB_LAUNCH_P128(T, Q)                                   \
+    do {                                                        \
+        if (variant == 0) CPB_LAUNCH_P128_V(T, Q, 0);           \
+        else if (variant == 1) CPB_LAUNCH_P128_V(T, Q, 1);      \
+        else CPB_LAUNCH_P128_V(T, Q, 2);                        \
     } while (0)
         if (h->comp_bytes == 1) {
             if (query) CPB_LAUNCH_P128(uint8_t, true);
@@ -422,6 +548,7 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
             else CPB_LAUNCH_P128(uint16_t, false);
         }
 #undef CPB_LAUNCH_P128
+#undef CPB_LAUNCH_P128_V
     } else if (P == kP1024 && h->d_signbits.p) {
         const bool query = d_rot || d_mag;
         const uint64_t blocks = (n + kWarps1024 - 1) / kWarps1024;
@@ -437,6 +564,28 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
             else CPB_LAUNCH_P1024(uint16_t, false);
         }
 #undef CPB_LAUNCH_P1024
+    } else if (P == 32 || P == 64 || P == 256 || P == 512) {
+        const bool query = d_rot || d_mag;
+        const uint64_t blocks = (n + 3) / 4;
+        const unsigned grid = unsigned(blocks < uint64_t(h->sm_count) * 32 ? blocks : uint64_t(h->sm_count) * 32);
+#define CPB_LAUNCH_WARP(T, Q, EE) \
+    encode_warp_kernel<T, Q, EE><<<grid, 128, 0, st>>>(d_x, n, dim, K, signs, flip_mask, (T*)d_codes, d_rot, d_mag)
+#define CPB_LAUNCH_WARP_E(T, Q)                      \
+    do {                                             \
+        if (P == 32) CPB_LAUNCH_WARP(T, Q, 1);       \
+        else if (P == 64) CPB_LAUNCH_WARP(T, Q, 2);  \
+        else if (P == 256) CPB_LAUNCH_WARP(T, Q, 8); \
+        else CPB_LAUNCH_WARP(T, Q, 16);              \
+    } while (0)
+        if (h->comp_bytes == 1) {
+            if (query) CPB_LAUNCH_WARP_E(uint8_t, true);
+            else CPB_LAUNCH_WARP_E(uint8_t, false);
+        } else {
+            if (query) CPB_LAUNCH_WARP_E(uint16_t, true);
+            else CPB_LAUNCH_WARP_E(uint16_t, false);
+        }
+#undef CPB_LAUNCH_WARP_E
+#undef CPB_LAUNCH_WARP
     } else {
         int warps = 4;
         while (warps > 1 && size_t(warps) * P * sizeof(float) > 96 * 1024) warps >>= 1;

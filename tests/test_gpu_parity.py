@@ -42,7 +42,10 @@ def test_encode_matches_reference_golden(cp, conv, ci):
 @pytest.mark.parametrize("dim,K,cb,n", [(128, 32, 1, 1), (128, 32, 1, 31), (128, 32, 1, 129), (128, 32, 1, 1000),
                                         (96, 32, 1, 777), (100, 16, 1, 300), (65, 1, 1, 50), (128, 32, 2, 200),
                                         (64, 32, 1, 500), (16, 16, 1, 100), (1, 4, 1, 9), (300, 16, 2, 100),
-                                        (960, 32, 2, 70), (1024, 4, 2, 33)])
+                                        (960, 32, 2, 70), (1024, 4, 2, 33),
+                                        # padded dims 32, 64, 256, 512 (the register / shuffle kernel), 2048 (shared memory)
+                                        (20, 8, 1, 333), (33, 16, 1, 257), (256, 32, 2, 300), (200, 32, 2, 129), (512, 8, 2, 65),
+                                        (400, 33, 2, 40), (1500, 3, 2, 20)])
 @pytest.mark.parametrize("conv", [0, 2])
 def test_encode_matches_oracle(cp, oracle, dim, K, cb, n, conv):
     rng = np.random.default_rng(dim * 1000 + n)
@@ -588,8 +591,12 @@ def test_load_rejects_bad_files(cp, tmp_path):
     path = str(tmp_path / "i.cphnsw")
     idx.save(path)
     raw = open(path, "rb").read()
+    # header after the 8-byte magic: 12 32-bit fields, then dim, seed, n as 64-bit fields at bytes 56, 64, 72
     cases = {"magic": b"NOTANIDX" + raw[8:], "version": raw[:8] + (99).to_bytes(4, "little") + raw[12:], "short": raw[:-100],
-             "empty": b""}
+             "empty": b"", "long": raw + b"\0" * 16,
+             "huge_dim": raw[:56] + (1 << 40).to_bytes(8, "little") + raw[64:],
+             "huge_n": raw[:72] + (1 << 30).to_bytes(8, "little") + raw[80:],
+             "zero_K": raw[:12] + (0).to_bytes(4, "little") + raw[16:]}
     for name, data in cases.items():
         p = str(tmp_path / name)
         open(p, "wb").write(data)

@@ -222,3 +222,40 @@ def test_narrow_launch_equals_wide_launch(cp):
         mp = idx.search_multiprobe_batch(q[:64], 10, 50, 4)
         one = idx.search_multiprobe_batch(q[3:4], 10, 50, 4)
         assert np.array_equal(one[0][0], mp[0][3]) and np.array_equal(one[1][0], mp[1][3])
+
+
+def test_binary_codes_cannot_be_switched_off_when_components_would_not_fit(cp):
+    # a binary-code handle keeps one byte per component whatever the dimension; full (index, sign) components
+    # of padded dim 512 do not fit a byte, so switching the mode off must be refused, not silently truncate
+    idx = cp.CPHNSWIndex.binary(300, K=32)
+    with pytest.raises(ValueError):
+        idx.set_param("binary_codes", 0)
+    assert idx.get_param("binary_codes") == 1
+    small = cp.CPHNSWIndex.binary(100, K=32)  # padded dim 128 fits a byte: allowed
+    small.set_param("binary_codes", 0)
+    assert small.get_param("binary_codes") == 0
+
+
+def test_installed_adjacency_with_foreign_ids_is_searched_safely(cp, oracle):
+    # rows installed from outside may hold ids that name no node: every kernel treats them as "no node"
+    n, M = 2000, 32
+    base, q = synthetic.gaussian_mixture(n, 50, 128, 8, 0.3, 12)
+    ref = make_index(cp, 128)
+    ref.set_param("entry_scan", 64)
+    ref.add_batch_parallel(base)
+    codes, adj = ref.codes(), ref.adjacency()
+    bad = adj.copy()
+    bad[::7, 5] = n + 11
+    bad[3::11, 0] = 0xFFFFFFFE
+    idx = make_index(cp, 128)
+    idx.set_param("entry_scan", 64)
+    idx.install(base, codes, bad)
+    clean = np.where(bad >= n, INVALID, bad).astype(np.uint32)
+    _, rot, _ = oracle.encode(q, 32, 1, oracle.sign_tables(128, 32, 42), 2, want_rotated=True)
+    want = oracle.search(rot, codes, clean, idx.entry_ids(), 100, 10, n_seed=4)
+    got = idx.search_batch(q, 10, 100)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+    assert idx.verify_connectivity() == oracle.connectivity(clean, idx.entry_ids())
+    more, _ = synthetic.gaussian_mixture(300, 1, 128, 8, 0.3, 13)
+    idx.add_batch(more)  # the reverse-edge pass reads the installed rows
+    assert idx.size() == n + 300 and (idx.adjacency()[n:] < n + 300).all()
