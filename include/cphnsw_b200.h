@@ -106,6 +106,12 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *   "rank_prune" (0/1, default 0: the bulk build prunes the kNN lists by rank, see cphnsw_b200_rank_prune, instead of
  *                 running select_neighbors) and "rank_pruning_alpha" (1.0..3.0, default 1.1; CPHNSWParams::rank_pruning_alpha,
  *                 types.hpp:399-400,459-466),
+ *   "exact_edges" (0/1, default 0: the bulk build chooses the links on the stored fp32 vectors instead of the codes - the
+ *                 legacy "hybrid" construction, "True Cosine edges - the production path", evaluation/eval_master.cpp:251-272:
+ *                 candidates of a node = its knn_k exact nearest neighbours by -<x,y> (the exact top-(knn_k+1) over all
+ *                 vectors by (distance, id) with the node itself removed), then select_neighbors on those exact distances,
+ *                 every distance summed in fp32 in d order; O(n^2 d) build, search unchanged; with "prune" = 0 the M exact
+ *                 nearest are the links; incremental add_batch keeps choosing by code distance),
  *   "first_wait_polls" (0..2^22, default 2^22: polls granted to the FIRST bounded wait of a kNN-graph launch; a test
  *                 sets 0 to make that wait give up, which the call reports as CPHNSW_B200_E_DEVICE_WAIT),
  *   "entry_scan" (evenly spaced nodes scored for every query before the walk; default = k_entry),

@@ -844,6 +844,62 @@ int orc_rank_prune(const uint32_t* cand, uint64_t n, uint64_t k, uint64_t M, flo
     return 0;
 }
 
+// Links chosen on the fp32 vectors: the legacy "hybrid" construction ("Hybrid (True Cosine edges) - the production
+// path", evaluation/eval_master.cpp:251-272; evaluation/test_tiered.cpp:4-7; source absent).
+// distance(a, b) = -<a, b>, products and sums separate, summed in d order (the loop of evaluation/eval_sift.cpp:546-551).
+static inline float neg_dot(const float* a, const float* b, size_t dim) {
+    float acc = 0.0f;
+    for (size_t d = 0; d < dim; ++d) acc = acc + a[d] * b[d];
+    return -acc;
+}
+
+// Candidates of row i: the exact top-(k+1) of ALL vectors by (distance to x_i, id) with i itself removed, cut to k
+// (i is in its own list unless more than k exact duplicates with lower ids precede it).
+int orc_exact_candidates(const float* base, uint64_t n, uint64_t dim, uint64_t k, uint64_t row_begin, uint64_t row_end,
+                         uint32_t* cand) {
+#pragma omp parallel for schedule(dynamic, 8)
+    for (int64_t i = (int64_t)row_begin; i < (int64_t)row_end; ++i) {
+        std::vector<Cand> all(n);
+        for (size_t j = 0; j < n; ++j) all[j] = {neg_dot(base + (size_t)i * dim, base + j * dim, dim), (uint32_t)j};
+        const size_t keep = std::min<size_t>(n, k + 1);
+        std::partial_sort(all.begin(), all.begin() + keep, all.end());
+        uint32_t* out = cand + ((size_t)i - row_begin) * k;
+        size_t o = 0;
+        for (size_t t = 0; t < keep && o < k; ++t)
+            if (all[t].second != (uint32_t)i) out[o++] = all[t].second;
+        for (; o < k; ++o) out[o] = kInvalid;
+    }
+    return 0;
+}
+
+// SELECT-NEIGHBORS-HEURISTIC with keepPrunedConnections on those exact distances
+// (resources/hnsw-paper/consolidated.tex:93-115): candidate e is kept iff d(e, q) < d(e, r) for every r kept so far.
+int orc_select_neighbors_exact(const float* base, uint64_t n, uint64_t dim, const uint32_t* cand, uint64_t k, uint64_t M,
+                               int keep_pruned, uint64_t row_begin, uint64_t row_end, uint32_t* adj) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = (int64_t)row_begin; i < (int64_t)row_end; ++i) {
+        const uint32_t* c = cand + ((size_t)i - row_begin) * k;
+        uint32_t* out = adj + ((size_t)i - row_begin) * M;
+        std::vector<uint32_t> R, Wd;
+        for (size_t t = 0; t < k && R.size() < M; ++t) {
+            const uint32_t e = c[t];
+            if (e >= n) continue;
+            const float d_eq = neg_dot(base + (size_t)e * dim, base + (size_t)i * dim, dim);
+            bool keep = true;
+            for (uint32_t r : R)
+                if (!(d_eq < neg_dot(base + (size_t)e * dim, base + (size_t)r * dim, dim))) {
+                    keep = false;
+                    break;
+                }
+            (keep ? R : Wd).push_back(e);
+        }
+        if (keep_pruned)
+            for (size_t t = 0; t < Wd.size() && R.size() < M; ++t) R.push_back(Wd[t]);
+        for (size_t t = 0; t < M; ++t) out[t] = t < R.size() ? R[t] : kInvalid;
+    }
+    return 0;
+}
+
 // Thread count of every parallel region from now on (launchers such as torchrun export OMP_NUM_THREADS=1).
 int orc_set_threads(int threads) {
 #ifdef _OPENMP

@@ -160,6 +160,29 @@ def rank_prune(cand, M, alpha=1.1):
     return adj
 
 
+def exact_candidates(base, k, row_begin=0, row_end=None):
+    """Exact nearest neighbours by -<x,y> of rows [row_begin, row_end) among all rows, the row itself removed."""
+    base = np.ascontiguousarray(base, np.float32)
+    n, dim = base.shape
+    row_end = n if row_end is None else row_end
+    cand = np.empty((row_end - row_begin, k), np.uint32)
+    lib().orc_exact_candidates(_ptr(base), C.c_uint64(n), C.c_uint64(dim), C.c_uint64(k), C.c_uint64(row_begin),
+                               C.c_uint64(row_end), _ptr(cand))
+    return cand
+
+
+def select_neighbors_exact(base, cand, M, keep_pruned=True, row_begin=0):
+    """select_neighbors on exact fp32 distances (the legacy hybrid construction)."""
+    base = np.ascontiguousarray(base, np.float32)
+    cand = np.ascontiguousarray(cand, np.uint32)
+    n, dim = base.shape
+    rows, k = cand.shape
+    adj = np.empty((rows, M), np.uint32)
+    lib().orc_select_neighbors_exact(_ptr(base), C.c_uint64(n), C.c_uint64(dim), _ptr(cand), C.c_uint64(k), C.c_uint64(M),
+                                     C.c_int(int(keep_pruned)), C.c_uint64(row_begin), C.c_uint64(row_begin + rows), _ptr(adj))
+    return adj
+
+
 def set_threads(threads):
     """Sets the OpenMP thread count of the oracle (returns the count now in force)."""
     return int(lib().orc_set_threads(C.c_int(int(threads))))

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcphnsw_b200.so")
-SOURCES = ["api.cu", "encode.cu", "distance.cu", "knn_sliced.cu", "search.cu", "search_team.cu", "multiprobe.cu", "diagnostics.cu", "exact.cu", "rank_prune.cu", "sharded.cu"]
+SOURCES = ["api.cu", "encode.cu", "distance.cu", "knn_sliced.cu", "search.cu", "search_team.cu", "multiprobe.cu", "diagnostics.cu", "exact.cu", "rank_prune.cu", "sharded.cu", "exact_edges.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "knn_common.cuh"), os.path.join(CSRC, "search_common.cuh"), os.path.join(HERE, "..", "include", "cphnsw_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--fmad=false", "-std=c++17",

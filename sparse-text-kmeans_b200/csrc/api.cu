@@ -151,6 +151,17 @@ int build_graph(cphnsw_b200_index* h, uint64_t n, DevBuf& adj, cudaStream_t st) 
     if (k < h->M) k = h->M;
     if (k > 64) k = 64;
     CPB_TRY(adj.reserve(size_t(n) * h->M * 4 + 16));
+    if (h->exact_edges) {
+        // the legacy hybrid construction: exact nearest neighbours as candidates, links chosen on exact distances
+        CPB_TRY(h->s_out.reserve(size_t(n) * k * 4 + 16));
+        CPB_TRY(launch_exact_candidates(h, h->d_vectors.as<float>(), n, h->prune ? k : h->M, 0, n,
+                                        h->prune ? h->s_out.as<uint32_t>() : adj.as<uint32_t>(), st));
+        if (h->prune)
+            CPB_TRY(launch_select_exact(h, h->d_vectors.as<float>(), n, h->s_out.as<uint32_t>(), k, 0, n, h->M, h->keep_pruned,
+                                        adj.as<uint32_t>(), st));
+        CPB_CUDA(cudaStreamSynchronize(st));
+        return check_status(h);
+    }
     if (!h->prune) {
         // build_with_gpu_knn(..., prune = false): the M nearest by (code distance, id) are the links
         CPB_TRY(launch_knn_graph(h, h->d_codes.p, n, h->M, 0, n, adj.as<uint32_t>(), nullptr, st));
@@ -627,7 +638,6 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         return 0;
     }
     if (s == "search_table_smem") { h->search_table_smem = v != 0.0; return 0; }
-    if (s == "encode_variant") { h->encode_variant = v < 0 ? 0 : (v > 2 ? 2 : int(v)); return 0; }
     if (s == "binary_codes") {
         if (v != 0 && v != 1) { set_error("binary_codes must be 0 or 1"); return CPHNSW_B200_E_INVALID; }
         if (h->n && int(v) != h->binary_codes) { set_error("binary_codes cannot change once vectors have been added"); return CPHNSW_B200_E_STATE; }
@@ -664,6 +674,7 @@ int cphnsw_b200_set_param(cphnsw_b200_index* h, const char* name, double v) {
         return 0;
     }
     if (s == "rank_prune") { h->rank_prune = v != 0.0; return 0; }
+    if (s == "exact_edges") { h->exact_edges = v != 0.0; return 0; }
     if (s == "rank_pruning_alpha") {
         // bounds of CPHNSWParams::finalize (include/cphnsw/core/types.hpp:459-466)
         if (!(v >= 1.0)) { set_error("CPHNSWParams: rank_pruning_alpha must be >= 1.0"); return CPHNSW_B200_E_INVALID; }
@@ -711,6 +722,7 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "build_seed") *v = h->build_seed;
     else if (s == "first_wait_polls") *v = h->first_wait_polls;
     else if (s == "rank_prune") *v = h->rank_prune;
+    else if (s == "exact_edges") *v = h->exact_edges;
     else if (s == "rank_pruning_alpha") *v = h->rank_pruning_alpha;
     else if (s == "binary_codes") *v = h->binary_codes;
     else if (s == "residual_bits") *v = h->residual_bits;

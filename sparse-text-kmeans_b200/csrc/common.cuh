@@ -129,7 +129,6 @@ struct cphnsw_b200_index {
     uint32_t k_entry = 4, knn_k = 0, entry_scan = 0;
     int knn_kernel = 0;  // 0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance
     int search_kernel = 0;  // 0 = pick, 1 = one warp per query, 2 = two warps per query
-    int encode_variant = 1;  // 128-point encode kernel: 0, 1, 2 (see encode.cu)
     int search_table_smem = 1;  // 0: the query table is read in place even when it would fit shared memory
     int binary_codes = 0;  // 1: components keep only the sign bit (Hamming metric), search walks under the code distance
     // residual codes of the binary mode: the last residual_bits components are residual bits, a primary mismatch
@@ -140,6 +139,7 @@ struct cphnsw_b200_index {
     // polls the kNN kernels grant their FIRST tile wait ("first_wait_polls"; every other wait keeps the full
     // limit).  0 makes that wait give up at once: the way a test reaches the lost-wait path.
     uint32_t first_wait_polls = 1u << 22;
+    int exact_edges = 0;              // bulk build picks candidates and links on the fp32 vectors (legacy hybrid construction)
     int rank_prune = 0;               // bulk build prunes by detourable-route count instead of select_neighbors
     float rank_pruning_alpha = 1.1f;  // CPHNSWParams::rank_pruning_alpha (include/cphnsw/core/types.hpp:399-400)
 
@@ -210,6 +210,11 @@ int launch_rank_merge(cphnsw_b200_index* h, uint64_t n, const uint32_t* d_kept, 
                       uint64_t row_end, uint32_t* d_adj, cudaStream_t st);
 int launch_rank_prune(cphnsw_b200_index* h, uint64_t n, const uint32_t* d_cand, uint32_t k, uint32_t M, float alpha,
                       uint32_t* d_adj, cudaStream_t st);
+// links chosen on the fp32 vectors (exact_edges.cu): exact nearest neighbours as candidates, select_neighbors on exact distances
+int launch_exact_candidates(cphnsw_b200_index* h, const float* d_vectors, uint64_t n, uint32_t k, uint64_t row_begin,
+                            uint64_t row_end, uint32_t* d_cand, cudaStream_t st);
+int launch_select_exact(cphnsw_b200_index* h, const float* d_vectors, uint64_t n, const uint32_t* d_cand, uint32_t k,
+                        uint64_t row_begin, uint64_t row_end, uint32_t M, int keep_pruned, uint32_t* d_adj, cudaStream_t st);
 // incremental insertion: old nodes chosen by the new rows [n_old, n_old + m) of d_adj re-select their rows
 int launch_reverse_edges(cphnsw_b200_index* h, const void* d_codes, uint64_t n_old, uint64_t m, uint32_t* d_adj,
                          uint32_t M, int keep_pruned, cudaStream_t st);

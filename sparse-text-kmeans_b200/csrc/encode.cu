@@ -28,13 +28,10 @@ namespace {
 
 constexpr int kP128 = 128;
 constexpr int kTileVecs = 128;          // vectors per block = threads per block
-// Row stride of the staged tile.  132 floats: rows start on 16-byte boundaries, so a thread reloads its vector with
-// 128-bit loads, and the eight threads of a quarter-warp read eight distinct 16-byte bank groups (4t mod 32).
-// (Variant 0, kept for comparison: 129 floats, 32-bit loads, thread t reads bank (t + i) & 31.)
-template <int V>
-struct TileStride {
-    static constexpr int value = V == 0 ? kP128 + 1 : kP128 + 4;
-};
+// Padded row of the staged tile: thread t reads bank (t + i) & 31.  (Measured and dropped: a 132-float stride with
+// 128-bit reloads, 3.875 ms per 1M vectors against 3.835 ms, and on top of it the diagonal applied as a sign-bit XOR
+// on the integer pipe with plain first-stage butterflies, 3.883 ms.)
+constexpr int kTileStride = kP128 + 1;
 
 template <int H>
 __device__ __forceinline__ void butterfly_stage(float (&v)[kP128]) {
@@ -51,26 +48,11 @@ __device__ __forceinline__ void butterfly_stage(float (&v)[kP128]) {
 
 // D then H on 128 registers.  `sg` points at 128 +-1 floats in shared memory, read by every
 // thread at the same address (broadcast).
-template <bool XORSIGN>
 __device__ __forceinline__ void diag_fht128(float (&v)[kP128], const float* __restrict__ sg) {
     const float4* s4 = reinterpret_cast<const float4*>(sg);
 #pragma unroll
     for (int c = 0; c < kP128 / 4; ++c) {
         float4 s = s4[c];
-        if (XORSIGN) {
-            // a -1 of the diagonal flips the sign bit (integer pipe), then the plain butterfly: exact, and two
-            // operations on the fp32 pipe per pair instead of three
-            const uint32_t m = 0x80000000u;
-            const float a = __uint_as_float(__float_as_uint(v[4 * c]) ^ (__float_as_uint(s.x) & m));
-            const float b = __uint_as_float(__float_as_uint(v[4 * c + 1]) ^ (__float_as_uint(s.y) & m));
-            const float cc = __uint_as_float(__float_as_uint(v[4 * c + 2]) ^ (__float_as_uint(s.z) & m));
-            const float d = __uint_as_float(__float_as_uint(v[4 * c + 3]) ^ (__float_as_uint(s.w) & m));
-            v[4 * c] = __fadd_rn(a, b);
-            v[4 * c + 1] = __fsub_rn(a, b);
-            v[4 * c + 2] = __fadd_rn(cc, d);
-            v[4 * c + 3] = __fsub_rn(cc, d);
-            continue;
-        }
         {
             float t = __fmul_rn(s.x, v[4 * c]);
             float y = v[4 * c + 1];
@@ -126,13 +108,12 @@ __device__ __forceinline__ uint32_t component_of(float win, int idx, int flip_ma
 }
 
 // QUERY = true additionally writes the rotated vectors and winning magnitudes (CPQuery).
-template <typename CompT, bool QUERY, int V>
+template <typename CompT, bool QUERY>
 __global__ void __launch_bounds__(kTileVecs, QUERY ? 2 : 3)
 encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
                    const float* __restrict__ signs /*[K][3][128]*/, int flip_mask,
                    CompT* __restrict__ codes, float* __restrict__ rotated, float* __restrict__ mags) {
-    constexpr int kTileStride = TileStride<V>::value;
-    extern __shared__ __align__(16) float smem[];
+    extern __shared__ float smem[];
     float* tile = smem;                                                 // [kTileVecs][kTileStride]
     float* sign_sm = tile + kTileVecs * kTileStride;                              // [2][3][128], double buffer
     CompT* code_tile = reinterpret_cast<CompT*>(sign_sm + 2 * 3 * kP128);         // [kTileVecs][K]
@@ -150,14 +131,10 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
             if (vec4) {
                 float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (4 * lane < dim) q = __ldg(reinterpret_cast<const float4*>(src) + lane);
-                if (V != 0) {
-                    reinterpret_cast<float4*>(dst)[lane] = q;
-                } else {
-                    dst[4 * lane] = q.x;
-                    dst[4 * lane + 1] = q.y;
-                    dst[4 * lane + 2] = q.z;
-                    dst[4 * lane + 3] = q.w;
-                }
+                dst[4 * lane] = q.x;
+                dst[4 * lane + 1] = q.y;
+                dst[4 * lane + 2] = q.z;
+                dst[4 * lane + 3] = q.w;
             } else {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -183,19 +160,11 @@ encode_p128_kernel(const float* __restrict__ x, uint64_t n, int dim, int K,
             reinterpret_cast<float4*>(sign_sm + ((r + 1) & 1) * 3 * kP128)[t] =
                 __ldg(reinterpret_cast<const float4*>(signs + size_t(r + 1) * 3 * kP128) + t);
         float v[kP128];
-        if (V != 0) {
 #pragma unroll
-            for (int c = 0; c < kP128 / 4; ++c) {
-                const float4 q = reinterpret_cast<const float4*>(mine)[c];
-                v[4 * c] = q.x, v[4 * c + 1] = q.y, v[4 * c + 2] = q.z, v[4 * c + 3] = q.w;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < kP128; ++i) v[i] = mine[i];
-        }
+        for (int i = 0; i < kP128; ++i) v[i] = mine[i];
         const float* sg = sign_sm + (r & 1) * 3 * kP128;
 #pragma unroll 1
-        for (int layer = 0; layer < 3; ++layer) diag_fht128<V == 2>(v, sg + layer * kP128);
+        for (int layer = 0; layer < 3; ++layer) diag_fht128(v, sg + layer * kP128);
         float win;
         int idx;
         argmax128(v, win, idx);
@@ -523,22 +492,15 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
     LaunchTimer timer(h, kKernelEncode, st);
 
     if (P == kP128) {
-        const int variant = h->encode_variant;
-        size_t smem = size_t(kTileVecs) * (variant == 0 ? TileStride<0>::value : TileStride<1>::value) * sizeof(float) +
-                      size_t(2) * 3 * kP128 * sizeof(float) + size_t(kTileVecs) * K * h->comp_bytes;
+        size_t smem = size_t(kTileVecs) * kTileStride * sizeof(float) + size_t(2) * 3 * kP128 * sizeof(float) +
+                      size_t(kTileVecs) * K * h->comp_bytes;
         unsigned grid = unsigned((n + kTileVecs - 1) / kTileVecs);
         const bool query = d_rot || d_mag;
-#define CPB_LAUNCH_P128_V(T, Q, VV)                                                                        \
+#define CPB_LAUNCH_P128(T, Q)                                                                              \
     do {                                                                                                   \
-        CPB_CUDA(allow_max_dynamic_smem(encode_p128_kernel<T, Q, VV>));                                    \
-        encode_p128_kernel<T, Q, VV><<<grid, kTileVecs, smem, st>>>(d_x, n, dim, K, signs, flip_mask,       \
-                                                                   (T*)d_codes, d_rot, d_mag);              \
-    } while (0)
-#define CPB_LAUNCH_P128(T, Q)                                   \
-    do {                                                        \
-        if (variant == 0) CPB_LAUNCH_P128_V(T, Q, 0);           \
-        else if (variant == 1) CPB_LAUNCH_P128_V(T, Q, 1);      \
-        else CPB_LAUNCH_P128_V(T, Q, 2);                        \
+        CPB_CUDA(allow_max_dynamic_smem(encode_p128_kernel<T, Q>));                                        \
+        encode_p128_kernel<T, Q><<<grid, kTileVecs, smem, st>>>(d_x, n, dim, K, signs, flip_mask,           \
+                                                               (T*)d_codes, d_rot, d_mag);                  \
     } while (0)
         if (h->comp_bytes == 1) {
             if (query) CPB_LAUNCH_P128(uint8_t, true);
@@ -548,7 +510,6 @@ int launch_encode(cphnsw_b200_index* h, const float* d_x, uint64_t n, void* d_co
             else CPB_LAUNCH_P128(uint16_t, false);
         }
 #undef CPB_LAUNCH_P128
-#undef CPB_LAUNCH_P128_V
     } else if (P == kP1024 && h->d_signbits.p) {
         const bool query = d_rot || d_mag;
         const uint64_t blocks = (n + kWarps1024 - 1) / kWarps1024;

@@ -303,8 +303,9 @@ int cphnsw_b200_sharded_add_batch_parallel(cphnsw_b200_sharded* s, const float* 
     const uint64_t old_n = cphnsw_b200_size(s->h[0]);
     double seeded = 0;
     cphnsw_b200_get_param(s->h[0], "build_seed", &seeded);
-    if (s->G == 1 || old_n != 0 || seeded != 0 || n < uint64_t(s->G) * 64) {
-        // one device, an index that already holds nodes, a seeded build or a handful of rows: every replica does
+    if (s->G == 1 || old_n != 0 || seeded != 0 || s->h[0]->exact_edges || n < uint64_t(s->G) * 64) {
+        // one device, an index that already holds nodes, a seeded build, links on exact distances or a handful of rows:
+        // every replica does
         // the whole call (same input, same kernels: the replicas stay identical)
         return per_device(s, [&](int g) { return cphnsw_b200_add_batch_parallel(s->h[g], x, n); });
     }

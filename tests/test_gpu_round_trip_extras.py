@@ -259,3 +259,44 @@ def test_installed_adjacency_with_foreign_ids_is_searched_safely(cp, oracle):
     more, _ = synthetic.gaussian_mixture(300, 1, 128, 8, 0.3, 13)
     idx.add_batch(more)  # the reverse-edge pass reads the installed rows
     assert idx.size() == n + 300 and (idx.adjacency()[n:] < n + 300).all()
+
+
+# ---- links chosen on the fp32 vectors ("exact_edges": the legacy hybrid construction) ---------------------------
+@pytest.mark.parametrize("n,dim,M,knn_k,keep", [(2500, 128, 32, 64, True), (1800, 96, 16, 32, True), (900, 40, 32, 64, False),
+                                                (1200, 200, 8, 20, True), (60, 128, 32, 64, True)])
+def test_exact_edges_build_matches_oracle(cp, oracle, n, dim, M, knn_k, keep):
+    base, q = synthetic.gaussian_sphere(n, 40, dim, n + M)
+    base[7] = base[3]  # exact duplicates: equal distances, ties by id
+    base[8] = base[3]
+    idx = cp.CPHNSWIndex(dim, M=M, ef_construction=200, K=32, component_bytes=2 if dim > 128 else 1)
+    idx.set_param("exact_edges", 1)
+    idx.set_param("knn_k", knn_k)
+    idx.set_param("keep_pruned", int(keep))
+    idx.set_param("entry_scan", min(n, 64))
+    idx.add_batch_parallel(base)
+    k = max(M, min(knn_k, 64))
+    cand = oracle.exact_candidates(base, k)
+    assert np.array_equal(idx.adjacency(), oracle.select_neighbors_exact(base, cand, M, keep))
+    ids, _ = idx.search_and_rerank_batch(q, 10, 100, 100)
+    assert (ids[ids != INVALID] < n).all()
+    # "prune" = 0: the M exact nearest are the links
+    cut = cp.CPHNSWIndex(dim, M=M, ef_construction=200, K=32, component_bytes=2 if dim > 128 else 1)
+    cut.set_param("exact_edges", 1)
+    cut.set_param("prune", 0)
+    cut.add_batch_parallel(base)
+    assert np.array_equal(cut.adjacency(), oracle.exact_candidates(base, M))
+
+
+def test_exact_edges_lift_recall_on_unclustered_data(cp, oracle):
+    # on vectors without cluster structure the code-distance kNN graph navigates poorly; exact links let the walk
+    # reach what the code can rank
+    base, q = synthetic.gaussian_sphere(30000, 300, 128, 5)
+    gt = oracle.ground_truth(q, base, 10)
+    rec = {}
+    for exact in (0, 1):
+        idx = make_index(cp, 128)
+        idx.set_param("exact_edges", exact)
+        idx.add_batch_parallel(base)
+        ids, _ = idx.search_and_rerank_batch(q, 10, 500, 500)
+        rec[exact] = oracle.recall_at_k(ids, gt, 10)
+    assert rec[1] > rec[0] + 0.1 and rec[1] > 0.8, rec
