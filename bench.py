@@ -53,6 +53,9 @@ def parse_args():
                     help="run on fvecs files (rows are normalised) instead of a synthetic workload")
     ap.add_argument("--search-kernel", type=int, default=0, choices=[0, 1, 2],
                     help="0 = the library's choice, 1 = one warp per query, 2 = two warps per query")
+    ap.add_argument("--K", type=int, default=None, help="code width (rotations); default: the workload's (32)")
+    ap.add_argument("--exact-edges", action="store_true",
+                    help="graph links chosen on the fp32 vectors (set_param exact_edges; single GPU builds)")
     ap.add_argument("--single-process", action="store_true",
                     help="drive all --gpus devices from this one process through the sharded C ABI (cphnsw_b200_sharded_*: "
                          "NCCL inside the library) instead of one torchrun rank per GPU; host pointers in and out")
@@ -120,6 +123,8 @@ def overrides(w, args):
         w["rerank_k"] = args.rerank_k
     if args.entry_scan is not None:
         w["entry_scan"] = args.entry_scan
+    if args.K is not None:
+        w["K"] = args.K
     return w
 
 
@@ -305,7 +310,7 @@ def b200_config(args, w, n, dim, nq, n_entry, knn_k):
     K, cb, M = w["K"], w["component_bytes"], w["M"]
     return {"workload": w["name"], "n_base": n, "dim": dim, "queries_per_rank": nq, "k": w["k"], "ef": w["ef"],
             "rerank_k": w["rerank_k"], "K": K, "component_bytes": cb, "M": M, "entry_scan": n_entry,
-            "k_entry": w.get("k_entry", 4), "knn_k": knn_k,
+            "k_entry": w.get("k_entry", 4), "knn_k": knn_k, "exact_edges": bool(getattr(args, "exact_edges", False)),
             "l2": "index (vectors+codes+adjacency = %.0f MB) larger than L2" % (n * (dim * 4 + K * cb + M * 4) / 1e6)}
 
 
@@ -431,6 +436,15 @@ def run_b200(args):
     del warm_codes, warm_cand
     codes_all, adj_all = sharded.build_sharded(stages, d_base[rb:re], n, rank, world, dist if world > 1 else None, knn_k, M,
                                                True, timers=Timer)
+    if args.exact_edges:
+        # links on the fp32 vectors: built by the library's own bulk build on this rank (not sharded), timed as a whole
+        with Timer("exact_edges_build"):
+            ex = cp.CPHNSWIndex(dim, M=M, ef_construction=w["ef_construction"], K=K, component_bytes=cb, device=local_rank)
+            ex.set_param("exact_edges", 1)
+            ex.set_param("knn_k", knn_k)
+            ex.add_batch_parallel(base)
+        adj_all = torch.from_numpy(ex.adjacency().view(np.int32)).to(dev)
+        ex.close()
     idx.check_device_status()
     # rows computed by other ranks against rows this GPU computes alone from the gathered codes: 8 blocks of 250 rows
     # spread over all shards
@@ -587,6 +601,8 @@ def run_b200(args):
         "allgather_codes_ms": stage_ms["allgather_codes"], "allgather_adjacency_ms": stage_ms["allgather_adjacency"],
         "scaling": "strong",
     }
+    if args.exact_edges:
+        build["exact_edges_build_ms_from_host_memory"] = stage_ms["exact_edges_build"]
 
     sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
     lanes = idx_sm_count * 128 * sm_mhz * 1e6  # fp32 add lanes of the GPU per second at the sampled clock
