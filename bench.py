@@ -605,23 +605,23 @@ def run_b200(args):
         build["exact_edges_build_ms_from_host_memory"] = stage_ms["exact_edges_build"]
 
     sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
-    lanes = idx_sm_count * 128 * sm_mhz * 1e6  # fp32 add lanes of the GPU per second at the sampled clock
+    lanes = world * idx_sm_count * 128 * sm_mhz * 1e6  # fp32 add lanes of all GPUs per second at the sampled clock
     roofline_build = {
         "encode": {"bound": "fp32-add pipe", "achieved": build["encode_fp32_addsub_per_s"], "peak": lanes, "unit": "add/s",
                    "frac": build["encode_fp32_addsub_per_s"] / lanes,
-                   "note": "K*3*P*log2(P) butterflies per vector over the measured stage time; peak = SMs x 128 lanes x sampled SM clock"},
+                   "note": "K*3*P*log2(P) butterflies per vector over the measured stage time; peak = GPUs x SMs x 128 lanes x sampled SM clock"},
         "knn_graph": None, "select_neighbors": None}
     if K == 32 and cb == 1:
         # bit-sliced kernel: 330 integer instructions per (row, 32 candidates) = 10.3 per pair on the ALU pipe, which
         # issues 64 lanes per SM and clock
-        alu = idx_sm_count * 64 * sm_mhz * 1e6
+        alu = world * idx_sm_count * 64 * sm_mhz * 1e6
         roofline_build["knn_graph"] = {"bound": "integer ALU pipe", "achieved": build["knn_pairs_per_s"] * 330.0 / 32.0, "peak": alu,
                                        "unit": "instr/s", "frac": build["knn_pairs_per_s"] * 330.0 / 32.0 / alu,
                                        "note": "10.3 integer instructions per pair (kernel source count); ncu sm__pipe_alu_cycles_active "
                                                "67.5 % on C2 at 1/4 size (profiles/knn_sliced_kernel_c2_quarter.md)"}
     sel_bytes = n * (knn_k * 4 + knn_k * code_row + M * 4.0)
-    roofline_build["select_neighbors"] = {"bound": "hbm gather", "achieved": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9, "peak": peak,
-                                          "unit": "GB/s", "frac": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9 / peak,
+    roofline_build["select_neighbors"] = {"bound": "hbm gather", "achieved": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9, "peak": peak * world,
+                                          "unit": "GB/s", "frac": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9 / (peak * world),
                                           "note": "k*4 + k*code_row gathered + M*4 written per node; gather-latency bound, 1 % of the build"}
 
     if rank == 0:

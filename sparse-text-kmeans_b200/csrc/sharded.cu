@@ -165,6 +165,42 @@ int exchange_blocks(cphnsw_b200_sharded* s, std::vector<unsigned char*>& bufs, u
     return 0;
 }
 
+// streams, communicators and one small rehearsal exchange: NCCL connects the peers and sets its channels up at the
+// first collective of a communicator, which would otherwise be paid inside the first build
+int init_exchange(cphnsw_b200_sharded* s) {
+    const int G = s->G;
+    s->streams.assign(G, nullptr);
+    s->comms.assign(G, nullptr);
+    for (int g = 0; g < G; ++g) {
+        CPB_CUDA(cudaSetDevice(s->devices[g]));
+        CPB_CUDA(cudaStreamCreateWithFlags(&s->streams[g], cudaStreamNonBlocking));
+    }
+    if (G == 1) return 0;
+    CPB_TRY(load_nccl(s->nccl));
+    const int rc = s->nccl.CommInitAll(s->comms.data(), G, s->devices.data());
+    if (rc != 0) {
+        set_error("ncclCommInitAll failed: %d (%s)", rc, s->nccl.GetErrorString ? s->nccl.GetErrorString(rc) : "?");
+        for (auto& c : s->comms) c = nullptr;
+        return CPHNSW_B200_E_CUDA;
+    }
+    std::vector<DevBuf> buf(G);
+    std::vector<unsigned char*> p(G);
+    for (uint64_t rows : {uint64_t(G) * 64, uint64_t(G) * 64 + 1}) {  // equal blocks (all-gather), unequal (broadcasts)
+        for (int g = 0; g < G; ++g) {
+            CPB_CUDA(cudaSetDevice(s->devices[g]));
+            CPB_TRY(buf[g].reserve(rows * 64));
+            CPB_CUDA(cudaMemset(buf[g].p, 0, rows * 64));
+            p[g] = buf[g].as<unsigned char>();
+        }
+        CPB_TRY(exchange_blocks(s, p, rows, 64));
+    }
+    for (int g = 0; g < G; ++g) {
+        CPB_CUDA(cudaSetDevice(s->devices[g]));
+        buf[g].release();
+    }
+    return 0;
+}
+
 }  // namespace
 
 extern "C" {
@@ -200,21 +236,7 @@ int cphnsw_b200_sharded_create(uint64_t dim, uint32_t K, uint32_t component_byte
         if (rc != 0) return rc;
         s->h.push_back(h);
     }
-    s->streams.assign(n_gpus, nullptr);
-    s->comms.assign(n_gpus, nullptr);
-    for (int g = 0; g < n_gpus; ++g) {
-        CPB_CUDA(cudaSetDevice(s->devices[g]));
-        CPB_CUDA(cudaStreamCreateWithFlags(&s->streams[g], cudaStreamNonBlocking));
-    }
-    if (n_gpus > 1) {
-        CPB_TRY(load_nccl(s->nccl));
-        const int rc = s->nccl.CommInitAll(s->comms.data(), n_gpus, s->devices.data());
-        if (rc != 0) {
-            set_error("ncclCommInitAll failed: %d (%s)", rc, s->nccl.GetErrorString ? s->nccl.GetErrorString(rc) : "?");
-            for (auto& c : s->comms) c = nullptr;
-            return CPHNSW_B200_E_CUDA;
-        }
-    }
+    CPB_TRY(init_exchange(s.get()));
     *out = s.release();
     return 0;
 }
@@ -239,21 +261,7 @@ int cphnsw_b200_sharded_load(const char* path, int n_gpus, const int* devices, c
         CPB_TRY(cphnsw_b200_load(path, s->devices[g], &h));
         s->h.push_back(h);
     }
-    s->streams.assign(n_gpus, nullptr);
-    s->comms.assign(n_gpus, nullptr);
-    for (int g = 0; g < n_gpus; ++g) {
-        CPB_CUDA(cudaSetDevice(s->devices[g]));
-        CPB_CUDA(cudaStreamCreateWithFlags(&s->streams[g], cudaStreamNonBlocking));
-    }
-    if (n_gpus > 1) {
-        CPB_TRY(load_nccl(s->nccl));
-        const int rc = s->nccl.CommInitAll(s->comms.data(), n_gpus, s->devices.data());
-        if (rc != 0) {
-            set_error("ncclCommInitAll failed: %d (%s)", rc, s->nccl.GetErrorString ? s->nccl.GetErrorString(rc) : "?");
-            for (auto& c : s->comms) c = nullptr;
-            return CPHNSW_B200_E_CUDA;
-        }
-    }
+    CPB_TRY(init_exchange(s.get()));
     *out = s.release();
     return 0;
 }
