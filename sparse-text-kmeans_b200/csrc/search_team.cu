@@ -171,25 +171,23 @@ __device__ __forceinline__ void tier_admit(TierList& T, float d, uint32_t id, in
     // later buckets, up to the one holding position wcap - 1: take the predecessor's last element
     // at the front, in the slot of the own last element, which moves on
     const int wb = int(T.wcap - 1) >> 5;
-    if (b < wb) {  // (an admission into W's last bucket, the common case, pushes nothing further)
-        const bool casc = lane > b && lane <= wb;
-        const int last_slot = (lane & 31) * 32 + ((T.head + 31) & 31);
-        float ld = out_d;
-        uint32_t li = out_i;
-        if (casc) {
-            ld = T.d[last_slot];
-            li = T.id[last_slot];
-        }
-        const float in_d = __shfl_up_sync(kFull, ld, 1);  // lane b passes on out_d
-        const uint32_t in_i = __shfl_up_sync(kFull, li, 1);
-        if (casc) {
-            T.d[last_slot] = in_d;
-            T.id[last_slot] = in_i;
-            T.head = (T.head + 31) & 31;
-            const int nl = lane * 32 + ((T.head + 31) & 31);
-            T.max_d = T.d[nl];
-            T.max_i = T.id[nl];
-        }
+    const bool casc = lane > b && lane <= wb;
+    const int last_slot = (lane & 31) * 32 + ((T.head + 31) & 31);
+    float ld = out_d;
+    uint32_t li = out_i;
+    if (casc) {
+        ld = T.d[last_slot];
+        li = T.id[last_slot];
+    }
+    const float in_d = __shfl_up_sync(kFull, ld, 1);  // lane b passes on out_d
+    const uint32_t in_i = __shfl_up_sync(kFull, li, 1);
+    if (casc) {
+        T.d[last_slot] = in_d;
+        T.id[last_slot] = in_i;
+        T.head = (T.head + 31) & 31;
+        const int nl = lane * 32 + ((T.head + 31) & 31);
+        T.max_d = T.d[nl];
+        T.max_i = T.id[nl];
     }
     if (lane == b) {
         T.max_d = top_d;
