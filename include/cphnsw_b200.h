@@ -203,7 +203,7 @@ int cphnsw_b200_get_entry_ids(const cphnsw_b200_index* h, uint32_t* ids_out, uin
 /* Batched CPHNSWIndex::search(q,k,ef) (evaluation/eval_sift.cpp:387; engine
  * include/cphnsw/search/search_engine.hpp:86-193): graph walk under the asymmetric CP score,
  * ids uint32[nq][k], dists float[nq][k] ascending (negative scores), padded 0xFFFFFFFF / +inf.
- * Beam width is max(ef, k).  stats (optional) uint32[nq][2] = expansions, distance evaluations. */
+ * Beam width is max(ef, k), at most 4096 (wider than 1024: the one-warp kernel).  stats (optional) uint32[nq][2] = expansions, distance evaluations. */
 int cphnsw_b200_search_batch(cphnsw_b200_index* h, const float* q, uint64_t nq, uint32_t k,
                              uint32_t ef, uint32_t* ids_out, float* dists_out, uint32_t* stats_out);
 

@@ -256,8 +256,8 @@ int do_search(cphnsw_b200_index* h, const float* q, bool q_on_device, uint64_t n
         set_error("search_and_rerank: rerank_k (%u) must be >= k (%u)", rerank_k, k);
         return CPHNSW_B200_E_INVALID;
     }
-    if (beam > 1024) {
-        set_error("search: beam width max(ef, k, rerank_k) must be <= 1024 (got %u)", beam);
+    if (beam > kMaxBeam) {
+        set_error("search: beam width max(ef, k, rerank_k) must be <= %u (got %u)", kMaxBeam, beam);
         return CPHNSW_B200_E_INVALID;
     }
     if (nq == 0) return 0;

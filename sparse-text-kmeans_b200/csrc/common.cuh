@@ -98,6 +98,9 @@ struct DevBuf {
 // evaluation/eval_sift.cpp:380-387).  `wide` contexts own visited slots for a launch that fills the GPU,
 // narrow ones for launches of up to kNarrowQueries queries, one block per query.
 constexpr uint32_t kNarrowQueries = 32;
+// widest beam of a search: the one-warp kernel keeps W as one sorted array of up to this many members in shared
+// memory (32 KB at 4,096); the two-warp kernel's tiered W holds 1,024 and is used up to that width
+constexpr uint32_t kMaxBeam = 4096;
 struct SearchCtx {
     cudaStream_t stream = nullptr;
     cudaEvent_t done = nullptr;  // recorded behind the last work that used this scratch on a caller's stream

@@ -114,9 +114,14 @@ __global__ void search_kernel(SearchArgs a) {
                 const bool in = uint32_t(lane) * stride < count;
                 const bool less = in && key_less(sd[e], sid[e] & kIdMask, d, id);
                 const uint32_t b = __popc(__ballot_sync(kFull, less));  // blocks entirely below
-                const uint32_t j = b * stride + lane;
-                const bool less2 = b < 32 && uint32_t(lane) < stride && j < count && key_less(sd[j], sid[j] & kIdMask, d, id);
-                p = min(count, b * stride) + __popc(__ballot_sync(kFull, less2));
+                // second round inside block b: one pass of 32 members, more for a beam wider than 1,024
+                uint32_t inside = 0;
+                for (uint32_t o = 0; o < stride; o += 32) {
+                    const uint32_t j = b * stride + o + lane;
+                    const bool less2 = b < 32 && o + uint32_t(lane) < stride && j < count && key_less(sd[j], sid[j] & kIdMask, d, id);
+                    inside += __popc(__ballot_sync(kFull, less2));
+                }
+                p = min(count, b * stride) + inside;
             }
             // shift [p, end) up by one, highest chunk first; a full W drops its last member
             const int end = int(count == wcap ? wcap - 1 : count);
@@ -496,8 +501,8 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
                   cudaStream_t st, const void* d_qcodes, int scan_only) {
     const bool sym = d_qcodes != nullptr;  // symmetric code-distance walk (search_multiprobe)
     if (nq == 0) return 0;
-    if (beam > 1024) {
-        set_error("search: beam width max(ef, k, rerank_k) must be <= 1024 (got %u)", beam);
+    if (beam > kMaxBeam) {
+        set_error("search: beam width max(ef, k, rerank_k) must be <= %u (got %u)", kMaxBeam, beam);
         return CPHNSW_B200_E_INVALID;
     }
     if (nq > 0xffffffffull) {
@@ -561,7 +566,7 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
     LaunchTimer timer(h, kKernelSearch, st);
 
     // two warps per query: asymmetric metric, table in shared memory, one adjacency row per warp
-    const bool team_ok = !sym && !scan_only && (c.table_smem || h->K <= 32) && h->M <= 32 && h->k_entry <= 128;
+    const bool team_ok = beam <= 1024 && !sym && !scan_only && (c.table_smem || h->K <= 32) && h->M <= 32 && h->k_entry <= 128;
     a.table_in_smem = c.table_smem ? 1 : 0;
     if (h->search_kernel == 2 && !team_ok && !sym) {
         set_error("search_kernel=2 needs the asymmetric metric, M <= 32 and K*P*4 <= 32 KB or K <= 32");
