@@ -501,7 +501,23 @@ __global__ void search_team_kernel(SearchArgs a) {
                     offer(id, id < a.n);
                 }
             } else {
-                const uint32_t P0 = mb[1], P1 = mb[2], P2 = mb[3], snap = mb[5];
+                // The load the turn waits for goes out first: the visited bytes of the neighbours of P0, the node
+                // selected next (its row is normally in registers since the last turn).  Whether the row is already
+                // prepared is only known a few instructions later; the bytes are asked for either way.
+                const uint32_t P0 = mb[1];
+                uint32_t u_id = kInvalidNode;
+                if (P0 != kInvalidNode) {
+                    if (held_key == P0) u_id = held_id;
+                    else if (lane < a.M) u_id = __ldg(a.adj + size_t(P0) * a.M + lane);
+                }
+                bool u_first = u_id < a.n;
+                if (!a.rows_distinct) {
+                    const uint32_t grp = __match_any_sync(kFull, u_id);
+                    u_first = u_first && (__ffs(grp) - 1) == lane;
+                }
+                uint32_t u_vis = 0;
+                if (u_first) u_vis = __ldcg(vis + u_id);
+                const uint32_t P1 = mb[2], P2 = mb[3], snap = mb[5];
                 // adjacency row of the node three expansions away towards L2
                 if (lane == 0 && P2 != kInvalidNode) {
                     prefetch_l2(a.adj + size_t(P2) * a.M);
@@ -511,24 +527,10 @@ __global__ void search_team_kernel(SearchArgs a) {
                 const bool do_u = P0 != kInvalidNode && !in_r(P0);  // the node selected next: prepare it now
                 const bool do_v = P1 != kInvalidNode && !in_r(P1);  // the one after: bring its data closer
                 // the row of P1 is loaded now and kept for the next turn, when P1 has become P0
-                uint32_t u_id = kInvalidNode, v_id = kInvalidNode;
+                uint32_t v_id = kInvalidNode;
                 if (do_v) {
                     if (held_key == P1) v_id = held_id;
                     else if (lane < a.M) v_id = __ldg(a.adj + size_t(P1) * a.M + lane);
-                }
-                if (do_u) {
-                    if (held_key == P0) u_id = held_id;
-                    else if (lane < a.M) u_id = __ldg(a.adj + size_t(P0) * a.M + lane);
-                }
-                uint32_t u_vis = 0;
-                bool u_first = false;
-                if (do_u) {
-                    u_first = u_id < a.n;
-                    if (!a.rows_distinct) {
-                        const uint32_t grp = __match_any_sync(kFull, u_id);
-                        u_first = u_first && (__ffs(grp) - 1) == lane;
-                    }
-                    if (u_first) u_vis = __ldcg(vis + u_id);
                 }
                 if (do_u) {
                     // a slot whose node is neither being consumed nor announced
