@@ -26,6 +26,10 @@ def all_gather_rows(local, n, rank, world, dist=None):
     import torch
     if world == 1:
         return local
+    if local.dtype == torch.int16:
+        # NCCL's torch binding moves no 16-bit integers (two-byte codes): the rows travel as bytes
+        as_bytes = local.contiguous().view(torch.uint8)
+        return all_gather_rows(as_bytes, n, rank, world, dist).view(torch.int16)
     counts = [shard_range(n, r, world)[1] - shard_range(n, r, world)[0] for r in range(world)]
     width = max(counts)
     pad = torch.zeros((width,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)

@@ -27,20 +27,26 @@ class OracleStages:
 
     def encode(self, x):
         import torch
-        return torch.from_numpy(self.O.encode(x.numpy(), self.K, self.cb, self.signs))
+        codes = self.O.encode(x.numpy(), self.K, self.cb, self.signs)
+        # two-byte codes travel as int16 tensors, as in CudaStages
+        return torch.from_numpy(codes.view(np.int16) if self.cb == 2 else codes)
+
+    def _codes(self, codes_all):
+        a = codes_all.numpy()
+        return a.view(np.uint16) if self.cb == 2 else a
 
     def knn(self, codes_all, k, rb, re):
         import torch
-        nb, _ = self.O.knn_graph(codes_all.numpy(), k, rb, re)
+        nb, _ = self.O.knn_graph(self._codes(codes_all), k, rb, re)
         return torch.from_numpy(nb.astype(np.int64))
 
     def select(self, codes_all, cand, k, rb, re, M, keep_pruned):
         import torch
-        adj = self.O.select_neighbors(codes_all.numpy(), cand.numpy().astype(np.uint32), M, keep_pruned, row_begin=rb)
+        adj = self.O.select_neighbors(self._codes(codes_all), cand.numpy().astype(np.uint32), M, keep_pruned, row_begin=rb)
         return torch.from_numpy(adj.astype(np.int64))
 
 
-def _worker(rank, world, port, n, out_dir):
+def _worker(rank, world, port, n, cb, out_dir):
     for p in (os.path.join(ROOT, "sparse-text-kmeans_b200"), os.path.join(ROOT, "oracle")):
         sys.path.insert(0, p)
     import torch
@@ -50,7 +56,7 @@ def _worker(rank, world, port, n, out_dir):
     dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
     try:
         base, _ = synthetic.gaussian_mixture(n, 4, 32, 5, 0.3, 77)
-        K, cb, M, knn_k = 16, 1, 8, 16
+        K, M, knn_k = 16, 8, 16
         signs = O.sign_tables(32, K, 42)
         rb, re = sharded.shard_range(n, rank, world)
         stages = OracleStages(O, signs, K, cb)
@@ -61,19 +67,20 @@ def _worker(rank, world, port, n, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n", [401, 512])  # uneven and even row blocks
-def test_sharded_build_equals_single_process(oracle, tmp_path, n):
+@pytest.mark.parametrize("n,cb", [(401, 1), (512, 1), (401, 2)])  # uneven and even row blocks; one- and two-byte codes
+def test_sharded_build_equals_single_process(oracle, tmp_path, n, cb):
     import torch.multiprocessing as mp
     from cphnsw_b200 import sharded, synthetic
     world = 2
-    mp.spawn(_worker, args=(world, _free_port(), n, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), n, cb, str(tmp_path)), nprocs=world, join=True)
     base, _ = synthetic.gaussian_mixture(n, 4, 32, 5, 0.3, 77)
     signs = oracle.sign_tables(32, 16, 42)
-    codes = oracle.encode(base, 16, 1, signs)
+    codes = oracle.encode(base, 16, cb, signs)
     cand, _ = oracle.knn_graph(codes, 16)
     adj = oracle.select_neighbors(codes, cand, 8, True)
     for r in range(world):
-        assert np.array_equal(np.load(tmp_path / ("codes_%d.npy" % r)), codes)
+        got = np.load(tmp_path / ("codes_%d.npy" % r))
+        assert np.array_equal(got.view(np.uint16) if cb == 2 else got, codes)
         assert np.array_equal(np.load(tmp_path / ("adj_%d.npy" % r)).astype(np.uint32), adj)
 
 
