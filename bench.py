@@ -573,11 +573,15 @@ def run_b200(args):
                        + rr * dim * 4 + k * 8)             # rerank gather + results
     peak, peak_kind = measured_peaks()
     search_ms_per_launch = search_ms / max(1, search_launches)
-    achieved = bytes_per_query * nq / (search_ms_per_launch * 1e-3) / 1e9
+    # a batch beyond the library's visited-slot budget is served by several launches: units per launch, not per step
+    q_per_launch = nq * args.steps / max(1, search_launches)
+    achieved = bytes_per_query * q_per_launch / (search_ms_per_launch * 1e-3) / 1e9
     # the library takes the two-warp kernel when the query table fits shared memory and M <= 32
-    team = args.search_kernel != 1 and (K * idx.padded_dim * 4 <= 32 * 1024 or K <= 32) and M <= 32
+    small_table = K * idx.padded_dim * 4 <= 32 * 1024
+    team = M <= 32 and max(ef, rerank_k) <= 1024 and (small_table if args.search_kernel == 0 else
+                                                     args.search_kernel == 2 and (small_table or K <= 32))
     dram_per_query = NCU_SEARCH_DRAM_BYTES_PER_QUERY if team else NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP
-    traffic = dram_per_query * nq if w["name"] == "C2" else None
+    traffic = dram_per_query * q_per_launch if w["name"] == "C2" else None
     roofline = {"kernel": "search_team_kernel" if team else "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": "of " + peak_kind,
                 "traffic": traffic,
@@ -585,7 +589,7 @@ def run_b200(args):
                 # really asks of HBM (it is bound by dependent latencies, not by bandwidth)
                 "frac_measured_dram": (traffic / (search_ms_per_launch * 1e-3) / 1e9 / peak) if traffic else None,
                 "traffic_note": "bytes per launch, scaled by queries from the ncu capture of C2 at 1/4 size",
-                "ms_per_launch": search_ms_per_launch, "algorithmic_bytes_per_query": bytes_per_query,
+                "ms_per_launch": search_ms_per_launch, "queries_per_launch": q_per_launch, "algorithmic_bytes_per_query": bytes_per_query,
                 "expansions_per_query": exp_mean, "distance_evals_per_query": evals_mean,
                 "share_of_step": search_ms / (ms_total if ms_total else 1.0),
                 "query_encode_ms_per_step": qenc_ms / args.steps}

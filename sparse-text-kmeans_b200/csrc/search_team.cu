@@ -210,6 +210,72 @@ __device__ __forceinline__ void tier_admit_lanes(TierList& T, uint32_t m, bool m
     }
 }
 
+// ---- filling W (walker only) -----------------------------------------------------------------------
+// Until W holds `wcap` members every scored candidate is admitted, so nothing has to be ranked: the walk
+// starts with W as a plain array (live members in any order in [0, count), fillers behind), appends a row's
+// candidates in one step and selects the closest unexpanded member by a scan.  The array is sorted once, when a
+// row would overflow it, and the tiered list takes over.  The selected nodes and the final W are the same either
+// way (the closest unexpanded member under the total order (distance, id); the wcap best of everything scored).
+constexpr uint32_t kFillMin = 256;  // free places in W at the start of the walk from which the plain array pays (measured)
+
+// bucket rotations undone: logical order becomes slot order (flags kept)
+__device__ __forceinline__ void tier_flatten(TierList& T, int lane) {
+    for (int b = 0; b < T.nb; ++b) {
+        const int hb = __shfl_sync(kFull, T.head, b);
+        if (hb == 0) continue;
+        const int from = b * 32 + ((hb + lane) & 31);
+        const float v = T.d[from];
+        const uint32_t w = T.id[from];
+        __syncwarp();
+        T.d[b * 32 + lane] = v;
+        T.id[b * 32 + lane] = w;
+    }
+    __syncwarp();
+    T.head = 0;
+}
+
+// bitonic sort of n (a power of two) pairs by (distance, id without the expanded flag); the flag travels with the id
+__device__ __forceinline__ void warp_sort_flagged(float* d, uint32_t* id, int n, int lane) {
+    for (int k2 = 2; k2 <= n; k2 <<= 1) {
+        for (int j = k2 >> 1; j > 0; j >>= 1) {
+            for (int t = lane; t < n / 2; t += 32) {
+                const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                const int hi = lo | j;
+                const bool asc = (lo & k2) == 0;
+                const float dl = d[lo], dh = d[hi];
+                const uint32_t il = id[lo], ih = id[hi];
+                const bool hi_less = key_less(dh, ih & kIdMask, dl, il & kIdMask);
+                if (hi_less == asc) {
+                    d[lo] = dh;
+                    id[lo] = ih;
+                    d[hi] = dl;
+                    id[hi] = il;
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// the plain array becomes the tiered list: sorted, heads zero, cursor on the first unexpanded member
+__device__ __forceinline__ void tier_from_plain(TierList& T, int lane) {
+    int n = 32;
+    while (n < int(T.count)) n <<= 1;
+    __syncwarp();
+    warp_sort_flagged(T.d, T.id, n, lane);
+    tier_reset_heads(T, lane);
+    T.cur = T.count;
+    for (uint32_t base = 0; base < T.count; base += 32) {
+        const uint32_t ei = T.id[base + lane];
+        const uint32_t un = __ballot_sync(kFull, !(ei & kExpanded) && base + lane < T.count);
+        if (un) {
+            T.cur = base + uint32_t(__ffs(un) - 1);
+            break;
+        }
+    }
+    tier_refresh_worst(T);
+}
+
 // TSM: the query table is copied to shared memory (a compile-time fact, so that its reads stay
 // shared-memory loads); otherwise it is read in place.
 // No register cap: holding the kernel to 64 registers (15 teams per SM instead of 11 when the table is read in
@@ -293,6 +359,43 @@ __global__ void search_team_kernel(SearchArgs a) {
         T.max_i = kInvalidNode;
         uint32_t total_marks = 0;  // walker: nodes marked since the query began (ring write position)
 
+        // admissions go to the plain array while W is filling, to the tiered list afterwards
+        bool filling = false;
+        auto admit_one = [&](float d, uint32_t id) {  // (d, id) known to every lane
+            if (filling) {
+                if (T.count < T.wcap) {
+                    if (lane == 0) {
+                        sd[T.count] = d;
+                        sid[T.count] = id;
+                    }
+                    ++T.count;
+                    __syncwarp();
+                    return;
+                }
+                tier_from_plain(T, lane);
+                filling = false;
+            }
+            tier_admit(T, d, id, lane);
+        };
+        auto admit_lanes = [&](uint32_t m, bool mine, float dist, uint32_t id) {
+            if (filling) {
+                const uint32_t nf = uint32_t(__popc(m));
+                if (T.count + nf <= T.wcap) {
+                    if (mine) {
+                        const uint32_t pos = T.count + uint32_t(__popc(m & ((1u << lane) - 1u)));
+                        sd[pos] = dist;
+                        sid[pos] = id;
+                    }
+                    T.count += nf;
+                    __syncwarp();
+                    return;
+                }
+                tier_from_plain(T, lane);
+                filling = false;
+            }
+            tier_admit_lanes(T, m, mine, dist, id, lane);
+        };
+
         // walker alone: visited test-and-set of one row, scoring, admission
         // (search_engine.hpp:153-177); the marked ids go to the ring
         auto offer = [&](uint32_t id, bool in_range) {
@@ -327,11 +430,11 @@ __global__ void search_team_kernel(SearchArgs a) {
                 }
 #pragma unroll
                 for (int f = 0; f < kCoopMax; ++f)
-                    if (f < nf) tier_admit(T, asym_distance_coop(table, a.K, a.P, comp[f], lane), cid[f], lane);
+                    if (f < nf) admit_one(asym_distance_coop(table, a.K, a.P, comp[f], lane), cid[f]);
             } else {
                 float dist = 0.0f;
                 if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
-                tier_admit_lanes(T, m, fresh, dist, id, lane);
+                admit_lanes(m, fresh, dist, id);
             }
         };
 
@@ -416,12 +519,75 @@ __global__ void search_team_kernel(SearchArgs a) {
         // the node to expand and announces it together with the next three unexpanded members of W;
         // after it the walker consumes the prepared row of that node (if the scout has one) while the
         // scout moves the announced nodes one stage further.
+        if (role == 0 && T.wcap >= T.count + kFillMin) {
+            tier_flatten(T, lane);
+            filling = true;
+        }
         uint32_t rkey = kInvalidNode;  // scout: lane j < kSlots holds the node of result slot j
         uint32_t held_key = kInvalidNode, held_id = kInvalidNode;  // scout: adjacency row loaded at the previous turn
         uint32_t step = 0;
         while (true) {
             volatile uint32_t* mb = mail + kPostBase + (step & 1) * 8;  // this step's announcement
-            if (role == 0) {
+            if (role == 0 && filling) {
+                // the two closest unexpanded members of the plain array: the first is expanded now, the second announced
+                float b1d = INFINITY, b2d = INFINITY;
+                uint32_t b1i = kInvalidNode, b2i = kInvalidNode;
+                int b1s = 0;
+                for (uint32_t p = lane; p < T.count; p += 32) {
+                    const float v = sd[p];
+                    const uint32_t w = sid[p];
+                    if (!(w & kExpanded)) {
+                        if (key_less(v, w, b1d, b1i)) {
+                            b2d = b1d;
+                            b2i = b1i;
+                            b1d = v;
+                            b1i = w;
+                            b1s = int(p);
+                        } else if (key_less(v, w, b2d, b2i)) {
+                            b2d = v;
+                            b2i = w;
+                        }
+                    }
+                }
+                float md = b1d;
+                uint32_t mi = b1i;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) {
+                    const float od = __shfl_xor_sync(kFull, md, o);
+                    const uint32_t oi = __shfl_xor_sync(kFull, mi, o);
+                    if (key_less(od, oi, md, mi)) {
+                        md = od;
+                        mi = oi;
+                    }
+                }
+                if (mi != kInvalidNode) {
+                    const bool win = b1i == mi;  // ids are unique in W
+                    if (win) sid[b1s] = mi | kExpanded;
+                    ++nexp;
+                    float xd = win ? b2d : b1d;
+                    uint32_t xi = win ? b2i : b1i;
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) {
+                        const float od = __shfl_xor_sync(kFull, xd, o);
+                        const uint32_t oi = __shfl_xor_sync(kFull, xi, o);
+                        if (key_less(od, oi, xd, xi)) {
+                            xd = od;
+                            xi = oi;
+                        }
+                    }
+                    if (lane == 0) {
+                        mb[0] = mi;
+                        mb[1] = xi;
+                        mb[2] = kInvalidNode;
+                        mb[3] = kInvalidNode;
+                        mb[4] = 0;
+                        mb[5] = total_marks;
+                    }
+                    __syncwarp();
+                } else if (lane == 0) {
+                    mb[4] = 1;
+                }
+            } else if (role == 0) {
                 if (T.cur < T.count) {
                     // closest member of W that has not been expanded (search_engine.hpp:121-123)
                     const int cb = int(T.cur >> 5), cl = int(T.cur & 31);
@@ -495,7 +661,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                     if (fresh) ring[(total_marks + __popc(fm & ((1u << lane) - 1u))) & (kRing - 1)] = id;
                     total_marks += __popc(fm);
                     nevals += __popc(fm);
-                    tier_admit_lanes(T, fm, fresh, dist, id, lane);
+                    admit_lanes(fm, fresh, dist, id);
                 } else {
                     const uint32_t id = lane < a.M ? __ldg(a.adj + size_t(node) * a.M + lane) : kInvalidNode;
                     offer(id, id < a.n);
@@ -587,6 +753,7 @@ __global__ void search_team_kernel(SearchArgs a) {
 
         // ---- rerank (both warps) and output (walker)
         if (role == 0) {
+            if (filling) tier_from_plain(T, lane);  // W never filled: sorted now
             // back to a flat list, expanded flags dropped
             const int nbl = int(T.count + 31) >> 5;
             for (int b = 0; b < nbl; ++b) {
