@@ -182,5 +182,28 @@ __device__ __forceinline__ void warp_sort_smem(float* d, uint32_t* id, int n, in
     }
 }
 
+// bitonic sort of n (a power of two) pairs by (distance, id without the expanded flag); the flag travels with the id
+__device__ __forceinline__ void warp_sort_flagged(float* d, uint32_t* id, int n, int lane) {
+    for (int k2 = 2; k2 <= n; k2 <<= 1) {
+        for (int j = k2 >> 1; j > 0; j >>= 1) {
+            for (int t = lane; t < n / 2; t += 32) {
+                const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                const int hi = lo | j;
+                const bool asc = (lo & k2) == 0;
+                const float dl = d[lo], dh = d[hi];
+                const uint32_t il = id[lo], ih = id[hi];
+                const bool hi_less = key_less(dh, ih & kIdMask, dl, il & kIdMask);
+                if (hi_less == asc) {
+                    d[lo] = dh;
+                    id[lo] = ih;
+                    d[hi] = dl;
+                    id[hi] = il;
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
 }  // namespace srch
 }  // namespace cpb

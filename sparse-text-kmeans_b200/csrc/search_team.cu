@@ -234,29 +234,6 @@ __device__ __forceinline__ void tier_flatten(TierList& T, int lane) {
     T.head = 0;
 }
 
-// bitonic sort of n (a power of two) pairs by (distance, id without the expanded flag); the flag travels with the id
-__device__ __forceinline__ void warp_sort_flagged(float* d, uint32_t* id, int n, int lane) {
-    for (int k2 = 2; k2 <= n; k2 <<= 1) {
-        for (int j = k2 >> 1; j > 0; j >>= 1) {
-            for (int t = lane; t < n / 2; t += 32) {
-                const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));
-                const int hi = lo | j;
-                const bool asc = (lo & k2) == 0;
-                const float dl = d[lo], dh = d[hi];
-                const uint32_t il = id[lo], ih = id[hi];
-                const bool hi_less = key_less(dh, ih & kIdMask, dl, il & kIdMask);
-                if (hi_less == asc) {
-                    d[lo] = dh;
-                    id[lo] = ih;
-                    d[hi] = dl;
-                    id[hi] = il;
-                }
-            }
-            __syncwarp();
-        }
-    }
-}
-
 // the plain array becomes the tiered list: sorted, heads zero, cursor on the first unexpanded member
 __device__ __forceinline__ void tier_from_plain(TierList& T, int lane) {
     int n = 32;
@@ -523,6 +500,7 @@ __global__ void search_team_kernel(SearchArgs a) {
             tier_flatten(T, lane);
             filling = true;
         }
+        uint32_t low_rows = 0;  // walker: consecutive expansions that brought at most two new members
         uint32_t rkey = kInvalidNode;  // scout: lane j < kSlots holds the node of result slot j
         uint32_t held_key = kInvalidNode, held_id = kInvalidNode;  // scout: adjacency row loaded at the previous turn
         uint32_t step = 0;
@@ -637,6 +615,7 @@ __global__ void search_team_kernel(SearchArgs a) {
             if (mb[4]) break;
             const uint32_t node = mb[0];
             if (role == 0) {
+                const uint32_t evals_before = nevals;
                 // result slot of this node, if the scout got that far
                 uint32_t key = kInvalidNode;
                 if (lane < kSlots) key = mail[kKeyBase + lane];
@@ -665,6 +644,15 @@ __global__ void search_team_kernel(SearchArgs a) {
                 } else {
                     const uint32_t id = lane < a.M ? __ldg(a.adj + size_t(node) * a.M + lane) : kInvalidNode;
                     offer(id, id < a.n);
+                }
+                // the plain array is left as soon as it stops paying: once rows bring a member or two, ranking them
+                // costs less than scanning the array at every selection
+                if (filling) {
+                    low_rows = nevals - evals_before <= 2 ? low_rows + 1 : 0;
+                    if (low_rows >= 3) {
+                        tier_from_plain(T, lane);
+                        filling = false;
+                    }
                 }
             } else {
                 // The load the turn waits for goes out first: the visited bytes of the neighbours of P0, the node
