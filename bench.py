@@ -32,7 +32,7 @@ METRIC = "batch-search QPS @ recall@10>=0.9 (search_and_rerank)"
 # DRAM bytes (read + written) per query of search_team_kernel, from the ncu capture summarised in
 # profiles/search_team_kernel_c2_quarter.md (C2 at 1/4 size, 2,500 queries: 1.281 GB + 0.080 GB per launch);
 # the traffic per query does not depend on the number of queries, so a launch of nq queries moves nq times this
-NCU_SEARCH_DRAM_BYTES_PER_QUERY = 544e3
+NCU_SEARCH_DRAM_BYTES_PER_QUERY = 537e3
 # the same for the one-warp search_kernel (profiles/search_kernel_c2_quarter.md: 1.215 GB + 0.080 GB per launch)
 NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP = 518e3
 
