@@ -30,7 +30,10 @@ constexpr int kP128 = 128;
 constexpr int kTileVecs = 128;          // vectors per block = threads per block
 // Padded row of the staged tile: thread t reads bank (t + i) & 31.  (Measured and dropped: a 132-float stride with
 // 128-bit reloads, 3.875 ms per 1M vectors against 3.835 ms, and on top of it the diagonal applied as a sign-bit XOR
-// on the integer pipe with plain first-stage butterflies, 3.883 ms.)
+// on the integer pipe with plain first-stage butterflies, 3.883 ms.  Also measured and dropped: the diagonal folded
+// into every stage - block multipliers t = s[i] * s[i + h], butterflies fma(+-t, y, x), one overall sign per layer
+// left for the end - which is bit-equal and saves the 64 multiplies per layer, 3.894 ms: the three-operand
+// instructions cost what the saved ones gave.)
 constexpr int kTileStride = kP128 + 1;
 
 template <int H>
