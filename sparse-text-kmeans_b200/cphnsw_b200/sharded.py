@@ -32,12 +32,13 @@ def all_gather_rows(local, n, rank, world, dist=None):
         return all_gather_rows(as_bytes, n, rank, world, dist).view(torch.int16)
     counts = [shard_range(n, r, world)[1] - shard_range(n, r, world)[0] for r in range(world)]
     width = max(counts)
+    out = torch.empty((world * width,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    if all(c == width for c in counts):  # equal blocks travel as they are
+        dist.all_gather_into_tensor(out, local.contiguous())
+        return out
     pad = torch.zeros((width,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     pad[: local.shape[0]] = local
-    out = torch.empty((world * width,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(out, pad)
-    if all(c == width for c in counts):
-        return out
     return torch.cat([out[r * width: r * width + counts[r]] for r in range(world)], dim=0)
 
 
