@@ -343,7 +343,7 @@ def full_base_size(name):
 def full_entry_scan(args):
     if args.entry_scan is not None:
         return args.entry_scan
-    return {"C2": 8192, "C5": 8192, "C4": 65536}.get(args.workload, 4)
+    return {"C2": 8192, "C3": 8192, "C5": 8192, "C4": 65536}.get(args.workload, 4)
 
 
 def run_b200(args):
@@ -577,9 +577,7 @@ def run_b200(args):
     q_per_launch = nq * args.steps / max(1, search_launches)
     achieved = bytes_per_query * q_per_launch / (search_ms_per_launch * 1e-3) / 1e9
     # the library takes the two-warp kernel when the query table fits shared memory and M <= 32
-    small_table = K * idx.padded_dim * 4 <= 32 * 1024
-    team = M <= 32 and max(ef, rerank_k) <= 1024 and (small_table if args.search_kernel == 0 else
-                                                     args.search_kernel == 2 and (small_table or K <= 32))
+    team = args.search_kernel != 1 and M <= 32 and max(ef, rerank_k) <= 1024 and (K * idx.padded_dim * 4 <= 32 * 1024 or K <= 32)
     dram_per_query = NCU_SEARCH_DRAM_BYTES_PER_QUERY if team else NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP
     traffic = dram_per_query * q_per_launch if w["name"] == "C2" else None
     roofline = {"kernel": "search_team_kernel" if team else "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

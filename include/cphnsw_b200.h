@@ -84,8 +84,8 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *   "knn_kernel" (0 = pick, 1 = byte-wise distance, 2 = bit-sliced distance; K = 16/32/64 with uint8 codes or
  *                 in binary-code mode, K = 16/32 with uint16 codes of padded dim 1024, and one-byte binary codes of
  *                 any K <= 120 that is a multiple of 8, residual bits included when the primary part is one too),
- *   "search_kernel" (0 = pick: two warps per query when the query table K*P*4 is at most 32 KB or the call has
- *   fewer than 33 queries, else one warp; 1 = one warp per query, 2 = two warps per query; the second needs
+ *   "search_kernel" (0 = pick: two warps per query whenever that kernel applies; 1 = one warp per query,
+ *                    2 = two warps per query; the second needs
  *                    M <= 32 and either K * padded_dim * 4 <= 32 KB or K <= 32; both return identical results),
  *   "binary_codes" (0/1, before any vector is added: 1 = the unified index's primary binary code
  *                   (include/cphnsw/core/codes.hpp:76-129 with R = 0): a component keeps only its sign bit, so

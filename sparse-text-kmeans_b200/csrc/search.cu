@@ -572,11 +572,10 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
         set_error("search_kernel=2 needs the asymmetric metric, M <= 32 and K*P*4 <= 32 KB or K <= 32");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
-    // A table too large for shared memory (padded dim 1024: 128 KB) makes every score a gather from L2; the
-    // one-warp kernel then keeps more walks in flight per SM and is the faster one for full batches (1M x 960:
-    // 97 k against 90 k queries/s), while a handful of queries still finish sooner with two warps each.
-    const bool team_auto = size_t(h->K) * h->P * 4 <= 32 * 1024 || narrow;
-    if (team_ok && (h->search_kernel == 2 || (h->search_kernel == 0 && team_auto))) {
+    // (Also for a table too large for shared memory, read in place: on 1M x 960 clustered vectors the two-warp kernel
+    // does 301 k queries/s against 237 k for one warp per query; only on unclustered vectors, where an expansion
+    // scores ~26 neighbours instead of ~2, one warp per query was 7 % ahead.)
+    if (team_ok && h->search_kernel != 1) {
         const size_t per_team = (c.per_warp + search_team_extra_smem() + 15) & ~size_t(15);
         CPB_TRY(launch_search_team(h, a, per_team, narrow ? int(nq) : 0, st));
         h->launches++;
