@@ -322,7 +322,7 @@ def run_reference(args):
     # the arm's config is the b200 arm's: the full workload; what the CPU actually ran is the bounded sample below
     from cphnsw_b200 import synthetic  # noqa: F401  (generators only; no GPU code is touched by this arm)
     n_full = int(full_base_size(args.workload) * args.scale)
-    nq_full = {"C1": 1000, "C2": 10_000, "C3": 10_000, "C4": 1000, "C5": 100_000}[args.workload]
+    nq_full = {"C1": 1000, "C2": 10_000, "C3": 10_000, "C3c": 10_000, "C4": 1000, "C5": 100_000}[args.workload]
     cfg = b200_config(args, w, n_full, w["base"].shape[1], max(10, int(round(nq_full * args.scale))),
                       min(full_entry_scan(args), n_full), w.get("knn_k", min(64, 2 * w["M"])))
     cfg["cpu_sample"] = {"index_points": r["index_points"], "scale_of_workload": r["scale"], "queries_per_step": 2000}
@@ -337,13 +337,13 @@ def run_reference(args):
 
 
 def full_base_size(name):
-    return {"C1": 100_000, "C2": 1_000_000, "C3": 1_000_000, "C4": 10_000_000, "C5": 10_000_000}[name]
+    return {"C1": 100_000, "C2": 1_000_000, "C3": 1_000_000, "C3c": 1_000_000, "C4": 10_000_000, "C5": 10_000_000}[name]
 
 
 def full_entry_scan(args):
     if args.entry_scan is not None:
         return args.entry_scan
-    return {"C2": 8192, "C3": 8192, "C5": 8192, "C4": 65536}.get(args.workload, 4)
+    return {"C2": 8192, "C3c": 8192, "C5": 8192, "C4": 65536}.get(args.workload, 4)
 
 
 def run_b200(args):

@@ -1,5 +1,5 @@
 """Seeded synthetic stand-ins for the datasets the reference measures on (SIFT-1M: 1M x 128 with
-10k queries; GIST-1M: 1M x 960 non-negative, clustered).  Shapes and value ranges follow those datasets;
+10k queries; GIST-1M: 1M x 960 non-negative).  Shapes and value ranges follow those datasets;
 no item of them is reproduced.  All vectors are float32 and L2-normalised with the
 ``norm > 1e-10`` guard of evaluation/datasets/dataset_loader.hpp:225-240.
 """
@@ -42,6 +42,18 @@ def gaussian_mixture(n, nq, dim, n_clusters, sigma, seed, query_stream=0, chunk=
     return base, queries
 
 
+def abs_gaussian(n, nq, dim, seed, query_stream=0, chunk=1 << 16):
+    """Non-negative |N(0,1)| coordinates, normalised (GIST-like value range)."""
+    def draw(m, stream):
+        out = np.empty((m, dim), np.float32)
+        for i0 in range(0, m, chunk):
+            i1 = min(m, i0 + chunk)
+            out[i0:i1] = normalize(np.abs(stream.standard_normal((i1 - i0, dim), dtype=np.float32)))
+        return out
+
+    return draw(n, np.random.default_rng([seed, 1])), draw(nq, np.random.default_rng([seed, 2, query_stream]))
+
+
 def abs_mixture(n, nq, dim, n_clusters, sigma, seed, query_stream=0, chunk=1 << 16):
     """Non-negative clustered vectors (GIST-like: every coordinate >= 0, so all vectors share one orthant and a
     large common component, with neighbourhood structure on top): centres |N(0,1)| per coordinate, points =
@@ -60,7 +72,7 @@ def abs_mixture(n, nq, dim, n_clusters, sigma, seed, query_stream=0, chunk=1 << 
     return draw(n, np.random.default_rng([seed, 1])), draw(nq, np.random.default_rng([seed, 2, query_stream]))
 
 
-# The five benchmark workloads (full sizes); ``scale`` shrinks base, queries and clusters together
+# The five benchmark workloads (full sizes) and a clustered variant of the third; ``scale`` shrinks base, queries and clusters together
 # so that cluster populations stay the same.
 def workload(name, scale=1.0, query_stream=0):
     """``query_stream`` picks an independent query set from the same distribution (one per rank)."""
@@ -79,8 +91,14 @@ def workload(name, scale=1.0, query_stream=0):
         return dict(name="C2", base=base, queries=q, K=32, component_bytes=1, M=32, ef_construction=200,
                     k=10, ef=100, rerank_k=500, entry_scan=sz(8_192, 4), k_entry=32)
     if name == "C3":
-        base, q = abs_mixture(sz(1_000_000), sz(10_000, 10), 960, sz(1_000), 0.3, 2, qs)
+        base, q = abs_gaussian(sz(1_000_000), sz(10_000, 10), 960, 2, qs)
         return dict(name="C3", base=base, queries=q, K=32, component_bytes=2, M=32, ef_construction=200,
+                    k=10, ef=200, rerank_k=1000, entry_scan=4)
+    if name == "C3c":
+        # the shape and parameters of C3 on vectors that have neighbourhoods (independent coordinates have none: every
+        # pair sits at cosine ~0.64 and no index can rank them): 1,000 clusters and, as for C2, an entry scan
+        base, q = abs_mixture(sz(1_000_000), sz(10_000, 10), 960, sz(1_000), 0.3, 2, qs)
+        return dict(name="C3c", base=base, queries=q, K=32, component_bytes=2, M=32, ef_construction=200,
                     k=10, ef=200, rerank_k=1000, entry_scan=sz(8_192, 4), k_entry=32)
     if name == "C4":
         base, q = gaussian_mixture(sz(10_000_000), sz(1_000, 10), 96, sz(10_000), 0.25, 3, qs)

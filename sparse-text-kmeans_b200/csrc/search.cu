@@ -573,8 +573,8 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     // (Also for a table too large for shared memory, read in place: on 1M x 960 clustered vectors the two-warp kernel
-    // does 301 k queries/s against 237 k for one warp per query; only on unclustered vectors, where an expansion
-    // scores ~26 neighbours instead of ~2, one warp per query was 7 % ahead.)
+    // does 301 k queries/s against 237 k for one warp per query; only on vectors with independent coordinates, where an
+    // expansion scores ~26 neighbours instead of ~2, one warp per query was 3-7 % ahead.)
     if (team_ok && h->search_kernel != 1) {
         const size_t per_team = (c.per_warp + search_team_extra_smem() + 15) & ~size_t(15);
         CPB_TRY(launch_search_team(h, a, per_team, narrow ? int(nq) : 0, st));

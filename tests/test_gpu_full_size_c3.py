@@ -17,7 +17,7 @@ def c3(cp):
     w["queries"] = w["queries"][:200]
     idx = cp.CPHNSWIndex(960, M=32, ef_construction=200, K=32, component_bytes=2)
     idx.set_param("entry_scan", w["entry_scan"])
-    idx.set_param("k_entry", w["k_entry"])
+    idx.set_param("k_entry", w.get("k_entry", 4))
     idx.add_batch_parallel(w["base"])
     return w, idx, idx.codes(), idx.adjacency()
 
@@ -56,11 +56,11 @@ def test_c3_full_size_search(c3, oracle):
     sample = np.arange(0, q.shape[0], 10)  # 20 queries walked by the oracle over the full graph
     signs = oracle.sign_tables(960, 32, 42)
     _, rot, _ = oracle.encode(q[sample], 32, 2, signs, 2, want_rotated=True)
-    cand, _, ws = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, rr, k), rr, want_stats=True, n_seed=w["k_entry"])
+    cand, _, ws = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, rr, k), rr, want_stats=True, n_seed=w.get("k_entry", 4))
     wi, wd = oracle.rerank(q[sample], base, cand, k)
     assert np.array_equal(stats[sample], ws)
     assert np.allclose(dist[sample], wd, rtol=1e-5, atol=1e-6)
     assert (ids[sample] == wi).mean() > 0.99
     pid, pd, ps = idx.search_batch(q[sample], k, ef, want_stats=True)
-    oi, od, os_ = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, k), k, want_stats=True, n_seed=w["k_entry"])
+    oi, od, os_ = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, k), k, want_stats=True, n_seed=w.get("k_entry", 4))
     assert np.array_equal(pid, oi) and np.array_equal(pd, od) and np.array_equal(ps, os_)
