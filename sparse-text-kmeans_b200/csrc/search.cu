@@ -55,7 +55,8 @@ __global__ void search_kernel(SearchArgs a) {
     const uint32_t beam = a.beam;
     const bool scan_mode = a.scan_only || a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
-    const bool coop_ok = !SYM && a.K <= 32;
+    const bool coop_ok = !SYM && a.K <= 64;
+    const bool two_blocks = a.K > 32;  // a lane owns two rotations in the whole-warp scoring
     const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm + a.qvec_floats);  // symmetric metric only
 
     // queries are handed out one at a time from a global counter, so that warps that draw short
@@ -178,24 +179,27 @@ __global__ void search_kernel(SearchArgs a) {
             }
             if (coop_ok && nf <= kCoopMax) {
                 // few fresh nodes: the whole warp scores each of them, one rotation per lane
-                uint32_t cid[kCoopMax], comp[kCoopMax];
+                uint32_t cid[kCoopMax], comp[kCoopMax], comph[kCoopMax];
 #pragma unroll
                 for (int f = 0; f < kCoopMax; ++f) {
                     cid[f] = kInvalidNode;
                     comp[f] = 0;
+                    comph[f] = 0;
                     if (f < nf) {
                         const int src = __ffs(m) - 1;
                         m &= m - 1;
                         cid[f] = __shfl_sync(kFull, id, src);
-                        if (lane < a.K)
-                            comp[f] = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes, lane);
+                        const unsigned char* crow = static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes;
+                        if (lane < a.K) comp[f] = load_component<U16>(crow, lane);
+                        if (32 + lane < a.K) comph[f] = load_component<U16>(crow, 32 + lane);
                     }
                 }
                 ahead();
 #pragma unroll
                 for (int f = 0; f < kCoopMax; ++f) {
                     if (f < nf) {
-                        const float d = asym_distance_coop(table, a.K, a.P, comp[f], lane);
+                        const float d = two_blocks ? asym_distance_coop2(table, a.K, a.P, comp[f], comph[f], lane)
+                                                   : asym_distance_coop(table, a.K, a.P, comp[f], lane);
                         try_admit(d, cid[f]);
                     }
                 }

@@ -149,12 +149,26 @@ __device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, c
 
 // The whole warp scores one node: lane j owns rotation c0 + j of each block; the butterfly
 // reduction adds exactly the pairs the one-lane form adds.  `comp` is this lane's component of
-// block 0 (K <= 32 on this path).
+// block 0 (K <= 32 here; asym_distance_coop2 takes 32 < K <= 64).
 __device__ __forceinline__ float asym_distance_coop(const float* table, int K, int P, uint32_t comp, int lane) {
     float t = signed_term(table, lane, K, P, comp);
 #pragma unroll
     for (int step = 16; step >= 1; step >>= 1) t = __fadd_rn(t, __shfl_xor_sync(kFull, t, step));
     return -__fadd_rn(0.0f, t);
+}
+
+// The same for two blocks (32 < K <= 64): lane j owns rotations j and 32 + j; the block sums are formed side by
+// side and added in block order, as the one-lane form does.
+__device__ __forceinline__ float asym_distance_coop2(const float* table, int K, int P, uint32_t comp_lo, uint32_t comp_hi,
+                                                     int lane) {
+    float t0 = signed_term(table, lane, K, P, comp_lo);
+    float t1 = signed_term(table, 32 + lane, K, P, comp_hi);
+#pragma unroll
+    for (int step = 16; step >= 1; step >>= 1) {
+        t0 = __fadd_rn(t0, __shfl_xor_sync(kFull, t0, step));
+        t1 = __fadd_rn(t1, __shfl_xor_sync(kFull, t1, step));
+    }
+    return -__fadd_rn(__fadd_rn(0.0f, t0), t1);
 }
 
 // ---- warp-wide bitonic sort of n (a power of two) (distance, id) pairs in shared memory ------------

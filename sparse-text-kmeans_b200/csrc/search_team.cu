@@ -257,7 +257,7 @@ __device__ __forceinline__ void tier_from_plain(TierList& T, int lane) {
 // shared-memory loads); otherwise it is read in place.
 // No register cap: holding the kernel to 64 registers (15 teams per SM instead of 11 when the table is read in
 // place) spills inside the walk and was measured slower on every configuration.
-template <bool U16, bool TSM>
+template <bool U16, bool TSM, bool K2>
 __global__ void search_team_kernel(SearchArgs a) {
     extern __shared__ __align__(16) unsigned char team_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -289,7 +289,9 @@ __global__ void search_team_kernel(SearchArgs a) {
     const uint32_t beam = a.beam;
     const bool scan_mode = a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
-    const bool coop_ok = a.K <= 32;
+    const bool coop_ok = a.K <= 64;
+    constexpr bool two_blocks = K2;  // 32 < K <= 64: a lane owns two rotations in the whole-warp scoring (a compile-time
+                                     // fact, so that the narrower codes pay nothing for it)
 
     while (true) {
         if (role == 0 && lane == 0) mail[0] = atomicAdd(a.next_query, 1u);
@@ -392,22 +394,26 @@ __global__ void search_team_kernel(SearchArgs a) {
             nevals += nf;
             if (nf == 0) return;
             if (coop_ok && nf <= kCoopMax) {
-                uint32_t cid[kCoopMax], comp[kCoopMax];
+                uint32_t cid[kCoopMax], comp[kCoopMax], comph[kCoopMax];
 #pragma unroll
                 for (int f = 0; f < kCoopMax; ++f) {
                     cid[f] = kInvalidNode;
                     comp[f] = 0;
+                    comph[f] = 0;
                     if (f < nf) {
                         const int src = __ffs(m) - 1;
                         m &= m - 1;
                         cid[f] = __shfl_sync(kFull, id, src);
-                        if (lane < a.K)
-                            comp[f] = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes, lane);
+                        const unsigned char* crow = static_cast<const unsigned char*>(a.codes) + size_t(cid[f]) * row_bytes;
+                        if (lane < a.K) comp[f] = load_component<U16>(crow, lane);
+                        if (two_blocks && 32 + lane < a.K) comph[f] = load_component<U16>(crow, 32 + lane);
                     }
                 }
 #pragma unroll
                 for (int f = 0; f < kCoopMax; ++f)
-                    if (f < nf) admit_one(asym_distance_coop(table, a.K, a.P, comp[f], lane), cid[f]);
+                    if (f < nf)
+                        admit_one(two_blocks ? asym_distance_coop2(table, a.K, a.P, comp[f], comph[f], lane)
+                                             : asym_distance_coop(table, a.K, a.P, comp[f], lane), cid[f]);
             } else {
                 float dist = 0.0f;
                 if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
@@ -703,13 +709,21 @@ __global__ void search_team_kernel(SearchArgs a) {
                             const int s1 = m ? __ffs(m) - 1 : s0;
                             m &= m - 1;
                             const uint32_t id0 = __shfl_sync(kFull, u_id, s0), id1 = __shfl_sync(kFull, u_id, s1);
-                            uint32_t comp0 = 0, comp1 = 0;
+                            uint32_t comp0 = 0, comp1 = 0, comp0h = 0, comp1h = 0;
+                            const unsigned char* row0 = static_cast<const unsigned char*>(a.codes) + size_t(id0) * row_bytes;
+                            const unsigned char* row1 = static_cast<const unsigned char*>(a.codes) + size_t(id1) * row_bytes;
                             if (lane < a.K) {
-                                comp0 = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(id0) * row_bytes, lane);
-                                comp1 = load_component<U16>(static_cast<const unsigned char*>(a.codes) + size_t(id1) * row_bytes, lane);
+                                comp0 = load_component<U16>(row0, lane);
+                                comp1 = load_component<U16>(row1, lane);
                             }
-                            const float d0 = asym_distance_coop(table, a.K, a.P, comp0, lane);
-                            const float d1 = asym_distance_coop(table, a.K, a.P, comp1, lane);
+                            if (two_blocks && 32 + lane < a.K) {
+                                comp0h = load_component<U16>(row0, 32 + lane);
+                                comp1h = load_component<U16>(row1, 32 + lane);
+                            }
+                            const float d0 = two_blocks ? asym_distance_coop2(table, a.K, a.P, comp0, comp0h, lane)
+                                                        : asym_distance_coop(table, a.K, a.P, comp0, lane);
+                            const float d1 = two_blocks ? asym_distance_coop2(table, a.K, a.P, comp1, comp1h, lane)
+                                                        : asym_distance_coop(table, a.K, a.P, comp1, lane);
                             if (lane == s0) dist = d0;
                             if (lane == s1) dist = d1;
                         }
@@ -826,9 +840,9 @@ size_t search_team_extra_smem() { return size_t(kSeedCap) * 8 + kRing * 4 + kMai
 
 // Teams per block: as many as shared memory allows (at most 15, one named barrier each), fewer if
 // the register file does not hold them.
-template <bool U16, bool TSM>
+template <bool U16, bool TSM, bool K2>
 static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
-    auto kernel = search_team_kernel<U16, TSM>;
+    auto kernel = search_team_kernel<U16, TSM, K2>;
     int teams = int((226 * 1024) / per_team);
     if (teams > 15) teams = 15;
     if (narrow_blocks) teams = 1;  // one query per block
@@ -848,8 +862,15 @@ static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, in
 
 int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
     a.per_warp_smem = uint32_t(per_team);
-    if (a.table_in_smem) return h->comp_bytes == 2 ? launch_team_t<true, true>(h, a, per_team, narrow_blocks, st) : launch_team_t<false, true>(h, a, per_team, narrow_blocks, st);
-    return h->comp_bytes == 2 ? launch_team_t<true, false>(h, a, per_team, narrow_blocks, st) : launch_team_t<false, false>(h, a, per_team, narrow_blocks, st);
+    const bool u16 = h->comp_bytes == 2, k2 = h->K > 32;
+#define CPB_TEAM(U, T, W) launch_team_t<U, T, W>(h, a, per_team, narrow_blocks, st)
+    if (a.table_in_smem) {
+        if (k2) return u16 ? CPB_TEAM(true, true, true) : CPB_TEAM(false, true, true);
+        return u16 ? CPB_TEAM(true, true, false) : CPB_TEAM(false, true, false);
+    }
+    // a table read in place belongs to K <= 32 here (wider codes need it in shared memory)
+    return u16 ? CPB_TEAM(true, false, false) : CPB_TEAM(false, false, false);
+#undef CPB_TEAM
 }
 
 }  // namespace cpb

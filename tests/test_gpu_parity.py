@@ -166,6 +166,7 @@ def oracle_index(oracle, base, K, cb, M, knn_k, conv=2):
                                                      (1500, 200, 16, 2, 32, 32, 8), (50, 128, 32, 1, 32, 4, 4),
                                                      (1200, 300, 32, 2, 16, 32, 8), (900, 960, 32, 2, 32, 16, 4),  # table > 32 KB
                                                      (1000, 100, 64, 2, 16, 32, 8),  # 128-byte code rows
+                                                     (2000, 128, 64, 1, 32, 64, 8), (1500, 128, 48, 1, 16, 32, 8),  # two rotations per lane in the whole-warp scoring
                                                      (50, 128, 32, 1, 32, 50, 1)])
 @pytest.mark.parametrize("skernel", [1, 2])  # one warp per query, two warps per query
 def test_build_and_search_match_oracle(cp, oracle, n, dim, K, cb, M, scan, seeds, skernel):
