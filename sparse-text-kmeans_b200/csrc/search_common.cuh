@@ -196,6 +196,47 @@ __device__ __forceinline__ void warp_sort_smem(float* d, uint32_t* id, int n, in
     }
 }
 
+// The k smallest of n pairs, ascending, into positions [0, k): k rounds of "find the smallest of [r, n), swap it to r".
+// For the few results a query returns this is a fraction of the full sort (k = 10 of 500 reranked candidates: about
+// 1,500 instead of 7,000 warp instructions) and yields the same pairs in the same order, the order being total.
+constexpr uint32_t kSelectMax = 16;  // above this many results the full sort is taken
+__device__ __forceinline__ void warp_select_smem(float* d, uint32_t* id, int n, int k, int lane) {
+    for (int r = 0; r < k && r < n; ++r) {
+        float bd = INFINITY;
+        uint32_t bi = kInvalidNode;
+        int bp = r;
+        for (int p = r + lane; p < n; p += 32) {
+            const float v = d[p];
+            const uint32_t w = id[p];
+            if (key_less(v, w, bd, bi)) {
+                bd = v;
+                bi = w;
+                bp = p;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+            const float od = __shfl_xor_sync(kFull, bd, o);
+            const uint32_t oi = __shfl_xor_sync(kFull, bi, o);
+            const int op = __shfl_xor_sync(kFull, bp, o);
+            if (key_less(od, oi, bd, bi)) {
+                bd = od;
+                bi = oi;
+                bp = op;
+            }
+        }
+        if (lane == 0 && bi != kInvalidNode && bp != r) {
+            const float td = d[r];
+            const uint32_t ti = id[r];
+            d[r] = bd;
+            id[r] = bi;
+            d[bp] = td;
+            id[bp] = ti;
+        }
+        __syncwarp();
+    }
+}
+
 // bitonic sort of n (a power of two) pairs by (distance, id without the expanded flag); the flag travels with the id
 __device__ __forceinline__ void warp_sort_flagged(float* d, uint32_t* id, int n, int lane) {
     for (int k2 = 2; k2 <= n; k2 <<= 1) {

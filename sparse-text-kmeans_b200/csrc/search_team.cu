@@ -806,14 +806,20 @@ __global__ void search_team_kernel(SearchArgs a) {
         team_sync();
         if (role == 0) {
             if (a.rerank_k) {
-                nsort = 32;
-                while (nsort < int(ncand)) nsort <<= 1;
-                for (int pos = int(ncand) + lane; pos < nsort; pos += 32) {
-                    sd[pos] = INFINITY;
-                    sid[pos] = kInvalidNode;
+                if (a.k <= kSelectMax) {  // the few results wanted are picked out; everything behind them stays unsorted
+                    nsort = int(ncand);
+                    __syncwarp();
+                    warp_select_smem(sd, sid, nsort, int(a.k), lane);
+                } else {
+                    nsort = 32;
+                    while (nsort < int(ncand)) nsort <<= 1;
+                    for (int pos = int(ncand) + lane; pos < nsort; pos += 32) {
+                        sd[pos] = INFINITY;
+                        sid[pos] = kInvalidNode;
+                    }
+                    __syncwarp();
+                    warp_sort_smem(sd, sid, nsort, lane);
                 }
-                __syncwarp();
-                warp_sort_smem(sd, sid, nsort, lane);
             }
             uint32_t* oid = a.out_ids + size_t(q) * a.k;
             float* od = a.out_dist + size_t(q) * a.k;
