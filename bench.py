@@ -577,7 +577,9 @@ def run_b200(args):
     q_per_launch = nq * args.steps / max(1, search_launches)
     achieved = bytes_per_query * q_per_launch / (search_ms_per_launch * 1e-3) / 1e9
     # the library takes the two-warp kernel when the query table fits shared memory and M <= 32
-    team = args.search_kernel != 1 and M <= 32 and max(ef, rerank_k) <= 1024 and (K * idx.padded_dim * 4 <= 32 * 1024 or K <= 32)
+    small_table = K * idx.padded_dim * 4 <= 32 * 1024
+    beam = max(ef, rerank_k, k)
+    team = args.search_kernel != 1 and M <= 32 and (beam <= 1024 or (beam <= 2048 and small_table)) and (small_table or K <= 32)
     dram_per_query = NCU_SEARCH_DRAM_BYTES_PER_QUERY if team else NCU_SEARCH_DRAM_BYTES_PER_QUERY_ONE_WARP
     traffic = dram_per_query * q_per_launch if w["name"] == "C2" else None
     roofline = {"kernel": "search_team_kernel" if team else "search_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

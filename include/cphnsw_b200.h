@@ -86,7 +86,8 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *                 any K <= 120 that is a multiple of 8, residual bits included when the primary part is one too),
  *   "search_kernel" (0 = pick: two warps per query whenever that kernel applies; 1 = one warp per query,
  *                    2 = two warps per query; the second needs
- *                    M <= 32 and either K * padded_dim * 4 <= 32 KB or K <= 32; both return identical results),
+ *                    M <= 32, either K * padded_dim * 4 <= 32 KB or K <= 32, and a beam max(ef, k, rerank_k) of at most
+ *                    1024 (2048 when K * padded_dim * 4 <= 32 KB); both return identical results),
  *   "binary_codes" (0/1, before any vector is added: 1 = the unified index's primary binary code
  *                   (include/cphnsw/core/codes.hpp:76-129 with R = 0): a component keeps only its sign bit, so
  *                   code distance = Hamming distance and the graph is built under it; search / search_and_rerank

@@ -576,10 +576,12 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
     LaunchTimer timer(h, kKernelSearch, st);
 
     // two warps per query: asymmetric metric, table in shared memory, one adjacency row per warp
-    const bool team_ok = beam <= 1024 && !sym && !scan_only && (c.table_smem || h->K <= 32) && h->M <= 32 && h->k_entry <= 128;
+    // (beams over 1,024 up to 2,048 in its wide form, which exists for tables in shared memory)
+    const bool team_ok = (beam <= 1024 || (beam <= 2048 && c.table_smem)) && !sym && !scan_only && (c.table_smem || h->K <= 32) &&
+                         h->M <= 32 && h->k_entry <= 128;
     a.table_in_smem = c.table_smem ? 1 : 0;
     if (h->search_kernel == 2 && !team_ok && !sym) {
-        set_error("search_kernel=2 needs the asymmetric metric, M <= 32 and K*P*4 <= 32 KB or K <= 32");
+        set_error("search_kernel=2 needs the asymmetric metric, M <= 32, K*P*4 <= 32 KB or K <= 32, and a beam of at most 1024 (2048 with the table in shared memory)");
         return CPHNSW_B200_E_UNSUPPORTED;
     }
     // (Also for a table too large for shared memory, read in place: on 1M x 960 clustered vectors the two-warp kernel

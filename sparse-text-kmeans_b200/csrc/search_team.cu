@@ -28,7 +28,8 @@
 // the rerank are split between the two warps.
 //
 // Used for the asymmetric metric with M <= 32; the query table sits in shared memory when it is at
-// most 32 KB and is read in place (global memory, through L1 / L2) otherwise.
+// most 32 KB and is read in place (global memory, through L1 / L2) otherwise.  Beams up to 1,024 take 32 buckets,
+// one per lane; beams up to 2,048 the wide form with 64 buckets, two per lane.
 #include "search_common.cuh"
 
 namespace cpb {
@@ -115,16 +116,27 @@ __device__ __forceinline__ void beam_admit_lanes(BeamList& L, uint32_t m, bool m
 struct TierList {
     float* d;
     uint32_t* id;    // expanded flag in the top bit
-    int nb;          // buckets (cap / 32 <= 32)
+    int nb;          // buckets (cap / 32: up to 32, up to 64 in the wide form)
     uint32_t count, wcap, cur;
     float wd;        // worst live member once count == wcap
     uint32_t wi;
     int head;        // lane b: head of bucket b
     float max_d;     // lane b: last logical element of bucket b
     uint32_t max_i;
+    int head2;       // wide form (beams over 1,024): lane b also keeps bucket 32 + b
+    float max_d2;
+    uint32_t max_i2;
 };
 
+// head of bucket b (b known to every lane)
+template <bool WIDE>
+__device__ __forceinline__ int tier_head(const TierList& T, int b) {
+    if (WIDE && b >= 32) return __shfl_sync(kFull, T.head2, b - 32);
+    return __shfl_sync(kFull, T.head, b);
+}
+
 // heads to zero (the arrays are then read flat) and the per-bucket maxima re-read
+template <bool WIDE>
 __device__ __forceinline__ void tier_reset_heads(TierList& T, int lane) {
     T.head = 0;
     T.max_d = INFINITY;
@@ -133,12 +145,22 @@ __device__ __forceinline__ void tier_reset_heads(TierList& T, int lane) {
         T.max_d = T.d[lane * 32 + 31];
         T.max_i = T.id[lane * 32 + 31];
     }
+    if (WIDE) {
+        T.head2 = 0;
+        T.max_d2 = INFINITY;
+        T.max_i2 = kInvalidNode;
+        if (32 + lane < T.nb) {
+            T.max_d2 = T.d[(32 + lane) * 32 + 31];
+            T.max_i2 = T.id[(32 + lane) * 32 + 31];
+        }
+    }
 }
 
+template <bool WIDE>
 __device__ __forceinline__ void tier_refresh_worst(TierList& T) {
     if (T.count == T.wcap) {
         const int wb = int(T.wcap - 1) >> 5;
-        const int hw = __shfl_sync(kFull, T.head, wb);
+        const int hw = tier_head<WIDE>(T, wb);
         const int ws = wb * 32 + ((hw + int((T.wcap - 1) & 31)) & 31);
         T.wd = T.d[ws];
         T.wi = T.id[ws] & kIdMask;
@@ -146,12 +168,18 @@ __device__ __forceinline__ void tier_refresh_worst(TierList& T) {
 }
 
 // Admission of (d, id), known to every lane (search_engine.hpp:166-176).
+template <bool WIDE>
 __device__ __forceinline__ void tier_admit(TierList& T, float d, uint32_t id, int lane) {
     if (T.count == T.wcap && !key_less(d, id, T.wd, T.wi)) return;
-    // first bucket whose largest element is not below the key (fillers are +inf: there is one)
+    // first bucket whose largest element is not below the key (fillers are +inf: there is one); the maxima ascend
+    // with the bucket, so the buckets below the key are a prefix and counting them gives the index
     const bool below = lane < T.nb && key_less(T.max_d, T.max_i & kIdMask, d, id);
-    const int b = __popc(__ballot_sync(kFull, below));
-    const int hb = __shfl_sync(kFull, T.head, b);
+    int b = __popc(__ballot_sync(kFull, below));
+    if (WIDE) {
+        const bool below2 = 32 + lane < T.nb && key_less(T.max_d2, T.max_i2 & kIdMask, d, id);
+        b += __popc(__ballot_sync(kFull, below2));
+    }
+    const int hb = tier_head<WIDE>(T, b);
     const int slot = b * 32 + ((hb + lane) & 31);
     const float ed = T.d[slot];  // logical element `lane` of bucket b
     const uint32_t ei = T.id[slot];
@@ -181,6 +209,38 @@ __device__ __forceinline__ void tier_admit(TierList& T, float d, uint32_t id, in
     }
     const float in_d = __shfl_up_sync(kFull, ld, 1);  // lane b passes on out_d
     const uint32_t in_i = __shfl_up_sync(kFull, li, 1);
+    if (WIDE) {
+        // the second set of buckets (32 + lane) does the same; bucket 32 takes what bucket 31 passes on
+        const int bb = 32 + lane;
+        const bool casc2 = bb > b && bb <= wb;
+        const int last2 = bb * 32 + ((T.head2 + 31) & 31);
+        float ld2 = out_d;
+        uint32_t li2 = out_i;
+        if (casc2) {
+            ld2 = T.d[last2];
+            li2 = T.id[last2];
+        }
+        float in2_d = __shfl_up_sync(kFull, ld2, 1);
+        uint32_t in2_i = __shfl_up_sync(kFull, li2, 1);
+        const float from31_d = __shfl_sync(kFull, ld, 31);
+        const uint32_t from31_i = __shfl_sync(kFull, li, 31);
+        if (lane == 0) {
+            in2_d = from31_d;
+            in2_i = from31_i;
+        }
+        if (casc2) {
+            T.d[last2] = in2_d;
+            T.id[last2] = in2_i;
+            T.head2 = (T.head2 + 31) & 31;
+            const int nl2 = bb * 32 + ((T.head2 + 31) & 31);
+            T.max_d2 = T.d[nl2];
+            T.max_i2 = T.id[nl2];
+        }
+        if (bb == b) {
+            T.max_d2 = top_d;
+            T.max_i2 = top_i;
+        }
+    }
     if (casc) {
         T.d[last_slot] = in_d;
         T.id[last_slot] = in_i;
@@ -197,16 +257,17 @@ __device__ __forceinline__ void tier_admit(TierList& T, float d, uint32_t id, in
     if (T.count < T.wcap) ++T.count;
     const uint32_t p = uint32_t(b) * 32 + r;
     if (p <= T.cur) T.cur = p;
-    tier_refresh_worst(T);
+    tier_refresh_worst<WIDE>(T);
 }
 
 // admit the scored candidates of the lanes in mask m, lowest lane first
+template <bool WIDE>
 __device__ __forceinline__ void tier_admit_lanes(TierList& T, uint32_t m, bool mine, float dist, uint32_t id, int lane) {
     if (T.count == T.wcap) m &= __ballot_sync(kFull, mine && key_less(dist, id, T.wd, T.wi));
     while (m) {
         const int src = __ffs(m) - 1;
         m &= m - 1;
-        tier_admit(T, __shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src), lane);
+        tier_admit<WIDE>(T, __shfl_sync(kFull, dist, src), __shfl_sync(kFull, id, src), lane);
     }
 }
 
@@ -219,9 +280,10 @@ __device__ __forceinline__ void tier_admit_lanes(TierList& T, uint32_t m, bool m
 constexpr uint32_t kFillMin = 256;  // free places in W at the start of the walk from which the plain array pays (measured)
 
 // bucket rotations undone: logical order becomes slot order (flags kept)
+template <bool WIDE>
 __device__ __forceinline__ void tier_flatten(TierList& T, int lane) {
     for (int b = 0; b < T.nb; ++b) {
-        const int hb = __shfl_sync(kFull, T.head, b);
+        const int hb = tier_head<WIDE>(T, b);
         if (hb == 0) continue;
         const int from = b * 32 + ((hb + lane) & 31);
         const float v = T.d[from];
@@ -232,15 +294,17 @@ __device__ __forceinline__ void tier_flatten(TierList& T, int lane) {
     }
     __syncwarp();
     T.head = 0;
+    if (WIDE) T.head2 = 0;
 }
 
 // the plain array becomes the tiered list: sorted, heads zero, cursor on the first unexpanded member
+template <bool WIDE>
 __device__ __forceinline__ void tier_from_plain(TierList& T, int lane) {
     int n = 32;
     while (n < int(T.count)) n <<= 1;
     __syncwarp();
     warp_sort_flagged(T.d, T.id, n, lane);
-    tier_reset_heads(T, lane);
+    tier_reset_heads<WIDE>(T, lane);
     T.cur = T.count;
     for (uint32_t base = 0; base < T.count; base += 32) {
         const uint32_t ei = T.id[base + lane];
@@ -250,14 +314,14 @@ __device__ __forceinline__ void tier_from_plain(TierList& T, int lane) {
             break;
         }
     }
-    tier_refresh_worst(T);
+    tier_refresh_worst<WIDE>(T);
 }
 
 // TSM: the query table is copied to shared memory (a compile-time fact, so that its reads stay
 // shared-memory loads); otherwise it is read in place.
 // No register cap: holding the kernel to 64 registers (15 teams per SM instead of 11 when the table is read in
 // place) spills inside the walk and was measured slower on every configuration.
-template <bool U16, bool TSM, bool K2>
+template <bool U16, bool TSM, bool K2, bool WIDE>
 __global__ void search_team_kernel(SearchArgs a) {
     extern __shared__ __align__(16) unsigned char team_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -336,6 +400,9 @@ __global__ void search_team_kernel(SearchArgs a) {
         T.head = 0;
         T.max_d = INFINITY;
         T.max_i = kInvalidNode;
+        T.head2 = 0;
+        T.max_d2 = INFINITY;
+        T.max_i2 = kInvalidNode;
         uint32_t total_marks = 0;  // walker: nodes marked since the query began (ring write position)
 
         // admissions go to the plain array while W is filling, to the tiered list afterwards
@@ -351,10 +418,10 @@ __global__ void search_team_kernel(SearchArgs a) {
                     __syncwarp();
                     return;
                 }
-                tier_from_plain(T, lane);
+                tier_from_plain<WIDE>(T, lane);
                 filling = false;
             }
-            tier_admit(T, d, id, lane);
+            tier_admit<WIDE>(T, d, id, lane);
         };
         auto admit_lanes = [&](uint32_t m, bool mine, float dist, uint32_t id) {
             if (filling) {
@@ -369,10 +436,10 @@ __global__ void search_team_kernel(SearchArgs a) {
                     __syncwarp();
                     return;
                 }
-                tier_from_plain(T, lane);
+                tier_from_plain<WIDE>(T, lane);
                 filling = false;
             }
-            tier_admit_lanes(T, m, mine, dist, id, lane);
+            tier_admit_lanes<WIDE>(T, m, mine, dist, id, lane);
         };
 
         // walker alone: visited test-and-set of one row, scoring, admission
@@ -442,7 +509,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                 if (ok) dist = asym_distance_lane<U16>(table, a.entry_codes, e, a.K, a.P);
                 const uint32_t m = __ballot_sync(kFull, ok);
                 nevals += __popc(m);
-                if (role == 0) tier_admit_lanes(T, m, ok, dist, id, lane);
+                if (role == 0) tier_admit_lanes<WIDE>(T, m, ok, dist, id, lane);
                 else beam_admit_lanes(S, m, ok, dist, id, lane);
             }
             if (role == 1 && lane == 0) {
@@ -453,12 +520,12 @@ __global__ void search_team_kernel(SearchArgs a) {
             if (role == 0) {
                 const uint32_t n1 = mail[9];
                 nevals += mail[8];
-                for (uint32_t i = 0; i < n1; ++i) tier_admit(T, seed_d[i], seed_id[i], lane);
+                for (uint32_t i = 0; i < n1; ++i) tier_admit<WIDE>(T, seed_d[i], seed_id[i], lane);
                 // W now holds the seeds (within bucket (n_seed - 1) / 32 and before): bring it back
                 // to a flat list, fillers after the live members
                 const int wb = int(T.wcap - 1) >> 5;
                 for (int b = 0; b <= wb; ++b) {
-                    const int hb = __shfl_sync(kFull, T.head, b);
+                    const int hb = tier_head<WIDE>(T, b);
                     const int from = b * 32 + ((hb + lane) & 31);
                     float v = sd[from];
                     uint32_t w = sid[from];
@@ -486,8 +553,8 @@ __global__ void search_team_kernel(SearchArgs a) {
                 __syncwarp();
                 T.wcap = beam;
                 T.cur = 0;
-                tier_reset_heads(T, lane);
-                tier_refresh_worst(T);
+                tier_reset_heads<WIDE>(T, lane);
+                tier_refresh_worst<WIDE>(T);
             }
         } else if (role == 0) {
             for (uint32_t e0 = 0; e0 < a.n_entry; e0 += 32) {  // search_engine.hpp:105-115
@@ -503,7 +570,7 @@ __global__ void search_team_kernel(SearchArgs a) {
         // after it the walker consumes the prepared row of that node (if the scout has one) while the
         // scout moves the announced nodes one stage further.
         if (role == 0 && T.wcap >= T.count + kFillMin) {
-            tier_flatten(T, lane);
+            tier_flatten<WIDE>(T, lane);
             filling = true;
         }
         uint32_t low_rows = 0;  // walker: consecutive expansions that brought at most two new members
@@ -575,7 +642,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                 if (T.cur < T.count) {
                     // closest member of W that has not been expanded (search_engine.hpp:121-123)
                     const int cb = int(T.cur >> 5), cl = int(T.cur & 31);
-                    const int hb = __shfl_sync(kFull, T.head, cb);
+                    const int hb = tier_head<WIDE>(T, cb);
                     const int cslot = cb * 32 + ((hb + lane) & 31);
                     uint32_t ei = sid[cslot];  // logical element `lane` of the cursor's bucket
                     const uint32_t node = __shfl_sync(kFull, ei, cl) & kIdMask;
@@ -587,7 +654,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                     while (!un) {
                         base += 32;
                         if (base >= T.count) break;
-                        const int h2 = __shfl_sync(kFull, T.head, int(base >> 5));
+                        const int h2 = tier_head<WIDE>(T, int(base >> 5));
                         ei = sid[base + ((h2 + lane) & 31)];
                         un = __ballot_sync(kFull, !(ei & kExpanded) && base + lane < T.count);
                     }
@@ -656,7 +723,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                 if (filling) {
                     low_rows = nevals - evals_before <= 2 ? low_rows + 1 : 0;
                     if (low_rows >= 3) {
-                        tier_from_plain(T, lane);
+                        tier_from_plain<WIDE>(T, lane);
                         filling = false;
                     }
                 }
@@ -755,11 +822,11 @@ __global__ void search_team_kernel(SearchArgs a) {
 
         // ---- rerank (both warps) and output (walker)
         if (role == 0) {
-            if (filling) tier_from_plain(T, lane);  // W never filled: sorted now
+            if (filling) tier_from_plain<WIDE>(T, lane);  // W never filled: sorted now
             // back to a flat list, expanded flags dropped
             const int nbl = int(T.count + 31) >> 5;
             for (int b = 0; b < nbl; ++b) {
-                const int hb = __shfl_sync(kFull, T.head, b);
+                const int hb = tier_head<WIDE>(T, b);
                 const int from = b * 32 + ((hb + lane) & 31);
                 const float v = sd[from];
                 const uint32_t w = sid[from];
@@ -846,9 +913,9 @@ size_t search_team_extra_smem() { return size_t(kSeedCap) * 8 + kRing * 4 + kMai
 
 // Teams per block: as many as shared memory allows (at most 15, one named barrier each), fewer if
 // the register file does not hold them.
-template <bool U16, bool TSM, bool K2>
+template <bool U16, bool TSM, bool K2, bool WIDE>
 static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
-    auto kernel = search_team_kernel<U16, TSM, K2>;
+    auto kernel = search_team_kernel<U16, TSM, K2, WIDE>;
     int teams = int((226 * 1024) / per_team);
     if (teams > 15) teams = 15;
     if (narrow_blocks) teams = 1;  // one query per block
@@ -868,14 +935,18 @@ static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, in
 
 int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
     a.per_warp_smem = uint32_t(per_team);
-    const bool u16 = h->comp_bytes == 2, k2 = h->K > 32;
-#define CPB_TEAM(U, T, W) launch_team_t<U, T, W>(h, a, per_team, narrow_blocks, st)
+    const bool u16 = h->comp_bytes == 2, k2 = h->K > 32, wide = a.cap > 1024;
+#define CPB_TEAM(U, T, W, X) launch_team_t<U, T, W, X>(h, a, per_team, narrow_blocks, st)
     if (a.table_in_smem) {
-        if (k2) return u16 ? CPB_TEAM(true, true, true) : CPB_TEAM(false, true, true);
-        return u16 ? CPB_TEAM(true, true, false) : CPB_TEAM(false, true, false);
+        if (wide) {  // beams over 1,024: 64 buckets, two per lane
+            if (k2) return u16 ? CPB_TEAM(true, true, true, true) : CPB_TEAM(false, true, true, true);
+            return u16 ? CPB_TEAM(true, true, false, true) : CPB_TEAM(false, true, false, true);
+        }
+        if (k2) return u16 ? CPB_TEAM(true, true, true, false) : CPB_TEAM(false, true, true, false);
+        return u16 ? CPB_TEAM(true, true, false, false) : CPB_TEAM(false, true, false, false);
     }
-    // a table read in place belongs to K <= 32 here (wider codes need it in shared memory)
-    return u16 ? CPB_TEAM(true, false, false) : CPB_TEAM(false, false, false);
+    // a table read in place belongs to K <= 32 and beams up to 1,024 here
+    return u16 ? CPB_TEAM(true, false, false, false) : CPB_TEAM(false, false, false, false);
 #undef CPB_TEAM
 }
 

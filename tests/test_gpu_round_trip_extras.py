@@ -302,18 +302,21 @@ def test_exact_edges_lift_recall_on_unclustered_data(cp, oracle):
     assert rec[1] > rec[0] + 0.1 and rec[1] > 0.8, rec
 
 
-def test_beams_wider_than_1024_match_oracle(cp, oracle):
-    # up to 1,024 the two-warp kernel's tiered W; beyond it the one-warp kernel's flat W (three-level rank search)
-    n, dim, K, M = 6000, 128, 32, 32
+@pytest.mark.parametrize("kernel,K", [(0, 32), (1, 32), (0, 64)])
+def test_beams_wider_than_1024_match_oracle(cp, oracle, kernel, K):
+    # the two-warp kernel's tiered W: 32 buckets up to 1,024, 64 buckets (two per lane) up to 2,048; beyond that, and when
+    # asked for, the one-warp kernel's flat W (three-level rank search)
+    n, dim, M = 6000, 128, 32
     base, q = synthetic.gaussian_mixture(n, 24, dim, 6, 0.3, 17)
     idx = make_index(cp, dim, K, 1, M)
+    idx.set_param("search_kernel", kernel)
     idx.set_param("entry_scan", 64)
     idx.set_param("k_entry", 8)
     idx.add_batch_parallel(base)
     signs = oracle.sign_tables(dim, K, 42)
     codes, adj = idx.codes(), idx.adjacency()
     _, rot, _ = oracle.encode(q, K, 1, signs, 2, want_rotated=True)
-    for k, ef in ((10, 1025), (100, 1500), (10, 2047), (2000, 2000), (50, 4096)):
+    for k, ef in ((10, 1025), (100, 1500), (10, 2047), (10, 2048), (2000, 2000), (50, 4096)):
         ids, dist, stats = idx.search_batch(q, k, ef, want_stats=True)
         wi, wd, ws = oracle.search(rot, codes, adj, idx.entry_ids(), max(ef, k), k, want_stats=True, n_seed=8)
         assert np.array_equal(ids, wi) and np.array_equal(dist, wd) and np.array_equal(stats, ws), (k, ef)
