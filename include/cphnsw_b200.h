@@ -93,7 +93,11 @@ int cphnsw_b200_destroy(cphnsw_b200_index* h);
  *                   code distance = Hamming distance and the graph is built under it; search / search_and_rerank
  *                   walk under the Hamming distance to the query's code (unified search, include/cphnsw/api/index.hpp:177-214),
  *                   distances returned are Hamming distances (exact -<q,x> after a rerank); brute_force_search ranks by
- *                   Hamming distance; calibrate and search_multiprobe are not available),
+ *                   Hamming distance; calibrate and search_multiprobe are not available.  Between build stages the
+ *                   stored code of a node is its sign bits packed 32 per word (include/cphnsw/core/codes.hpp:21-52
+ *                   packs 64 per word), which the walk compares by XOR and popcount; the array of one component per
+ *                   bit exists only while add_batch_parallel / add_batch run; get_code, get_codes and the index file
+ *                   still give one component per bit; get_param("stored_code_bytes") tells the bytes per node),
  *   "residual_bits" / "residual_shift" (binary-code mode only, before any vector is added: the unified index's
  *                   residual codes, ResidualCode<K, R> (include/cphnsw/core/codes.hpp:76-129).  The handle's K
  *                   counts primary + residual bits; the last residual_bits components are the residual bits (the

@@ -122,6 +122,26 @@ int set_entry_ids(cphnsw_b200_index* h) {
     CPB_TRY(gather_entry_codes(h, 0));
     CPB_TRY(scan_adjacency_rows(h, 0));
     CPB_CUDA(cudaStreamSynchronize(0));
+    if (h->binary_codes && h->packed_words) {
+        // binary-code mode: from here on the packed sign bits are the stored code (the walk reads them, and so do the
+        // accessors); the array of one byte per bit comes back when a build stage needs it (ensure_codes)
+        h->d_codes.release();
+        h->codes_released = true;
+    }
+    return 0;
+}
+
+// the stored codes of binary-code mode, one component per bit, rebuilt on the host from the packed bits
+// (accessors that hold the handle shared and may not touch its device buffers)
+int host_codes_from_packed(const cphnsw_b200_index* h, uint64_t first, uint64_t count, unsigned char* out) {
+    if (count == 0) return 0;
+    const size_t words = size_t(h->packed_words);
+    std::vector<uint32_t> w(count * words);
+    CPB_CUDA(cudaMemcpy(w.data(), h->d_packed.as<uint32_t>() + first * words, w.size() * 4, cudaMemcpyDeviceToHost));
+    const size_t cb = h->comp_bytes, K = h->K;
+    std::memset(out, 0, count * K * cb);
+    for (uint64_t i = 0; i < count; ++i)
+        for (size_t r = 0; r < K; ++r) out[(i * K + r) * cb] = (unsigned char)((w[i * words + (r >> 5)] >> (r & 31)) & 1u);
     return 0;
 }
 
@@ -725,6 +745,8 @@ int cphnsw_b200_get_param(const cphnsw_b200_index* h, const char* name, double* 
     else if (s == "exact_edges") *v = h->exact_edges;
     else if (s == "rank_pruning_alpha") *v = h->rank_pruning_alpha;
     else if (s == "binary_codes") *v = h->binary_codes;
+    else if (s == "stored_code_bytes")  // bytes of HBM a node's code takes while no build stage runs
+        *v = h->codes_released ? double(h->packed_words) * 4.0 : double(h->K) * h->comp_bytes;
     else if (s == "residual_bits") *v = h->residual_bits;
     else if (s == "residual_shift") *v = h->residual_shift;
     else if (s == "k_entry") *v = h->k_entry;
@@ -810,6 +832,7 @@ int cphnsw_b200_install_dev(cphnsw_b200_index* h, const float* d_vectors, const 
     cudaStream_t st = (cudaStream_t)stream;
     CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
     CPB_TRY(h->d_codes.reserve(n * code_row_bytes(h) + 16));
+    h->codes_released = false;  // the codes are replaced as a whole
     CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
     CPB_CUDA(cudaMemcpyAsync(h->d_vectors.p, d_vectors, n * h->dim * 4, cudaMemcpyDeviceToDevice, st));
     CPB_CUDA(cudaMemcpyAsync(h->d_codes.p, d_codes, n * code_row_bytes(h), cudaMemcpyDeviceToDevice, st));
@@ -828,6 +851,7 @@ int cphnsw_b200_install(cphnsw_b200_index* h, const float* vectors, const void* 
     const size_t rb = code_row_bytes(h);
     CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
     CPB_TRY(h->d_codes.reserve(n * rb + 16));
+    h->codes_released = false;  // the codes are replaced as a whole
     CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
     CPB_CUDA(cudaMemcpy(h->d_vectors.p, vectors, n * h->dim * 4, cudaMemcpyHostToDevice));
     CPB_CUDA(cudaMemcpy(h->d_codes.p, codes, n * rb, cudaMemcpyHostToDevice));
@@ -850,6 +874,7 @@ int cphnsw_b200_get_code(const cphnsw_b200_index* h, uint32_t id, void* code_out
     if (!code_out) { set_error("get_code: null pointer"); return CPHNSW_B200_E_INVALID; }
     if (id >= h->n) { set_error("get_code: node %u does not exist (size %llu)", id, (unsigned long long)h->n); return CPHNSW_B200_E_INVALID; }
     const size_t rb = code_row_bytes(h);
+    if (h->codes_released) return host_codes_from_packed(h, id, 1, static_cast<unsigned char*>(code_out));
     CPB_CUDA(cudaMemcpy(code_out, h->d_codes.as<unsigned char>() + size_t(id) * rb, rb, cudaMemcpyDeviceToHost));
     return 0;
 }
@@ -991,6 +1016,7 @@ int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out
     cphnsw_b200_index* m = const_cast<cphnsw_b200_index*>(h);  // scratch and launch counter only
     const size_t bytes = h->n * ((h->K + 63) / 64) * 8;
     CPB_TRY(m->s_out.reserve(bytes));
+    CPB_TRY(ensure_codes(m, 0));
     CPB_TRY(launch_pack_sign_bits(m, h->d_codes.p, h->n, m->s_out.as<uint64_t>(), 0));
     CPB_CUDA(cudaMemcpy(words_out, m->s_out.p, bytes, cudaMemcpyDeviceToHost));
     return 0;
@@ -1049,7 +1075,13 @@ int cphnsw_b200_save(cphnsw_b200_index* h, const char* path) {
     std::vector<char> buf(size_t(64) << 20);
     if (h->n) {
         CPB_TRY(write_device(fc.f, h->d_vectors.p, h->n * h->dim * 4, buf));
-        CPB_TRY(write_device(fc.f, h->d_codes.p, h->n * code_row_bytes(h), buf));
+        if (h->codes_released) {  // the file keeps one component per bit
+            std::vector<unsigned char> codes(h->n * code_row_bytes(h));
+            CPB_TRY(host_codes_from_packed(h, 0, h->n, codes.data()));
+            if (std::fwrite(codes.data(), 1, codes.size(), fc.f) != codes.size()) { set_error("save: write failed"); return CPHNSW_B200_E_INVALID; }
+        } else {
+            CPB_TRY(write_device(fc.f, h->d_codes.p, h->n * code_row_bytes(h), buf));
+        }
         CPB_TRY(write_device(fc.f, h->d_adj.p, h->n * h->M * 4, buf));
     }
     std::FILE* f = fc.f;
@@ -1115,6 +1147,7 @@ int cphnsw_b200_load(const char* path, int device, cphnsw_b200_index** out) {
         const uint64_t n = hd.n;
         CPB_TRY(h->d_vectors.reserve(n * h->dim * 4));
         CPB_TRY(h->d_codes.reserve(n * code_row_bytes(h) + 16));
+        h->codes_released = false;
         CPB_TRY(h->d_adj.reserve(n * h->M * 4 + 16));
         std::vector<char> buf(size_t(64) << 20);
         CPB_TRY(read_device(fc.f, h->d_vectors.p, n * h->dim * 4, buf));
@@ -1267,6 +1300,7 @@ static int add_batch_parallel_impl(cphnsw_b200_index* h, const float* x, uint64_
     // everything has succeeded: a failure on the way leaves the index as it was
     const uint64_t old_n = h->n, total = h->n + n;
     const size_t rb = code_row_bytes(h);
+    CPB_TRY(ensure_codes(h, 0));
     CPB_TRY(grow_keep(h->d_vectors, old_n * h->dim * 4, total * h->dim * 4));
     CPB_TRY(grow_keep(h->d_codes, old_n * rb, total * rb + 16));
     float* d_new = h->d_vectors.as<float>() + old_n * h->dim;
@@ -1303,6 +1337,7 @@ static int add_batch_impl(cphnsw_b200_index* h, const float* x, uint64_t n) {
     for (uint64_t done = 0; done < n;) {
         const uint64_t n_old = h->n;
         const uint64_t m = n - done < n_old ? n - done : n_old;  // a piece never outnumbers the graph it joins
+        CPB_TRY(ensure_codes(h, st));
         CPB_TRY(grow_keep(h->d_vectors, n_old * h->dim * 4, (n_old + m) * h->dim * 4));
         CPB_TRY(grow_keep(h->d_codes, n_old * rb, (n_old + m) * rb + 16));
         CPB_TRY(grow_keep(h->d_adj, n_old * h->M * 4, (n_old + m) * h->M * 4 + 16));
@@ -1338,6 +1373,7 @@ int cphnsw_b200_get_codes(const cphnsw_b200_index* h, void* codes_out) {
     CPB_TRY(bind(h));
     std::shared_lock<std::shared_mutex> guard(h->rw);
     if (!codes_out) { set_error("get_codes: null pointer"); return CPHNSW_B200_E_INVALID; }
+    if (h->n && h->codes_released) return host_codes_from_packed(h, 0, h->n, static_cast<unsigned char*>(codes_out));
     if (h->n) CPB_CUDA(cudaMemcpy(codes_out, h->d_codes.p, h->n * code_row_bytes(h), cudaMemcpyDeviceToHost));
     return 0;
 }

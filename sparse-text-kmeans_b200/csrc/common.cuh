@@ -156,6 +156,10 @@ struct cphnsw_b200_index {
     // index contents
     uint64_t n = 0;
     cpb::DevBuf d_vectors, d_codes, d_adj, d_entry, d_entry_codes;
+    cpb::DevBuf d_packed;       // binary-code mode: the sign bits of every node packed 32 per word, uint32 [n][packed_words],
+    int packed_words = 0;       // which is what the walk reads (popcount of an XOR); 0 outside that mode
+    bool codes_released = false;  // binary-code mode between build stages: d_codes is freed, the packed bits are the stored
+                                  // code (8 times smaller); stages that need one byte per bit unpack them first
     cpb::DevBuf d_exact_base;  // vectors given to set_exact_base (exact_search / rerank run over them instead of d_vectors)
     uint64_t n_exact = 0;
     uint32_t n_entry = 0;
@@ -250,6 +254,8 @@ void drop_search_scratch(cphnsw_b200_index* h);
 int scan_adjacency_rows(cphnsw_b200_index* h, cudaStream_t st);
 // copies the codes of the entry ids into one contiguous buffer (after d_entry / d_codes change)
 int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st);
+// binary-code mode: d_codes rebuilt from the packed bits if it was released (callers hold the handle exclusively)
+int ensure_codes(cphnsw_b200_index* h, cudaStream_t st);
 
 // Brackets one kernel launch with an event pair when profiling is on (no-ops otherwise).
 struct LaunchTimer {

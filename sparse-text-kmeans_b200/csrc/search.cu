@@ -58,6 +58,8 @@ __global__ void search_kernel(SearchArgs a) {
     const bool coop_ok = !SYM && a.K <= 64;
     const bool two_blocks = a.K > 32;  // a lane owns two rotations in the whole-warp scoring
     const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm + a.qvec_floats);  // symmetric metric only
+    // binary-code mode: the query's sign bits packed 32 per word, behind its code
+    uint32_t* qpacked_sm = reinterpret_cast<uint32_t*>(qsm + a.qvec_floats + ((row_bytes + 15) / 16) * 4);
 
     // queries are handed out one at a time from a global counter, so that warps that draw short
     // walks take more of them
@@ -70,6 +72,14 @@ __global__ void search_kernel(SearchArgs a) {
         if (SYM) {
             const unsigned char* src = static_cast<const unsigned char*>(a.qcodes) + size_t(q) * row_bytes;
             for (int i = lane; i < row_bytes; i += 32) reinterpret_cast<unsigned char*>(qsm + a.qvec_floats)[i] = src[i];
+            if (a.packed) {
+                __syncwarp();
+                for (int w = 0; w < a.packed_words; ++w) {
+                    const int r = 32 * w + lane;
+                    const uint32_t word = __ballot_sync(kFull, r < a.K && (qcode_sm[r * (U16 ? 2 : 1)] & 1u));
+                    if (lane == 0) qpacked_sm[w] = word;
+                }
+            }
         }
         if (TABLE_SMEM && !SYM) {
             const float4* src = reinterpret_cast<const float4*>(table);
@@ -100,7 +110,11 @@ __global__ void search_kernel(SearchArgs a) {
 
         // one lane scores one node (row `row` of `code_base`) under the kernel's metric
         auto score_lane = [&](const void* code_base, uint32_t row) -> float {
-            if (SYM) return sym_distance_lane<U16>(qcode_sm, code_base, row, a.K, a.resid_kp, a.resid_mul);
+            if (SYM) {
+                if (a.packed && code_base == a.codes)  // the walk (the entry scan reads its own contiguous copy of the codes)
+                    return packed_distance_lane(qpacked_sm, a.packed, row, a.packed_words, a.resid_kp, a.resid_mul);
+                return sym_distance_lane<U16>(qcode_sm, code_base, row, a.K, a.resid_kp, a.resid_mul);
+            }
             return asym_distance_lane<U16>(table, code_base, row, a.K, a.P);
         };
         // Admission of (d, id), known to every lane: W stays the wcap best seen so far, sorted
@@ -420,6 +434,7 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
     const size_t qvec = (size_t(h->dim) + 3) & ~size_t(3);
     // under the symmetric metric the query code follows the query vector
     size_t dim_pad = qvec + (sym ? ((size_t(h->K) * h->comp_bytes + 15) / 16) * 4 : 0);
+    if (sym) dim_pad += (((size_t(h->K) + 31) / 32 * 4 + 15) / 16) * 4;  // and its sign bits, packed (binary-code mode)
     c.qvec_floats = qvec;
     size_t per_warp = (c.table_smem ? table_bytes : 0) + size_t(c.cap) * 8 + dim_pad * 4;
     per_warp = (per_warp + 15) & ~size_t(15);
@@ -439,7 +454,64 @@ LaunchCfg pick_cfg(const cphnsw_b200_index* h, uint32_t beam, bool sym) {
 size_t search_team_extra_smem();
 int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st);
 
+// sign bits of every node, 32 per word: bit b of word w = bit 0 of component 32 * w + b (binary-code mode)
+__global__ void pack_walk_codes_kernel(const unsigned char* __restrict__ codes, uint64_t n, int K, int comp_bytes, int words,
+                                       uint32_t* __restrict__ out) {
+    const uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= n * uint64_t(words)) return;
+    const uint64_t node = t / words;
+    const int w = int(t % words);
+    const unsigned char* row = codes + node * uint64_t(K) * comp_bytes;
+    uint32_t bits = 0;
+    for (int b = 0; b < 32 && w * 32 + b < K; ++b)
+        if (row[size_t(w * 32 + b) * comp_bytes] & 1u) bits |= 1u << b;
+    out[t] = bits;
+}
+
+// the inverse: one component (0 or 1) per bit
+__global__ void unpack_walk_codes_kernel(const uint32_t* __restrict__ packed, uint64_t n, int K, int comp_bytes, int words,
+                                         unsigned char* __restrict__ codes) {
+    const uint64_t t = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= n * uint64_t(K)) return;
+    const uint64_t node = t / K;
+    const int r = int(t % K);
+    const uint32_t bit = (packed[node * words + (r >> 5)] >> (r & 31)) & 1u;
+    unsigned char* c = codes + t * comp_bytes;
+    c[0] = (unsigned char)bit;
+    if (comp_bytes == 2) c[1] = 0;
+}
+
+int ensure_codes(cphnsw_b200_index* h, cudaStream_t st) {
+    if (!h->codes_released) return 0;
+    const size_t rb = size_t(h->K) * h->comp_bytes;
+    CPB_TRY(h->d_codes.reserve(size_t(h->n) * rb + 16));
+    const uint64_t total = uint64_t(h->n) * h->K;
+    if (total) {
+        unpack_walk_codes_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(h->d_packed.as<uint32_t>(), h->n, int(h->K),
+                                                                               int(h->comp_bytes), h->packed_words,
+                                                                               h->d_codes.as<unsigned char>());
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+    }
+    h->codes_released = false;
+    return 0;
+}
+
+// after the stored codes or the entry ids change: the contiguous copy of the entry nodes' codes and, in binary-code
+// mode, the packed sign bits the walk reads
 int gather_entry_codes(cphnsw_b200_index* h, cudaStream_t st) {
+    CPB_TRY(ensure_codes(h, st));
+    h->packed_words = 0;
+    if (h->binary_codes && h->n) {
+        const int words = int((h->K + 31) / 32);
+        CPB_TRY(h->d_packed.reserve(size_t(h->n) * words * 4 + 16));
+        const uint64_t total = uint64_t(h->n) * words;
+        pack_walk_codes_kernel<<<unsigned((total + 255) / 256), 256, 0, st>>>(h->d_codes.as<unsigned char>(), h->n, int(h->K),
+                                                                             int(h->comp_bytes), words, h->d_packed.as<uint32_t>());
+        h->launches++;
+        CPB_CUDA(cudaGetLastError());
+        h->packed_words = words;
+    }
     const int row_bytes = int(h->K * h->comp_bytes);
     CPB_TRY(h->d_entry_codes.reserve(size_t(h->n_entry) * row_bytes + 16));
     const uint64_t total = uint64_t(h->n_entry) * row_bytes;
@@ -532,6 +604,8 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
     a.tables = d_tables;
     a.queries = d_q;
     a.codes = h->d_codes.p;
+    a.packed = (sym && h->binary_codes && h->packed_words) ? h->d_packed.as<uint32_t>() : nullptr;
+    a.packed_words = h->packed_words;
     a.adj = h->d_adj.as<uint32_t>();
     a.vectors = h->d_vectors.as<float>();
     a.entry = h->d_entry.as<uint32_t>();

@@ -20,6 +20,8 @@ struct SearchArgs {
     const void* qcodes;    // [nq][K] query codes (symmetric metric)
     const float* queries;  // [nq][dim] (rerank only)
     const void* codes;     // [n][K] components
+    const uint32_t* packed;  // binary-code mode: [n][packed_words] sign bits, 32 per word (else nullptr)
+    int packed_words;
     const uint32_t* adj;   // [n][M]
     const float* vectors;  // [n][dim] (rerank only)
     const uint32_t* entry;     // ids scored for every query before the walk
@@ -143,6 +145,24 @@ __device__ __forceinline__ float sym_distance_lane(const unsigned char* qcode, c
     } else {
         for (int r = 0; r < K; ++r)
             d += (load_component<U16>(row, r) != load_component<U16>(qcode, r)) ? (r < kp ? 1 + mul : 1) : 0;
+    }
+    return float(d);
+}
+
+// The same distance on sign bits packed 32 per word (binary-code mode): the Hamming distance is the popcount of the
+// XOR; with residual codes the first kp bits are primary and count 1 + mul.  q holds the query's packed code.
+__device__ __forceinline__ float packed_distance_lane(const uint32_t* q, const uint32_t* packed, uint32_t row_index, int words,
+                                                      int kp, int mul) {
+    const uint32_t* x = packed + size_t(row_index) * words;
+    uint32_t d = 0;
+    for (int w = 0; w < words; ++w) {
+        const uint32_t v = q[w] ^ __ldg(x + w);
+        d += __popc(v);
+        if (mul) {
+            const int lo = kp - 32 * w;  // primary bits in this word
+            const uint32_t pm = lo >= 32 ? 0xffffffffu : (lo > 0 ? (1u << lo) - 1u : 0u);
+            d += uint32_t(mul) * __popc(v & pm);
+        }
     }
     return float(d);
 }

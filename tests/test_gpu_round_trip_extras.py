@@ -326,3 +326,42 @@ def test_beams_wider_than_1024_match_oracle(cp, oracle, kernel, K):
     assert np.allclose(dist, wd, rtol=1e-5, atol=1e-6) and (ids == wi).mean() > 0.99
     with pytest.raises(ValueError):
         idx.search_batch(q, 10, 4097)
+
+
+def test_binary_mode_stores_packed_sign_bits(cp, oracle, tmp_path):
+    """Binary-code mode keeps a node's code as packed sign bits between build stages (8 times smaller than one byte per
+    bit); accessors, insertion, the index file and the walk give what the byte form gave."""
+    n, dim, K, M = 5000, 128, 64, 16
+    base, q = synthetic.gaussian_mixture(n + 700, 40, dim, 10, 0.3, 5)
+    plain = make_index(cp, dim, 32, 1, M)
+    plain.add_batch_parallel(base[:n])
+    assert plain.get_param("stored_code_bytes") == 32            # full components: one byte each
+    idx = cp.CPHNSWIndex.binary(dim, K=K, M=M)
+    idx.set_param("entry_scan", 64)
+    idx.set_param("k_entry", 8)
+    idx.add_batch_parallel(base[:n])
+    assert idx.get_param("stored_code_bytes") == K // 8         # 64 sign bits in two words
+    signs = oracle.sign_tables(dim, K, 42)
+    want = oracle.encode(base[:n + 700], K, 1, signs, 2) & 1
+    codes = idx.codes()
+    assert codes.shape == (n, K) and np.array_equal(codes, want[:n])
+    assert np.array_equal(idx.get_code(4321), want[4321])
+    assert np.array_equal(idx.binary_codes()[:, 0], oracle.pack_sign_bits(want[:n]))
+    ids0, d0, st0 = idx.search_batch(q, 10, 100, want_stats=True)
+    wi, wd = oracle.search_codes(oracle.encode(q, K, 1, signs, 2) & 1, want[:n], idx.adjacency(), idx.entry_ids(), 100, 10, n_seed=8)
+    assert np.array_equal(ids0, wi) and np.array_equal(d0, wd)
+    path = str(tmp_path / "binary.cph")
+    idx.save(path)
+    back = cp.CPHNSWIndex.load(path)
+    assert back.get_param("stored_code_bytes") == K // 8
+    assert np.array_equal(back.codes(), codes)
+    ids1, d1, st1 = back.search_batch(q, 10, 100, want_stats=True)
+    assert np.array_equal(ids1, ids0) and np.array_equal(d1, d0) and np.array_equal(st1, st0)
+    # insertion unpacks, extends and packs again
+    idx.add_batch(base[n:])
+    back.add_batch(base[n:])
+    assert idx.size() == n + 700 and idx.get_param("stored_code_bytes") == K // 8
+    assert np.array_equal(idx.codes(), want) and np.array_equal(idx.adjacency(), back.adjacency())
+    a = idx.search_and_rerank_batch(q, 10, 100, 300)
+    b = back.search_and_rerank_batch(q, 10, 100, 300)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
