@@ -238,7 +238,8 @@ __global__ void search_kernel(SearchArgs a) {
                 const uint32_t e = e0 + lane;
                 if (e + 32 < a.n_entry) {  // pull the next batch towards L1 while this one is scored
                     if (a.entry) prefetch_l1(a.entry + e + 32);
-                    prefetch_l1(static_cast<const unsigned char*>(a.entry_codes) + size_t(e + 32) * row_bytes);
+                    if (a.entry_codes)  // (null for a brute-force scan in binary-code mode, which reads the packed bits)
+                        prefetch_l1(static_cast<const unsigned char*>(a.entry_codes) + size_t(e + 32) * row_bytes);
                 }
                 const uint32_t id = e < a.n_entry ? (a.entry ? __ldg(a.entry + e) : e) : kInvalidNode;
                 const bool ok = id < a.n;
@@ -650,9 +651,11 @@ int launch_search(cphnsw_b200_index* h, SearchCtx& cx, const float* d_q, const f
     LaunchTimer timer(h, kKernelSearch, st);
 
     // two warps per query: asymmetric metric, table in shared memory, one adjacency row per warp
-    // (beams over 1,024 up to 2,048 in its wide form, which exists for tables in shared memory)
-    const bool team_ok = (beam <= 1024 || (beam <= 2048 && c.table_smem)) && !sym && !scan_only && (c.table_smem || h->K <= 32) &&
-                         h->M <= 32 && h->k_entry <= 128;
+    // (beams over 1,024 up to 2,048 in its wide form, which exists for tables in shared memory; under the symmetric
+    // metric only on packed sign bits, i.e. in binary-code mode)
+    const bool team_ok = !scan_only && h->M <= 32 && h->k_entry <= 128 &&
+                         (sym ? (a.packed != nullptr && beam <= 1024)
+                              : ((beam <= 1024 || (beam <= 2048 && c.table_smem)) && (c.table_smem || h->K <= 32)));
     a.table_in_smem = c.table_smem ? 1 : 0;
     if (h->search_kernel == 2 && !team_ok && !sym) {
         set_error("search_kernel=2 needs the asymmetric metric, M <= 32, K*P*4 <= 32 KB or K <= 32, and a beam of at most 1024 (2048 with the table in shared memory)");

@@ -321,7 +321,7 @@ __device__ __forceinline__ void tier_from_plain(TierList& T, int lane) {
 // shared-memory loads); otherwise it is read in place.
 // No register cap: holding the kernel to 64 registers (15 teams per SM instead of 11 when the table is read in
 // place) spills inside the walk and was measured slower on every configuration.
-template <bool U16, bool TSM, bool K2, bool WIDE>
+template <bool U16, bool TSM, bool K2, bool WIDE, bool SYM>
 __global__ void search_team_kernel(SearchArgs a) {
     extern __shared__ __align__(16) unsigned char team_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -353,7 +353,11 @@ __global__ void search_team_kernel(SearchArgs a) {
     const uint32_t beam = a.beam;
     const bool scan_mode = a.n_seed < a.n_entry;
     const int row_bytes = a.K * (U16 ? 2 : 1);
-    const bool coop_ok = a.K <= 64;
+    const bool coop_ok = !SYM && a.K <= 64;
+    // symmetric metric (binary-code mode): the query's code follows its vector in the team's query area, its packed sign
+    // bits follow the code; the walk compares packed bits, the entry scan the contiguous byte copy of the entry codes
+    const unsigned char* qcode_sm = reinterpret_cast<const unsigned char*>(qsm + a.qvec_floats);
+    uint32_t* qpacked_sm = reinterpret_cast<uint32_t*>(qsm + a.qvec_floats + ((row_bytes + 15) / 16) * 4);
     constexpr bool two_blocks = K2;  // 32 < K <= 64: a lane owns two rotations in the whole-warp scoring (a compile-time
                                      // fact, so that the narrower codes pay nothing for it)
 
@@ -363,7 +367,15 @@ __global__ void search_team_kernel(SearchArgs a) {
         const uint32_t q = mail[0];
         if (q >= a.nq) break;
         // a table too large for shared memory is read in place (through L1 / L2)
-        const float* table = TSM ? table_sm : a.tables + size_t(q) * table_floats;
+        const float* table = SYM ? nullptr : (TSM ? table_sm : a.tables + size_t(q) * table_floats);
+        // one lane scores one node (row `row` of `code_base`) under the kernel's metric
+        auto score_lane = [&](const void* code_base, uint32_t row) -> float {
+            if (SYM) {
+                if (code_base == a.codes) return packed_distance_lane(qpacked_sm, a.packed, row, a.packed_words, a.resid_kp, a.resid_mul);
+                return sym_distance_lane<U16>(qcode_sm, code_base, row, a.K, a.resid_kp, a.resid_mul);
+            }
+            return asym_distance_lane<U16>(table, code_base, row, a.K, a.P);
+        };
         {   // set-up by all 64 lanes
             if (TSM) {
                 const float4* src = reinterpret_cast<const float4*>(a.tables + size_t(q) * table_floats);
@@ -372,7 +384,18 @@ __global__ void search_team_kernel(SearchArgs a) {
             }
             if (a.rerank_k) {
                 const float* qv = a.queries + size_t(q) * a.dim;
-                for (int i = tl; i < int(dim_pad); i += 64) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
+                for (int i = tl; i < int(SYM ? a.qvec_floats : dim_pad); i += 64) qsm[i] = i < a.dim ? __ldg(qv + i) : 0.0f;
+            }
+            if (SYM) {
+                const unsigned char* src = static_cast<const unsigned char*>(a.qcodes) + size_t(q) * row_bytes;
+                for (int i = tl; i < row_bytes; i += 64) reinterpret_cast<unsigned char*>(qsm + a.qvec_floats)[i] = src[i];
+                if (role == 0) {  // the packed bits straight from the code in global memory (one warp: the vote is its own)
+                    for (int w = 0; w < a.packed_words; ++w) {
+                        const int r = 32 * w + lane;
+                        const uint32_t word = __ballot_sync(kFull, r < a.K && (src[r * (U16 ? 2 : 1)] & 1u));
+                        if (lane == 0) qpacked_sm[w] = word;
+                    }
+                }
             }
             for (int p = tl; p < cap; p += 64) {
                 sd[p] = INFINITY;
@@ -483,7 +506,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                                              : asym_distance_coop(table, a.K, a.P, comp[f], lane), cid[f]);
             } else {
                 float dist = 0.0f;
-                if (fresh) dist = asym_distance_lane<U16>(table, a.codes, id, a.K, a.P);
+                if (fresh) dist = score_lane(a.codes, id);
                 admit_lanes(m, fresh, dist, id);
             }
         };
@@ -506,7 +529,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                 const uint32_t id = e < a.n_entry ? __ldg(a.entry + e) : kInvalidNode;
                 const bool ok = id < a.n;
                 float dist = 0.0f;
-                if (ok) dist = asym_distance_lane<U16>(table, a.entry_codes, e, a.K, a.P);
+                if (ok) dist = score_lane(a.entry_codes, e);
                 const uint32_t m = __ballot_sync(kFull, ok);
                 nevals += __popc(m);
                 if (role == 0) tier_admit_lanes<WIDE>(T, m, ok, dist, id, lane);
@@ -795,7 +818,7 @@ __global__ void search_team_kernel(SearchArgs a) {
                             if (lane == s1) dist = d1;
                         }
                     } else if (cand) {
-                        dist = asym_distance_lane<U16>(table, a.codes, u_id, a.K, a.P);
+                        dist = score_lane(a.codes, u_id);
                     }
                     if (s >= 0) {
                         res_id[s * 32 + lane] = u_id;
@@ -811,7 +834,8 @@ __global__ void search_team_kernel(SearchArgs a) {
                 if (do_v) {  // visited bytes and codes of the next row towards L2
                     if (v_id < a.n && held_key != P1) {
                         prefetch_l2(vis + v_id);
-                        prefetch_l2(static_cast<const unsigned char*>(a.codes) + size_t(v_id) * row_bytes);
+                        if (SYM) prefetch_l2(a.packed + size_t(v_id) * a.packed_words);  // (the byte codes are not resident)
+                        else prefetch_l2(static_cast<const unsigned char*>(a.codes) + size_t(v_id) * row_bytes);
                     }
                     held_key = P1;
                     held_id = v_id;
@@ -913,9 +937,9 @@ size_t search_team_extra_smem() { return size_t(kSeedCap) * 8 + kRing * 4 + kMai
 
 // Teams per block: as many as shared memory allows (at most 15, one named barrier each), fewer if
 // the register file does not hold them.
-template <bool U16, bool TSM, bool K2, bool WIDE>
+template <bool U16, bool TSM, bool K2, bool WIDE, bool SYM>
 static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
-    auto kernel = search_team_kernel<U16, TSM, K2, WIDE>;
+    auto kernel = search_team_kernel<U16, TSM, K2, WIDE, SYM>;
     int teams = int((226 * 1024) / per_team);
     if (teams > 15) teams = 15;
     if (narrow_blocks) teams = 1;  // one query per block
@@ -936,7 +960,10 @@ static int launch_team_t(cphnsw_b200_index* h, SearchArgs a, size_t per_team, in
 int launch_search_team(cphnsw_b200_index* h, SearchArgs a, size_t per_team, int narrow_blocks, cudaStream_t st) {
     a.per_warp_smem = uint32_t(per_team);
     const bool u16 = h->comp_bytes == 2, k2 = h->K > 32, wide = a.cap > 1024;
-#define CPB_TEAM(U, T, W, X) launch_team_t<U, T, W, X>(h, a, per_team, narrow_blocks, st)
+#define CPB_TEAM(U, T, W, X) launch_team_t<U, T, W, X, false>(h, a, per_team, narrow_blocks, st)
+    // binary-code mode: symmetric metric on packed sign bits, no query table
+    if (a.packed) return u16 ? launch_team_t<true, false, false, false, true>(h, a, per_team, narrow_blocks, st)
+                             : launch_team_t<false, false, false, false, true>(h, a, per_team, narrow_blocks, st);
     if (a.table_in_smem) {
         if (wide) {  // beams over 1,024: 64 buckets, two per lane
             if (k2) return u16 ? CPB_TEAM(true, true, true, true) : CPB_TEAM(false, true, true, true);
