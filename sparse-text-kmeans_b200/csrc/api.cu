@@ -1015,8 +1015,20 @@ int cphnsw_b200_get_binary_codes(const cphnsw_b200_index* h, uint64_t* words_out
     if (h->n == 0) return 0;
     cphnsw_b200_index* m = const_cast<cphnsw_b200_index*>(h);  // scratch and launch counter only
     const size_t bytes = h->n * ((h->K + 63) / 64) * 8;
+    if (h->codes_released) {
+        // the stored code is the packed bits already, 32 per word: two words make one of the output's
+        const size_t pw = size_t(h->packed_words), nw = (h->K + 63) / 64;
+        std::vector<uint32_t> w(h->n * pw);
+        CPB_CUDA(cudaMemcpy(w.data(), h->d_packed.p, w.size() * 4, cudaMemcpyDeviceToHost));
+        for (uint64_t i = 0; i < h->n; ++i)
+            for (size_t j = 0; j < nw; ++j) {
+                const uint64_t lo = w[i * pw + 2 * j];
+                const uint64_t hi = 2 * j + 1 < pw ? w[i * pw + 2 * j + 1] : 0;
+                words_out[i * nw + j] = lo | (hi << 32);
+            }
+        return 0;
+    }
     CPB_TRY(m->s_out.reserve(bytes));
-    CPB_TRY(ensure_codes(m, 0));
     CPB_TRY(launch_pack_sign_bits(m, h->d_codes.p, h->n, m->s_out.as<uint64_t>(), 0));
     CPB_CUDA(cudaMemcpy(words_out, m->s_out.p, bytes, cudaMemcpyDeviceToHost));
     return 0;
