@@ -615,14 +615,18 @@ def run_b200(args):
                    "frac": build["encode_fp32_addsub_per_s"] / lanes,
                    "note": "K*3*P*log2(P) butterflies per vector over the measured stage time; peak = GPUs x SMs x 128 lanes x sampled SM clock"},
         "knn_graph": None, "select_neighbors": None}
-    if K == 32 and cb == 1:
-        # bit-sliced kernel: 330 integer instructions per (row, 32 candidates) = 10.3 per pair on the ALU pipe, which
-        # issues 64 lanes per SM and clock
+    planes = 8 if cb == 1 else (11 if idx.padded_dim == 1024 else 0)  # bit planes of a component in the bit-sliced kernel
+    if K == 32 and planes:
+        # bit-sliced kernel: one logic instruction per bit plane and rotation (256 at 8 planes, 352 at 11), 62 for the
+        # carry-save sum and ~12 for the threshold compare per (row, 32 candidates): 330 = 10.3 per pair (one-byte
+        # components), 426 = 13.3 per pair (two-byte components of padded dim 1024), on the ALU pipe, which issues 64
+        # lanes per SM and clock
+        per_group = planes * K + 62 + 12
         alu = world * idx_sm_count * 64 * sm_mhz * 1e6
-        roofline_build["knn_graph"] = {"bound": "integer ALU pipe", "achieved": build["knn_pairs_per_s"] * 330.0 / 32.0, "peak": alu,
-                                       "unit": "instr/s", "frac": build["knn_pairs_per_s"] * 330.0 / 32.0 / alu,
-                                       "note": "10.3 integer instructions per pair (kernel source count); ncu sm__pipe_alu_cycles_active "
-                                               "67.5 % on C2 at 1/4 size (profiles/knn_sliced_kernel_c2_quarter.md)"}
+        roofline_build["knn_graph"] = {"bound": "integer ALU pipe", "achieved": build["knn_pairs_per_s"] * per_group / 32.0, "peak": alu,
+                                       "unit": "instr/s", "frac": build["knn_pairs_per_s"] * per_group / 32.0 / alu,
+                                       "note": "%.1f integer instructions per pair (kernel source count); ncu sm__pipe_alu_cycles_active "
+                                               "67.5 %% on C2 at 1/4 size (profiles/knn_sliced_kernel_c2_quarter.md)" % (per_group / 32.0)}
     sel_bytes = n * (knn_k * 4 + knn_k * code_row + M * 4.0)
     roofline_build["select_neighbors"] = {"bound": "hbm gather", "achieved": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9, "peak": peak * world,
                                           "unit": "GB/s", "frac": sel_bytes / (stage_ms["select_neighbors"] * 1e-3) / 1e9 / (peak * world),
