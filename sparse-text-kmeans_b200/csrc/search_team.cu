@@ -20,16 +20,19 @@
 // W is a tiered vector: buckets of 32 slots, each a circular buffer, globally sorted.  An
 // admission shifts inside one bucket (one load, two shuffles and one store per lane) and every
 // later bucket takes the element pushed out of its predecessor at its front in place of its
-// own last, all buckets at once (one lane per bucket).
+// own last, all buckets at once (one lane per bucket).  While W still has room it is a plain array instead: every
+// scored candidate is admitted then, so a row's candidates are appended, the closest unexpanded member is found by a
+// scan, and the array is sorted once, when a row would overflow it or rows stop bringing more than a member or two.
 //
 // The two warps meet at a named barrier (bar.sync id, 64) once per expansion; every barrier sits
 // in control flow that depends only on values both warps read after the previous barrier, so the
 // two warps always execute the same sequence of barriers and nothing spins.  The entry scan and
 // the rerank are split between the two warps.
 //
-// Used for the asymmetric metric with M <= 32; the query table sits in shared memory when it is at
-// most 32 KB and is read in place (global memory, through L1 / L2) otherwise.  Beams up to 1,024 take 32 buckets,
-// one per lane; beams up to 2,048 the wide form with 64 buckets, two per lane.
+// Used with M <= 32.  Asymmetric metric: the query table sits in shared memory when it is at most 32 KB and is read in
+// place (global memory, through L1 / L2) otherwise; codes of up to 64 rotations are scored by the whole warp.
+// Symmetric metric: binary-code mode only, on sign bits packed 32 per word (XOR and popcount, no table).  Beams up to
+// 1,024 take 32 buckets, one per lane; beams up to 2,048 the wide form with 64 buckets, two per lane.
 #include "search_common.cuh"
 
 namespace cpb {
